@@ -1,0 +1,378 @@
+"""Decoder building blocks: GQA attention, MLA, dense gated MLP, routed MoE.
+
+Parameter names, reference shapes and logical axes follow MaxText so that checkpoints and sharding
+rules carry over (attention kernels src/maxtext/layers/attentions.py:660-830, MLP
+src/maxtext/layers/linears.py:422-625, MoE src/maxtext/layers/moe.py:395-615, MLA
+src/maxtext/layers/attention_mla.py:785-1115). Storage is `[out, in]` per matrix; q|k|v and
+wi_0|wi_1 are adjacent in the unit's flat buffer and are consumed as single fused GEMM operands.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import reference as ref
+from ..parallel.param_store import Param, ParamDef, ALIGN
+
+
+# ------------------------------------------------------------------------------------------ param helpers
+class Builder:
+  """Collects ParamDefs for one unit while layers are constructed."""
+
+  def __init__(self, config, unit: str, layer: int | None, stack: str | None, tp_size=1, tp_rank=0, ep_size=1, ep_rank=0,
+               prefix: tuple = ()):
+    self.config, self.unit, self.layer, self.stack = config, unit, layer, stack
+    self.tp_size, self.tp_rank, self.ep_size, self.ep_rank = tp_size, tp_rank, ep_size, ep_rank
+    self.prefix = tuple(prefix)
+    self.params: list[Param] = []
+
+  def sub(self, *names) -> "Builder":
+    b = Builder(self.config, self.unit, self.layer, self.stack, self.tp_size, self.tp_rank, self.ep_size, self.ep_rank,
+                self.prefix + tuple(names))
+    b.params = self.params
+    return b
+
+  def _add(self, leaf: str, **kw) -> Param:
+    path = self.prefix + (leaf,)
+    name = "/".join(((f"{self.stack}_{self.layer}",) if self.layer is not None else ()) + path)
+    p = Param(ParamDef(name=name, unit=self.unit, ref_path=path, layer=self.layer, stack=self.stack, **kw))
+    self.params.append(p)
+    return p
+
+  def linear(self, leaf, in_shape, out_shape, axes, init="fan_in_trunc", init_scale=1.0, tp: str | None = None) -> Param:
+    """Matrix with reference layout [in..., out...]; internal [prod(out), prod(in)].
+    tp = "col" splits the first out dim, "row" the first in dim over the tensor-parallel group."""
+    in_shape, out_shape = tuple(in_shape), tuple(out_shape)
+    n_in, n_out = int(math.prod(in_shape)), int(math.prod(out_shape))
+    lo, li = n_out, n_in
+    tp_dim = None
+    if tp == "col" and self.tp_size > 1:
+      assert out_shape[0] % self.tp_size == 0, f"{leaf}: {out_shape} not divisible by tp {self.tp_size}"
+      lo, tp_dim = n_out // self.tp_size, 0
+    elif tp == "row" and self.tp_size > 1:
+      assert in_shape[0] % self.tp_size == 0
+      li, tp_dim = n_in // self.tp_size, 1
+    return self._add(leaf, shape=(lo, li), ref_shape=in_shape + out_shape, logical_axes=tuple(axes), kind="linear",
+                     n_in_dims=len(in_shape), init=init, init_scale=init_scale, tp_dim=tp_dim)
+
+  def vector(self, leaf, n, axes=("norm",), init="ones", tp=False) -> Param:
+    ln = n // self.tp_size if tp and self.tp_size > 1 else n
+    return self._add(leaf, shape=(ln,), ref_shape=(n,), logical_axes=tuple(axes), kind="same", init=init,
+                     tp_dim=0 if (tp and self.tp_size > 1) else None)
+
+  def table(self, leaf, shape, axes, init="embed") -> Param:
+    return self._add(leaf, shape=tuple(shape), ref_shape=tuple(shape), logical_axes=tuple(axes), kind="same", init=init)
+
+  def experts(self, leaf, num_experts, d_in, d_out, axes, tp: str | None = None) -> Param:
+    """Expert weights, reference [E, in, out]; internal [E_local, out, in]."""
+    assert num_experts % self.ep_size == 0
+    el = num_experts // self.ep_size
+    lo, li = d_out, d_in
+    if tp == "col" and self.tp_size > 1:
+      lo = d_out // self.tp_size
+    elif tp == "row" and self.tp_size > 1:
+      li = d_in // self.tp_size
+    return self._add(leaf, shape=(el, lo, li), ref_shape=(num_experts, d_in, d_out), logical_axes=tuple(axes),
+                     kind="expert_linear", init="fan_in_trunc", ep_dim=0 if self.ep_size > 1 else None,
+                     tp_dim=(1 if tp == "col" else 2) if (tp and self.tp_size > 1) else None)
+
+
+class FusedParam:
+  """Several parameters that sit back to back in the flat unit buffer, seen as one [sum(out), in] matrix."""
+
+  def __init__(self, parts: list[Param]):
+    self.parts = parts
+    self.rows = [p.shape[0] for p in parts]
+
+  @staticmethod
+  def possible(parts: list[Param]) -> bool:
+    cols = parts[0].shape[-1]
+    return all(len(p.shape) == 2 and p.shape[1] == cols and p.pdef.numel % ALIGN == 0 for p in parts)
+
+  def _span(self, attr):
+    first = getattr(self.parts[0], attr)
+    if first is None:
+      return None
+    total = sum(self.rows)
+    cols = self.parts[0].shape[1]
+    # verify adjacency (cheap pointer arithmetic)
+    ptr, esz = first.data_ptr(), first.element_size()
+    for p, r in zip(self.parts, self.rows):
+      t = getattr(p, attr)
+      if t is None or t.data_ptr() != ptr:
+        return None
+      ptr += r * cols * esz
+    return torch.as_strided(first, (total, cols), (cols, 1))
+
+  @property
+  def data(self):
+    return self._span("data")
+
+  @property
+  def main_grad(self):
+    return self._span("main_grad")
+
+  @property
+  def grad_written(self):
+    return all(p.grad_written for p in self.parts)
+
+  @grad_written.setter
+  def grad_written(self, v):
+    for p in self.parts:
+      p.grad_written = v
+
+  @property
+  def shape(self):
+    return (sum(self.rows), self.parts[0].shape[1])
+
+
+# ------------------------------------------------------------------------------------------ tensor-parallel glue
+class _CopyToTP(torch.autograd.Function):
+  """Identity forward, all-reduce backward (input of a column-parallel linear)."""
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    return x
+
+  @staticmethod
+  def backward(ctx, dy):
+    dy = dy.contiguous()
+    dist.all_reduce(dy, group=ctx.group)
+    return dy, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+  """All-reduce forward, identity backward (output of a row-parallel linear)."""
+  @staticmethod
+  def forward(ctx, x, group):
+    x = x.contiguous()
+    dist.all_reduce(x, group=group)
+    return x
+
+  @staticmethod
+  def backward(ctx, dy):
+    return dy, None
+
+
+def tp_enter(x, ctx):
+  return _CopyToTP.apply(x, ctx.tp_group) if ctx.tp_size > 1 and torch.is_grad_enabled() else x
+
+
+def tp_exit(x, ctx):
+  if ctx.tp_size <= 1:
+    return x
+  if torch.is_grad_enabled():
+    return _ReduceFromTP.apply(x, ctx.tp_group)
+  x = x.contiguous()
+  dist.all_reduce(x, group=ctx.tp_group)
+  return x
+
+
+# ------------------------------------------------------------------------------------------ norms
+class Norm:
+  def __init__(self, b: Builder, name: str, dim: int, eps: float, offset: float = 0.0, with_scale: bool = True,
+               kind: str = "rms", axes=("norm",)):
+    self.eps, self.offset, self.kind = eps, offset, kind
+    nb = b.sub(name)
+    self.scale = nb.vector("scale", dim, axes) if with_scale else None
+    self.bias = nb.vector("bias", dim, axes, init="zeros") if kind == "layernorm" else None
+
+  def __call__(self, x):
+    if self.kind == "layernorm":
+      return ref.layernorm(x, self.scale.leaf(), self.bias.leaf(), self.eps)
+    return F.rmsnorm(x, self.scale, self.eps, self.offset)
+
+
+# ------------------------------------------------------------------------------------------ attention (MHA / GQA / MQA)
+class Attention:
+  """Multi/grouped-query attention with RoPE; the 1/sqrt(head_dim) factor lives in the query weights
+  (src/maxtext/layers/attentions.py:663-677) unless QK-norm or an explicit query scalar is used."""
+
+  def __init__(self, b: Builder, config, name="self_attention", window: int = 0, rope_inv_ts=None, interleaved=False,
+               use_rope=True, qk_norm=False, query_scalar: float | None = None, soft_cap: float = 0.0, bias=False,
+               rotary_dim=None, sinks=False):
+    c = config
+    self.config = c
+    self.hq, self.hkv, self.dh, self.d = c.num_query_heads, c.num_kv_heads, c.head_dim, c.emb_dim
+    tp = b.tp_size
+    self.hq_l = self.hq // tp
+    self.hkv_l = max(1, self.hkv // tp) if self.hkv >= tp else self.hkv
+    self.window, self.inv_ts, self.interleaved, self.use_rope = window, rope_inv_ts, interleaved, use_rope
+    self.qk_norm, self.query_scalar, self.soft_cap, self.rotary_dim = qk_norm, query_scalar, soft_cap, rotary_dim
+    ab = b.sub(name)
+    depth_scale = 1.0 if (qk_norm or (query_scalar is not None and query_scalar != 1.0)) else 1.0 / math.sqrt(self.dh)
+    kv_tp = "col" if self.hkv >= tp else None
+    self.q = ab.sub("query").linear("kernel", (self.d,), (self.hq, self.dh), ("embed", "q_heads", "kv"), "fan_in_normal",
+                                    depth_scale, tp="col")
+    self.k = ab.sub("key").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
+                                  "fan_in_normal", tp=kv_tp)
+    self.v = ab.sub("value").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
+                                    "fan_in_normal", tp=kv_tp)
+    self.o = ab.sub("out").linear("kernel", (self.hq, self.dh), (self.d,), ("heads", "kv", "embed"), "fan_in_normal",
+                                  tp="row")
+    self.qkv = FusedParam([self.q, self.k, self.v]) if FusedParam.possible([self.q, self.k, self.v]) else None
+    self.bq = self.bk = self.bv = None
+    if bias:
+      self.bq = ab.sub("query").vector("bias", self.hq * self.dh, ("q_heads",), init="zeros", tp=True)
+      self.bk = ab.sub("key").vector("bias", self.hkv * self.dh, ("kv_heads",), init="zeros", tp=kv_tp is not None)
+      self.bv = ab.sub("value").vector("bias", self.hkv * self.dh, ("kv_heads",), init="zeros", tp=kv_tp is not None)
+    self.qn = self.kn = None
+    if qk_norm:
+      self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
+      self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
+    self.sinks = ab.vector("sinks", self.hq, ("q_heads",), init="zeros", tp=True) if sinks else None
+
+  def _project(self, x, ctx):
+    B, S, _ = x.shape
+    hq, hkv, dh = self.hq_l, self.hkv_l, self.dh
+    fused = self.qkv.data if (self.qkv is not None and self.bq is None) else None
+    if fused is not None:
+      saved = ctx.reuse("qkv_proj")
+      qkv = F.linear(x, self.qkv, saved_out=saved)
+      ctx.keep("qkv_proj", qkv)
+      return qkv.view(B, S, hq + 2 * hkv, dh), None
+    q = ctx.keep("query_proj", F.linear(x, self.q, ctx.reuse("query_proj"), self.bq))
+    k = ctx.keep("key_proj", F.linear(x, self.k, ctx.reuse("key_proj"), self.bk))
+    v = ctx.keep("value_proj", F.linear(x, self.v, ctx.reuse("value_proj"), self.bv))
+    return None, (q.view(B, S, hq, dh), k.view(B, S, hkv, dh), v.view(B, S, hkv, dh))
+
+  def __call__(self, x, ctx):
+    B, S, _ = x.shape
+    x = tp_enter(x, ctx)
+    packed, sep = self._project(x, ctx)
+    plain = not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None
+    saved_ctx = ctx.reuse("context")
+    if saved_ctx is not None and packed is not None and plain:
+      # attention output kept by the remat policy: only the backward of the packed op is needed
+      out = F.packed_attention(packed, ctx.positions, ctx.segment_ids, self.inv_ts, self.hq_l, self.hkv_l, self.interleaved,
+                               1.0, self.soft_cap, self.window, self.use_rope)
+    elif packed is not None and plain:
+      out = F.packed_attention(packed, ctx.positions, ctx.segment_ids, self.inv_ts, self.hq_l, self.hkv_l, self.interleaved,
+                               1.0, self.soft_cap, self.window, self.use_rope)
+    else:
+      if sep is None:
+        q, k, v = packed[:, :, :self.hq_l], packed[:, :, self.hq_l:self.hq_l + self.hkv_l], packed[:, :, self.hq_l + self.hkv_l:]
+      else:
+        q, k, v = sep
+      if self.qk_norm:
+        q, k = self.qn(q), self.kn(k)
+      if self.use_rope:
+        q = F.rope(q, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
+        k = F.rope(k, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
+      if self.query_scalar and self.query_scalar != 1.0:
+        q = q * self.query_scalar
+      if ctx.cache is not None:
+        out = ctx.cache.attend(q, k, v, ctx, window=self.window, soft_cap=self.soft_cap, sinks=self.sinks)
+      elif self.sinks is not None:
+        m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window)
+        out = ref.attention(q, k, v, m, 1.0, self.soft_cap, sinks=self.sinks.leaf())
+      else:
+        out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window)
+    ctx.keep("context", out)
+    y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"))
+    y = tp_exit(y, ctx)
+    ctx.keep("out_proj", y)
+    return y
+
+
+# ------------------------------------------------------------------------------------------ MLA
+class MLA:
+  """DeepSeek multi-head latent attention (src/maxtext/layers/attention_mla.py:785-1115).
+
+  q = query(x) (or wq_b(q_norm(wq_a(x)))), split [nope | rope]; wkv_a(x) -> [kv_lora | k_rope];
+  kv_norm on the latent; wkv_b -> per head [k_nope | v]; the single RoPE'd k_rope head is broadcast to
+  all heads. Softmax scale (incl. YaRN mscale) multiplies the query at runtime."""
+
+  def __init__(self, b: Builder, config, rope_inv_ts, interleaved, name="self_attention"):
+    c = config
+    self.c = c
+    self.h = c.num_query_heads // b.tp_size
+    self.nope, self.rope_d, self.vd = c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
+    self.qk = self.nope + self.rope_d
+    self.inv_ts, self.interleaved = rope_inv_ts, interleaved
+    ab = b.sub(name)
+    d = c.emb_dim
+    if c.q_lora_rank > 0:
+      self.wq_a = ab.sub("wq_a").linear("kernel", (d,), (c.q_lora_rank,), ("embed", "q_lora"))
+      self.q_norm = Norm(ab, "q_norm", c.q_lora_rank, c.normalization_layer_epsilon)
+      self.wq_b = ab.sub("wq_b").linear("kernel", (c.q_lora_rank,), (c.num_query_heads, self.qk),
+                                        ("q_lora", "q_heads", "kv"), tp="col")
+      self.query = None
+    else:
+      self.query = ab.sub("query").linear("kernel", (d,), (c.num_query_heads, self.qk), ("embed", "q_heads", "kv"), tp="col")
+    self.wkv_a = ab.sub("wkv_a").linear("kernel", (d,), (c.kv_lora_rank + self.rope_d,), ("embed", "kv_lora"))
+    self.kv_norm = Norm(ab, "kv_norm", c.kv_lora_rank, c.normalization_layer_epsilon)
+    self.wkv_b = ab.sub("wkv_b").linear("kernel", (c.kv_lora_rank,), (c.num_query_heads, self.nope + self.vd),
+                                        ("kv_lora", "kv_heads", "kv_head_dim"), tp="col")
+    self.o = ab.sub("out").linear("kernel", (c.num_query_heads, self.vd), (d,), ("heads", "kv", "embed"), tp="row")
+    scale = self.qk ** -0.5
+    if c.max_position_embeddings > c.original_max_position_embeddings and c.rope_type == "yarn":
+      m = 0.1 * c.mscale * math.log(c.rope_factor) + 1.0
+      scale = scale * m * m
+    self.softmax_scale = scale
+
+  def __call__(self, x, ctx):
+    c = self.c
+    B, S, _ = x.shape
+    x = tp_enter(x, ctx)
+    if self.query is not None:
+      q = F.linear(x, self.query)
+    else:
+      q = F.linear(self.q_norm(F.linear(x, self.wq_a)), self.wq_b)
+    q = q.view(B, S, self.h, self.qk)
+    q_nope, q_rope = q[..., :self.nope], q[..., self.nope:]
+    q_rope = F.rope(q_rope, ctx.positions, self.inv_ts, self.interleaved)
+    q = torch.cat([q_nope, q_rope], dim=-1) * self.softmax_scale
+    kva = F.linear(x, self.wkv_a)
+    latent, k_rope = kva[..., :c.kv_lora_rank], kva[..., c.kv_lora_rank:]
+    k_rope = F.rope(k_rope.reshape(B, S, 1, self.rope_d), ctx.positions, self.inv_ts, self.interleaved)
+    latent = self.kv_norm(latent.contiguous())
+    if ctx.cache is not None:
+      out = ctx.cache.attend_mla(q, latent, k_rope, self, ctx)
+    else:
+      kv = F.linear(latent, self.wkv_b).view(B, S, self.h, self.nope + self.vd)
+      k = torch.cat([kv[..., :self.nope], k_rope.expand(B, S, self.h, self.rope_d)], dim=-1)
+      v = kv[..., self.nope:]
+      out = F.attention(q, k.contiguous(), v.contiguous(), ctx.positions, ctx.segment_ids, 1.0, 0.0, 0)
+    y = F.linear(out.reshape(B, S, -1), self.o)
+    return tp_exit(y, ctx)
+
+
+# ------------------------------------------------------------------------------------------ dense MLP
+class MLP:
+  """wo( act(wi_0 x) * (wi_1 x) ) (src/maxtext/layers/linears.py:422-625)."""
+
+  def __init__(self, b: Builder, config, name="mlp", hidden: int | None = None, acts=None, bias=False):
+    c = config
+    self.acts = list(acts or c.mlp_activations)
+    f = hidden or c.mlp_dim
+    mb = b.sub(name)
+    d = c.emb_dim
+    self.gated = len(self.acts) == 2
+    self.wi_0 = mb.sub("wi_0" if self.gated else "wi").linear("kernel", (d,), (f,), ("embed", "mlp"), tp="col")
+    self.wi_1 = mb.sub("wi_1").linear("kernel", (d,), (f,), ("embed", "mlp"), tp="col") if self.gated else None
+    self.wo = mb.sub("wo").linear("kernel", (f,), (d,), ("mlp", "embed"), tp="row")
+    self.wi = FusedParam([self.wi_0, self.wi_1]) if self.gated and FusedParam.possible([self.wi_0, self.wi_1]) else None
+    self.bi = mb.sub("wi_0" if self.gated else "wi").vector("bias", f, ("mlp",), init="zeros", tp=True) if bias else None
+    self.bo = mb.sub("wo").vector("bias", d, ("embed",), init="zeros") if bias else None
+
+  def __call__(self, x, ctx):
+    x = tp_enter(x, ctx)
+    if self.gated:
+      if self.wi is not None and self.wi.data is not None:
+        gu = ctx.keep("mlpwi", F.linear(x, self.wi, ctx.reuse("mlpwi")))
+      else:
+        g = ctx.keep("mlpwi_0", F.linear(x, self.wi_0, ctx.reuse("mlpwi_0")))
+        u = ctx.keep("mlpwi_1", F.linear(x, self.wi_1, ctx.reuse("mlpwi_1")))
+        gu = torch.cat([g, u], dim=-1)
+      h = F.gated_act(gu, self.acts[0])
+    else:
+      h = F.linear(x, self.wi_0, bias=self.bi)
+      h = ref.act_fn(self.acts[0])(h.float()).to(x.dtype) if self.acts[0] != "linear" else h
+    y = F.linear(h, self.wo, ctx.reuse("mlpwo"), self.bo if ctx.tp_size == 1 else None)
+    y = tp_exit(y, ctx)
+    ctx.keep("mlpwo", y)
+    return y

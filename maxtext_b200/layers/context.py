@@ -1,0 +1,87 @@
+"""Per-call state handed to every layer: token geometry, parallel groups, remat bookkeeping, caches."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+# tensors a remat policy may keep, by policy name (src/maxtext/layers/nnx_decoders.py:1140-1268)
+_PROJ = ("query_proj", "key_proj", "value_proj", "kv_proj", "qkv_proj", "out_proj")
+_MLP = ("mlpwi_0", "mlpwi_1", "mlpwi", "mlpwo")
+REMAT_SAVED = {
+    "full": (),
+    "minimal": _PROJ + _MLP,
+    "minimal_with_context": _PROJ + _MLP + ("context",),
+    "minimal_flash": _PROJ + _MLP + ("context",),
+    "minimal_with_quantization": _PROJ + _MLP,
+    "minimal_with_context_and_quantization": _PROJ + _MLP + ("context",),
+    "save_dot_except_mlp": _PROJ,
+    "save_dot_with_context_except_mlp": _PROJ + ("context",),
+    "save_dot_except_mlpwi": _PROJ + ("mlpwo",),
+    "save_qkv_proj": ("query_proj", "key_proj", "value_proj", "qkv_proj"),
+    "save_out_proj": ("out_proj",),
+    "qkv_proj_offloaded": (),
+    "minimal_offloaded": (),
+    "custom": (),
+}
+REMAT_OFFLOADED = {
+    "qkv_proj_offloaded": ("query_proj", "key_proj", "value_proj", "qkv_proj"),
+    "minimal_offloaded": _PROJ + _MLP,
+}
+
+
+def saved_names(config) -> tuple[tuple, tuple]:
+  """(kept on device, kept on pinned host) tensor names for config.remat_policy."""
+  pol = config.remat_policy
+  dev = tuple(REMAT_SAVED.get(pol, ()))
+  off = tuple(REMAT_OFFLOADED.get(pol, ()))
+  if pol == "custom":
+    dev = tuple(config.tensors_on_device)
+    off = tuple(config.tensors_to_offload)
+  return dev, off
+
+
+@dataclass
+class LayerCtx:
+  config: object
+  positions: torch.Tensor            # [B, S] original token positions
+  segment_ids: torch.Tensor | None   # [B, S] (0 = padding)
+  mode: str = "train"                # train | prefill | decode
+  mesh: object = None
+  tp_group: object = None
+  tp_size: int = 1
+  ep_group: object = None
+  ep_size: int = 1
+  cp_group: object = None
+  cp_size: int = 1
+  # remat: first forward stores named tensors, recompute forward consumes them
+  save_names: tuple = ()
+  offload_names: tuple = ()
+  saved: dict | None = None          # name -> tensor for the current layer
+  recompute: bool = False
+  layer_index: int = 0
+  aux_losses: list = field(default_factory=list)   # (name, tensor) produced by layers (e.g. moe_lb_loss)
+  metrics: dict = field(default_factory=dict)
+  cache: object = None               # inference KV cache for the current layer
+  tokens: torch.Tensor | None = None
+  name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
+
+  def keep(self, name: str, t: torch.Tensor) -> torch.Tensor:
+    """Called on a named intermediate in the first (no-grad) forward of a rematerialised layer."""
+    if self.saved is not None and not self.recompute:
+      if name in self.save_names:
+        self.saved[self.name_prefix + name] = t
+      elif name in self.offload_names:
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=t.is_cuda)
+        host.copy_(t, non_blocking=True)
+        self.saved[self.name_prefix + name] = host
+    return t
+
+  def reuse(self, name: str):
+    """In the recompute forward: the kept tensor for `name`, or None if it must be recomputed."""
+    if self.recompute and self.saved is not None and (self.name_prefix + name) in self.saved:
+      t = self.saved[self.name_prefix + name]
+      if t.device.type == "cpu" and self.positions.is_cuda:
+        t = t.to(self.positions.device, non_blocking=True)
+      return t
+    return None

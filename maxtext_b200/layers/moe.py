@@ -1,0 +1,147 @@
+"""Routed mixture-of-experts: router, dropless permutation, grouped expert FFN, expert parallelism.
+
+Semantics follow src/maxtext/layers/moe.py: gate 247-392, top-k 717-765 (softmax over the selected
+logits for Mixtral-style blocks; DeepSeek uses pre-scored values, optionally group-limited and
+bias-corrected 775-838), dropless permutation 872-1002 (stable sort by expert id) and combine
+1004-1063, load-balance loss 2662-2687, shared experts 3259-3371. Expert parallelism moves rows with
+a variable-size all-to-all whose split sizes come from an exchanged count matrix (1202-1361);
+`ops.moe_ops` provides the kernels (router top-k, counting-sort permutation, grouped GEMM).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F
+from ..ops import moe_ops
+from .blocks import Builder, FusedParam, MLP, tp_enter, tp_exit
+
+
+class _AllToAllRows(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, rows, send_sizes, recv_sizes, group):
+    ctx.group, ctx.send, ctx.recv = group, send_sizes, recv_sizes
+    out = rows.new_empty((sum(recv_sizes),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), recv_sizes, send_sizes, group=group)
+    return out
+
+  @staticmethod
+  def backward(ctx, dy):
+    dx = dy.new_empty((sum(ctx.send),) + tuple(dy.shape[1:]))
+    dist.all_to_all_single(dx, dy.contiguous(), ctx.send, ctx.recv, group=ctx.group)
+    return dx, None, None, None
+
+
+class RoutedMoE:
+  def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False):
+    c = config
+    self.c = c
+    self.E, self.k = c.num_experts, c.num_experts_per_tok
+    self.deepseek = deepseek_style
+    mb = b.sub(name)
+    d, f = c.emb_dim, c.moe_mlp_dim
+    self.gate = mb.sub("gate").linear("kernel", (d,), (self.E,), ("embed", None))
+    self.gate_bias = mb.sub("gate").vector("bias", self.E, (None,), init="zeros") if c.routed_bias else None
+    self.wi_0 = mb.experts("wi_0", self.E, d, f, ("exp", "embed_moe", "mlp_moe"), tp="col")
+    self.wi_1 = mb.experts("wi_1", self.E, d, f, ("exp", "embed_moe", "mlp_moe"), tp="col")
+    self.wo = mb.experts("wo", self.E, f, d, ("exp", "mlp_moe", "embed_moe"), tp="row")
+    self.act = c.mlp_activations[0]
+    self.e_local = self.E // b.ep_size
+
+  # ---- routing
+  def route(self, x2, B, S):
+    c = self.c
+    xg = x2.float() if c.float32_gate_logits else x2
+    w = self.gate.leaf()
+    logits = torch.nn.functional.linear(xg, w.to(xg.dtype))
+    if self.deepseek:
+      func = c.routed_score_func or "softmax"
+      lf = logits.float()
+      scores = torch.softmax(lf, -1) if func == "softmax" else torch.sigmoid(lf) if func == "sigmoid" else lf
+      sel = scores + self.gate_bias.leaf().float() if self.gate_bias is not None else scores
+      if c.n_routing_groups > 0 and c.topk_routing_group > 0:
+        G = c.n_routing_groups
+        grp = sel.view(-1, G, self.E // G)
+        gscore = grp.topk(2, dim=-1).values.sum(-1) if self.gate_bias is not None else grp.max(-1).values
+        gidx = gscore.topk(c.topk_routing_group, dim=-1).indices
+        gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0).bool()
+        sel = sel.masked_fill(~gmask[:, :, None].expand_as(grp).reshape(sel.shape), float("-inf"))
+      idx = sel.topk(self.k, dim=-1).indices
+      wts = scores.gather(-1, idx)
+      if func in ("sigmoid", "sqrtsoftplus"):
+        wts = wts / (wts.sum(-1, keepdim=True) + 1e-20)
+      wts = wts * c.routed_scaling_factor
+      probs = scores
+    else:
+      vals, idx = logits.topk(self.k, dim=-1)
+      wts = torch.softmax(vals.float(), -1)
+      if c.norm_topk_prob:
+        wts = wts / wts.sum(-1, keepdim=True)
+      probs = torch.softmax(logits.float(), -1)
+    aux = None
+    if c.load_balance_loss_weight > 0:
+      onehot = torch.zeros(B * S, self.E, dtype=torch.float32, device=x2.device).scatter_add_(
+          1, idx, torch.ones_like(idx, dtype=torch.float32))
+      density = onehot.view(B, S, self.E).mean(1)
+      density_prob = probs.view(B, S, self.E).mean(1)
+      aux = (density * density_prob).mean() * (self.E ** 2) * c.load_balance_loss_weight
+    return wts, idx, aux
+
+  # ---- expert FFN on rows grouped by (local) expert
+  def experts_ffn(self, rows, sizes):
+    g = moe_ops.grouped_linear(rows, self.wi_0, sizes)
+    u = moe_ops.grouped_linear(rows, self.wi_1, sizes)
+    h = F.gated_act(torch.cat([g, u], dim=-1), self.act)
+    return moe_ops.grouped_linear(h, self.wo, sizes)
+
+  def __call__(self, x, ctx):
+    B, S, D = x.shape
+    x2 = x.reshape(B * S, D)
+    wts, idx, aux = self.route(x2, B, S)
+    if aux is not None:
+      ctx.aux_losses.append(("moe_lb_loss", aux))
+    rows, order, sizes = moe_ops.permute(x2, idx, self.E)          # rows sorted by global expert id
+    if ctx.ep_size > 1:
+      y = self._expert_parallel(rows, sizes, ctx)
+    else:
+      y = self.experts_ffn(rows, sizes)
+      if ctx.tp_size > 1:
+        y = tp_exit(y, ctx)
+    out = moe_ops.unpermute_combine(y, order, wts, B * S, self.k, fp32_sum=self.c.float32_weight_sum)
+    return out.view(B, S, D).to(x.dtype)
+
+  def _expert_parallel(self, rows, sizes, ctx):
+    """NCCL reference path: counts exchange -> a2a dispatch -> local regroup -> FFN -> reverse."""
+    ep, el = ctx.ep_size, self.e_local
+    counts = sizes.view(ep, el)                                  # rows this rank sends to (dest rank, its expert)
+    recv_counts = torch.empty_like(counts)
+    dist.all_to_all_single(recv_counts, counts.contiguous(), group=ctx.ep_group)   # [src rank, my expert]
+    send_sizes = counts.sum(1).tolist()
+    recv_sizes = recv_counts.sum(1).tolist()
+    recv = _AllToAllRows.apply(rows, send_sizes, recv_sizes, ctx.ep_group)         # grouped by src rank, then expert
+    # regroup by local expert
+    src_expert = torch.repeat_interleave(torch.arange(el, device=rows.device).repeat(ep), recv_counts.reshape(-1))
+    local_order = torch.argsort(src_expert, stable=True)
+    local_sizes = recv_counts.sum(0)
+    grouped = recv[local_order]
+    y = self.experts_ffn(grouped, local_sizes)
+    inv = torch.empty_like(local_order)
+    inv[local_order] = torch.arange(local_order.numel(), device=rows.device)
+    y = y[inv]
+    return _AllToAllRows.apply(y, recv_sizes, send_sizes, ctx.ep_group)
+
+
+class RoutedAndSharedMoE:
+  """Routed experts plus always-on shared experts (src/maxtext/layers/moe.py:3259-3371)."""
+
+  def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0"):
+    mb = b.sub(name)
+    self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=True)
+    self.shared = MLP(mb, config, "shared_experts", hidden=config.shared_experts * config.moe_mlp_dim) \
+        if config.shared_experts > 0 else None
+
+  def __call__(self, x, ctx):
+    y = self.routed(x, ctx)
+    if self.shared is not None:
+      y = y + self.shared(x, ctx)
+    return y

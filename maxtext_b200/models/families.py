@@ -1,0 +1,117 @@
+"""Per-family layer plans: which blocks make a layer, how they are named, which RoPE they use.
+
+One entry per `decoder_block` value (src/maxtext/common/common_types.py:92-118), reproducing the
+structure of the reference model files: llama2.py (Llama 2/3/3.x), mistral.py, mixtral.py,
+deepseek.py, gemma.py / gemma2.py / gemma3.py, qwen2.py / qwen3.py, gpt3.py, gpt_oss.py, olmo3.py,
+simple_layer.py.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from ..ops import reference as ref
+from .transformer import BlockPlan, LayerPlan
+
+
+@dataclass
+class Family:
+  norm_kind: str = "rms"
+  norm_offset: float = 0.0
+  scale_embedding: bool = False
+
+
+def describe(c) -> Family:
+  blk = c.decoder_block
+  if blk in ("gemma", "gemma2", "gemma3"):
+    return Family(scale_embedding=True)
+  if blk == "gpt3":
+    return Family(norm_kind="layernorm")
+  return Family()
+
+
+def rope_tables(c, device) -> dict:
+  """name -> (inverse timescales [rot_dim/2] fp32 on `device`, interleaved-lane flag)."""
+  yarn = dict(rope_factor=c.rope_factor, original_max_position_embeddings=c.original_max_position_embeddings,
+              beta_fast=c.beta_fast, beta_slow=c.beta_slow, rope_truncate=c.rope_truncate)
+  rt = c.rope_type
+  if c.model_name.startswith("llama3.1") or c.model_name.startswith("llama3.3"):
+    rt = "llama3.1"
+  dim = c.qk_rope_head_dim if c.attention_type == "mla" else c.head_dim
+  rot = int(dim * c.partial_rotary_factor) if c.partial_rotary_factor < 1.0 else dim
+  interleaved = rt.startswith("llama3.1") or (rt == "yarn" and c.rope_interleave)
+  scaling = c.rope_linear_scaling_factor
+  tables = {
+      "default": (ref.rope_inv_timescale(rot, c.rope_min_timescale, c.rope_max_timescale, scaling, rt, c.rope_use_scale,
+                                         yarn).to(device), interleaved),
+  }
+  local_max = c.local_rope_max_timescale if c.local_rope_max_timescale > 0 else c.rope_max_timescale
+  # local (sliding-window) layers never use the long-context linear scaling (gemma3)
+  tables["local"] = (ref.rope_inv_timescale(rot, c.rope_min_timescale, local_max, 1.0, "default").to(device), False)
+  return tables
+
+
+def _llama_like(c, **kw) -> BlockPlan:
+  return BlockPlan(window=c.sliding_window_size if c.attention_type == "local_sliding" or c.decoder_block == "mistral" else 0,
+                   qk_norm=c.use_qk_norm, attn_bias=c.attention_bias, soft_cap=c.attn_logits_soft_cap, **kw)
+
+
+def layer_plans(c) -> list[LayerPlan]:
+  n = c.num_decoder_layers
+  blk = c.decoder_block
+  mla = c.attention_type == "mla"
+  attn = "mla" if mla else "gqa"
+  if blk in ("default", "llama2", "mistral", "qwen3", "olmo3", "simple", "simple_mlp", "llama4"):
+    return [LayerPlan("layers", [_llama_like(c, attention=attn)]) for _ in range(n)]
+  if blk == "qwen2":
+    bp = _llama_like(c, attention=attn)
+    bp.attn_bias = True
+    return [LayerPlan("layers", [bp]) for _ in range(n)]
+  if blk == "mixtral":
+    return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="MoeBlock_0")]) for _ in range(n)]
+  if blk in ("qwen3_moe", "qwen3_custom_moe"):
+    return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="moe_block")]) for _ in range(n)]
+  if blk == "deepseek":
+    nd = c.first_num_dense_layers
+    dense = [LayerPlan("dense_layers", [_llama_like(c, attention=attn)]) for _ in range(nd)]
+    moe = [LayerPlan("moe_layers", [_llama_like(c, attention=attn, mlp="moe_shared", mlp_name="DeepSeekMoeBlock_0")])
+           for _ in range(n - nd)]
+    return dense + moe
+  if blk == "gemma":
+    bp = BlockPlan(pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="pre_ffw_norm", soft_cap=c.attn_logits_soft_cap)
+    return [LayerPlan("layers", [bp]) for _ in range(n)]
+  if blk == "gemma2":
+    def sub(suffix, window):
+      return BlockPlan(suffix=suffix, pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="pre_ffw_norm",
+                       post_attn_norm="post_self_attention_norm" if c.use_post_attn_norm else None,
+                       post_mlp_norm="post_ffw_norm" if c.use_post_ffw_norm else None, window=window,
+                       soft_cap=c.attn_logits_soft_cap)
+    return [LayerPlan("layers", [sub("_local", c.sliding_window_size), sub("_global", 0)]) for _ in range(n)]
+  if blk == "gemma3":
+    plans = []
+    if c.model_name in ("gemma3-27b",):
+      qs = (c.base_emb_dim // c.base_num_query_heads) ** -0.5
+    else:
+      qs = c.head_dim ** -0.5
+    for i in range(n):
+      local = (i % 6) != 5
+      plans.append(LayerPlan("layers", [BlockPlan(
+          pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="pre_ffw_norm",
+          post_attn_norm="post_self_attention_norm" if c.use_post_attn_norm else None,
+          post_mlp_norm="post_ffw_norm" if c.use_post_ffw_norm else None,
+          window=c.sliding_window_size if local else 0, rope="local" if local else "default", qk_norm=True,
+          query_scalar=qs, soft_cap=c.attn_logits_soft_cap)]))
+    return plans
+  if blk == "gpt3":
+    bp = BlockPlan(pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="post_self_attention_norm", use_rope=False,
+                   attn_bias=True, mlp_bias=True, norm_kind="layernorm")
+    return [LayerPlan("layers", [bp]) for _ in range(n)]
+  if blk == "gpt_oss":
+    plans = []
+    for i in range(n):
+      local = (i % 2) == 0
+      plans.append(LayerPlan("layers", [BlockPlan(window=c.sliding_window_size if local else 0, attn_bias=True, sinks=True,
+                                                  mlp="moe", mlp_name="GptOssMlp")]))
+    return plans
+  raise NotImplementedError(
+      f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, gpt3, gpt_oss, olmo3, simple)")

@@ -1,0 +1,235 @@
+"""Decoder-only transformer assembled from a per-family layer plan.
+
+The role of src/maxtext/models/models.py:330-619 (`Transformer`) and
+src/maxtext/layers/nnx_decoders.py:380-2025 (`NNXDecoder`): token embedding, a stack of decoder
+layers chosen by `decoder_block`, final norm and output head. Instead of one traced function the
+model is a list of *units* (embedding, each layer, head) that the training engine runs with an
+explicit schedule (gather -> forward -> [recompute ->] backward -> reduce-scatter).
+
+Family specifics (block structure, parameter names, norms, RoPE flavour, MoE style) are described by
+`LayerPlan` entries built in `models/families.py`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from ..layers import blocks as L
+from ..layers import moe as M
+from ..layers.context import LayerCtx
+from ..ops import functional as F
+from ..ops import reference as ref
+from ..parallel.param_store import ParamStore
+
+
+@dataclass
+class BlockPlan:
+  """One attention + feed-forward residual pair."""
+  suffix: str = ""                       # appended to every module name (gemma2: _local / _global)
+  pre_attn_norm: str = "pre_self_attention_layer_norm"
+  post_attn_norm: str | None = None      # norm applied to the attention output before the residual add
+  pre_mlp_norm: str = "post_self_attention_layer_norm"
+  post_mlp_norm: str | None = None
+  attn_name: str = "self_attention"
+  mlp_name: str = "mlp"
+  attention: str = "gqa"                 # gqa | mla
+  window: int = 0
+  rope: str = "default"                  # key into Transformer.rope_tables
+  use_rope: bool = True
+  qk_norm: bool = False
+  attn_bias: bool = False
+  query_scalar: float | None = None
+  soft_cap: float = 0.0
+  sinks: bool = False
+  mlp: str = "dense"                     # dense | moe | moe_shared
+  mlp_hidden: int | None = None
+  mlp_bias: bool = False
+  norm_kind: str = "rms"
+  norm_offset: float = 0.0
+  parallel_residual: bool = False
+
+
+@dataclass
+class LayerPlan:
+  stack: str = "layers"                  # name of the stacked collection in the checkpoint tree
+  blocks: list = field(default_factory=lambda: [BlockPlan()])
+
+
+class DecoderBlock:
+  def __init__(self, b: L.Builder, config, plan: BlockPlan, rope_tables: dict):
+    c, s = config, plan.suffix
+    self.plan = plan
+    eps = c.normalization_layer_epsilon
+    mk = lambda n: L.Norm(b, n + s, c.emb_dim, eps, plan.norm_offset, kind=plan.norm_kind)  # noqa: E731
+    self.n1 = mk(plan.pre_attn_norm)
+    inv_ts, interleaved = rope_tables[plan.rope]
+    if plan.attention == "mla":
+      self.attn = L.MLA(b, c, inv_ts, interleaved, plan.attn_name + s)
+    else:
+      self.attn = L.Attention(b, c, plan.attn_name + s, plan.window, inv_ts, interleaved, plan.use_rope, plan.qk_norm,
+                              plan.query_scalar, plan.soft_cap, plan.attn_bias,
+                              rotary_dim=None, sinks=plan.sinks)
+    self.n1b = mk(plan.post_attn_norm) if plan.post_attn_norm else None
+    self.n2 = mk(plan.pre_mlp_norm)
+    if plan.mlp == "moe":
+      self.mlp = M.RoutedMoE(b, c, plan.mlp_name + s)
+    elif plan.mlp == "moe_shared":
+      self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s)
+    else:
+      self.mlp = L.MLP(b, c, plan.mlp_name + s, plan.mlp_hidden, bias=plan.mlp_bias)
+    self.n2b = mk(plan.post_mlp_norm) if plan.post_mlp_norm else None
+
+  def __call__(self, x, ctx: LayerCtx):
+    a = self.attn(self.n1(x), ctx)
+    if self.n1b is not None:
+      a = self.n1b(a)
+    x = x + a
+    m = self.mlp(self.n2(x), ctx)
+    if self.n2b is not None:
+      m = self.n2b(m)
+    return x + m
+
+
+class DecoderLayer:
+  """One schedulable unit: all parameters gathered / reduced together."""
+
+  def __init__(self, config, index: int, stack_index: int, plan: LayerPlan, rope_tables, par):
+    self.index, self.plan = index, plan
+    self.unit = f"layer_{index}"
+    b = L.Builder(config, self.unit, stack_index, plan.stack, **par)
+    self.blocks = [DecoderBlock(b, config, bp, rope_tables) for bp in plan.blocks]
+    self.params = b.params
+
+  def __call__(self, x, ctx: LayerCtx):
+    for i, blk in enumerate(self.blocks):
+      ctx.name_prefix = f"b{i}/" if len(self.blocks) > 1 else ""
+      x = blk(x, ctx)
+    ctx.name_prefix = ""
+    return x
+
+
+class Transformer:
+  def __init__(self, config, mesh=None, device="cpu", build_store: bool = True):
+    from . import families
+    c = self.config = config
+    self.mesh = mesh
+    self.device = torch.device(device)
+    tp_axes = ("tensor", "tensor_sequence")
+    tp_size = mesh.axis_size(tp_axes) if mesh is not None else 1
+    tp_rank = mesh.axis_index(tp_axes) if mesh is not None else 0
+    ep_size = mesh.axis_size("expert") if (mesh is not None and c.num_experts > 1) else 1
+    ep_rank = mesh.axis_index("expert") if (mesh is not None and c.num_experts > 1) else 0
+    self.par = dict(tp_size=tp_size, tp_rank=tp_rank, ep_size=ep_size, ep_rank=ep_rank)
+    self.rope_tables = families.rope_tables(c, self.device)
+    self.family = families.describe(c)
+    # ---- embedding unit
+    eb = L.Builder(c, "embed", None, None, **self.par)
+    self.embedding = eb.sub("token_embedder").table("embedding", (c.vocab_size, c.emb_dim), ("vocab", "embed_vocab"))
+    self.pos_embedding = None
+    if c.trainable_position_size > 0:
+      self.pos_embedding = eb.sub("decoder", "position_embedder").table(
+          "embedding", (c.trainable_position_size, c.emb_dim), (None, "embed"))
+    self.embed_params = eb.params
+    # ---- layers
+    self.layers: list[DecoderLayer] = []
+    counters: dict[str, int] = {}
+    for i, plan in enumerate(families.layer_plans(c)):
+      si = counters.get(plan.stack, 0)
+      counters[plan.stack] = si + 1
+      self.layers.append(DecoderLayer(c, i, si, plan, self.rope_tables, self.par))
+    self.stack_sizes = counters
+    # ---- head unit
+    hb = L.Builder(c, "head", None, None, **self.par)
+    self.final_norm = L.Norm(hb.sub("decoder"), "decoder_norm", c.emb_dim, c.normalization_layer_epsilon,
+                             self.family.norm_offset, kind=self.family.norm_kind)
+    self.logits_dense = None
+    if not c.logits_via_embedding:
+      self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
+                                                                   ("embed_vocab", "vocab"))
+    self.head_params = hb.params
+    self.store: ParamStore | None = None
+    if build_store:
+      self.store = ParamStore(self.all_params(), mesh or _SingleMesh(), c, self.device)
+
+  # ------------------------------------------------------------------ params
+  def all_params(self):
+    out = list(self.embed_params)
+    for l in self.layers:
+      out.extend(l.params)
+    out.extend(self.head_params)
+    return out
+
+  def units_in_order(self) -> list[str]:
+    return ["embed"] + [l.unit for l in self.layers] + ["head"]
+
+  # ------------------------------------------------------------------ contexts
+  def make_ctx(self, positions, segment_ids, mode="train", tokens=None) -> LayerCtx:
+    from ..layers.context import saved_names
+    m = self.mesh
+    dev, off = saved_names(self.config) if mode == "train" else ((), ())
+    ctx = LayerCtx(self.config, positions, segment_ids, mode, m, save_names=dev, offload_names=off, tokens=tokens)
+    if m is not None:
+      ctx.tp_size = m.axis_size(("tensor", "tensor_sequence"))
+      ctx.tp_group = m.group(("tensor", "tensor_sequence")) if ctx.tp_size > 1 else None
+      if self.config.num_experts > 1:
+        ctx.ep_size = m.axis_size("expert")
+        ctx.ep_group = m.group("expert") if ctx.ep_size > 1 else None
+      ctx.cp_size = m.axis_size("context")
+      ctx.cp_group = m.group("context") if ctx.cp_size > 1 else None
+    return ctx
+
+  # ------------------------------------------------------------------ pieces run by the engine
+  def embed(self, tokens, positions):
+    c = self.config
+    x = F.embedding(tokens, self.embedding)
+    if self.family.scale_embedding:
+      x = (x.float() * math.sqrt(c.emb_dim)).to(x.dtype)
+    if self.pos_embedding is not None:
+      x = x + self.pos_embedding.leaf()[positions.long()].to(x.dtype)
+    return x
+
+  def head_param(self):
+    return self.logits_dense if self.logits_dense is not None else self.embedding
+
+  def head_logit_scale(self) -> float:
+    c = self.config
+    if c.logits_via_embedding and c.normalize_embedding_logits:
+      return 1.0 / math.sqrt(c.emb_dim)
+    return 1.0
+
+  def logits(self, x):
+    h = self.final_norm(x)
+    return F.head_logits(h, self.head_param(), self.config.final_logits_soft_cap, self.head_logit_scale())
+
+  # ------------------------------------------------------------------ plain forward (eval / inference / tests)
+  @torch.no_grad()
+  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None):
+    """Full logits [B,S,V] in fp32; every unit must be resident (single rank or gathered by the caller)."""
+    B, S = tokens.shape
+    if positions is None:
+      positions = torch.arange(S, device=tokens.device)[None].expand(B, S)
+    ctx = self.make_ctx(positions, segment_ids, mode, tokens)
+    x = self.embed(tokens, positions)
+    for i, layer in enumerate(self.layers):
+      ctx.layer_index = i
+      ctx.cache = caches[i] if caches is not None else None
+      x = layer(x, ctx)
+    return self.logits(x)
+
+
+class _SingleMesh:
+  """Stand-in mesh for single-process use."""
+  axis_names = ("fsdp",)
+  shape = {"fsdp": 1}
+  rank, world = 0, 1
+
+  def axis_size(self, axes):
+    return 1
+
+  def axis_index(self, axes):
+    return 0
+
+  def group(self, axes):
+    return None

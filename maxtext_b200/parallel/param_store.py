@@ -1,0 +1,419 @@
+"""Flat, unit-wise parameter storage with ZeRO-3 style sharding.
+
+MaxText leaves parameter placement to GSPMD: each weight carries logical axis names, the rule table
+maps them to mesh axes, and XLA inserts per-layer all-gathers / reduce-scatters
+(src/maxtext/utils/sharding.py:362-469, docs/guides/optimization/sharding.md). Here placement is
+explicit and laid out for NVLink collectives:
+
+* every parameter belongs to a **unit** (embedding, one decoder layer, output head). All parameters
+  of a unit live back to back in one flat buffer, so a layer's weights move with ONE all-gather and
+  its gradients with ONE reduce-scatter, and adjacent tensors (q|k|v, wi_0|wi_1) can be consumed as
+  one fused GEMM operand without a copy;
+* the rule table still decides *which mesh axes* shard a parameter: tensor-like axes split a real
+  dimension (handled by the layer code, the store sees the local shape), every other axis that the
+  rules assign (fsdp, fsdp_transpose, context, expert-as-fsdp...) joins the unit's flat shard group:
+  rank r of that group owns elements [r*chunk, (r+1)*chunk) of the flat unit;
+* fp32 master weights, AdamW moments and fp32 gradient shards are single contiguous arrays over all
+  units, so the optimizer is one kernel launch over the local shard;
+* the compute-dtype copy of a unit is materialised into a small pool of gather buffers, prefetched
+  one unit ahead by `parallel.fsdp.FsdpSchedule`.
+
+Internal linear layout is `[out, in]`; the reference layout (`[in..., out...]`, layer axis stacked
+at `param_scan_axis`) is produced by `to_reference_tree` for checkpoints.
+"""
+from __future__ import annotations
+
+import hashlib
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import rules as _rules
+
+ALIGN = 256  # elements; keeps every parameter 512-byte aligned in bf16 (TMA needs 16 B)
+
+_TP_AXES = ("tensor", "tensor_sequence", "autoregressive")
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
+
+
+def torch_dtype(name) -> torch.dtype:
+  return name if isinstance(name, torch.dtype) else _DTYPES[name]
+
+
+@dataclass
+class ParamDef:
+  name: str                      # unique, e.g. "layers_3/self_attention/query/kernel"
+  unit: str                      # "embed" | "layer_<i>" | "head" | ...
+  shape: tuple                   # internal layout, local to this rank
+  ref_path: tuple                # path in the reference tree (without layer index)
+  ref_shape: tuple               # reference layout, global
+  logical_axes: tuple            # logical names of the reference dims
+  kind: str = "linear"           # "linear": ref [in..,out..] <-> internal [out,in]; "same": identical layout
+  n_in_dims: int = 1             # for kind=linear: how many leading ref dims are "in"
+  init: str = "fan_in_trunc"     # fan_in_trunc | fan_in_normal | embed | ones | zeros | normal
+  init_scale: float = 1.0
+  layer: int | None = None       # index along the stacked layer axis
+  stack: str | None = None       # name of the stacked collection in the reference tree ("layers", "dense_layers"...)
+  weight_decay: bool = True
+  tp_dim: int | None = None      # internal dim split over tensor axes (already applied to `shape`)
+  ep_dim: int | None = None      # internal dim split over the expert axis (already applied)
+  fsdp_axes: tuple = ()          # mesh axes of the flat shard group (filled by the store)
+
+  @property
+  def numel(self) -> int:
+    return int(math.prod(self.shape))
+
+
+class Param:
+  """Handle given to layer code. `.data` is the compute-dtype tensor (valid while the unit is
+  resident), `.main_grad` the fp32 gradient accumulator view (valid during backward)."""
+
+  __slots__ = ("pdef", "data", "main_grad", "grad_written", "_leaf")
+
+  def __init__(self, pdef: ParamDef):
+    self.pdef = pdef
+    self.data: torch.Tensor | None = None
+    self.main_grad: torch.Tensor | None = None
+    self.grad_written = False
+    self._leaf = None
+
+  @property
+  def name(self):
+    return self.pdef.name
+
+  @property
+  def shape(self):
+    return self.pdef.shape
+
+  def leaf(self) -> torch.Tensor:
+    """An autograd leaf aliasing `.data` for ops that rely on plain PyTorch differentiation; its
+    `.grad` is folded into `main_grad` by `collect_leaf_grads` after the unit's backward."""
+    if not torch.is_grad_enabled():
+      return self.data
+    if self._leaf is None or self._leaf.data_ptr() != self.data.data_ptr():
+      self._leaf = self.data.detach().requires_grad_(True)
+    return self._leaf
+
+  def accumulate_grad(self, g: torch.Tensor):
+    if self.grad_written:
+      self.main_grad.add_(g.reshape(self.main_grad.shape))
+    else:
+      self.main_grad.copy_(g.reshape(self.main_grad.shape))
+      self.grad_written = True
+
+  def collect_leaf_grad(self):
+    if self._leaf is not None:
+      if self._leaf.grad is not None:
+        self.accumulate_grad(self._leaf.grad)
+      self._leaf = None
+
+
+@dataclass
+class Unit:
+  name: str
+  fsdp_axes: tuple
+  params: list = field(default_factory=list)     # list[Param]
+  offsets: list = field(default_factory=list)
+  numel: int = 0          # padded to a multiple of ALIGN * shard group size
+  chunk: int = 0          # numel / shard group size
+  shard_offset: int = 0   # offset of this unit's chunk in the local flat arrays
+  group: object = None
+  group_size: int = 1
+  group_rank: int = 0
+  full: torch.Tensor | None = None        # compute-dtype full buffer while resident
+  full_grad: torch.Tensor | None = None   # fp32 full gradient buffer during backward
+  resident: bool = False
+
+
+def _seed_for(name: str, base_seed: int) -> int:
+  h = hashlib.sha256(f"{base_seed}:{name}".encode()).digest()
+  return int.from_bytes(h[:7], "little")
+
+
+def init_full_tensor(pdef: ParamDef, device, base_seed: int, mode: str = "reference", std: float = 0.02) -> torch.Tensor:
+  """Deterministic fp32 initial value of the whole (local-TP) parameter, independent of FSDP degree.
+
+  reference mode follows src/maxtext/layers/initializers.py:30-63 / linears.py:125 / attentions.py:276:
+  variance_scaling(1.0, fan_in, truncated_normal | normal); `normal` mode draws N(0, std^2) for every
+  matrix (the tiny-model and benchmark configurations)."""
+  gen = torch.Generator(device="cpu" if str(device) == "cpu" else device)
+  gen.manual_seed(_seed_for(pdef.name, base_seed))
+  shape = pdef.shape
+  if pdef.init == "ones":
+    return torch.ones(shape, dtype=torch.float32, device=device)
+  if pdef.init == "zeros":
+    return torch.zeros(shape, dtype=torch.float32, device=device)
+  t = torch.empty(shape, dtype=torch.float32, device=device)
+  if mode == "normal" or pdef.init == "normal":
+    t.normal_(0.0, std, generator=gen)
+    return t * pdef.init_scale
+  if pdef.kind == "linear":
+    fan_in = int(math.prod(pdef.ref_shape[:pdef.n_in_dims]))
+  elif pdef.init == "embed":
+    fan_in = pdef.ref_shape[-1]  # out_axis=0 -> fan_in is the feature dim
+  else:
+    fan_in = pdef.ref_shape[0]
+  s = math.sqrt(1.0 / max(1, fan_in))
+  if pdef.init == "fan_in_trunc":
+    torch.nn.init.trunc_normal_(t, 0.0, 1.0, -2.0, 2.0, generator=gen)
+    t.mul_(s / 0.87962566103423978)
+  else:
+    t.normal_(0.0, s, generator=gen)
+  return t * pdef.init_scale
+
+
+class ParamStore:
+  def __init__(self, params: Sequence[Param], mesh, config, device, logical_rules=None):
+    self.mesh, self.config, self.device = mesh, config, torch.device(device)
+    self.compute_dtype = torch_dtype(config.dtype)
+    self.weight_dtype = torch_dtype(config.weight_dtype)
+    self.grad_dtype = torch_dtype(config.grad_dtype)
+    self.mu_dtype = torch_dtype(config.mu_dtype)
+    rules = logical_rules if logical_rules is not None else config.logical_axis_rules
+    self.params: dict[str, Param] = {}
+    self.units: dict[str, Unit] = {}
+    self.specs: dict[str, _rules.ShardSpec] = {}
+    mesh_shape = mesh.shape
+    for p in params:
+      d = p.pdef
+      spec = _rules.make_spec(d.logical_axes, rules, mesh_shape, d.ref_shape)
+      self.specs[d.name] = spec
+      flat_axes = tuple(a for a in mesh.axis_names if a in spec.all_axes and a not in _TP_AXES and a != "stage"
+                        and not (a == "expert" and d.ep_dim is not None))
+      if config.shard_optimizer_over_data and mesh_shape.get("data", 1) > 1 and "data" not in flat_axes:
+        flat_axes = tuple(a for a in mesh.axis_names if a in flat_axes or a == "data")
+      d.fsdp_axes = flat_axes
+      ukey = d.unit if not self.units.get(d.unit) or self.units[d.unit].fsdp_axes == flat_axes else f"{d.unit}#{'+'.join(flat_axes) or 'rep'}"
+      if ukey not in self.units:
+        self.units[ukey] = Unit(name=ukey, fsdp_axes=flat_axes)
+      if d.name in self.params:
+        raise ValueError(f"duplicate parameter name {d.name}")
+      self.params[d.name] = p
+      self.units[ukey].params.append(p)
+    # layout
+    total_local = 0
+    for u in self.units.values():
+      u.group_size = mesh.axis_size(u.fsdp_axes) if u.fsdp_axes else 1
+      u.group_rank = mesh.axis_index(u.fsdp_axes) if u.fsdp_axes else 0
+      off = 0
+      for p in u.params:
+        u.offsets.append(off)
+        off += -(-p.pdef.numel // ALIGN) * ALIGN
+      quantum = ALIGN * u.group_size
+      u.numel = -(-off // quantum) * quantum
+      u.chunk = u.numel // u.group_size
+      u.shard_offset = total_local
+      total_local += u.chunk
+    self.local_numel = total_local
+    dev = self.device
+    self.master = torch.zeros(total_local, dtype=self.weight_dtype, device=dev)
+    self.alias_compute = self.compute_dtype == self.weight_dtype
+    self.compute_shard = self.master if self.alias_compute else torch.zeros(total_local, dtype=self.compute_dtype, device=dev)
+    self.grad_shard = None   # allocated on first backward (inference never needs it)
+    self.exp_avg = None
+    self.exp_avg_sq = None
+    # process groups (collective creation, deterministic order)
+    for u in self.units.values():
+      u.group = mesh.group(u.fsdp_axes) if u.group_size > 1 else None
+    self._pool: list[torch.Tensor] = []
+    self._grad_pool: list[torch.Tensor] = []
+    self._bind_resident_units()
+
+  # ------------------------------------------------------------------ views
+  def _views_into(self, u: Unit, flat: torch.Tensor, attr: str):
+    for p, off in zip(u.params, u.offsets):
+      setattr(p, attr, flat[off: off + p.pdef.numel].view(p.pdef.shape))
+
+  def _bind_resident_units(self):
+    for u in self.units.values():
+      if u.group_size == 1:
+        u.full = self.compute_shard[u.shard_offset: u.shard_offset + u.numel]
+        u.resident = True
+        self._views_into(u, u.full, "data")
+
+  def shard_view(self, u: Unit, flat: torch.Tensor) -> torch.Tensor:
+    return flat[u.shard_offset: u.shard_offset + u.chunk]
+
+  def ensure_grad_buffers(self):
+    if self.grad_shard is None:
+      self.grad_shard = torch.zeros(self.local_numel, dtype=self.grad_dtype, device=self.device)
+      for u in self.units.values():
+        if u.group_size == 1:
+          u.full_grad = self.grad_shard[u.shard_offset: u.shard_offset + u.numel]
+          self._views_into(u, u.full_grad, "main_grad")
+
+  def ensure_opt_state(self):
+    if self.exp_avg is None:
+      self.exp_avg = torch.zeros(self.local_numel, dtype=self.mu_dtype, device=self.device)
+      self.exp_avg_sq = torch.zeros(self.local_numel, dtype=torch.float32, device=self.device)
+
+  # ------------------------------------------------------------------ init
+  def initialize(self, seed: int = 0, mode: str | None = None, std: float | None = None):
+    mode = mode or getattr(self.config, "weight_init", "reference")
+    std = std if std is not None else getattr(self.config, "weight_init_std", 0.02)
+    for u in self.units.values():
+      lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+      dst = self.shard_view(u, self.master)
+      for p, off in zip(u.params, u.offsets):
+        n = p.pdef.numel
+        a, b = max(off, lo), min(off + n, hi)
+        if a >= b:
+          continue
+        full = init_full_tensor(p.pdef, self.device, seed, mode, std).reshape(-1)
+        dst[a - lo: b - lo].copy_(full[a - off: b - off].to(self.weight_dtype))
+        del full
+    self.sync_compute_from_master()
+
+  def sync_compute_from_master(self):
+    if not self.alias_compute:
+      self.compute_shard.copy_(self.master)
+
+  # ------------------------------------------------------------------ gather / scatter (synchronous forms; the
+  # overlapped schedule lives in parallel.fsdp)
+  def max_unit_numel(self) -> int:
+    return max((u.numel for u in self.units.values() if u.group_size > 1), default=0)
+
+  def acquire_full(self, u: Unit) -> torch.Tensor:
+    if self._pool:
+      buf = self._pool.pop()
+    else:
+      buf = torch.empty(self.max_unit_numel(), dtype=self.compute_dtype, device=self.device)
+    return buf[: u.numel]
+
+  def release_full(self, u: Unit):
+    if u.group_size > 1 and u.full is not None:
+      self._pool.append(u.full._base if u.full._base is not None else u.full)
+      u.full, u.resident = None, False
+      for p in u.params:
+        p.data = None
+
+  def gather_unit(self, u: Unit, async_op: bool = False):
+    """All-gather the compute-dtype shards of unit `u` into a pooled full buffer."""
+    if u.group_size == 1 or u.resident:
+      return None
+    buf = self.acquire_full(u)
+    work = dist.all_gather_into_tensor(buf, self.shard_view(u, self.compute_shard), group=u.group, async_op=async_op)
+    u.full = buf
+    u.resident = True
+    self._views_into(u, buf, "data")
+    return work
+
+  def acquire_full_grad(self, u: Unit):
+    if u.group_size == 1:
+      return
+    if self._grad_pool:
+      buf = self._grad_pool.pop()
+    else:
+      buf = torch.empty(self.max_unit_numel(), dtype=self.grad_dtype, device=self.device)
+    u.full_grad = buf[: u.numel]
+    self._views_into(u, u.full_grad, "main_grad")
+    for p in u.params:
+      p.grad_written = False
+
+  def reduce_scatter_unit(self, u: Unit, async_op: bool = False, accumulate: bool = False):
+    """Sum the unit's full gradient over the shard group into this rank's gradient shard."""
+    if u.group_size == 1:
+      return None
+    # parameters never touched this step must contribute zeros
+    for p in u.params:
+      if not p.grad_written:
+        p.main_grad.zero_()
+    dst = self.shard_view(u, self.grad_shard)
+    if accumulate:
+      tmp = torch.empty_like(dst)
+      dist.reduce_scatter_tensor(tmp, u.full_grad, group=u.group)
+      dst.add_(tmp)
+      work = None
+    else:
+      work = dist.reduce_scatter_tensor(dst, u.full_grad, group=u.group, async_op=async_op)
+    return work
+
+  def release_full_grad(self, u: Unit):
+    if u.group_size > 1 and u.full_grad is not None:
+      self._grad_pool.append(u.full_grad._base if u.full_grad._base is not None else u.full_grad)
+      u.full_grad = None
+      for p in u.params:
+        p.main_grad = None
+
+  def begin_step(self):
+    """Reset per-step gradient bookkeeping (resident units overwrite on first write)."""
+    self.ensure_grad_buffers()
+    for u in self.units.values():
+      for p in u.params:
+        p.grad_written = False
+
+  def finish_resident_grads(self):
+    for u in self.units.values():
+      if u.group_size == 1:
+        for p in u.params:
+          if not p.grad_written:
+            p.main_grad.zero_()
+            p.grad_written = True
+
+  # ------------------------------------------------------------------ replica (data-parallel) reduction
+  def replica_axes(self, u: Unit) -> tuple:
+    """Mesh axes over which this unit's parameters are replicated while the batch is split."""
+    batch_axes = ("data", "fsdp", "fsdp_transpose", "expert", "context", "context_usp_ulysses", "stage")
+    used = set(u.fsdp_axes)
+    for p in u.params:
+      used.update(self.specs[p.name].all_axes)
+    return tuple(a for a in self.mesh.axis_names if a in batch_axes and self.mesh.shape[a] > 1 and a not in used
+                 and a != "stage")
+
+  # ------------------------------------------------------------------ full tensors / reference tree
+  def full_master(self, p: Param) -> torch.Tensor:
+    """fp32 master value of one whole parameter (collective over the unit's shard group)."""
+    u = self.unit_of(p)
+    shard = self.shard_view(u, self.master)
+    if u.group_size > 1:
+      full = torch.empty(u.numel, dtype=shard.dtype, device=shard.device)
+      dist.all_gather_into_tensor(full, shard.contiguous(), group=u.group)
+    else:
+      full = shard
+    off = u.offsets[u.params.index(p)]
+    return full[off: off + p.pdef.numel].view(p.pdef.shape)
+
+  def unit_of(self, p: Param) -> Unit:
+    for u in self.units.values():
+      if p in u.params:
+        return u
+    raise KeyError(p.name)
+
+  def load_full(self, name: str, value: torch.Tensor):
+    """Set a parameter from a whole internal-layout tensor; every rank keeps its own chunk."""
+    p = self.params[name]
+    u = self.unit_of(p)
+    off = u.offsets[u.params.index(p)]
+    lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+    a, b = max(off, lo), min(off + p.pdef.numel, hi)
+    if a < b:
+      flat = value.reshape(-1)
+      self.shard_view(u, self.master)[a - lo: b - lo].copy_(flat[a - off: b - off].to(self.weight_dtype))
+
+  def named_specs(self) -> dict:
+    return dict(self.specs)
+
+  def num_parameters(self) -> int:
+    return sum(p.pdef.numel for p in self.params.values())
+
+
+# ---------------------------------------------------------------------- reference layout conversion
+def to_ref_layout(pdef: ParamDef, t: torch.Tensor) -> torch.Tensor:
+  if pdef.kind == "linear":
+    n_in = int(math.prod(pdef.ref_shape[:pdef.n_in_dims]))
+    return t.reshape(-1, n_in).t().reshape(pdef.ref_shape)
+  if pdef.kind == "expert_linear":   # internal [E, out, in] <-> ref [E, in, out]
+    return t.transpose(-1, -2).reshape(pdef.ref_shape)
+  return t.reshape(pdef.ref_shape)
+
+
+def from_ref_layout(pdef: ParamDef, t: torch.Tensor) -> torch.Tensor:
+  if pdef.kind == "linear":
+    n_in = int(math.prod(pdef.ref_shape[:pdef.n_in_dims]))
+    return t.reshape(n_in, -1).t().contiguous().reshape(pdef.shape)
+  if pdef.kind == "expert_linear":
+    return t.reshape(pdef.ref_shape).transpose(-1, -2).contiguous().reshape(pdef.shape)
+  return t.reshape(pdef.shape)

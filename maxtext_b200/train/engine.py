@@ -1,0 +1,337 @@
+"""Hand-scheduled training step.
+
+Where MaxText traces `train_step` once and lets XLA schedule the collectives
+(src/maxtext/trainers/pre_train/train.py:422-746; FSDP all-gather / reduce-scatter are implicit,
+overlap comes from the latency-hiding scheduler flags in src/maxtext/configs/gpu/a3/llama_2_7b/1vm.sh),
+this engine runs the model unit by unit with an explicit schedule:
+
+  forward   : [prefetch gather(u+1)] -> no-grad forward(u), keep the layer input (+ the tensors named by
+              remat_policy) -> release(u)
+  head      : fused output projection + cross entropy computes the loss AND d(hidden) in one pass
+  backward  : [prefetch gather(u-1)] -> recompute forward(u) with autograd -> backward -> dW lands in the
+              fp32 gradient buffer of the unit -> async reduce-scatter(u) -> release(u)
+  update    : global grad norm (one scalar all-reduce) -> clip factor and 1/total_weights stay on the
+              device -> single fused AdamW launch over the local flat shard
+
+The same code path serves one GPU (nothing to gather) and any FSDP/DP layout of the mesh. The
+step-wise API (`fwd_bwd` may be called several times before `update`) matches
+src/maxtext/training_engine/maxtext_engine.py:333-384 and implements gradient accumulation with
+token-weighted normalisation (src/maxtext/utils/gradient_accumulation.py:110-190).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..models.transformer import Transformer
+from ..ops import functional as F
+from ..optimizers import factory as opt_factory
+from ..optimizers.schedules import make_schedule
+
+EPS = 1e-8
+
+
+class TrainEngine:
+  def __init__(self, config, mesh=None, device=None, model: Transformer | None = None, init: bool = True):
+    self.config = c = config
+    self.mesh = mesh
+    if device is None:
+      device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and c.hardware != "cpu" \
+          else torch.device("cpu")
+    self.device = torch.device(device)
+    self.model = model or Transformer(c, mesh, self.device)
+    self.store = self.model.store
+    if init:
+      self.store.initialize(seed=c.init_weights_seed)
+    self.schedule = make_schedule(c)
+    self.optimizer = opt_factory.make_optimizer(c, self.store, self.model)
+    self.step_count = 0
+    self.world = mesh.world if mesh is not None else 1
+    self._accum = None
+    self._units = self._ordered_units()
+    self.n_moe_layers = sum(1 for l in self.model.layers for b in l.plan.blocks if b.mlp in ("moe", "moe_shared"))
+    self.all_group = None  # WORLD
+
+  # ------------------------------------------------------------------ unit bookkeeping
+  def _ordered_units(self):
+    """Store units in execution order: embed*, layer_i*, head* (a logical unit may be split by shard group)."""
+    order = []
+    for name in self.model.units_in_order():
+      order.append([u for k, u in self.store.units.items() if k == name or k.startswith(name + "#")])
+    return order
+
+  def _gather(self, idx, async_op=True):
+    if 0 <= idx < len(self._units):
+      for u in self._units[idx]:
+        if u.group_size > 1 and not u.resident:
+          u._work = self.store.gather_unit(u, async_op=async_op)
+
+  def _wait_gather(self, idx):
+    for u in self._units[idx]:
+      w = getattr(u, "_work", None)
+      if w is not None:
+        w.wait()
+        u._work = None
+
+  def _release(self, idx):
+    for u in self._units[idx]:
+      self.store.release_full(u)
+
+  # ------------------------------------------------------------------ forward + backward
+  def fwd_bwd(self, batch: dict, compute_grads: bool = True) -> dict:
+    """Accumulates gradients of sum_t w_t * loss_t (+ scaled aux losses) into the gradient shards.
+
+    batch: inputs, targets [B,S] int; inputs_position, inputs_segmentation, targets_segmentation optional.
+    """
+    c, model, store = self.config, self.model, self.store
+    tokens = batch["inputs"].to(self.device, non_blocking=True)
+    targets = batch["targets"].to(self.device, non_blocking=True)
+    B, S = tokens.shape
+    positions = batch.get("inputs_position")
+    positions = positions.to(self.device, non_blocking=True) if positions is not None else \
+        torch.arange(S, device=self.device, dtype=torch.int32)[None].expand(B, S)
+    seg = batch.get("inputs_segmentation")
+    seg = seg.to(self.device, non_blocking=True) if seg is not None else None
+    tseg = batch.get("targets_segmentation")
+    weights = (tseg.to(self.device) != 0).float() if tseg is not None else torch.ones(B, S, device=self.device)
+    if seg is not None and bool(getattr(c, "_assume_dense_segments", False)):
+      seg = None
+
+    first_micro = self._accum is None
+    if first_micro:
+      self._accum = dict(loss_sum=torch.zeros((), device=self.device), z_sum=torch.zeros((), device=self.device),
+                         weights=torch.zeros((), device=self.device), aux=torch.zeros((), device=self.device), micro=0)
+      if compute_grads:
+        store.begin_step()
+    acc = self._accum
+    acc["micro"] += 1
+    accumulate_rs = compute_grads and not first_micro
+
+    n_units = len(self._units)
+    ctx = model.make_ctx(positions, seg, "train", tokens)
+    # ---- forward
+    self._gather(0, async_op=False)
+    self._gather(1)
+    x = self._run_embed(tokens, positions, grad=False)
+    self._release(0) if self._units[0] and self._units[0][0].group_size > 1 and not c.logits_via_embedding else None
+    ckpts = []
+    for i, layer in enumerate(model.layers):
+      ui = i + 1
+      self._wait_gather(ui)
+      self._gather(ui + 1)
+      saved = {}
+      ctx.saved, ctx.recompute, ctx.layer_index, ctx.aux_losses = saved, False, i, []
+      with torch.no_grad():
+        y = layer(x, ctx)
+      aux_val = sum(a for _, a in ctx.aux_losses) if ctx.aux_losses else None
+      if aux_val is not None:
+        acc["aux"] += aux_val.detach().float()
+      ckpts.append((x, saved))
+      x = y
+      if not (i == len(model.layers) - 1):
+        self._release(ui)
+    # ---- head: loss and d(hidden) in one pass
+    hi = n_units - 1
+    self._wait_gather(hi)
+    if c.logits_via_embedding:
+      self._gather(0, async_op=False)
+    w_flat = weights.reshape(-1)
+    total_w = w_flat.sum()
+    head_units = self._units[hi] + (self._units[0] if c.logits_via_embedding else [])
+    if compute_grads:
+      for u in head_units:
+        store.acquire_full_grad(u)
+    loss_sum, z_sum, dx = self._run_head(x, targets.reshape(-1), w_flat, compute_grads)
+    acc["loss_sum"] += loss_sum
+    acc["z_sum"] += z_sum
+    acc["weights"] += total_w
+    if not compute_grads:
+      for i in range(n_units):
+        self._release(i)
+      return acc
+    self._finish_unit_grads(hi, accumulate_rs, skip_embed=True)
+    self._release(hi)
+    # ---- backward through the layers
+    aux_scale = None
+    if self.n_moe_layers and c.load_balance_loss_weight > 0:
+      aux_scale = self._global_weight(total_w) / self.n_moe_layers
+    self._gather(len(model.layers) - 1)  # unit index of layer L-2 is L-1
+    for i in reversed(range(len(model.layers))):
+      ui = i + 1
+      layer = model.layers[i]
+      self._wait_gather(ui)
+      self._gather(ui - 1)
+      for u in self._units[ui]:
+        store.acquire_full_grad(u)
+      x_in, saved = ckpts.pop()
+      x_in = x_in.detach().requires_grad_(True)
+      ctx.saved, ctx.recompute, ctx.layer_index, ctx.aux_losses = saved, True, i, []
+      with torch.enable_grad():
+        y = layer(x_in, ctx)
+        outs, grads = [y], [dx]
+        if aux_scale is not None and ctx.aux_losses:
+          for _, a in ctx.aux_losses:
+            outs.append(a)
+            grads.append(aux_scale.to(a.dtype))
+      torch.autograd.backward(outs, grads)
+      dx = x_in.grad
+      del y, outs, grads, x_in, saved
+      for p in layer.params:
+        p.collect_leaf_grad()
+      self._finish_unit_grads(ui, accumulate_rs)
+      self._release(ui)
+    # ---- embedding backward
+    self._wait_gather(0)
+    emb_units = self._units[0]
+    if not c.logits_via_embedding:
+      for u in emb_units:
+        store.acquire_full_grad(u)
+    self._run_embed(tokens, positions, grad=True, dx=dx)
+    self._finish_unit_grads(0, accumulate_rs)
+    self._release(0)
+    return acc
+
+  def _global_weight(self, total_w):
+    if self.world > 1:
+      t = total_w.clone()
+      dist.all_reduce(t)
+      return t
+    return total_w
+
+  def _run_embed(self, tokens, positions, grad: bool, dx=None):
+    model = self.model
+    if not grad:
+      with torch.no_grad():
+        return model.embed(tokens, positions)
+    with torch.enable_grad():
+      x = model.embed(tokens, positions)
+    torch.autograd.backward([x], [dx])
+    for p in model.embed_params:
+      p.collect_leaf_grad()
+    return None
+
+  def _run_head(self, x, targets, weights, compute_grads):
+    c, model = self.config, self.model
+    B, S, D = x.shape
+    x_in = x.detach().requires_grad_(compute_grads)
+    with torch.set_grad_enabled(compute_grads):
+      h = model.final_norm(x_in)
+    chunk = max(256, (B * S) // max(1, c.num_vocab_tiling)) if c.num_vocab_tiling > 1 else min(B * S, 2048)
+    loss_sum, z_sum, dh = F.fused_head_loss(h.detach().reshape(B * S, D), model.head_param(), targets, weights,
+                                            c.z_loss_multiplier, c.final_logits_soft_cap, chunk, model.head_logit_scale(),
+                                            compute_grads)
+    dx = None
+    if compute_grads:
+      torch.autograd.backward([h], [dh.view(B, S, D)])
+      dx = x_in.grad
+      for p in model.head_params:
+        p.collect_leaf_grad()
+    return loss_sum, z_sum, dx
+
+  def _finish_unit_grads(self, idx, accumulate, skip_embed=False):
+    """Launch the reduce-scatter (and replica all-reduce) of every store unit behind schedule slot `idx`."""
+    store = self.store
+    units = list(self._units[idx])
+    if idx == len(self._units) - 1 and self.config.logits_via_embedding and not skip_embed:
+      pass
+    for u in units:
+      if u.group_size > 1:
+        store.reduce_scatter_unit(u, async_op=False, accumulate=accumulate)
+        store.release_full_grad(u)
+
+  # ------------------------------------------------------------------ update
+  def update(self) -> dict:
+    """Normalise, clip, apply the optimizer; returns device-side metrics (no host sync here)."""
+    c, store = self.config, self.store
+    acc = self._accum
+    assert acc is not None, "update() called before fwd_bwd()"
+    self._accum = None
+    store.finish_resident_grads()
+    stats = torch.stack([acc["loss_sum"], acc["z_sum"], acc["weights"], acc["aux"]])
+    if self.world > 1:
+      dist.all_reduce(stats)
+      stats[3] /= self.world
+    loss_sum, z_sum, total_w, aux = stats[0], stats[1], stats[2], stats[3]
+    aux = aux / max(1, acc["micro"]) / max(1, self.n_moe_layers)
+    inv_w = 1.0 / (total_w + EPS)
+    # replica (data-parallel) gradient reduction for units replicated across batch axes
+    self._reduce_replicas()
+    raw_sq = self._grad_sumsq()
+    raw_norm = torch.sqrt(raw_sq) * inv_w
+    thr = float(c.gradient_clipping_threshold)
+    if thr > 0:
+      clip = torch.where(raw_norm < thr, torch.ones_like(raw_norm), thr / (raw_norm + 1e-30))
+    else:
+      clip = torch.ones_like(raw_norm)
+    grad_scale = (clip * inv_w).reshape(1).float()
+    lr = self.schedule(self.step_count)
+    opt_metrics = self.optimizer.step(grad_scale, lr, self.step_count + 1, loss=(loss_sum * inv_w), grad_norm=raw_norm)
+    self.step_count += 1
+    lm_loss = loss_sum * inv_w
+    metrics = {
+        "learning/loss": lm_loss + aux, "learning/lm_loss": lm_loss, "learning/z_loss": z_sum * inv_w,
+        "learning/moe_lb_loss": aux, "learning/total_weights": total_w, "learning/raw_grad_norm": raw_norm,
+        "learning/grad_norm": raw_norm * clip, "learning/current_learning_rate": torch.tensor(lr),
+    }
+    metrics.update(opt_metrics)
+    return metrics
+
+  def _reduce_replicas(self):
+    store, mesh = self.store, self.mesh
+    if mesh is None or self.world == 1:
+      return
+    for u in store.units.values():
+      axes = store.replica_axes(u)
+      if axes:
+        g = mesh.group(axes)
+        if g is not None:
+          dist.all_reduce(store.shard_view(u, store.grad_shard), group=g)
+
+  def _grad_sumsq(self):
+    """Sum of squares of the (un-normalised) global gradient: local shards, de-duplicated, all-reduced."""
+    store = self.store
+    if self.world == 1:
+      return F.sum_of_squares(store.grad_shard)
+    total = torch.zeros((), dtype=torch.float32, device=self.device)
+    for u in store.units.values():
+      sq = F.sum_of_squares(store.shard_view(u, store.grad_shard))
+      total = total + sq / self._replication(u)
+    dist.all_reduce(total)
+    return total
+
+  def _replication(self, u) -> float:
+    """How many ranks hold an identical copy of this unit's gradient shard."""
+    mesh = self.mesh
+    distinct = u.group_size
+    tp = mesh.axis_size(("tensor", "tensor_sequence"))
+    if tp > 1 and any(p.pdef.tp_dim is not None for p in u.params):
+      distinct *= tp
+    ep = mesh.axis_size("expert")
+    if ep > 1 and any(p.pdef.ep_dim is not None for p in u.params):
+      distinct *= ep
+    return max(1.0, self.world / distinct)
+
+  def train_step(self, batch: dict) -> dict:
+    """One optimizer step over `gradient_accumulation_steps` micro-batches split along the batch dim."""
+    g = int(self.config.gradient_accumulation_steps)
+    if g == 1:
+      self.fwd_bwd(batch)
+    else:
+      B = batch["inputs"].shape[0]
+      assert B % g == 0, "batch must divide by gradient_accumulation_steps"
+      mb = B // g
+      for k in range(g):
+        self.fwd_bwd({key: v[k * mb:(k + 1) * mb] for key, v in batch.items()})
+    return self.update()
+
+  @torch.no_grad()
+  def eval_step(self, batch: dict) -> dict:
+    acc = self.fwd_bwd(batch, compute_grads=False)
+    self._accum = None
+    stats = torch.stack([acc["loss_sum"], acc["weights"]])
+    if self.world > 1:
+      dist.all_reduce(stats)
+    return {"evaluation/total_loss": stats[0], "evaluation/total_weights": stats[1],
+            "evaluation/loss": stats[0] / (stats[1] + EPS)}

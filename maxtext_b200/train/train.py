@@ -1,0 +1,129 @@
+"""Pre-training entry point: `python -m maxtext.train <config.yml> key=value ...`.
+
+The counterpart of src/maxtext/trainers/pre_train/train.py (`main` 1143, `train_loop` 912-1069):
+configuration -> distributed runtime + mesh -> model / optimizer / data -> step loop with metrics,
+profiler window, periodic checkpoints and evaluation. The step itself is
+`train.engine.TrainEngine.train_step`.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import torch
+
+from ..config import pyconfig
+from ..parallel import mesh as mesh_lib
+from ..utils import max_logging
+from ..utils.metric_logger import MetricLogger
+from . import engine as engine_lib
+
+
+BATCH_AXES = ("data", "fsdp", "fsdp_transpose", "expert")
+
+
+def data_shard(mesh) -> tuple[int, int]:
+  """(index, count) of this rank's slice of the global batch: ranks that differ only along
+  sequence/tensor/stage axes read the same rows."""
+  if mesh is None:
+    return 0, 1
+  axes = tuple(a for a in mesh.axis_names if a in BATCH_AXES)
+  return mesh.axis_index(axes), mesh.axis_size(axes)
+
+
+def create_data_iterator(config, mesh):
+  from ..input_pipeline import interface
+  return interface.create_data_iterator(config, *data_shard(mesh))
+
+
+class StopTraining(Exception):
+  """Raised to end the loop early and cleanly (e.g. target eval loss reached)."""
+
+
+def setup(config, device=None):
+  rank, world, local_rank = mesh_lib.init_distributed(int(config.jax_distributed_initialization_timeout))
+  if world != config.num_target_devices:
+    config = config.replace(_num_devices=world)
+  mesh = mesh_lib.mesh_from_config(config, rank=rank, world=world) if world > 1 else None
+  if device is None:
+    use_cuda = torch.cuda.is_available() and config.hardware != "cpu"
+    device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+  eng = engine_lib.TrainEngine(config, mesh, device)
+  return config, mesh, eng
+
+
+def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None):
+  from ..checkpoint import manager as ckpt_lib
+  from ..utils import profiler as prof_lib, goodput
+  if engine is None:
+    config, mesh, engine = setup(config)
+  c = config
+  rank = mesh.rank if mesh is not None else 0
+  recorder = recorder or goodput.create_recorder(c, rank)
+  data_iterator = data_iterator or create_data_iterator(c, mesh)
+  logger = MetricLogger(c, is_writer=(rank == 0))
+  prof = prof_lib.Profiler(c, rank)
+  ckpt = ckpt_lib.CheckpointManager(c, engine, mesh) if c.enable_checkpointing and c.checkpoint_dir else None
+  start_step = 0
+  if ckpt is not None:
+    restored = ckpt.restore_if_possible(data_iterator)
+    if restored is not None:
+      start_step = restored
+  elif c.load_parameters_path:
+    ckpt_lib.load_params_only(c.load_parameters_path, engine)
+  engine.step_count = start_step
+  is_cuda = engine.device.type == "cuda"
+  try:
+    for step in range(start_step, int(c.steps)):
+      prof.maybe_start(step)
+      t0 = time.perf_counter()
+      with recorder.span("DATA_LOADING", step):
+        batch = next(data_iterator)
+      with recorder.span("STEP", step):
+        metrics = engine.train_step(batch)
+        if is_cuda and (c.profile_cleanly or True):
+          torch.cuda.synchronize()
+      dt = time.perf_counter() - t0
+      logger.record(step, metrics, dt)
+      if ckpt is not None:
+        ckpt.maybe_save(step, data_iterator)
+      if c.eval_interval > 0 and step >= c.eval_start_step and (step + 1) % c.eval_interval == 0:
+        ev = run_eval(c, engine, mesh)
+        if rank == 0:
+          max_logging.log(f"eval step {step}: loss {ev:.4f}")
+        if c.target_eval_loss > 0 and ev <= c.target_eval_loss:
+          raise StopTraining(f"target eval loss {c.target_eval_loss} reached")
+      prof.maybe_stop(step)
+  except StopTraining as e:
+    max_logging.log(f"training stopped: {e}")
+  finally:
+    if ckpt is not None:
+      if c.save_checkpoint_on_completion:
+        ckpt.save(engine.step_count - 1, data_iterator, force=True)
+      ckpt.wait_until_finished()
+    logger.close()
+    prof.close()
+    recorder.close()
+  return engine, logger.history
+
+
+def run_eval(config, engine, mesh) -> float:
+  it = create_data_iterator(config, mesh)
+  tot, w = 0.0, 0.0
+  n = config.eval_steps if config.eval_steps > 0 else 1
+  for _ in range(n):
+    m = engine.eval_step(next(it))
+    tot += float(m["evaluation/total_loss"].item())
+    w += float(m["evaluation/total_weights"].item())
+  return tot / max(w, 1e-8)
+
+
+def main(argv=None):
+  argv = list(sys.argv if argv is None else argv)
+  config = pyconfig.initialize(argv)
+  return train_loop(config)
+
+
+if __name__ == "__main__":
+  main()
