@@ -1,0 +1,224 @@
+"""Headline benchmark: Llama-3-8B pre-training throughput (tokens/s, whole job) in bf16 with fp32
+master weights and AdamW, sequence 8192, per-device batch 2, remat_policy=full, FSDP over N GPUs.
+
+  python bench.py --gpus 1 --steps 5 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints one JSON line. `value` is device-timed (CUDA events, max over ranks) over exactly K
+optimizer steps; `e2e` repeats the measurement through the public API including, every step, the
+host->device copy of the batch from pinned memory and a device->host read of the loss.
+`--impl reference` would run the unmodified reference (JAX) from baseline/_ref; it cannot be imported
+here and reports why.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PUBLISHED_TOK_S_PER_DEVICE = 7207.0   # Llama 3.1 8B, seq 8192, bf16, per device (docs/reference/models/tiering.md:16)
+NOMINAL_BF16_TFLOPS = 2250.0
+
+
+def reference_arm(args):
+  why = None
+  ref_dir = os.path.join(ROOT, "baseline", "_ref")
+  try:
+    sys.path.insert(0, ref_dir)
+    import jax  # noqa: F401  the reference's train step is a jax.jit program
+  except Exception as e:  # pylint: disable=broad-except
+    why = f"reference needs JAX (+jaxlib CUDA, flax, optax, orbax, grain) which are not installable offline here: {type(e).__name__}: {e}"
+  if why is None:
+    why = "reference runtime present but its GPU stack (jax[cuda12], transformer-engine-jax) is not in the offline wheelhouse"
+  print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}))
+  return 0
+
+
+class ClockSampler:
+  """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+  Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+       "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, gpu_index: int):
+    self.gpu = gpu_index
+    self.rows = []
+    self.proc = None
+    self.path = None
+
+  def start(self):
+    try:
+      fd, self.path = tempfile.mkstemp(suffix=".csv")
+      os.close(fd)
+      self.fh = open(self.path, "w")
+      self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                    "-i", str(self.gpu)], stdout=self.fh, stderr=subprocess.DEVNULL)
+    except Exception:  # pylint: disable=broad-except
+      self.proc = None
+
+  def stop(self) -> dict:
+    out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    if self.proc is None:
+      return out
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except Exception:  # pylint: disable=broad-except
+      self.proc.kill()
+    self.fh.close()
+    sm, mx, reasons = [], [], set()
+    with open(self.path) as fh:
+      for line in fh:
+        p = [x.strip() for x in line.split(",")]
+        if len(p) < 9:
+          continue
+        try:
+          sm.append(float(p[1]))
+          mx.append(float(p[2]))
+        except ValueError:
+          continue
+        for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+          if v.lower().startswith("active"):
+            reasons.add(name)
+    os.unlink(self.path)
+    if sm:
+      out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+    return out
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=4)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours")
+  ap.add_argument("--model", default="llama3-8b")
+  ap.add_argument("--seq", type=int, default=8192)
+  ap.add_argument("--pdbs", type=float, default=2.0)
+  ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is then not the headline config)")
+  ap.add_argument("--no-e2e", action="store_true")
+  args = ap.parse_args()
+  if args.impl == "reference":
+    return reference_arm(args)
+
+  import torch
+  import torch.distributed as dist
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.input_pipeline.synthetic import SyntheticDataIterator
+  from maxtext_b200.ops import backend
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as train_lib
+  from maxtext_b200.train.engine import TrainEngine
+  from maxtext_b200.utils import flops
+
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N>1 with torch.distributed.run"
+  rank, world, local_rank = mesh_lib.init_distributed()
+  dev = torch.device("cuda", torch.cuda.current_device())
+  overrides = [f"model_name={args.model}", f"per_device_batch_size={args.pdbs}", f"max_target_length={args.seq}",
+               "dataset_type=synthetic", "remat_policy=full", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal",
+               "log_config=false", "steps=1000", "learning_rate=3e-5", f"ici_fsdp_parallelism={world}", "dtype=bfloat16",
+               "weight_dtype=float32", "attention=flash"]
+  if args.layers > 0:
+    overrides += [f"base_num_decoder_layers={args.layers}", "override_model_config=true"]
+  cfg = pyconfig.initialize(["bench", os.path.join(ROOT, "maxtext_b200", "configs", "base.yml")] + overrides, num_devices=world)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world) if world > 1 else None
+  E = backend.ext(required=True)
+  eng = TrainEngine(cfg, mesh, dev)
+  it = SyntheticDataIterator(cfg, *train_lib.data_shard(mesh))
+  batch = next(it)   # pinned host tensors; every step copies them to the device
+
+  def barrier():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  for _ in range(args.warmup):
+    m = eng.train_step(batch)
+  barrier()
+  assert E.kernel_status(True) == 0, "kernel wait timed out during warm-up"
+
+  # ---- device-timed region
+  sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                         int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[torch.cuda.current_device()]))
+  sampler.start()
+  launches0 = E.launch_count()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  barrier()
+  e0.record()
+  for _ in range(args.steps):
+    m = eng.train_step(batch)
+  e1.record()
+  barrier()
+  ms = e0.elapsed_time(e1)
+  launches = E.launch_count() - launches0
+  clocks = sampler.stop()
+  loss = float(m["learning/loss"])
+  t = torch.tensor([ms], device=dev)
+  if world > 1:
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+  ms = float(t.item())
+
+  # ---- end-to-end through the public API: H2D of the batch from pinned memory + D2H of the loss, every step
+  e2e = None
+  if not args.no_e2e:
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+      mm = eng.train_step(batch)
+      _ = float(mm["learning/loss"])       # device -> host read of the step result
+    barrier()
+    dt = time.perf_counter() - t0
+    tt = torch.tensor([dt], device=dev)
+    if world > 1:
+      dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    dt = float(tt.item())
+    h2d = sum(v.numel() * v.element_size() for k, v in batch.items()
+              if k in ("inputs", "targets", "inputs_position", "inputs_segmentation", "targets_segmentation"))
+    tokens_total = cfg.global_batch_size_to_train_on * cfg.max_target_length * args.steps
+    e2e = {"value": tokens_total / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
+           "ms_per_step": 1e3 * dt / args.steps}
+  status = E.kernel_status(True)
+
+  if rank == 0:
+    gb = cfg.global_batch_size_to_train_on
+    tokens = gb * cfg.max_target_length * args.steps
+    value = tokens / (ms / 1e3)
+    tflops_step, _, _ = flops.training_tflops_per_device(cfg)
+    tf_s = tflops_step / (ms / 1e3 / args.steps)
+    peaks = {}
+    try:
+      peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:  # pylint: disable=broad-except
+      pass
+    out = {
+        "metric": "tokens/sec (whole job) Llama-3-8B FSDP bf16 seq 8192 pre-training", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": value / (PUBLISHED_TOK_S_PER_DEVICE * world), "dtype": "bf16", "data": "synthetic",
+        "config": {"model": args.model + ("" if args.layers <= 0 else f"-{args.layers}layers-DEBUG"), "global_batch": gb,
+                   "seq_len": cfg.max_target_length, "parallelism": f"fsdp{world}", "remat_policy": cfg.remat_policy,
+                   "optimizer": "adamw fp32 master", "l2": "inputs_larger_than_L2 (16 GB of weights streamed per step)"},
+        "tokens_per_sec_per_gpu": value / world, "model_tflops_per_sec_per_gpu": tf_s,
+        "mfu_of_nominal_2250": tf_s / NOMINAL_BF16_TFLOPS,
+        "mfu_of_measured_cublas_sustained": tf_s / peaks["bf16_tflops_sustained"] if peaks.get("bf16_tflops_sustained") else None,
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
+        "e2e": e2e, "gpu_launches": int(launches), "final_loss": loss, "kernel_status": int(status), "impl": "ours",
+    }
+    print(json.dumps(out))
+  if world > 1:
+    dist.destroy_process_group()
+  return 0
+
+
+if __name__ == "__main__":
+  sys.exit(main())

@@ -1,0 +1,73 @@
+"""Times the tcgen05 GEMM against torch.matmul (cuBLAS) on the Llama-3-8B layer shapes.
+
+  python -m maxtext_b200.benchmarks.gemm_bench [--tokens 16384] [--iters 10] [--small]
+
+CUDA events on the launching stream, 3 warm-up launches, operands far larger than L2 in aggregate
+(each shape allocates its own tensors and the loop alternates between two operand sets).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def time_fn(fn, iters):
+  for _ in range(3):
+    fn(0)
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for i in range(iters):
+    fn(i)
+  e1.record()
+  torch.cuda.synchronize()
+  return e0.elapsed_time(e1) / iters
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--tokens", type=int, default=16384)
+  ap.add_argument("--iters", type=int, default=10)
+  ap.add_argument("--small", action="store_true", help="one small shape only (profiling)")
+  ap.add_argument("--no-cublas", action="store_true")
+  args = ap.parse_args()
+  from maxtext_b200.ops import backend
+  E = backend.ext(required=True)
+  T = args.tokens
+  D, F, QKV = 4096, 14336, 6144
+  shapes = [("qkv fwd", T, QKV, D, False, True, torch.bfloat16), ("mlp up fwd", T, 2 * F, D, False, True, torch.bfloat16),
+            ("mlp down fwd", T, D, F, False, True, torch.bfloat16), ("mlp up dX", T, D, 2 * F, False, False, torch.bfloat16),
+            ("mlp down dX", T, F, D, False, False, torch.bfloat16), ("mlp up dW", 2 * F, D, T, True, False, torch.float32),
+            ("mlp down dW", D, F, T, True, False, torch.float32)]
+  if args.small:
+    shapes = [("small", 4096, 4096, 4096, False, True, torch.bfloat16)]
+  rows = []
+  for name, M, N, K, ta, tb, odt in shapes:
+    sets = []
+    for _ in range(2):
+      a = torch.randn((K, M) if ta else (M, K), device="cuda").bfloat16()
+      b = torch.randn((N, K) if tb else (K, N), device="cuda").bfloat16()
+      sets.append((a, b))
+    out = torch.empty(M, N, device="cuda", dtype=odt)
+    ms = time_fn(lambda i: E.gemm(sets[i & 1][0], sets[i & 1][1], out, ta, tb, False), args.iters)
+    row = {"shape": name, "M": M, "N": N, "K": K, "ta": ta, "tb": tb, "out": str(odt).split(".")[-1], "ms": ms,
+           "tflops": 2.0 * M * N * K / ms / 1e9}
+    if not args.no_cublas:
+      def cb(i):
+        a, b = sets[i & 1]
+        r = torch.mm(a.t() if ta else a, b.t() if tb else b)
+        if odt == torch.float32:
+          out.copy_(r)
+      ms2 = time_fn(cb, args.iters)
+      row.update(cublas_ms=ms2, cublas_tflops=2.0 * M * N * K / ms2 / 1e9, ratio=ms2 / ms)
+    rows.append(row)
+    print(json.dumps(row), flush=True)
+    del sets, out
+  st = E.kernel_status(True)
+  print(json.dumps({"kernel_status": st}))
+
+
+if __name__ == "__main__":
+  main()

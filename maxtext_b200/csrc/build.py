@@ -1,0 +1,39 @@
+"""In-tree build of the sm_100a kernel library (`csrc/build/maxtext_b200_C.so`).
+
+`python -m maxtext_b200.csrc.build` compiles every .cu/.cpp of this directory for
+`-gencode arch=compute_100a,code=sm_100a` with ninja through torch.utils.cpp_extension and leaves the
+shared object next to the sources so that it ships with the tree. nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import glob
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+BUILD_DIR = os.path.join(HERE, "build")
+EXT_NAME = "maxtext_b200_C"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--use_fast_math", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xptxas", "-v", "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__",
+]
+
+
+def sources() -> list[str]:
+  return sorted(glob.glob(os.path.join(HERE, "*.cu")) + glob.glob(os.path.join(HERE, "*.cpp")))
+
+
+def build_extension(verbose: bool = True):
+  from torch.utils import cpp_extension
+  os.makedirs(BUILD_DIR, exist_ok=True)
+  os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
+  mod = cpp_extension.load(
+      name=EXT_NAME, sources=sources(), extra_cflags=["-O2", "-std=c++17"], extra_cuda_cflags=NVCC_FLAGS,
+      extra_include_paths=[HERE], build_directory=BUILD_DIR, with_cuda=True, verbose=verbose)
+  return mod
+
+
+if __name__ == "__main__":
+  build_extension(verbose="-q" not in sys.argv)
+  print("built", os.path.join(BUILD_DIR, EXT_NAME + ".so"))

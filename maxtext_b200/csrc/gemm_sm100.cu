@@ -1,0 +1,357 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma with
+// fp32 accumulators in tensor memory -> epilogue through shared memory and TMA stores.
+//
+//   C[M,N] (+)= op(A) * op(B)      op(A) is M x K, op(B) is K x N
+//
+// Operand storage (row-major, leading stride a multiple of 8 elements):
+//   A "K-major"  : A[M,K]      A "MN-major": A[K,M]   (i.e. the transposed operand, no copy needed)
+//   B "K-major"  : B[N,K]      B "MN-major": B[K,N]
+// so the three products of a linear layer map to   fwd  y  = x  W^T : (A K-major,  B K-major)
+//                                                  dX   dx = dy W   : (A K-major,  B MN-major)
+//                                                  dW   dW = dy^T x : (A MN-major, B MN-major)
+// Output is bf16 (plain store) or fp32 (plain store, or a TMA reduce-add when accumulating into an
+// existing gradient buffer, which makes beta = 1 free of any read in the kernel).
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
+// epilogue (each reads its own 32-lane quarter of tensor memory). One CTA per SM, grid = min(tiles,
+// SMs); tiles are walked in groups of GROUP_M row-blocks so that concurrently running CTAs share A and
+// B tiles in L2. Accumulators are double buffered in TMEM (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1. Every wait is bounded (see mbar_wait): on a timeout the kernel
+// records a code in the status word, drains, frees its tensor memory and returns.
+#include "sm100_ptx.cuh"
+#include <cuda_bf16.h>
+
+namespace mt {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GROUP_M = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BYTES = 2 * BM * 128;  // two staging buffers of 128 rows x 128 B
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;  // power of two >= 32
+};
+
+struct GemmParams {
+  int M, N, K;
+  int accumulate;  // fp32 output only: C += result (TMA reduce-add)
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
+  const int per_group = GROUP_M * n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsz = min(GROUP_M, m_blocks - first_m);
+  const int r = t - g * per_group;
+  mb = first_m + (r % gsz);
+  nb = r / gsz;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c, GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a0 = smem_base;
+  const uint32_t smem_b0 = smem_base + STAGES * Cfg::A_BYTES;
+  const uint32_t smem_epi = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = smem_epi + Cfg::EPI_BYTES;
+  // barrier slots (8 bytes each)
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t abort_slot = tmem_slot + 8;
+  uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - smem_base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_slot - smem_base));
+  volatile int* epi_ok = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (p.M + BM - 1) / BM;
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), EPI_THREADS);
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, m_blocks, n_blocks, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_a0 + s * Cfg::A_BYTES;
+          const uint32_t sb = smem_b0 + s * Cfg::B_BYTES;
+          if (!A_MN) {
+            tma_load_2d(sa, &map_a, full_bar(s), kb * BK, mb * BM);                       // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)                                             // boxes {64 m, 64 k}
+              tma_load_2d(sa + j * 8192, &map_a, full_bar(s), mb * BM + j * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &map_b, full_bar(s), kb * BK, nb * BN);                       // box {64 k, BN n}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)                                             // boxes {64 n, 64 k}
+              tma_load_2d(sb + j * 8192, &map_b, full_bar(s), nb * BN + j * 64, kb * BK);
+          }
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t A_LBO = A_MN ? 8192 : 16, B_LBO = B_MN ? 8192 : 16;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32, B_KSTEP = B_MN ? 2048 : 32;  // bytes per UMMA_K
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_a0 + s * Cfg::A_BYTES, A_LBO, 1024);
+          const uint64_t db = make_smem_desc(smem_b0 + s * Cfg::B_BYTES, B_LBO, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_f16_ss(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));   // frees the smem stage when these MMAs retire
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(acc));   // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (128 threads)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;          // row of the tile owned by this thread
+    const int et = threadIdx.x - 64;        // 0..127 within the epilogue group
+    constexpr bool OUT_F32 = sizeof(OutT) == 4;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int mb, nb;
+      tile_coords(t, m_blocks, n_blocks, mb, nb);
+      // one thread waits, the verdict is shared so that all 128 threads leave the loop together
+      if (et == 0) *epi_ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE) ? 1 : 0;
+      named_bar_sync(3, EPI_THREADS);
+      if (*epi_ok == 0) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (c == BN / 32 - 1) {
+          // whole accumulator is in registers: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(tempty_bar(acc));
+        }
+        const bool new_store = OUT_F32 ? true : ((c & 1) == 0);
+        if (new_store) {
+          // the staging buffer we are about to overwrite must have been read by its previous TMA store
+          if (et == 0) tma_wait_group_read<1>();
+          named_bar_sync(1, EPI_THREADS);
+        }
+        const uint32_t sbuf = smem_epi + buf * (BM * 128);
+        if (OUT_F32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {     // 8 chunks of 16 B (4 floats) per 128-byte row
+            const uint32_t dst = sbuf + row * 128 + ((j ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]),
+                         "r"(r[4 * j + 3])
+                         : "memory");
+          }
+        } else {
+          const int half = c & 1;           // which 32-column half of the 64-column store tile
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {     // 4 chunks of 16 B (8 bf16)
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+              pk[e] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            const int chunk = half * 4 + j;
+            const uint32_t dst = sbuf + row * 128 + ((chunk ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                         : "memory");
+          }
+        }
+        const bool do_store = OUT_F32 ? true : ((c & 1) == 1);
+        if (do_store) {
+          fence_proxy_async_smem();
+          named_bar_sync(2, EPI_THREADS);
+          if (et == 0) {
+            const int col0 = nb * BN + (OUT_F32 ? c * 32 : (c >> 1) * 64);
+            if (col0 < p.N) {
+              if (OUT_F32 && p.accumulate) tma_reduce_add_2d(&map_c, sbuf, col0, mb * BM);
+              else tma_store_2d(&map_c, sbuf, col0, mb * BM);
+            }
+            tma_commit_group();
+          }
+          buf ^= 1;
+        }
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (et == 0) tma_wait_group<0>();
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // a wait ran out: give in-flight bulk copies time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || !ptr) return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] with leading stride `ld` elements; box = {box_cols, box_rows}, 128B swizzle.
+static int make_map_2d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+                       uint64_t ld, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, GemmParams p, int num_sms, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace mt
+
+// a: A operand storage, lda its leading stride (elements); a_mn = 1 when stored [K, M].
+// b: B operand storage; b_mn = 1 when stored [K, N] (else [N, K]).
+// c: output [M, N] with leading stride ldc; out_f32 selects fp32 output; accumulate needs out_f32.
+// status: device int that receives a non-zero code if a bounded wait timed out. Returns 0 on a successful launch.
+extern "C" int mt_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                            int a_mn, int b_mn, int out_f32, int accumulate, int* status, int num_sms, cudaStream_t stream) {
+  using namespace mt;
+  if (accumulate && !out_f32) return -10;
+  const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
+  CUtensorMap ma, mb, mc;
+  int e;
+  if (!a_mn) e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM);
+  else e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, 64, BK);
+  if (e) return 100 + e;
+  if (!b_mn) e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN);
+  else e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK);
+  if (e) return 200 + e;
+  if (out_f32) e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, BM);
+  else e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
+  if (e) return 300 + e;
+  GemmParams p{M, N, K, accumulate, status};
+#define MT_DISPATCH(BN_)                                                                                             \
+  do {                                                                                                               \
+    if (!a_mn && !b_mn) return out_f32 ? launch<BN_, false, false, float>(ma, mb, mc, p, num_sms, stream)            \
+                                       : launch<BN_, false, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);   \
+    if (!a_mn && b_mn) return out_f32 ? launch<BN_, false, true, float>(ma, mb, mc, p, num_sms, stream)              \
+                                      : launch<BN_, false, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);     \
+    if (a_mn && b_mn) return out_f32 ? launch<BN_, true, true, float>(ma, mb, mc, p, num_sms, stream)                \
+                                     : launch<BN_, true, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);       \
+    return out_f32 ? launch<BN_, true, false, float>(ma, mb, mc, p, num_sms, stream)                                 \
+                   : launch<BN_, true, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);                        \
+  } while (0)
+  if (BN == 256) MT_DISPATCH(256);
+  MT_DISPATCH(128);
+#undef MT_DISPATCH
+}

@@ -288,6 +288,11 @@ def attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, caus
                    kv_seg=kv_segment_ids if kv_segment_ids is not None else segment_ids, causal=causal,
                    sliding_window=window)
   if q.is_cuda:
+    if _ATTN_IMPL == "sdpa" and segment_ids is None and not window and not soft_cap and causal and kv_positions is None:
+      # comparison arm only (library attention); the product path is the flash kernel above
+      o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                           is_causal=True, scale=scale, enable_gqa=q.shape[2] != k.shape[2])
+      return o.transpose(1, 2).contiguous(), None
     return _attention_chunked(q, k, v, mask_args, scale, soft_cap)
   return _sdpa_reference(q, k, v, mask_args, scale, soft_cap)
 
@@ -314,6 +319,17 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
       seg = segment_ids.to(torch.int32).contiguous() if segment_ids is not None else None
       E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, float(scale), int(window))
       return
+  if lse is None:
+    # comparison arm (library attention): differentiate the library call
+    with torch.enable_grad():
+      ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+      o = torch.nn.functional.scaled_dot_product_attention(ql.transpose(1, 2), kl.transpose(1, 2), vl.transpose(1, 2),
+                                                           is_causal=True, scale=scale, enable_gqa=q.shape[2] != k.shape[2])
+      gq, gk, gv = torch.autograd.grad(o, (ql, kl, vl), dout.transpose(1, 2))
+    dq.copy_(gq)
+    dk.copy_(gk)
+    dv.copy_(gv)
+    return
   # reference: recompute probabilities from lse, chunked over queries
   B, Sq, Hq, D = q.shape
   Hkv = k.shape[2]

@@ -96,8 +96,8 @@ class TrainEngine:
     seg = seg.to(self.device, non_blocking=True) if seg is not None else None
     tseg = batch.get("targets_segmentation")
     weights = (tseg.to(self.device) != 0).float() if tseg is not None else torch.ones(B, S, device=self.device)
-    if seg is not None and bool(getattr(c, "_assume_dense_segments", False)):
-      seg = None
+    if c.dataset_type == "synthetic" and not c.packing_in_synthetic:
+      seg = None   # synthetic batches are one segment per row by construction: skip the mask work
 
     first_micro = self._accum is None
     if first_micro:

@@ -1,0 +1,72 @@
+"""tcgen05 GEMM vs an fp32 PyTorch reference: every operand layout, both output types, accumulate,
+ragged sizes (not multiples of the 128 x 256 x 64 tile)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+  from maxtext_b200.ops import backend
+  return backend.ext(required=True)
+
+
+def _run(M, N, K, ta, tb, out_dtype, accumulate=False, seed=0):
+  E = _ext()
+  g = torch.Generator(device="cuda").manual_seed(seed)
+  a = torch.randn((K, M) if ta else (M, K), device="cuda", generator=g).bfloat16()
+  b = torch.randn((N, K) if tb else (K, N), device="cuda", generator=g).bfloat16()
+  ref = (a.float().t() if ta else a.float()) @ (b.float().t() if tb else b.float())
+  if accumulate:
+    out = torch.randn(M, N, device="cuda", generator=g, dtype=out_dtype)
+    ref = ref + out.float()
+  else:
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+  assert E.gemm_supported(a, b, out, ta, tb)
+  E.gemm(a, b, out, ta, tb, accumulate)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0, "a bounded wait inside the GEMM kernel timed out"
+  err = (out.float() - ref).abs().max().item()
+  scale = ref.abs().max().item()
+  tol = (2e-2 if out_dtype == torch.bfloat16 else 2e-3) * max(scale, 1.0)
+  assert err <= tol, f"M={M} N={N} K={K} ta={ta} tb={tb} {out_dtype}: max err {err} (scale {scale})"
+
+
+def test_gemm_smallest_first():
+  # the first launch of the kernel in a process: one tile, one k-block pass
+  _run(128, 256, 64, False, True, torch.bfloat16)
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_layouts(ta, tb, out_dtype):
+  _run(512, 768, 320, ta, tb, out_dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(136, 264, 72), (1000, 520, 200), (128, 128, 64), (4096, 1536, 1024), (2048, 14336, 512)])
+def test_gemm_ragged_and_large(M, N, K):
+  _run(M, N, K, False, True, torch.bfloat16)
+  _run(M, N, K, True, False, torch.float32)
+
+
+def test_gemm_accumulate_fp32():
+  _run(640, 512, 384, True, False, torch.float32, accumulate=True)
+  _run(384, 1024, 256, False, True, torch.float32, accumulate=True)
+
+
+def test_gemm_many_tiles_persistent():
+  # more tiles than SMs: every CTA walks several tiles through both TMEM accumulator buffers
+  _run(8192, 4096, 256, False, True, torch.bfloat16)
+
+
+def test_gemm_strided_views():
+  E = _ext()
+  big = torch.randn(512, 1024, device="cuda").bfloat16()
+  a = big[:, 256:768]           # [512, 512] view with leading stride 1024
+  w = torch.randn(384, 512, device="cuda").bfloat16()
+  out = torch.empty(512, 384, device="cuda", dtype=torch.bfloat16)
+  E.gemm(a, w, out, False, True, False)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0
+  ref = a.float() @ w.float().t()
+  assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
