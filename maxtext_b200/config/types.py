@@ -265,8 +265,6 @@ def derive_and_validate(raw: dict, num_devices: int = 1) -> dict:
     raise ConfigValueError("gradient_accumulation_steps must be >= 1")
   if t["num_vocab_tiling"] < 1:
     raise ConfigValueError("num_vocab_tiling must be >= 1")
-  if t["max_prefill_predict_length"] > t["max_target_length"]:
-    raise ConfigValueError("max_prefill_predict_length cannot exceed max_target_length")
   if t["attention_type"] == "mla" and t["share_kv_projections"]:
     raise ConfigValueError("share_kv_projections is not compatible with attention_type=mla")
   if t["use_dpo"] and t["packing"]:

@@ -38,7 +38,8 @@ class Builder:
   def _add(self, leaf: str, **kw) -> Param:
     path = self.prefix + (leaf,)
     name = "/".join(((f"{self.stack}_{self.layer}",) if self.layer is not None else ()) + path)
-    p = Param(ParamDef(name=name, unit=self.unit, ref_path=path, layer=self.layer, stack=self.stack, **kw))
+    p = Param(ParamDef(name=name, unit=self.unit, ref_path=path, layer=self.layer, stack=self.stack, tp_rank=self.tp_rank,
+                       tp_size=self.tp_size, ep_rank=self.ep_rank, ep_size=self.ep_size, **kw))
     self.params.append(p)
     return p
 

@@ -61,6 +61,29 @@ class ParamDef:
   tp_dim: int | None = None      # internal dim split over tensor axes (already applied to `shape`)
   ep_dim: int | None = None      # internal dim split over the expert axis (already applied)
   fsdp_axes: tuple = ()          # mesh axes of the flat shard group (filled by the store)
+  tp_rank: int = 0
+  tp_size: int = 1
+  ep_rank: int = 0
+  ep_size: int = 1
+
+  def global_shape(self) -> tuple:
+    """Internal-layout shape before tensor / expert parallel slicing."""
+    s = list(self.shape)
+    if self.tp_dim is not None:
+      s[self.tp_dim] *= self.tp_size
+    if self.ep_dim is not None:
+      s[self.ep_dim] *= self.ep_size
+    return tuple(s)
+
+  def local_slice(self, t):
+    """This rank's tensor / expert parallel slice of a global internal-layout tensor."""
+    if self.tp_dim is not None and self.tp_size > 1:
+      n = self.shape[self.tp_dim]
+      t = t.narrow(self.tp_dim, self.tp_rank * n, n)
+    if self.ep_dim is not None and self.ep_size > 1:
+      n = self.shape[self.ep_dim]
+      t = t.narrow(self.ep_dim, self.ep_rank * n, n)
+    return t
 
   @property
   def numel(self) -> int:
@@ -141,15 +164,15 @@ def init_full_tensor(pdef: ParamDef, device, base_seed: int, mode: str = "refere
   matrix (the tiny-model and benchmark configurations)."""
   gen = torch.Generator(device="cpu" if str(device) == "cpu" else device)
   gen.manual_seed(_seed_for(pdef.name, base_seed))
-  shape = pdef.shape
   if pdef.init == "ones":
-    return torch.ones(shape, dtype=torch.float32, device=device)
+    return torch.ones(pdef.shape, dtype=torch.float32, device=device)
   if pdef.init == "zeros":
-    return torch.zeros(shape, dtype=torch.float32, device=device)
-  t = torch.empty(shape, dtype=torch.float32, device=device)
+    return torch.zeros(pdef.shape, dtype=torch.float32, device=device)
+  # draw the whole tensor, then keep this rank's tensor/expert-parallel slice: values do not depend on the mesh
+  t = torch.empty(pdef.global_shape(), dtype=torch.float32, device=device)
   if mode == "normal" or pdef.init == "normal":
     t.normal_(0.0, std, generator=gen)
-    return t * pdef.init_scale
+    return pdef.local_slice(t).contiguous() * pdef.init_scale
   if pdef.kind == "linear":
     fan_in = int(math.prod(pdef.ref_shape[:pdef.n_in_dims]))
   elif pdef.init == "embed":
@@ -162,7 +185,7 @@ def init_full_tensor(pdef: ParamDef, device, base_seed: int, mode: str = "refere
     t.mul_(s / 0.87962566103423978)
   else:
     t.normal_(0.0, s, generator=gen)
-  return t * pdef.init_scale
+  return pdef.local_slice(t).contiguous() * pdef.init_scale
 
 
 class ParamStore:
@@ -220,6 +243,8 @@ class ParamStore:
       u.group = mesh.group(u.fsdp_axes) if u.group_size > 1 else None
     self._pool: list[torch.Tensor] = []
     self._grad_pool: list[torch.Tensor] = []
+    self._rs_inflight: list = []
+    self.max_grad_buffers = 2
     self._bind_resident_units()
 
   # ------------------------------------------------------------------ views
@@ -302,8 +327,12 @@ class ParamStore:
     return work
 
   def acquire_full_grad(self, u: Unit):
+    """Bind a full-size gradient buffer to unit `u`. At most two buffers exist: when both are busy the
+    oldest in-flight reduce-scatter is completed first."""
     if u.group_size == 1:
       return
+    if not self._grad_pool and len(self._rs_inflight) >= self.max_grad_buffers - 1 and self._rs_inflight:
+      self._complete_oldest_rs()
     if self._grad_pool:
       buf = self._grad_pool.pop()
     else:
@@ -313,23 +342,43 @@ class ParamStore:
     for p in u.params:
       p.grad_written = False
 
-  def reduce_scatter_unit(self, u: Unit, async_op: bool = False, accumulate: bool = False):
-    """Sum the unit's full gradient over the shard group into this rank's gradient shard."""
+  def reduce_scatter_unit(self, u: Unit, async_op: bool = True, accumulate: bool = False):
+    """Sum the unit's full gradient over the shard group into this rank's gradient shard.
+
+    The collective is launched asynchronously (it overlaps the backward of the next unit); the full
+    buffer returns to the pool when the work item is completed by `acquire_full_grad` or
+    `wait_reduce_scatters`."""
     if u.group_size == 1:
-      return None
-    # parameters never touched this step must contribute zeros
-    for p in u.params:
+      return
+    for p in u.params:              # parameters never touched this step contribute zeros
       if not p.grad_written:
         p.main_grad.zero_()
     dst = self.shard_view(u, self.grad_shard)
+    full = u.full_grad
     if accumulate:
       tmp = torch.empty_like(dst)
-      dist.reduce_scatter_tensor(tmp, u.full_grad, group=u.group)
-      dst.add_(tmp)
-      work = None
+      work = dist.reduce_scatter_tensor(tmp, full, group=u.group, async_op=async_op)
+      self._rs_inflight.append((work, full, dst, tmp))
     else:
-      work = dist.reduce_scatter_tensor(dst, u.full_grad, group=u.group, async_op=async_op)
-    return work
+      work = dist.reduce_scatter_tensor(dst, full, group=u.group, async_op=async_op)
+      self._rs_inflight.append((work, full, None, None))
+    u.full_grad = None
+    for p in u.params:
+      p.main_grad = None
+    if not async_op:
+      self.wait_reduce_scatters()
+
+  def _complete_oldest_rs(self):
+    work, full, dst, tmp = self._rs_inflight.pop(0)
+    if work is not None:
+      work.wait()
+    if tmp is not None:
+      dst.add_(tmp)
+    self._grad_pool.append(full._base if full._base is not None else full)
+
+  def wait_reduce_scatters(self):
+    while self._rs_inflight:
+      self._complete_oldest_rs()
 
   def release_full_grad(self, u: Unit):
     if u.group_size > 1 and u.full_grad is not None:

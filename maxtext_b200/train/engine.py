@@ -191,6 +191,7 @@ class TrainEngine:
     self._run_embed(tokens, positions, grad=True, dx=dx)
     self._finish_unit_grads(0, accumulate_rs)
     self._release(0)
+    store.wait_reduce_scatters()
     return acc
 
   def _global_weight(self, total_w):
@@ -238,8 +239,7 @@ class TrainEngine:
       pass
     for u in units:
       if u.group_size > 1:
-        store.reduce_scatter_unit(u, async_op=False, accumulate=accumulate)
-        store.release_full_grad(u)
+        store.reduce_scatter_unit(u, async_op=True, accumulate=accumulate)
 
   # ------------------------------------------------------------------ update
   def update(self) -> dict:

@@ -1,0 +1,35 @@
+"""Worker for multi-rank CPU tests: runs a few train steps under gloo and writes its losses as JSON."""
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+  out_path, overrides = sys.argv[1], sys.argv[2:]
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as T
+  from maxtext_b200.train.engine import TrainEngine
+  rank, world, _ = mesh_lib.init_distributed(timeout_s=120)
+  cfg = pyconfig.initialize(["w", "maxtext_b200/configs/base.yml"] + overrides, num_devices=world)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world) if world > 1 else None
+  eng = TrainEngine(cfg, mesh, torch.device("cpu"))
+  it = T.create_data_iterator(cfg, mesh)
+  losses, norms = [], []
+  for _ in range(int(cfg.steps)):
+    m = eng.train_step(next(it))
+    losses.append(float(m["learning/loss"]))
+    norms.append(float(m["learning/raw_grad_norm"]))
+  if rank == 0:
+    with open(out_path, "w") as fh:
+      json.dump({"loss": losses, "grad_norm": norms}, fh)
+  if world > 1:
+    torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+  main()

@@ -1,0 +1,81 @@
+"""Multi-rank runs on CPU (gloo): a sharded mesh must reproduce the single-process loss curve.
+
+The analogue of the reference's virtual-device tests (XLA_FLAGS=--xla_force_host_platform_device_count,
+tests/unit/ulysses_collective_test.py:42): real collectives, tiny shapes, dense single-process oracle."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BASE = ["base_emb_dim=64", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=16", "base_mlp_dim=128",
+        "base_num_decoder_layers=2", "vocab_size=512", "max_target_length=32", "dataset_type=synthetic", "dtype=float32",
+        "hardware=cpu", "enable_checkpointing=false", "weight_init=normal", "log_config=false", "steps=3", "learning_rate=1e-3",
+        "warmup_steps_fraction=0.0"]
+
+
+def _free_port():
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  p = s.getsockname()[1]
+  s.close()
+  return p
+
+
+def run_ranks(world, overrides, tmp_path, tag):
+  out = os.path.join(tmp_path, f"{tag}.json")
+  port = _free_port()
+  procs = []
+  for r in range(world):
+    env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+               MAXTEXT_B200_QUIET="1", OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multirank_worker.py"), out] + BASE + overrides,
+                                  cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+  logs = []
+  for p in procs:
+    try:
+      o, _ = p.communicate(timeout=300)
+    except subprocess.TimeoutExpired:
+      for q in procs:
+        q.kill()
+      raise
+    logs.append(o.decode(errors="replace"))
+  for p, l in zip(procs, logs):
+    assert p.returncode == 0, l[-3000:]
+  return json.load(open(out))
+
+
+def _close(a, b, tol):
+  assert len(a) == len(b)
+  for x, y in zip(a, b):
+    assert abs(x - y) <= tol * max(1.0, abs(y)), (a, b)
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+  return run_ranks(1, ["per_device_batch_size=4"], str(tmp_path_factory.mktemp("single")), "single")
+
+
+def test_fsdp2_matches_single(single, tmp_path):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=2"], str(tmp_path), "fsdp2")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_dp2_matches_single(single, tmp_path):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_data_parallelism=2"], str(tmp_path), "dp2")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_fsdp2_x_tp2_matches_single(single, tmp_path):
+  got = run_ranks(4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_tensor_parallelism=2"], str(tmp_path), "fsdp2tp2")
+  _close(got["loss"], single["loss"], 2e-4)
+
+
+def test_grad_accum_matches_single(single, tmp_path):
+  got = run_ranks(1, ["per_device_batch_size=2", "gradient_accumulation_steps=2"], str(tmp_path), "ga2")
+  _close(got["loss"], single["loss"], 2e-4)
