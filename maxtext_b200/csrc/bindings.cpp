@@ -185,6 +185,9 @@ void sumsq(const torch::Tensor& x, torch::Tensor& out) {
 
 }  // namespace
 
+int* mt_status_ptr() { return status_tensor().data_ptr<int>(); }
+void mt_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
 void register_attention(pybind11::module_& m);
 void register_moe(pybind11::module_& m);
 

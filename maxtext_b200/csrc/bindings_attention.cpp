@@ -1,4 +1,69 @@
 // Bindings for the attention kernels (flash attention forward / backward).
 #include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
 
-void register_attention(pybind11::module_& m) { (void)m; }
+extern "C" {
+int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* seg, int B, int S, int Hq, int Hkv, int D,
+                 long ldq, long ldk, long ldv, long ldo, float scale, int window, int* status, cudaStream_t st);
+int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, void* dq,
+                 void* dk, void* dv, const int* seg, int B, int S, int Hq, int Hkv, int D, long ldq, long ldk, long ldv, long lddq,
+                 long lddk, long lddv, float scale, int window, int* status, cudaStream_t st);
+}
+
+int* mt_status_ptr();          // defined in bindings.cpp
+void mt_count_launches(int n); // defined in bindings.cpp
+
+namespace {
+
+// [B,S,H,D] view whose tokens are consecutive rows of one 2-D tensor: strides (S*ld, ld, D, 1)
+bool token_major(const torch::Tensor& t) {
+  return t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(0) == t.size(1) * t.stride(1) &&
+         t.stride(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0 && t.scalar_type() == torch::kBFloat16;
+}
+
+bool flash_supported(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v) {
+  if (!q.is_cuda() || !token_major(q) || !token_major(k) || !token_major(v)) return false;
+  const int64_t D = q.size(3);
+  if ((D != 128 && D != 64) || k.size(3) != D || v.size(3) != D) return false;
+  if (q.size(1) % 128 || k.size(1) != q.size(1) || v.size(1) != q.size(1)) return false;
+  if (k.size(2) != v.size(2) || q.size(2) % k.size(2)) return false;
+  return true;
+}
+
+void flash_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, torch::Tensor& out, torch::Tensor& lse,
+               const c10::optional<torch::Tensor>& seg, double scale, int64_t window) {
+  TORCH_CHECK(flash_supported(q, k, v) && token_major(out) && lse.is_contiguous() && lse.scalar_type() == torch::kFloat32);
+  if (seg) TORCH_CHECK(seg->is_contiguous() && seg->scalar_type() == torch::kInt32);
+  c10::cuda::CUDAGuard guard(q.device());
+  int rc = mt_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), seg ? seg->data_ptr<int>() : nullptr,
+                        (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)k.size(2), (int)q.size(3), q.stride(1), k.stride(1),
+                        v.stride(1), out.stride(1), (float)scale, (int)window, mt_status_ptr(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "mt_flash_fwd failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void flash_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
+               const torch::Tensor& lse, torch::Tensor& dq, torch::Tensor& dk, torch::Tensor& dv, const c10::optional<torch::Tensor>& seg,
+               double scale, int64_t window) {
+  TORCH_CHECK(flash_supported(q, k, v) && token_major(dq) && token_major(dk) && token_major(dv));
+  TORCH_CHECK(dout.is_contiguous() && out.is_contiguous() && lse.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  auto delta = torch::empty({q.size(0), q.size(2), q.size(1)}, lse.options());
+  int rc = mt_flash_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(),
+                        delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), seg ? seg->data_ptr<int>() : nullptr,
+                        (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)k.size(2), (int)q.size(3), q.stride(1), k.stride(1),
+                        v.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), (float)scale, (int)window, mt_status_ptr(),
+                        at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "mt_flash_bwd failed with code ", rc);
+  mt_count_launches(3);
+}
+
+}  // namespace
+
+void register_attention(pybind11::module_& m) {
+  m.def("flash_supported", &flash_supported);
+  m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
+}

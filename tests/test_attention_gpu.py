@@ -1,0 +1,116 @@
+"""tcgen05 flash attention (forward, dK/dV, dQ) against the fp32 PyTorch definition with autograd."""
+import pytest
+import torch
+
+from maxtext_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _E():
+  from maxtext_b200.ops import backend
+  return backend.ext(required=True)
+
+
+def _reference(q, k, v, seg, window, scale):
+  B, S = q.shape[:2]
+  pos = torch.arange(S, device=q.device)[None].expand(B, S)
+  qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+  mask = ref.attention_mask(pos, pos, seg, seg, True, window)
+  out, lse = ref.attention(qf, kf, vf, mask, scale, return_lse=True)
+  return qf, kf, vf, out, lse
+
+
+def _case(B, S, Hq, Hkv, D, seg_mode=None, window=0, scale=1.0, packed=True, seed=0):
+  E = _E()
+  g = torch.Generator(device="cuda").manual_seed(seed)
+  if packed:
+    qkv = (0.5 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda", generator=g)).bfloat16()
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+  else:
+    q = (0.5 * torch.randn(B, S, Hq, D, device="cuda", generator=g)).bfloat16()
+    k = (0.5 * torch.randn(B, S, Hkv, D, device="cuda", generator=g)).bfloat16()
+    v = (0.5 * torch.randn(B, S, Hkv, D, device="cuda", generator=g)).bfloat16()
+  seg = None
+  if seg_mode == "packed":
+    seg = torch.ones(B, S, dtype=torch.int32, device="cuda")
+    seg[:, S // 3:] = 2
+    seg[:, (2 * S) // 3 + 5:] = 3
+    seg[1, -17:] = 0     # padding tail
+  assert E.flash_supported(q, k, v)
+  out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
+  lse = torch.empty(B, Hq, S, device="cuda")
+  E.flash_fwd(q, k, v, out, lse, seg, scale, window)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0, "bounded wait timed out in the forward kernel"
+  qf, kf, vf, ro, rl = _reference(q, k, v, seg, window, scale)
+  valid = torch.ones(B, S, dtype=torch.bool, device="cuda") if seg is None else seg != 0
+  err = (out.float() - ro)[valid].abs().max().item()
+  assert err <= 2e-2, f"forward max err {err}"
+  lerr = (lse.transpose(1, 2)[valid] - rl.transpose(1, 2)[valid]).abs().max().item()
+  assert lerr <= 2e-2, f"lse max err {lerr}"
+  dout = (torch.randn(B, S, Hq, D, device="cuda", generator=g)).bfloat16()
+  if seg is not None:
+    dout = dout * valid[:, :, None, None]
+  ro.backward(dout.float())
+  if packed:
+    dqkv = torch.zeros_like(qkv)
+    dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
+  else:
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+  E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, scale, window)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0, "bounded wait timed out in a backward kernel"
+  for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+    gotf = got.float()
+    if seg is not None:
+      gotf, want = gotf[valid], want[valid]
+    e = (gotf - want).abs().max().item()
+    s = want.abs().max().item()
+    assert e <= 3e-2 * max(1.0, s), f"{name}: max err {e} (scale {s})"
+
+
+def test_flash_single_tile():
+  _case(1, 128, 1, 1, 128)
+
+
+def test_flash_causal_gqa_packed():
+  _case(2, 384, 4, 2, 128)
+
+
+def test_flash_long_rows_rescale():
+  # 8 key tiles per late query row: the running maximum moves and O is rescaled in tensor memory
+  _case(1, 1024, 2, 1, 128, scale=0.3)
+
+
+def test_flash_head_dim_64():
+  _case(2, 256, 4, 4, 64, packed=False)
+
+
+def test_flash_segments_and_padding():
+  _case(2, 384, 4, 2, 128, seg_mode="packed")
+
+
+def test_flash_sliding_window():
+  _case(1, 512, 2, 2, 128, window=200)
+
+
+def test_packed_attention_autograd_path():
+  """The op the decoder layer calls: rope + attention over the packed projection, forward and backward."""
+  from maxtext_b200.ops import functional as F
+  B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+  qkv = (0.5 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16().requires_grad_(True)
+  pos = torch.arange(S, device="cuda", dtype=torch.int32)[None].expand(B, S).contiguous()
+  inv = ref.rope_inv_timescale(D, 1, 10000).cuda()
+  out = F.packed_attention(qkv.clone(), pos, None, inv, Hq, Hkv)
+  dout = torch.randn_like(out)
+  out.backward(dout)
+  # reference
+  x = qkv.detach().float().requires_grad_(True)
+  qr = ref.apply_rope(x[:, :, :Hq], pos, inv, False)
+  kr = ref.apply_rope(x[:, :, Hq:Hq + Hkv], pos, inv, False)
+  m = ref.attention_mask(pos, pos)
+  ro = ref.attention(qr, kr, x[:, :, Hq + Hkv:], m)
+  ro.backward(dout.float())
+  assert (out.float() - ro).abs().max() <= 3e-2
+  assert (qkv.grad.float() - x.grad).abs().max() <= 4e-2 * max(1.0, x.grad.abs().max().item())
