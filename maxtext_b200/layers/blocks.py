@@ -233,7 +233,8 @@ class Attention:
     if fused is not None:
       saved = ctx.reuse("qkv_proj")
       qkv = F.linear(x, self.qkv, saved_out=saved)
-      ctx.keep("qkv_proj", qkv)
+      if ctx.wants("qkv_proj"):
+        ctx.keep("qkv_proj", qkv.clone())      # the rotary embedding below rewrites qkv in place
       return qkv.view(B, S, hq + 2 * hkv, dh), None
     q = ctx.keep("query_proj", F.linear(x, self.q, ctx.reuse("query_proj"), self.bq))
     k = ctx.keep("key_proj", F.linear(x, self.k, ctx.reuse("key_proj"), self.bk))

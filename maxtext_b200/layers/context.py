@@ -66,6 +66,10 @@ class LayerCtx:
   tokens: torch.Tensor | None = None
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
 
+  def wants(self, name: str) -> bool:
+    """True in the first forward of a rematerialised layer when the policy keeps `name`."""
+    return self.saved is not None and not self.recompute and (name in self.save_names or name in self.offload_names)
+
   def keep(self, name: str, t: torch.Tensor) -> torch.Tensor:
     """Called on a named intermediate in the first (no-grad) forward of a rematerialised layer."""
     if self.saved is not None and not self.recompute:

@@ -68,7 +68,8 @@ class _LinearFn(torch.autograd.Function):
     ctx.save_for_backward(x2, w)
     ctx.has_bias = bias is not None
     if saved_out is not None:
-      return saved_out.reshape(-1, w.shape[0])
+      # a copy: callers may transform the projection in place (rotary embedding on the packed q|k|v)
+      return saved_out.reshape(-1, w.shape[0]).clone()
     y = mm(x2, w, False, True)
     if bias is not None:
       y = y + bias.to(y.dtype)

@@ -1,0 +1,113 @@
+"""Configuration loader: defaults, YAML chain, model catalog, CLI / env overrides, derived values, validation."""
+import glob
+import os
+
+import pytest
+
+from helpers import BASE_YML, ROOT
+from maxtext_b200.config import pyconfig
+from maxtext_b200.config.pyconfig import ConfigError
+
+
+def init(*args, n=1, **kw):
+  return pyconfig.initialize(["t", BASE_YML, "log_config=false", *args], num_devices=n, **kw)
+
+
+def test_every_model_catalog_entry_parses():
+  files = sorted(glob.glob(os.path.join(ROOT, "maxtext_b200", "configs", "models", "*.yml")))
+  assert len(files) >= 70
+  for f in files:
+    c = init(f"model_name={os.path.basename(f)[:-4]}")
+    assert c.emb_dim > 0 and c.num_decoder_layers > 0
+
+
+def test_every_shipped_recipe_parses():
+  for sub, n in (("gpu", 8), ("post_train", 8), ("inference", 8)):
+    for f in sorted(glob.glob(os.path.join(ROOT, "maxtext_b200", "configs", sub, "*.yml"))):
+      if "lora_module_path" in f or f.endswith("vllm.yml") or "gpt_oss_20b" in f:
+        continue   # not a run config / fixed 1-device mesh / 128-device recipe
+      pyconfig.initialize(["t", f, "log_config=false"], num_devices=n)
+
+
+def test_headline_configuration_derived_values():
+  c = init("model_name=llama3-8b", "per_device_batch_size=2", "max_target_length=8192", "dataset_type=synthetic", n=8)
+  assert (c.emb_dim, c.num_query_heads, c.num_kv_heads, c.mlp_dim, c.num_decoder_layers, c.vocab_size) == (4096, 32, 8, 14336, 32, 128256)
+  assert c.global_batch_size_to_train_on == 16 and c.micro_batch_size_to_train_on == 16
+  assert c.ici_parallelism[list(c.mesh_axes).index("fsdp")] == 8       # the -1 default filled with all devices
+  assert c.learning_rate_schedule_steps == c.steps
+
+
+def test_fractional_batch_and_accumulation():
+  c = init("per_device_batch_size=0.5", "gradient_accumulation_steps=2", n=8)
+  assert c.micro_batch_size_to_train_on == 4 and c.global_batch_size_to_train_on == 8 and c.global_batch_size_to_load == 16
+
+
+def test_global_parameter_scale():
+  c = init("global_parameter_scale=8")
+  d = init()
+  assert c.emb_dim == 2 * d.emb_dim and c.num_query_heads == 2 * d.num_query_heads and c.num_decoder_layers == 2 * d.num_decoder_layers
+  with pytest.raises(ValueError):
+    init("global_parameter_scale=3")
+
+
+def test_unknown_key_and_double_override_are_errors(monkeypatch):
+  with pytest.raises(ConfigError):
+    init("no_such_key=1")
+  with pytest.raises(ConfigError):
+    init("steps=1", "steps=2")
+  monkeypatch.setenv("M_STEPS", "7")
+  assert init().steps == 7
+  with pytest.raises(ConfigError):
+    init("steps=3")
+
+
+def test_model_catalog_beats_yaml_and_needs_override_flag():
+  with pytest.raises(ConfigError):
+    init("model_name=llama3-8b", "base_emb_dim=128")
+  c = init("model_name=llama3-8b", "base_emb_dim=128", "override_model_config=true")
+  assert c.emb_dim == 128
+
+
+def test_config_is_read_only_and_replace_recomputes():
+  c = init(n=2)
+  with pytest.raises(AttributeError):
+    c.steps = 5
+  d = c.replace(per_device_batch_size=3.0)
+  assert d.global_batch_size_to_train_on == 6 and c.global_batch_size_to_train_on == 24
+
+
+def test_logical_axis_rules_merge_and_override():
+  c = init("logical_axis_rules=[['embed', ['fsdp']], ['my_axis', ['tensor']]]")
+  rules = [tuple(r) for r in map(lambda r: (r[0], tuple(r[1]) if isinstance(r[1], list) else r[1]), c.logical_axis_rules)]
+  assert [r for r in rules if r[0] == "embed"] == [("embed", ("fsdp",))]
+  assert ("my_axis", ("tensor",)) in rules and any(r[0] == "mlp" for r in rules)
+  o = init("logical_axis_rules=[['embed', ['fsdp']]]", "override_logical_axis_rules=true")
+  assert len(o.logical_axis_rules) == 1
+
+
+def test_custom_mesh_and_rule_and_mesh_fill():
+  c = init("custom_mesh_and_rule=pure-fsdp", n=4)
+  assert list(c.mesh_axes) == ["fsdp"] and c.mesh_shape == [4]
+  c = init("ici_fsdp_parallelism=2", "ici_tensor_parallelism=-1", n=8)
+  assert c.tensor_mesh_size == 4 and c.fsdp_mesh_size == 2
+  with pytest.raises(ValueError):
+    init("ici_fsdp_parallelism=3", n=8)
+
+
+def test_validators():
+  for bad in ("remat_policy=nope", "opt_type=lion", "decoder_block=bert", "quantization=int3", "context_parallel_strategy=zigzag"):
+    with pytest.raises(ValueError):
+      init(bad)
+  with pytest.raises(ValueError):
+    init("ici_pipeline_parallelism=2", "ici_fsdp_parallelism=2", "base_num_decoder_layers=3", n=4)
+  c = init("ici_pipeline_parallelism=2", "ici_fsdp_parallelism=2", "base_num_decoder_layers=8", "num_layers_per_pipeline_stage=2", n=4)
+  assert c.num_pipeline_repeats == 2 and c.num_pipeline_microbatches == 2
+
+
+def test_yaml_base_config_chain(tmp_path):
+  child = tmp_path / "child.yml"
+  child.write_text("base_config: base.yml\nsteps: 11\nmodel_name: llama2-7b\n")
+  grand = tmp_path / "grand.yml"
+  grand.write_text(f"base_config: {child}\nsteps: 12\n")
+  c = pyconfig.initialize(["t", str(grand), "log_config=false"], num_devices=1)
+  assert c.steps == 12 and c.emb_dim == 4096

@@ -1,0 +1,137 @@
+"""Train engine on CPU: gradients against finite differences and an independent autograd Llama, remat policies,
+the tiny-Llama loss curve, determinism."""
+import math
+
+import pytest
+import torch
+
+from helpers import FAMILIES, batch_of, make_engine, tiny_config
+
+
+def _loss(eng, batch):
+  m = eng.eval_step(batch)
+  return float(m["evaluation/total_loss"]) / float(m["evaluation/total_weights"])
+
+
+@pytest.mark.parametrize("model", sorted(FAMILIES))
+def test_family_trains_and_gradient_matches_directional_derivative(model):
+  torch.manual_seed(0)
+  extra = ["load_balance_loss_weight=0.0"] if "load_balance_loss_weight=0.01" in FAMILIES[model] else []
+  cfg = tiny_config(model, extra + ["gradient_clipping_threshold=0"])
+  eng = make_engine(cfg)
+  batch = batch_of(cfg)
+  store = eng.store
+  eng.fwd_bwd(batch)
+  store.finish_resident_grads()
+  acc = eng._accum
+  eng._accum = None
+  g = store.grad_shard.clone() / float(acc["weights"])          # gradient of the mean loss
+  assert torch.isfinite(g).all()
+  v = torch.randn_like(g)
+  v = v / v.norm()
+  eps = 2e-2
+  w0 = store.master.clone()
+  store.master.copy_(w0 + eps * v)
+  store.sync_compute_from_master()
+  lp = _loss(eng, batch)
+  store.master.copy_(w0 - eps * v)
+  store.sync_compute_from_master()
+  lm = _loss(eng, batch)
+  store.master.copy_(w0)
+  store.sync_compute_from_master()
+  fd = (lp - lm) / (2 * eps)
+  an = float((g * v).sum())
+  assert abs(fd - an) <= 0.05 * max(abs(fd), abs(an)) + 2e-4, (model, fd, an)
+  # and a few optimizer steps reduce the loss on the fixed synthetic batch
+  eng2 = make_engine(tiny_config(model))
+  losses = [float(eng2.train_step(batch)["learning/loss"]) for _ in range(4)]
+  assert losses[-1] < losses[0], losses
+
+
+def _ref_llama_loss(store, cfg, batch):
+  """Plain PyTorch Llama (autograd) reading the engine's weights."""
+  from maxtext_b200.ops import reference as ref
+  P = {n: p.data.detach().clone().requires_grad_(True) for n, p in store.params.items()}
+  tok, tgt = batch["inputs"].long(), batch["targets"].long()
+  B, S = tok.shape
+  pos = torch.arange(S)[None].expand(B, S)
+  inv = ref.rope_inv_timescale(cfg.head_dim, cfg.rope_min_timescale, cfg.rope_max_timescale)
+  x = P["token_embedder/embedding"][tok]
+  hq, hkv, dh = cfg.num_query_heads, cfg.num_kv_heads, cfg.head_dim
+  eps = cfg.normalization_layer_epsilon
+  mask = ref.attention_mask(pos, pos)
+  for l in range(cfg.num_decoder_layers):
+    pre = f"layers_{l}/"
+    h = ref.rmsnorm(x, P[pre + "pre_self_attention_layer_norm/scale"], eps)
+    q = (h @ P[pre + "self_attention/query/kernel"].t()).view(B, S, hq, dh)
+    k = (h @ P[pre + "self_attention/key/kernel"].t()).view(B, S, hkv, dh)
+    v = (h @ P[pre + "self_attention/value/kernel"].t()).view(B, S, hkv, dh)
+    q, k = ref.apply_rope(q, pos, inv, False), ref.apply_rope(k, pos, inv, False)
+    a = ref.attention(q, k, v, mask).reshape(B, S, hq * dh)
+    x = x + a @ P[pre + "self_attention/out/kernel"].t()
+    h = ref.rmsnorm(x, P[pre + "post_self_attention_layer_norm/scale"], eps)
+    g = torch.nn.functional.silu(h @ P[pre + "mlp/wi_0/kernel"].t()) * (h @ P[pre + "mlp/wi_1/kernel"].t())
+    x = x + g @ P[pre + "mlp/wo/kernel"].t()
+  h = ref.rmsnorm(x, P["decoder/decoder_norm/scale"], eps)
+  logits = h @ P["decoder/logits_dense/kernel"].t()
+  loss = torch.nn.functional.cross_entropy(logits.view(B * S, -1), tgt.view(-1), reduction="sum")
+  loss.backward()
+  return float(loss), {n: t.grad for n, t in P.items()}
+
+
+def test_llama_grads_match_independent_autograd_model():
+  cfg = tiny_config("llama3-8b")
+  eng = make_engine(cfg)
+  batch = batch_of(cfg)
+  eng.fwd_bwd(batch)
+  eng.store.finish_resident_grads()
+  acc = eng._accum
+  eng._accum = None
+  ref_loss, ref_grads = _ref_llama_loss(eng.store, cfg, batch)
+  assert abs(float(acc["loss_sum"]) - ref_loss) <= 1e-3 * abs(ref_loss)
+  for name, p in eng.store.params.items():
+    want = ref_grads[name]
+    got = p.main_grad
+    err = (got - want).abs().max().item()
+    assert err <= 2e-3 * max(1.0, want.abs().max().item()), (name, err)
+
+
+@pytest.mark.parametrize("policy", ["minimal", "minimal_with_context", "save_dot_except_mlp", "save_qkv_proj", "save_out_proj"])
+def test_remat_policy_does_not_change_gradients(policy):
+  base = make_engine(tiny_config("llama3-8b", ["remat_policy=full"]))
+  other = make_engine(tiny_config("llama3-8b", [f"remat_policy={policy}"]))
+  batch = batch_of(base.config)
+  for e in (base, other):
+    e.fwd_bwd(batch)
+    e.store.finish_resident_grads()
+  assert torch.allclose(base.store.grad_shard, other.store.grad_shard, rtol=1e-4, atol=1e-5)
+
+
+def test_tiny_llama_reference_configuration_loss_curve():
+  """2 layers, emb 256, 4/4 heads x 64, mlp 1024, vocab 32000, seq 128, batch 2, AdamW 3e-4 (0.9, 0.95, wd 0.1),
+  N(0, 0.02) init, 5 steps on the fixed synthetic batch."""
+  from maxtext_b200.config import pyconfig
+  from helpers import BASE_YML
+  cfg = pyconfig.initialize(
+      ["t", BASE_YML, "base_num_decoder_layers=2", "base_emb_dim=256", "base_num_query_heads=4", "base_num_kv_heads=4", "head_dim=64",
+       "base_mlp_dim=1024", "vocab_size=32000", "max_target_length=128", "per_device_batch_size=2", "dataset_type=synthetic", "steps=5",
+       "dtype=float32", "weight_dtype=float32", "learning_rate=3e-4", "adam_b1=0.9", "adam_b2=0.95", "adam_weight_decay=0.1",
+       "hardware=cpu", "enable_checkpointing=false", "weight_init=normal", "log_config=false", "warmup_steps_fraction=0.0",
+       "learning_rate_final_fraction=1.0", "rope_max_timescale=10000"], num_devices=1)
+  eng = make_engine(cfg)
+  batch = batch_of(cfg)
+  losses = [float(eng.train_step(batch)["learning/loss"]) for _ in range(5)]
+  assert abs(losses[0] - math.log(32000)) < 0.2
+  assert all(b < a for a, b in zip(losses, losses[1:])), losses
+  # determinism: a second engine reproduces the curve exactly
+  eng2 = make_engine(cfg)
+  losses2 = [float(eng2.train_step(batch)["learning/loss"]) for _ in range(5)]
+  assert losses == losses2
+
+
+def test_grad_norm_and_clipping():
+  cfg = tiny_config("llama3-8b", ["gradient_clipping_threshold=0.5"])
+  eng = make_engine(cfg)
+  m = eng.train_step(batch_of(cfg))
+  raw, clipped = float(m["learning/raw_grad_norm"]), float(m["learning/grad_norm"])
+  assert raw > 0.5 and abs(clipped - 0.5) < 1e-4

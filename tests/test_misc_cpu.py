@@ -1,0 +1,116 @@
+"""Schedules, FLOPs accounting, synthetic data, metric logger, op-level reference identities."""
+import json
+import math
+
+import pytest
+import torch
+
+from helpers import tiny_config
+from maxtext_b200.ops import reference as ref
+
+
+def test_cosine_schedule_pieces():
+  from maxtext_b200.optimizers.schedules import make_schedule
+  c = tiny_config("llama3-8b", ["steps=120", "learning_rate_schedule_steps=100", "learning_rate=1.0", "warmup_steps_fraction=0.1",
+                                "learning_rate_final_fraction=0.1"])
+  s = make_schedule(c)
+  assert s(0) == 0.0 and abs(s(5) - 0.5) < 1e-9 and abs(s(10) - 1.0) < 1e-9          # linear warm-up, then cosine from its step 0
+  assert abs(s(99) - 0.1) < 1e-9                                                    # last cosine step reaches the final fraction
+  mid = 10 + 89 / 2
+  assert abs(s(int(mid)) - (0.5 * (1 + math.cos(math.pi * (int(mid) - 10) / 89)) * 0.9 + 0.1)) < 1e-9
+  assert s(100) == 0.0 and s(119) == 0.0                                            # zero tail
+
+
+def test_wsd_schedule():
+  from maxtext_b200.optimizers.schedules import make_schedule
+  c = tiny_config("llama3-8b", ["steps=100", "learning_rate=2.0", "lr_schedule_type=wsd", "warmup_steps_fraction=0.1",
+                                "wsd_decay_steps_fraction=0.2", "learning_rate_final_fraction=0.5"])
+  s = make_schedule(c)
+  assert s(9) == pytest.approx(1.8) and s(10) == 2.0 and s(79) == 2.0 and s(99) == pytest.approx(1.0)
+
+
+def test_flops_formula_llama3_8b():
+  from maxtext_b200.utils import flops
+  from maxtext_b200.config import pyconfig
+  from helpers import BASE_YML
+  c = pyconfig.initialize(["t", BASE_YML, "model_name=llama3-8b", "per_device_batch_size=2", "max_target_length=8192", "log_config=false"],
+                          num_devices=1)
+  total, weights, attn = flops.training_tflops_per_device(c)
+  B, S, D, F, L, V, H, KV, Dh = 2, 8192, 4096, 14336, 32, 128256, 32, 8, 128
+  per_layer = 2 * B * S * D * F * 3 + 2 * B * S * D * (H + 2 * KV) * Dh + 2 * B * S * D * H * Dh
+  want_w = 3 * (L * per_layer + 2 * B * S * D * V) / 1e12
+  want_a = 3 * L * (4 * B * S * S * H * Dh / 2) / 1e12
+  assert weights == pytest.approx(want_w) and attn == pytest.approx(want_a) and total == pytest.approx(want_w + want_a)
+  assert total / (B * S) * 1e3 == pytest.approx(51.5, rel=0.02)      # GFLOP per token
+
+
+def test_flops_moe_counts_active_experts_only():
+  from maxtext_b200.utils import flops
+  a = flops.training_tflops_per_device(tiny_config("mixtral-8x7b", ["num_experts=8", "num_experts_per_tok=2"]))[0]
+  b = flops.training_tflops_per_device(tiny_config("mixtral-8x7b", ["num_experts=16", "num_experts_per_tok=2"]))[0]
+  assert b > a and (b - a) / a < 0.05     # only the router grows
+
+
+def test_synthetic_iterator_contract():
+  from maxtext_b200.input_pipeline.synthetic import SyntheticDataIterator
+  c = tiny_config("llama3-8b", ["per_device_batch_size=4"])
+  it = SyntheticDataIterator(c, pin=False)
+  b1, b2 = next(it), next(it)
+  assert b1 is b2 and b1["inputs"].shape == (4, 32)
+  assert torch.equal(b1["inputs"][:, 1:], b1["targets"][:, :-1])
+  assert int(b1["inputs"].max()) < c.vocab_size and (b1["inputs_segmentation"] == 1).all()
+  halves = [SyntheticDataIterator(c, r, 2, pin=False).batch["inputs"] for r in (0, 1)]
+  assert torch.equal(torch.cat(halves), b1["inputs"])                # ranks read disjoint rows of the same global batch
+
+
+def test_metric_logger_line_file_and_nan_abort(tmp_path, capsys):
+  from maxtext_b200.utils.metric_logger import MetricLogger, TrainingAborted
+  c = tiny_config("llama3-8b", [f"metrics_file={tmp_path}/m.jsonl"])
+  lg = MetricLogger(c)
+  lg.record(0, {"learning/loss": torch.tensor(2.5), "learning/lm_loss": torch.tensor(2.5), "learning/total_weights": torch.tensor(64.)}, 0.5)
+  lg.record(1, {"learning/loss": torch.tensor(float("nan")), "learning/total_weights": torch.tensor(64.)}, 0.5)   # writes step 0
+  out = capsys.readouterr().out
+  assert "completed step: 0, seconds: 0.500, TFLOP/s/device:" in out and "loss: 2.500" in out
+  with pytest.raises(TrainingAborted):
+    lg.flush()
+  rows = [json.loads(l) for l in open(f"{tmp_path}/m.jsonl")]
+  assert rows[0]["step"] == 0 and rows[0]["perf/step_time_seconds"] == 0.5 and math.isnan(rows[1]["learning/loss"])
+
+
+def test_rope_layouts_and_inverse():
+  x = torch.randn(2, 5, 3, 16)
+  pos = torch.arange(5)[None].expand(2, 5)
+  inv = ref.rope_inv_timescale(16, 1, 10000)
+  for inter in (False, True):
+    y = ref.apply_rope(x, pos, inv, inter)
+    assert torch.allclose(ref.apply_rope(y, pos, inv, inter, inverse=True), x, atol=1e-5)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+  # interleaved layout == rotate-half layout applied to de-interleaved lanes
+  perm = torch.cat([torch.arange(0, 16, 2), torch.arange(1, 16, 2)])
+  assert torch.allclose(ref.apply_rope(x, pos, inv, True)[..., perm], ref.apply_rope(x[..., perm], pos, inv, False), atol=1e-5)
+  scaled = ref.rope_inv_timescale(128, 1, 500000, rope_type="llama3.1")
+  plain = ref.rope_inv_timescale(128, 1, 500000)
+  assert torch.allclose(scaled[:20], plain[:20]) and torch.allclose(scaled[-1], plain[-1] / 8)
+
+
+def test_cross_entropy_gradient_identity():
+  lg = torch.randn(7, 50, requires_grad=True)
+  tg = torch.randint(0, 50, (7,))
+  w = torch.rand(7)
+  loss, _ = ref.cross_entropy(lg, tg, 1e-3)
+  (loss * w).sum().backward()
+  assert torch.allclose(lg.grad, ref.cross_entropy_dlogits(lg.detach(), tg, w, 1e-3), atol=1e-5)
+
+
+def test_adamw_matches_torch_optimizer():
+  p = torch.randn(100)
+  g = torch.randn(100)
+  ref_p = torch.nn.Parameter(p.clone())
+  opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+  m, v = torch.zeros(100), torch.zeros(100)
+  q = p.clone()
+  for step in (1, 2, 3):
+    ref_p.grad = g.clone()
+    opt.step()
+    ref.adamw_step(q, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.0, 0.1, step)
+  assert torch.allclose(q, ref_p.detach(), atol=2e-5)
