@@ -5,7 +5,13 @@ import sys
 
 _logger = logging.getLogger("maxtext_b200")
 if not _logger.handlers:
-  _h = logging.StreamHandler(sys.stdout)
+  class _Stdout(logging.StreamHandler):
+    """Always writes to the current sys.stdout (which test harnesses and launchers may swap)."""
+    def emit(self, record):
+      self.stream = sys.stdout
+      super().emit(record)
+
+  _h = _Stdout(sys.stdout)
   _h.setFormatter(logging.Formatter("%(message)s"))
   _logger.addHandler(_h)
   _logger.setLevel(os.environ.get("MAXTEXT_B200_LOGLEVEL", "INFO"))
