@@ -190,6 +190,7 @@ void mt_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxe
 
 void register_attention(pybind11::module_& m);
 void register_moe(pybind11::module_& m);
+void register_comm(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
@@ -208,4 +209,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   register_attention(m);
   register_moe(m);
+  register_comm(m);
 }

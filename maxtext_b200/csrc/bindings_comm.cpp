@@ -1,0 +1,103 @@
+// Bindings for the peer-memory communication kernels (flags, fused reduce-scatter, gather, all-gather GEMM).
+// Pointer tables are int64 CUDA tensors holding one device pointer per rank (built from symmetric-memory handles).
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+
+extern "C" {
+int mt_comm_signal(int* const* peer_flags, int slot, int my_rank, int world, int epoch, cudaStream_t st);
+int mt_comm_wait(const int* my_flags, int slot, int world, int epoch, int* status, unsigned long long limit_ns, cudaStream_t st);
+int mt_rs_num_partials(long n, int ctas);
+int mt_rs_sumsq(const float* const* peer, long offset, long n, float* dst, int accumulate, float scale, int world, float* partials,
+                float* sumsq_out, int ctas, cudaStream_t st);
+int mt_gather_segments(const void* const* peer_shards, void* full, long chunk_bytes, long seg_bytes, int world, int* seg_flags, int ctas,
+                       cudaStream_t st);
+int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int64_t lda, int64_t ldc, const void* const* peer_shards, void* full,
+                    long chunk_elems, long seg_elems, long b_offset, int world, int* seg_flags, int comm_ctas, int* status, int num_sms,
+                    cudaStream_t stream);
+}
+
+int* mt_status_ptr();
+void mt_count_launches(int n);
+
+namespace {
+
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int sm_count() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+void ptr_table_ok(const torch::Tensor& t, int64_t world) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt64 && t.is_contiguous() && t.numel() >= world, "bad pointer table");
+}
+
+void comm_signal(const torch::Tensor& peer_flags, int64_t slot, int64_t my_rank, int64_t world, int64_t epoch) {
+  ptr_table_ok(peer_flags, world);
+  c10::cuda::CUDAGuard g(peer_flags.device());
+  TORCH_CHECK(mt_comm_signal(reinterpret_cast<int* const*>(peer_flags.data_ptr<int64_t>()), (int)slot, (int)my_rank, (int)world, (int)epoch,
+                             cur()) == 0, "mt_comm_signal failed");
+  mt_count_launches(1);
+}
+
+void comm_wait(const torch::Tensor& my_flags, int64_t slot, int64_t world, int64_t epoch, double limit_ms) {
+  TORCH_CHECK(my_flags.is_cuda() && my_flags.scalar_type() == torch::kInt32);
+  c10::cuda::CUDAGuard g(my_flags.device());
+  TORCH_CHECK(mt_comm_wait(my_flags.data_ptr<int>(), (int)slot, (int)world, (int)epoch, mt_status_ptr(),
+                           (unsigned long long)(limit_ms * 1e6), cur()) == 0, "mt_comm_wait failed");
+  mt_count_launches(1);
+}
+
+void rs_sumsq(const torch::Tensor& peer_bufs, int64_t offset, int64_t n, torch::Tensor& dst, bool accumulate, double scale, int64_t world,
+              const c10::optional<torch::Tensor>& sumsq_out, int64_t ctas) {
+  ptr_table_ok(peer_bufs, world);
+  TORCH_CHECK(dst.is_cuda() && dst.scalar_type() == torch::kFloat32 && dst.is_contiguous() && dst.numel() >= n);
+  c10::cuda::CUDAGuard g(dst.device());
+  const int parts = mt_rs_num_partials(n, (int)ctas);
+  auto partials = torch::empty({parts}, dst.options());
+  TORCH_CHECK(mt_rs_sumsq(reinterpret_cast<const float* const*>(peer_bufs.data_ptr<int64_t>()), offset, n, dst.data_ptr<float>(),
+                          accumulate ? 1 : 0, (float)scale, (int)world, partials.data_ptr<float>(),
+                          sumsq_out ? sumsq_out->data_ptr<float>() : nullptr, (int)ctas, cur()) == 0, "mt_rs_sumsq failed");
+  mt_count_launches(sumsq_out ? 2 : 1);
+}
+
+void gather_segments(const torch::Tensor& peer_shards, torch::Tensor& full, int64_t chunk_bytes, int64_t seg_bytes, int64_t world,
+                     int64_t ctas) {
+  ptr_table_ok(peer_shards, world);
+  TORCH_CHECK(full.is_cuda() && full.is_contiguous() && full.numel() * full.element_size() >= chunk_bytes * world);
+  c10::cuda::CUDAGuard g(full.device());
+  TORCH_CHECK(mt_gather_segments(reinterpret_cast<const void* const*>(peer_shards.data_ptr<int64_t>()), full.data_ptr(), chunk_bytes,
+                                 seg_bytes, (int)world, nullptr, (int)ctas, cur()) == 0, "mt_gather_segments failed");
+  mt_count_launches(1);
+}
+
+// out[M,N] = a[M,K] . W^T with W = full[b_offset : b_offset + N*K] viewed [N,K]; gathers the whole unit on the way.
+void gemm_ag(const torch::Tensor& a, torch::Tensor& out, const torch::Tensor& peer_shards, torch::Tensor& full, int64_t N, int64_t K,
+             int64_t chunk_elems, int64_t seg_elems, int64_t b_offset, int64_t world, torch::Tensor& seg_flags, int64_t comm_ctas) {
+  ptr_table_ok(peer_shards, world);
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kBFloat16 && a.dim() == 2 && a.stride(1) == 1 && a.size(1) == K);
+  TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.dim() == 2 && out.stride(1) == 1 && out.size(0) == a.size(0) && out.size(1) == N);
+  TORCH_CHECK(full.scalar_type() == torch::kBFloat16 && full.is_contiguous() && full.numel() >= chunk_elems * world);
+  TORCH_CHECK(seg_flags.scalar_type() == torch::kInt32 && seg_flags.numel() >= world * ((chunk_elems + seg_elems - 1) / seg_elems));
+  TORCH_CHECK(a.size(0) >= 128 && N >= 256 && K >= 64 && K % 8 == 0 && b_offset + N * K <= chunk_elems * world);
+  c10::cuda::CUDAGuard g(a.device());
+  int rc = mt_gemm_bf16_ag(a.data_ptr(), out.data_ptr(), (int)a.size(0), (int)N, (int)K, a.stride(0), out.stride(0),
+                           reinterpret_cast<const void* const*>(peer_shards.data_ptr<int64_t>()), full.data_ptr(), chunk_elems, seg_elems,
+                           b_offset, (int)world, seg_flags.data_ptr<int>(), (int)comm_ctas, mt_status_ptr(), sm_count(), cur());
+  TORCH_CHECK(rc == 0, "mt_gemm_bf16_ag failed with code ", rc);
+  mt_count_launches(1);
+}
+
+}  // namespace
+
+void register_comm(pybind11::module_& m) {
+  m.def("comm_signal", &comm_signal);
+  m.def("comm_wait", &comm_wait);
+  m.def("rs_sumsq", &rs_sumsq);
+  m.def("gather_segments", &gather_segments);
+  m.def("gemm_ag", &gemm_ag);
+}

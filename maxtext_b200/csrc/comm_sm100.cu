@@ -1,0 +1,166 @@
+// Communication kernels over NVLink peer memory (symmetric buffers mapped into every rank of a node).
+//
+//   * signal / wait: per-peer epoch flags with release / acquire at system scope. Every wait is bounded: when the
+//     limit passes the kernel records ST_TIMEOUT_FLAG in the status word and returns, it never spins forever.
+//   * rs_sumsq: fused gradient reduce-scatter. Each rank reads ITS chunk of every peer's full gradient buffer
+//     with plain peer loads, adds the copies in rank order (bitwise reproducible), applies the bucket scale,
+//     writes (or accumulates into) its fp32 gradient shard and emits the sum-of-squares partials of the
+//     global gradient norm in the same pass. What the reference gets from an NCCL reduce-scatter followed by
+//     separate cast / norm fusions.
+//   * gather_segments: pulls the peers' parameter shards into the local full buffer, segment by segment, and
+//     publishes one flag per segment; the GEMM in gemm_sm100.cu runs the same loop in spare CTAs of its own
+//     launch so that tiles start as soon as their rows have arrived.
+// No kernel here uses bulk-tensor copies from peer memory: remote data is read with ld.global by the copying CTA.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mt {
+
+enum : int { COMM_ST_TIMEOUT_FLAG = 4 };
+
+__device__ __forceinline__ uint64_t comm_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Thread r tells rank r that this rank reached `epoch` on slot `slot`: flags[r][slot * world + my_rank] = epoch.
+__global__ void signal_kernel(int* const* __restrict__ peer_flags, int slot, int my_rank, int world, int epoch) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(peer_flags[r] + slot * world + my_rank, epoch);
+  }
+}
+
+// Wait until every peer's flag on `slot` reached `epoch`, at most limit_ns.
+__global__ void wait_kernel(const int* __restrict__ my_flags, int slot, int world, int epoch, int* status, unsigned long long limit_ns) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  const int* f = my_flags + slot * world + r;
+  const uint64_t t0 = comm_timer_ns();
+  while (ld_acquire_sys(f) < epoch) {
+    if (comm_timer_ns() - t0 > limit_ns) {
+      atomicCAS(status, 0, COMM_ST_TIMEOUT_FLAG);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+constexpr int RS_THREADS = 512;
+
+__device__ __forceinline__ float rs_block_sum(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (RS_THREADS >> 5)) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  }
+  return t;
+}
+
+// dst[i] (+)= scale * sum_r peer[r][offset + i];  partials[block] = sum of squares of what was written this call.
+__global__ void __launch_bounds__(RS_THREADS)
+rs_sumsq_kernel(const float* const* __restrict__ peer, long offset, long n, float* __restrict__ dst, int accumulate, float scale,
+                int world, float* __restrict__ partials) {
+  __shared__ float sh[32];
+  float acc = 0.f;
+  const long n4 = n / 4;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = reinterpret_cast<const float4*>(peer[r] + offset)[i];
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    if (accumulate) {
+      const float4 o = reinterpret_cast<const float4*>(dst)[i];
+      s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+    }
+    reinterpret_cast<float4*>(dst)[i] = s;
+    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  const float t = rs_block_sum(acc, sh);
+  if (threadIdx.x == 0 && partials) partials[blockIdx.x] = t;
+}
+
+__global__ void __launch_bounds__(RS_THREADS) rs_stage2_kernel(const float* __restrict__ partials, int nparts, float* __restrict__ out) {
+  __shared__ float sh[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partials[i];
+  const float t = rs_block_sum(acc, sh);
+  if (threadIdx.x == 0) *out += t;
+}
+
+// Segment s of the gathered buffer = rank (s / segs_per_chunk), piece (s % segs_per_chunk) of its chunk.
+__global__ void __launch_bounds__(256)
+gather_segments_kernel(const uint4* const* __restrict__ peer_shards, uint4* __restrict__ full, long chunk_vec, long seg_vec, int segs_per_chunk,
+                       int n_segs, int first_seg, int* __restrict__ seg_flags) {
+  for (int k = blockIdx.x; k < n_segs; k += gridDim.x) {
+    const int s = (first_seg + k) % n_segs;
+    const int r = s / segs_per_chunk;
+    const long lo = (long)(s % segs_per_chunk) * seg_vec;
+    const long hi = lo + seg_vec < chunk_vec ? lo + seg_vec : chunk_vec;
+    const uint4* src = peer_shards[r];
+    uint4* dst = full + (long)r * chunk_vec;
+    for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0 && seg_flags) atomicExch(seg_flags + s, 1);
+  }
+}
+
+}  // namespace mt
+
+using namespace mt;
+
+extern "C" int mt_comm_signal(int* const* peer_flags, int slot, int my_rank, int world, int epoch, cudaStream_t st) {
+  if (world > 32) return -1;
+  signal_kernel<<<1, 32, 0, st>>>(peer_flags, slot, my_rank, world, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int mt_comm_wait(const int* my_flags, int slot, int world, int epoch, int* status, unsigned long long limit_ns, cudaStream_t st) {
+  if (world > 32) return -1;
+  wait_kernel<<<1, 32, 0, st>>>(my_flags, slot, world, epoch, status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int mt_rs_num_partials(long n, int ctas) {
+  long blocks = (n / 4 + RS_THREADS - 1) / RS_THREADS;
+  if (blocks < 1) blocks = 1;
+  return (int)(blocks < ctas ? blocks : ctas);
+}
+
+// partials: scratch of mt_rs_num_partials(n, ctas) floats; sumsq_out[0] += sum of squares (pass nullptr to skip).
+extern "C" int mt_rs_sumsq(const float* const* peer, long offset, long n, float* dst, int accumulate, float scale, int world, float* partials,
+                           float* sumsq_out, int ctas, cudaStream_t st) {
+  if (n % 4 || offset % 4) return -1;
+  if (n == 0) return 0;
+  const int parts = mt_rs_num_partials(n, ctas);
+  rs_sumsq_kernel<<<parts, RS_THREADS, 0, st>>>(peer, offset, n, dst, accumulate, scale, world, partials);
+  if (sumsq_out && partials) rs_stage2_kernel<<<1, RS_THREADS, 0, st>>>(partials, parts, sumsq_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Stand-alone all-gather by peer loads (the GEMM-fused form runs the same kernel body inside the GEMM launch).
+extern "C" int mt_gather_segments(const void* const* peer_shards, void* full, long chunk_bytes, long seg_bytes, int world, int* seg_flags,
+                                  int ctas, cudaStream_t st) {
+  if (chunk_bytes % 16 || seg_bytes % 16) return -1;
+  const long chunk_vec = chunk_bytes / 16, seg_vec = seg_bytes / 16;
+  const int spc = (int)((chunk_vec + seg_vec - 1) / seg_vec);
+  gather_segments_kernel<<<ctas, 256, 0, st>>>(reinterpret_cast<const uint4* const*>(peer_shards), reinterpret_cast<uint4*>(full), chunk_vec,
+                                               seg_vec, spc, spc * world, 0, seg_flags);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -46,7 +46,58 @@ struct GemmParams {
   int M, N, K;
   int accumulate;  // fp32 output only: C += result (TMA reduce-add)
   int* status;
+  // Fused FSDP all-gather (forward layout only, B = W[N,K] inside a flat parameter unit). When g_comm_ctas > 0 the
+  // last g_comm_ctas CTAs of the launch copy the peers' shards of the whole unit into the local full buffer, one
+  // segment at a time, publishing a flag per segment; the TMA producers of the other CTAs wait for the segments
+  // that hold the rows of their B tile before loading it. Remote data is read with plain ld.global by the copier.
+  int g_comm_ctas;
+  int g_world;
+  int g_segs_per_chunk;
+  int g_first_seg;
+  long g_chunk_vec;      // 16-byte vectors per rank chunk
+  long g_seg_vec;        // 16-byte vectors per segment
+  long g_chunk_elems;    // bf16 elements per rank chunk
+  long g_seg_elems;
+  long g_b_offset;       // element offset of W inside the unit
+  const uint4* const* g_peer_shards;
+  uint4* g_full;
+  int* g_seg_flags;
 };
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Wait (bounded) until every segment covering unit elements [lo, hi) has been published.
+__device__ __forceinline__ bool wait_segments(const GemmParams& p, long lo, long hi, volatile int* abort_flag) {
+  long e = lo;
+  while (e < hi) {
+    const long r = e / p.g_chunk_elems;
+    const long j = (e - r * p.g_chunk_elems) / p.g_seg_elems;
+    const int* f = p.g_seg_flags + r * p.g_segs_per_chunk + j;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(f) == 0) {
+      if ((++spins & 0xFF) == 0) {
+        if (*abort_flag) return false;
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > 4000000000ull) {
+          *abort_flag = 1;
+          if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_FLAG);
+          return false;
+        }
+      }
+    }
+    const long seg_end = r * p.g_chunk_elems + (j + 1) * p.g_seg_elems;
+    const long chunk_end = (r + 1) * p.g_chunk_elems;
+    e = seg_end < chunk_end ? seg_end : chunk_end;
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");   // peer data was written with generic stores, TMA reads it next
+  return true;
+}
 
 __device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
   const int per_group = GROUP_M * n_blocks;
@@ -88,6 +139,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int cta_stride = (int)gridDim.x - p.g_comm_ctas;        // CTAs that compute tiles
+  const bool is_comm_cta = (int)blockIdx.x >= cta_stride;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -113,15 +166,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  if (warp == 0) {
+  if (is_comm_cta) {
+    // ------------------------------------------------------------ all-gather copier (all 192 threads)
+    const int n_segs = p.g_segs_per_chunk * p.g_world;
+    for (int k = (int)blockIdx.x - cta_stride; k < n_segs; k += p.g_comm_ctas) {
+      const int sgm = (p.g_first_seg + k) % n_segs;
+      const int r = sgm / p.g_segs_per_chunk;
+      const long lo = (long)(sgm % p.g_segs_per_chunk) * p.g_seg_vec;
+      const long hi = lo + p.g_seg_vec < p.g_chunk_vec ? lo + p.g_seg_vec : p.g_chunk_vec;
+      const uint4* src = p.g_peer_shards[r];
+      uint4* dst = p.g_full + (long)r * p.g_chunk_vec;
+      for (long i = lo + threadIdx.x; i < hi; i += NUM_THREADS) dst[i] = src[i];
+      __threadfence();
+      named_bar_sync(4, NUM_THREADS);
+      if (threadIdx.x == 0) atomicExch(p.g_seg_flags + sgm, 1);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
         int mb, nb;
         tile_coords(t, m_blocks, n_blocks, mb, nb);
+        if (p.g_seg_flags) {
+          const long n1 = (long)(nb + 1) * BN < p.N ? (long)(nb + 1) * BN : p.N;
+          if (!wait_segments(p, p.g_b_offset + (long)nb * BN * p.K, p.g_b_offset + n1 * p.K, abort_flag)) { ok = false; break; }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
@@ -156,7 +228,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -188,7 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
       int mb, nb;
       tile_coords(t, m_blocks, n_blocks, mb, nb);
       // one thread waits, the verdict is shared so that all 128 threads leave the loop together
@@ -339,7 +411,8 @@ extern "C" int mt_gemm_bf16(const void* a, const void* b, void* c, int M, int N,
   if (out_f32) e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, BM);
   else e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
   if (e) return 300 + e;
-  GemmParams p{M, N, K, accumulate, status};
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = accumulate; p.status = status;
 #define MT_DISPATCH(BN_)                                                                                             \
   do {                                                                                                               \
     if (!a_mn && !b_mn) return out_f32 ? launch<BN_, false, false, float>(ma, mb, mc, p, num_sms, stream)            \
@@ -354,4 +427,48 @@ extern "C" int mt_gemm_bf16(const void* a, const void* b, void* c, int M, int N,
   if (BN == 256) MT_DISPATCH(256);
   MT_DISPATCH(128);
 #undef MT_DISPATCH
+}
+
+// Forward GEMM out[M,N] = a[M,K] . W[N,K]^T fused with the FSDP all-gather of the flat parameter unit that holds W.
+//   peer_shards: device array of `world` pointers, entry r = rank r's compute-dtype shard of this unit (chunk_elems bf16)
+//   full: local full buffer of the unit (world * chunk_elems bf16); W = full + b_offset, leading stride K
+//   seg_flags: device ints, one per segment (world * ceil(chunk/seg)); cleared here, stream-ordered
+// `comm_ctas` CTAs of the launch do the copying. After the kernel the whole unit is resident in `full`.
+extern "C" int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int64_t lda, int64_t ldc, const void* const* peer_shards,
+                               void* full, long chunk_elems, long seg_elems, long b_offset, int world, int* seg_flags, int comm_ctas,
+                               int* status, int num_sms, cudaStream_t stream) {
+  using namespace mt;
+  if (chunk_elems % 8 || seg_elems % 8 || b_offset % 8 || comm_ctas < 1 || comm_ctas >= num_sms) return -10;
+  constexpr int BN = 256;
+  const char* w = reinterpret_cast<const char*>(full) + b_offset * 2;
+  CUtensorMap ma, mb, mc;
+  int e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM);
+  if (e) return 100 + e;
+  e = make_map_2d(&mb, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, BK, BN);
+  if (e) return 200 + e;
+  e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
+  if (e) return 300 + e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = 0; p.status = status;
+  p.g_comm_ctas = comm_ctas; p.g_world = world;
+  p.g_chunk_elems = chunk_elems; p.g_seg_elems = seg_elems;
+  p.g_chunk_vec = chunk_elems / 8; p.g_seg_vec = seg_elems / 8;
+  p.g_segs_per_chunk = (int)((chunk_elems + seg_elems - 1) / seg_elems);
+  p.g_b_offset = b_offset;
+  p.g_first_seg = (int)(b_offset / chunk_elems) * p.g_segs_per_chunk + (int)((b_offset % chunk_elems) / seg_elems);
+  p.g_peer_shards = reinterpret_cast<const uint4* const*>(peer_shards);
+  p.g_full = reinterpret_cast<uint4*>(full);
+  p.g_seg_flags = seg_flags;
+  if (cudaMemsetAsync(seg_flags, 0, sizeof(int) * (size_t)p.g_segs_per_chunk * world, stream) != cudaSuccess) return -11;
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, false, false, __nv_bfloat16>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int compute = tiles < num_sms - comm_ctas ? tiles : num_sms - comm_ctas;
+  kern<<<compute + comm_ctas, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

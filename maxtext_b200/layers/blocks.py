@@ -112,6 +112,9 @@ class FusedParam:
   def data(self):
     return self._span("data")
 
+  def pending_unit(self):
+    return self.parts[0].pending_unit()
+
   @property
   def main_grad(self):
     return self._span("main_grad")

@@ -62,11 +62,13 @@ def mm(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out: torch.Tensor |
 
 class _LinearFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, x, w, pv, saved_out, bias):
+  def forward(ctx, x, w, pv, saved_out, bias, precomputed=None):
     ctx.pv = pv
     x2 = x
     ctx.save_for_backward(x2, w)
     ctx.has_bias = bias is not None
+    if precomputed is not None:
+      return precomputed
     if saved_out is not None:
       # a copy: callers may transform the projection in place (rotary embedding on the packed q|k|v)
       return saved_out.reshape(-1, w.shape[0]).clone()
@@ -87,22 +89,27 @@ class _LinearFn(torch.autograd.Function):
       mm(dy2, x2, True, False, out=pv.main_grad.view(w.shape), accumulate=pv.grad_written)
       pv.grad_written = True
     dbias = dy2.float().sum(0) if ctx.has_bias else None
-    return dx, None, None, None, dbias
+    return dx, None, None, None, dbias, None
 
 
 def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None) -> torch.Tensor:
   """y = x @ W.T for W = p.data stored [out, in]. `saved_out` short-cuts the forward GEMM when a remat
   policy kept this projection's output."""
   b = bias.leaf() if bias is not None else None
-  if not torch.is_grad_enabled():
-    if saved_out is not None:
-      return saved_out
-    y = mm(x.reshape(-1, x.shape[-1]), p.data, False, True).view(*x.shape[:-1], p.data.shape[0])
-    return y + b.to(y.dtype) if b is not None else y
   x2 = x.reshape(-1, x.shape[-1])
   if not x2.is_contiguous():
     x2 = x2.contiguous()
-  return _LinearFn.apply(x2, p.data, p, saved_out, b).view(*x.shape[:-1], p.data.shape[0])
+  # FSDP: when the unit's all-gather is still pending, this GEMM performs it inside its own launch
+  pre = None
+  pend = p.pending_unit() if hasattr(p, "pending_unit") else None
+  if pend is not None and saved_out is None and b is None:
+    pre = pend.store.ag_linear(pend, p, x2)
+  if not torch.is_grad_enabled():
+    if saved_out is not None:
+      return saved_out
+    y = (pre if pre is not None else mm(x2, p.data, False, True)).view(*x.shape[:-1], p.shape[0])
+    return y + b.to(y.dtype) if b is not None else y
+  return _LinearFn.apply(x2, p.data, p, saved_out, b, pre).view(*x.shape[:-1], p.shape[0])
 
 
 # =============================================================================== RMSNorm

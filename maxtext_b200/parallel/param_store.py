@@ -94,14 +94,32 @@ class Param:
   """Handle given to layer code. `.data` is the compute-dtype tensor (valid while the unit is
   resident), `.main_grad` the fp32 gradient accumulator view (valid during backward)."""
 
-  __slots__ = ("pdef", "data", "main_grad", "grad_written", "_leaf")
+  __slots__ = ("pdef", "_data", "main_grad", "grad_written", "_leaf", "unit")
 
   def __init__(self, pdef: ParamDef):
     self.pdef = pdef
-    self.data: torch.Tensor | None = None
+    self._data: torch.Tensor | None = None
     self.main_grad: torch.Tensor | None = None
     self.grad_written = False
     self._leaf = None
+    self.unit = None          # set by the store
+
+  @property
+  def data(self):
+    """The compute-dtype tensor. If the unit's all-gather was deferred so that it could be fused into the first
+    GEMM that reads it, any other reader triggers the stand-alone gather here."""
+    u = self.unit
+    if u is not None and u.pending_ag:
+      u.store.ensure_gathered(u)
+    return self._data
+
+  @data.setter
+  def data(self, t):
+    self._data = t
+
+  def pending_unit(self):
+    u = self.unit
+    return u if (u is not None and u.pending_ag) else None
 
   @property
   def name(self):
@@ -149,6 +167,9 @@ class Unit:
   full: torch.Tensor | None = None        # compute-dtype full buffer while resident
   full_grad: torch.Tensor | None = None   # fp32 full gradient buffer during backward
   resident: bool = False
+  pending_ag: bool = False                # full buffer bound but not yet filled (fused all-gather mode)
+  store: object = None
+  grad_slot: int = -1                     # symmetric gradient buffer in use (fused reduce-scatter mode)
 
 
 def _seed_for(name: str, base_seed: int) -> int:
@@ -216,6 +237,8 @@ class ParamStore:
         raise ValueError(f"duplicate parameter name {d.name}")
       self.params[d.name] = p
       self.units[ukey].params.append(p)
+      self.units[ukey].store = self
+      p.unit = self.units[ukey]
     # layout
     total_local = 0
     for u in self.units.values():
@@ -234,7 +257,32 @@ class ParamStore:
     dev = self.device
     self.master = torch.zeros(total_local, dtype=self.weight_dtype, device=dev)
     self.alias_compute = self.compute_dtype == self.weight_dtype
-    self.compute_shard = self.master if self.alias_compute else torch.zeros(total_local, dtype=self.compute_dtype, device=dev)
+    # ---- fused communication (symmetric memory over NVLink): only for pure shard groups spanning every rank
+    self.fused = False
+    self.symm = None
+    world = getattr(mesh, "world", 1)
+    sharded = [u for u in self.units.values() if u.group_size > 1]
+    if (bool(getattr(config, "use_fused_comm_kernels", False)) and self.device.type == "cuda" and world > 1 and sharded
+        and all(u.group_size == world for u in sharded) and not self.alias_compute and self.compute_dtype == torch.bfloat16
+        and self.grad_dtype == torch.float32 and not bool(config.logits_via_embedding)):
+      from . import symm as _symm
+      if _symm.available():
+        self.symm = _symm.SymmGroup(None, self.device)
+        self.fused = True
+    if self.fused:
+      self._cs = self.symm.alloc(total_local, self.compute_dtype, zero=True)
+      self.compute_shard = self._cs.tensor
+      self.seg_elems = 512 * 1024
+      max_chunk = max(u.chunk for u in sharded)
+      self.seg_flags = torch.zeros(world * (-(-max_chunk // self.seg_elems)), dtype=torch.int32, device=dev)
+      self.comm_ctas = int(getattr(config, "fsdp_comm_ctas", 8))
+      self.comm_stream = torch.cuda.Stream(device=dev)
+      self._gbufs = None
+      self._gslot_pending = [None, None]
+      self.gradsq = torch.zeros(1, dtype=torch.float32, device=dev)
+      self.gradsq_valid = False
+    else:
+      self.compute_shard = self.master if self.alias_compute else torch.zeros(total_local, dtype=self.compute_dtype, device=dev)
     self.grad_shard = None   # allocated on first backward (inference never needs it)
     self.exp_avg = None
     self.exp_avg_sq = None
@@ -291,6 +339,8 @@ class ParamStore:
         dst[a - lo: b - lo].copy_(full[a - off: b - off].to(self.weight_dtype))
         del full
     self.sync_compute_from_master()
+    if self.fused:
+      self.symm.barrier(0)        # every rank's shard is final before anyone reads it over NVLink
 
   def sync_compute_from_master(self):
     if not self.alias_compute:
@@ -311,13 +361,20 @@ class ParamStore:
   def release_full(self, u: Unit):
     if u.group_size > 1 and u.full is not None:
       self._pool.append(u.full._base if u.full._base is not None else u.full)
-      u.full, u.resident = None, False
+      u.full, u.resident, u.pending_ag = None, False, False
       for p in u.params:
         p.data = None
 
   def gather_unit(self, u: Unit, async_op: bool = False):
     """All-gather the compute-dtype shards of unit `u` into a pooled full buffer."""
     if u.group_size == 1 or u.resident:
+      return None
+    if self.fused:
+      # defer: the first GEMM that reads the unit gathers it inside its own launch (see ag_linear)
+      buf = self.acquire_full(u)
+      u.full, u.resident = buf, True
+      self._views_into(u, buf, "data")
+      u.pending_ag = True
       return None
     buf = self.acquire_full(u)
     work = dist.all_gather_into_tensor(buf, self.shard_view(u, self.compute_shard), group=u.group, async_op=async_op)
@@ -326,11 +383,92 @@ class ParamStore:
     self._views_into(u, buf, "data")
     return work
 
+  # ------------------------------------------------------------------ fused paths (symmetric memory)
+  def peer_table(self, u: Unit) -> torch.Tensor:
+    """Device table with every rank's address of this unit's compute-dtype shard."""
+    t = getattr(u, "_peer_table", None)
+    if t is None:
+      t = self._cs.table_at(u.shard_offset)
+      u._peer_table = t
+    return t
+
+  def ensure_gathered(self, u: Unit):
+    """Stand-alone all-gather by peer loads (used when the first reader of a unit is not a GEMM)."""
+    if not u.pending_ag:
+      return
+    u.pending_ag = False
+    from ..ops import backend
+    esz = u.full.element_size()
+    backend.ext().gather_segments(self.peer_table(u), u.full, u.chunk * esz, self.seg_elems * esz, u.group_size, 2 * self.comm_ctas)
+
+  def ag_linear(self, u: Unit, p, x2: torch.Tensor):
+    """y = x2 @ W.T where W is a parameter (or a run of adjacent parameters) of a unit whose all-gather is still
+    pending: one launch copies the peers' shards of the whole unit and computes the product, tile by tile as rows
+    arrive. Returns None when the shapes do not fit the fused kernel (the caller then gathers and multiplies)."""
+    first = p.parts[0] if hasattr(p, "parts") else p
+    N, K = p.shape
+    M = x2.shape[0]
+    if not (x2.is_cuda and x2.dtype == torch.bfloat16 and M >= 128 and N >= 256 and K >= 64 and K % 8 == 0 and x2.stride(1) == 1):
+      return None
+    from ..ops import backend
+    off = u.offsets[u.params.index(first)]
+    out = torch.empty(M, N, dtype=x2.dtype, device=x2.device)
+    u.pending_ag = False
+    backend.ext().gemm_ag(x2, out, self.peer_table(u), u.full, N, K, u.chunk, self.seg_elems, off, u.group_size, self.seg_flags,
+                          self.comm_ctas)
+    return out
+
+  def _fused_acquire_grad(self, u: Unit):
+    if self._gbufs is None:
+      n = self.max_unit_numel()
+      self._gbufs = [self.symm.alloc(n, self.grad_dtype), self.symm.alloc(n, self.grad_dtype)]
+      self._next_slot = 0
+    b = self._next_slot
+    self._next_slot ^= 1
+    pend = self._gslot_pending[b]
+    if pend is not None:
+      ev, epoch = pend
+      torch.cuda.current_stream().wait_event(ev)          # my own reduction of this buffer has finished
+      self.symm.wait(3 + 2 * b, epoch)                    # and every peer has finished reading my copy
+      self._gslot_pending[b] = None
+    u.grad_slot = b
+    u.full_grad = self._gbufs[b].tensor[: u.numel]
+    self._views_into(u, u.full_grad, "main_grad")
+    for p in u.params:
+      p.grad_written = False
+
+  def _fused_reduce_scatter(self, u: Unit, accumulate: bool):
+    from ..ops import backend
+    for p in u.params:
+      if not p.grad_written:
+        p.main_grad.zero_()
+    b = u.grad_slot
+    dst = self.shard_view(u, self.grad_shard)
+    main = torch.cuda.current_stream()
+    ready = torch.cuda.Event()
+    ready.record(main)
+    with torch.cuda.stream(self.comm_stream):
+      self.comm_stream.wait_event(ready)
+      self.symm.signal(2 + 2 * b)                         # my gradients for this buffer are complete
+      self.symm.wait(2 + 2 * b)                           # ... and so are everyone else's
+      backend.ext().rs_sumsq(self._gbufs[b].table, u.group_rank * u.chunk, u.chunk, dst, bool(accumulate), 1.0, u.group_size,
+                             self.gradsq if self.gradsq_valid else None, 48)
+      epoch = self.symm.signal(3 + 2 * b)                 # I am done reading the peers' copies
+      done = torch.cuda.Event()
+      done.record(self.comm_stream)
+    self._gslot_pending[b] = (done, epoch)
+    self._rs_inflight.append((None, None, None, done))
+    u.full_grad, u.grad_slot = None, -1
+    for p in u.params:
+      p.main_grad = None
+
   def acquire_full_grad(self, u: Unit):
     """Bind a full-size gradient buffer to unit `u`. At most two buffers exist: when both are busy the
     oldest in-flight reduce-scatter is completed first."""
     if u.group_size == 1:
       return
+    if self.fused:
+      return self._fused_acquire_grad(u)
     if not self._grad_pool and len(self._rs_inflight) >= self.max_grad_buffers - 1 and self._rs_inflight:
       self._complete_oldest_rs()
     if self._grad_pool:
@@ -350,6 +488,8 @@ class ParamStore:
     `wait_reduce_scatters`."""
     if u.group_size == 1:
       return
+    if self.fused:
+      return self._fused_reduce_scatter(u, accumulate)
     for p in u.params:              # parameters never touched this step contribute zeros
       if not p.grad_written:
         p.main_grad.zero_()
@@ -370,6 +510,9 @@ class ParamStore:
 
   def _complete_oldest_rs(self):
     work, full, dst, tmp = self._rs_inflight.pop(0)
+    if full is None:                # fused path: `tmp` is the completion event of the reduction on the comm stream
+      torch.cuda.current_stream().wait_event(tmp)
+      return
     if work is not None:
       work.wait()
     if tmp is not None:
@@ -390,6 +533,9 @@ class ParamStore:
   def begin_step(self):
     """Reset per-step gradient bookkeeping (resident units overwrite on first write)."""
     self.ensure_grad_buffers()
+    if self.fused:
+      self.gradsq.zero_()
+      self.gradsq_valid = int(self.config.gradient_accumulation_steps) == 1
     for u in self.units.values():
       for p in u.params:
         p.grad_written = False

@@ -1,0 +1,99 @@
+"""Symmetric memory over NVLink: buffers that every rank of a node can address, plus epoch flags.
+
+MaxText has no communication code of its own: XLA lowers collectives to NCCL. Here, next to the
+NCCL process groups of `parallel.mesh`, each shard group owns a *symmetric heap*: every rank allocates the same
+buffers and exchanges handles, so a kernel running on one GPU can load from (or store to) the same offset of a
+peer's buffer with plain memory instructions. The fused kernels of `csrc/comm_sm100.cu` and the all-gather GEMM
+of `csrc/gemm_sm100.cu` take tables of such peer pointers.
+
+Allocation and handle exchange use `torch.distributed._symmetric_memory` (CUDA VMM + fd passing under the hood);
+everything that moves data is this repository's kernels. Synchronisation is by monotonically increasing epochs:
+`signal(slot)` writes this rank's epoch into every peer's flag row, `wait(slot)` spins on the local row until all
+peers reached it, with a time limit after which the kernel records a status code and returns (the host raises
+`CommTimeoutError` when it next checks `kernel_status`).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import backend
+
+
+class CommTimeoutError(RuntimeError):
+  pass
+
+
+def available() -> bool:
+  if not torch.cuda.is_available():
+    return False
+  try:
+    import torch.distributed._symmetric_memory as sm  # noqa: F401
+    return True
+  except Exception:  # pylint: disable=broad-except
+    return False
+
+
+class SymmTensor:
+  """A local tensor plus the device addresses of the same allocation on every rank of the group."""
+
+  def __init__(self, tensor: torch.Tensor, ptrs: list[int]):
+    self.tensor = tensor
+    self.ptrs = list(ptrs)
+    self.table = torch.tensor(self.ptrs, dtype=torch.int64, device=tensor.device)
+
+  def table_at(self, elem_offset: int) -> torch.Tensor:
+    """Pointer table of the sub-buffer that starts `elem_offset` elements into the allocation."""
+    if elem_offset == 0:
+      return self.table
+    return self.table + elem_offset * self.tensor.element_size()
+
+
+class SymmGroup:
+  N_SLOTS = 16
+
+  def __init__(self, group, device, wait_limit_ms: float = 20000.0):
+    import torch.distributed._symmetric_memory as sm
+    self._sm = sm
+    self.group = group if group is not None else dist.group.WORLD
+    self.device = torch.device(device)
+    self.rank = dist.get_rank(self.group)
+    self.world = dist.get_world_size(self.group)
+    self.wait_limit_ms = wait_limit_ms
+    self._handles = []
+    self.flags = self.alloc(self.N_SLOTS * self.world, torch.int32, zero=True)
+    self.epochs = [0] * self.N_SLOTS
+    dist.barrier(group=self.group)
+
+  def alloc(self, numel: int, dtype: torch.dtype, zero: bool = False) -> SymmTensor:
+    t = self._sm.empty(int(numel), dtype=dtype, device=self.device)
+    if zero:
+      t.zero_()
+      torch.cuda.synchronize(self.device)
+    hdl = self._sm.rendezvous(t, self.group.group_name if hasattr(self.group, "group_name") else self.group)
+    self._handles.append(hdl)
+    ptrs = [int(p) for p in hdl.buffer_ptrs]
+    # torch hands out one slab per rendezvous; the tensor may sit at an offset inside it
+    off = int(getattr(hdl, "offset", 0) or 0)
+    ptrs = [p + off for p in ptrs] if off and ptrs[self.rank] + off == t.data_ptr() else ptrs
+    assert ptrs[self.rank] == t.data_ptr(), "symmetric allocation does not start at the local tensor"
+    return SymmTensor(t, ptrs)
+
+  # ---- epoch flags (stream ordered)
+  def signal(self, slot: int) -> int:
+    self.epochs[slot] += 1
+    backend.ext().comm_signal(self.flags.table, slot, self.rank, self.world, self.epochs[slot])
+    return self.epochs[slot]
+
+  def wait(self, slot: int, epoch: int | None = None):
+    backend.ext().comm_wait(self.flags.tensor, slot, self.world, self.epochs[slot] if epoch is None else epoch, self.wait_limit_ms)
+
+  def barrier(self, slot: int = 0):
+    """All ranks' streams reach this point before any continues (device side, no host sync)."""
+    self.signal(slot)
+    self.wait(slot)
+
+  def check(self):
+    st = backend.ext().kernel_status(True)
+    if st != 0:
+      raise CommTimeoutError(f"a device-side wait timed out (status {st}) on rank {self.rank}")

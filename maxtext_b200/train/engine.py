@@ -269,6 +269,8 @@ class TrainEngine:
     lr = self.schedule(self.step_count)
     opt_metrics = self.optimizer.step(grad_scale, lr, self.step_count + 1, loss=(loss_sum * inv_w), grad_norm=raw_norm)
     self.step_count += 1
+    if getattr(store, "fused", False):
+      store.symm.barrier(0)       # updated shards are final on every rank before the next step reads them over NVLink
     lm_loss = loss_sum * inv_w
     metrics = {
         "learning/loss": lm_loss + aux, "learning/lm_loss": lm_loss, "learning/z_loss": z_sum * inv_w,
@@ -295,7 +297,12 @@ class TrainEngine:
     if self.world == 1:
       return F.sum_of_squares(store.grad_shard)
     total = torch.zeros((), dtype=torch.float32, device=self.device)
+    fused_sq = getattr(store, "fused", False) and store.gradsq_valid
+    if fused_sq:
+      total = total + store.gradsq[0]      # partials emitted by the fused reduce-scatter kernels
     for u in store.units.values():
+      if fused_sq and u.group_size > 1:
+        continue
       sq = F.sum_of_squares(store.shard_view(u, store.grad_shard))
       total = total + sq / self._replication(u)
     dist.all_reduce(total)

@@ -1,0 +1,50 @@
+"""Multi-GPU tier (needs >= 2 GPUs): peer-memory kernels against NCCL compositions, and the fused-communication
+train step against the NCCL-only step."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(mode, tmp_path, world=2):
+  if torch.cuda.device_count() < world:
+    pytest.skip(f"needs {world} GPUs")
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  port = s.getsockname()[1]
+  s.close()
+  res = os.path.join(str(tmp_path), "res")
+  procs = []
+  for r in range(world):
+    env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+               MAXTEXT_B200_QUIET="1")
+    procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multigpu_worker.py"), mode, res], cwd=ROOT, env=env,
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+  outs = []
+  for p in procs:
+    try:
+      o, _ = p.communicate(timeout=420)
+    except subprocess.TimeoutExpired:
+      for q in procs:
+        q.kill()
+      raise
+    outs.append(o.decode(errors="replace"))
+  for r in range(world):
+    path = f"{res}.{r}"
+    assert os.path.exists(path), outs[r][-3000:]
+    msg = open(path).read()
+    assert msg.startswith("ok"), msg[-3000:] + "\n" + outs[r][-1500:]
+
+
+def test_peer_memory_kernels(tmp_path):
+  _run("kernels", tmp_path)
+
+
+def test_fused_comm_train_step_matches_nccl(tmp_path):
+  _run("train", tmp_path)
