@@ -114,7 +114,15 @@ gather_segments_kernel(const uint4* const* __restrict__ peer_shards, uint4* __re
     const long hi = lo + seg_vec < chunk_vec ? lo + seg_vec : chunk_vec;
     const uint4* src = peer_shards[r];
     uint4* dst = full + (long)r * chunk_vec;
-    for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = src[i];
+    long i = lo + threadIdx.x;
+    for (; i + 7 * (long)blockDim.x < hi; i += 8 * (long)blockDim.x) {     // eight independent peer loads in flight per thread
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = src[i + u * (long)blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) dst[i + u * (long)blockDim.x] = v[u];
+    }
+    for (; i < hi; i += blockDim.x) dst[i] = src[i];
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0 && seg_flags) atomicExch(seg_flags + s, 1);

@@ -167,19 +167,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (is_comm_cta) {
-    // ------------------------------------------------------------ all-gather copier (all 192 threads)
-    const int n_segs = p.g_segs_per_chunk * p.g_world;
-    for (int k = (int)blockIdx.x - cta_stride; k < n_segs; k += p.g_comm_ctas) {
-      const int sgm = (p.g_first_seg + k) % n_segs;
-      const int r = sgm / p.g_segs_per_chunk;
-      const long lo = (long)(sgm % p.g_segs_per_chunk) * p.g_seg_vec;
-      const long hi = lo + p.g_seg_vec < p.g_chunk_vec ? lo + p.g_seg_vec : p.g_chunk_vec;
-      const uint4* src = p.g_peer_shards[r];
-      uint4* dst = p.g_full + (long)r * p.g_chunk_vec;
-      for (long i = lo + threadIdx.x; i < hi; i += NUM_THREADS) dst[i] = src[i];
-      __threadfence();
-      named_bar_sync(4, NUM_THREADS);
-      if (threadIdx.x == 0) atomicExch(p.g_seg_flags + sgm, 1);
+    // ------------------------------------------------------------ all-gather copier (one thread drives the copy engine)
+    // Peer shard -> shared memory -> local full buffer with untiled bulk copies (cp.async.bulk, per-CTA form), four
+    // 48 KB pieces in flight per CTA, so NVLink latency is covered by bytes in flight rather than by threads.
+    if (threadIdx.x == 0) {
+      constexpr uint32_t PIECE = Cfg::STAGE_BYTES;          // the GEMM's smem ring doubles as the staging area
+      const int n_segs = p.g_segs_per_chunk * p.g_world;
+      const long seg_bytes = p.g_seg_vec * 16, chunk_bytes = p.g_chunk_vec * 16;
+      uint32_t issued = 0, stored = 0;                      // pieces loaded / stored so far (ring position = count % STAGES)
+      bool ok = true;
+      // a piece in flight: where it goes and how long it is
+      long pend_dst[STAGES];
+      uint32_t pend_len[STAGES];
+      auto store_one = [&]() {
+        const uint32_t sidx = stored % STAGES;
+        if (!mbar_wait(full_bar(sidx), (stored / STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; return; }
+        const uint64_t gdst = reinterpret_cast<uint64_t>(p.g_full) + (uint64_t)pend_dst[sidx];
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_a0 + sidx * PIECE),
+                     "r"(pend_len[sidx]) : "memory");
+        tma_commit_group();
+        ++stored;
+      };
+      for (int k = (int)blockIdx.x - cta_stride; k < n_segs && ok; k += p.g_comm_ctas) {
+        const int sgm = (p.g_first_seg + k) % n_segs;
+        const int r = sgm / p.g_segs_per_chunk;
+        const long lo = (long)(sgm % p.g_segs_per_chunk) * seg_bytes;
+        const long hi = lo + seg_bytes < chunk_bytes ? lo + seg_bytes : chunk_bytes;
+        const uint64_t src = reinterpret_cast<uint64_t>(p.g_peer_shards[r]);
+        for (long off = lo; off < hi && ok; off += PIECE) {
+          const uint32_t len = (uint32_t)(hi - off < (long)PIECE ? hi - off : (long)PIECE);
+          if (issued - stored == STAGES) store_one();       // ring full: retire the oldest piece first
+          if (!ok) break;
+          const uint32_t sidx = issued % STAGES;
+          if (issued >= STAGES) tma_wait_group_read<0>();            // the stage's previous store has finished reading smem
+          mbar_arrive_expect_tx(full_bar(sidx), len);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_a0 + sidx * PIECE),
+                       "l"(src + (uint64_t)off), "r"(len), "r"(full_bar(sidx)) : "memory");
+          pend_dst[sidx] = (long)r * chunk_bytes + off;
+          pend_len[sidx] = len;
+          ++issued;
+        }
+        while (ok && stored < issued) store_one();          // drain this segment, then publish it
+        if (!ok) break;
+        tma_wait_group<0>();
+        __threadfence();
+        atomicExch(p.g_seg_flags + sgm, 1);
+      }
+      tma_wait_group<0>();
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)

@@ -399,7 +399,7 @@ class ParamStore:
     u.pending_ag = False
     from ..ops import backend
     esz = u.full.element_size()
-    backend.ext().gather_segments(self.peer_table(u), u.full, u.chunk * esz, self.seg_elems * esz, u.group_size, 2 * self.comm_ctas)
+    backend.ext().gather_segments(self.peer_table(u), u.full, u.chunk * esz, self.seg_elems * esz, u.group_size, 64)
 
   def ag_linear(self, u: Unit, p, x2: torch.Tensor):
     """y = x2 @ W.T where W is a parameter (or a run of adjacent parameters) of a unit whose all-gather is still
