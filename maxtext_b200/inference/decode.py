@@ -1,0 +1,48 @@
+"""`python -m maxtext.inference.decode <config.yml> prompt="..."`: load -> prefill -> insert -> generate loop -> text
+(src/maxtext/inference/decode.py:88-237)."""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from ..config import pyconfig
+from ..input_pipeline.tokenizer import build_tokenizer
+from ..utils import max_logging
+from .maxengine import MaxEngine
+
+
+def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -> str:
+  eng = engine or MaxEngine(config)
+  if engine is None:
+    eng.load_params()
+  tok = build_tokenizer(config)
+  ids = tok.encode(prompt if prompt is not None else config.prompt, add_bos=bool(config.add_bos))
+  ids = [i % config.vocab_size for i in ids][: int(config.max_prefill_predict_length)]
+  n = len(ids)
+  padded = torch.tensor(ids + [0] * (int(config.max_prefill_predict_length) - n), dtype=torch.long)
+  prefix, first = eng.prefill(padded, n)
+  state = eng.insert(prefix, eng.init_decode_state(1), 0)
+  out = [int(first.data[0, 0])]
+  for _ in range(n, int(config.max_target_length) - 1):
+    state, res = eng.generate(state)
+    t = int(res.data[0, 0])
+    out.append(t)
+    if t == getattr(tok, "eos_id", -1) or not bool(state.active[0]):
+      break
+  text = tok.decode(out)
+  if config.autoregressive_decode_assert:
+    assert text.startswith(config.autoregressive_decode_assert), f"generated {text!r}, expected prefix {config.autoregressive_decode_assert!r}"
+  return text
+
+
+def main(argv=None):
+  argv = list(sys.argv if argv is None else argv)
+  config = pyconfig.initialize(argv)
+  text = decode(config)
+  max_logging.log(f"Input `{config.prompt}` -> `{text}`")
+  return text
+
+
+if __name__ == "__main__":
+  main()

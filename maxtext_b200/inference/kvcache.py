@@ -1,0 +1,124 @@
+"""Key/value caches for prefill and autoregressive decoding.
+
+The reference keeps two caches per layer (prefill and AR) with configurable axis orders and merges the two
+attention partials (src/maxtext/inference/kvcache.py:249-1137; attention_op.py:2730). On a GPU one contiguous cache
+per layer is simpler and faster: `[slots, max_len, kv_heads, head_dim]`, written in place at each slot's current
+length; a prefill result is inserted by copying its rows into a slot. Optional int8 / fp8 storage with per
+(token, head) scales mirrors `KVQuant` (kvcache.py:49-150). `MlaKVCache` stores the compressed latent and the
+shared RoPE key (kvcache.py:1204) and expands them with `wkv_b` at attention time.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import reference as ref
+
+
+class KVQuant:
+  def __init__(self, dtype: str = "int8"):
+    self.kind = dtype
+    self.tdtype = torch.int8 if dtype == "int8" else torch.float8_e4m3fn
+    self.maxv = 127.0 if dtype == "int8" else 448.0
+
+  def quantize(self, x: torch.Tensor):
+    scale = x.float().abs().amax(dim=-1, keepdim=True).clamp_min(1e-8) / self.maxv
+    q = x.float() / scale
+    q = q.round().clamp(-127, 127).to(torch.int8) if self.kind == "int8" else q.to(self.tdtype)
+    return q, scale.to(torch.float32)
+
+  def dequantize(self, q, scale, dtype):
+    return (q.float() * scale).to(dtype)
+
+
+class LayerKVCache:
+  """Cache of one attention layer for `slots` concurrent sequences."""
+
+  def __init__(self, slots, max_len, kv_heads, head_dim, v_dim, dtype, device, quant: KVQuant | None = None):
+    self.slots, self.max_len, self.quant = slots, max_len, quant
+    sd = quant.tdtype if quant else dtype
+    self.dtype = dtype
+    self.k = torch.zeros(slots, max_len, kv_heads, head_dim, dtype=sd, device=device)
+    self.v = torch.zeros(slots, max_len, kv_heads, v_dim, dtype=sd, device=device)
+    if quant:
+      self.ks = torch.ones(slots, max_len, kv_heads, 1, dtype=torch.float32, device=device)
+      self.vs = torch.ones(slots, max_len, kv_heads, 1, dtype=torch.float32, device=device)
+    self.slot_ids: torch.Tensor | None = None     # which cache rows the current batch maps to
+    self.lengths: torch.Tensor | None = None      # tokens already cached per batch row (before this call)
+
+  def bind(self, slot_ids, lengths):
+    self.slot_ids, self.lengths = slot_ids, lengths
+
+  def _write(self, buf, sbuf, x, pos):
+    B, S = x.shape[:2]
+    rows = self.slot_ids[:, None].expand(B, S)
+    if self.quant:
+      q, s = self.quant.quantize(x)
+      buf[rows, pos] = q
+      sbuf[rows, pos] = s
+    else:
+      buf[rows, pos] = x.to(buf.dtype)
+
+  def _read(self, buf, sbuf, upto):
+    x = buf[self.slot_ids, :upto]
+    if self.quant:
+      return self.quant.dequantize(x, sbuf[self.slot_ids, :upto], self.dtype)
+    return x
+
+  def attend(self, q, k, v, ctx, window=0, soft_cap=0.0, sinks=None):
+    """Append k/v of the S new tokens at each row's current length, then attend over everything cached."""
+    B, S = q.shape[:2]
+    pos = self.lengths[:, None] + torch.arange(S, device=q.device)[None]           # absolute positions of the new tokens
+    self._write(self.k, getattr(self, "ks", None), k, pos)
+    self._write(self.v, getattr(self, "vs", None), v, pos)
+    upto = int((self.lengths.max() + S).item()) if ctx.mode != "prefill" else int(S + self.lengths.max().item())
+    K, V = self._read(self.k, getattr(self, "ks", None), upto), self._read(self.v, getattr(self, "vs", None), upto)
+    kv_pos = torch.arange(upto, device=q.device)[None].expand(B, upto)
+    valid_len = (self.lengths + S)[:, None]
+    mask = ref.attention_mask(pos, kv_pos, None, None, True, window) & (kv_pos < valid_len)[:, None, None, :]
+    if ctx.segment_ids is not None and ctx.mode == "prefill":
+      mask = mask & (ctx.segment_ids[:, None, :, None] != 0)
+    return ref.attention(q, K, V, mask, 1.0, soft_cap, sinks=sinks.data if sinks is not None else None)
+
+
+class MlaLayerCache(LayerKVCache):
+  """Latent cache: kv_lora_rank + rope_dim numbers per token instead of heads x (qk + v)."""
+
+  def __init__(self, slots, max_len, kv_lora_rank, rope_dim, dtype, device):
+    self.slots, self.max_len, self.quant, self.dtype = slots, max_len, None, dtype
+    self.latent = torch.zeros(slots, max_len, kv_lora_rank, dtype=dtype, device=device)
+    self.k_rope = torch.zeros(slots, max_len, rope_dim, dtype=dtype, device=device)
+    self.slot_ids = self.lengths = None
+
+  def attend_mla(self, q, latent, k_rope, mla, ctx):
+    from ..ops import functional as F
+    B, S = q.shape[:2]
+    pos = self.lengths[:, None] + torch.arange(S, device=q.device)[None]
+    rows = self.slot_ids[:, None].expand(B, S)
+    self.latent[rows, pos] = latent.to(self.dtype)
+    self.k_rope[rows, pos] = k_rope.reshape(B, S, -1).to(self.dtype)
+    upto = int((self.lengths.max() + S).item())
+    lat, kr = self.latent[self.slot_ids, :upto], self.k_rope[self.slot_ids, :upto]
+    kv = F.linear(lat, mla.wkv_b).view(B, upto, mla.h, mla.nope + mla.vd)
+    k = torch.cat([kv[..., :mla.nope], kr[:, :, None, :].expand(B, upto, mla.h, mla.rope_d)], dim=-1)
+    v = kv[..., mla.nope:]
+    kv_pos = torch.arange(upto, device=q.device)[None].expand(B, upto)
+    mask = ref.attention_mask(pos, kv_pos) & (kv_pos < (self.lengths + S)[:, None])[:, None, None, :]
+    return ref.attention(q, k, v, mask, 1.0)
+
+
+def make_caches(model, slots: int, max_len: int, device, quantize: bool = False):
+  """One cache per attention block of the model, in layer order."""
+  c = model.config
+  dt = model.store.compute_dtype
+  quant = KVQuant(c.kv_quant_dtype) if (quantize or c.quantize_kvcache) else None
+  out = []
+  for layer in model.layers:
+    per_layer = []
+    for blk in layer.blocks:
+      if blk.plan.attention == "mla":
+        per_layer.append(MlaLayerCache(slots, max_len, c.kv_lora_rank, c.qk_rope_head_dim, dt, device))
+      else:
+        a = blk.attn
+        per_layer.append(LayerKVCache(slots, max_len, a.hkv_l, a.dh, a.dh, dt, device, quant))
+    out.append(per_layer)
+  return out

@@ -1,0 +1,165 @@
+"""Decode engine with the MaxEngine API shape: load_params / prefill / insert / generate / init_decode_state
+(src/maxtext/inference/maxengine/maxengine.py:114-1933).
+
+State lives in `DecodeState`: per-layer KV caches with `slots` rows, the last sampled token and the next position of
+every slot. `prefill` runs one prompt through the model into a private single-row cache and samples the first
+token; `insert` copies that cache into a slot of the decode state; `generate` advances every active slot by one
+token. All units of the model must be resident (single GPU, or tensor-parallel ranks each holding their slice).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.transformer import Transformer
+from . import inference_utils, kvcache
+
+
+@dataclass
+class Prefix:
+  caches: list
+  length: int
+  first_token: torch.Tensor       # [1]
+  logits: torch.Tensor            # [1, V] logits at the last prompt position
+  log_prob: torch.Tensor | None = None
+
+
+@dataclass
+class DecodeState:
+  caches: list
+  tokens: torch.Tensor            # [slots] last sampled token per slot
+  next_pos: torch.Tensor          # [slots] position the next token will be written at (= cached length)
+  active: torch.Tensor            # [slots] bool
+  generated: torch.Tensor         # [slots] tokens generated so far
+  token_logp: torch.Tensor | None = None
+
+
+@dataclass
+class ResultTokens:
+  data: torch.Tensor              # [slots, 3] = token, valid flag, generated length
+  log_prob: torch.Tensor | None = None
+
+
+class MaxEngine:
+  def __init__(self, config, mesh=None, device=None, model: Transformer | None = None):
+    self.config = c = config
+    if device is None:
+      device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and c.hardware != "cpu" else "cpu"
+    self.device = torch.device(device)
+    self.model = model or Transformer(c, mesh, self.device)
+    self.max_len = int(c.max_target_length)
+    self.max_prefill = int(c.max_prefill_predict_length)
+    self.generator = torch.Generator(device=self.device)
+    self.generator.manual_seed(int(c.init_weights_seed))
+
+  # ------------------------------------------------------------------ params
+  def load_params(self, path: str | None = None, seed: int | None = None):
+    """Params-only checkpoint (`load_parameters_path`) or random init when no path is configured."""
+    from ..checkpoint import manager as ckpt
+    path = path or self.config.load_parameters_path
+    if path:
+      ckpt.load_params_only(path, _EngineView(self), self.model.mesh)
+    else:
+      self.model.store.initialize(seed=self.config.init_weights_seed if seed is None else seed)
+    return self.model.store
+
+  # ------------------------------------------------------------------ state
+  def init_decode_state(self, slots: int | None = None) -> DecodeState:
+    c = self.config
+    slots = int(slots or max(1, int(c.per_device_batch_size)))
+    dev = self.device
+    return DecodeState(kvcache.make_caches(self.model, slots, self.max_len, dev), torch.zeros(slots, dtype=torch.long, device=dev),
+                       torch.zeros(slots, dtype=torch.long, device=dev), torch.zeros(slots, dtype=torch.bool, device=dev),
+                       torch.zeros(slots, dtype=torch.long, device=dev),
+                       torch.zeros(slots, device=dev) if c.return_log_prob else None)
+
+  def _bind(self, caches, slot_ids, lengths):
+    for per_layer in caches:
+      for cch in per_layer:
+        cch.bind(slot_ids, lengths)
+
+  def _sample(self, logits):
+    c = self.config
+    return inference_utils.sampling(logits, c.decode_sampling_strategy, int(c.decode_sampling_top_k), float(c.decode_sampling_nucleus_p),
+                                    float(c.decode_sampling_temperature), self.generator)
+
+  # ------------------------------------------------------------------ prefill / insert / generate
+  @torch.no_grad()
+  def prefill(self, padded_tokens: torch.Tensor, true_length: int, params=None) -> tuple[Prefix, ResultTokens]:
+    """padded_tokens [P] (right padded); only the first `true_length` enter the cache."""
+    dev = self.device
+    toks = padded_tokens[:true_length].to(dev).long()[None]
+    caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, true_length), dev)
+    self._bind(caches, torch.zeros(1, dtype=torch.long, device=dev), torch.zeros(1, dtype=torch.long, device=dev))
+    pos = torch.arange(true_length, device=dev)[None]
+    logits = self.model.forward(toks, pos, None, mode="prefill", caches=caches)[:, -1]
+    tok = self._sample(logits)
+    lp = inference_utils.log_prob_of(logits, tok) if self.config.return_log_prob else None
+    res = ResultTokens(torch.tensor([[int(tok), 1, 1]], device=dev), lp)
+    return Prefix(caches, true_length, tok, logits, lp), res
+
+  def prefill_chunked(self, tokens: torch.Tensor, chunk: int | None = None) -> tuple[Prefix, ResultTokens]:
+    """Chunked prefill (src/maxtext/inference/kvcache.py:609-712): the prompt enters the cache `chunk` tokens at a time."""
+    dev = self.device
+    chunk = int(chunk or self.config.prefill_chunk_size)
+    n = int(tokens.numel())
+    caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, n), dev)
+    slot = torch.zeros(1, dtype=torch.long, device=dev)
+    logits = None
+    with torch.no_grad():
+      for s in range(0, n, chunk):
+        e = min(n, s + chunk)
+        self._bind(caches, slot, torch.full((1,), s, dtype=torch.long, device=dev))
+        pos = torch.arange(s, e, device=dev)[None]
+        logits = self.model.forward(tokens[s:e].to(dev).long()[None], pos, None, mode="decode", caches=caches)[:, -1]
+    tok = self._sample(logits)
+    return Prefix(caches, n, tok, logits), ResultTokens(torch.tensor([[int(tok), 1, 1]], device=dev))
+
+  @torch.no_grad()
+  def insert(self, prefix: Prefix, state: DecodeState, slot: int) -> DecodeState:
+    n = prefix.length
+    for dst_layer, src_layer in zip(state.caches, prefix.caches):
+      for d, s in zip(dst_layer, src_layer):
+        for name in ("k", "v", "ks", "vs", "latent", "k_rope"):
+          if hasattr(s, name) and hasattr(d, name):
+            getattr(d, name)[slot, :n] = getattr(s, name)[0, :n]
+    state.tokens[slot] = prefix.first_token.reshape(-1)[0]
+    state.next_pos[slot] = n
+    state.active[slot] = True
+    state.generated[slot] = 1
+    return state
+
+  @torch.no_grad()
+  def generate(self, state: DecodeState, params=None) -> tuple[DecodeState, ResultTokens]:
+    """One autoregressive step for every slot (inactive slots compute too; their results are flagged invalid)."""
+    dev = self.device
+    slots = state.tokens.shape[0]
+    ids = torch.arange(slots, device=dev)
+    self._bind(state.caches, ids, state.next_pos.clone())
+    logits = self.model.forward(state.tokens[:, None], state.next_pos[:, None], None, mode="decode", caches=state.caches)[:, -1]
+    tok = self._sample(logits)
+    if state.token_logp is not None:
+      state.token_logp = inference_utils.log_prob_of(logits, tok)
+    state.tokens = torch.where(state.active, tok, state.tokens)
+    state.next_pos = state.next_pos + state.active.long()
+    state.generated = state.generated + state.active.long()
+    full = state.next_pos >= self.max_len - 1
+    res = ResultTokens(torch.stack([state.tokens, state.active.long(), state.generated], dim=1), state.token_logp)
+    state.active = state.active & ~full
+    return state, res
+
+  def free_slot(self, state: DecodeState, slot: int):
+    state.active[slot] = False
+    state.next_pos[slot] = 0
+    state.generated[slot] = 0
+
+
+class _EngineView:
+  """Adapter so checkpoint loading can treat an inference engine like a train engine."""
+
+  def __init__(self, eng: MaxEngine):
+    self.store, self.config, self.model = eng.model.store, eng.config, eng.model
+    self.optimizer = type("NoOpt", (), {"state_arrays": staticmethod(lambda: {})})()
+    self.step_count = 0
+    self.device = eng.device

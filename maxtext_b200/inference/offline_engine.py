@@ -1,0 +1,77 @@
+"""In-process continuous batching over the decode engine (src/maxtext/inference/offline_engine.py:742-954).
+
+Requests wait in a queue; whenever a slot is free the next prompt is prefilled and inserted, every `generate` call
+advances all active slots by one token, finished sequences (EOS or length limit) free their slot at once."""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+import torch
+
+from .maxengine import MaxEngine
+
+
+@dataclass
+class Request:
+  rid: int
+  tokens: list
+  max_new_tokens: int = 32
+  output: list = field(default_factory=list)
+  done: bool = False
+
+
+class OfflineEngine:
+  def __init__(self, engine: MaxEngine, slots: int = 4, eos_id: int = -1):
+    self.eng, self.slots, self.eos_id = engine, slots, eos_id
+    self.state = engine.init_decode_state(slots)
+    self.queue: deque[Request] = deque()
+    self.running: dict[int, Request] = {}
+    self.steps = 0
+
+  def submit(self, tokens, max_new_tokens=32) -> Request:
+    r = Request(len(self.queue) + len(self.running) + self.steps * 1000, list(tokens), max_new_tokens)
+    self.queue.append(r)
+    return r
+
+  def _fill_free_slots(self):
+    for s in range(self.slots):
+      if s in self.running or not self.queue:
+        continue
+      r = self.queue.popleft()
+      t = torch.tensor(r.tokens, dtype=torch.long)
+      prefix, first = self.eng.prefill(t, len(r.tokens))
+      self.state = self.eng.insert(prefix, self.state, s)
+      r.output.append(int(first.data[0, 0]))
+      self.running[s] = r
+      self._maybe_finish(s)
+
+  def _maybe_finish(self, s):
+    r = self.running.get(s)
+    if r is None:
+      return
+    if len(r.output) >= r.max_new_tokens or r.output[-1] == self.eos_id or not bool(self.state.active[s]):
+      r.done = True
+      self.eng.free_slot(self.state, s)
+      del self.running[s]
+
+  def step(self):
+    self._fill_free_slots()
+    if not self.running:
+      return
+    self.state, res = self.eng.generate(self.state)
+    self.steps += 1
+    for s in list(self.running):
+      self.running[s].output.append(int(res.data[s, 0]))
+      self._maybe_finish(s)
+
+  def run_until_done(self, max_steps: int = 100000):
+    n = 0
+    while (self.queue or self.running) and n < max_steps:
+      self.step()
+      n += 1
+
+  def batch_inference(self, prompts, max_new_tokens=32):
+    reqs = [self.submit(p, max_new_tokens) for p in prompts]
+    self.run_until_done()
+    return [r.output for r in reqs]

@@ -103,10 +103,14 @@ class DecoderLayer:
     self.params = b.params
 
   def __call__(self, x, ctx: LayerCtx):
+    caches = ctx.cache                      # inference: one cache per block of this layer
     for i, blk in enumerate(self.blocks):
       ctx.name_prefix = f"b{i}/" if len(self.blocks) > 1 else ""
+      if caches is not None:
+        ctx.cache = caches[i] if isinstance(caches, (list, tuple)) else caches
       x = blk(x, ctx)
     ctx.name_prefix = ""
+    ctx.cache = caches
     return x
 
 

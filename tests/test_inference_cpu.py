@@ -1,0 +1,92 @@
+"""Decode engine: greedy decode equals the argmax of a full forward pass; insert / slots / sampling / cache quantization."""
+import pytest
+import torch
+
+from helpers import tiny_config
+from maxtext_b200.inference import inference_utils
+from maxtext_b200.inference.maxengine import MaxEngine
+
+
+def _engine(model="llama3-8b", extra=()):
+  cfg = tiny_config(model, ["max_target_length=48", "max_prefill_predict_length=16", "per_device_batch_size=2", *extra])
+  eng = MaxEngine(cfg, device="cpu")
+  eng.load_params()
+  return eng, cfg
+
+
+@pytest.mark.parametrize("model", ["llama3-8b", "gemma2-2b", "deepseek2-16b", "qwen3-8b", "mixtral-8x7b"])
+def test_greedy_decode_matches_full_forward(model):
+  eng, cfg = _engine(model)
+  torch.manual_seed(0)
+  prompt = torch.randint(1, cfg.vocab_size, (9,))
+  prefix, first = eng.prefill(torch.nn.functional.pad(prompt, (0, 7)), 9)
+  state = eng.init_decode_state(2)
+  state = eng.insert(prefix, state, 1)
+  seq = [int(first.data[0, 0])]
+  for _ in range(6):
+    state, res = eng.generate(state)
+    assert int(res.data[1, 1]) == 1 and int(res.data[0, 1]) == 0       # slot 1 active, slot 0 idle
+    seq.append(int(res.data[1, 0]))
+  # oracle: re-run the whole sequence without a cache, step by step
+  cur = prompt.clone()
+  want = []
+  for _ in range(7):
+    logits = eng.model.forward(cur[None])
+    nxt = int(logits[0, -1].argmax())
+    want.append(nxt)
+    cur = torch.cat([cur, torch.tensor([nxt])])
+  assert seq == want
+
+
+def test_chunked_prefill_equals_prefill():
+  eng, cfg = _engine()
+  prompt = torch.randint(1, cfg.vocab_size, (13,))
+  a, _ = eng.prefill(prompt, 13)
+  b, _ = eng.prefill_chunked(prompt, chunk=4)
+  assert torch.allclose(a.logits, b.logits, atol=1e-4) and int(a.first_token) == int(b.first_token)
+
+
+def test_quantized_kv_cache_stays_close():
+  eng, cfg = _engine(extra=["quantize_kvcache=true", "kv_quant_dtype=int8"])
+  ref_eng, _ = _engine()
+  prompt = torch.randint(1, cfg.vocab_size, (12,))
+  a, _ = eng.prefill(prompt, 12)
+  b, _ = ref_eng.prefill(prompt, 12)
+  st = eng.insert(a, eng.init_decode_state(1), 0)
+  st, _ = eng.generate(st)
+  assert a.caches[0][0].k.dtype == torch.int8
+  assert (a.logits - b.logits).abs().max() < 0.15                        # int8 keys/values perturb the logits only slightly
+  assert int(st.next_pos[0]) == 13
+
+
+def test_sampling_strategies():
+  g = torch.Generator().manual_seed(0)
+  logits = torch.tensor([[0.0, 5.0, 4.0, -1.0, 3.0]]).repeat(2000, 1)
+  assert (inference_utils.sampling(logits, "greedy") == 1).all()
+  tk = inference_utils.sampling(logits, "topk", topk=2, generator=g)
+  assert set(tk.unique().tolist()) <= {1, 2}
+  nu = inference_utils.sampling(logits, "nucleus", nucleus_p=0.7, generator=g)
+  assert set(nu.unique().tolist()) <= {1, 2}
+  co = inference_utils.sampling(logits, "composite", topk=3, nucleus_p=0.99, temperature=0.5, generator=g)
+  assert set(co.unique().tolist()) <= {1, 2, 4}
+  w = inference_utils.sampling(logits, "weighted", temperature=1.0, generator=g)
+  frac = (w == 1).float().mean().item()
+  assert abs(frac - torch.softmax(logits[0], -1)[1].item()) < 0.05
+
+
+def test_decode_cli_and_offline_engine_and_microbenchmark():
+  from maxtext_b200.inference import decode as D, microbenchmark
+  from maxtext_b200.inference.offline_engine import OfflineEngine
+  eng, cfg = _engine(extra=["vocab_size=300", "prompt=hello"])
+  text = D.decode(cfg, engine=eng)
+  assert isinstance(text, str)
+  off = OfflineEngine(eng, slots=2)
+  prompts = [[5, 6, 7], [9, 10, 11, 12], [3, 4], [8, 8, 8, 8, 8]]
+  outs = off.batch_inference(prompts, max_new_tokens=5)
+  assert [len(o) for o in outs] == [5, 5, 5, 5]
+  # continuous batching must give each request the same tokens as running it alone
+  solo = OfflineEngine(eng, slots=1).batch_inference([prompts[2]], max_new_tokens=5)[0]
+  assert outs[2] == solo
+  res = microbenchmark.run(tiny_config("llama3-8b", ["max_target_length=48", "max_prefill_predict_length=16", "inference_microbenchmark_prefill_lengths=8,16",
+                                                    "inference_microbenchmark_loop_iters=1"]), eng)
+  assert set(res["prefill"]) == {8, 16} and res["generate"]["tokens_per_s"] > 0
