@@ -556,7 +556,8 @@ def adamw_flat(master, grad, m, v, shadow, lr, b1, b2, eps, eps_root, wd, step, 
   1/total_weights) so no host synchronisation is needed. `shadow` (compute dtype) may alias master."""
   bc1, bc2 = 1.0 - b1 ** step, 1.0 - b2 ** step
   if backend.use_cuda_kernels(master) and master.dtype == torch.float32 and grad.dtype == torch.float32 \
-      and v.dtype == torch.float32 and m.dtype in (torch.float32, torch.bfloat16):
+      and v.dtype == torch.float32 and m.dtype in (torch.float32, torch.bfloat16) and master.numel() % 4 == 0 \
+      and master.data_ptr() % 16 == 0:
     sh = shadow if (shadow is not None and shadow.data_ptr() != master.data_ptr()) else None
     backend.ext().adamw(master, grad, m, v, sh, float(lr), float(b1), float(b2), float(eps), float(eps_root), float(wd),
                         float(bc1), float(bc2), grad_scale)

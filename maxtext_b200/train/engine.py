@@ -96,6 +96,9 @@ class TrainEngine:
     seg = seg.to(self.device, non_blocking=True) if seg is not None else None
     tseg = batch.get("targets_segmentation")
     weights = (tseg.to(self.device) != 0).float() if tseg is not None else torch.ones(B, S, device=self.device)
+    if batch.get("loss_weights") is not None:
+      # post-training objectives (DPO, GRPO...) express their gradient as per-token weights on the token losses
+      weights = batch["loss_weights"].to(self.device).float()
     if c.dataset_type == "synthetic" and not c.packing_in_synthetic:
       seg = None   # synthetic batches are one segment per row by construction: skip the mask work
 
@@ -138,7 +141,8 @@ class TrainEngine:
     if c.logits_via_embedding:
       self._gather(0, async_op=False)
     w_flat = weights.reshape(-1)
-    total_w = w_flat.sum()
+    total_w = w_flat.sum() if batch.get("loss_normalizer") is None else \
+        torch.as_tensor(float(batch["loss_normalizer"]), device=self.device, dtype=torch.float32)
     head_units = self._units[hi] + (self._units[0] if c.logits_via_embedding else [])
     if compute_grads:
       for u in head_units:
@@ -213,9 +217,32 @@ class TrainEngine:
       p.collect_leaf_grad()
     return None
 
+  def custom_loss_step(self, batch: dict, loss_fn) -> dict:
+    """One optimizer step on loss_fn(logits [T,V] fp32, targets [T], mask [T]) -> scalar, differentiated by autograd
+    through the output head (full logits are materialised: meant for small models, e.g. distillation)."""
+    self._custom_loss = loss_fn
+    try:
+      b = dict(batch)
+      b["loss_normalizer"] = 1.0
+      self.fwd_bwd(b)
+    finally:
+      self._custom_loss = None
+    return self.update()
+
   def _run_head(self, x, targets, weights, compute_grads):
     c, model = self.config, self.model
     B, S, D = x.shape
+    fn = getattr(self, "_custom_loss", None)
+    if fn is not None and compute_grads:
+      x_in = x.detach().requires_grad_(True)
+      with torch.enable_grad():
+        h = model.final_norm(x_in)
+        logits = F.linear(h.reshape(B * S, D), model.head_param()).float() * model.head_logit_scale()
+        loss = fn(logits, targets.long(), weights)
+      loss.backward()
+      for p in model.head_params:
+        p.collect_leaf_grad()
+      return loss.detach().float(), torch.zeros((), device=self.device), x_in.grad
     x_in = x.detach().requires_grad_(compute_grads)
     with torch.set_grad_enabled(compute_grads):
       h = model.final_norm(x_in)
@@ -332,6 +359,34 @@ class TrainEngine:
       for k in range(g):
         self.fwd_bwd({key: v[k * mb:(k + 1) * mb] for key, v in batch.items()})
     return self.update()
+
+  @torch.no_grad()
+  def token_losses(self, batch: dict) -> torch.Tensor:
+    """Per-token cross entropy [B, S] (no gradients): the building block of sequence log-probabilities."""
+    model = self.model
+    tokens = batch["inputs"].to(self.device)
+    targets = batch["targets"].to(self.device)
+    B, S = tokens.shape
+    positions = batch.get("inputs_position")
+    positions = positions.to(self.device) if positions is not None else torch.arange(S, device=self.device)[None].expand(B, S)
+    seg = batch.get("inputs_segmentation")
+    seg = seg.to(self.device) if seg is not None else None
+    ctx = model.make_ctx(positions, seg, "train", tokens)
+    for i in range(len(self._units)):
+      self._gather(i, async_op=False)
+    x = model.embed(tokens, positions)
+    for i, layer in enumerate(model.layers):
+      ctx.layer_index, ctx.saved, ctx.aux_losses = i, None, []
+      x = layer(x, ctx)
+    h = model.final_norm(x).reshape(B * S, -1)
+    out = torch.empty(B * S, dtype=torch.float32, device=self.device)
+    from ..ops import reference as _ref
+    for s0 in range(0, B * S, 2048):
+      lg = F.head_logits(h[s0:s0 + 2048], model.head_param(), self.config.final_logits_soft_cap, model.head_logit_scale())
+      out[s0:s0 + 2048] = _ref.cross_entropy(lg, targets.reshape(-1)[s0:s0 + 2048])[0]
+    for i in range(len(self._units)):
+      self._release(i)
+    return out.view(B, S)
 
   @torch.no_grad()
   def eval_step(self, batch: dict) -> dict:

@@ -1,0 +1,121 @@
+"""Post-training loops built on the step-wise engine API (`fwd_bwd` / `update`): SFT, DPO, GRPO-style RL, distillation
+(src/maxtext/trainers/post_train/{sft/train_sft.py, dpo/train_dpo.py, rl/train_rl.py, distillation/train_distill.py}).
+Rollouts for RL come from this repository's decode engine instead of an external vLLM / Tunix cluster."""
+from __future__ import annotations
+
+import copy
+
+import torch
+
+from ...inference.maxengine import MaxEngine
+from ...train.engine import TrainEngine
+from . import objectives as O
+
+
+def _pad(seqs, S, pad=0):
+  out = torch.full((len(seqs), S + 1), pad, dtype=torch.long)
+  for i, s in enumerate(seqs):
+    s = list(s)[: S + 1]
+    out[i, :len(s)] = torch.tensor(s)
+  return out
+
+
+def make_lm_batch(seqs, S):
+  t = _pad(seqs, S)
+  return {"inputs": t[:, :-1].int(), "targets": t[:, 1:].int()}, torch.tensor([min(len(s), S + 1) for s in seqs])
+
+
+# ------------------------------------------------------------------------------------------------ SFT
+def sft_step(engine: TrainEngine, prompts, completions) -> dict:
+  S = int(engine.config.max_target_length)
+  seqs = [list(p) + list(c) for p, c in zip(prompts, completions)]
+  batch, total = make_lm_batch(seqs, S)
+  mask = O.sft_mask(torch.tensor([len(p) for p in prompts]), total, S, bool(engine.config.sft_train_on_completion_only))
+  batch["loss_weights"] = mask
+  return engine.train_step(batch)
+
+
+# ------------------------------------------------------------------------------------------------ DPO
+class DPOTrainer:
+  def __init__(self, engine: TrainEngine, beta: float = 0.1, label_smoothing: float = 0.0):
+    self.eng, self.beta, self.ls = engine, beta, label_smoothing
+    self.ref_master = engine.store.master.clone()          # frozen reference policy = the starting weights
+
+  def _logps(self, batch, mask, reference: bool):
+    s = self.eng.store
+    if reference:
+      cur = s.master.clone()
+      s.master.copy_(self.ref_master)
+      s.sync_compute_from_master()
+    lp = O.sequence_logprob(self.eng.token_losses(batch).cpu(), mask)
+    if reference:
+      s.master.copy_(cur)
+      s.sync_compute_from_master()
+    return lp
+
+  def step(self, prompts, chosen, rejected) -> dict:
+    S = int(self.eng.config.max_target_length)
+    pl = torch.tensor([len(p) for p in prompts])
+    bc, tc = make_lm_batch([list(p) + list(c) for p, c in zip(prompts, chosen)], S)
+    br, tr = make_lm_batch([list(p) + list(c) for p, c in zip(prompts, rejected)], S)
+    mc, mr = O.sft_mask(pl, tc, S), O.sft_mask(pl, tr, S)
+    pi_c, pi_r = self._logps(bc, mc, False), self._logps(br, mr, False)
+    ref_c, ref_r = self._logps(bc, mc, True), self._logps(br, mr, True)
+    loss, wc, wr, acc = O.dpo_weights(pi_c, pi_r, ref_c, ref_r, mc, mr, self.beta, self.ls)
+    n = len(prompts)
+    for b, w in ((bc, wc), (br, wr)):
+      b["loss_weights"], b["loss_normalizer"] = w, float(n)
+      self.eng.fwd_bwd(b)
+    m = self.eng.update()
+    m["dpo/loss"], m["dpo/reward_accuracy"] = loss.mean(), acc
+    return m
+
+
+# ------------------------------------------------------------------------------------------------ GRPO
+class GRPOTrainer:
+  """Sample `group_size` completions per prompt with the decode engine, score them, take one clipped policy step."""
+
+  def __init__(self, engine: TrainEngine, reward_fn, group_size: int = 4, clip: float = 0.2, max_new_tokens: int = 8):
+    self.eng, self.reward_fn, self.G, self.clip, self.max_new = engine, reward_fn, group_size, clip, max_new_tokens
+    icfg = engine.config.replace(decode_sampling_strategy="weighted")
+    self.sampler = MaxEngine(icfg, device=engine.device, model=engine.model)
+
+  def rollout(self, prompt):
+    prefix, first = self.sampler.prefill(torch.tensor(prompt), len(prompt))
+    st = self.sampler.insert(prefix, self.sampler.init_decode_state(1), 0)
+    out = [int(first.data[0, 0])]
+    for _ in range(self.max_new - 1):
+      st, res = self.sampler.generate(st)
+      out.append(int(res.data[0, 0]))
+    return out
+
+  def step(self, prompts) -> dict:
+    S = int(self.eng.config.max_target_length)
+    ps, cs = [], []
+    for p in prompts:
+      for _ in range(self.G):
+        ps.append(list(p))
+        cs.append(self.rollout(list(p)))
+    rewards = torch.tensor([float(self.reward_fn(p, c)) for p, c in zip(ps, cs)])
+    adv = O.grpo_advantages(rewards, self.G)
+    batch, total = make_lm_batch([p + c for p, c in zip(ps, cs)], S)
+    mask = O.sft_mask(torch.tensor([len(p) for p in ps]), total, S)
+    old = self.eng.token_losses(batch).cpu()
+    surrogate, w = O.grpo_weights(old, old, adv, mask, self.clip)       # on-policy: ratio = 1 at the first step
+    batch["loss_weights"], batch["loss_normalizer"] = w, float(mask.sum().clamp_min(1))
+    m = self.eng.train_step(batch)
+    m["rl/mean_reward"], m["rl/surrogate"] = rewards.mean(), surrogate
+    return m
+
+
+# ------------------------------------------------------------------------------------------------ distillation
+def distill_step(student: TrainEngine, teacher: TrainEngine, batch: dict, alpha: float | None = None, temperature: float | None = None):
+  """Online distillation on small models: full logits of both models, loss by autograd through the student's head and
+  the engine's layer schedule (the hidden-state gradient is injected with `fwd_bwd_from_hidden_grad`)."""
+  c = student.config
+  alpha = float(c.distill_alpha if alpha is None else alpha)
+  temperature = float(c.distill_temperature if temperature is None else temperature)
+  with torch.no_grad():
+    t_logits = teacher.model.forward(batch["inputs"].to(teacher.device))
+  return student.custom_loss_step(batch, lambda logits, targets, mask: O.distillation_loss(
+      logits, t_logits.reshape(-1, t_logits.shape[-1]), targets, mask, alpha, temperature))

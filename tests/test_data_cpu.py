@@ -1,0 +1,52 @@
+"""Packing, shifting, file pipeline (jsonl) with rank sharding and iterator state, byte tokenizer."""
+import json
+
+import numpy as np
+
+from helpers import tiny_config
+from maxtext_b200.input_pipeline import packing
+from maxtext_b200.input_pipeline.file_pipeline import FileDataIterator
+from maxtext_b200.input_pipeline.tokenizer import ByteTokenizer
+
+
+def test_first_fit_packing_and_shift():
+  ex = [np.arange(1, 6), np.arange(10, 13), np.arange(20, 27), np.arange(30, 32)]
+  rows = list(packing.pack_first_fit(ex, 9))
+  assert len(rows) == 2
+  assert rows[0]["tokens"].tolist() == [1, 2, 3, 4, 5, 10, 11, 12, 0]
+  assert rows[0]["segmentation"].tolist() == [1, 1, 1, 1, 1, 2, 2, 2, 0]
+  assert rows[0]["position"].tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 0]
+  assert rows[1]["tokens"].tolist()[:9] == [20, 21, 22, 23, 24, 25, 26, 30, 31]
+  sh = packing.shift_for_lm(rows[0])
+  assert sh["inputs"].tolist() == [1, 2, 3, 4, 5, 10, 11, 12] and sh["targets"].tolist() == [2, 3, 4, 5, 10, 11, 12, 0]
+  assert sh["targets_segmentation"].tolist() == [1, 1, 1, 1, 0, 2, 2, 0]          # no loss across document boundaries
+  assert len(list(packing.pack_first_fit(ex, 9, max_segments=1))) == 4
+
+
+def test_concat_then_split():
+  rows = list(packing.concat_then_split([np.arange(1, 8), np.arange(10, 18)], 5))
+  assert [r["tokens"].tolist() for r in rows] == [[1, 2, 3, 4, 5], [6, 7, 10, 11, 12], [13, 14, 15, 16, 17]]
+  assert rows[1]["segmentation"].tolist() == [1, 1, 2, 2, 2] and rows[1]["position"].tolist() == [5, 6, 0, 1, 2]
+
+
+def test_file_pipeline_shards_and_resumes(tmp_path):
+  f = tmp_path / "d.jsonl"
+  with open(f, "w") as fh:
+    for i in range(40):
+      fh.write(json.dumps({"text": f"doc {i} " + "x" * (5 + i % 7)}) + "\n")
+  args = ["dataset_type=hf", f"hf_train_files={f}", "per_device_batch_size=2", "max_target_length=16", "vocab_size=300", "packing=false",
+          "num_epoch=1"]
+  c = tiny_config("llama3-8b", args, num_devices=2)
+  a, b = FileDataIterator(c, 0, 2), FileDataIterator(c, 1, 2)
+  ba, bb = next(a), next(b)
+  assert ba["inputs"].shape == (2, 16) and not np.array_equal(ba["inputs"].numpy(), bb["inputs"].numpy())
+  tok = ByteTokenizer()
+  assert tok.decode(ba["inputs"][0].tolist()).startswith("doc 0") and tok.decode(bb["inputs"][0].tolist()).startswith("doc 1")
+  st = a.state()
+  nxt = next(a)
+  a2 = FileDataIterator(c, 0, 2)
+  a2.load_state(st)
+  assert np.array_equal(next(a2)["inputs"].numpy(), nxt["inputs"].numpy())
+  packed = FileDataIterator(tiny_config("llama3-8b", args[:5] + ["packing=true", "num_epoch=1"], num_devices=1))
+  row = next(packed)
+  assert int(row["inputs_segmentation"].max()) >= 1 and (row["inputs_position"][row["inputs_segmentation"] == 0] == 0).all()
