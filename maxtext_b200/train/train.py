@@ -53,9 +53,19 @@ def setup(config, device=None):
   return config, mesh, eng
 
 
-def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None):
+def _default_store():
+  import torch.distributed as dist
+  if dist.is_available() and dist.is_initialized():
+    try:
+      return dist.distributed_c10d._get_default_store()  # pylint: disable=protected-access
+    except Exception:  # pylint: disable=broad-except
+      return None
+  return None
+
+
+def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None, attempt: int = 0, preemption=None):
   from ..checkpoint import manager as ckpt_lib
-  from ..utils import profiler as prof_lib, goodput
+  from ..utils import profiler as prof_lib, goodput, elastic
   if engine is None:
     config, mesh, engine = setup(config)
   c = config
@@ -66,7 +76,16 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
   prof = prof_lib.Profiler(c, rank)
   ckpt = ckpt_lib.CheckpointManager(c, engine, mesh) if c.enable_checkpointing and c.checkpoint_dir else None
   start_step = 0
+  own_watcher = preemption is None
+  preemption = preemption or elastic.PreemptionWatcher(_default_store())
+  injector = elastic.FaultInjector(rank=rank)
+  heartbeat = None
+  if c.elastic_enabled and _default_store() is not None:
+    heartbeat = elastic.Heartbeat(_default_store(), rank, mesh.world if mesh is not None else 1,
+                                  c.heartbeat_reporting_interval_in_seconds).start()
   if ckpt is not None:
+    if attempt > 0:
+      ckpt.cleanup_incomplete()
     restored = ckpt.restore_if_possible(data_iterator)
     if restored is not None:
       start_step = restored
@@ -74,8 +93,12 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
     ckpt_lib.load_params_only(c.load_parameters_path, engine)
   engine.step_count = start_step
   is_cuda = engine.device.type == "cuda"
+  clean = False     # a failed attempt must not try a collective save on its way out
   try:
     for step in range(start_step, int(c.steps)):
+      injector.maybe_fire(step, attempt, heartbeat)
+      if heartbeat is not None:
+        heartbeat.raise_if_peer_dead(c.elastic_timeout_seconds)
       prof.maybe_start(step)
       t0 = time.perf_counter()
       with recorder.span("DATA_LOADING", step):
@@ -88,6 +111,10 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
       logger.record(step, metrics, dt)
       if ckpt is not None:
         ckpt.maybe_save(step, data_iterator)
+      if preemption.reached_preemption(step):
+        if ckpt is not None and ckpt.latest_step() != step:
+          ckpt.save(step, data_iterator, force=True)
+        raise StopTraining(f"preemption notice at step {step}")
       if c.eval_interval > 0 and step >= c.eval_start_step and (step + 1) % c.eval_interval == 0:
         ev = run_eval(c, engine, mesh)
         if rank == 0:
@@ -95,16 +122,22 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
         if c.target_eval_loss > 0 and ev <= c.target_eval_loss:
           raise StopTraining(f"target eval loss {c.target_eval_loss} reached")
       prof.maybe_stop(step)
+    clean = True
   except StopTraining as e:
+    clean = True
     max_logging.log(f"training stopped: {e}")
   finally:
     if ckpt is not None:
-      if c.save_checkpoint_on_completion:
+      if clean and c.save_checkpoint_on_completion:
         ckpt.save(engine.step_count - 1, data_iterator, force=True)
       ckpt.wait_until_finished()
     logger.close()
     prof.close()
     recorder.close()
+    if heartbeat is not None:
+      heartbeat.stop()
+    if own_watcher:
+      preemption.close()
   return engine, logger.history
 
 
@@ -122,7 +155,12 @@ def run_eval(config, engine, mesh) -> float:
 def main(argv=None):
   argv = list(sys.argv if argv is None else argv)
   config = pyconfig.initialize(argv)
-  return train_loop(config)
+  if not config.elastic_enabled:
+    return train_loop(config)
+  # the whole initialise + train function is what gets retried (src/maxtext/trainers/pre_train/train.py:1111-1140)
+  from ..utils import elastic
+  sup = elastic.ElasticSupervisor.from_config(config, cleanup=elastic.teardown_distributed)
+  return sup.run(lambda attempt, world: train_loop(config, attempt=attempt))
 
 
 if __name__ == "__main__":
