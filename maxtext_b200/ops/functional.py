@@ -551,10 +551,17 @@ def sum_of_squares(flat: torch.Tensor) -> torch.Tensor:
   return flat.float().pow(2).sum()
 
 
-def adamw_flat(master, grad, m, v, shadow, lr, b1, b2, eps, eps_root, wd, step, grad_scale: torch.Tensor):
+def adamw_flat(master, grad, m, v, shadow, lr, b1, b2, eps, eps_root, wd, step, grad_scale: torch.Tensor, pax: bool = False):
   """Single-launch AdamW over a flat shard. `grad_scale` is a 1-element device tensor (clip factor x
-  1/total_weights) so no host synchronisation is needed. `shadow` (compute dtype) may alias master."""
+  1/total_weights) so no host synchronisation is needed. `shadow` (compute dtype) may alias master.
+
+  `pax` selects the praxis form (src/maxtext/optimizers/optimizers.py:289-310): the bias correction is folded into
+  step-dependent decays, so the moments themselves are the corrected estimates and no division follows."""
   bc1, bc2 = 1.0 - b1 ** step, 1.0 - b2 ** step
+  if pax:
+    b1 = b1 * (1.0 - b1 ** (step - 1)) / bc1
+    b2 = b2 * (1.0 - b2 ** (step - 1)) / bc2
+    bc1 = bc2 = 1.0
   if backend.use_cuda_kernels(master) and master.dtype == torch.float32 and grad.dtype == torch.float32 \
       and v.dtype == torch.float32 and m.dtype in (torch.float32, torch.bfloat16) and master.numel() % 4 == 0 \
       and master.data_ptr() % 16 == 0:

@@ -35,7 +35,7 @@ class AdamW(_Base):
   def step(self, grad_scale, lr, step, **kw):
     c, s = self.c, self.store
     F.adamw_flat(s.master, s.grad_shard, s.exp_avg, s.exp_avg_sq, s.compute_shard, lr, c.adam_b1, c.adam_b2, c.adam_eps,
-                 c.adam_eps_root, c.adam_weight_decay, step, grad_scale)
+                 c.adam_eps_root, c.adam_weight_decay, step, grad_scale, pax=self.pax)
     return {}
 
   def state_arrays(self):

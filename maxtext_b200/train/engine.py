@@ -49,6 +49,10 @@ class TrainEngine:
     self.optimizer = opt_factory.make_optimizer(c, self.store, self.model)
     self.step_count = 0
     self.world = mesh.world if mesh is not None else 1
+    # DiLoCo: a replica (all axes but `diloco`) is a self-contained training job; losses, norms and gradients stay inside it
+    n_rep = mesh.axis_size("diloco") if mesh is not None else 1
+    self.inner_group = mesh.group(tuple(a for a in mesh.axis_names if a != "diloco")) if n_rep > 1 else None
+    self.inner_world = self.world // n_rep
     self._accum = None
     self._units = self._ordered_units()
     self.n_moe_layers = sum(1 for l in self.model.layers for b in l.plan.blocks if b.mlp in ("moe", "moe_shared"))
@@ -277,9 +281,9 @@ class TrainEngine:
     self._accum = None
     store.finish_resident_grads()
     stats = torch.stack([acc["loss_sum"], acc["z_sum"], acc["weights"], acc["aux"]])
-    if self.world > 1:
-      dist.all_reduce(stats)
-      stats[3] /= self.world
+    if self.inner_world > 1:
+      dist.all_reduce(stats, group=self.inner_group)
+      stats[3] /= self.inner_world
     loss_sum, z_sum, total_w, aux = stats[0], stats[1], stats[2], stats[3]
     aux = aux / max(1, acc["micro"]) / max(1, self.n_moe_layers)
     inv_w = 1.0 / (total_w + EPS)
@@ -309,7 +313,7 @@ class TrainEngine:
 
   def _reduce_replicas(self):
     store, mesh = self.store, self.mesh
-    if mesh is None or self.world == 1:
+    if mesh is None or self.inner_world == 1:
       return
     for u in store.units.values():
       axes = store.replica_axes(u)
@@ -321,7 +325,7 @@ class TrainEngine:
   def _grad_sumsq(self):
     """Sum of squares of the (un-normalised) global gradient: local shards, de-duplicated, all-reduced."""
     store = self.store
-    if self.world == 1:
+    if self.inner_world == 1:
       return F.sum_of_squares(store.grad_shard)
     total = torch.zeros((), dtype=torch.float32, device=self.device)
     fused_sq = getattr(store, "fused", False) and store.gradsq_valid
@@ -332,7 +336,7 @@ class TrainEngine:
         continue
       sq = F.sum_of_squares(store.shard_view(u, store.grad_shard))
       total = total + sq / self._replication(u)
-    dist.all_reduce(total)
+    dist.all_reduce(total, group=self.inner_group)
     return total
 
   def _replication(self, u) -> float:
@@ -345,7 +349,7 @@ class TrainEngine:
     ep = mesh.axis_size("expert")
     if ep > 1 and any(p.pdef.ep_dim is not None for p in u.params):
       distinct *= ep
-    return max(1.0, self.world / distinct)
+    return max(1.0, self.inner_world / distinct)
 
   def train_step(self, batch: dict) -> dict:
     """One optimizer step over `gradient_accumulation_steps` micro-batches split along the batch dim."""

@@ -20,7 +20,7 @@ from ..utils.metric_logger import MetricLogger
 from . import engine as engine_lib
 
 
-BATCH_AXES = ("data", "fsdp", "fsdp_transpose", "expert")
+BATCH_AXES = ("diloco", "data", "fsdp", "fsdp_transpose", "expert")
 
 
 def data_shard(mesh) -> tuple[int, int]:
@@ -93,6 +93,10 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
     ckpt_lib.load_params_only(c.load_parameters_path, engine)
   engine.step_count = start_step
   is_cuda = engine.device.type == "cuda"
+  stepper = engine
+  if c.enable_diloco:
+    from ..trainers.diloco import DiLoCoTrainer
+    stepper = DiLoCoTrainer(engine, c, mesh)
   clean = False     # a failed attempt must not try a collective save on its way out
   try:
     for step in range(start_step, int(c.steps)):
@@ -104,7 +108,7 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
       with recorder.span("DATA_LOADING", step):
         batch = next(data_iterator)
       with recorder.span("STEP", step):
-        metrics = engine.train_step(batch)
+        metrics = stepper.train_step(batch)
         if is_cuda and (c.profile_cleanly or True):
           torch.cuda.synchronize()
       dt = time.perf_counter() - t0

@@ -20,8 +20,12 @@ def main():
   eng = TrainEngine(cfg, mesh, torch.device("cpu"))
   it = T.create_data_iterator(cfg, mesh)
   losses, norms = [], []
+  stepper = eng
+  if cfg.enable_diloco:
+    from maxtext_b200.trainers.diloco import DiLoCoTrainer
+    stepper = DiLoCoTrainer(eng, cfg, mesh)
   for _ in range(int(cfg.steps)):
-    m = eng.train_step(next(it))
+    m = stepper.train_step(next(it))
     losses.append(float(m["learning/loss"]))
     norms.append(float(m["learning/raw_grad_norm"]))
   if rank == 0:

@@ -114,3 +114,23 @@ def test_adamw_matches_torch_optimizer():
     opt.step()
     ref.adamw_step(q, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.0, 0.1, step)
   assert torch.allclose(q, ref_p.detach(), atol=2e-5)
+
+
+def test_adam_pax_matches_praxis_formula():
+  """adam_pax: bias correction folded into the decays (reference optimizers.py:289-346)."""
+  import torch
+  from maxtext_b200.ops import functional as F
+  torch.manual_seed(0)
+  n, b1, b2, eps, epsr, wd, lr = 64, 0.9, 0.95, 1e-8, 1e-12, 0.1, 1e-2
+  p = torch.randn(n); m = torch.zeros(n); v = torch.zeros(n)
+  rp, rm, rv = p.clone(), m.clone(), v.clone()
+  for step in range(1, 5):
+    g = torch.randn(n)
+    F.adamw_flat(p, g.clone(), m, v, None, lr, b1, b2, eps, epsr, wd, step, torch.ones(1), pax=True)
+    t = float(step)
+    d1 = b1 * (1 - b1 ** (t - 1)) / (1 - b1 ** t)
+    d2 = b2 * (1 - b2 ** (t - 1)) / (1 - b2 ** t)
+    rm = (1 - d1) * g + d1 * rm
+    rv = (1 - d2) * g * g + d2 * rv
+    rp = rp - lr * (rm / (torch.sqrt(rv + epsr) + eps) + wd * rp)
+    assert torch.allclose(p, rp, atol=1e-6)

@@ -25,6 +25,14 @@ def _free_port():
   return p
 
 
+def _merge(*lists):
+  d = {}
+  for l in lists:
+    for e in l:
+      d[e.split("=")[0]] = e     # later entries win
+  return list(d.values())
+
+
 def run_ranks(world, overrides, tmp_path, tag):
   out = os.path.join(tmp_path, f"{tag}.json")
   port = _free_port()
@@ -32,7 +40,7 @@ def run_ranks(world, overrides, tmp_path, tag):
   for r in range(world):
     env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
                MAXTEXT_B200_QUIET="1", OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
-    procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multirank_worker.py"), out] + BASE + overrides,
+    procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multirank_worker.py"), out] + _merge(BASE, overrides),
                                   cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
   logs = []
   for p in procs:
@@ -79,3 +87,37 @@ def test_fsdp2_x_tp2_matches_single(single, tmp_path):
 def test_grad_accum_matches_single(single, tmp_path):
   got = run_ranks(1, ["per_device_batch_size=2", "gradient_accumulation_steps=2"], str(tmp_path), "ga2")
   _close(got["loss"], single["loss"], 2e-4)
+
+
+def _diloco_oracle(overrides, replicas, steps, period, lr, mu):
+  """Replica 0's loss curve from a hand-written simulation: independent engines, plain-tensor outer step."""
+  import torch
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.input_pipeline import interface
+  from maxtext_b200.train.engine import TrainEngine
+  cfg = pyconfig.initialize(["w", os.path.join(ROOT, "maxtext_b200/configs/base.yml")] + _merge(BASE, overrides, [f"ici_diloco_parallelism={replicas}"]),
+                            num_devices=replicas)     # same global batch as the multi-rank run; the engines below are single-rank
+  engs = [TrainEngine(cfg, None, torch.device("cpu")) for _ in range(replicas)]
+  its = [interface.create_data_iterator(cfg, r, replicas) for r in range(replicas)]
+  outer = engs[0].store.master.clone()
+  trace = torch.zeros_like(outer)
+  losses = []
+  for s in range(1, steps + 1):
+    ms = [e.train_step(next(it)) for e, it in zip(engs, its)]
+    losses.append(float(ms[0]["learning/loss"]))
+    if s % period == 0:
+      g = sum(outer - e.store.master for e in engs) / replicas
+      trace = g + mu * trace
+      outer = outer - lr * (g + mu * trace)
+      for e in engs:
+        e.store.master.copy_(outer)
+        e.store.sync_compute_from_master()
+  return losses
+
+
+def test_diloco2_matches_simulation(tmp_path):
+  over = ["enable_diloco=true", "diloco_sync_period=2", "diloco_outer_lr=0.7",
+          "diloco_outer_momentum=0.9", "steps=5", "per_device_batch_size=2"]
+  got = run_ranks(2, over + ["ici_diloco_parallelism=2"], str(tmp_path), "diloco2")
+  want = _diloco_oracle(over, 2, 5, 2, 0.7, 0.9)
+  assert got["loss"] == pytest.approx(want, rel=2e-5), (got["loss"], want)
