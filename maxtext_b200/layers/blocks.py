@@ -248,7 +248,7 @@ class Attention:
     B, S, _ = x.shape
     x = tp_enter(x, ctx)
     packed, sep = self._project(x, ctx)
-    plain = not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None
+    plain = not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
       # attention output kept by the remat policy: only the backward of the packed op is needed
@@ -271,6 +271,9 @@ class Attention:
         q = q * self.query_scalar
       if ctx.cache is not None:
         out = ctx.cache.attend(q, k, v, ctx, window=self.window, soft_cap=self.soft_cap, sinks=self.sinks)
+      elif ctx.cp_size > 1:
+        from ..parallel.context_parallel import context_attention
+        out = context_attention(q, k, v, ctx.positions, ctx.segment_ids, ctx, 1.0, self.soft_cap, self.window)
       elif self.sinks is not None:
         m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window)
         out = ref.attention(q, k, v, m, 1.0, self.soft_cap, sinks=self.sinks.leaf())

@@ -52,8 +52,9 @@ class LayerCtx:
   tp_size: int = 1
   ep_group: object = None
   ep_size: int = 1
-  cp_group: object = None
-  cp_size: int = 1
+  cp_group: object = None       # ranks along `context`
+  cp_size: int = 1              # total sequence split: context x context_usp_ulysses
+  usp_group: object = None      # ranks along `context_usp_ulysses`
   # remat: first forward stores named tensors, recompute forward consumes them
   save_names: tuple = ()
   offload_names: tuple = ()

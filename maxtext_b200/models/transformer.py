@@ -180,8 +180,9 @@ class Transformer:
       if self.config.num_experts > 1:
         ctx.ep_size = m.axis_size("expert")
         ctx.ep_group = m.group("expert") if ctx.ep_size > 1 else None
-      ctx.cp_size = m.axis_size("context")
-      ctx.cp_group = m.group("context") if ctx.cp_size > 1 else None
+      ctx.cp_size = m.axis_size(("context", "context_usp_ulysses"))
+      ctx.cp_group = m.group("context") if m.axis_size("context") > 1 else None
+      ctx.usp_group = m.group("context_usp_ulysses") if m.axis_size("context_usp_ulysses") > 1 else None
     return ctx
 
   # ------------------------------------------------------------------ pieces run by the engine

@@ -320,13 +320,19 @@ def _attention_chunked(q, k, v, mask_args, scale, soft_cap, chunk=1024):
   return torch.cat(outs, 1), torch.cat(lses, 2)
 
 
-def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal=True):
-  if backend.use_cuda_kernels(q):
+def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal=True,
+                  kv_positions=None, kv_segment_ids=None):
+  """Gradients of attention given the forward's `out` and `lse`. With kv_positions the keys are a block of a longer
+  (context-parallel) sequence: `out`/`lse` are then the merged global results and the returned dq/dk/dv are this
+  block's exact contributions."""
+  if backend.use_cuda_kernels(q) and kv_positions is None:
     E = backend.ext()
     if hasattr(E, "flash_bwd") and _flash_ok(q, k, v, soft_cap) and causal and E.flash_supported(q, k, v):
       seg = segment_ids.to(torch.int32).contiguous() if segment_ids is not None else None
       E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, float(scale), int(window))
       return
+  kpos = kv_positions if kv_positions is not None else positions
+  kseg = kv_segment_ids if kv_segment_ids is not None else segment_ids
   if lse is None:
     # comparison arm (library attention): differentiate the library call
     with torch.enable_grad():
@@ -349,8 +355,8 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
   for s in range(0, Sq, chunk):
     e = min(Sq, s + chunk)
     qf = q[:, s:e].float().reshape(B, e - s, Hkv, g, D)
-    mask = ref.attention_mask(positions[:, s:e], positions, segment_ids[:, s:e] if segment_ids is not None else None,
-                              segment_ids, causal, window)
+    mask = ref.attention_mask(positions[:, s:e], kpos, segment_ids[:, s:e] if segment_ids is not None else None,
+                              kseg, causal, window)
     raw = torch.einsum("bqhgd,bkhd->bhgqk", qf, kf) * scale
     if soft_cap and soft_cap > 0:
       t = torch.tanh(raw / soft_cap)
@@ -378,25 +384,26 @@ class _AttnFn(torch.autograd.Function):
   """Attention over separate q/k/v tensors (used when q/k need per-head norms or differ in width)."""
 
   @staticmethod
-  def forward(ctx, q, k, v, positions, segment_ids, scale, soft_cap, window, causal):
-    out, lse = attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal)
-    ctx.save_for_backward(q, k, v, out, lse, positions, segment_ids)
+  def forward(ctx, q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions=None, kv_segment_ids=None):
+    out, lse = attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)
+    ctx.save_for_backward(q, k, v, out, lse, positions, segment_ids, kv_positions, kv_segment_ids)
     ctx.cfg = (scale, soft_cap, window, causal)
     return out
 
   @staticmethod
   def backward(ctx, dout):
-    q, k, v, out, lse, positions, segment_ids = ctx.saved_tensors
+    q, k, v, out, lse, positions, segment_ids, kpos, kseg = ctx.saved_tensors
     scale, soft_cap, window, causal = ctx.cfg
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    attention_bwd(dout.contiguous(), q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal)
-    return dq, dk, dv, None, None, None, None, None, None
+    attention_bwd(dout.contiguous(), q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal, kpos, kseg)
+    return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
-def attention(q, k, v, positions, segment_ids, scale=1.0, soft_cap=0.0, window=0, causal=True):
+def attention(q, k, v, positions, segment_ids, scale=1.0, soft_cap=0.0, window=0, causal=True, kv_positions=None, kv_segment_ids=None):
+  """kv_positions / kv_segment_ids describe keys that are not the queries' own tokens (context parallelism)."""
   if not torch.is_grad_enabled():
-    return attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal)[0]
-  return _AttnFn.apply(q, k, v, positions, segment_ids, scale, soft_cap, window, causal)
+    return attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)[0]
+  return _AttnFn.apply(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)
 
 
 class _RopeFn(torch.autograd.Function):

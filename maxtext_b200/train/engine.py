@@ -83,6 +83,17 @@ class TrainEngine:
     for u in self._units[idx]:
       self.store.release_full(u)
 
+  def _shard_for_context(self, batch: dict) -> dict:
+    """Context parallelism: every rank of a context group reads the same rows and keeps its slice of the sequence."""
+    if self.mesh is None:
+      return batch
+    axes = ("context", "context_usp_ulysses")
+    cp = self.mesh.axis_size(axes)
+    if cp == 1:
+      return batch
+    from ..parallel.context_parallel import shard_batch
+    return shard_batch(batch, self.mesh.axis_index(axes), cp, bool(self.config.context_parallel_load_balance))
+
   # ------------------------------------------------------------------ forward + backward
   def fwd_bwd(self, batch: dict, compute_grads: bool = True) -> dict:
     """Accumulates gradients of sum_t w_t * loss_t (+ scaled aux losses) into the gradient shards.
@@ -90,6 +101,7 @@ class TrainEngine:
     batch: inputs, targets [B,S] int; inputs_position, inputs_segmentation, targets_segmentation optional.
     """
     c, model, store = self.config, self.model, self.store
+    batch = self._shard_for_context(batch)
     tokens = batch["inputs"].to(self.device, non_blocking=True)
     targets = batch["targets"].to(self.device, non_blocking=True)
     B, S = tokens.shape
@@ -368,6 +380,7 @@ class TrainEngine:
   def token_losses(self, batch: dict) -> torch.Tensor:
     """Per-token cross entropy [B, S] (no gradients): the building block of sequence log-probabilities."""
     model = self.model
+    batch = self._shard_for_context(batch)
     tokens = batch["inputs"].to(self.device)
     targets = batch["targets"].to(self.device)
     B, S = tokens.shape

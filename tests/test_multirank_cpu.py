@@ -121,3 +121,24 @@ def test_diloco2_matches_simulation(tmp_path):
   got = run_ranks(2, over + ["ici_diloco_parallelism=2"], str(tmp_path), "diloco2")
   want = _diloco_oracle(over, 2, 5, 2, 0.7, 0.9)
   assert got["loss"] == pytest.approx(want, rel=2e-5), (got["loss"], want)
+
+
+@pytest.mark.parametrize("strategy", ["all_gather", "ulysses", "ring"])
+def test_context_parallel2_matches_single(single, tmp_path, strategy):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_context_parallelism=2",
+                      f"context_parallel_strategy={strategy}"], str(tmp_path), f"cp2{strategy}")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_context_parallel_without_load_balance(single, tmp_path):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_context_parallelism=2", "context_parallel_strategy=ulysses",
+                      "context_parallel_load_balance=false"], str(tmp_path), "cp2nolb")
+  _close(got["loss"], single["loss"], 2e-4)
+
+
+def test_usp_ring2_x_ulysses2_matches_single(single, tmp_path):
+  got = run_ranks(4, ["per_device_batch_size=1", "ici_fsdp_parallelism=1", "ici_context_parallelism=2", "ici_context_usp_ulysses_parallelism=2",
+                      "context_parallel_strategy=usp"], str(tmp_path), "usp4")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
