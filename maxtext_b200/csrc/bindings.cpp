@@ -187,6 +187,7 @@ void sumsq(const torch::Tensor& x, torch::Tensor& out) {
 
 int* mt_status_ptr() { return status_tensor().data_ptr<int>(); }
 void mt_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int mt_num_sms() { return num_sms(); }
 
 void register_attention(pybind11::module_& m);
 void register_moe(pybind11::module_& m);

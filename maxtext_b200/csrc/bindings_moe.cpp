@@ -1,4 +1,120 @@
-// Bindings for the mixture-of-experts kernels (router top-k, permutation, grouped GEMM).
+// Bindings for the mixture-of-experts kernels (stable padded sort, row gather / combine, grouped GEMM).
 #include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
 
-void register_moe(pybind11::module_& m) { (void)m; }
+extern "C" {
+int mt_moe_sort(const int* idx, int n, int E, int rows_max, int* sizes, int* offs, int* blk_expert, int* dest, int* row_pair, cudaStream_t st);
+int mt_moe_gather(const void* x, const int* row_pair, const int* offs, int E, int k, int D, int rows_max, void* rows, int sms, cudaStream_t st);
+int mt_moe_combine(const void* y, const int* dest, const float* w, int T, int k, int D, void* out, int sms, cudaStream_t st);
+int mt_moe_combine_bwd(const void* dout, const void* y, const int* row_pair, const int* offs, int E, const float* w, int k, int D,
+                       int rows_max, void* dy, float* dw, int sms, cudaStream_t st);
+int mt_gemm_bf16_grouped(int mode, const void* a, const void* b, void* c, int rows_max, int n_out, int k_in, int experts, const int* offs,
+                         const int* blk_expert, int accumulate, long lda, long ldb, long ldc, int* status, int num_sms, cudaStream_t stream);
+}
+
+int* mt_status_ptr();          // defined in bindings.cpp
+void mt_count_launches(int n); // defined in bindings.cpp
+int mt_num_sms();              // defined in bindings.cpp
+
+namespace {
+
+cudaStream_t cur() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+bool i32(const torch::Tensor& t) { return t.is_cuda() && t.is_contiguous() && t.scalar_type() == torch::kInt32; }
+bool bf16_rows(const torch::Tensor& t) {
+  return t.is_cuda() && t.dim() == 2 && t.scalar_type() == torch::kBFloat16 && t.stride(1) == 1 && t.stride(0) % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0;
+}
+
+// idx [n] int32 -> fills sizes [E], offs [E+1], blk_expert [rows_max/128], dest [n], row_pair [rows_max]
+void moe_sort(const torch::Tensor& idx, int64_t E, torch::Tensor& sizes, torch::Tensor& offs, torch::Tensor& blk_expert, torch::Tensor& dest,
+              torch::Tensor& row_pair) {
+  TORCH_CHECK(i32(idx) && i32(sizes) && i32(offs) && i32(blk_expert) && i32(dest) && i32(row_pair));
+  const int64_t n = idx.numel(), rows_max = row_pair.numel();
+  TORCH_CHECK(sizes.numel() == E && offs.numel() == E + 1 && dest.numel() == n && blk_expert.numel() * 128 == rows_max);
+  TORCH_CHECK(rows_max >= n + E * 127 || rows_max >= (n + 127) / 128 * 128 + E * 128 - 128, "rows_max too small for the padded layout");
+  c10::cuda::CUDAGuard guard(idx.device());
+  int rc = mt_moe_sort(idx.data_ptr<int>(), (int)n, (int)E, (int)rows_max, sizes.data_ptr<int>(), offs.data_ptr<int>(),
+                       blk_expert.data_ptr<int>(), dest.data_ptr<int>(), row_pair.data_ptr<int>(), cur());
+  TORCH_CHECK(rc == 0, "mt_moe_sort failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void moe_gather(const torch::Tensor& x, const torch::Tensor& row_pair, const torch::Tensor& offs, int64_t k, torch::Tensor& rows) {
+  TORCH_CHECK(x.is_contiguous() && rows.is_contiguous() && bf16_rows(x) && bf16_rows(rows) && x.size(1) == rows.size(1));
+  TORCH_CHECK(i32(row_pair) && i32(offs) && row_pair.numel() == rows.size(0));
+  c10::cuda::CUDAGuard guard(x.device());
+  int rc = mt_moe_gather(x.data_ptr(), row_pair.data_ptr<int>(), offs.data_ptr<int>(), (int)offs.numel() - 1, (int)k, (int)x.size(1),
+                         (int)rows.size(0), rows.data_ptr(), mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_moe_gather failed with code ", rc);
+  mt_count_launches(1);
+}
+
+// out[t] = sum_c w[t,c] * y[dest[t*k+c]]; w undefined -> plain sum
+void moe_combine(const torch::Tensor& y, const torch::Tensor& dest, const c10::optional<torch::Tensor>& w, int64_t k, torch::Tensor& out) {
+  TORCH_CHECK(y.is_contiguous() && out.is_contiguous() && bf16_rows(y) && bf16_rows(out) && y.size(1) == out.size(1) && i32(dest));
+  TORCH_CHECK(dest.numel() == out.size(0) * k);
+  if (w) TORCH_CHECK(w->is_contiguous() && w->scalar_type() == torch::kFloat32 && w->numel() == dest.numel());
+  c10::cuda::CUDAGuard guard(y.device());
+  int rc = mt_moe_combine(y.data_ptr(), dest.data_ptr<int>(), w ? w->data_ptr<float>() : nullptr, (int)out.size(0), (int)k, (int)y.size(1),
+                          out.data_ptr(), mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_moe_combine failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void moe_combine_bwd(const torch::Tensor& dout, const torch::Tensor& y, const torch::Tensor& row_pair, const torch::Tensor& offs,
+                     const torch::Tensor& w, int64_t k, torch::Tensor& dy, torch::Tensor& dw) {
+  TORCH_CHECK(dout.is_contiguous() && y.is_contiguous() && dy.is_contiguous() && bf16_rows(dout) && bf16_rows(y) && bf16_rows(dy));
+  TORCH_CHECK(i32(row_pair) && i32(offs) && w.scalar_type() == torch::kFloat32 && dw.scalar_type() == torch::kFloat32 && w.is_contiguous() &&
+              dw.is_contiguous() && dw.numel() == w.numel() && row_pair.numel() == y.size(0) && dy.size(0) == y.size(0));
+  c10::cuda::CUDAGuard guard(y.device());
+  int rc = mt_moe_combine_bwd(dout.data_ptr(), y.data_ptr(), row_pair.data_ptr<int>(), offs.data_ptr<int>(), (int)offs.numel() - 1,
+                              w.data_ptr<float>(), (int)k, (int)y.size(1), (int)y.size(0), dy.data_ptr(), dw.data_ptr<float>(), mt_num_sms(),
+                              cur());
+  TORCH_CHECK(rc == 0, "mt_moe_combine_bwd failed with code ", rc);
+  mt_count_launches(1);
+}
+
+bool grouped_gemm_supported(int64_t rows_max, int64_t n_out, int64_t k_in) {
+  return rows_max % 128 == 0 && n_out % 128 == 0 && k_in % 128 == 0;
+}
+
+// mode 1: c = a W^T; mode 2: c = a W; mode 3: c (+)= a^T b per expert (see gemm_sm100.cu). w / c are [E, n_out, k_in] where a weight.
+void grouped_gemm(int64_t mode, const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& c, const torch::Tensor& offs,
+                  const torch::Tensor& blk_expert, bool accumulate) {
+  TORCH_CHECK(bf16_rows(a) && i32(offs) && i32(blk_expert));
+  const int64_t E = offs.numel() - 1, rows_max = a.size(0);
+  int64_t n_out, k_in;
+  long lda = a.stride(0), ldb = 0, ldc = 0;
+  if (mode == 1 || mode == 2) {
+    TORCH_CHECK(b.dim() == 3 && b.is_contiguous() && b.scalar_type() == torch::kBFloat16 && b.size(0) == E && bf16_rows(c));
+    n_out = b.size(1); k_in = b.size(2);
+    TORCH_CHECK(a.size(1) == (mode == 1 ? k_in : n_out) && c.size(0) == rows_max && c.size(1) == (mode == 1 ? n_out : k_in));
+    ldc = c.stride(0);
+  } else {
+    TORCH_CHECK(mode == 3 && bf16_rows(b) && b.size(0) == rows_max && c.dim() == 3 && c.is_contiguous() && c.scalar_type() == torch::kFloat32);
+    n_out = c.size(1); k_in = c.size(2);
+    TORCH_CHECK(c.size(0) == E && a.size(1) == n_out && b.size(1) == k_in);
+    ldb = b.stride(0);
+  }
+  TORCH_CHECK(grouped_gemm_supported(rows_max, n_out, k_in) && blk_expert.numel() * 128 == rows_max, "grouped_gemm: unsupported shape");
+  c10::cuda::CUDAGuard guard(a.device());
+  int rc = mt_gemm_bf16_grouped((int)mode, a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)rows_max, (int)n_out, (int)k_in, (int)E,
+                                offs.data_ptr<int>(), blk_expert.data_ptr<int>(), accumulate ? 1 : 0, lda, ldb, ldc, mt_status_ptr(),
+                                mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_gemm_bf16_grouped failed with code ", rc);
+  mt_count_launches(1);
+}
+
+}  // namespace
+
+void register_moe(pybind11::module_& m) {
+  m.def("moe_sort", &moe_sort);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd", &moe_combine_bwd);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("grouped_gemm_supported", &grouped_gemm_supported);
+}

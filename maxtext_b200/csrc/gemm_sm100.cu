@@ -62,7 +62,38 @@ struct GemmParams {
   const uint4* const* g_peer_shards;
   uint4* g_full;
   int* g_seg_flags;
+  // Grouped (mixture-of-experts) products. Rows are grouped by expert and every group is padded to a multiple of BM
+  // rows, so each 128-row block belongs to one expert: x_offs[e] is the first padded row of expert e (x_offs[E] = rows in
+  // use, read on the device, so no host synchronisation is needed), x_blk_expert[mb] the expert of row block mb.
+  //   1: y = x W_e^T      B = W [E*N, K] K-major, B tile rows start at e*N
+  //   2: dx = dy W_e      B = W [E*Kc, N] MN-major, contraction rows start at e*Kc (Kc = p.K)
+  //   3: dW_e = dy_e^T x_e  A = dy [R, x_nw] and B = x [R, N] MN-major, contraction over the rows of group e,
+  //                          C = [E*x_nw, N] fp32; an empty group writes zeros (or nothing when accumulating)
+  int x_mode;
+  int x_experts;
+  int x_nw;
+  const int* x_offs;
+  const int* x_blk_expert;
 };
+
+struct TileInfo {
+  int a_m0, b_n0, c_m0, k0a, k0b, num_kb;
+};
+
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int mb, int nb, int BN, int num_kb_full) {
+  TileInfo t{mb * BM, nb * BN, mb * BM, 0, 0, num_kb_full};
+  if (p.x_mode == 1) {
+    t.b_n0 += p.x_blk_expert[mb] * p.N;
+  } else if (p.x_mode == 2) {
+    t.k0b = p.x_blk_expert[mb] * p.K;
+  } else if (p.x_mode == 3) {
+    const int e = (mb * BM) / p.x_nw;
+    t.a_m0 = mb * BM - e * p.x_nw;
+    t.k0a = t.k0b = p.x_offs[e];
+    t.num_kb = (p.x_offs[e + 1] - p.x_offs[e]) / BK;
+  }
+  return t;
+}
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -135,7 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m_blocks = (p.M + BM - 1) / BM;
+  const int m_blocks = (p.x_mode == 1 || p.x_mode == 2) ? p.x_offs[p.x_experts] / BM : (p.M + BM - 1) / BM;
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -228,24 +259,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const long n1 = (long)(nb + 1) * BN < p.N ? (long)(nb + 1) * BN : p.N;
           if (!wait_segments(p, p.g_b_offset + (long)nb * BN * p.K, p.g_b_offset + n1 * p.K, abort_flag)) { ok = false; break; }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileInfo ti = tile_info(p, mb, nb, BN, num_kb);
+        for (int kb = 0; kb < ti.num_kb; ++kb) {
           if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
           const uint32_t sa = smem_a0 + s * Cfg::A_BYTES;
           const uint32_t sb = smem_b0 + s * Cfg::B_BYTES;
           if (!A_MN) {
-            tma_load_2d(sa, &map_a, full_bar(s), kb * BK, mb * BM);                       // box {64 k, 128 m}
+            tma_load_2d(sa, &map_a, full_bar(s), ti.k0a + kb * BK, ti.a_m0);              // box {64 k, 128 m}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)                                             // boxes {64 m, 64 k}
-              tma_load_2d(sa + j * 8192, &map_a, full_bar(s), mb * BM + j * 64, kb * BK);
+              tma_load_2d(sa + j * 8192, &map_a, full_bar(s), ti.a_m0 + j * 64, ti.k0a + kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &map_b, full_bar(s), kb * BK, nb * BN);                       // box {64 k, BN n}
+            tma_load_2d(sb, &map_b, full_bar(s), ti.k0b + kb * BK, ti.b_n0);              // box {64 k, BN n}
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)                                             // boxes {64 n, 64 k}
-              tma_load_2d(sb + j * 8192, &map_b, full_bar(s), nb * BN + j * 64, kb * BK);
+              tma_load_2d(sb + j * 8192, &map_b, full_bar(s), ti.b_n0 + j * 64, ti.k0b + kb * BK);
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -266,7 +298,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int tile_kb = num_kb;
+        if (p.x_mode == 3) {
+          int mb, nb;
+          tile_coords(t, m_blocks, n_blocks, mb, nb);
+          tile_kb = tile_info(p, mb, nb, BN, num_kb).num_kb;
+        }
+        for (int kb = 0; kb < tile_kb; ++kb) {
           if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_a0 + s * Cfg::A_BYTES, A_LBO, 1024);
@@ -297,6 +335,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
       int mb, nb;
       tile_coords(t, m_blocks, n_blocks, mb, nb);
+      const bool empty_tile = p.x_mode == 3 && tile_info(p, mb, nb, BN, num_kb).num_kb == 0;   // nothing was accumulated
       // one thread waits, the verdict is shared so that all 128 threads leave the loop together
       if (et == 0) *epi_ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE) ? 1 : 0;
       named_bar_sync(3, EPI_THREADS);
@@ -308,6 +347,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
+        if (empty_tile) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         if (c == BN / 32 - 1) {
           // whole accumulator is in registers: hand the TMEM buffer back to the MMA warp
           tc_fence_before();
@@ -350,7 +393,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           named_bar_sync(2, EPI_THREADS);
           if (et == 0) {
             const int col0 = nb * BN + (OUT_F32 ? c * 32 : (c >> 1) * 64);
-            if (col0 < p.N) {
+            if (col0 < p.N && !(empty_tile && p.accumulate)) {
               if (OUT_F32 && p.accumulate) tma_reduce_add_2d(&map_c, sbuf, col0, mb * BM);
               else tma_store_2d(&map_c, sbuf, col0, mb * BM);
             }
@@ -505,4 +548,54 @@ extern "C" int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int6
   const int compute = tiles < num_sms - comm_ctas ? tiles : num_sms - comm_ctas;
   kern<<<compute + comm_ctas, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Grouped (mixture-of-experts) products over rows grouped by expert, every group padded to a multiple of 128 rows.
+//   offs: E + 1 device ints, first padded row of each expert, offs[E] = rows in use (<= rows_max)
+//   blk_expert: device ints, expert of each 128-row block (rows_max / 128 entries)
+//   mode 1  y[r, :]  = x[r, :] . W[e(r)]^T     a = x [rows_max, k_in], b = W [E, n_out, k_in],  c = y  [rows_max, n_out] bf16
+//   mode 2  dx[r, :] = dy[r, :] . W[e(r)]      a = dy [rows_max, n_out], b = W [E, n_out, k_in], c = dx [rows_max, k_in] bf16
+//   mode 3  dW[e] (+)= dy_e^T . x_e            a = dy [rows_max, n_out], b = x [rows_max, k_in], c = dW [E, n_out, k_in] fp32
+// The tile count depends on offs[E], which stays on the device: the grid is sized for rows_max and surplus CTAs exit.
+// lda / ldb / ldc: leading strides (elements) of the row-grouped operands a, b (mode 3 only) and of c (modes 1, 2), so that
+// column slices of wider buffers (gate | up halves) can be used in place; 0 = dense.
+extern "C" int mt_gemm_bf16_grouped(int mode, const void* a, const void* b, void* c, int rows_max, int n_out, int k_in, int experts,
+                                    const int* offs, const int* blk_expert, int accumulate, long lda, long ldb, long ldc, int* status,
+                                    int num_sms, cudaStream_t stream) {
+  using namespace mt;
+  if (rows_max % BM || n_out % 128 || k_in % 128 || experts < 1 || lda % 8 || ldb % 8 || ldc % 8) return -10;
+  if (accumulate && mode != 3) return -11;
+  CUtensorMap ma, mb, mc;
+  GemmParams p{};
+  p.accumulate = accumulate; p.status = status;
+  p.x_mode = mode; p.x_experts = experts; p.x_offs = offs; p.x_blk_expert = blk_expert; p.x_nw = n_out;
+  int e = 0;
+  if (mode == 1) {
+    p.M = rows_max; p.N = n_out; p.K = k_in;
+    const int BN = (n_out % 256 == 0) ? 256 : 128;
+    if ((e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, k_in, lda ? lda : k_in, BK, BM))) return 100 + e;
+    if ((e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)experts * n_out, k_in, k_in, BK, BN))) return 200 + e;
+    if ((e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, n_out, ldc ? ldc : n_out, 64, BM))) return 300 + e;
+    return BN == 256 ? launch<256, false, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream)
+                     : launch<128, false, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+  }
+  if (mode == 2) {
+    p.M = rows_max; p.N = k_in; p.K = n_out;
+    const int BN = (k_in % 256 == 0) ? 256 : 128;
+    if ((e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, n_out, lda ? lda : n_out, BK, BM))) return 100 + e;
+    if ((e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)experts * n_out, k_in, k_in, 64, BK))) return 200 + e;
+    if ((e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, k_in, ldc ? ldc : k_in, 64, BM))) return 300 + e;
+    return BN == 256 ? launch<256, false, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream)
+                     : launch<128, false, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+  }
+  if (mode == 3) {
+    p.M = experts * n_out; p.N = k_in; p.K = rows_max;
+    const int BN = (k_in % 256 == 0) ? 256 : 128;
+    if ((e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, n_out, lda ? lda : n_out, 64, BK))) return 100 + e;
+    if ((e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_max, k_in, ldb ? ldb : k_in, 64, BK))) return 200 + e;
+    if ((e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)experts * n_out, k_in, k_in, 32, BM))) return 300 + e;
+    return BN == 256 ? launch<256, true, true, float>(ma, mb, mc, p, num_sms, stream)
+                     : launch<128, true, true, float>(ma, mb, mc, p, num_sms, stream);
+  }
+  return -12;
 }

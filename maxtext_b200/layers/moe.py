@@ -100,6 +100,12 @@ class RoutedMoE:
     wts, idx, aux = self.route(x2, B, S)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))
+    if ctx.ep_size == 1 and self.act in F._ACT_CODE and moe_ops.padded_path_supported(x2, D, self.wi_0.data.shape[1], self.E):
+      # GPU path: device-side stable sort into 128-row-padded expert groups, grouped tcgen05 GEMMs, no host synchronisation
+      out = moe_ops.moe_ffn_padded(x2, wts, idx, self.wi_0, self.wi_1, self.wo, self.E, self.act)
+      if ctx.tp_size > 1:
+        out = tp_exit(out, ctx)
+      return out.view(B, S, D)
     rows, order, sizes = moe_ops.permute(x2, idx, self.E)          # rows sorted by global expert id
     if ctx.ep_size > 1:
       y = self._expert_parallel(rows, sizes, ctx)

@@ -109,3 +109,140 @@ def grouped_linear(x: torch.Tensor, p, sizes: torch.Tensor) -> torch.Tensor:
   if not torch.is_grad_enabled():
     return grouped_mm_fwd(x, p.data, sizes)
   return _GroupedLinearFn.apply(x, p.data, p, sizes)
+
+
+# ======================================================================================== padded-group GPU path
+class GroupPlan:
+  """Device-side description of one token->expert assignment in the padded row layout (no host synchronisation).
+
+  Every expert's rows are padded to a multiple of 128 so that each GEMM tile belongs to one expert; `rows_max` is the
+  static upper bound n + E * 127 rounded to 128 that sizes every buffer."""
+
+  def __init__(self, expert_idx: torch.Tensor, num_experts: int):
+    E_ = backend.ext()
+    T, k = expert_idx.shape
+    n = T * k
+    self.T, self.k, self.E, self.n = T, k, num_experts, n
+    self.rows_max = -(-(n + num_experts * 127) // 128) * 128
+    dev = expert_idx.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    self.sizes = torch.empty(num_experts, **i32)
+    self.offs = torch.empty(num_experts + 1, **i32)
+    self.blk_expert = torch.empty(self.rows_max // 128, **i32)
+    self.dest = torch.empty(n, **i32)
+    self.row_pair = torch.empty(self.rows_max, **i32)
+    E_.moe_sort(expert_idx.reshape(-1).to(torch.int32).contiguous(), num_experts, self.sizes, self.offs, self.blk_expert, self.dest,
+                self.row_pair)
+
+
+def padded_path_supported(x2: torch.Tensor, d_model: int, d_ff: int, num_experts: int) -> bool:
+  if not backend.use_cuda_kernels(x2) or x2.dtype != torch.bfloat16:
+    return False
+  E_ = backend.ext()
+  return hasattr(E_, "grouped_gemm") and d_model % 128 == 0 and d_ff % 128 == 0 and num_experts <= 512
+
+
+class _GatherRowsFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, x2, plan):
+    ctx.plan = plan
+    rows = torch.empty(plan.rows_max, x2.shape[1], dtype=x2.dtype, device=x2.device)
+    backend.ext().moe_gather(x2.contiguous(), plan.row_pair, plan.offs, plan.k, rows)
+    return rows
+
+  @staticmethod
+  def backward(ctx, drows):
+    plan = ctx.plan
+    dx = torch.empty(plan.T, drows.shape[1], dtype=drows.dtype, device=drows.device)
+    backend.ext().moe_combine(drows.contiguous(), plan.dest, None, plan.k, dx)      # each token sums its k rows, fixed order
+    return dx, None
+
+
+class _CombineFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, y, weights, plan):
+    ctx.plan = plan
+    w = weights.float().contiguous()
+    ctx.save_for_backward(y, w)
+    ctx.w_dtype = weights.dtype
+    out = torch.empty(plan.T, y.shape[1], dtype=y.dtype, device=y.device)
+    backend.ext().moe_combine(y, plan.dest, w.reshape(-1), plan.k, out)
+    return out
+
+  @staticmethod
+  def backward(ctx, dout):
+    y, w = ctx.saved_tensors
+    plan = ctx.plan
+    dy = torch.empty_like(y)
+    dw = torch.empty_like(w)
+    backend.ext().moe_combine_bwd(dout.contiguous(), y, plan.row_pair, plan.offs, w.reshape(-1), plan.k, dy, dw.view(-1))
+    return dy, dw.to(ctx.w_dtype), None
+
+
+def _dw_into(pv, dy, x, plan, shape):
+  """dW[e] = dy_e^T x_e straight into the fp32 gradient store of parameter `pv` (accumulating if it already holds a gradient)."""
+  E_ = backend.ext()
+  if pv is not None and pv.main_grad is not None:
+    E_.grouped_gemm(3, dy, x, pv.main_grad.view(shape), plan.offs, plan.blk_expert, bool(pv.grad_written))
+    pv.grad_written = True
+    return None
+  g = torch.empty(shape, dtype=torch.float32, device=dy.device)
+  E_.grouped_gemm(3, dy, x, g, plan.offs, plan.blk_expert, False)
+  return g
+
+
+class _ExpertsFFNFn(torch.autograd.Function):
+  """h = act(rows W0_e^T) * (rows W1_e^T); y = h Wo_e^T over padded expert groups; every product is one grouped tcgen05 GEMM."""
+
+  @staticmethod
+  def forward(ctx, rows, w0, w1, wo, p0, p1, po, plan, act):
+    E_ = backend.ext()
+    Fdim = w0.shape[1]
+    gu = torch.empty(plan.rows_max, 2 * Fdim, dtype=rows.dtype, device=rows.device)
+    E_.grouped_gemm(1, rows, w0, gu[:, :Fdim], plan.offs, plan.blk_expert, False)
+    E_.grouped_gemm(1, rows, w1, gu[:, Fdim:], plan.offs, plan.blk_expert, False)
+    h = torch.empty(plan.rows_max, Fdim, dtype=rows.dtype, device=rows.device)
+    E_.gated_act_fwd(gu, h, F._ACT_CODE[act])
+    y = torch.empty(plan.rows_max, wo.shape[1], dtype=rows.dtype, device=rows.device)
+    E_.grouped_gemm(1, h, wo, y, plan.offs, plan.blk_expert, False)
+    ctx.save_for_backward(rows, gu, w0, w1, wo)
+    ctx.misc = (p0, p1, po, plan, act)
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    E_ = backend.ext()
+    rows, gu, w0, w1, wo = ctx.saved_tensors
+    p0, p1, po, plan, act = ctx.misc
+    Fdim = w0.shape[1]
+    dy = dy.contiguous()
+    h = torch.empty(plan.rows_max, Fdim, dtype=rows.dtype, device=rows.device)
+    E_.gated_act_fwd(gu, h, F._ACT_CODE[act])                     # recomputed: cheaper than keeping it
+    g_o = _dw_into(po, dy, h, plan, wo.shape)
+    dh = h                                                          # reuse the buffer
+    E_.grouped_gemm(2, dy, wo, dh, plan.offs, plan.blk_expert, False)
+    dgu = torch.empty_like(gu)
+    E_.gated_act_bwd(dh, gu, dgu, F._ACT_CODE[act])
+    d0, d1 = dgu[:, :Fdim], dgu[:, Fdim:]
+    g_0 = _dw_into(p0, d0, rows, plan, w0.shape)
+    g_1 = _dw_into(p1, d1, rows, plan, w1.shape)
+    drows = torch.empty_like(rows)
+    E_.grouped_gemm(2, d0, w0, drows, plan.offs, plan.blk_expert, False)
+    tmp = torch.empty_like(rows)
+    E_.grouped_gemm(2, d1, w1, tmp, plan.offs, plan.blk_expert, False)
+    drows.add_(tmp)
+    return drows, g_0, g_1, g_o, None, None, None, None, None
+
+
+def moe_ffn_padded(x2, weights, expert_idx, p_wi0, p_wi1, p_wo, num_experts: int, act: str):
+  """Whole routed-expert computation for one rank's experts: sort -> gather -> grouped FFN -> weighted combine."""
+  plan = GroupPlan(expert_idx, num_experts)
+  grad = torch.is_grad_enabled()
+  w0, w1, wo = p_wi0.data, p_wi1.data, p_wo.data
+  if grad:
+    rows = _GatherRowsFn.apply(x2, plan)
+    y = _ExpertsFFNFn.apply(rows, w0, w1, wo, p_wi0, p_wi1, p_wo, plan, act)
+    return _CombineFn.apply(y, weights, plan)
+  rows = _GatherRowsFn.forward(F._Dummy(), x2, plan)
+  y = _ExpertsFFNFn.forward(F._Dummy(), rows, w0, w1, wo, None, None, None, plan, act)
+  return _CombineFn.forward(F._Dummy(), y, weights, plan)
