@@ -12,6 +12,13 @@ int mt_moe_combine_bwd(const void* dout, const void* y, const int* row_pair, con
                        int rows_max, void* dy, float* dw, int sms, cudaStream_t st);
 int mt_gemm_bf16_grouped(int mode, const void* a, const void* b, void* c, int rows_max, int n_out, int k_in, int experts, const int* offs,
                          const int* blk_expert, int accumulate, long lda, long ldb, long ldc, int* status, int num_sms, cudaStream_t stream);
+int mt_ep_put_counts(const int* sizes, int E, int my_rank, int ep, int* const* counts_peer, cudaStream_t st);
+int mt_ep_index(const int* counts, int ep, int E, int my_rank, int cap, int* offs, int* blk_expert, int* valid_rows, int* send_base,
+                int* status, cudaStream_t st);
+int mt_ep_push(const void* src, int src_div, const int* idx, const int* dest_local, const int* offs_local, const int* send_base, int n,
+               int el, int cap, int D, void* const* peer_buf, int* pair_owner, int* pair_row, int sms, cudaStream_t st);
+int mt_ep_pull(void* const* peer_buf, const int* pair_owner, const int* pair_row, int n, int cap, int D, void* out, int sms, cudaStream_t st);
+int mt_ep_zero_pads(void* buf, const int* offs, const int* valid_rows, int el, int D, cudaStream_t st);
 }
 
 int* mt_status_ptr();          // defined in bindings.cpp
@@ -108,9 +115,70 @@ void grouped_gemm(int64_t mode, const torch::Tensor& a, const torch::Tensor& b, 
   mt_count_launches(1);
 }
 
+// ---- expert-parallel dispatch over peer memory. `*_table` tensors are int64 device arrays of per-rank base addresses.
+void ep_put_counts(const torch::Tensor& sizes, int64_t my_rank, const torch::Tensor& counts_table) {
+  TORCH_CHECK(i32(sizes) && counts_table.is_cuda() && counts_table.scalar_type() == torch::kInt64);
+  c10::cuda::CUDAGuard guard(sizes.device());
+  int rc = mt_ep_put_counts(sizes.data_ptr<int>(), (int)sizes.numel(), (int)my_rank, (int)counts_table.numel(),
+                            reinterpret_cast<int* const*>(counts_table.data_ptr<int64_t>()), cur());
+  TORCH_CHECK(rc == 0, "mt_ep_put_counts failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void ep_index(const torch::Tensor& counts, int64_t ep, int64_t my_rank, torch::Tensor& offs, torch::Tensor& blk_expert,
+              torch::Tensor& valid_rows, torch::Tensor& send_base) {
+  TORCH_CHECK(i32(counts) && i32(offs) && i32(blk_expert) && i32(valid_rows) && i32(send_base));
+  const int64_t E = send_base.numel(), el = E / ep;
+  TORCH_CHECK(counts.numel() == ep * E && offs.numel() == el + 1 && valid_rows.numel() == el);
+  c10::cuda::CUDAGuard guard(counts.device());
+  int rc = mt_ep_index(counts.data_ptr<int>(), (int)ep, (int)E, (int)my_rank, (int)blk_expert.numel() * 128, offs.data_ptr<int>(),
+                       blk_expert.data_ptr<int>(), valid_rows.data_ptr<int>(), send_base.data_ptr<int>(), mt_status_ptr(), cur());
+  TORCH_CHECK(rc == 0, "mt_ep_index failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void ep_push(const torch::Tensor& src, int64_t src_div, const torch::Tensor& idx, const torch::Tensor& dest_local, const torch::Tensor& offs_local,
+             const torch::Tensor& send_base, int64_t el, int64_t cap, const torch::Tensor& buf_table, torch::Tensor& pair_owner,
+             torch::Tensor& pair_row) {
+  TORCH_CHECK(src.is_contiguous() && bf16_rows(src) && i32(idx) && i32(dest_local) && i32(offs_local) && i32(send_base) && i32(pair_owner) &&
+              i32(pair_row) && buf_table.scalar_type() == torch::kInt64);
+  const int64_t n = idx.numel();
+  TORCH_CHECK(pair_owner.numel() == n && pair_row.numel() == n && src.size(0) * src_div >= n);
+  c10::cuda::CUDAGuard guard(src.device());
+  int rc = mt_ep_push(src.data_ptr(), (int)src_div, idx.data_ptr<int>(), dest_local.data_ptr<int>(), offs_local.data_ptr<int>(),
+                      send_base.data_ptr<int>(), (int)n, (int)el, (int)cap, (int)src.size(1),
+                      reinterpret_cast<void* const*>(buf_table.data_ptr<int64_t>()), pair_owner.data_ptr<int>(), pair_row.data_ptr<int>(),
+                      mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_ep_push failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void ep_pull(const torch::Tensor& buf_table, const torch::Tensor& pair_owner, const torch::Tensor& pair_row, int64_t cap, torch::Tensor& out) {
+  TORCH_CHECK(out.is_contiguous() && bf16_rows(out) && i32(pair_owner) && i32(pair_row) && buf_table.scalar_type() == torch::kInt64);
+  TORCH_CHECK(pair_owner.numel() == out.size(0) && pair_row.numel() == out.size(0));
+  c10::cuda::CUDAGuard guard(out.device());
+  int rc = mt_ep_pull(reinterpret_cast<void* const*>(buf_table.data_ptr<int64_t>()), pair_owner.data_ptr<int>(), pair_row.data_ptr<int>(),
+                      (int)out.size(0), (int)cap, (int)out.size(1), out.data_ptr(), mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_ep_pull failed with code ", rc);
+  mt_count_launches(1);
+}
+
+void ep_zero_pads(torch::Tensor& buf, const torch::Tensor& offs, const torch::Tensor& valid_rows) {
+  TORCH_CHECK(buf.is_contiguous() && bf16_rows(buf) && i32(offs) && i32(valid_rows) && offs.numel() == valid_rows.numel() + 1);
+  c10::cuda::CUDAGuard guard(buf.device());
+  int rc = mt_ep_zero_pads(buf.data_ptr(), offs.data_ptr<int>(), valid_rows.data_ptr<int>(), (int)valid_rows.numel(), (int)buf.size(1), cur());
+  TORCH_CHECK(rc == 0, "mt_ep_zero_pads failed with code ", rc);
+  mt_count_launches(1);
+}
+
 }  // namespace
 
 void register_moe(pybind11::module_& m) {
+  m.def("ep_put_counts", &ep_put_counts);
+  m.def("ep_index", &ep_index);
+  m.def("ep_push", &ep_push);
+  m.def("ep_pull", &ep_pull);
+  m.def("ep_zero_pads", &ep_zero_pads);
   m.def("moe_sort", &moe_sort);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);

@@ -106,6 +106,14 @@ class RoutedMoE:
       if ctx.tp_size > 1:
         out = tp_exit(out, ctx)
       return out.view(B, S, D)
+    if ctx.ep_size > 1 and x2.is_cuda:
+      from . import moe_ep
+      if moe_ep.supported(x2, self, ctx):
+        # dispatch / return through the peers' symmetric buffers (this repository's kernels); the NCCL path below is the fallback
+        out = moe_ep.expert_parallel_ffn(x2, wts, idx, self, ctx)
+        if ctx.tp_size > 1:
+          out = tp_exit(out, ctx)
+        return out.view(B, S, D)
     rows, order, sizes = moe_ops.permute(x2, idx, self.E)          # rows sorted by global expert id
     if ctx.ep_size > 1:
       y = self._expert_parallel(rows, sizes, ctx)

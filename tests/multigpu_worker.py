@@ -60,6 +60,29 @@ def kernels(rank, world, dev):
   sg.check()
 
 
+def train_moe_ep(rank, world, dev, fused):
+  """Mixtral-style model with its experts spread over the `expert` axis: peer-memory dispatch vs the NCCL all-to-all path."""
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as T
+  from maxtext_b200.train.engine import TrainEngine
+  cfg = pyconfig.initialize(
+      ["w", "maxtext_b200/configs/base.yml", "model_name=mixtral-8x7b", "override_model_config=true", "base_emb_dim=512",
+       "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128", "base_mlp_dim=1024", "base_moe_mlp_dim=1024", "num_experts=8",
+       "num_experts_per_tok=2", "base_num_decoder_layers=2", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
+       "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal", "log_config=false", "steps=3",
+       "learning_rate=1e-3", "warmup_steps_fraction=0.0", "ici_fsdp_parallelism=1", f"ici_expert_parallelism={world}",
+       f"use_fused_comm_kernels={'true' if fused else 'false'}"], num_devices=world)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world)
+  eng = TrainEngine(cfg, mesh, dev)
+  it = T.create_data_iterator(cfg, mesh)
+  out = []
+  for _ in range(3):
+    m = eng.train_step(next(it))
+    out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  return out
+
+
 def train(rank, world, dev, fused):
   from maxtext_b200.config import pyconfig
   from maxtext_b200.parallel import mesh as mesh_lib
@@ -91,8 +114,9 @@ def main():
       kernels(rank, world, dev)
       msg = "ok"
     else:
-      a = train(rank, world, dev, fused=False)
-      b = train(rank, world, dev, fused=True)
+      fn = train_moe_ep if mode == "moe_ep" else train
+      a = fn(rank, world, dev, fused=False)
+      b = fn(rank, world, dev, fused=True)
       for (la, na), (lb, nb) in zip(a, b):
         assert abs(la - lb) < 2e-2 and abs(na - nb) < 5e-2 * max(1.0, na), (a, b)
       from maxtext_b200.ops import backend

@@ -48,3 +48,7 @@ def test_peer_memory_kernels(tmp_path):
 
 def test_fused_comm_train_step_matches_nccl(tmp_path):
   _run("train", tmp_path)
+
+
+def test_expert_parallel_peer_dispatch_matches_nccl(tmp_path):
+  _run("moe_ep", tmp_path)
