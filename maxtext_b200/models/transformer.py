@@ -115,7 +115,10 @@ class DecoderLayer:
 
 
 class Transformer:
-  def __init__(self, config, mesh=None, device="cpu", build_store: bool = True):
+  def __init__(self, config, mesh=None, device="cpu", build_store: bool = True, stage: tuple | None = None):
+    """`stage` = (index, count) builds only what pipeline stage `index` owns: layer l belongs to stage
+    (l // num_layers_per_pipeline_stage) % count (circular repeats wrap around), the embedding to stage 0, the
+    final norm and output head to the last stage (src/maxtext/layers/pipeline.py)."""
     from . import families
     c = self.config = config
     self.mesh = mesh
@@ -128,6 +131,9 @@ class Transformer:
     self.par = dict(tp_size=tp_size, tp_rank=tp_rank, ep_size=ep_size, ep_rank=ep_rank)
     self.rope_tables = families.rope_tables(c, self.device)
     self.family = families.describe(c)
+    self.stage = stage
+    self.has_embed = stage is None or stage[0] == 0
+    self.has_head = stage is None or stage[0] == stage[1] - 1
     # ---- embedding unit
     eb = L.Builder(c, "embed", None, None, **self.par)
     self.embedding = eb.sub("token_embedder").table("embedding", (c.vocab_size, c.emb_dim), ("vocab", "embed_vocab"))
@@ -135,13 +141,15 @@ class Transformer:
     if c.trainable_position_size > 0:
       self.pos_embedding = eb.sub("decoder", "position_embedder").table(
           "embedding", (c.trainable_position_size, c.emb_dim), (None, "embed"))
-    self.embed_params = eb.params
+    self.embed_params = eb.params if self.has_embed else []
     # ---- layers
     self.layers: list[DecoderLayer] = []
     counters: dict[str, int] = {}
     for i, plan in enumerate(families.layer_plans(c)):
       si = counters.get(plan.stack, 0)
       counters[plan.stack] = si + 1
+      if stage is not None and (i // max(1, int(c.num_layers_per_pipeline_stage))) % stage[1] != stage[0]:
+        continue
       self.layers.append(DecoderLayer(c, i, si, plan, self.rope_tables, self.par))
     self.stack_sizes = counters
     # ---- head unit
@@ -152,7 +160,7 @@ class Transformer:
     if not c.logits_via_embedding:
       self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
                                                                    ("embed_vocab", "vocab"))
-    self.head_params = hb.params
+    self.head_params = hb.params if self.has_head else []
     self.store: ParamStore | None = None
     if build_store:
       self.store = ParamStore(self.all_params(), mesh or _SingleMesh(), c, self.device)
@@ -166,7 +174,7 @@ class Transformer:
     return out
 
   def units_in_order(self) -> list[str]:
-    return ["embed"] + [l.unit for l in self.layers] + ["head"]
+    return (["embed"] if self.has_embed else []) + [l.unit for l in self.layers] + (["head"] if self.has_head else [])
 
   # ------------------------------------------------------------------ contexts
   def make_ctx(self, positions, segment_ids, mode="train", tokens=None) -> LayerCtx:

@@ -49,7 +49,8 @@ def setup(config, device=None):
   if device is None:
     use_cuda = torch.cuda.is_available() and config.hardware != "cpu"
     device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
-  eng = engine_lib.TrainEngine(config, mesh, device)
+  from . import pipeline as pipeline_lib
+  eng = pipeline_lib.make_engine(config, mesh, device)
   return config, mesh, eng
 
 

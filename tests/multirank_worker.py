@@ -17,7 +17,8 @@ def main():
   rank, world, _ = mesh_lib.init_distributed(timeout_s=120)
   cfg = pyconfig.initialize(["w", "maxtext_b200/configs/base.yml"] + overrides, num_devices=world)
   mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world) if world > 1 else None
-  eng = TrainEngine(cfg, mesh, torch.device("cpu"))
+  from maxtext_b200.train.pipeline import make_engine
+  eng = make_engine(cfg, mesh, torch.device("cpu"))
   it = T.create_data_iterator(cfg, mesh)
   losses, norms = [], []
   stepper = eng

@@ -142,3 +142,24 @@ def test_usp_ring2_x_ulysses2_matches_single(single, tmp_path):
                       "context_parallel_strategy=usp"], str(tmp_path), "usp4")
   _close(got["loss"], single["loss"], 2e-4)
   _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_pipeline2_gpipe_matches_single(single, tmp_path):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2"], str(tmp_path), "pp2")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_pipeline2_circular_and_microbatches(tmp_path):
+  four = ["base_num_decoder_layers=4"]
+  ref = run_ranks(1, four + ["per_device_batch_size=4"], str(tmp_path), "single4")
+  got = run_ranks(2, four + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2", "num_layers_per_pipeline_stage=1",
+                             "num_pipeline_microbatches=4"], str(tmp_path), "pp2circ")
+  _close(got["loss"], ref["loss"], 2e-4)
+  _close(got["grad_norm"], ref["grad_norm"], 2e-3)
+
+
+def test_pipeline2_x_fsdp2_matches_single(single, tmp_path):
+  got = run_ranks(4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_pipeline_parallelism=2"], str(tmp_path), "pp2fsdp2")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
