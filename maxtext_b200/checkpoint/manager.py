@@ -246,7 +246,11 @@ class CheckpointManager:
       return True
     return False
 
-  def save(self, step: int, data_iterator=None, force: bool = False):
+  def save_params_only(self, step: int = 0):
+    """Parameters without optimizer state: what `load_parameters_path` consumers (decode, fine-tuning) need."""
+    self.save(step, None, force=True, params_only=True)
+
+  def save(self, step: int, data_iterator=None, force: bool = False, params_only: bool = False):
     if self._inflight is not None:
       self.wait_until_finished()
     if step in self.all_steps():
@@ -261,7 +265,7 @@ class CheckpointManager:
     futures = []
     store = self.engine.store
     self.io.write_tree(items, ("params", "params"), store.master, self.pool, futures)
-    opt = self.engine.optimizer.state_arrays()
+    opt = {} if params_only else self.engine.optimizer.state_arrays()
     for name, flat in opt.items():
       self.io.write_tree(items, ("opt_state", "0", name, "params"), flat, self.pool, futures)
     if self.rank == 0:

@@ -434,6 +434,7 @@ class ParamStore:
     u.grad_slot = b
     u.full_grad = self._gbufs[b].tensor[: u.numel]
     self._views_into(u, u.full_grad, "main_grad")
+    self._zero_gaps(u)
     for p in u.params:
       p.grad_written = False
 
@@ -477,8 +478,21 @@ class ParamStore:
       buf = torch.empty(self.max_unit_numel(), dtype=self.grad_dtype, device=self.device)
     u.full_grad = buf[: u.numel]
     self._views_into(u, u.full_grad, "main_grad")
+    self._zero_gaps(u)
     for p in u.params:
       p.grad_written = False
+
+  def _zero_gaps(self, u: Unit):
+    """Alignment padding between parameters is reduced and normed with everything else: it must hold zeros."""
+    gaps = getattr(u, "_gaps", None)
+    if gaps is None:
+      gaps, ends = [], [o + p.pdef.numel for o, p in zip(u.offsets, u.params)]
+      for end, nxt in zip(ends, list(u.offsets[1:]) + [u.numel]):
+        if nxt > end:
+          gaps.append((end, nxt))
+      u._gaps = gaps
+    for lo, hi in gaps:
+      u.full_grad[lo:hi].zero_()
 
   def reduce_scatter_unit(self, u: Unit, async_op: bool = True, accumulate: bool = False):
     """Sum the unit's full gradient over the shard group into this rank's gradient shard.

@@ -163,3 +163,17 @@ def test_pipeline2_x_fsdp2_matches_single(single, tmp_path):
   got = run_ranks(4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_pipeline_parallelism=2"], str(tmp_path), "pp2fsdp2")
   _close(got["loss"], single["loss"], 2e-4)
   _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_zero1_optimizer_sharded_over_data_matches_single(single, tmp_path):
+  got = run_ranks(2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_data_parallelism=2", "shard_optimizer_over_data=true"],
+                  str(tmp_path), "zero1")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
+
+
+def test_expert_parallel2_matches_single(tmp_path):
+  moe = ["model_name=mixtral-8x7b", "override_model_config=true", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=64"]
+  ref = run_ranks(1, moe + ["per_device_batch_size=4"], str(tmp_path), "moe1")
+  got = run_ranks(2, moe + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_expert_parallelism=2"], str(tmp_path), "ep2")
+  _close(got["loss"], ref["loss"], 5e-4)
