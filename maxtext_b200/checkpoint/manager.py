@@ -370,3 +370,56 @@ def load_params_only(path: str, engine, mesh=None):
   """`load_parameters_path`: restore weights, keep a fresh optimizer (checkpointing.py:704-768)."""
   items = os.path.join(path, "items") if os.path.isdir(os.path.join(path, "items")) else path
   _restore_tree(TreeIO(engine, mesh), items, engine, full_state=False)
+
+
+class MultiTierCheckpointManager:
+  """Two tiers: frequent saves to node-local storage, rarer saves to the persistent directory; restore takes the newest
+  committed step of either tier.
+
+  The role of emergency / multi-tier checkpointing (src/maxtext/common/emergency_checkpointing.py; train_utils.py:54-114:
+  `local_checkpoint_directory`, `local_checkpoint_period`, `enable_emergency_checkpoint`): after a restart on the same
+  hosts the local copy saves a trip to shared storage; after losing hosts the persistent tier still has a recent step.
+  Both tiers use the same on-disk tree, so either can feed `load_full_state_path`.
+  """
+
+  def __init__(self, config, engine, mesh=None):
+    self.c = config
+    self.persistent = CheckpointManager(config, engine, mesh)
+    local_cfg = config.replace(checkpoint_period=max(1, int(config.local_checkpoint_period)),
+                               max_num_checkpoints_to_keep=2 if config.max_num_checkpoints_to_keep is None else config.max_num_checkpoints_to_keep)
+    self.local = CheckpointManager(local_cfg, engine, mesh, directory=config.local_checkpoint_directory)
+    self.engine = engine
+
+  def maybe_save(self, step, data_iterator=None) -> bool:
+    a = self.persistent.maybe_save(step, data_iterator)
+    b = False if a else self.local.maybe_save(step, data_iterator)      # a persistent save makes the local one redundant
+    return a or b
+
+  def save(self, step, data_iterator=None, force=False):
+    self.persistent.save(step, data_iterator, force=force)
+
+  def latest_step(self):
+    steps = [s for s in (self.persistent.latest_step(), self.local.latest_step()) if s is not None]
+    return max(steps) if steps else None
+
+  def cleanup_incomplete(self):
+    self.persistent.cleanup_incomplete()
+    self.local.cleanup_incomplete()
+
+  def wait_until_finished(self):
+    self.persistent.wait_until_finished()
+    self.local.wait_until_finished()
+
+  def restore_if_possible(self, data_iterator=None):
+    p, l = self.persistent.latest_step(), self.local.latest_step()
+    if l is not None and (p is None or l > p):
+      self.local.restore(os.path.join(self.local.dir, str(l)), full_state=True, data_iterator=data_iterator)
+      max_logging.log(f"restored full state from local tier, step {l}")
+      return l + 1
+    return self.persistent.restore_if_possible(data_iterator)
+
+
+def create_checkpoint_manager(config, engine, mesh=None):
+  if config.enable_emergency_checkpoint and config.local_checkpoint_directory and int(config.local_checkpoint_period) > 0:
+    return MultiTierCheckpointManager(config, engine, mesh)
+  return CheckpointManager(config, engine, mesh)

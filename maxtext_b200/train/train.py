@@ -75,7 +75,7 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
   data_iterator = data_iterator or create_data_iterator(c, mesh)
   logger = MetricLogger(c, is_writer=(rank == 0))
   prof = prof_lib.Profiler(c, rank)
-  ckpt = ckpt_lib.CheckpointManager(c, engine, mesh) if c.enable_checkpointing and c.checkpoint_dir else None
+  ckpt = ckpt_lib.create_checkpoint_manager(c, engine, mesh) if c.enable_checkpointing and c.checkpoint_dir else None
   start_step = 0
   own_watcher = preemption is None
   preemption = preemption or elastic.PreemptionWatcher(_default_store())

@@ -113,3 +113,22 @@ def test_retention(tmp_path):
   for s in range(4):
     mgr.save(s, force=True)
   assert mgr.all_steps() == [2, 3]
+
+
+def test_local_tier_restores_newer_step_than_persistent(tmp_path):
+  """Persistent saves every 4 steps, local every step: after 'losing' the job at step 5 the restart resumes from the
+  local step 5 copy, and the curve continues exactly as an uninterrupted run."""
+  import os
+  from helpers import tiny_config
+  from maxtext_b200.train import train as train_lib
+  args = ["checkpoint_period=4", "enable_checkpointing=true", "async_checkpointing=false", f"base_output_directory={tmp_path}",
+          "enable_emergency_checkpoint=true", f"local_checkpoint_directory={tmp_path}/local", "local_checkpoint_period=1",
+          "save_checkpoint_on_completion=false", "learning_rate_schedule_steps=8"]
+  _, ref = train_lib.train_loop(tiny_config(extra=args + ["steps=8", "run_name=ref", f"local_checkpoint_directory={tmp_path}/local_ref"]))
+  train_lib.train_loop(tiny_config(extra=args + ["steps=6", "run_name=a"]))
+  persistent = sorted(int(n) for n in os.listdir(os.path.join(tmp_path, "a", "checkpoints")) if n.isdigit())
+  local = sorted(int(n) for n in os.listdir(os.path.join(tmp_path, "local")) if n.isdigit())
+  assert persistent == [0, 4] and local[-1] == 5 and len(local) <= 2
+  _, hist = train_lib.train_loop(tiny_config(extra=args + ["steps=8", "run_name=a"]))
+  assert [h["step"] for h in hist] == [6, 7]
+  assert abs(hist[-1]["learning/loss"] - ref[-1]["learning/loss"]) < 1e-5

@@ -50,3 +50,40 @@ def test_file_pipeline_shards_and_resumes(tmp_path):
   packed = FileDataIterator(tiny_config("llama3-8b", args[:5] + ["packing=true", "num_epoch=1"], num_devices=1))
   row = next(packed)
   assert int(row["inputs_segmentation"].max()) >= 1 and (row["inputs_position"][row["inputs_segmentation"] == 0] == 0).all()
+
+
+def test_rampup_batches_grow_without_skipping_samples():
+  import torch
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline.interface import RampupIterator
+  cfg = tiny_config(extra=["per_device_batch_size=8", "enable_rampup_batch_size=true", "per_device_batch_size_start=2",
+                           "per_device_batch_size_increment=3", "global_rampup_samples=20"])
+  assert cfg.rampup_end_step == 2
+
+  class Counter:
+    def __init__(self):
+      self.n = 0
+
+    def __next__(self):
+      b = {"inputs": torch.arange(self.n, self.n + 8)[:, None].repeat(1, 4)}
+      self.n += 8
+      return b
+
+  it = RampupIterator(cfg, Counter())
+  sizes, seen = [], []
+  for _ in range(12):
+    b = next(it)
+    sizes.append(b["inputs"].shape[0])
+    seen += b["inputs"][:, 0].tolist()
+  assert sizes[:5] == [2] * 5 and sizes[5:7] == [5, 5] and sizes[7:] == [8] * 5     # 10 samples per increment
+  assert seen == list(range(len(seen)))                                              # contiguous stream: nothing lost or repeated
+
+
+def test_rampup_trains_end_to_end():
+  from helpers import tiny_config
+  from maxtext_b200.train import train as train_lib
+  cfg = tiny_config(extra=["per_device_batch_size=4", "enable_rampup_batch_size=true", "per_device_batch_size_start=2",
+                           "per_device_batch_size_increment=2", "global_rampup_samples=4", "steps=4"])
+  _, hist = train_lib.train_loop(cfg)
+  toks = [int(h["learning/total_weights"]) for h in hist]
+  assert toks[0] == 2 * cfg.max_target_length and toks[-1] == 4 * cfg.max_target_length
