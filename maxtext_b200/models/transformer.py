@@ -114,6 +114,43 @@ class DecoderLayer:
     return x
 
 
+class MTPLayer:
+  """One multi-token-prediction module (src/maxtext/layers/multi_token_prediction.py:160-310): the previous hidden state and
+  the embedding of the token one step further ahead are normalised separately, concatenated [embedding | hidden], projected
+  back to the model width and passed through one decoder layer of the model's own kind."""
+
+  def __init__(self, b: L.Builder, config, k: int, plan: LayerPlan, rope_tables, norm_offset, norm_kind):
+    c = config
+    mb = b.sub("mtp_block", f"mtp_layer_{k}")
+    eps = c.normalization_layer_epsilon
+    self.k = k
+    self.embedding_norm = L.Norm(mb, f"mtp_{k}_embedding_norm", c.emb_dim, eps, norm_offset, kind=norm_kind)
+    self.hidden_state_norm = L.Norm(mb, f"mtp_{k}_hidden_state_norm", c.emb_dim, eps, norm_offset, kind=norm_kind)
+    self.projection = mb.sub(f"mtp_{k}_projection").linear("kernel", (2 * c.emb_dim,), (c.emb_dim,), ("concat_embed", "embed"))
+    tb = mb.sub(f"mtp_{k}_transformer_layer")
+    self.blocks = [DecoderBlock(tb, c, bp, rope_tables) for bp in plan.blocks]
+
+  def __call__(self, prev_hidden, target_embedding, ctx: LayerCtx):
+    feats = torch.cat([self.embedding_norm(target_embedding), self.hidden_state_norm(prev_hidden)], dim=-1)
+    x = F.linear(feats, self.projection)
+    for blk in self.blocks:
+      x = blk(x, ctx)
+    return x
+
+
+def roll_left(x: torch.Tensor, segment_ids: torch.Tensor | None = None) -> torch.Tensor:
+  """Shift one position to the left along the sequence; the last position, and positions whose right neighbour belongs to
+  another document, become zero (multi_token_prediction.py:91-158)."""
+  out = torch.zeros_like(x)
+  out[:, :-1] = x[:, 1:]
+  if segment_ids is not None:
+    nxt = torch.zeros_like(segment_ids)
+    nxt[:, :-1] = segment_ids[:, 1:]
+    keep = (nxt == segment_ids) & (segment_ids != 0)
+    out = out * keep.to(out.dtype) if out.dtype != torch.bool else out & keep
+  return out
+
+
 class Transformer:
   def __init__(self, config, mesh=None, device="cpu", build_store: bool = True, stage: tuple | None = None):
     """`stage` = (index, count) builds only what pipeline stage `index` owns: layer l belongs to stage
@@ -152,6 +189,15 @@ class Transformer:
         continue
       self.layers.append(DecoderLayer(c, i, si, plan, self.rope_tables, self.par))
     self.stack_sizes = counters
+    # ---- multi-token prediction unit (training only; the last stage owns it)
+    self.mtp_layers: list[MTPLayer] = []
+    self.mtp_params = []
+    if int(c.mtp_num_layers) > 0 and self.has_head:
+      mb = L.Builder(c, "mtp", None, None, **self.par)
+      last_plan = families.layer_plans(c)[-1]
+      self.mtp_layers = [MTPLayer(mb, c, k, last_plan, self.rope_tables, self.family.norm_offset, self.family.norm_kind)
+                         for k in range(1, int(c.mtp_num_layers) + 1)]
+      self.mtp_params = mb.params
     # ---- head unit
     hb = L.Builder(c, "head", None, None, **self.par)
     self.final_norm = L.Norm(hb.sub("decoder"), "decoder_norm", c.emb_dim, c.normalization_layer_epsilon,
@@ -170,11 +216,13 @@ class Transformer:
     out = list(self.embed_params)
     for l in self.layers:
       out.extend(l.params)
+    out.extend(self.mtp_params)
     out.extend(self.head_params)
     return out
 
   def units_in_order(self) -> list[str]:
-    return (["embed"] if self.has_embed else []) + [l.unit for l in self.layers] + (["head"] if self.has_head else [])
+    return (["embed"] if self.has_embed else []) + [l.unit for l in self.layers] + (["mtp"] if self.mtp_layers else []) + \
+        (["head"] if self.has_head else [])
 
   # ------------------------------------------------------------------ contexts
   def make_ctx(self, positions, segment_ids, mode="train", tokens=None) -> LayerCtx:

@@ -153,6 +153,7 @@ class TrainEngine:
         self._release(ui)
     # ---- head: loss and d(hidden) in one pass
     hi = n_units - 1
+    self._gather(hi)                 # a no-op when the prefetch above already covered it
     self._wait_gather(hi)
     if c.logits_via_embedding:
       self._gather(0, async_op=False)
@@ -167,6 +168,9 @@ class TrainEngine:
     acc["loss_sum"] += loss_sum
     acc["z_sum"] += z_sum
     acc["weights"] += total_w
+    mtp_embed_grads = []
+    if model.mtp_layers and compute_grads:
+      dx, mtp_embed_grads = self._run_mtp(x, dx, tokens, targets, weights, positions, seg, total_w, acc, ctx, accumulate_rs)
     if not compute_grads:
       for i in range(n_units):
         self._release(i)
@@ -209,10 +213,59 @@ class TrainEngine:
       for u in emb_units:
         store.acquire_full_grad(u)
     self._run_embed(tokens, positions, grad=True, dx=dx)
+    for r_tokens, r_pos, d_emb in mtp_embed_grads:          # embeddings of the tokens further ahead, used by the MTP modules
+      self._run_embed(r_tokens, r_pos, grad=True, dx=d_emb)
     self._finish_unit_grads(0, accumulate_rs)
     self._release(0)
     store.wait_reduce_scatters()
     return acc
+
+  def _run_mtp(self, x, dx_main, tokens, targets, weights, positions, seg, total_w, acc, ctx, accumulate_rs):
+    """Multi-token prediction (src/maxtext/layers/multi_token_prediction.py:334-531): module k predicts the token k + 1
+    steps ahead from the previous module's hidden state and the embedding of the token k steps ahead, through the shared
+    output head. loss = mtp_loss_scaling_factor * sum_k sum(xent_k * mask_k) / sum_k sum(mask_k), added to the main loss.
+    Returns d(final hidden) including the MTP paths, and the deferred embedding gradients."""
+    from ..models.transformer import roll_left
+    c, model, store = self.config, self.model, self.store
+    mi = len(self._units) - 2
+    self._gather(mi, async_op=False)
+    self._wait_gather(mi)
+    self._gather(0, async_op=False)          # the modules embed the tokens further ahead with the shared table
+    for u in self._units[mi]:
+      store.acquire_full_grad(u)
+    B, S = tokens.shape
+    r_tok, r_tgt, r_w, r_pos, r_seg = tokens, targets, weights, positions, seg
+    rolled = []
+    for _ in model.mtp_layers:
+      r_tok, r_tgt, r_w, r_pos = (roll_left(t, r_seg) for t in (r_tok, r_tgt, r_w, r_pos))
+      r_seg = roll_left(r_seg) if r_seg is not None else None
+      rolled.append((r_tok, r_tgt, r_w, r_pos))
+    mtp_w = sum(w.sum() for _, _, w, _ in rolled)
+    # token losses are summed un-normalised and divided by the main total weight in the optimizer; rescale so that the
+    # MTP term ends up divided by its own weight and multiplied by the scaling factor
+    factor = float(c.mtp_loss_scaling_factor) * self._global_weight(total_w) / (self._global_weight(mtp_w) + EPS)
+    x_in = x.detach().requires_grad_(True)
+    h, outs, grads, embs = x_in, [], [], []
+    ctx.saved, ctx.recompute, ctx.aux_losses = {}, False, []
+    mtp_loss = torch.zeros((), device=self.device)
+    with torch.enable_grad():
+      for layer, (tk, tg, w, ps) in zip(model.mtp_layers, rolled):
+        with torch.no_grad():
+          e = model.embed(tk, ps)
+        e = e.detach().requires_grad_(True)
+        embs.append((tk, ps, e))
+        h = layer(h, e, ctx)
+        loss_k, _, dh = self._run_head(h, tg.reshape(-1), (w * factor).reshape(-1), True)
+        mtp_loss = mtp_loss + loss_k
+        outs.append(h)
+        grads.append(dh)
+    torch.autograd.backward(outs, grads)
+    for p in model.mtp_params:
+      p.collect_leaf_grad()
+    self._finish_unit_grads(mi, accumulate_rs)
+    self._release(mi)
+    acc["mtp"] = acc.get("mtp", torch.zeros((), device=self.device)) + mtp_loss
+    return dx_main + x_in.grad, [(tk, ps, e.grad) for tk, ps, e in embs]
 
   def _global_weight(self, total_w):
     if self.world > 1:
@@ -292,11 +345,11 @@ class TrainEngine:
     assert acc is not None, "update() called before fwd_bwd()"
     self._accum = None
     store.finish_resident_grads()
-    stats = torch.stack([acc["loss_sum"], acc["z_sum"], acc["weights"], acc["aux"]])
+    stats = torch.stack([acc["loss_sum"], acc["z_sum"], acc["weights"], acc["aux"], acc.get("mtp", torch.zeros((), device=self.device))])
     if self.inner_world > 1:
       dist.all_reduce(stats, group=self.inner_group)
       stats[3] /= self.inner_world
-    loss_sum, z_sum, total_w, aux = stats[0], stats[1], stats[2], stats[3]
+    loss_sum, z_sum, total_w, aux, mtp_sum = stats[0], stats[1], stats[2], stats[3], stats[4]
     aux = aux / max(1, acc["micro"]) / max(1, self.n_moe_layers)
     inv_w = 1.0 / (total_w + EPS)
     # replica (data-parallel) gradient reduction for units replicated across batch axes
@@ -316,7 +369,8 @@ class TrainEngine:
       store.symm.barrier(0)       # updated shards are final on every rank before the next step reads them over NVLink
     lm_loss = loss_sum * inv_w
     metrics = {
-        "learning/loss": lm_loss + aux, "learning/lm_loss": lm_loss, "learning/z_loss": z_sum * inv_w,
+        "learning/loss": lm_loss + aux + mtp_sum * inv_w, "learning/lm_loss": lm_loss, "learning/mtp_loss": mtp_sum * inv_w,
+        "learning/z_loss": z_sum * inv_w,
         "learning/moe_lb_loss": aux, "learning/total_weights": total_w, "learning/raw_grad_norm": raw_norm,
         "learning/grad_norm": raw_norm * clip, "learning/current_learning_rate": torch.tensor(lr),
     }
