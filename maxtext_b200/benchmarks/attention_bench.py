@@ -39,7 +39,7 @@ def main():
   ap.add_argument("--no-lib", action="store_true")
   a = ap.parse_args()
   if a.small:
-    a.batch, a.seq, a.hq, a.hkv, a.iters = 1, 2048, 8, 2, 3
+    a.batch, a.seq, a.hq, a.hkv, a.iters = 2, 4096, 32, 8, 3     # 160 MB of q, k, v, out: larger than L2, small enough to profile
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
   B, S, Hq, Hkv, D = a.batch, a.seq, a.hq, a.hkv, a.dim

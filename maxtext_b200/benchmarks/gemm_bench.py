@@ -42,7 +42,7 @@ def main():
             ("mlp down dX", T, F, D, False, False, torch.bfloat16), ("mlp up dW", 2 * F, D, T, True, False, torch.float32),
             ("mlp down dW", D, F, T, True, False, torch.float32)]
   if args.small:
-    shapes = [("small", 4096, 4096, 4096, False, True, torch.bfloat16)]
+    shapes = [("small", 8192, 8192, 4096, False, True, torch.bfloat16)]   # 256 MB of operands: larger than L2, small enough to profile
   rows = []
   for name, M, N, K, ta, tb, odt in shapes:
     sets = []
