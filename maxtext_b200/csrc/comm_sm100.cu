@@ -11,6 +11,7 @@
 //     publishes one flag per segment; the GEMM in gemm_sm100.cu runs the same loop in spare CTAs of its own
 //     launch so that tiles start as soon as their rows have arrived.
 // No kernel here uses bulk-tensor copies from peer memory: remote data is read with ld.global by the copying CTA.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -129,9 +130,32 @@ gather_segments_kernel(const uint4* const* __restrict__ peer_shards, uint4* __re
   }
 }
 
+// out[r * rows + i, :] = bf16(acc_r[i, :]) for every rank r: the all-gather half of an all-reduce whose reduce-scatter half was
+// done by the GEMM epilogue (gemm_sm100.cu, mt_gemm_bf16_rs). Peer chunks are read with plain loads.
+__global__ void __launch_bounds__(256)
+gather_cvt_kernel(const float4* const* __restrict__ peer_acc, long chunk_vec4, int world, uint2* __restrict__ out) {
+  const long total = chunk_vec4 * world;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / chunk_vec4);
+    const float4 v = peer_acc[r][i - (long)r * chunk_vec4];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    out[i] = o;
+  }
+}
+
 }  // namespace mt
 
 using namespace mt;
+
+extern "C" int mt_gather_cvt(const float* const* peer_acc, long chunk_elems, int world, void* out, int ctas, cudaStream_t st) {
+  if (chunk_elems % 4) return -1;
+  gather_cvt_kernel<<<ctas, 256, 0, st>>>(reinterpret_cast<const float4* const*>(peer_acc), chunk_elems / 4, world,
+                                          reinterpret_cast<uint2*>(out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int mt_comm_signal(int* const* peer_flags, int slot, int my_rank, int world, int epoch, cudaStream_t st) {
   if (world > 32) return -1;

@@ -69,6 +69,11 @@ struct GemmParams {
   //   2: dx = dy W_e      B = W [E*Kc, N] MN-major, contraction rows start at e*Kc (Kc = p.K)
   //   3: dW_e = dy_e^T x_e  A = dy [R, x_nw] and B = x [R, N] MN-major, contraction over the rows of group e,
   //                          C = [E*x_nw, N] fp32; an empty group writes zeros (or nothing when accumulating)
+  // Fused reduce-scatter of the output over a tensor-parallel group (fp32 output only): row block mb belongs to rank
+  // (mb * BM) / r_rows; its tile is added into that rank's accumulation buffer (peer memory) by a TMA reduce-add through
+  // r_maps[owner] (tensor maps in global memory, one per rank, each over a [r_rows, N] fp32 buffer).
+  const CUtensorMap* r_maps;
+  int r_rows;
   int x_mode;
   int x_experts;
   int x_nw;
@@ -332,6 +337,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t acc_phase = 0;
     int buf = 0;
     bool ok = true;
+    if (p.r_maps && et == 0) {
+      // the owners' tensor maps live in global memory (written by the host before the launch): order them for the tensor-map proxy
+      for (int r = 0; r < p.M / p.r_rows; ++r)
+        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(p.r_maps + r) : "memory");
+    }
     for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
       int mb, nb;
       tile_coords(t, m_blocks, n_blocks, mb, nb);
@@ -394,8 +404,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (et == 0) {
             const int col0 = nb * BN + (OUT_F32 ? c * 32 : (c >> 1) * 64);
             if (col0 < p.N && !(empty_tile && p.accumulate)) {
-              if (OUT_F32 && p.accumulate) tma_reduce_add_2d(&map_c, sbuf, col0, mb * BM);
-              else tma_store_2d(&map_c, sbuf, col0, mb * BM);
+              if (OUT_F32 && p.r_maps) {
+                const int owner = (mb * BM) / p.r_rows;
+                tma_reduce_add_2d(p.r_maps + owner, sbuf, col0, mb * BM - owner * p.r_rows);
+              } else if (OUT_F32 && p.accumulate) {
+                tma_reduce_add_2d(&map_c, sbuf, col0, mb * BM);
+              } else {
+                tma_store_2d(&map_c, sbuf, col0, mb * BM);
+              }
             }
             tma_commit_group();
           }
@@ -598,4 +614,41 @@ extern "C" int mt_gemm_bf16_grouped(int mode, const void* a, const void* b, void
                      : launch<128, true, true, float>(ma, mb, mc, p, num_sms, stream);
   }
   return -12;
+}
+
+
+// Tensor maps for the fused reduce-scatter epilogue: entry r covers rank r's fp32 accumulation buffer [rows, N].
+// `out_maps` is host memory (world * sizeof(CUtensorMap) bytes); the caller copies it to the device once.
+extern "C" int mt_gemm_rs_encode_maps(void* out_maps, const void* const* bufs, int world, int rows, int N) {
+  using namespace mt;
+  CUtensorMap* m = reinterpret_cast<CUtensorMap*>(out_maps);
+  for (int r = 0; r < world; ++r) {
+    const int e = make_map_2d(&m[r], bufs[r], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rows, N, N, 32, BM);
+    if (e) return 100 + e;
+  }
+  return 0;
+}
+
+extern "C" int mt_tensor_map_bytes() { return (int)sizeof(CUtensorMap); }
+
+// out_r[M / world, N] (fp32, zeroed by the caller) += rows of a . op(b) that rank r owns, for every rank r of the group:
+// a [M, K] (K-major), b [N, K] (b_mn = 0) or [K, N] (b_mn = 1). dev_maps: device copy of mt_gemm_rs_encode_maps' output.
+extern "C" int mt_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const void* dev_maps,
+                               int world, int* status, int num_sms, cudaStream_t stream) {
+  using namespace mt;
+  if (M % (world * BM) || N % 32) return -10;
+  const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
+  CUtensorMap ma, mb;
+  int e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM);
+  if (e) return 100 + e;
+  if (!b_mn) e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, BN);
+  else e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK);
+  if (e) return 200 + e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = 1; p.status = status;
+  p.r_maps = reinterpret_cast<const CUtensorMap*>(dev_maps);
+  p.r_rows = M / world;
+  // map_c is not used on this path; the A map stands in so that the prefetch has a valid descriptor
+  if (BN == 256) return b_mn ? launch<256, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<256, false, false, float>(ma, mb, ma, p, num_sms, stream);
+  return b_mn ? launch<128, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<128, false, false, float>(ma, mb, ma, p, num_sms, stream);
 }

@@ -14,6 +14,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import functional as F
+from ..parallel import tp_fused
 from ..ops import reference as ref
 from ..parallel.param_store import Param, ParamDef, ALIGN
 
@@ -229,13 +230,13 @@ class Attention:
       self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
     self.sinks = ab.vector("sinks", self.hq, ("q_heads",), init="zeros", tp=True) if sinks else None
 
-  def _project(self, x, ctx):
+  def _project(self, x, ctx, tp_rt=None):
     B, S, _ = x.shape
     hq, hkv, dh = self.hq_l, self.hkv_l, self.dh
     fused = self.qkv.data if (self.qkv is not None and self.bq is None) else None
     if fused is not None:
       saved = ctx.reuse("qkv_proj")
-      qkv = F.linear(x, self.qkv, saved_out=saved)
+      qkv = F.linear(x, self.qkv, saved_out=saved, tp_reduce_dx=tp_rt)
       if ctx.wants("qkv_proj"):
         ctx.keep("qkv_proj", qkv.clone())      # the rotary embedding below rewrites qkv in place
       return qkv.view(B, S, hq + 2 * hkv, dh), None
@@ -246,8 +247,12 @@ class Attention:
 
   def __call__(self, x, ctx):
     B, S, _ = x.shape
-    x = tp_enter(x, ctx)
-    packed, sep = self._project(x, ctx)
+    # tensor parallelism: with the fused runtime the two all-reduces of this block run inside GEMM epilogues
+    tp_rt = tp_fused.runtime_for(ctx, x, self.d) if ctx.tp_size > 1 else None
+    fuse_in = tp_rt is not None and self.qkv is not None and self.bq is None and self.qkv.data is not None
+    if not fuse_in:
+      x = tp_enter(x, ctx)
+    packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
     plain = not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
@@ -280,8 +285,11 @@ class Attention:
       else:
         out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window)
     ctx.keep("context", out)
-    y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"))
-    y = tp_exit(y, ctx)
+    if tp_rt is not None and ctx.reuse("out_proj") is None:
+      y = F.linear(out.reshape(B, S, -1), self.o, tp_reduce=tp_rt)
+    else:
+      y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"))
+      y = tp_exit(y, ctx) if ctx.reuse("out_proj") is None else y
     ctx.keep("out_proj", y)
     return y
 
@@ -368,10 +376,13 @@ class MLP:
     self.bo = mb.sub("wo").vector("bias", d, ("embed",), init="zeros") if bias else None
 
   def __call__(self, x, ctx):
-    x = tp_enter(x, ctx)
+    tp_rt = tp_fused.runtime_for(ctx, x, x.shape[-1]) if ctx.tp_size > 1 else None
+    fuse_in = tp_rt is not None and self.gated and self.wi is not None and self.wi.data is not None
+    if not fuse_in:
+      x = tp_enter(x, ctx)
     if self.gated:
       if self.wi is not None and self.wi.data is not None:
-        gu = ctx.keep("mlpwi", F.linear(x, self.wi, ctx.reuse("mlpwi")))
+        gu = ctx.keep("mlpwi", F.linear(x, self.wi, ctx.reuse("mlpwi"), tp_reduce_dx=tp_rt if fuse_in else None))
       else:
         g = ctx.keep("mlpwi_0", F.linear(x, self.wi_0, ctx.reuse("mlpwi_0")))
         u = ctx.keep("mlpwi_1", F.linear(x, self.wi_1, ctx.reuse("mlpwi_1")))
@@ -380,7 +391,10 @@ class MLP:
     else:
       h = F.linear(x, self.wi_0, bias=self.bi)
       h = ref.act_fn(self.acts[0])(h.float()).to(x.dtype) if self.acts[0] != "linear" else h
-    y = F.linear(h, self.wo, ctx.reuse("mlpwo"), self.bo if ctx.tp_size == 1 else None)
-    y = tp_exit(y, ctx)
+    if tp_rt is not None and ctx.reuse("mlpwo") is None and self.bo is None:
+      y = F.linear(h, self.wo, tp_reduce=tp_rt)
+    else:
+      y = F.linear(h, self.wo, ctx.reuse("mlpwo"), self.bo if ctx.tp_size == 1 else None)
+      y = tp_exit(y, ctx) if ctx.reuse("mlpwo") is None else y
     ctx.keep("mlpwo", y)
     return y

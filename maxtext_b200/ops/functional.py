@@ -62,8 +62,9 @@ def mm(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out: torch.Tensor |
 
 class _LinearFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, x, w, pv, saved_out, bias, precomputed=None):
+  def forward(ctx, x, w, pv, saved_out, bias, precomputed=None, tp_reduce_dx=None):
     ctx.pv = pv
+    ctx.tp_reduce_dx = tp_reduce_dx
     x2 = x
     ctx.save_for_backward(x2, w)
     ctx.has_bias = bias is not None
@@ -84,17 +85,24 @@ class _LinearFn(torch.autograd.Function):
     dy2 = dy.reshape(-1, dy.shape[-1])
     if not dy2.is_contiguous():
       dy2 = dy2.contiguous()
-    dx = mm(dy2, w, False, False) if ctx.needs_input_grad[0] else None
+    if not ctx.needs_input_grad[0]:
+      dx = None
+    elif ctx.tp_reduce_dx is not None:
+      dx = ctx.tp_reduce_dx.all_reduce_gemm(dy2, w, False)      # column-parallel input gradient: summed over the TP ranks in the GEMM
+    else:
+      dx = mm(dy2, w, False, False)
     if pv is not None and pv.main_grad is not None:
       mm(dy2, x2, True, False, out=pv.main_grad.view(w.shape), accumulate=pv.grad_written)
       pv.grad_written = True
     dbias = dy2.float().sum(0) if ctx.has_bias else None
-    return dx, None, None, None, dbias, None
+    return dx, None, None, None, dbias, None, None
 
 
-def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None) -> torch.Tensor:
+def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None, tp_reduce=None, tp_reduce_dx=None) -> torch.Tensor:
   """y = x @ W.T for W = p.data stored [out, in]. `saved_out` short-cuts the forward GEMM when a remat
-  policy kept this projection's output."""
+  policy kept this projection's output. `tp_reduce` (a parallel.tp_fused runtime) sums the product over the
+  tensor-parallel ranks inside the GEMM (row-parallel layers); `tp_reduce_dx` does the same for the input gradient
+  (column-parallel layers)."""
   b = bias.leaf() if bias is not None else None
   x2 = x.reshape(-1, x.shape[-1])
   if not x2.is_contiguous():
@@ -102,14 +110,16 @@ def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None)
   # FSDP: when the unit's all-gather is still pending, this GEMM performs it inside its own launch
   pre = None
   pend = p.pending_unit() if hasattr(p, "pending_unit") else None
-  if pend is not None and saved_out is None and b is None:
+  if tp_reduce is not None and saved_out is None and b is None:
+    pre = tp_reduce.all_reduce_gemm(x2, p.data, True)
+  elif pend is not None and saved_out is None and b is None:
     pre = pend.store.ag_linear(pend, p, x2)
   if not torch.is_grad_enabled():
     if saved_out is not None:
       return saved_out
     y = (pre if pre is not None else mm(x2, p.data, False, True)).view(*x.shape[:-1], p.shape[0])
     return y + b.to(y.dtype) if b is not None else y
-  return _LinearFn.apply(x2, p.data, p, saved_out, b, pre).view(*x.shape[:-1], p.shape[0])
+  return _LinearFn.apply(x2, p.data, p, saved_out, b, pre, tp_reduce_dx).view(*x.shape[:-1], p.shape[0])
 
 
 # =============================================================================== RMSNorm

@@ -83,6 +83,31 @@ def train_moe_ep(rank, world, dev, fused):
   return out
 
 
+def train_tp(rank, world, dev, fused):
+  """Tensor parallelism over all ranks: all-reduces inside GEMM epilogues (peer-memory reduce-add) vs NCCL all-reduce."""
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as T
+  from maxtext_b200.train.engine import TrainEngine
+  cfg = pyconfig.initialize(
+      ["w", "maxtext_b200/configs/base.yml", "base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128",
+       "base_mlp_dim=1024", "base_num_decoder_layers=3", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
+       "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal", "log_config=false", "steps=3",
+       "learning_rate=1e-3", "warmup_steps_fraction=0.0", "ici_fsdp_parallelism=1", f"ici_tensor_parallelism={world}",
+       f"use_fused_comm_kernels={'true' if fused else 'false'}"], num_devices=world)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world)
+  eng = TrainEngine(cfg, mesh, dev)
+  it = T.create_data_iterator(cfg, mesh)
+  out = []
+  for _ in range(3):
+    m = eng.train_step(next(it))
+    out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  if fused:
+    from maxtext_b200.parallel import tp_fused
+    assert tp_fused._RT and all(rt.use > 0 for rt in tp_fused._RT.values()), "fused TP path did not run"
+  return out
+
+
 def train(rank, world, dev, fused):
   from maxtext_b200.config import pyconfig
   from maxtext_b200.parallel import mesh as mesh_lib
@@ -114,7 +139,7 @@ def main():
       kernels(rank, world, dev)
       msg = "ok"
     else:
-      fn = train_moe_ep if mode == "moe_ep" else train
+      fn = {"moe_ep": train_moe_ep, "tp": train_tp}.get(mode, train)
       a = fn(rank, world, dev, fused=False)
       b = fn(rank, world, dev, fused=True)
       for (la, na), (lb, nb) in zip(a, b):

@@ -52,3 +52,7 @@ def test_fused_comm_train_step_matches_nccl(tmp_path):
 
 def test_expert_parallel_peer_dispatch_matches_nccl(tmp_path):
   _run("moe_ep", tmp_path)
+
+
+def test_tensor_parallel_gemm_reduce_scatter_matches_nccl(tmp_path):
+  _run("tp", tmp_path)
