@@ -107,6 +107,7 @@ def main():
   ap.add_argument("--pdbs", type=float, default=2.0)
   ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is then not the headline config)")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--quantization", default="", help="'' (headline: bf16) or fp8: linear layers on the 8-bit tensor-core path (a different configuration)")
   ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                   help="FSDP collectives: this repository's NVLink kernels fused with the GEMMs (default) or plain NCCL (comparison arm)")
   args = ap.parse_args()
@@ -131,6 +132,8 @@ def main():
                "dataset_type=synthetic", "remat_policy=full", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal",
                "log_config=false", "steps=1000", "learning_rate=3e-5", f"ici_fsdp_parallelism={world}", "dtype=bfloat16",
                "weight_dtype=float32", "attention=flash", f"use_fused_comm_kernels={'true' if args.comm == 'fused' else 'false'}"]
+  if args.quantization:
+    overrides += [f"quantization={args.quantization}"]
   if args.layers > 0:
     overrides += [f"base_num_decoder_layers={args.layers}", "override_model_config=true"]
   cfg = pyconfig.initialize(["bench", os.path.join(ROOT, "maxtext_b200", "configs", "base.yml")] + overrides, num_devices=world)
@@ -206,7 +209,7 @@ def main():
     out = {
         "metric": "tokens/sec (whole job) Llama-3-8B FSDP bf16 seq 8192 pre-training", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": value / (PUBLISHED_TOK_S_PER_DEVICE * world), "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": value / (PUBLISHED_TOK_S_PER_DEVICE * world), "dtype": "bf16" if not args.quantization else f"{args.quantization} linears, bf16 elsewhere", "data": "synthetic",
         "config": {"model": args.model + ("" if args.layers <= 0 else f"-{args.layers}layers-DEBUG"), "global_batch": gb,
                    "seq_len": cfg.max_target_length, "parallelism": f"fsdp{world}", "collectives": args.comm if world > 1 else "none", "remat_policy": cfg.remat_policy,
                    "optimizer": "adamw fp32 master", "l2": "inputs_larger_than_L2 (16 GB of weights streamed per step)"},

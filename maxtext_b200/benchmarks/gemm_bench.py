@@ -32,6 +32,7 @@ def main():
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--small", action="store_true", help="one small shape only (profiling)")
   ap.add_argument("--no-cublas", action="store_true")
+  ap.add_argument("--fp8", action="store_true", help="also time the 8-bit (E4M3 x E4M3) path on the forward shapes, quantisation excluded")
   args = ap.parse_args()
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
@@ -62,6 +63,13 @@ def main():
           out.copy_(r)
       ms2 = time_fn(cb, args.iters)
       row.update(cublas_ms=ms2, cublas_tflops=2.0 * M * N * K / ms2 / 1e9, ratio=ms2 / ms)
+    if args.fp8 and not ta and tb and odt == torch.bfloat16:
+      q = [(E.quantize_fp8(a, 0, True, False), E.quantize_fp8(b, 0, True, False)) for a, b in sets]
+      ms8 = time_fn(lambda i: E.gemm_fp8(q[i & 1][0][0], q[i & 1][1][0], out, 0, 0, q[i & 1][0][2], q[i & 1][1][2], False), args.iters)
+      row.update(fp8_ms=ms8, fp8_tflops=2.0 * M * N * K / ms8 / 1e9)
+      ref = torch.mm(sets[1][0].float()[:256], sets[1][1].float().t())
+      E.gemm_fp8(q[1][0][0], q[1][1][0], out, 0, 0, q[1][0][2], q[1][1][2], False)
+      row.update(fp8_rel_err=float((out[:256].float() - ref).abs().max() / ref.abs().max()))
     rows.append(row)
     print(json.dumps(row), flush=True)
     del sets, out

@@ -22,6 +22,10 @@ int mt_xent(void* logits, const int* targets, const float* weights, float z_loss
             int V, int write_grad, cudaStream_t st);
 int mt_adamw(float* p, const float* g, void* m, int m_is_bf16, float* v, void* shadow, long n, float lr, float b1, float b2, float eps,
              float eps_root, float wd, float bc1, float bc2, const float* grad_scale, int sms, cudaStream_t st);
+int mt_amax(const void* x, long n, float* amax, int sms, cudaStream_t st);
+int mt_quantize_fp8(const void* x, int R, int C, const float* amax, int fmt, void* q, void* qt, float* dequant, cudaStream_t st);
+int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt, int b_fmt,
+                int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms, cudaStream_t stream);
 int mt_sumsq_num_partials(long n, int sms);
 int mt_sumsq(const float* x, long n, float* partials, float* out, int sms, cudaStream_t st);
 }
@@ -85,6 +89,43 @@ void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bo
   int rc = mt_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), out.stride(0),
                         ta ? 1 : 0, tb ? 0 : 1, f32 ? 1 : 0, accumulate ? 1 : 0, status_tensor().data_ptr<int>(), num_sms(), cur_stream());
   check(rc, "mt_gemm_bf16");
+}
+
+// x [R, C] bf16 -> (q [R, C] uint8 or None, qt [C, R] uint8 or None, dequant scale [1]); fmt 0 = E4M3, 1 = E5M2. Current scaling:
+// the scale comes from this tensor's own absolute maximum, computed on the device.
+std::tuple<c10::optional<torch::Tensor>, c10::optional<torch::Tensor>, torch::Tensor> quantize_fp8(const torch::Tensor& x, int64_t fmt,
+                                                                                                     bool want_q, bool want_t) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(x.size(0) % 64 == 0 && x.size(1) % 64 == 0, "quantize_fp8: dims must be multiples of 64");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto fo = torch::dtype(torch::kFloat32).device(x.device());
+  auto amax = torch::zeros({1}, fo);
+  auto deq = torch::empty({1}, fo);
+  check(mt_amax(x.data_ptr(), x.numel(), amax.data_ptr<float>(), num_sms(), cur_stream()), "mt_amax");
+  c10::optional<torch::Tensor> q, qt;
+  auto bo = torch::dtype(torch::kUInt8).device(x.device());
+  if (want_q) q = torch::empty({x.size(0), x.size(1)}, bo);
+  if (want_t) qt = torch::empty({x.size(1), x.size(0)}, bo);
+  check(mt_quantize_fp8(x.data_ptr(), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(), (int)fmt, q ? q->data_ptr() : nullptr,
+                        qt ? qt->data_ptr() : nullptr, deq.data_ptr<float>(), cur_stream()),
+        "mt_quantize_fp8");
+  return {q, qt, deq};
+}
+
+// out [M, N] (+)= a [M, K] . b [N, K]^T * sa * sb, a / b uint8 holding E4M3 (fmt 0) or E5M2 (fmt 1)
+void gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, int64_t a_fmt, int64_t b_fmt, const torch::Tensor& sa,
+              const torch::Tensor& sb, bool accumulate) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == torch::kUInt8 && b.scalar_type() == torch::kUInt8 && a.dim() == 2 && b.dim() == 2);
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && a.size(1) == b.size(1) && out.size(0) == a.size(0) && out.size(1) == b.size(0));
+  TORCH_CHECK(a.size(1) % 128 == 0 && a.size(0) % 128 == 0 && b.size(0) % 128 == 0, "gemm_fp8: dims must be multiples of 128");
+  const bool f32 = out.scalar_type() == torch::kFloat32;
+  TORCH_CHECK((f32 || out.scalar_type() == torch::kBFloat16) && out.stride(1) == 1 && (!accumulate || f32));
+  TORCH_CHECK(sa.scalar_type() == torch::kFloat32 && sb.scalar_type() == torch::kFloat32);
+  c10::cuda::CUDAGuard guard(a.device());
+  check(mt_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), a.stride(0), b.stride(0),
+                    out.stride(0), (int)a_fmt, (int)b_fmt, f32 ? 1 : 0, accumulate ? 1 : 0, sa.data_ptr<float>(), sb.data_ptr<float>(),
+                    status_tensor().data_ptr<int>(), num_sms(), cur_stream()),
+        "mt_gemm_fp8");
 }
 
 int64_t kernel_status(bool reset) {
@@ -196,6 +237,8 @@ void register_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
   m.def("gemm", &gemm);
+  m.def("quantize_fp8", &quantize_fp8);
+  m.def("gemm_fp8", &gemm_fp8);
   m.def("kernel_status", &kernel_status);
   m.def("launch_count", &launch_count);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

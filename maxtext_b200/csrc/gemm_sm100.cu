@@ -74,6 +74,11 @@ struct GemmParams {
   // r_maps[owner] (tensor maps in global memory, one per rank, each over a [r_rows, N] fp32 buffer).
   const CUtensorMap* r_maps;
   int r_rows;
+  // 8-bit operands (FP8 template flag): formats per operand (0 = E4M3, 1 = E5M2) and the de-quantisation factors, read from
+  // device memory so that scales derived from a running amax never visit the host. out = acc * (*q_scale_a) * (*q_scale_b).
+  int q_fmt_a, q_fmt_b;
+  const float* q_scale_a;
+  const float* q_scale_b;
   int x_mode;
   int x_experts;
   int x_nw;
@@ -145,7 +150,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, i
   nb = r / gsz;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, GemmParams p) {
@@ -174,7 +179,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int m_blocks = (p.x_mode == 1 || p.x_mode == 2) ? p.x_offs[p.x_experts] / BM : (p.M + BM - 1) / BM;
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;      // elements per 128-byte smem row: the byte layout of a stage is the same for both widths
+  static_assert(!FP8 || (!A_MN && !B_MN), "8-bit operands are K-major only");
+  const int num_kb = (p.K + BKE - 1) / BKE;
   const int cta_stride = (int)gridDim.x - p.g_comm_ctas;        // CTAs that compute tiles
   const bool is_comm_cta = (int)blockIdx.x >= cta_stride;
 
@@ -271,14 +278,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t sa = smem_a0 + s * Cfg::A_BYTES;
           const uint32_t sb = smem_b0 + s * Cfg::B_BYTES;
           if (!A_MN) {
-            tma_load_2d(sa, &map_a, full_bar(s), ti.k0a + kb * BK, ti.a_m0);              // box {64 k, 128 m}
+            tma_load_2d(sa, &map_a, full_bar(s), ti.k0a + kb * BKE, ti.a_m0);             // box {128 B of k, 128 m}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)                                             // boxes {64 m, 64 k}
               tma_load_2d(sa + j * 8192, &map_a, full_bar(s), ti.a_m0 + j * 64, ti.k0a + kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &map_b, full_bar(s), ti.k0b + kb * BK, ti.b_n0);              // box {64 k, BN n}
+            tma_load_2d(sb, &map_b, full_bar(s), ti.k0b + kb * BKE, ti.b_n0);             // box {128 B of k, BN n}
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)                                             // boxes {64 n, 64 k}
@@ -291,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? make_idesc_fp8(BM, BN, (uint32_t)p.q_fmt_a, (uint32_t)p.q_fmt_b) : make_idesc_bf16(BM, BN, A_MN, B_MN);
       constexpr uint32_t A_LBO = A_MN ? 8192 : 16, B_LBO = B_MN ? 8192 : 16;
       constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32, B_KSTEP = B_MN ? 2048 : 32;  // bytes per UMMA_K
       int s = 0;
@@ -316,8 +323,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t db = make_smem_desc(smem_b0 + s * Cfg::B_BYTES, B_LBO, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_f16_ss(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
-                        (kb | k) != 0 ? 1u : 0u);
+            if (FP8) umma_f8_ss(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+            else umma_f16_ss(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                             (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(s));   // frees the smem stage when these MMAs retire
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -360,6 +369,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (empty_tile) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (FP8) {
+          const float qs = __ldg(p.q_scale_a) * __ldg(p.q_scale_b);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * qs);
         }
         if (c == BN / 32 - 1) {
           // whole accumulator is in registers: hand the TMEM buffer back to the MMA warp
@@ -467,10 +481,10 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT>
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, GemmParams p, int num_sms, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, FP8>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -2;
@@ -651,4 +665,29 @@ extern "C" int mt_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K
   // map_c is not used on this path; the A map stands in so that the prefetch has a valid descriptor
   if (BN == 256) return b_mn ? launch<256, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<256, false, false, float>(ma, mb, ma, p, num_sms, stream);
   return b_mn ? launch<128, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<128, false, false, float>(ma, mb, ma, p, num_sms, stream);
+}
+
+
+// C[M,N] (+)= (A . B^T) * (*scale_a) * (*scale_b) with 8-bit floating point operands: a [M, K], b [N, K], both K-major,
+// formats a_fmt / b_fmt (0 = E4M3, 1 = E5M2); fp32 accumulation in tensor memory; output bf16 or fp32 (accumulate needs fp32).
+extern "C" int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt,
+                           int b_fmt, int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms,
+                           cudaStream_t stream) {
+  using namespace mt;
+  if ((accumulate && !out_f32) || K % 128 || lda % 16 || ldb % 16) return -10;
+  const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
+  CUtensorMap ma, mb, mc;
+  int e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, 2 * BK, BM);
+  if (e) return 100 + e;
+  if ((e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, 2 * BK, BN))) return 200 + e;
+  if (out_f32) e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, BM);
+  else e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
+  if (e) return 300 + e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = accumulate; p.status = status;
+  p.q_fmt_a = a_fmt; p.q_fmt_b = b_fmt; p.q_scale_a = scale_a; p.q_scale_b = scale_b;
+  if (BN == 256) return out_f32 ? launch<256, false, false, float, true>(ma, mb, mc, p, num_sms, stream)
+                                : launch<256, false, false, __nv_bfloat16, true>(ma, mb, mc, p, num_sms, stream);
+  return out_f32 ? launch<128, false, false, float, true>(ma, mb, mc, p, num_sms, stream)
+                 : launch<128, false, false, __nv_bfloat16, true>(ma, mb, mc, p, num_sms, stream);
 }

@@ -42,6 +42,8 @@ class TrainEngine:
           else torch.device("cpu")
     self.device = torch.device(device)
     self.model = model or Transformer(c, mesh, self.device)
+    from ..ops import quantization as _quant
+    _quant.set_mode(str(c.quantization or ""))
     self.store = self.model.store
     if init:
       self.store.initialize(seed=c.init_weights_seed)
