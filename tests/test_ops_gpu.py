@@ -50,14 +50,17 @@ def test_rope_roundtrip_and_reference(interleaved):
 @pytest.mark.parametrize("act,code", [("silu", 0), ("gelu", 1)])
 def test_gated_act(act, code):
   E = _E()
+  torch.manual_seed(0)
   gu = torch.randn(200, 2 * 1408, device="cuda").bfloat16()
   out = torch.empty(200, 1408, device="cuda", dtype=torch.bfloat16)
   E.gated_act_fwd(gu, out, code)
-  assert (out.float() - ref.gated_act(gu, act).float()).abs().max() <= 3e-2
+  want = ref.gated_act(gu, act).float()
+  assert bool(((out.float() - want).abs() <= 1e-2 + want.abs() / 64).all())          # within two bf16 ulps of the reference
   dy = torch.randn_like(out)
   dgu = torch.empty_like(gu)
   E.gated_act_bwd(dy, gu, dgu, code)
-  assert (dgu.float() - ref.gated_act_bwd(dy, gu, act).float()).abs().max() <= 6e-2
+  wantg = ref.gated_act_bwd(dy, gu, act).float()
+  assert bool(((dgu.float() - wantg).abs() <= 2e-2 + wantg.abs() / 64).all())
 
 
 @pytest.mark.parametrize("V", [32000, 128256, 1003 * 8])
