@@ -198,7 +198,7 @@ class Attention:
 
   def __init__(self, b: Builder, config, name="self_attention", window: int = 0, rope_inv_ts=None, interleaved=False,
                use_rope=True, qk_norm=False, query_scalar: float | None = None, soft_cap: float = 0.0, bias=False,
-               rotary_dim=None, sinks=False):
+               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0):
     c = config
     self.config = c
     self.hq, self.hkv, self.dh, self.d = c.num_query_heads, c.num_kv_heads, c.head_dim, c.emb_dim
@@ -207,6 +207,7 @@ class Attention:
     self.hkv_l = max(1, self.hkv // tp) if self.hkv >= tp else self.hkv
     self.window, self.inv_ts, self.interleaved, self.use_rope = window, rope_inv_ts, interleaved, use_rope
     self.qk_norm, self.query_scalar, self.soft_cap, self.rotary_dim = qk_norm, query_scalar, soft_cap, rotary_dim
+    self.l2_qk_norm, self.temperature_tuning, self.chunk = l2_qk_norm, temperature_tuning, int(chunk)
     ab = b.sub(name)
     depth_scale = 1.0 if (qk_norm or (query_scalar is not None and query_scalar != 1.0)) else 1.0 / math.sqrt(self.dh)
     kv_tp = "col" if self.hkv >= tp else None
@@ -253,7 +254,8 @@ class Attention:
     if not fuse_in:
       x = tp_enter(x, ctx)
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
-    plain = not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
+    plain = (not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
+             and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
       # attention output kept by the remat policy: only the backward of the packed op is needed
@@ -272,9 +274,23 @@ class Attention:
       if self.use_rope:
         q = F.rope(q, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
         k = F.rope(k, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
+      if self.l2_qk_norm:
+        # llama4 (src/maxtext/layers/attentions.py:1292-1296): x * rsqrt(mean(x^2) + eps), no learned scale, after RoPE
+        eps = self.config.normalization_layer_epsilon
+        q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + eps)).to(q.dtype)
+        k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + eps)).to(k.dtype)
       if self.query_scalar and self.query_scalar != 1.0:
         q = q * self.query_scalar
-      if ctx.cache is not None:
+      if self.temperature_tuning and not self.use_rope:
+        # llama4 NoPE layers (attentions.py:1302-1308): log(floor((pos + 1) / floor_scale) + 1) * scale + 1
+        c_ = self.config
+        sc = torch.log(torch.floor((ctx.positions.float() + 1.0) / float(getattr(c_, "temperature_tuning_floor_scale", 8192.0))) + 1.0) \
+            * float(getattr(c_, "temperature_tuning_scale", 0.1)) + 1.0
+        q = (q.float() * sc[:, :, None, None]).to(q.dtype)
+      if ctx.cache is None and self.chunk and S > self.chunk and ctx.cp_size == 1:
+        m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window, chunk=self.chunk)
+        out = ref.attention(q, k, v, m, 1.0, self.soft_cap)
+      elif ctx.cache is not None:
         out = ctx.cache.attend(q, k, v, ctx, window=self.window, soft_cap=self.soft_cap, sinks=self.sinks)
       elif ctx.cp_size > 1:
         from ..parallel.context_parallel import context_attention

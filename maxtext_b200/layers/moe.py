@@ -33,9 +33,13 @@ class _AllToAllRows(torch.autograd.Function):
 
 
 class RoutedMoE:
-  def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False):
+  def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False, style: str = ""):
+    """style: "llama4" (raw top-k logits, sigmoid score applied to the expert input, unit combine weights;
+    src/maxtext/layers/moe.py:752,902-906,1051-1053) or "gpt_oss" (router bias on the logits, per-expert biases and the
+    clamped x * sigmoid(1.702 x) * (up + 1) activation; moe.py:617-637,841-853,2239-2242)."""
     c = config
     self.c = c
+    self.style = style
     self.E, self.k = c.num_experts, c.num_experts_per_tok
     self.deepseek = deepseek_style
     mb = b.sub(name)
@@ -47,6 +51,11 @@ class RoutedMoE:
     self.wo = mb.experts("wo", self.E, f, d, ("exp", "mlp_moe", "embed_moe"), tp="row")
     self.act = c.mlp_activations[0]
     self.e_local = self.E // b.ep_size
+    self.b0 = self.b1 = self.bo = None
+    if c.mlp_bias:
+      self.b0 = mb.table("wi_0_bias", (self.E, f), ("exp", "activation_mlp"), init="zeros")
+      self.b1 = mb.table("wi_1_bias", (self.E, f), ("exp", "activation_mlp"), init="zeros")
+      self.bo = mb.table("wo_bias", (self.E, d), ("exp", "activation_embed"), init="zeros")
 
   # ---- routing
   def route(self, x2, B, S):
@@ -73,8 +82,10 @@ class RoutedMoE:
       wts = wts * c.routed_scaling_factor
       probs = scores
     else:
+      if self.gate_bias is not None:
+        logits = logits + self.gate_bias.leaf().to(logits.dtype)
       vals, idx = logits.topk(self.k, dim=-1)
-      wts = torch.softmax(vals.float(), -1)
+      wts = vals.float() if self.style == "llama4" else torch.softmax(vals.float(), -1)
       if c.norm_topk_prob:
         wts = wts / wts.sum(-1, keepdim=True)
       probs = torch.softmax(logits.float(), -1)
@@ -91,8 +102,21 @@ class RoutedMoE:
   def experts_ffn(self, rows, sizes):
     g = moe_ops.grouped_linear(rows, self.wi_0, sizes)
     u = moe_ops.grouped_linear(rows, self.wi_1, sizes)
-    h = F.gated_act(torch.cat([g, u], dim=-1), self.act)
-    return moe_ops.grouped_linear(h, self.wo, sizes)
+    row_e = None
+    if self.b0 is not None:
+      row_e = torch.repeat_interleave(torch.arange(sizes.numel(), device=rows.device), sizes.long(), output_size=rows.shape[0])
+      g = g + self.b0.leaf()[row_e].to(g.dtype)
+      u = u + self.b1.leaf()[row_e].to(u.dtype)
+    if self.style == "gpt_oss":
+      lim = float(self.c.mlp_activations_limit)
+      gf, uf = g.float().clamp(max=lim), u.float().clamp(-lim, lim)
+      h = (gf * torch.sigmoid(1.702 * gf) * (uf + 1.0)).to(rows.dtype)
+    else:
+      h = F.gated_act(torch.cat([g, u], dim=-1), self.act)
+    y = moe_ops.grouped_linear(h, self.wo, sizes)
+    if self.bo is not None:
+      y = y + self.bo.leaf()[row_e].to(y.dtype)
+    return y
 
   def __call__(self, x, ctx):
     B, S, D = x.shape
@@ -100,13 +124,18 @@ class RoutedMoE:
     wts, idx, aux = self.route(x2, B, S)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))
-    if ctx.ep_size == 1 and self.act in F._ACT_CODE and moe_ops.padded_path_supported(x2, D, self.wi_0.data.shape[1], self.E):
+    if self.style == "llama4":
+      assert self.k == 1, "llama4 routing scales the expert input by its single score"
+      x2 = (x2.float() * torch.sigmoid(wts)).to(x2.dtype)
+      wts = torch.ones_like(wts)
+    plain_ffn = self.b0 is None and self.style != "gpt_oss"
+    if plain_ffn and ctx.ep_size == 1 and self.act in F._ACT_CODE and moe_ops.padded_path_supported(x2, D, self.wi_0.data.shape[1], self.E):
       # GPU path: device-side stable sort into 128-row-padded expert groups, grouped tcgen05 GEMMs, no host synchronisation
       out = moe_ops.moe_ffn_padded(x2, wts, idx, self.wi_0, self.wi_1, self.wo, self.E, self.act)
       if ctx.tp_size > 1:
         out = tp_exit(out, ctx)
       return out.view(B, S, D)
-    if ctx.ep_size > 1 and x2.is_cuda:
+    if plain_ffn and ctx.ep_size > 1 and x2.is_cuda:
       from . import moe_ep
       if moe_ep.supported(x2, self, ctx):
         # dispatch / return through the peers' symmetric buffers (this repository's kernels); the NCCL path below is the fallback
@@ -148,9 +177,9 @@ class RoutedMoE:
 class RoutedAndSharedMoE:
   """Routed experts plus always-on shared experts (src/maxtext/layers/moe.py:3259-3371)."""
 
-  def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0"):
+  def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0", style: str = ""):
     mb = b.sub(name)
-    self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=True)
+    self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=(style == ""), style=style)
     self.shared = MLP(mb, config, "shared_experts", hidden=config.shared_experts * config.moe_mlp_dim) \
         if config.shared_experts > 0 else None
 

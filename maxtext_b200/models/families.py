@@ -60,8 +60,31 @@ def layer_plans(c) -> list[LayerPlan]:
   blk = c.decoder_block
   mla = c.attention_type == "mla"
   attn = "mla" if mla else "gqa"
-  if blk in ("default", "llama2", "mistral", "qwen3", "olmo3", "simple", "simple_mlp", "llama4"):
+  if blk in ("default", "llama2", "mistral", "qwen3", "simple", "simple_mlp"):
     return [LayerPlan("layers", [_llama_like(c, attention=attn)]) for _ in range(n)]
+  if blk == "olmo3":
+    # src/maxtext/models/olmo3.py: no pre-norms; the attention and MLP outputs are normalised before the residual add;
+    # cycles of (local, local, local, global) attention form one scanned block with sub-trees layers_0 .. layers_3
+    cyc = max(1, int(c.inhomogeneous_layer_cycle_interval))
+    assert n % cyc == 0, "olmo3 layers must be a multiple of inhomogeneous_layer_cycle_interval"
+    blocks = [BlockPlan(prefix=f"layers_{j}", pre_attn_norm=None, pre_mlp_norm=None, attn_name="attention",
+                        post_attn_norm="post_self_attention_layer_norm", post_mlp_norm="post_mlp_layer_norm",
+                        window=c.sliding_window_size if (j % 4) != 3 else 0, qk_norm=c.use_qk_norm, query_scalar=c.head_dim ** -0.5,
+                        attn_bias=c.attention_bias) for j in range(cyc)]
+    return [LayerPlan("layers", blocks) for _ in range(n // cyc)]
+  if blk == "llama4":
+    # src/maxtext/models/llama4.py:267-420: every nope_layer_interval-th layer has no RoPE, global attention and the
+    # temperature-tuned query; the others use RoPE, chunked attention and scale-free q/k normalisation; MoE layers
+    # (routed top-1 + shared expert) every interleave_moe_layer_step layers
+    plans = []
+    for i in range(n):
+      nope = c.nope_layer_interval > 0 and (i + 1) % c.nope_layer_interval == 0
+      is_moe = c.num_experts > 1 and (i + 1) % max(1, c.interleave_moe_layer_step) == 0
+      plans.append(LayerPlan("layers", [BlockPlan(
+          use_rope=not nope, chunk=0 if nope else int(c.chunk_attn_window_size), l2_qk_norm=bool(c.use_qk_norm) and not nope,
+          temperature_tuning=bool(c.temperature_tuning) and nope, mlp="moe_shared" if is_moe else "dense",
+          mlp_name="Llama4MoEBlock_0" if is_moe else "mlp", moe_style="llama4" if is_moe else "")]))
+    return plans
   if blk == "qwen2":
     bp = _llama_like(c, attention=attn)
     bp.attn_bias = True
@@ -110,8 +133,8 @@ def layer_plans(c) -> list[LayerPlan]:
     for i in range(n):
       local = (i % 2) == 0
       plans.append(LayerPlan("layers", [BlockPlan(window=c.sliding_window_size if local else 0, attn_bias=True, sinks=True,
-                                                  mlp="moe", mlp_name="GptOssMlp")]))
+                                                  mlp="moe", mlp_name="GptOssMlp", moe_style="gpt_oss")]))
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, gpt3, gpt_oss, olmo3, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, gpt3, gpt_oss, olmo3, llama4, simple)")

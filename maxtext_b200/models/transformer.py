@@ -49,6 +49,11 @@ class BlockPlan:
   norm_kind: str = "rms"
   norm_offset: float = 0.0
   parallel_residual: bool = False
+  prefix: str = ""                       # extra level in the parameter tree (olmo3: layers_0 .. layers_3 inside one cycle)
+  l2_qk_norm: bool = False               # llama4: scale-free RMS normalisation of q and k after RoPE
+  temperature_tuning: bool = False       # llama4 NoPE layers: position-dependent query scale
+  chunk: int = 0                         # llama4 RoPE layers: attention restricted to chunks of this many tokens
+  moe_style: str = ""                    # "" | "llama4" | "gpt_oss"
 
 
 @dataclass
@@ -61,32 +66,35 @@ class DecoderBlock:
   def __init__(self, b: L.Builder, config, plan: BlockPlan, rope_tables: dict):
     c, s = config, plan.suffix
     self.plan = plan
+    if plan.prefix:
+      b = b.sub(plan.prefix)
     eps = c.normalization_layer_epsilon
     mk = lambda n: L.Norm(b, n + s, c.emb_dim, eps, plan.norm_offset, kind=plan.norm_kind)  # noqa: E731
-    self.n1 = mk(plan.pre_attn_norm)
+    self.n1 = mk(plan.pre_attn_norm) if plan.pre_attn_norm else None
     inv_ts, interleaved = rope_tables[plan.rope]
     if plan.attention == "mla":
       self.attn = L.MLA(b, c, inv_ts, interleaved, plan.attn_name + s)
     else:
       self.attn = L.Attention(b, c, plan.attn_name + s, plan.window, inv_ts, interleaved, plan.use_rope, plan.qk_norm,
                               plan.query_scalar, plan.soft_cap, plan.attn_bias,
-                              rotary_dim=None, sinks=plan.sinks)
+                              rotary_dim=None, sinks=plan.sinks, l2_qk_norm=plan.l2_qk_norm,
+                              temperature_tuning=plan.temperature_tuning, chunk=plan.chunk)
     self.n1b = mk(plan.post_attn_norm) if plan.post_attn_norm else None
-    self.n2 = mk(plan.pre_mlp_norm)
+    self.n2 = mk(plan.pre_mlp_norm) if plan.pre_mlp_norm else None
     if plan.mlp == "moe":
-      self.mlp = M.RoutedMoE(b, c, plan.mlp_name + s)
+      self.mlp = M.RoutedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
     elif plan.mlp == "moe_shared":
-      self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s)
+      self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
     else:
       self.mlp = L.MLP(b, c, plan.mlp_name + s, plan.mlp_hidden, bias=plan.mlp_bias)
     self.n2b = mk(plan.post_mlp_norm) if plan.post_mlp_norm else None
 
   def __call__(self, x, ctx: LayerCtx):
-    a = self.attn(self.n1(x), ctx)
+    a = self.attn(self.n1(x) if self.n1 is not None else x, ctx)
     if self.n1b is not None:
       a = self.n1b(a)
     x = x + a
-    m = self.mlp(self.n2(x), ctx)
+    m = self.mlp(self.n2(x) if self.n2 is not None else x, ctx)
     if self.n2b is not None:
       m = self.n2b(m)
     return x + m

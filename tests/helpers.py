@@ -27,6 +27,9 @@ FAMILIES = {
     "qwen2.5-7b": [],
     "qwen3-30b-a3b": ["num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32"],
     "gpt3-6b": ["trainable_position_size=32"],
+    "olmo3-7b": ["base_num_decoder_layers=4", "sliding_window_size=8"],
+    "llama4-17b-16e": ["base_num_decoder_layers=4", "num_experts=4", "base_moe_mlp_dim=32", "chunk_attn_window_size=16", "nope_layer_interval=2"],
+    "gpt-oss-20b": ["base_num_decoder_layers=2", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "sliding_window_size=8"],
 }
 
 
