@@ -107,6 +107,8 @@ def main():
   ap.add_argument("--pdbs", type=float, default=2.0)
   ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is then not the headline config)")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (secondary benchmarks; the headline uses fsdp only)")
+  ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (secondary benchmarks)")
   ap.add_argument("--quantization", default="", help="'' (headline: bf16) or fp8: linear layers on the 8-bit tensor-core path (a different configuration)")
   ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                   help="FSDP collectives: this repository's NVLink kernels fused with the GEMMs (default) or plain NCCL (comparison arm)")
@@ -130,7 +132,8 @@ def main():
   dev = torch.device("cuda", torch.cuda.current_device())
   overrides = [f"model_name={args.model}", f"per_device_batch_size={args.pdbs}", f"max_target_length={args.seq}",
                "dataset_type=synthetic", "remat_policy=full", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal",
-               "log_config=false", "steps=1000", "learning_rate=3e-5", f"ici_fsdp_parallelism={world}", "dtype=bfloat16",
+               "log_config=false", "steps=1000", "learning_rate=3e-5", f"ici_fsdp_parallelism={world // (args.ep * args.tp)}", f"ici_expert_parallelism={args.ep}",
+               f"ici_tensor_parallelism={args.tp}", "dtype=bfloat16",
                "weight_dtype=float32", "attention=flash", f"use_fused_comm_kernels={'true' if args.comm == 'fused' else 'false'}"]
   if args.quantization:
     overrides += [f"quantization={args.quantization}"]
@@ -207,11 +210,13 @@ def main():
     except Exception:  # pylint: disable=broad-except
       pass
     out = {
-        "metric": "tokens/sec (whole job) Llama-3-8B FSDP bf16 seq 8192 pre-training", "value": value, "unit": "tokens/s",
+        "metric": "tokens/sec (whole job) Llama-3-8B FSDP bf16 seq 8192 pre-training" if (args.model == "llama3-8b" and args.layers <= 0 and
+                                                                                              args.ep == 1 and args.tp == 1)
+        else f"tokens/sec (whole job) {args.model} seq {args.seq} pre-training (secondary benchmark)", "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": value / (PUBLISHED_TOK_S_PER_DEVICE * world), "dtype": "bf16" if not args.quantization else f"{args.quantization} linears, bf16 elsewhere", "data": "synthetic",
         "config": {"model": args.model + ("" if args.layers <= 0 else f"-{args.layers}layers-DEBUG"), "global_batch": gb,
-                   "seq_len": cfg.max_target_length, "parallelism": f"fsdp{world}", "collectives": args.comm if world > 1 else "none", "remat_policy": cfg.remat_policy,
+                   "seq_len": cfg.max_target_length, "parallelism": f"fsdp{world // (args.ep * args.tp)}" + (f"xep{args.ep}" if args.ep > 1 else "") + (f"xtp{args.tp}" if args.tp > 1 else ""), "collectives": args.comm if world > 1 else "none", "remat_policy": cfg.remat_policy,
                    "optimizer": "adamw fp32 master", "l2": "inputs_larger_than_L2 (16 GB of weights streamed per step)"},
         "tokens_per_sec_per_gpu": value / world, "model_tflops_per_sec_per_gpu": tf_s,
         "mfu_of_nominal_2250": tf_s / NOMINAL_BF16_TFLOPS,

@@ -12,6 +12,10 @@ int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, 
                  long lddk, long lddv, float scale, int window, int* status, cudaStream_t st);
 }
 
+extern "C" int mt_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* slot_ids, const int* lengths, int B,
+                                   int max_len, int Hq, int Hkv, int D, int window, float scale, float soft_cap, int splits, float* part,
+                                   void* out, cudaStream_t st);
+
 int* mt_status_ptr();          // defined in bindings.cpp
 void mt_count_launches(int n); // defined in bindings.cpp
 
@@ -60,9 +64,28 @@ void flash_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::T
   mt_count_launches(3);
 }
 
+// q [B, Hq, D], caches [slots, max_len, Hkv, D] (bf16), slot_ids / lengths int32 [B] (lengths include the new token); out [B, Hq, D].
+void decode_attention(const torch::Tensor& q, const torch::Tensor& k_cache, const torch::Tensor& v_cache, const torch::Tensor& slot_ids,
+                      const torch::Tensor& lengths, torch::Tensor& out, double scale, double soft_cap, int64_t window, int64_t splits) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && q.is_contiguous() && out.is_contiguous() && q.scalar_type() == torch::kBFloat16);
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.is_contiguous() && v_cache.is_contiguous() && k_cache.scalar_type() == torch::kBFloat16 &&
+              v_cache.sizes() == k_cache.sizes() && k_cache.size(3) == q.size(2));
+  TORCH_CHECK(slot_ids.scalar_type() == torch::kInt32 && lengths.scalar_type() == torch::kInt32 && slot_ids.numel() == q.size(0) &&
+              lengths.numel() == q.size(0) && slot_ids.is_contiguous() && lengths.is_contiguous());
+  const int B = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)k_cache.size(2);
+  c10::cuda::CUDAGuard guard(q.device());
+  auto part = torch::empty({(int64_t)B * Hkv * splits * (Hq / Hkv) * (D + 2)}, torch::dtype(torch::kFloat32).device(q.device()));
+  int rc = mt_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), slot_ids.data_ptr<int>(), lengths.data_ptr<int>(), B,
+                               (int)k_cache.size(1), Hq, Hkv, D, (int)window, (float)scale, (float)soft_cap, (int)splits, part.data_ptr<float>(),
+                               out.data_ptr(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "mt_decode_attention failed with code ", rc);
+  mt_count_launches(2);
+}
+
 }  // namespace
 
 void register_attention(pybind11::module_& m) {
+  m.def("decode_attention", &decode_attention);
   m.def("flash_supported", &flash_supported);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);

@@ -58,6 +58,14 @@ class LayerKVCache:
     else:
       buf[rows, pos] = x.to(buf.dtype)
 
+  def _decode_kernel_ok(self, q, S, sinks) -> bool:
+    if not (q.is_cuda and S == 1 and self.quant is None and sinks is None and q.dtype == torch.bfloat16 and self.k.dtype == torch.bfloat16):
+      return False
+    from ..ops import backend
+    D, g = q.shape[3], q.shape[2] // self.k.shape[2]
+    return (backend.use_cuda_kernels(q) and hasattr(backend.ext(), "decode_attention") and D in (64, 128) and self.v.shape[3] == D
+            and g <= 16 and q.shape[2] % self.k.shape[2] == 0)
+
   def _read(self, buf, sbuf, upto):
     x = buf[self.slot_ids, :upto]
     if self.quant:
@@ -70,6 +78,14 @@ class LayerKVCache:
     pos = self.lengths[:, None] + torch.arange(S, device=q.device)[None]           # absolute positions of the new tokens
     self._write(self.k, getattr(self, "ks", None), k, pos)
     self._write(self.v, getattr(self, "vs", None), v, pos)
+    if self._decode_kernel_ok(q, S, sinks):
+      # one new token per sequence: split-KV decode kernel straight on the cache, lengths stay on the device (no host sync)
+      from ..ops import backend
+      out = torch.empty(B, q.shape[2], q.shape[3], dtype=q.dtype, device=q.device)
+      splits = max(1, min(16, 296 // max(1, B * self.k.shape[2])))
+      backend.ext().decode_attention(q[:, 0].contiguous(), self.k, self.v, self.slot_ids.to(torch.int32), (self.lengths + 1).to(torch.int32),
+                                     out, 1.0, float(soft_cap), int(window), splits)
+      return out[:, None]
     upto = int((self.lengths.max() + S).item()) if ctx.mode != "prefill" else int(S + self.lengths.max().item())
     K, V = self._read(self.k, getattr(self, "ks", None), upto), self._read(self.v, getattr(self, "vs", None), upto)
     kv_pos = torch.arange(upto, device=q.device)[None].expand(B, upto)

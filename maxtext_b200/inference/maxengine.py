@@ -52,6 +52,7 @@ class MaxEngine:
     self.max_prefill = int(c.max_prefill_predict_length)
     self.generator = torch.Generator(device=self.device)
     self.generator.manual_seed(int(c.init_weights_seed))
+    self._graphs: dict = {}          # id(state) -> (CUDAGraph, static result tensors) when cuda_graphs is on
 
   # ------------------------------------------------------------------ params
   def load_params(self, path: str | None = None, seed: int | None = None):
@@ -132,7 +133,69 @@ class MaxEngine:
 
   @torch.no_grad()
   def generate(self, state: DecodeState, params=None) -> tuple[DecodeState, ResultTokens]:
-    """One autoregressive step for every slot (inactive slots compute too; their results are flagged invalid)."""
+    """One autoregressive step for every slot (inactive slots compute too; their results are flagged invalid).
+
+    With `cuda_graphs=true` on a GPU the step is captured once per decode state and replayed: a decode step is a few
+    hundred small launches, so replaying one graph removes the launch latency that otherwise dominates it. The state
+    tensors are updated in place (the graph reads and writes fixed addresses); everything data-dependent (lengths, slot
+    ids, sampling) stays on the device."""
+    if self.device.type == "cuda" and bool(getattr(self.config, "cuda_graphs", False)):
+      out = self._generate_graphed(state)
+      if out is not None:
+        return out
+    return self._generate_eager(state)
+
+  def _step_inplace(self, state: DecodeState):
+    """The decode step with every state update written into the existing tensors."""
+    dev = self.device
+    slots = state.tokens.shape[0]
+    ids = torch.arange(slots, device=dev)
+    self._bind(state.caches, ids, state.next_pos.clone())
+    logits = self.model.forward(state.tokens[:, None], state.next_pos[:, None], None, mode="decode", caches=state.caches)[:, -1]
+    tok = self._sample(logits)
+    if state.token_logp is not None:
+      state.token_logp.copy_(inference_utils.log_prob_of(logits, tok))
+    state.tokens.copy_(torch.where(state.active, tok, state.tokens))
+    state.next_pos.add_(state.active.long())
+    state.generated.add_(state.active.long())
+    data = torch.stack([state.tokens, state.active.long(), state.generated], dim=1)
+    state.active.logical_and_(state.next_pos < self.max_len - 1)
+    return data
+
+  def _generate_graphed(self, state: DecodeState):
+    key = id(state)
+    entry = self._graphs.get(key)
+    if entry is None:
+      try:
+        keep = [t.clone() for t in (state.tokens, state.next_pos, state.active, state.generated)]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                       # warm-up: lazy initialisation must happen outside the capture
+          for _ in range(2):
+            self._step_inplace(state)
+        torch.cuda.current_stream().wait_stream(side)
+        for t, k in zip((state.tokens, state.next_pos, state.active, state.generated), keep):
+          t.copy_(k)                                        # the warm-up steps wrote only beyond the cached lengths
+        g = torch.cuda.CUDAGraph()
+        if hasattr(g, "register_generator_state"):
+          g.register_generator_state(self.generator)
+        with torch.cuda.graph(g):
+          data = self._step_inplace(state)
+        for t, k in zip((state.tokens, state.next_pos, state.active, state.generated), keep):
+          t.copy_(k)                                        # capture does not execute, but keep the contract explicit
+        entry = (g, data)
+      except Exception as e:  # pylint: disable=broad-except
+        from ..utils import max_logging
+        max_logging.log(f"decode graph capture failed ({e!r}); running eagerly")
+        entry = False
+      self._graphs[key] = entry
+    if entry is False:
+      return None
+    g, data = entry
+    g.replay()
+    return state, ResultTokens(data.clone(), state.token_logp)
+
+  def _generate_eager(self, state: DecodeState) -> tuple[DecodeState, ResultTokens]:
     dev = self.device
     slots = state.tokens.shape[0]
     ids = torch.arange(slots, device=dev)

@@ -368,9 +368,27 @@ class MLA:
       kv = F.linear(latent, self.wkv_b).view(B, S, self.h, self.nope + self.vd)
       k = torch.cat([kv[..., :self.nope], k_rope.expand(B, S, self.h, self.rope_d)], dim=-1)
       v = kv[..., self.nope:]
+      if c.use_qk_clip and ctx.mode == "train" and not ctx.recompute and ctx.max_logits is not None:
+        ctx.max_logits[(ctx.layer_index, self)] = _max_logit_per_head(q, k, ctx.positions, ctx.segment_ids)
       out = F.attention(q, k.contiguous(), v.contiguous(), ctx.positions, ctx.segment_ids, 1.0, 0.0, 0)
     y = F.linear(out.reshape(B, S, -1), self.o)
     return tp_exit(y, ctx)
+
+
+@torch.no_grad()
+def _max_logit_per_head(q, k, positions, segment_ids, chunk: int = 512) -> torch.Tensor:
+  """Largest causal attention logit of every head over the batch ([H] fp32): what QK-clip compares with its threshold
+  (src/maxtext/layers/attention_mla.py:1330-1341 `record_max_logits`)."""
+  B, S, H, _ = q.shape
+  best = torch.full((H,), -1e30, dtype=torch.float32, device=q.device)
+  kf = k.float()
+  for s0 in range(0, S, chunk):
+    e = min(S, s0 + chunk)
+    logits = torch.einsum("bqhd,bkhd->bhqk", q[:, s0:e].float(), kf[:, :e])
+    m = ref.attention_mask(positions[:, s0:e], positions[:, :e], segment_ids[:, s0:e] if segment_ids is not None else None,
+                           segment_ids[:, :e] if segment_ids is not None else None, True, 0)
+    best = torch.maximum(best, logits.masked_fill(~m, -1e30).amax(dim=(0, 2, 3)))
+  return best
 
 
 # ------------------------------------------------------------------------------------------ dense MLP

@@ -132,6 +132,9 @@ class TrainEngine:
 
     n_units = len(self._units)
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    if c.use_qk_clip:
+      self._max_logits = getattr(self, "_max_logits", None) or {}
+      ctx.max_logits = self._max_logits
     # ---- forward
     self._gather(0, async_op=False)
     self._gather(1)
@@ -367,6 +370,9 @@ class TrainEngine:
     lr = self.schedule(self.step_count)
     opt_metrics = self.optimizer.step(grad_scale, lr, self.step_count + 1, loss=(loss_sum * inv_w), grad_norm=raw_norm)
     self.step_count += 1
+    if c.use_qk_clip and getattr(self, "_max_logits", None):
+      opt_metrics = dict(opt_metrics)
+      opt_metrics["learning/max_attention_logit"] = self._apply_qk_clip()
     if getattr(store, "fused", False):
       store.symm.barrier(0)       # updated shards are final on every rank before the next step reads them over NVLink
     lm_loss = loss_sum * inv_w
@@ -378,6 +384,36 @@ class TrainEngine:
     }
     metrics.update(opt_metrics)
     return metrics
+
+  @torch.no_grad()
+  def _apply_qk_clip(self):
+    """QK-clip (MuonClip; src/maxtext/utils/qk_clip_utils.py:86-136): after the update, every MLA head whose largest
+    attention logit exceeded qk_clip_threshold has its query / key weights shrunk by gamma = tau / s_max: the no-position
+    parts of wq_b and wkv_b by sqrt(gamma) each, the rotary part of wq_b by gamma (the rotary key is shared by all heads)."""
+    c, store = self.config, self.store
+    tau = float(c.qk_clip_threshold)
+    overall = torch.zeros((), device=self.device)
+    for (_, mla), smax in self._max_logits.items():
+      if self.inner_world > 1:
+        dist.all_reduce(smax, op=dist.ReduceOp.MAX, group=self.inner_group)
+      overall = torch.maximum(overall, smax.max())
+      gamma = torch.clamp(tau / (smax + 1e-6), max=1.0)                        # [heads on this rank]
+      rt = torch.sqrt(gamma)
+      q_rows = torch.cat([rt[:, None].expand(-1, mla.nope), gamma[:, None].expand(-1, mla.rope_d)], 1).reshape(-1)
+      kv_rows = torch.cat([rt[:, None].expand(-1, mla.nope), torch.ones_like(rt)[:, None].expand(-1, mla.vd)], 1).reshape(-1)
+      wq = mla.wq_b if mla.query is None else mla.query
+      for p, rows in ((wq, q_rows), (mla.wkv_b, kv_rows)):
+        u = store.unit_of(p)
+        off = u.offsets[u.params.index(p)]
+        lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+        a, b = max(off, lo), min(off + p.pdef.numel, hi)
+        if a < b:
+          n_in = p.pdef.shape[1]
+          idx = torch.arange(a - off, b - off, device=self.device) // n_in          # internal layout [out rows, in]
+          store.shard_view(u, store.master)[a - lo: b - lo].mul_(rows[idx].to(store.master.dtype))
+    store.sync_compute_from_master()
+    self._max_logits.clear()
+    return overall
 
   def _reduce_replicas(self):
     store, mesh = self.store, self.mesh

@@ -114,3 +114,28 @@ def test_packed_attention_autograd_path():
   ro.backward(dout.float())
   assert (out.float() - ro).abs().max() <= 3e-2
   assert (qkv.grad.float() - x.grad).abs().max() <= 4e-2 * max(1.0, x.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,window", [(3, 8, 2, 128, 0), (2, 16, 16, 64, 0), (4, 32, 8, 128, 96), (1, 4, 1, 128, 0)])
+def test_decode_attention_matches_reference(B, Hq, Hkv, D, window):
+  """Split-KV decode kernel on a slot-indexed cache vs the fp32 reference on the gathered rows, ragged lengths."""
+  from maxtext_b200.ops import backend, reference as ref
+  E = backend.ext(required=True)
+  torch.manual_seed(0)
+  slots, max_len = 6, 700
+  kc = (torch.randn(slots, max_len, Hkv, D, device="cuda") * 0.5).bfloat16()
+  vc = (torch.randn(slots, max_len, Hkv, D, device="cuda") * 0.5).bfloat16()
+  q = (torch.randn(B, Hq, D, device="cuda") * 0.3).bfloat16()
+  slot_ids = torch.randperm(slots, device="cuda")[:B].to(torch.int32)
+  lengths = torch.tensor([1, 64, 333, 700][:B] if B <= 4 else None, device="cuda", dtype=torch.int32)
+  out = torch.empty(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+  for splits in (1, 5):
+    E.decode_attention(q, kc, vc, slot_ids, lengths, out, 1.0, 0.0, window, splits)
+    for b in range(B):
+      n = int(lengths[b])
+      K, V = kc[slot_ids[b].long(), :n][None], vc[slot_ids[b].long(), :n][None]
+      qpos = torch.tensor([[n - 1]], device="cuda")
+      kpos = torch.arange(n, device="cuda")[None]
+      m = ref.attention_mask(qpos, kpos, None, None, True, window)
+      want = ref.attention(q[b][None, None], K, V, m, 1.0, 0.0)[0, 0]
+      assert (out[b].float() - want.float()).abs().max() < 2e-2, (b, splits)
