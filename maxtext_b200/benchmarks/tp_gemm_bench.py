@@ -24,6 +24,7 @@ def main():
   ap.add_argument("--cols", type=int, default=8192)
   ap.add_argument("--depth", type=int, default=28672)
   ap.add_argument("--iters", type=int, default=10)
+  ap.add_argument("--mode", default="staged", choices=["staged", "atomic"])
   a = ap.parse_args()
   from maxtext_b200.ops import backend
   from maxtext_b200.ops import functional as F
@@ -35,7 +36,7 @@ def main():
   torch.manual_seed(rank)
   x = [(torch.randn(a.tokens, kl, device=dev) * 0.1).bfloat16() for _ in range(2)]
   w = [(torch.randn(a.cols, kl, device=dev) * 0.1).bfloat16() for _ in range(2)]
-  rt = tp_fused.TPReduceRuntime(dist.group.WORLD, dev, a.tokens, a.cols)
+  rt = tp_fused.TPReduceRuntime(dist.group.WORLD, dev, a.tokens, a.cols, a.mode)
 
   def fused(i):
     return rt.all_reduce_gemm(x[i & 1], w[i & 1], True)
@@ -66,7 +67,7 @@ def main():
 
   t_f, t_n = timeit(fused), timeit(nccl)
   flops = 2.0 * a.tokens * a.cols * kl
-  link_bytes = (world - 1) / world * a.tokens * a.cols * 6
+  link_bytes = (world - 1) / world * a.tokens * a.cols * (4 if a.mode == "staged" else 6)
   peaks = {}
   try:
     peaks = json.load(open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")))
@@ -75,7 +76,7 @@ def main():
   pk = float(peaks.get("bf16_tflops", 1590.0))
   roof_ms = max(flops / (pk * 1e9), link_bytes / 770e9 * 1e3)
   if rank == 0:
-    print(json.dumps({"world": world, "tokens": a.tokens, "n": a.cols, "k_local": kl, "fused_ms": round(t_f, 4), "gemm_plus_nccl_ms": round(t_n, 4),
+    print(json.dumps({"world": world, "mode": a.mode, "tokens": a.tokens, "n": a.cols, "k_local": kl, "fused_ms": round(t_f, 4), "gemm_plus_nccl_ms": round(t_n, 4),
                       "speedup": round(t_n / t_f, 3), "fused_tflops_per_gpu": round(flops / t_f / 1e9, 1), "roofline_ms": round(roof_ms, 4),
                       "fraction_of_roofline": round(roof_ms / t_f, 3), "max_rel_err_vs_nccl": err, "status": E.kernel_status(True)}))
   dist.destroy_process_group()

@@ -16,10 +16,11 @@ int mt_gather_segments(const void* const* peer_shards, void* full, long chunk_by
 int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int64_t lda, int64_t ldc, const void* const* peer_shards, void* full,
                     long chunk_elems, long seg_elems, long b_offset, int world, int* seg_flags, int comm_ctas, int* status, int num_sms,
                     cudaStream_t stream);
-int mt_gemm_rs_encode_maps(void* out_maps, const void* const* bufs, int world, int rows, int N);
+int mt_gemm_rs_encode_maps(void* out_maps, const void* const* bufs, int world, int rows, int N, int bf16);
+int mt_reduce_staged(const void* staged, long chunk_elems, int world, void* out, int ctas, cudaStream_t st);
 int mt_tensor_map_bytes();
 int mt_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const void* dev_maps, int world,
-                    int* status, int num_sms, cudaStream_t stream);
+                    int out_bf16, int* status, int num_sms, cudaStream_t stream);
 int mt_gather_cvt(const float* const* peer_acc, long chunk_elems, int world, void* out, int ctas, cudaStream_t st);
 }
 
@@ -100,14 +101,14 @@ void gemm_ag(const torch::Tensor& a, torch::Tensor& out, const torch::Tensor& pe
 }  // namespace
 
 // Device tensor holding one tensor map per rank over that rank's fp32 accumulation buffer [rows, N] (addresses from `ptrs`).
-torch::Tensor gemm_rs_maps(const std::vector<int64_t>& ptrs, int64_t rows, int64_t N, const torch::Device& device) {
+torch::Tensor gemm_rs_maps(const std::vector<int64_t>& ptrs, int64_t rows, int64_t N, const torch::Device& device, bool bf16) {
   const int world = (int)ptrs.size();
   const int mb = mt_tensor_map_bytes();
   std::vector<const void*> bufs(world);
   for (int r = 0; r < world; ++r) bufs[r] = reinterpret_cast<const void*>(ptrs[r]);
   auto host = torch::empty({world * mb}, torch::dtype(torch::kUInt8).pinned_memory(false));
   TORCH_CHECK(reinterpret_cast<uintptr_t>(host.data_ptr()) % 64 == 0, "tensor map staging buffer is not 64-byte aligned");
-  int rc = mt_gemm_rs_encode_maps(host.data_ptr(), bufs.data(), world, (int)rows, (int)N);
+  int rc = mt_gemm_rs_encode_maps(host.data_ptr(), bufs.data(), world, (int)rows, (int)N, bf16 ? 1 : 0);
   TORCH_CHECK(rc == 0, "mt_gemm_rs_encode_maps failed with code ", rc);
   auto dev = host.to(device);
   TORCH_CHECK(reinterpret_cast<uintptr_t>(dev.data_ptr()) % 64 == 0);
@@ -116,14 +117,14 @@ torch::Tensor gemm_rs_maps(const std::vector<int64_t>& ptrs, int64_t rows, int64
 
 // Partial product a . op(w) reduce-scattered over the group: every rank's fp32 buffer (zeroed beforehand) receives the sum
 // of the rows it owns. tb: w stored [N, K] (y = a w^T); else [K, N].
-void gemm_rs(const torch::Tensor& a, const torch::Tensor& w, bool tb, const torch::Tensor& dev_maps, int64_t world) {
+void gemm_rs(const torch::Tensor& a, const torch::Tensor& w, bool tb, const torch::Tensor& dev_maps, int64_t world, bool out_bf16) {
   TORCH_CHECK(a.is_cuda() && a.dim() == 2 && w.dim() == 2 && a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(a.stride(1) == 1 && w.stride(1) == 1 && a.stride(0) % 8 == 0 && w.stride(0) % 8 == 0);
   const int64_t M = a.size(0), K = a.size(1), N = tb ? w.size(0) : w.size(1);
   TORCH_CHECK((tb ? w.size(1) : w.size(0)) == K && K % 64 == 0 && N % 128 == 0, "gemm_rs: unsupported shape");
   c10::cuda::CUDAGuard guard(a.device());
   int rc = mt_gemm_bf16_rs(a.data_ptr(), w.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), w.stride(0), tb ? 0 : 1, dev_maps.data_ptr(),
-                           (int)world, mt_status_ptr(), sm_count(), cur());
+                           (int)world, out_bf16 ? 1 : 0, mt_status_ptr(), sm_count(), cur());
   TORCH_CHECK(rc == 0, "mt_gemm_bf16_rs failed with code ", rc);
   mt_count_launches(1);
 }
@@ -138,7 +139,18 @@ void gather_cvt(const torch::Tensor& acc_table, int64_t chunk_elems, int64_t wor
   mt_count_launches(1);
 }
 
+// out [chunk] bf16 = sum over the `world` staged copies (consecutive chunks of `staged`), fixed order
+void reduce_staged(const torch::Tensor& staged, int64_t world, torch::Tensor& out) {
+  TORCH_CHECK(staged.is_cuda() && staged.is_contiguous() && out.is_contiguous() && staged.scalar_type() == torch::kBFloat16 &&
+              out.scalar_type() == torch::kBFloat16 && staged.numel() == out.numel() * world);
+  c10::cuda::CUDAGuard guard(out.device());
+  int rc = mt_reduce_staged(staged.data_ptr(), out.numel(), (int)world, out.data_ptr(), sm_count() * 4, cur());
+  TORCH_CHECK(rc == 0, "mt_reduce_staged failed with code ", rc);
+  mt_count_launches(1);
+}
+
 void register_comm(pybind11::module_& m) {
+  m.def("reduce_staged", &reduce_staged);
   m.def("gemm_rs_maps", &gemm_rs_maps);
   m.def("gemm_rs", &gemm_rs);
   m.def("gather_cvt", &gather_cvt);

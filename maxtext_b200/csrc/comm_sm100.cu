@@ -146,9 +146,39 @@ gather_cvt_kernel(const float4* const* __restrict__ peer_acc, long chunk_vec4, i
   }
 }
 
+// out[i] = sum over sources s (in order) of staged[s * chunk + i], fp32 accumulation, bf16 in and out: the owner's half of a
+// reduce-scatter whose partial tiles were stored into `staged` by the peers' GEMM epilogues.
+__global__ void __launch_bounds__(256)
+reduce_staged_kernel(const uint4* __restrict__ staged, long chunk_vec, int world, uint4* __restrict__ out) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < chunk_vec; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < world; ++s) {
+      const uint4 v = staged[(long)s * chunk_vec + i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[i] = o;
+  }
+}
+
 }  // namespace mt
 
 using namespace mt;
+
+extern "C" int mt_reduce_staged(const void* staged, long chunk_elems, int world, void* out, int ctas, cudaStream_t st) {
+  if (chunk_elems % 8) return -1;
+  reduce_staged_kernel<<<ctas, 256, 0, st>>>(reinterpret_cast<const uint4*>(staged), chunk_elems / 8, world, reinterpret_cast<uint4*>(out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int mt_gather_cvt(const float* const* peer_acc, long chunk_elems, int world, void* out, int ctas, cudaStream_t st) {
   if (chunk_elems % 4) return -1;

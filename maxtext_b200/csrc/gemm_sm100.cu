@@ -418,9 +418,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (et == 0) {
             const int col0 = nb * BN + (OUT_F32 ? c * 32 : (c >> 1) * 64);
             if (col0 < p.N && !(empty_tile && p.accumulate)) {
-              if (OUT_F32 && p.r_maps) {
+              if (p.r_maps) {
+                // fused reduce-scatter: fp32 tiles are added into the owner's accumulator, bf16 tiles are stored into the
+                // owner's staging area for this source rank (plain stores; the owner sums the staged copies afterwards)
                 const int owner = (mb * BM) / p.r_rows;
-                tma_reduce_add_2d(p.r_maps + owner, sbuf, col0, mb * BM - owner * p.r_rows);
+                if (OUT_F32) tma_reduce_add_2d(p.r_maps + owner, sbuf, col0, mb * BM - owner * p.r_rows);
+                else tma_store_2d(p.r_maps + owner, sbuf, col0, mb * BM - owner * p.r_rows);
               } else if (OUT_F32 && p.accumulate) {
                 tma_reduce_add_2d(&map_c, sbuf, col0, mb * BM);
               } else {
@@ -633,11 +636,12 @@ extern "C" int mt_gemm_bf16_grouped(int mode, const void* a, const void* b, void
 
 // Tensor maps for the fused reduce-scatter epilogue: entry r covers rank r's fp32 accumulation buffer [rows, N].
 // `out_maps` is host memory (world * sizeof(CUtensorMap) bytes); the caller copies it to the device once.
-extern "C" int mt_gemm_rs_encode_maps(void* out_maps, const void* const* bufs, int world, int rows, int N) {
+extern "C" int mt_gemm_rs_encode_maps(void* out_maps, const void* const* bufs, int world, int rows, int N, int bf16) {
   using namespace mt;
   CUtensorMap* m = reinterpret_cast<CUtensorMap*>(out_maps);
   for (int r = 0; r < world; ++r) {
-    const int e = make_map_2d(&m[r], bufs[r], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rows, N, N, 32, BM);
+    const int e = bf16 ? make_map_2d(&m[r], bufs[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, N, N, 64, BM)
+                       : make_map_2d(&m[r], bufs[r], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rows, N, N, 32, BM);
     if (e) return 100 + e;
   }
   return 0;
@@ -647,8 +651,9 @@ extern "C" int mt_tensor_map_bytes() { return (int)sizeof(CUtensorMap); }
 
 // out_r[M / world, N] (fp32, zeroed by the caller) += rows of a . op(b) that rank r owns, for every rank r of the group:
 // a [M, K] (K-major), b [N, K] (b_mn = 0) or [K, N] (b_mn = 1). dev_maps: device copy of mt_gemm_rs_encode_maps' output.
+// out_bf16 = 1: tiles are stored (not added) as bf16 through maps that point at the owner's staging area for THIS rank.
 extern "C" int mt_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const void* dev_maps,
-                               int world, int* status, int num_sms, cudaStream_t stream) {
+                               int world, int out_bf16, int* status, int num_sms, cudaStream_t stream) {
   using namespace mt;
   if (M % (world * BM) || N % 32) return -10;
   const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
@@ -659,10 +664,16 @@ extern "C" int mt_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K
   else e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK);
   if (e) return 200 + e;
   GemmParams p{};
-  p.M = M; p.N = N; p.K = K; p.accumulate = 1; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.accumulate = out_bf16 ? 0 : 1; p.status = status;
   p.r_maps = reinterpret_cast<const CUtensorMap*>(dev_maps);
   p.r_rows = M / world;
   // map_c is not used on this path; the A map stands in so that the prefetch has a valid descriptor
+  if (out_bf16) {
+    if (BN == 256) return b_mn ? launch<256, false, true, __nv_bfloat16>(ma, mb, ma, p, num_sms, stream)
+                               : launch<256, false, false, __nv_bfloat16>(ma, mb, ma, p, num_sms, stream);
+    return b_mn ? launch<128, false, true, __nv_bfloat16>(ma, mb, ma, p, num_sms, stream)
+                : launch<128, false, false, __nv_bfloat16>(ma, mb, ma, p, num_sms, stream);
+  }
   if (BN == 256) return b_mn ? launch<256, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<256, false, false, float>(ma, mb, ma, p, num_sms, stream);
   return b_mn ? launch<128, false, true, float>(ma, mb, ma, p, num_sms, stream) : launch<128, false, false, float>(ma, mb, ma, p, num_sms, stream);
 }
