@@ -9,10 +9,13 @@ ARGS = ["base_emb_dim=256", "base_num_query_heads=4", "base_num_kv_heads=2", "he
         "vocab_size=512", "max_target_length=160", "max_prefill_predict_length=64", "per_device_batch_size=3", "weight_init=normal"]
 
 
-def _run(cfg, device, steps=12):
+def _run(cfg, device, steps=12, weights=None):
   from maxtext_b200.inference.maxengine import MaxEngine
   eng = MaxEngine(cfg, device=device)
   eng.load_params(seed=3)
+  if weights is not None:              # the initialiser draws from the device's own generator: share one set of weights
+    eng.model.store.master.copy_(weights.to(device))
+    eng.model.store.sync_compute_from_master()
   state = eng.init_decode_state(3)
   g = torch.Generator().manual_seed(0)
   for s, n in enumerate((5, 17, 40)):
@@ -29,13 +32,14 @@ def _run(cfg, device, steps=12):
 def test_gpu_decode_matches_cpu_reference_and_graph_replay():
   from helpers import tiny_config
   cpu_cfg = tiny_config(extra=ARGS + ["dtype=float32", "hardware=cpu"])
-  want, _ = _run(cpu_cfg, "cpu")
+  want, cpu_eng = _run(cpu_cfg, "cpu")
+  w = cpu_eng.model.store.master.clone()
   gpu_cfg = tiny_config(extra=ARGS + ["dtype=bfloat16", "hardware=gpu"])
-  got, eng = _run(gpu_cfg, "cuda")
+  got, eng = _run(gpu_cfg, "cuda", weights=w)
   # bf16 vs fp32 can flip a near-tie; the first tokens of every slot must agree and most of the rest
   assert torch.equal(got[0], want[0])
   assert (got == want).float().mean() > 0.8
   graph_cfg = tiny_config(extra=ARGS + ["dtype=bfloat16", "hardware=gpu", "cuda_graphs=true"])
-  got_g, eng_g = _run(graph_cfg, "cuda")
+  got_g, eng_g = _run(graph_cfg, "cuda", weights=w)
   assert any(v is not False for v in eng_g._graphs.values()), "graph capture fell back to eager"
   assert torch.equal(got_g, got)
