@@ -32,10 +32,13 @@ def main():
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--small", action="store_true", help="one small shape only (profiling)")
   ap.add_argument("--no-cublas", action="store_true")
+  ap.add_argument("--group-m", type=int, default=0, help="tuning: row blocks per tile group of the persistent walk (0 = default)")
   ap.add_argument("--fp8", action="store_true", help="also time the 8-bit (E4M3 x E4M3) path on the forward shapes, quantisation excluded")
   args = ap.parse_args()
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
+  if args.group_m > 0:
+    E.gemm_set_group_m(args.group_m)
   T = args.tokens
   D, F, QKV = 4096, 14336, 6144
   shapes = [("qkv fwd", T, QKV, D, False, True, torch.bfloat16), ("mlp up fwd", T, 2 * F, D, False, True, torch.bfloat16),

@@ -26,6 +26,7 @@ int mt_amax(const void* x, long n, float* amax, int sms, cudaStream_t st);
 int mt_quantize_fp8(const void* x, int R, int C, const float* amax, int fmt, void* q, void* qt, float* dequant, cudaStream_t st);
 int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt, int b_fmt,
                 int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms, cudaStream_t stream);
+int mt_gemm_set_group_m(int v);
 int mt_sumsq_num_partials(long n, int sms);
 int mt_sumsq(const float* x, long n, float* partials, float* out, int sms, cudaStream_t st);
 }
@@ -237,6 +238,7 @@ void register_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
   m.def("gemm", &gemm);
+  m.def("gemm_set_group_m", [](int64_t v) { TORCH_CHECK(mt_gemm_set_group_m((int)v) == 0, "bad group size"); });
   m.def("quantize_fp8", &quantize_fp8);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("kernel_status", &kernel_status);

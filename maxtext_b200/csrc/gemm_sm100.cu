@@ -140,11 +140,14 @@ __device__ __forceinline__ bool wait_segments(const GemmParams& p, long lo, long
   return true;
 }
 
+__device__ int g_group_m = GROUP_M;     // row blocks per tile group; set from the host (mt_gemm_set_group_m) for tuning runs
+
 __device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
-  const int per_group = GROUP_M * n_blocks;
+  const int gm = g_group_m;
+  const int per_group = gm * n_blocks;
   const int g = t / per_group;
-  const int first_m = g * GROUP_M;
-  const int gsz = min(GROUP_M, m_blocks - first_m);
+  const int first_m = g * gm;
+  const int gsz = min(gm, m_blocks - first_m);
   const int r = t - g * per_group;
   mb = first_m + (r % gsz);
   nb = r / gsz;
@@ -701,4 +704,11 @@ extern "C" int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, 
                                 : launch<256, false, false, __nv_bfloat16, true>(ma, mb, mc, p, num_sms, stream);
   return out_f32 ? launch<128, false, false, float, true>(ma, mb, mc, p, num_sms, stream)
                  : launch<128, false, false, __nv_bfloat16, true>(ma, mb, mc, p, num_sms, stream);
+}
+
+
+// Tuning hook: row blocks per tile group of the persistent tile walk (default 16).
+extern "C" int mt_gemm_set_group_m(int v) {
+  if (v < 1 || v > 1024) return -1;
+  return cudaMemcpyToSymbol(mt::g_group_m, &v, sizeof(int)) == cudaSuccess ? 0 : -2;
 }

@@ -32,6 +32,40 @@ class _AllToAllRows(torch.autograd.Function):
     return dx, None, None, None
 
 
+class _AllGatherRows(torch.autograd.Function):
+  """[t, ...] -> [ep * t, ...] (rank-major); the backward reduce-scatters."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    out = x.new_empty((dist.get_world_size(group) * x.shape[0],) + tuple(x.shape[1:]))
+    dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+    return out
+
+  @staticmethod
+  def backward(ctx, g):
+    n = dist.get_world_size(ctx.group)
+    out = g.new_empty((g.shape[0] // n,) + tuple(g.shape[1:]))
+    dist.reduce_scatter_tensor(out, g.contiguous(), group=ctx.group)
+    return out, None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    n = dist.get_world_size(group)
+    out = x.new_empty((x.shape[0] // n,) + tuple(x.shape[1:]))
+    dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+    return out
+
+  @staticmethod
+  def backward(ctx, g):
+    out = g.new_empty((dist.get_world_size(ctx.group) * g.shape[0],) + tuple(g.shape[1:]))
+    dist.all_gather_into_tensor(out, g.contiguous(), group=ctx.group)
+    return out, None
+
+
 class RoutedMoE:
   def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False, style: str = ""):
     """style: "llama4" (raw top-k logits, sigmoid score applied to the expert input, unit combine weights;
@@ -118,9 +152,36 @@ class RoutedMoE:
       y = y + self.bo.leaf()[row_e].to(y.dtype)
     return y
 
+  def _ring_of_experts(self, x2, B, S, ctx):
+    """`use_ring_of_experts` (src/maxtext/layers/moe.py:1700-1716): instead of moving routed rows, every expert shard
+    receives ALL tokens (all-gather over the expert axis), routes them itself, runs only its own experts on the rows that
+    chose them, and the partial outputs are reduce-scattered back. No variable-size exchange, at the price of gathering
+    the activations."""
+    ep, el = ctx.ep_size, self.e_local
+    rank = dist.get_rank(ctx.ep_group)
+    xg = _AllGatherRows.apply(x2, ctx.ep_group) if torch.is_grad_enabled() else _AllGatherRows.forward(F._Dummy(), x2, ctx.ep_group)
+    wts, idx, aux = self.route(xg, B * ep, S)
+    if aux is not None:
+      ctx.aux_losses.append(("moe_lb_loss", aux))
+    mine = (idx // el) == rank
+    idx_l = torch.where(mine, idx - rank * el, torch.full_like(idx, el))      # group `el` collects the rows of other shards
+    wts_l = torch.where(mine, wts, torch.zeros_like(wts))
+    rows, order, sizes = moe_ops.permute(xg, idx_l, el + 1)
+    n_mine = int(sizes[:el].sum().item())
+    y_mine = self.experts_ffn(rows[:n_mine], sizes[:el])
+    y = torch.cat([y_mine, y_mine.new_zeros(rows.shape[0] - n_mine, y_mine.shape[1])], 0)
+    out = moe_ops.unpermute_combine(y, order, wts_l, xg.shape[0], self.k, fp32_sum=self.c.float32_weight_sum).to(x2.dtype)
+    red = _ReduceScatterRows.apply(out, ctx.ep_group) if torch.is_grad_enabled() else _ReduceScatterRows.forward(F._Dummy(), out, ctx.ep_group)
+    return red
+
   def __call__(self, x, ctx):
     B, S, D = x.shape
     x2 = x.reshape(B * S, D)
+    if ctx.ep_size > 1 and self.c.use_ring_of_experts and self.style != "llama4":
+      out = self._ring_of_experts(x2, B, S, ctx)
+      if ctx.tp_size > 1:
+        out = tp_exit(out, ctx)
+      return out.view(B, S, D)
     wts, idx, aux = self.route(x2, B, S)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))

@@ -177,3 +177,12 @@ def test_expert_parallel2_matches_single(tmp_path):
   ref = run_ranks(1, moe + ["per_device_batch_size=4"], str(tmp_path), "moe1")
   got = run_ranks(2, moe + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_expert_parallelism=2"], str(tmp_path), "ep2")
   _close(got["loss"], ref["loss"], 5e-4)
+
+
+def test_ring_of_experts_matches_single(tmp_path):
+  moe = ["model_name=mixtral-8x7b", "override_model_config=true", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=64"]
+  ref = run_ranks(1, moe + ["per_device_batch_size=4"], str(tmp_path), "moe1r")
+  got = run_ranks(2, moe + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_expert_parallelism=2", "use_ring_of_experts=true"],
+                  str(tmp_path), "roe2")
+  _close(got["loss"], ref["loss"], 5e-4)
+  _close(got["grad_norm"], ref["grad_norm"], 5e-3)
