@@ -90,3 +90,33 @@ def test_decode_cli_and_offline_engine_and_microbenchmark():
   res = microbenchmark.run(tiny_config("llama3-8b", ["max_target_length=48", "max_prefill_predict_length=16", "inference_microbenchmark_prefill_lengths=8,16",
                                                     "inference_microbenchmark_loop_iters=1"]), eng)
   assert set(res["prefill"]) == {8, 16} and res["generate"]["tokens_per_s"] > 0
+
+
+def test_serving_loop_batches_concurrent_requests():
+  """Two threads post completions at once; the background loop serves both through the shared decode slots and each gets
+  the tokens a direct batch_inference call produces for its prompt."""
+  import threading
+  from helpers import tiny_config
+  from maxtext_b200.inference.maxengine import MaxEngine
+  from maxtext_b200.inference.maxengine_server import ServingLoop, create_app
+  from maxtext_b200.inference.offline_engine import OfflineEngine
+  from maxtext_b200.input_pipeline.tokenizer import ByteTokenizer
+  cfg = tiny_config(extra=["vocab_size=300", "max_target_length=48", "max_prefill_predict_length=16", "per_device_batch_size=2"])
+  eng = MaxEngine(cfg, device="cpu")
+  eng.load_params(seed=1)
+  prompts = [[5, 6, 7, 8], [9, 10, 11]]
+  want = OfflineEngine(eng, slots=2).batch_inference(prompts, max_new_tokens=6)
+  loop = ServingLoop(cfg, engine=eng, tokenizer=ByteTokenizer()).start()
+  out = [None, None]
+
+  def call(i):
+    out[i] = loop.complete({"prompt_tokens": prompts[i], "max_tokens": 6})
+
+  ts = [threading.Thread(target=call, args=(i,)) for i in range(2)]
+  [t.start() for t in ts]
+  [t.join(60) for t in ts]
+  loop.stop()
+  assert [o["choices"][0]["tokens"] for o in out] == want
+  assert out[0]["usage"]["prompt_tokens"] == 4 and loop.served == 2
+  app = create_app(loop)
+  assert {r.path for r in app.routes} >= {"/v1/health", "/v1/completions"}
