@@ -33,10 +33,13 @@ def main():
   ap.add_argument("--small", action="store_true", help="one small shape only (profiling)")
   ap.add_argument("--no-cublas", action="store_true")
   ap.add_argument("--group-m", type=int, default=0, help="tuning: row blocks per tile group of the persistent walk (0 = default)")
+  ap.add_argument("--raster", type=int, default=-1, help="tuning: -1 heuristic, 0 row groups, 1 column groups")
+  ap.add_argument("--pair", action="store_true", help="also time the CTA-pair (cta_group::2) variant")
   ap.add_argument("--fp8", action="store_true", help="also time the 8-bit (E4M3 x E4M3) path on the forward shapes, quantisation excluded")
   args = ap.parse_args()
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
+  E.gemm_set_raster(args.raster)
   if args.group_m > 0:
     E.gemm_set_group_m(args.group_m)
   T = args.tokens
@@ -66,6 +69,9 @@ def main():
           out.copy_(r)
       ms2 = time_fn(cb, args.iters)
       row.update(cublas_ms=ms2, cublas_tflops=2.0 * M * N * K / ms2 / 1e9, ratio=ms2 / ms)
+    if args.pair and N % 128 == 0:
+      msp = time_fn(lambda i: E.gemm_pair(sets[i & 1][0], sets[i & 1][1], out, ta, tb, False), args.iters)
+      row.update(pair_ms=msp, pair_tflops=2.0 * M * N * K / msp / 1e9)
     if args.fp8 and not ta and tb and odt == torch.bfloat16:
       q = [(E.quantize_fp8(a, 0, True, False), E.quantize_fp8(b, 0, True, False)) for a, b in sets]
       ms8 = time_fn(lambda i: E.gemm_fp8(q[i & 1][0][0], q[i & 1][1][0], out, 0, 0, q[i & 1][0][2], q[i & 1][1][2], False), args.iters)

@@ -27,6 +27,9 @@ int mt_quantize_fp8(const void* x, int R, int C, const float* amax, int fmt, voi
 int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt, int b_fmt,
                 int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms, cudaStream_t stream);
 int mt_gemm_set_group_m(int v);
+int mt_gemm_set_raster(int v);
+int mt_gemm_bf16_pair(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn,
+                      int out_f32, int accumulate, int* status, int num_sms, cudaStream_t stream);
 int mt_sumsq_num_partials(long n, int sms);
 int mt_sumsq(const float* x, long n, float* partials, float* out, int sms, cudaStream_t st);
 }
@@ -127,6 +130,19 @@ void gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out
                     out.stride(0), (int)a_fmt, (int)b_fmt, f32 ? 1 : 0, accumulate ? 1 : 0, sa.data_ptr<float>(), sb.data_ptr<float>(),
                     status_tensor().data_ptr<int>(), num_sms(), cur_stream()),
         "mt_gemm_fp8");
+}
+
+// the CTA-pair (cta_group::2) variant of `gemm`; N must be a multiple of 128
+void gemm_pair(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bool ta, bool tb, bool accumulate) {
+  TORCH_CHECK(gemm_supported(a, b, out, ta, tb), "gemm_pair: unsupported operands");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = ta ? a.size(1) : a.size(0), K = ta ? a.size(0) : a.size(1), N = tb ? b.size(0) : b.size(1);
+  TORCH_CHECK(N % 128 == 0 && M >= 256, "gemm_pair: N must be a multiple of 128 and M at least 256");
+  const bool f32 = out.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(!accumulate || f32, "gemm_pair: accumulate requires an fp32 output");
+  int rc = mt_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), out.stride(0),
+                             ta ? 1 : 0, tb ? 0 : 1, f32 ? 1 : 0, accumulate ? 1 : 0, status_tensor().data_ptr<int>(), num_sms(), cur_stream());
+  check(rc, "mt_gemm_bf16_pair");
 }
 
 int64_t kernel_status(bool reset) {
@@ -238,6 +254,8 @@ void register_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
   m.def("gemm", &gemm);
+  m.def("gemm_pair", &gemm_pair);
+  m.def("gemm_set_raster", [](int64_t v) { mt_gemm_set_raster((int)v); });
   m.def("gemm_set_group_m", [](int64_t v) { TORCH_CHECK(mt_gemm_set_group_m((int)v) == 0, "bad group size"); });
   m.def("quantize_fp8", &quantize_fp8);
   m.def("gemm_fp8", &gemm_fp8);

@@ -76,6 +76,7 @@ struct GemmParams {
   int r_rows;
   // 8-bit operands (FP8 template flag): formats per operand (0 = E4M3, 1 = E5M2) and the de-quantisation factors, read from
   // device memory so that scales derived from a running amax never visit the host. out = acc * (*q_scale_a) * (*q_scale_b).
+  int raster_n;          // tile walk: 0 = groups of row blocks (A slice stays in L2, B streams), 1 = groups of column blocks
   int q_fmt_a, q_fmt_b;
   const float* q_scale_a;
   const float* q_scale_b;
@@ -142,7 +143,11 @@ __device__ __forceinline__ bool wait_segments(const GemmParams& p, long lo, long
 
 __device__ int g_group_m = GROUP_M;     // row blocks per tile group; set from the host (mt_gemm_set_group_m) for tuning runs
 
-__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb) {
+__device__ __forceinline__ void tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb, int raster_n = 0) {
+  if (raster_n) {        // the same walk with the roles of the two dimensions exchanged
+    tile_coords(t, n_blocks, m_blocks, nb, mb, 0);
+    return;
+  }
   const int gm = g_group_m;
   const int per_group = gm * n_blocks;
   const int g = t / per_group;
@@ -269,7 +274,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
         int mb, nb;
-        tile_coords(t, m_blocks, n_blocks, mb, nb);
+        tile_coords(t, m_blocks, n_blocks, mb, nb, p.raster_n);
         if (p.g_seg_flags) {
           const long n1 = (long)(nb + 1) * BN < p.N ? (long)(nb + 1) * BN : p.N;
           if (!wait_segments(p, p.g_b_offset + (long)nb * BN * p.K, p.g_b_offset + n1 * p.K, abort_flag)) { ok = false; break; }
@@ -316,7 +321,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int tile_kb = num_kb;
         if (p.x_mode == 3) {
           int mb, nb;
-          tile_coords(t, m_blocks, n_blocks, mb, nb);
+          tile_coords(t, m_blocks, n_blocks, mb, nb, p.raster_n);
           tile_kb = tile_info(p, mb, nb, BN, num_kb).num_kb;
         }
         for (int kb = 0; kb < tile_kb; ++kb) {
@@ -356,7 +361,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     for (int t = blockIdx.x; t < num_tiles && ok; t += cta_stride) {
       int mb, nb;
-      tile_coords(t, m_blocks, n_blocks, mb, nb);
+      tile_coords(t, m_blocks, n_blocks, mb, nb, p.raster_n);
       const bool empty_tile = p.x_mode == 3 && tile_info(p, mb, nb, BN, num_kb).num_kb == 0;   // nothing was accumulated
       // one thread waits, the verdict is shared so that all 128 threads leave the loop together
       if (et == 0) *epi_ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE) ? 1 : 0;
@@ -487,6 +492,15 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
+// Which operand should stay resident in L2 while the other streams? Groups of 16 row blocks (2048 rows) re-read B once per
+// group: M / 2048 times N * K elements; groups of 16 column blocks (4096 columns) re-read A N / 4096 times M * K elements.
+static int g_raster_override = -1;
+static int pick_raster(int M, int N) {
+  if (g_raster_override >= 0) return g_raster_override;
+  const double by_rows = (double)((M + 2047) / 2048) * N, by_cols = (double)((N + 4095) / 4096) * M;
+  return by_cols < by_rows ? 1 : 0;
+}
+
 template <int BN, bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, GemmParams p, int num_sms, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
@@ -526,6 +540,7 @@ extern "C" int mt_gemm_bf16(const void* a, const void* b, void* c, int M, int N,
   if (e) return 300 + e;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.accumulate = accumulate; p.status = status;
+  p.raster_n = pick_raster(M, N);
 #define MT_DISPATCH(BN_)                                                                                             \
   do {                                                                                                               \
     if (!a_mn && !b_mn) return out_f32 ? launch<BN_, false, false, float>(ma, mb, mc, p, num_sms, stream)            \
@@ -708,7 +723,317 @@ extern "C" int mt_gemm_fp8(const void* a, const void* b, void* c, int M, int N, 
 
 
 // Tuning hook: row blocks per tile group of the persistent tile walk (default 16).
+extern "C" int mt_gemm_set_raster(int v) {     // tuning hook: -1 = heuristic, 0 = row groups, 1 = column groups
+  mt::g_raster_override = v;
+  return 0;
+}
+
 extern "C" int mt_gemm_set_group_m(int v) {
   if (v < 1 || v > 1024) return -1;
   return cudaMemcpyToSymbol(mt::g_group_m, &v, sizeof(int)) == cudaSuccess ? 0 : -2;
+}
+
+// ================================================================================================ CTA-pair variant
+// Same pipeline with cta_group::2: two CTAs of a cluster (consecutive block ids, two SMs) compute one 256 x 256 output tile.
+// Each CTA loads its own 128 rows of A and only HALF of the B tile (128 of the 256 columns); the leader CTA's single MMA thread
+// issues tcgen05.mma.cta_group::2 instructions that read both CTAs' shared memory and write 128 accumulator rows into each
+// CTA's tensor memory. Per output tile that halves the B traffic from L2 into shared memory, and with 32 KB per stage the
+// ring is six stages deep. Barrier protocol:
+//   full[s]   leader only: armed by the leader's producer with the bytes of BOTH CTAs; both producers' TMA loads complete on it
+//   empty[s]  in each CTA: the leader's MMA thread commits to both after the MMAs that read stage s have finished
+//   tfull[a]  in each CTA: committed to both when a tile's accumulation is complete
+//   tempty[a] leader only, count 2: one epilogue thread per CTA arrives when its accumulator half has been read
+// Every wait is bounded exactly as in the single-CTA kernel; the two cluster-wide barriers (start, end) are reached by both
+// CTAs on every path.
+namespace mt {
+
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BN = 256;               // columns of the pair's tile; each CTA stages PAIR_BN / 2 of them
+constexpr int PAIR_A_BYTES = BM * BK * 2;
+constexpr int PAIR_B_BYTES = (PAIR_BN / 2) * BK * 2;
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_EPI_BYTES = 2 * BM * 128;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_EPI_BYTES + 256 + 1024;
+
+__device__ __forceinline__ void pair_tile_coords(int t, int m_blocks, int n_blocks, int& mb, int& nb, int raster_n = 0) {
+  if (raster_n) {
+    pair_tile_coords(t, n_blocks, m_blocks, nb, mb, 0);
+    return;
+  }
+  constexpr int GM = 8;                    // 8 x 256 rows (or columns) per group
+  const int per_group = GM * n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * GM;
+  const int gsz = min(GM, m_blocks - first_m);
+  const int r = t - g * per_group;
+  mb = first_m + (r % gsz);
+  nb = r / gsz;
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_c, GemmParams p) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int BN = PAIR_BN;
+  constexpr int BNH = PAIR_BN / 2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a0 = smem_base;
+  const uint32_t smem_b0 = smem_base + STAGES * PAIR_A_BYTES;
+  const uint32_t smem_epi = smem_base + STAGES * PAIR_STAGE_BYTES;
+  const uint32_t bar_base = smem_epi + PAIR_EPI_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t abort_slot = tmem_slot + 8;
+  uint8_t* gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen_base + (tmem_slot - smem_base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen_base + (abort_slot - smem_base));
+  volatile int* epi_ok = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const int pair = (int)blockIdx.x >> 1;
+  const int pair_stride = (int)gridDim.x >> 1;
+  const int m_blocks = (p.M + 2 * BM - 1) / (2 * BM);
+  const int n_blocks = (p.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 2);
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {                                   // the same warp in both CTAs, the same destination slot
+    tmem_alloc_2cta(tmem_slot, 2 * BN);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one thread per CTA)
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += pair_stride) {
+        int mb, nb;
+        pair_tile_coords(t, m_blocks, n_blocks, mb, nb, p.raster_n);
+        const int m0 = mb * 2 * BM + (int)rank * BM;          // this CTA's rows of the pair tile
+        const int n0 = nb * BN + (int)rank * BNH;             // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(s), phase ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * PAIR_STAGE_BYTES);
+          const uint32_t fb = mapa_shared(full_bar(s), 0);    // the leader's barrier counts both CTAs' bytes
+          const uint32_t sa = smem_a0 + s * PAIR_A_BYTES;
+          const uint32_t sb = smem_b0 + s * PAIR_B_BYTES;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &map_a, fb, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, fb, m0 + j * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &map_b, fb, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, fb, n0 + j * 64, kb * BK);
+          }
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one thread of the leader CTA)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      constexpr uint32_t A_LBO = A_MN ? 8192 : 16, B_LBO = B_MN ? 8192 : 16;
+      constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32, B_KSTEP = B_MN ? 2048 : 32;
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += pair_stride) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(s), phase, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_a0 + s * PAIR_A_BYTES, A_LBO, 1024);
+          const uint64_t db = make_smem_desc(smem_b0 + s * PAIR_B_BYTES, B_LBO, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_f16_ss_2cta(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                             (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_2cta(mapa_shared(empty_bar(s), 0));      // frees the stage in both CTAs
+          umma_commit_2cta(mapa_shared(empty_bar(s), 1));
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_2cta(mapa_shared(tfull_bar(acc), 0));       // accumulator complete, both halves
+        umma_commit_2cta(mapa_shared(tfull_bar(acc), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (128 threads per CTA, own accumulator half)
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int et = threadIdx.x - 64;
+    constexpr bool OUT_F32 = sizeof(OutT) == 4;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int buf = 0;
+    bool ok = true;
+    const uint32_t leader_tempty0 = mapa_shared(tempty_bar(0), 0), leader_tempty1 = mapa_shared(tempty_bar(1), 0);
+    for (int t = pair; t < num_tiles && ok; t += pair_stride) {
+      int mb, nb;
+      pair_tile_coords(t, m_blocks, n_blocks, mb, nb, p.raster_n);
+      const int m0 = mb * 2 * BM + (int)rank * BM;
+      if (et == 0) *epi_ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, ST_TIMEOUT_EPILOGUE) ? 1 : 0;
+      named_bar_sync(3, EPI_THREADS);
+      if (*epi_ok == 0) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (c == BN / 32 - 1) {
+          tc_fence_before();
+          named_bar_sync(4, EPI_THREADS);                       // all 128 threads have read their rows
+          if (et == 0) mbar_arrive_cluster(acc == 0 ? leader_tempty0 : leader_tempty1);
+        }
+        const bool new_store = OUT_F32 ? true : ((c & 1) == 0);
+        if (new_store) {
+          if (et == 0) tma_wait_group_read<1>();
+          named_bar_sync(1, EPI_THREADS);
+        }
+        const uint32_t sbuf = smem_epi + buf * (BM * 128);
+        if (OUT_F32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = sbuf + row * 128 + ((j ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]),
+                         "r"(r[4 * j + 3])
+                         : "memory");
+          }
+        } else {
+          const int half = c & 1;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+              pk[e] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            const int chunk = half * 4 + j;
+            const uint32_t dst = sbuf + row * 128 + ((chunk ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                         : "memory");
+          }
+        }
+        const bool do_store = OUT_F32 ? true : ((c & 1) == 1);
+        if (do_store) {
+          fence_proxy_async_smem();
+          named_bar_sync(2, EPI_THREADS);
+          if (et == 0) {
+            const int col0 = nb * BN + (OUT_F32 ? c * 32 : (c >> 1) * 64);
+            if (col0 < p.N && m0 < p.M) {
+              if (OUT_F32 && p.accumulate) tma_reduce_add_2d(&map_c, sbuf, col0, m0);
+              else tma_store_2d(&map_c, sbuf, col0, m0);
+            }
+            tma_commit_group();
+          }
+          buf ^= 1;
+        }
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (et == 0) tma_wait_group<0>();
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                  // the peer may still read this CTA's shared memory / signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, 2 * BN);
+  }
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, GemmParams p, int num_sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + PAIR_BN - 1) / PAIR_BN);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, NUM_THREADS, PAIR_SMEM_BYTES, stream>>>(ma, mb, mc, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace mt
+
+// Same contract as mt_gemm_bf16, computed by CTA pairs (cta_group::2). N must be a multiple of 128 so that every CTA's half
+// tile starts inside the matrix.
+extern "C" int mt_gemm_bf16_pair(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                                 int a_mn, int b_mn, int out_f32, int accumulate, int* status, int num_sms, cudaStream_t stream) {
+  using namespace mt;
+  if ((accumulate && !out_f32) || N % 128) return -10;
+  CUtensorMap ma, mb, mc;
+  int e;
+  if (!a_mn) e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BK, BM);
+  else e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, 64, BK);
+  if (e) return 100 + e;
+  if (!b_mn) e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BK, PAIR_BN / 2);
+  else e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, 64, BK);
+  if (e) return 200 + e;
+  if (out_f32) e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, BM);
+  else e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
+  if (e) return 300 + e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = accumulate; p.status = status;
+  p.raster_n = pick_raster(M, N);
+  if (!a_mn && !b_mn) return out_f32 ? launch_pair<false, false, float>(ma, mb, mc, p, num_sms, stream)
+                                     : launch_pair<false, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+  if (!a_mn && b_mn) return out_f32 ? launch_pair<false, true, float>(ma, mb, mc, p, num_sms, stream)
+                                    : launch_pair<false, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+  if (a_mn && b_mn) return out_f32 ? launch_pair<true, true, float>(ma, mb, mc, p, num_sms, stream)
+                                   : launch_pair<true, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+  return out_f32 ? launch_pair<true, false, float>(ma, mb, mc, p, num_sms, stream)
+                 : launch_pair<true, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
 }

@@ -11,7 +11,7 @@ def _ext():
   return backend.ext(required=True)
 
 
-def _run(M, N, K, ta, tb, out_dtype, accumulate=False, seed=0):
+def _run(M, N, K, ta, tb, out_dtype, accumulate=False, seed=0, pair=False):
   E = _ext()
   g = torch.Generator(device="cuda").manual_seed(seed)
   a = torch.randn((K, M) if ta else (M, K), device="cuda", generator=g).bfloat16()
@@ -23,7 +23,7 @@ def _run(M, N, K, ta, tb, out_dtype, accumulate=False, seed=0):
   else:
     out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
   assert E.gemm_supported(a, b, out, ta, tb)
-  E.gemm(a, b, out, ta, tb, accumulate)
+  (E.gemm_pair if pair else E.gemm)(a, b, out, ta, tb, accumulate)
   torch.cuda.synchronize()
   assert E.kernel_status(True) == 0, "a bounded wait inside the GEMM kernel timed out"
   err = (out.float() - ref).abs().max().item()
@@ -70,3 +70,23 @@ def test_gemm_strided_views():
   assert E.kernel_status(True) == 0
   ref = a.float() @ w.float().t()
   assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+
+
+def test_gemm_pair_smallest_first():
+  # CTA-pair (cta_group::2) variant: one 256 x 256 tile, one k-block
+  _run(256, 256, 64, False, True, torch.bfloat16, pair=True)
+
+
+@pytest.mark.parametrize("ta,tb,out_dtype", [(False, True, torch.bfloat16), (False, False, torch.bfloat16), (True, False, torch.float32),
+                                             (False, True, torch.float32)])
+def test_gemm_pair_layouts(ta, tb, out_dtype):
+  _run(512, 768, 320, ta, tb, out_dtype, pair=True)
+
+
+@pytest.mark.parametrize("M,N,K", [(384, 384, 192), (1000, 640, 72), (4096, 4096, 1024), (8192, 1536, 4096)])
+def test_gemm_pair_ragged_and_large(M, N, K):
+  _run(M, N, K, False, True, torch.bfloat16, pair=True)
+
+
+def test_gemm_pair_accumulate_fp32():
+  _run(512, 512, 256, True, False, torch.float32, accumulate=True, pair=True)
