@@ -84,12 +84,22 @@ bool gemm_supported(const torch::Tensor& a, const torch::Tensor& b, const torch:
   return M >= 128 && N >= 128 && K >= 64 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0;
 }
 
+// CTA-pair (cta_group::2) kernel for shapes it covers: measured 3-10 % faster than the single-CTA kernel under sustained load
+bool g_use_pair = true;
+
 void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bool ta, bool tb, bool accumulate) {
   TORCH_CHECK(gemm_supported(a, b, out, ta, tb), "gemm: unsupported operands");
   c10::cuda::CUDAGuard guard(a.device());
   const int64_t M = ta ? a.size(1) : a.size(0), K = ta ? a.size(0) : a.size(1), N = tb ? b.size(0) : b.size(1);
   const bool f32 = out.scalar_type() == torch::kFloat32;
   TORCH_CHECK(!accumulate || f32, "gemm: accumulate requires an fp32 output");
+  if (g_use_pair && N % 256 == 0 && M >= 512) {
+    int rc = mt_gemm_bf16_pair(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), out.stride(0),
+                               ta ? 1 : 0, tb ? 0 : 1, f32 ? 1 : 0, accumulate ? 1 : 0, status_tensor().data_ptr<int>(), num_sms(),
+                               cur_stream());
+    check(rc, "mt_gemm_bf16_pair");
+    return;
+  }
   int rc = mt_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0), out.stride(0),
                         ta ? 1 : 0, tb ? 0 : 1, f32 ? 1 : 0, accumulate ? 1 : 0, status_tensor().data_ptr<int>(), num_sms(), cur_stream());
   check(rc, "mt_gemm_bf16");
@@ -255,6 +265,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
   m.def("gemm", &gemm);
   m.def("gemm_pair", &gemm_pair);
+  m.def("gemm_use_pair", [](bool v) { g_use_pair = v; });
   m.def("gemm_set_raster", [](int64_t v) { mt_gemm_set_raster((int)v); });
   m.def("gemm_set_group_m", [](int64_t v) { TORCH_CHECK(mt_gemm_set_group_m((int)v) == 0, "bad group size"); });
   m.def("quantize_fp8", &quantize_fp8);
