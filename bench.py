@@ -107,6 +107,7 @@ def main():
   ap.add_argument("--pdbs", type=float, default=2.0)
   ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is then not the headline config)")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--trace", default="", help="write a chrome trace of one extra (untimed) step to this path")
   ap.add_argument("--ep", type=int, default=1, help="expert-parallel degree (secondary benchmarks; the headline uses fsdp only)")
   ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (secondary benchmarks)")
   ap.add_argument("--quantization", default="", help="'' (headline: bf16) or fp8: linear layers on the 8-bit tensor-core path (a different configuration)")
@@ -197,6 +198,16 @@ def main():
     e2e = {"value": tokens_total / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
            "ms_per_step": 1e3 * dt / args.steps}
   status = E.kernel_status(True)
+
+  if args.trace:
+    # one extra, untimed step under the PyTorch profiler: a per-stream kernel timeline (chrome trace) for overlap analysis
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+      eng.train_step(batch)
+      torch.cuda.synchronize()
+    if rank == 0:
+      prof.export_chrome_trace(args.trace)
 
   if rank == 0:
     gb = cfg.global_batch_size_to_train_on

@@ -11,6 +11,8 @@ int mt_comm_wait(const int* my_flags, int slot, int world, int epoch, int* statu
 int mt_rs_num_partials(long n, int ctas);
 int mt_rs_sumsq(const float* const* peer, long offset, long n, float* dst, int accumulate, float scale, int world, float* partials,
                 float* sumsq_out, int ctas, cudaStream_t st);
+int mt_rs_sumsq_mc(const float* mc, long offset, long n, float* dst, int accumulate, float scale, float* partials, float* sumsq_out, int ctas,
+                   cudaStream_t st);
 int mt_gather_segments(const void* const* peer_shards, void* full, long chunk_bytes, long seg_bytes, int world, int* seg_flags, int ctas,
                        cudaStream_t st);
 int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int64_t lda, int64_t ldc, const void* const* peer_shards, void* full,
@@ -68,6 +70,19 @@ void rs_sumsq(const torch::Tensor& peer_bufs, int64_t offset, int64_t n, torch::
   TORCH_CHECK(mt_rs_sumsq(reinterpret_cast<const float* const*>(peer_bufs.data_ptr<int64_t>()), offset, n, dst.data_ptr<float>(),
                           accumulate ? 1 : 0, (float)scale, (int)world, partials.data_ptr<float>(),
                           sumsq_out ? sumsq_out->data_ptr<float>() : nullptr, (int)ctas, cur()) == 0, "mt_rs_sumsq failed");
+  mt_count_launches(sumsq_out ? 2 : 1);
+}
+
+// reduce-scatter through the switch: mc_ptr is the multicast address of the symmetric gradient buffer
+void rs_sumsq_mc(int64_t mc_ptr, int64_t offset, int64_t n, torch::Tensor& dst, bool accumulate, double scale,
+                 const c10::optional<torch::Tensor>& sumsq_out, int64_t ctas) {
+  TORCH_CHECK(mc_ptr != 0 && dst.is_cuda() && dst.scalar_type() == torch::kFloat32 && dst.is_contiguous() && dst.numel() >= n);
+  c10::cuda::CUDAGuard g(dst.device());
+  const int parts = mt_rs_num_partials(n, (int)ctas);
+  auto partials = torch::empty({parts}, dst.options());
+  TORCH_CHECK(mt_rs_sumsq_mc(reinterpret_cast<const float*>(mc_ptr), offset, n, dst.data_ptr<float>(), accumulate ? 1 : 0, (float)scale,
+                             partials.data_ptr<float>(), sumsq_out ? sumsq_out->data_ptr<float>() : nullptr, (int)ctas, cur()) == 0,
+              "mt_rs_sumsq_mc failed");
   mt_count_launches(sumsq_out ? 2 : 1);
 }
 
@@ -151,6 +166,7 @@ void reduce_staged(const torch::Tensor& staged, int64_t world, torch::Tensor& ou
 
 void register_comm(pybind11::module_& m) {
   m.def("reduce_staged", &reduce_staged);
+  m.def("rs_sumsq_mc", &rs_sumsq_mc);
   m.def("gemm_rs_maps", &gemm_rs_maps);
   m.def("gemm_rs", &gemm_rs);
   m.def("gather_cvt", &gather_cvt);

@@ -96,6 +96,34 @@ rs_sumsq_kernel(const float* const* __restrict__ peer, long offset, long n, floa
   if (threadIdx.x == 0 && partials) partials[blockIdx.x] = t;
 }
 
+// The same reduce-scatter with the sum done inside the NVSwitch: `mc` is the multicast address of the symmetric gradient
+// buffer, and one multimem.ld_reduce returns the element-wise sum of every rank's copy, so each element costs this SM one
+// load instead of `world` loads (and the reduction traffic never enters the GPU).
+__global__ void __launch_bounds__(RS_THREADS)
+rs_sumsq_mc_kernel(const float* __restrict__ mc, long offset, long n, float* __restrict__ dst, int accumulate, float scale,
+                   float* __restrict__ partials) {
+  __shared__ float sh[32];
+  float acc = 0.f;
+  const long n4 = n / 4;
+  const float* base = mc + offset;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    float4 s;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w)
+                 : "l"(base + 4 * i)
+                 : "memory");
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    if (accumulate) {
+      const float4 o = reinterpret_cast<const float4*>(dst)[i];
+      s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+    }
+    reinterpret_cast<float4*>(dst)[i] = s;
+    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  const float t = rs_block_sum(acc, sh);
+  if (threadIdx.x == 0 && partials) partials[blockIdx.x] = t;
+}
+
 __global__ void __launch_bounds__(RS_THREADS) rs_stage2_kernel(const float* __restrict__ partials, int nparts, float* __restrict__ out) {
   __shared__ float sh[32];
   float acc = 0.f;
@@ -212,6 +240,17 @@ extern "C" int mt_rs_sumsq(const float* const* peer, long offset, long n, float*
   if (n == 0) return 0;
   const int parts = mt_rs_num_partials(n, ctas);
   rs_sumsq_kernel<<<parts, RS_THREADS, 0, st>>>(peer, offset, n, dst, accumulate, scale, world, partials);
+  if (sumsq_out && partials) rs_stage2_kernel<<<1, RS_THREADS, 0, st>>>(partials, parts, sumsq_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// mc: multicast (NVLS) address of the symmetric buffer; otherwise as mt_rs_sumsq.
+extern "C" int mt_rs_sumsq_mc(const float* mc, long offset, long n, float* dst, int accumulate, float scale, float* partials, float* sumsq_out,
+                              int ctas, cudaStream_t st) {
+  if (n % 4 || offset % 4 || !mc) return -1;
+  if (n == 0) return 0;
+  const int parts = mt_rs_num_partials(n, ctas);
+  rs_sumsq_mc_kernel<<<parts, RS_THREADS, 0, st>>>(mc, offset, n, dst, accumulate, scale, partials);
   if (sumsq_out && partials) rs_stage2_kernel<<<1, RS_THREADS, 0, st>>>(partials, parts, sumsq_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -113,6 +113,22 @@ class FusedParam:
   def data(self):
     return self._span("data")
 
+  def fusable(self) -> bool:
+    """Do the parts sit back to back in their unit? Answered from the static layout, so that asking does not read `.data`
+    (reading it would trigger the stand-alone all-gather of a unit whose gather is meant to ride inside this GEMM)."""
+    f = getattr(self, "_fusable", None)
+    if f is None:
+      u = self.parts[0].unit
+      if u is None:
+        return self.data is not None
+      if any(p.unit is not u for p in self.parts):
+        f = False
+      else:
+        offs = [u.offsets[u.params.index(p)] for p in self.parts]
+        f = all(offs[i + 1] == offs[i] + self.parts[i].pdef.numel for i in range(len(offs) - 1))
+      self._fusable = f
+    return f
+
   def pending_unit(self):
     return self.parts[0].pending_unit()
 
@@ -234,8 +250,8 @@ class Attention:
   def _project(self, x, ctx, tp_rt=None):
     B, S, _ = x.shape
     hq, hkv, dh = self.hq_l, self.hkv_l, self.dh
-    fused = self.qkv.data if (self.qkv is not None and self.bq is None) else None
-    if fused is not None:
+    fused = self.qkv is not None and self.bq is None and self.qkv.fusable()
+    if fused:
       saved = ctx.reuse("qkv_proj")
       qkv = F.linear(x, self.qkv, saved_out=saved, tp_reduce_dx=tp_rt)
       if ctx.wants("qkv_proj"):
@@ -250,7 +266,7 @@ class Attention:
     B, S, _ = x.shape
     # tensor parallelism: with the fused runtime the two all-reduces of this block run inside GEMM epilogues
     tp_rt = tp_fused.runtime_for(ctx, x, self.d) if ctx.tp_size > 1 else None
-    fuse_in = tp_rt is not None and self.qkv is not None and self.bq is None and self.qkv.data is not None
+    fuse_in = tp_rt is not None and self.qkv is not None and self.bq is None and self.qkv.fusable()
     if not fuse_in:
       x = tp_enter(x, ctx)
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
@@ -411,11 +427,11 @@ class MLP:
 
   def __call__(self, x, ctx):
     tp_rt = tp_fused.runtime_for(ctx, x, x.shape[-1]) if ctx.tp_size > 1 else None
-    fuse_in = tp_rt is not None and self.gated and self.wi is not None and self.wi.data is not None
+    fuse_in = tp_rt is not None and self.gated and self.wi is not None and self.wi.fusable()
     if not fuse_in:
       x = tp_enter(x, ctx)
     if self.gated:
-      if self.wi is not None and self.wi.data is not None:
+      if self.wi is not None and self.wi.fusable():
         gu = ctx.keep("mlpwi", F.linear(x, self.wi, ctx.reuse("mlpwi"), tp_reduce_dx=tp_rt if fuse_in else None))
       else:
         g = ctx.keep("mlpwi_0", F.linear(x, self.wi_0, ctx.reuse("mlpwi_0")))

@@ -37,9 +37,10 @@ def available() -> bool:
 class SymmTensor:
   """A local tensor plus the device addresses of the same allocation on every rank of the group."""
 
-  def __init__(self, tensor: torch.Tensor, ptrs: list[int]):
+  def __init__(self, tensor: torch.Tensor, ptrs: list[int], mc_ptr: int = 0):
     self.tensor = tensor
     self.ptrs = list(ptrs)
+    self.mc_ptr = int(mc_ptr)          # multicast (NVLS) address of the allocation, 0 when the platform has none
     self.table = torch.tensor(self.ptrs, dtype=torch.int64, device=tensor.device)
 
   def table_at(self, elem_offset: int) -> torch.Tensor:
@@ -77,7 +78,14 @@ class SymmGroup:
     off = int(getattr(hdl, "offset", 0) or 0)
     ptrs = [p + off for p in ptrs] if off and ptrs[self.rank] + off == t.data_ptr() else ptrs
     assert ptrs[self.rank] == t.data_ptr(), "symmetric allocation does not start at the local tensor"
-    return SymmTensor(t, ptrs)
+    mc = 0
+    try:
+      mc = int(hdl.multicast_ptr or 0)
+      if mc and off:
+        mc += off
+    except Exception:  # pylint: disable=broad-except
+      mc = 0
+    return SymmTensor(t, ptrs, mc)
 
   # ---- epoch flags (stream ordered)
   def signal(self, slot: int) -> int:
