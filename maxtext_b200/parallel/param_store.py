@@ -310,7 +310,8 @@ class ParamStore:
     self.exp_avg_sq = None
     # process groups (collective creation, deterministic order)
     for u in self.units.values():
-      u.group = mesh.group(u.fsdp_axes) if u.group_size > 1 else None
+      # planning runs build the store on the meta device for worlds that are not attached: no process groups there
+      u.group = mesh.group(u.fsdp_axes) if (u.group_size > 1 and self.device.type != "meta") else None
     self._pool: list[torch.Tensor] = []
     self._grad_pool: list[torch.Tensor] = []
     self._rs_inflight: list = []

@@ -41,3 +41,16 @@ def test_estimator_prefers_less_recompute_when_it_fits():
   assert rows and rows[0]["remat_policy"] == "minimal"
   full = [r for r in rows if r["remat_policy"] == "full"][0]
   assert full["per_device_batch_size"] >= rows[0]["per_device_batch_size"]
+
+
+def test_every_recipe_resolves_and_plans():
+  """Each named recipe parses into a valid configuration for its GPU count and yields a plan; the ones meant for one
+  node fit 180 GB per GPU."""
+  from maxtext_b200.benchmarks import benchmark_runner, recipes
+  for r in recipes.RECIPES.values():
+    cfg = pyconfig.initialize(["t", BASE_YML] + r.overrides() + ["log_config=false"], num_devices=r.gpus)
+    p = train_compile.plan(cfg, r.gpus)
+    assert p["world"] == r.gpus and p["parameters_total"] > 1e9, r.name
+    assert p["fits"], (r.name, p["memory_total_gb"])
+    cmd = benchmark_runner.command(r)
+    assert ("torch.distributed.run" in cmd) == (r.gpus > 1)
