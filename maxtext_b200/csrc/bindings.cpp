@@ -30,6 +30,8 @@ int mt_gemm_set_group_m(int v);
 int mt_gemm_set_raster(int v);
 int mt_gemm_bf16_pair(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn,
                       int out_f32, int accumulate, int* status, int num_sms, cudaStream_t stream);
+int mt_gemm_fp8_pair(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt, int b_fmt,
+                     int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms, cudaStream_t stream);
 int mt_sumsq_num_partials(long n, int sms);
 int mt_sumsq(const float* x, long n, float* partials, float* out, int sms, cudaStream_t st);
 }
@@ -107,8 +109,19 @@ void gemm(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out, bo
 
 // x [R, C] bf16 -> (q [R, C] uint8 or None, qt [C, R] uint8 or None, dequant scale [1]); fmt 0 = E4M3, 1 = E5M2. Current scaling:
 // the scale comes from this tensor's own absolute maximum, computed on the device.
+std::tuple<c10::optional<torch::Tensor>, c10::optional<torch::Tensor>, torch::Tensor, torch::Tensor> quantize_fp8_with(
+    const torch::Tensor& x, int64_t fmt, bool want_q, bool want_t, const c10::optional<torch::Tensor>& amax_for_scale);
+
 std::tuple<c10::optional<torch::Tensor>, c10::optional<torch::Tensor>, torch::Tensor> quantize_fp8(const torch::Tensor& x, int64_t fmt,
                                                                                                      bool want_q, bool want_t) {
+  auto r = quantize_fp8_with(x, fmt, want_q, want_t, c10::nullopt);
+  return {std::get<0>(r), std::get<1>(r), std::get<2>(r)};
+}
+
+// As quantize_fp8, but the scale may come from `amax_for_scale` (delayed scaling: the maximum of an amax history) instead of
+// this tensor's own maximum; the tensor's own amax is always computed and returned last, for the caller's history.
+std::tuple<c10::optional<torch::Tensor>, c10::optional<torch::Tensor>, torch::Tensor, torch::Tensor> quantize_fp8_with(
+    const torch::Tensor& x, int64_t fmt, bool want_q, bool want_t, const c10::optional<torch::Tensor>& amax_for_scale) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && x.scalar_type() == torch::kBFloat16);
   TORCH_CHECK(x.size(0) % 64 == 0 && x.size(1) % 64 == 0, "quantize_fp8: dims must be multiples of 64");
   c10::cuda::CUDAGuard guard(x.device());
@@ -120,10 +133,12 @@ std::tuple<c10::optional<torch::Tensor>, c10::optional<torch::Tensor>, torch::Te
   auto bo = torch::dtype(torch::kUInt8).device(x.device());
   if (want_q) q = torch::empty({x.size(0), x.size(1)}, bo);
   if (want_t) qt = torch::empty({x.size(1), x.size(0)}, bo);
-  check(mt_quantize_fp8(x.data_ptr(), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(), (int)fmt, q ? q->data_ptr() : nullptr,
+  if (amax_for_scale) TORCH_CHECK(amax_for_scale->is_cuda() && amax_for_scale->scalar_type() == torch::kFloat32 && amax_for_scale->numel() == 1);
+  const float* scale_src = amax_for_scale ? amax_for_scale->data_ptr<float>() : amax.data_ptr<float>();
+  check(mt_quantize_fp8(x.data_ptr(), (int)x.size(0), (int)x.size(1), scale_src, (int)fmt, q ? q->data_ptr() : nullptr,
                         qt ? qt->data_ptr() : nullptr, deq.data_ptr<float>(), cur_stream()),
         "mt_quantize_fp8");
-  return {q, qt, deq};
+  return {q, qt, deq, amax};
 }
 
 // out [M, N] (+)= a [M, K] . b [N, K]^T * sa * sb, a / b uint8 holding E4M3 (fmt 0) or E5M2 (fmt 1)
@@ -136,7 +151,8 @@ void gemm_fp8(const torch::Tensor& a, const torch::Tensor& b, torch::Tensor& out
   TORCH_CHECK((f32 || out.scalar_type() == torch::kBFloat16) && out.stride(1) == 1 && (!accumulate || f32));
   TORCH_CHECK(sa.scalar_type() == torch::kFloat32 && sb.scalar_type() == torch::kFloat32);
   c10::cuda::CUDAGuard guard(a.device());
-  check(mt_gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), a.stride(0), b.stride(0),
+  auto fn = (g_use_pair && b.size(0) % 256 == 0 && a.size(0) >= 512) ? mt_gemm_fp8_pair : mt_gemm_fp8;
+  check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), a.stride(0), b.stride(0),
                     out.stride(0), (int)a_fmt, (int)b_fmt, f32 ? 1 : 0, accumulate ? 1 : 0, sa.data_ptr<float>(), sb.data_ptr<float>(),
                     status_tensor().data_ptr<int>(), num_sms(), cur_stream()),
         "mt_gemm_fp8");
@@ -269,6 +285,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_set_raster", [](int64_t v) { mt_gemm_set_raster((int)v); });
   m.def("gemm_set_group_m", [](int64_t v) { TORCH_CHECK(mt_gemm_set_group_m((int)v) == 0, "bad group size"); });
   m.def("quantize_fp8", &quantize_fp8);
+  m.def("quantize_fp8_with", &quantize_fp8_with);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("kernel_status", &kernel_status);
   m.def("launch_count", &launch_count);

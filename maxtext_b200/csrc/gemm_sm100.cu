@@ -770,7 +770,7 @@ __device__ __forceinline__ void pair_tile_coords(int t, int m_blocks, int n_bloc
   nb = r / gsz;
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
+template <bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __grid_constant__ CUtensorMap map_c, GemmParams p) {
@@ -802,7 +802,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int m_blocks = (p.M + 2 * BM - 1) / (2 * BM);
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;               // elements per 128-byte row of a stage
+  static_assert(!FP8 || (!A_MN && !B_MN), "8-bit operands are K-major only");
+  const int num_kb = (p.K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -847,13 +849,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const uint32_t sa = smem_a0 + s * PAIR_A_BYTES;
           const uint32_t sb = smem_b0 + s * PAIR_B_BYTES;
           if (!A_MN) {
-            tma_load_2d_pair(sa, &map_a, fb, kb * BK, m0);
+            tma_load_2d_pair(sa, &map_a, fb, kb * BKE, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, fb, m0 + j * 64, kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &map_b, fb, kb * BK, n0);
+            tma_load_2d_pair(sb, &map_b, fb, kb * BKE, n0);
           } else {
 #pragma unroll
             for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, fb, n0 + j * 64, kb * BK);
@@ -865,7 +867,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (one thread of the leader CTA)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? make_idesc_fp8(2 * BM, BN, (uint32_t)p.q_fmt_a, (uint32_t)p.q_fmt_b) : make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       constexpr uint32_t A_LBO = A_MN ? 8192 : 16, B_LBO = B_MN ? 8192 : 16;
       constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32, B_KSTEP = B_MN ? 2048 : 32;
       int s = 0;
@@ -884,8 +886,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const uint64_t db = make_smem_desc(smem_b0 + s * PAIR_B_BYTES, B_LBO, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_f16_ss_2cta(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
-                             (kb | k) != 0 ? 1u : 0u);
+            if (FP8) umma_f8_ss_2cta(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                                     (kb | k) != 0 ? 1u : 0u);
+            else umma_f16_ss_2cta(d_tmem, da + (uint64_t)((k * A_KSTEP) >> 4), db + (uint64_t)((k * B_KSTEP) >> 4), idesc,
+                                  (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_2cta(mapa_shared(empty_bar(s), 0));      // frees the stage in both CTAs
           umma_commit_2cta(mapa_shared(empty_bar(s), 1));
@@ -922,6 +926,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
+        if (FP8) {
+          const float qs = __ldg(p.q_scale_a) * __ldg(p.q_scale_b);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * qs);
+        }
         if (c == BN / 32 - 1) {
           tc_fence_before();
           named_bar_sync(4, EPI_THREADS);                       // all 128 threads have read their rows
@@ -991,9 +1000,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   }
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
+template <bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, GemmParams p, int num_sms, cudaStream_t stream) {
-  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OutT>;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, OutT, FP8>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess) return -2;
@@ -1036,4 +1045,26 @@ extern "C" int mt_gemm_bf16_pair(const void* a, const void* b, void* c, int M, i
                                    : launch_pair<true, true, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
   return out_f32 ? launch_pair<true, false, float>(ma, mb, mc, p, num_sms, stream)
                  : launch_pair<true, false, __nv_bfloat16>(ma, mb, mc, p, num_sms, stream);
+}
+
+
+// 8-bit operands on CTA pairs (see mt_gemm_fp8 for the contract); N a multiple of 128.
+extern "C" int mt_gemm_fp8_pair(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_fmt,
+                                int b_fmt, int out_f32, int accumulate, const float* scale_a, const float* scale_b, int* status, int num_sms,
+                                cudaStream_t stream) {
+  using namespace mt;
+  if ((accumulate && !out_f32) || K % 128 || lda % 16 || ldb % 16 || N % 128) return -10;
+  CUtensorMap ma, mb, mc;
+  int e = make_map_2d(&ma, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, 2 * BK, BM);
+  if (e) return 100 + e;
+  if ((e = make_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, 2 * BK, PAIR_BN / 2))) return 200 + e;
+  if (out_f32) e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, BM);
+  else e = make_map_2d(&mc, c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 64, BM);
+  if (e) return 300 + e;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.accumulate = accumulate; p.status = status;
+  p.q_fmt_a = a_fmt; p.q_fmt_b = b_fmt; p.q_scale_a = scale_a; p.q_scale_b = scale_b;
+  p.raster_n = pick_raster(M, N);
+  return out_f32 ? launch_pair<false, false, float, true>(ma, mb, mc, p, num_sms, stream)
+                 : launch_pair<false, false, __nv_bfloat16, true>(ma, mb, mc, p, num_sms, stream);
 }

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives used by the kernels in this
-// directory: mbarrier, TMA (cp.async.bulk.tensor, plain per-CTA form only), tcgen05 MMA /
+// directory: mbarrier, TMA (cp.async.bulk.tensor: per-CTA form and the cta_group::2 form of CTA pairs), tcgen05 MMA /
 // TMEM allocation / TMEM loads, and the bounded waits every kernel here uses instead of open spins.
 #pragma once
 #include <cuda.h>
@@ -235,6 +235,14 @@ __device__ __forceinline__ void umma_f16_ss_2cta(uint32_t tmem_d, uint64_t desc_
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8_ss_2cta(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }

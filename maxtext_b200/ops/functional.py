@@ -76,7 +76,7 @@ class _LinearFn(torch.autograd.Function):
       # a copy: callers may transform the projection in place (rotary embedding on the packed q|k|v)
       return saved_out.reshape(-1, w.shape[0]).clone()
     ctx.fp8 = _quant.supported(x2, w)
-    y = _quant.linear_fwd(x2, w) if ctx.fp8 else mm(x2, w, False, True)
+    y = _quant.linear_fwd(x2, w, pv) if ctx.fp8 else mm(x2, w, False, True)
     if bias is not None:
       y = y + bias.to(y.dtype)
     return y
@@ -90,7 +90,7 @@ class _LinearFn(torch.autograd.Function):
       dy2 = dy2.contiguous()
     if getattr(ctx, "fp8", False) and ctx.tp_reduce_dx is None and _quant.supported(dy2, w):
       go = pv.main_grad.view(w.shape) if (pv is not None and pv.main_grad is not None) else None
-      dx = _quant.linear_bwd(dy2, x2, w, bool(ctx.needs_input_grad[0]), go, bool(pv.grad_written) if go is not None else False)
+      dx = _quant.linear_bwd(dy2, x2, w, bool(ctx.needs_input_grad[0]), go, bool(pv.grad_written) if go is not None else False, pv)
       if go is not None:
         pv.grad_written = True
       dbias = dy2.float().sum(0) if ctx.has_bias else None
@@ -127,7 +127,7 @@ def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None,
   if not torch.is_grad_enabled():
     if saved_out is not None:
       return saved_out
-    y = (pre if pre is not None else (_quant.linear_fwd(x2, p.data) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
+    y = (pre if pre is not None else (_quant.linear_fwd(x2, p.data, p) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
     y = y.view(*x.shape[:-1], p.shape[0])
     return y + b.to(y.dtype) if b is not None else y
   return _LinearFn.apply(x2, p.data, p, saved_out, b, pre, tp_reduce_dx).view(*x.shape[:-1], p.shape[0])

@@ -19,6 +19,8 @@ from . import backend
 
 E4M3, E5M2 = 0, 1
 _MODE = ""
+_HISTORY_LEN = 0          # 0: current scaling; n > 0: delayed scaling over the last n amax values (the reference uses 1024)
+_HISTORY: dict = {}       # (owner id, role) -> [ring tensor [n], write position]
 
 
 def set_mode(mode: str):
@@ -31,31 +33,61 @@ def mode() -> str:
   return _MODE
 
 
+def set_delayed_scaling(history_len: int):
+  """Delayed scaling (src/maxtext/layers/quantizations.py:333-391 `Fp8Einsum`: amax history, scale from its maximum): the
+  scale used for a tensor comes from the amax values seen in earlier steps, so quantisation does not wait for a reduction
+  over the tensor it is about to cast. History lives on the device; 0 returns to current scaling."""
+  global _HISTORY_LEN
+  _HISTORY_LEN = int(history_len)
+  _HISTORY.clear()
+
+
+def _quantize(x2, fmt, want_q, want_t, key=None):
+  E = backend.ext()
+  if _HISTORY_LEN <= 0 or key is None:
+    return E.quantize_fp8(x2, fmt, want_q, want_t)
+  ent = _HISTORY.get(key)
+  if ent is None:
+    q, qt, deq, amax = E.quantize_fp8_with(x2, fmt, want_q, want_t, None)       # first sight of this tensor: its own amax
+    ring = amax.repeat(_HISTORY_LEN)
+    _HISTORY[key] = [ring, 0]
+    return q, qt, deq
+  ring, pos = ent
+  q, qt, deq, amax = E.quantize_fp8_with(x2, fmt, want_q, want_t, ring.max().reshape(1))
+  ring[pos % _HISTORY_LEN] = amax[0]
+  ent[1] = pos + 1
+  return q, qt, deq
+
+
 def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
   return (_MODE == "fp8" and backend.use_cuda_kernels(x2) and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
           and x2.shape[0] % 128 == 0 and x2.shape[1] % 128 == 0 and w.shape[0] % 128 == 0 and w.is_contiguous()
           and hasattr(backend.ext(), "gemm_fp8"))
 
 
-def linear_fwd(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def linear_fwd(x2: torch.Tensor, w: torch.Tensor, owner=None) -> torch.Tensor:
+  """`owner` (the parameter object) keys the amax histories when delayed scaling is on."""
   E = backend.ext()
-  xq, _, sx = E.quantize_fp8(x2, E4M3, True, False)
-  wq, _, sw = E.quantize_fp8(w, E4M3, True, False)
+  k = id(owner) if owner is not None else None
+  xq, _, sx = _quantize(x2, E4M3, True, False, (k, "x") if k else None)
+  wq, _, sw = _quantize(w, E4M3, True, False, (k, "w") if k else None)
   y = torch.empty(x2.shape[0], w.shape[0], dtype=torch.bfloat16, device=x2.device)
   E.gemm_fp8(xq, wq, y, E4M3, E4M3, sx, sw, False)
   return y
 
 
-def linear_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, need_dx: bool, grad_out: torch.Tensor | None, accumulate: bool):
+def linear_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, need_dx: bool, grad_out: torch.Tensor | None, accumulate: bool,
+               owner=None):
   """Returns dx (bf16) or None; writes dW into grad_out [out, in] fp32 when given."""
   E = backend.ext()
-  dyq, dyt, sdy = E.quantize_fp8(dy2, E5M2, need_dx, grad_out is not None)
+  k = id(owner) if owner is not None else None
+  dyq, dyt, sdy = _quantize(dy2, E5M2, need_dx, grad_out is not None, (k, "dy") if k else None)
   dx = None
   if need_dx:
-    _, wt, sw = E.quantize_fp8(w, E4M3, False, True)             # W^T [in, out]: the contraction runs over `out`
+    _, wt, sw = _quantize(w, E4M3, False, True, (k, "w") if k else None)             # W^T [in, out]: the contraction runs over `out`
     dx = torch.empty(dy2.shape[0], w.shape[1], dtype=torch.bfloat16, device=dy2.device)
     E.gemm_fp8(dyq, wt, dx, E5M2, E4M3, sdy, sw, False)
   if grad_out is not None:
-    _, xt, sx = E.quantize_fp8(x2, E4M3, False, True)            # x^T [in, tokens]
+    _, xt, sx = _quantize(x2, E4M3, False, True, (k, "x") if k else None)            # x^T [in, tokens]
     E.gemm_fp8(dyt, xt, grad_out, E5M2, E4M3, sdy, sx, accumulate)
   return dx

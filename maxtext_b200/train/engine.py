@@ -44,6 +44,7 @@ class TrainEngine:
     self.model = model or Transformer(c, mesh, self.device)
     from ..ops import quantization as _quant
     _quant.set_mode(str(c.quantization or ""))
+    _quant.set_delayed_scaling(int(getattr(c, "fp8_amax_history_len", 0)))
     self.store = self.model.store
     if init:
       self.store.initialize(seed=c.init_weights_seed)

@@ -75,3 +75,23 @@ def test_fp8_training_reduces_loss():
     from maxtext_b200.ops import quantization as Q
     Q.set_mode("")
   assert hist[-1]["learning/loss"] < hist[0]["learning/loss"] - 0.3
+
+
+def test_delayed_scaling_uses_history_maximum():
+  from maxtext_b200.ops import quantization as Q
+  E = _ext()
+  torch.manual_seed(5)
+  x1 = (torch.randn(128, 128, device="cuda")).bfloat16()
+  x2 = (torch.randn(128, 128, device="cuda") * 0.1).bfloat16()          # much smaller than the history's maximum
+  Q.set_delayed_scaling(4)
+  try:
+    owner = object()
+    _, _, s1 = Q._quantize(x1, 0, True, False, (id(owner), "x"))
+    q2, _, s2 = Q._quantize(x2, 0, True, False, (id(owner), "x"))
+    assert torch.allclose(s2, s1)                                        # the scale still comes from the first tensor's amax
+    want = (x2.float() / s1).to(torch.float8_e4m3fn)
+    assert torch.equal(q2.view(torch.float8_e4m3fn).float(), want.float())
+    ring = Q._HISTORY[(id(owner), "x")][0]
+    assert torch.allclose(ring[0], x2.float().abs().max())                # ...and x2's amax entered the history
+  finally:
+    Q.set_delayed_scaling(0)
