@@ -56,6 +56,7 @@ class LayerCtx:
   cp_size: int = 1              # total sequence split: context x context_usp_ulysses
   usp_group: object = None      # ranks along `context_usp_ulysses`
   max_logits: dict | None = None  # QK-clip: (layer, module) -> per-head maximum attention logit of this step
+  expert_counts: dict | None = None  # DeepSeek bias update: MoE module -> tokens routed to each expert this step
   # remat: first forward stores named tensors, recompute forward consumes them
   save_names: tuple = ()
   offload_names: tuple = ()

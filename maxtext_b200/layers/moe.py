@@ -185,6 +185,10 @@ class RoutedMoE:
     wts, idx, aux = self.route(x2, B, S)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))
+    if (self.gate_bias is not None and self.deepseek and self.c.routed_bias_update_rate > 0 and ctx.expert_counts is not None
+        and ctx.mode == "train" and not ctx.recompute):
+      cnt = torch.bincount(idx.reshape(-1), minlength=self.E).float()
+      ctx.expert_counts[self] = ctx.expert_counts[self] + cnt if self in ctx.expert_counts else cnt
     if self.style == "llama4":
       assert self.k == 1, "llama4 routing scales the expert input by its single score"
       x2 = (x2.float() * torch.sigmoid(wts)).to(x2.dtype)

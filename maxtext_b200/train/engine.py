@@ -136,6 +136,9 @@ class TrainEngine:
     if c.use_qk_clip:
       self._max_logits = getattr(self, "_max_logits", None) or {}
       ctx.max_logits = self._max_logits
+    if c.routed_bias and c.routed_bias_update_rate > 0:
+      self._expert_counts = getattr(self, "_expert_counts", None) or {}
+      ctx.expert_counts = self._expert_counts
     # ---- forward
     self._gather(0, async_op=False)
     self._gather(1)
@@ -371,6 +374,8 @@ class TrainEngine:
     lr = self.schedule(self.step_count)
     opt_metrics = self.optimizer.step(grad_scale, lr, self.step_count + 1, loss=(loss_sum * inv_w), grad_norm=raw_norm)
     self.step_count += 1
+    if getattr(self, "_expert_counts", None):
+      self._apply_routed_bias_update()
     if c.use_qk_clip and getattr(self, "_max_logits", None):
       opt_metrics = dict(opt_metrics)
       opt_metrics["learning/max_attention_logit"] = self._apply_qk_clip()
@@ -385,6 +390,27 @@ class TrainEngine:
     }
     metrics.update(opt_metrics)
     return metrics
+
+  @torch.no_grad()
+  def _apply_routed_bias_update(self):
+    """Auxiliary-loss-free load balancing (DeepSeek-V3; src/maxtext/layers/moe.py:215-236, train.py:646-690): after the
+    optimizer step every routed expert's selection bias moves by +rate if it received fewer tokens than average this step
+    and by -rate if it received more."""
+    c, store = self.config, self.store
+    rate = float(c.routed_bias_update_rate)
+    for moe, cnt in self._expert_counts.items():
+      if self.inner_world > 1:
+        dist.all_reduce(cnt, group=self.inner_group)
+      delta = torch.sign(cnt.sum() / cnt.numel() - cnt) * rate
+      p = moe.gate_bias
+      u = store.unit_of(p)
+      off = u.offsets[u.params.index(p)]
+      lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+      a, b = max(off, lo), min(off + p.pdef.numel, hi)
+      if a < b:
+        store.shard_view(u, store.master)[a - lo: b - lo].add_(delta[a - off: b - off].to(store.master.dtype))
+    store.sync_compute_from_master()
+    self._expert_counts.clear()
 
   @torch.no_grad()
   def _apply_qk_clip(self):

@@ -19,7 +19,7 @@ FAMILIES = {
                       "qk_nope_head_dim=16", "qk_rope_head_dim=8", "v_head_dim=16", "shared_experts=1"],
     "deepseek3-tiny": ["num_experts=8", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "base_num_decoder_layers=3", "kv_lora_rank=32",
                        "q_lora_rank=24", "qk_nope_head_dim=16", "qk_rope_head_dim=8", "v_head_dim=16", "n_routing_groups=4",
-                       "topk_routing_group=2"],
+                       "topk_routing_group=2", "first_num_dense_layers=1"],
     "gemma-2b": [],
     "gemma2-2b": ["sliding_window_size=8"],
     "gemma3-4b": ["sliding_window_size=8", "base_num_decoder_layers=6"],

@@ -209,3 +209,22 @@ def test_qk_clip_shrinks_heads_above_threshold():
   assert second <= 0.05 * 1.5 and second < first / 20, (first, second)
   v_after = eng.store.full_master(mla.wkv_b).view(mla.h, mla.nope + mla.vd, -1)[:, mla.nope:]
   assert torch.equal(v_before, v_after)
+
+
+def test_deepseek_routed_bias_moves_against_load():
+  """With learning rate 0 the only change to the gate bias is the load-balancing update: +rate for experts below the
+  average load of the step, -rate for experts above it."""
+  from helpers import batch_of, make_engine, tiny_config
+  cfg = tiny_config("deepseek3-tiny", ["routed_bias=true", "routed_bias_update_rate=0.01", "learning_rate=0.0", "adam_weight_decay=0.0",
+                                       "first_num_dense_layers=1"])
+  eng = make_engine(cfg)
+  moe = [b.mlp.routed for l in eng.model.layers for b in l.blocks if hasattr(b.mlp, "routed")][0]
+  before = eng.store.full_master(moe.gate_bias).clone()
+  batch = batch_of(cfg)
+  eng.fwd_bwd(batch)
+  counts = eng._expert_counts[moe].clone()
+  eng.update()
+  after = eng.store.full_master(moe.gate_bias)
+  want = torch.sign(counts.sum() / counts.numel() - counts) * 0.01
+  assert torch.allclose(after - before, want, atol=1e-7)
+  assert (after - before).abs().max() > 0
