@@ -294,10 +294,10 @@ class ParamStore:
       self.ag_mode = os.environ.get("MAXTEXT_B200_AG_MODE", "prefetch")
       self.ag_in_gemm = self.ag_mode == "gemm"
       self.ag_stream = torch.cuda.Stream(device=dev)
-      # in-switch (NVLS) reduction of the gradient reduce-scatter when the buffers have a multicast address: "auto" uses it for
-      # groups of four ranks or more (at two ranks the plain peer loads measured faster: 1135 vs 1150 ms per step)
-      nv = os.environ.get("MAXTEXT_B200_RS_NVLS", "auto")
-      self.rs_nvls = (world >= 4) if nv == "auto" else nv != "0"
+      # in-switch (NVLS) reduction of the gradient reduce-scatter when the buffers have a multicast address. Off unless
+      # MAXTEXT_B200_RS_NVLS=1: at two ranks the plain peer loads measured faster (1135 vs 1150 ms per step); larger groups,
+      # where the switch saves seven of eight loads, are the intended use.
+      self.rs_nvls = os.environ.get("MAXTEXT_B200_RS_NVLS", "0") == "1"
       self.comm_stream = torch.cuda.Stream(device=dev)
       self._gbufs = None
       self._gslot_pending = [None, None]
