@@ -36,12 +36,15 @@ def main():
   ap.add_argument("--dim", type=int, default=128)
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--small", action="store_true")
+  ap.add_argument("--fwd-variant", type=int, default=0, help="tuning: 1 = one CTA per SM, 2 = two CTAs per SM (0 = library default)")
   ap.add_argument("--no-lib", action="store_true")
   a = ap.parse_args()
   if a.small:
     a.batch, a.seq, a.hq, a.hkv, a.iters = 2, 4096, 32, 8, 3     # 160 MB of q, k, v, out: larger than L2, small enough to profile
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
+  if a.fwd_variant:
+    E.flash_fwd_set_variant(a.fwd_variant)
   B, S, Hq, Hkv, D = a.batch, a.seq, a.hq, a.hkv, a.dim
   qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
   q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]

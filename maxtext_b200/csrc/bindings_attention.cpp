@@ -16,6 +16,8 @@ extern "C" int mt_decode_attention(const void* q, const void* k_cache, const voi
                                    int max_len, int Hq, int Hkv, int D, int window, float scale, float soft_cap, int splits, float* part,
                                    void* out, cudaStream_t st);
 
+extern "C" int mt_flash_fwd_set_variant(int v);
+
 int* mt_status_ptr();          // defined in bindings.cpp
 void mt_count_launches(int n); // defined in bindings.cpp
 
@@ -86,6 +88,7 @@ void decode_attention(const torch::Tensor& q, const torch::Tensor& k_cache, cons
 
 void register_attention(pybind11::module_& m) {
   m.def("decode_attention", &decode_attention);
+  m.def("flash_fwd_set_variant", [](int64_t v) { TORCH_CHECK(mt_flash_fwd_set_variant((int)v) == 0, "variant must be 1 or 2"); });
   m.def("flash_supported", &flash_supported);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);

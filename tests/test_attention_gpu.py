@@ -139,3 +139,28 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, window):
       m = ref.attention_mask(qpos, kpos, None, None, True, window)
       want = ref.attention(q[b][None, None], K, V, m, 1.0, 0.0)[0, 0]
       assert (out[b].float() - want.float()).abs().max() < 2e-2, (b, splits)
+
+
+def test_flash_forward_two_ctas_per_sm_variant_matches_default():
+  """The experimental forward variant (two co-resident CTAs per SM, single score buffer) gives the default kernel's result."""
+  from maxtext_b200.ops import backend
+  E = backend.ext(required=True)
+  torch.manual_seed(0)
+  B, S, Hq, Hkv, D = 2, 512, 8, 2, 128
+  qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
+  q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+  seg = torch.ones(B, S, device="cuda", dtype=torch.int32)
+  seg[:, 300:] = 2
+  outs = []
+  try:
+    for variant in (1, 2):
+      E.flash_fwd_set_variant(variant)
+      out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
+      lse = torch.empty(B, Hq, S, device="cuda")
+      E.flash_fwd(q, k, v, out, lse, seg, 1.0, 64)
+      outs.append((out.float(), lse))
+  finally:
+    E.flash_fwd_set_variant(1)
+  assert (outs[0][0] - outs[1][0]).abs().max() < 2e-2
+  assert (outs[0][1] - outs[1][1]).abs().max() < 1e-3
+  assert E.kernel_status(True) == 0
