@@ -76,7 +76,11 @@ class _LinearFn(torch.autograd.Function):
       # a copy: callers may transform the projection in place (rotary embedding on the packed q|k|v)
       return saved_out.reshape(-1, w.shape[0]).clone()
     ctx.fp8 = _quant.supported(x2, w)
-    y = _quant.linear_fwd(x2, w, pv) if ctx.fp8 else mm(x2, w, False, True)
+    ctx.fp8_saved = None
+    if ctx.fp8:
+      y, ctx.fp8_saved = _quant.linear_fwd(x2, w, pv, keep_for_bwd=True)     # this forward will be differentiated: quantise once for both passes
+    else:
+      y = mm(x2, w, False, True)
     if bias is not None:
       y = y + bias.to(y.dtype)
     return y
@@ -90,7 +94,9 @@ class _LinearFn(torch.autograd.Function):
       dy2 = dy2.contiguous()
     if getattr(ctx, "fp8", False) and ctx.tp_reduce_dx is None and _quant.supported(dy2, w):
       go = pv.main_grad.view(w.shape) if (pv is not None and pv.main_grad is not None) else None
-      dx = _quant.linear_bwd(dy2, x2, w, bool(ctx.needs_input_grad[0]), go, bool(pv.grad_written) if go is not None else False, pv)
+      dx = _quant.linear_bwd(dy2, x2, w, bool(ctx.needs_input_grad[0]), go, bool(pv.grad_written) if go is not None else False, pv,
+                             getattr(ctx, "fp8_saved", None))
+      ctx.fp8_saved = None
       if go is not None:
         pv.grad_written = True
       dbias = dy2.float().sum(0) if ctx.has_bias else None

@@ -65,24 +65,37 @@ def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
           and hasattr(backend.ext(), "gemm_fp8"))
 
 
-def linear_fwd(x2: torch.Tensor, w: torch.Tensor, owner=None) -> torch.Tensor:
-  """`owner` (the parameter object) keys the amax histories when delayed scaling is on."""
+def linear_fwd(x2: torch.Tensor, w: torch.Tensor, owner=None, keep_for_bwd: bool = False):
+  """`owner` (the parameter object) keys the amax histories when delayed scaling is on. With keep_for_bwd the same quantise
+  pass also writes the transposed copies the backward products need; they are returned as (y, saved) so that the backward
+  does not read x and W again."""
   E = backend.ext()
   k = id(owner) if owner is not None else None
-  xq, _, sx = _quantize(x2, E4M3, True, False, (k, "x") if k else None)
-  wq, _, sw = _quantize(w, E4M3, True, False, (k, "w") if k else None)
+  xq, xt, sx = _quantize(x2, E4M3, True, keep_for_bwd, (k, "x") if k else None)
+  wq, wt, sw = _quantize(w, E4M3, True, keep_for_bwd, (k, "w") if k else None)
   y = torch.empty(x2.shape[0], w.shape[0], dtype=torch.bfloat16, device=x2.device)
   E.gemm_fp8(xq, wq, y, E4M3, E4M3, sx, sw, False)
+  if keep_for_bwd:
+    return y, (xt, sx, wt, sw)
   return y
 
 
 def linear_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, need_dx: bool, grad_out: torch.Tensor | None, accumulate: bool,
-               owner=None):
-  """Returns dx (bf16) or None; writes dW into grad_out [out, in] fp32 when given."""
+               owner=None, saved=None):
+  """Returns dx (bf16) or None; writes dW into grad_out [out, in] fp32 when given. `saved` = the transposed 8-bit copies of
+  x and W that linear_fwd(keep_for_bwd=True) produced."""
   E = backend.ext()
   k = id(owner) if owner is not None else None
   dyq, dyt, sdy = _quantize(dy2, E5M2, need_dx, grad_out is not None, (k, "dy") if k else None)
   dx = None
+  if saved is not None:
+    xt, sx, wt, sw = saved
+    if need_dx:
+      dx = torch.empty(dy2.shape[0], w.shape[1], dtype=torch.bfloat16, device=dy2.device)
+      E.gemm_fp8(dyq, wt, dx, E5M2, E4M3, sdy, sw, False)
+    if grad_out is not None:
+      E.gemm_fp8(dyt, xt, grad_out, E5M2, E4M3, sdy, sx, accumulate)
+    return dx
   if need_dx:
     _, wt, sw = _quantize(w, E4M3, False, True, (k, "w") if k else None)             # W^T [in, out]: the contraction runs over `out`
     dx = torch.empty(dy2.shape[0], w.shape[1], dtype=torch.bfloat16, device=dy2.device)

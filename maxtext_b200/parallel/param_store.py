@@ -279,8 +279,14 @@ class ParamStore:
         and self.grad_dtype == torch.float32 and not bool(config.logits_via_embedding)):
       from . import symm as _symm
       if _symm.available():
-        self.symm = _symm.SymmGroup(None, self.device)
-        self.fused = True
+        try:
+          self.symm = _symm.SymmGroup(None, self.device)
+          self.fused = True
+        except Exception as e:  # pylint: disable=broad-except
+          # no peer mapping on this platform (or the allocator refused): the NCCL composition below does the same job
+          from ..utils import max_logging
+          max_logging.log(f"symmetric memory unavailable ({e!r}); FSDP collectives use NCCL")
+          self.symm, self.fused = None, False
     if self.fused:
       self._cs = self.symm.alloc(total_local, self.compute_dtype, zero=True)
       self.compute_shard = self._cs.tensor
