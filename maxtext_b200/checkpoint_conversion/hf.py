@@ -28,11 +28,45 @@ def _deinterleave(w_out_in: torch.Tensor, heads: int, dh: int) -> torch.Tensor:
   return w.permute(0, 2, 1, 3).reshape(heads * dh, -1)
 
 
-def _hf_name(pdef, cfg) -> tuple[str, str] | None:
-  """(hf key, kind) for one of our parameters; kind in {linear, norm, embed, q, k, expert:<j>...}."""
-  path = "/".join(pdef.ref_path)
+def _locate(pdef, cfg) -> tuple[str, int | None]:
+  """(path relative to one HF decoder layer, HF layer index) of one of our parameters.
+
+  Stacks that hold several HF layers per scanned unit are unrolled here: gemma2 keeps a (local, global) pair per
+  unit with suffixed module names, olmo3 a cycle of `layers_<j>` sub-trees, deepseek numbers its MoE stack after
+  the dense one."""
+  parts = list(pdef.ref_path)
   L = pdef.layer
+  if L is None:
+    return "/".join(parts), None
+  blk = cfg.decoder_block
+  if blk == "olmo3" and parts[0].startswith("layers_"):
+    cyc = max(1, int(cfg.inhomogeneous_layer_cycle_interval))
+    L = L * cyc + int(parts[0].split("_")[1])
+    parts = parts[1:]
+    if parts[0] == "attention":
+      parts[0] = "self_attention"
+  elif blk == "gemma2":
+    for sfx, j in (("_local", 0), ("_global", 1)):
+      if parts[0].endswith(sfx):
+        parts[0] = parts[0][:-len(sfx)]
+        L = 2 * L + j
+        break
+  elif blk == "deepseek" and getattr(pdef, "stack", "") == "moe_layers":
+    L = L + int(cfg.first_num_dense_layers)
+  return "/".join(parts), L
+
+
+# which expert matrix a stacked MoE parameter is, by the last path component
+_EXPERT_PART = {"wi_0": "gate", "wi_1": "up", "wo": "down", "wi_0_bias": "gate_bias", "wi_1_bias": "up_bias", "wo_bias": "down_bias"}
+
+
+def _hf_name(pdef, cfg) -> tuple[str, str] | None:
+  """(hf key, kind) for one of our parameters. Kinds: linear, vec, norm, embed, q, k, qbias, kbias, and
+  experts:<part> for stacked expert tensors (the key is then the HF layer prefix)."""
+  path, L = _locate(pdef, cfg)
   pre = f"model.layers.{L}." if L is not None else ""
+  blk = cfg.decoder_block
+  sandwich = blk in ("gemma2", "gemma3")
   table = {
       "token_embedder/embedding": ("model.embed_tokens.weight", "embed"),
       "decoder/decoder_norm/scale": ("model.norm.weight", "norm"),
@@ -44,23 +78,133 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
       "self_attention/query/bias": (pre + "self_attn.q_proj.bias", "qbias"),
       "self_attention/key/bias": (pre + "self_attn.k_proj.bias", "kbias"),
       "self_attention/value/bias": (pre + "self_attn.v_proj.bias", "vec"),
+      "self_attention/out/bias": (pre + "self_attn.o_proj.bias", "vec"),
+      "self_attention/sinks": (pre + "self_attn.sinks", "vec"),
       "self_attention/query_norm/scale": (pre + "self_attn.q_norm.weight", "norm"),
       "self_attention/key_norm/scale": (pre + "self_attn.k_norm.weight", "norm"),
+      # multi-head latent attention (DeepSeek)
+      "self_attention/query/kernel#mla": (pre + "self_attn.q_proj.weight", "linear"),
+      "self_attention/wq_a/kernel": (pre + "self_attn.q_a_proj.weight", "linear"),
+      "self_attention/q_norm/scale": (pre + "self_attn.q_a_layernorm.weight", "norm"),
+      "self_attention/wq_b/kernel": (pre + "self_attn.q_b_proj.weight", "linear"),
+      "self_attention/wkv_a/kernel": (pre + "self_attn.kv_a_proj_with_mqa.weight", "linear"),
+      "self_attention/kv_norm/scale": (pre + "self_attn.kv_a_layernorm.weight", "norm"),
+      "self_attention/wkv_b/kernel": (pre + "self_attn.kv_b_proj.weight", "linear"),
       "pre_self_attention_layer_norm/scale": (pre + "input_layernorm.weight", "norm"),
       "post_self_attention_layer_norm/scale": (pre + "post_attention_layernorm.weight", "norm"),
+      "post_mlp_layer_norm/scale": (pre + "post_feedforward_layernorm.weight", "norm"),
       "pre_self_attention_norm/scale": (pre + "input_layernorm.weight", "norm"),
-      "pre_ffw_norm/scale": (pre + ("pre_feedforward_layernorm.weight" if cfg.decoder_block in ("gemma2", "gemma3") else "post_attention_layernorm.weight"), "norm"),
+      "pre_ffw_norm/scale": (pre + ("pre_feedforward_layernorm.weight" if sandwich else "post_attention_layernorm.weight"), "norm"),
       "post_self_attention_norm/scale": (pre + "post_attention_layernorm.weight", "norm"),
       "post_ffw_norm/scale": (pre + "post_feedforward_layernorm.weight", "norm"),
       "mlp/wi_0/kernel": (pre + "mlp.gate_proj.weight", "linear"),
       "mlp/wi_1/kernel": (pre + "mlp.up_proj.weight", "linear"),
       "mlp/wo/kernel": (pre + "mlp.down_proj.weight", "linear"),
       "MoeBlock_0/gate/kernel": (pre + "block_sparse_moe.gate.weight", "linear"),
-      "MoeBlock_0/wi_0": (pre + "block_sparse_moe.experts.{e}.w1.weight", "experts"),
-      "MoeBlock_0/wi_1": (pre + "block_sparse_moe.experts.{e}.w3.weight", "experts"),
-      "MoeBlock_0/wo": (pre + "block_sparse_moe.experts.{e}.w2.weight", "experts"),
+      "moe_block/gate/kernel": (pre + "mlp.gate.weight", "linear"),
+      "DeepSeekMoeBlock_0/MoeBlock_0/gate/kernel": (pre + "mlp.gate.weight", "linear"),
+      "DeepSeekMoeBlock_0/MoeBlock_0/gate/bias": (pre + "mlp.gate.e_score_correction_bias", "vec"),
+      "DeepSeekMoeBlock_0/shared_experts/wi_0/kernel": (pre + "mlp.shared_experts.gate_proj.weight", "linear"),
+      "DeepSeekMoeBlock_0/shared_experts/wi_1/kernel": (pre + "mlp.shared_experts.up_proj.weight", "linear"),
+      "DeepSeekMoeBlock_0/shared_experts/wo/kernel": (pre + "mlp.shared_experts.down_proj.weight", "linear"),
+      "GptOssMlp/gate/kernel": (pre + "mlp.router.weight", "linear"),
+      "GptOssMlp/gate/bias": (pre + "mlp.router.bias", "vec"),
+      "Llama4MoEBlock_0/MoeBlock_0/gate/kernel": (pre + "feed_forward.router.weight", "linear"),
+      "Llama4MoEBlock_0/shared_experts/wi_0/kernel": (pre + "feed_forward.shared_expert.gate_proj.weight", "linear"),
+      "Llama4MoEBlock_0/shared_experts/wi_1/kernel": (pre + "feed_forward.shared_expert.up_proj.weight", "linear"),
+      "Llama4MoEBlock_0/shared_experts/wo/kernel": (pre + "feed_forward.shared_expert.down_proj.weight", "linear"),
   }
-  return table.get(path)
+  if cfg.attention_type == "mla" and path == "self_attention/query/kernel":
+    path += "#mla"
+  if blk == "llama4" and path.startswith("mlp/"):
+    return pre + "feed_forward." + {"wi_0": "gate_proj", "wi_1": "up_proj", "wo": "down_proj"}[path.split("/")[1]] + ".weight", "linear"
+  hit = table.get(path)
+  if hit is not None:
+    return hit
+  last = path.split("/")[-1]
+  if pdef.kind == "experts" or (last in _EXPERT_PART and path.split("/")[0] in
+                                ("MoeBlock_0", "moe_block", "DeepSeekMoeBlock_0", "GptOssMlp", "Llama4MoEBlock_0")):
+    return pre, "experts:" + _EXPERT_PART[last]
+  return None
+
+
+def _expert_style(cfg) -> str:
+  return {"mixtral": "mixtral", "gpt_oss": "gpt_oss", "llama4": "llama4"}.get(cfg.decoder_block, "split")
+
+
+def _load_experts(hf_state: dict, pre: str, part: str, cfg) -> torch.Tensor | None:
+  """Stacked `[E, out, in]` (or `[E, out]` bias) tensor of one expert matrix from whichever layout the HF dict uses:
+  one module per expert (hub checkpoints) or one stacked tensor with gate and up fused (in-memory models)."""
+  E = cfg.num_experts
+  style = _expert_style(cfg)
+  if style == "gpt_oss":
+    # gate_up_proj [E, in, 2*out] with gate and up in alternating columns; down_proj [E, in, out]
+    base = pre + "mlp.experts."
+    if part in ("gate", "up"):
+      gu = hf_state.get(base + "gate_up_proj")
+      return None if gu is None else gu.float()[:, :, (0 if part == "gate" else 1)::2].transpose(1, 2).contiguous()
+    if part in ("gate_bias", "up_bias"):
+      gb = hf_state.get(base + "gate_up_proj_bias")
+      return None if gb is None else gb.float()[:, (0 if part == "gate_bias" else 1)::2].contiguous()
+    if part == "down":
+      d = hf_state.get(base + "down_proj")
+      return None if d is None else d.float().transpose(1, 2).contiguous()
+    d = hf_state.get(base + "down_proj_bias")
+    return None if d is None else d.float()
+  if style == "llama4":
+    # gate_up_proj [E, in, 2*out] (gate | up halves); down_proj [E, in, out]
+    base = pre + "feed_forward.experts."
+    if part == "down":
+      d = hf_state.get(base + "down_proj")
+      return None if d is None else d.float().transpose(1, 2).contiguous()
+    gu = hf_state.get(base + "gate_up_proj")
+    if gu is None:
+      return None
+    half = gu.shape[2] // 2
+    return (gu.float()[:, :, :half] if part == "gate" else gu.float()[:, :, half:]).transpose(1, 2).contiguous()
+  if style == "mixtral":
+    per = pre + "block_sparse_moe.experts.{e}." + {"gate": "w1", "up": "w3", "down": "w2"}[part] + ".weight"
+  else:
+    per = pre + "mlp.experts.{e}." + part + "_proj.weight"
+  if per.format(e=0) in hf_state:
+    return torch.stack([hf_state[per.format(e=e)].float() for e in range(E)])
+  base = pre + "mlp.experts."
+  if part == "down":
+    d = hf_state.get(base + "down_proj")
+    return None if d is None else d.float()
+  gu = hf_state.get(base + "gate_up_proj")
+  if gu is None:
+    return None
+  half = gu.shape[1] // 2
+  return gu.float()[:, :half] if part == "gate" else gu.float()[:, half:]
+
+
+def _store_experts(out: dict, pre: str, part: str, w: torch.Tensor, cfg):
+  """Inverse of `_load_experts`, writing the layout hub checkpoints of the family use."""
+  style = _expert_style(cfg)
+  if style in ("gpt_oss", "llama4"):
+    base = pre + ("mlp.experts." if style == "gpt_oss" else "feed_forward.experts.")
+    if part == "down":
+      out[base + "down_proj"] = w.transpose(1, 2).contiguous()
+    elif part == "down_bias":
+      out[base + "down_proj_bias"] = w.contiguous()
+    else:
+      bias = part.endswith("_bias")
+      key = base + ("gate_up_proj_bias" if bias else "gate_up_proj")
+      piece = w if bias else w.transpose(1, 2)                       # [E, out] or [E, in, out]
+      if key not in out:
+        out[key] = torch.zeros(*piece.shape[:-1], 2 * piece.shape[-1])
+      o = piece.shape[-1]
+      first = part.startswith("gate")
+      if style == "gpt_oss":
+        out[key][..., (0 if first else 1)::2] = piece
+      else:
+        out[key][..., (slice(0, o) if first else slice(o, 2 * o))] = piece
+    return
+  per = (pre + "block_sparse_moe.experts.{e}." + {"gate": "w1", "up": "w3", "down": "w2"}[part] + ".weight") if style == "mixtral" \
+      else (pre + "mlp.experts.{e}." + part + "_proj.weight")
+  for e in range(w.shape[0]):
+    out[per.format(e=e)] = w[e].contiguous()
 
 
 def _norm_offset(cfg) -> float:
@@ -68,14 +212,28 @@ def _norm_offset(cfg) -> float:
   return 1.0 if cfg.decoder_block in ("gemma", "gemma2", "gemma3") else 0.0
 
 
+def _embed_scale(cfg) -> float:
+  # Gemma: HF multiplies the looked-up embedding by sqrt(hidden) at run time; here the factor lives in the table
+  return math.sqrt(cfg.emb_dim) if cfg.decoder_block in ("gemma", "gemma2", "gemma3") else 1.0
+
+
 def _q_scale(cfg) -> float:
-  if cfg.use_qk_norm or cfg.decoder_block in ("gemma3",):
+  """Factor folded into the stored query projection: 1/sqrt(head_dim) unless the family scales at run time."""
+  if cfg.use_qk_norm or cfg.attention_type == "mla" or cfg.decoder_block in ("gemma3", "qwen3", "qwen3_moe", "qwen3_custom_moe", "olmo3",
+                                                                              "llama4", "gpt_oss"):
     return 1.0
   return 1.0 / math.sqrt(cfg.head_dim)
 
 
 def _interleaved(cfg) -> bool:
+  """Whether q/k lanes must be permuted from HF's concatenated halves to adjacent pairs. HF Llama-4 rotates adjacent
+  pairs itself, so its tensors are already in that order."""
+  if cfg.decoder_block == "llama4":
+    return False
   return cfg.rope_type.startswith("llama3.1") or cfg.model_name.startswith("llama3.1") or cfg.model_name.startswith("llama3.3")
+
+
+_ALIASES = (("block_sparse_moe.gate", "mlp.gate"),)
 
 
 def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
@@ -88,20 +246,17 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       missing.append(name)
       continue
     key, kind = m
-    if kind == "experts":
-      fused = key.split("block_sparse_moe")[0] + "mlp.experts."
-      if key.format(e=0) in hf_state:
-        w = torch.stack([hf_state[key.format(e=e)].float() for e in range(cfg.num_experts)])
-      elif key.endswith("w2.weight"):                      # newer HF layout: experts stacked, gate|up fused
-        w = hf_state[fused + "down_proj"].float()
-      else:
-        gu = hf_state[fused + "gate_up_proj"].float()
-        half = gu.shape[1] // 2
-        w = gu[:, :half] if key.endswith("w1.weight") else gu[:, half:]
-      store.load_full(name, p.pdef.local_slice(w.contiguous()))
+    if kind.startswith("experts:"):
+      w = _load_experts(hf_state, key, kind.split(":")[1], cfg)
+      if w is None:
+        missing.append(name)
+        continue
+      store.load_full(name, p.pdef.local_slice(w.contiguous().reshape(p.pdef.global_shape())))
       continue
-    if key not in hf_state and "block_sparse_moe.gate" in key:
-      key = key.replace("block_sparse_moe.gate", "mlp.gate")
+    if key not in hf_state:
+      for a, b_ in _ALIASES:
+        if a in key and key.replace(a, b_) in hf_state:
+          key = key.replace(a, b_)
     if key not in hf_state:
       if key == "lm_head.weight" and "model.embed_tokens.weight" in hf_state:
         key = "model.embed_tokens.weight"
@@ -121,6 +276,8 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       w = _interleave(w[:, None], cfg.num_kv_heads, cfg.head_dim)[:, 0]
     elif kind == "norm":
       w = w + _norm_offset(cfg)
+    elif kind == "embed":
+      w = w * _embed_scale(cfg)
     store.load_full(name, p.pdef.local_slice(w.reshape(p.pdef.global_shape())))
   store.sync_compute_from_master()
   return missing
@@ -136,9 +293,8 @@ def to_hf(store, cfg) -> dict:
       continue
     key, kind = m
     w = store.full_master(p).float().clone()
-    if kind == "experts":
-      for e in range(w.shape[0]):
-        out[key.format(e=e)] = w[e].contiguous()
+    if kind.startswith("experts:"):
+      _store_experts(out, key, kind.split(":")[1], w, cfg)
       continue
     if kind == "q":
       w = w / _q_scale(cfg)
@@ -154,6 +310,8 @@ def to_hf(store, cfg) -> dict:
       w = _deinterleave(w[:, None], cfg.num_kv_heads, cfg.head_dim)[:, 0]
     elif kind == "norm":
       w = w - _norm_offset(cfg)
+    elif kind == "embed":
+      w = w / _embed_scale(cfg)
     out[key] = w.contiguous()
   return out
 

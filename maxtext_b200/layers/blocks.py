@@ -214,7 +214,7 @@ class Attention:
 
   def __init__(self, b: Builder, config, name="self_attention", window: int = 0, rope_inv_ts=None, interleaved=False,
                use_rope=True, qk_norm=False, query_scalar: float | None = None, soft_cap: float = 0.0, bias=False,
-               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0):
+               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0, out_bias=None, global_qk_norm=False):
     c = config
     self.config = c
     self.hq, self.hkv, self.dh, self.d = c.num_query_heads, c.num_kv_heads, c.head_dim, c.emb_dim
@@ -224,6 +224,11 @@ class Attention:
     self.window, self.inv_ts, self.interleaved, self.use_rope = window, rope_inv_ts, interleaved, use_rope
     self.qk_norm, self.query_scalar, self.soft_cap, self.rotary_dim = qk_norm, query_scalar, soft_cap, rotary_dim
     self.l2_qk_norm, self.temperature_tuning, self.chunk = l2_qk_norm, temperature_tuning, int(chunk)
+    # YaRN "attention scaling" (src/maxtext/layers/embeddings.py:1020-1022): rotated q and k are each multiplied by
+    # 0.1 ln(factor) + 1; here the product of the two factors scales the logits
+    self.logit_scale = 1.0
+    if use_rope and getattr(c, "rope_attention_scaling", False) and str(c.rope_type).lower() == "yarn" and c.rope_factor > 1:
+      self.logit_scale = (0.1 * math.log(float(c.rope_factor)) + 1.0) ** 2
     ab = b.sub(name)
     depth_scale = 1.0 if (qk_norm or (query_scalar is not None and query_scalar != 1.0)) else 1.0 / math.sqrt(self.dh)
     kv_tp = "col" if self.hkv >= tp else None
@@ -241,8 +246,16 @@ class Attention:
       self.bq = ab.sub("query").vector("bias", self.hq * self.dh, ("q_heads",), init="zeros", tp=True)
       self.bk = ab.sub("key").vector("bias", self.hkv * self.dh, ("kv_heads",), init="zeros", tp=kv_tp is not None)
       self.bv = ab.sub("value").vector("bias", self.hkv * self.dh, ("kv_heads",), init="zeros", tp=kv_tp is not None)
+    # the output projection carries a bias whenever q/k/v do, except for qwen2 (src/maxtext/layers/attentions.py:833)
+    self.bo = ab.sub("out").vector("bias", self.d, ("embed",), init="zeros") if (bias if out_bias is None else out_bias) else None
     self.qn = self.kn = None
-    if qk_norm:
+    self.global_qk_norm = bool(global_qk_norm) and qk_norm
+    if self.global_qk_norm:
+      # olmo3 (src/maxtext/layers/attentions.py:486-494): one RMS statistic over all heads of a token, scale per lane
+      assert tp == 1, "the all-head q/k normalisation of olmo3 is not implemented under tensor parallelism"
+      self.qn = Norm(ab, "query_norm", self.hq * self.dh, c.normalization_layer_epsilon, axes=("norm",))
+      self.kn = Norm(ab, "key_norm", self.hkv * self.dh, c.normalization_layer_epsilon, axes=("norm",))
+    elif qk_norm:
       self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
       self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
     self.sinks = ab.vector("sinks", self.hq, ("q_heads",), init="zeros", tp=True) if sinks else None
@@ -270,22 +283,25 @@ class Attention:
     if not fuse_in:
       x = tp_enter(x, ctx)
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
-    plain = (not self.qk_norm and not self.query_scalar and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
+    plain = (not self.qk_norm and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
       # attention output kept by the remat policy: only the backward of the packed op is needed
       out = F.packed_attention(packed, ctx.positions, ctx.segment_ids, self.inv_ts, self.hq_l, self.hkv_l, self.interleaved,
-                               1.0, self.soft_cap, self.window, self.use_rope)
+                               self.logit_scale * (self.query_scalar or 1.0), self.soft_cap, self.window, self.use_rope)
     elif packed is not None and plain:
       out = F.packed_attention(packed, ctx.positions, ctx.segment_ids, self.inv_ts, self.hq_l, self.hkv_l, self.interleaved,
-                               1.0, self.soft_cap, self.window, self.use_rope)
+                               self.logit_scale * (self.query_scalar or 1.0), self.soft_cap, self.window, self.use_rope)
     else:
       if sep is None:
         q, k, v = packed[:, :, :self.hq_l], packed[:, :, self.hq_l:self.hq_l + self.hkv_l], packed[:, :, self.hq_l + self.hkv_l:]
       else:
         q, k, v = sep
-      if self.qk_norm:
+      if self.global_qk_norm:
+        q = self.qn(q.reshape(B, S, -1)).view(B, S, self.hq_l, self.dh)
+        k = self.kn(k.reshape(B, S, -1)).view(B, S, self.hkv_l, self.dh)
+      elif self.qk_norm:
         q, k = self.qn(q), self.kn(k)
       if self.use_rope:
         q = F.rope(q, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
@@ -295,8 +311,8 @@ class Attention:
         eps = self.config.normalization_layer_epsilon
         q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + eps)).to(q.dtype)
         k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + eps)).to(k.dtype)
-      if self.query_scalar and self.query_scalar != 1.0:
-        q = q * self.query_scalar
+      if (self.query_scalar and self.query_scalar != 1.0) or self.logit_scale != 1.0:
+        q = q * ((self.query_scalar or 1.0) * self.logit_scale)
       if self.temperature_tuning and not self.use_rope:
         # llama4 NoPE layers (attentions.py:1302-1308): log(floor((pos + 1) / floor_scale) + 1) * scale + 1
         c_ = self.config
@@ -317,11 +333,17 @@ class Attention:
       else:
         out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window)
     ctx.keep("context", out)
-    if tp_rt is not None and ctx.reuse("out_proj") is None:
+    if tp_rt is not None and ctx.reuse("out_proj") is None and self.bo is None:
       y = F.linear(out.reshape(B, S, -1), self.o, tp_reduce=tp_rt)
     else:
-      y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"))
-      y = tp_exit(y, ctx) if ctx.reuse("out_proj") is None else y
+      y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"), self.bo if ctx.tp_size == 1 else None)
+      if ctx.reuse("out_proj") is None:
+        y = tp_exit(y, ctx)
+        if self.bo is not None and ctx.tp_size > 1:
+          y = y + self.bo.leaf().to(y.dtype)       # row-parallel: the bias is added once, after the reduction
+      elif self.bo is not None and ctx.tp_size > 1:
+        bl = self.bo.leaf().to(y.dtype)
+        y = y + (bl - bl.detach())                 # the saved output already holds the bias; keep its gradient path
     ctx.keep("out_proj", y)
     return y
 
@@ -445,6 +467,12 @@ class MLP:
       y = F.linear(h, self.wo, tp_reduce=tp_rt)
     else:
       y = F.linear(h, self.wo, ctx.reuse("mlpwo"), self.bo if ctx.tp_size == 1 else None)
-      y = tp_exit(y, ctx) if ctx.reuse("mlpwo") is None else y
+      if ctx.reuse("mlpwo") is None:
+        y = tp_exit(y, ctx)
+        if self.bo is not None and ctx.tp_size > 1:
+          y = y + self.bo.leaf().to(y.dtype)       # row-parallel: the bias is added once, after the reduction
+      elif self.bo is not None and ctx.tp_size > 1:
+        bl = self.bo.leaf().to(y.dtype)
+        y = y + (bl - bl.detach())                 # the saved output already holds the bias; keep its gradient path
     ctx.keep("mlpwo", y)
     return y

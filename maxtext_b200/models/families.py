@@ -22,8 +22,9 @@ class Family:
 
 def describe(c) -> Family:
   blk = c.decoder_block
-  if blk in ("gemma", "gemma2", "gemma3"):
-    return Family(scale_embedding=True)
+  # Gemma checkpoints store the embedding table already multiplied by sqrt(emb_dim) and divide the tied logits by the
+  # same factor (normalize_embedding_logits), so nothing is scaled at lookup (src/maxtext/layers/decoders.py:823-825,
+  # src/maxtext/checkpoint_conversion/utils/param_mapping.py:498-508)
   if blk == "gpt3":
     return Family(norm_kind="layernorm")
   return Family()
@@ -60,8 +61,12 @@ def layer_plans(c) -> list[LayerPlan]:
   blk = c.decoder_block
   mla = c.attention_type == "mla"
   attn = "mla" if mla else "gqa"
-  if blk in ("default", "llama2", "mistral", "qwen3", "simple", "simple_mlp"):
+  if blk in ("default", "llama2", "mistral", "simple", "simple_mlp"):
     return [LayerPlan("layers", [_llama_like(c, attention=attn)]) for _ in range(n)]
+  if blk == "qwen3":
+    # src/maxtext/models/qwen3.py:1451: q and k are RMS-normalised per head, so 1/sqrt(head_dim) cannot live in the
+    # query weights; it multiplies the normalised query at run time
+    return [LayerPlan("layers", [_llama_like(c, attention=attn, query_scalar=c.head_dim ** -0.5)]) for _ in range(n)]
   if blk == "olmo3":
     # src/maxtext/models/olmo3.py: no pre-norms; the attention and MLP outputs are normalised before the residual add;
     # cycles of (local, local, local, global) attention form one scanned block with sub-trees layers_0 .. layers_3
@@ -70,7 +75,7 @@ def layer_plans(c) -> list[LayerPlan]:
     blocks = [BlockPlan(prefix=f"layers_{j}", pre_attn_norm=None, pre_mlp_norm=None, attn_name="attention",
                         post_attn_norm="post_self_attention_layer_norm", post_mlp_norm="post_mlp_layer_norm",
                         window=c.sliding_window_size if (j % 4) != 3 else 0, qk_norm=c.use_qk_norm, query_scalar=c.head_dim ** -0.5,
-                        attn_bias=c.attention_bias) for j in range(cyc)]
+                        global_qk_norm=True, attn_bias=c.attention_bias) for j in range(cyc)]
     return [LayerPlan("layers", blocks) for _ in range(n // cyc)]
   if blk == "llama4":
     # src/maxtext/models/llama4.py:267-420: every nope_layer_interval-th layer has no RoPE, global attention and the
@@ -81,18 +86,20 @@ def layer_plans(c) -> list[LayerPlan]:
       nope = c.nope_layer_interval > 0 and (i + 1) % c.nope_layer_interval == 0
       is_moe = c.num_experts > 1 and (i + 1) % max(1, c.interleave_moe_layer_step) == 0
       plans.append(LayerPlan("layers", [BlockPlan(
-          use_rope=not nope, chunk=0 if nope else int(c.chunk_attn_window_size), l2_qk_norm=bool(c.use_qk_norm) and not nope,
+          use_rope=not nope, chunk=0 if nope else int(c.chunk_attn_window_size), query_scalar=c.head_dim ** -0.5, l2_qk_norm=bool(c.use_qk_norm) and not nope,
           temperature_tuning=bool(c.temperature_tuning) and nope, mlp="moe_shared" if is_moe else "dense",
           mlp_name="Llama4MoEBlock_0" if is_moe else "mlp", moe_style="llama4" if is_moe else "")]))
     return plans
   if blk == "qwen2":
     bp = _llama_like(c, attention=attn)
     bp.attn_bias = True
+    bp.attn_out_bias = False
     return [LayerPlan("layers", [bp]) for _ in range(n)]
   if blk == "mixtral":
     return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="MoeBlock_0")]) for _ in range(n)]
   if blk in ("qwen3_moe", "qwen3_custom_moe"):
-    return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="moe_block")]) for _ in range(n)]
+    return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="moe_block", query_scalar=c.head_dim ** -0.5)])
+            for _ in range(n)]
   if blk == "deepseek":
     nd = c.first_num_dense_layers
     dense = [LayerPlan("dense_layers", [_llama_like(c, attention=attn)]) for _ in range(nd)]
@@ -133,7 +140,7 @@ def layer_plans(c) -> list[LayerPlan]:
     for i in range(n):
       local = (i % 2) == 0
       plans.append(LayerPlan("layers", [BlockPlan(window=c.sliding_window_size if local else 0, attn_bias=True, sinks=True,
-                                                  mlp="moe", mlp_name="GptOssMlp", moe_style="gpt_oss")]))
+                                                  query_scalar=c.head_dim ** -0.5, mlp="moe", mlp_name="GptOssMlp", moe_style="gpt_oss")]))
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "

@@ -50,6 +50,8 @@ class BlockPlan:
   norm_offset: float = 0.0
   parallel_residual: bool = False
   prefix: str = ""                       # extra level in the parameter tree (olmo3: layers_0 .. layers_3 inside one cycle)
+  attn_out_bias: bool | None = None      # None: same as attn_bias (qwen2 has q/k/v biases only)
+  global_qk_norm: bool = False           # olmo3: q/k RMS statistic over all heads instead of per head
   l2_qk_norm: bool = False               # llama4: scale-free RMS normalisation of q and k after RoPE
   temperature_tuning: bool = False       # llama4 NoPE layers: position-dependent query scale
   chunk: int = 0                         # llama4 RoPE layers: attention restricted to chunks of this many tokens
@@ -78,7 +80,8 @@ class DecoderBlock:
       self.attn = L.Attention(b, c, plan.attn_name + s, plan.window, inv_ts, interleaved, plan.use_rope, plan.qk_norm,
                               plan.query_scalar, plan.soft_cap, plan.attn_bias,
                               rotary_dim=None, sinks=plan.sinks, l2_qk_norm=plan.l2_qk_norm,
-                              temperature_tuning=plan.temperature_tuning, chunk=plan.chunk)
+                              temperature_tuning=plan.temperature_tuning, chunk=plan.chunk, out_bias=plan.attn_out_bias,
+                              global_qk_norm=plan.global_qk_norm)
     self.n1b = mk(plan.post_attn_norm) if plan.post_attn_norm else None
     self.n2 = mk(plan.pre_mlp_norm) if plan.pre_mlp_norm else None
     if plan.mlp == "moe":

@@ -79,3 +79,4 @@ def test_checkpoint_cli_roundtrip(tmp_path):
   back = load_file(str(tmp_path / "export" / "model.safetensors"))
   for k, v in hf.state_dict().items():
     assert torch.allclose(back[k], v.float(), atol=1e-5), k
+
