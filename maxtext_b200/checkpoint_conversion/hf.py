@@ -45,6 +45,12 @@ def _locate(pdef, cfg) -> tuple[str, int | None]:
     parts = parts[1:]
     if parts[0] == "attention":
       parts[0] = "self_attention"
+  elif blk == "qwen3_next" and parts[0].startswith("layer_"):
+    cyc = max(1, int(cfg.inhomogeneous_layer_cycle_interval))
+    L = L * cyc + int(parts[0].split("_")[1])
+    parts = parts[1:]
+    if parts[:2] == ["attention", "attention"]:
+      parts = ["self_attention"] + parts[2:]
   elif blk == "gemma2":
     for sfx, j in (("_local", 0), ("_global", 1)):
       if parts[0].endswith(sfx):
@@ -107,6 +113,21 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
       "DeepSeekMoeBlock_0/shared_experts/wi_0/kernel": (pre + "mlp.shared_experts.gate_proj.weight", "linear"),
       "DeepSeekMoeBlock_0/shared_experts/wi_1/kernel": (pre + "mlp.shared_experts.up_proj.weight", "linear"),
       "DeepSeekMoeBlock_0/shared_experts/wo/kernel": (pre + "mlp.shared_experts.down_proj.weight", "linear"),
+      # qwen3-next: gated delta network layers and the gated shared expert
+      "input_layernorm/scale": (pre + "input_layernorm.weight", "norm"),
+      "post_attention_layernorm/scale": (pre + "post_attention_layernorm.weight", "norm"),
+      "attention/in_proj_qkvz/kernel": (pre + "linear_attn.in_proj_qkvz.weight", "linear"),
+      "attention/in_proj_ba/kernel": (pre + "linear_attn.in_proj_ba.weight", "linear"),
+      "attention/conv1d/kernel": (pre + "linear_attn.conv1d.weight", "conv"),
+      "attention/A_log": (pre + "linear_attn.A_log", "vec"),
+      "attention/dt_bias": (pre + "linear_attn.dt_bias", "vec"),
+      "attention/norm/rms_norm/scale": (pre + "linear_attn.norm.weight", "vec"),
+      "attention/out_proj/kernel": (pre + "linear_attn.out_proj.weight", "linear"),
+      "mlp/routed_experts/gate/kernel": (pre + "mlp.gate.weight", "linear"),
+      "mlp/shared_expert/wi_0/kernel": (pre + "mlp.shared_expert.gate_proj.weight", "linear"),
+      "mlp/shared_expert/wi_1/kernel": (pre + "mlp.shared_expert.up_proj.weight", "linear"),
+      "mlp/shared_expert/wo/kernel": (pre + "mlp.shared_expert.down_proj.weight", "linear"),
+      "mlp/shared_expert_gate/kernel": (pre + "mlp.shared_expert_gate.weight", "linear"),
       "GptOssMlp/gate/kernel": (pre + "mlp.router.weight", "linear"),
       "GptOssMlp/gate/bias": (pre + "mlp.router.bias", "vec"),
       "Llama4MoEBlock_0/MoeBlock_0/gate/kernel": (pre + "feed_forward.router.weight", "linear"),
@@ -123,7 +144,7 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
     return hit
   last = path.split("/")[-1]
   if pdef.kind == "experts" or (last in _EXPERT_PART and path.split("/")[0] in
-                                ("MoeBlock_0", "moe_block", "DeepSeekMoeBlock_0", "GptOssMlp", "Llama4MoEBlock_0")):
+                                ("MoeBlock_0", "moe_block", "DeepSeekMoeBlock_0", "GptOssMlp", "Llama4MoEBlock_0", "mlp")):
     return pre, "experts:" + _EXPERT_PART[last]
   return None
 
@@ -220,7 +241,7 @@ def _embed_scale(cfg) -> float:
 def _q_scale(cfg) -> float:
   """Factor folded into the stored query projection: 1/sqrt(head_dim) unless the family scales at run time."""
   if cfg.use_qk_norm or cfg.attention_type == "mla" or cfg.decoder_block in ("gemma3", "qwen3", "qwen3_moe", "qwen3_custom_moe", "olmo3",
-                                                                              "llama4", "gpt_oss"):
+                                                                              "llama4", "gpt_oss", "qwen3_next"):
     return 1.0
   return 1.0 / math.sqrt(cfg.head_dim)
 
@@ -278,6 +299,8 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       w = w + _norm_offset(cfg)
     elif kind == "embed":
       w = w * _embed_scale(cfg)
+    elif kind == "conv":
+      w = w.permute(2, 1, 0)               # HF depthwise filter [channels, 1, kernel] -> [kernel, 1, channels]
     store.load_full(name, p.pdef.local_slice(w.reshape(p.pdef.global_shape())))
   store.sync_compute_from_master()
   return missing
@@ -312,6 +335,8 @@ def to_hf(store, cfg) -> dict:
       w = w - _norm_offset(cfg)
     elif kind == "embed":
       w = w / _embed_scale(cfg)
+    elif kind == "conv":
+      w = w.permute(2, 1, 0)
     out[key] = w.contiguous()
   return out
 

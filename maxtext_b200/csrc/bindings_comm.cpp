@@ -13,6 +13,7 @@ int mt_rs_sumsq(const float* const* peer, long offset, long n, float* dst, int a
                 float* sumsq_out, int ctas, cudaStream_t st);
 int mt_rs_sumsq_mc(const float* mc, long offset, long n, float* dst, int accumulate, float scale, float* partials, float* sumsq_out, int ctas,
                    cudaStream_t st);
+int mt_gather_dma(const long long* peer_ptrs, void* full, long chunk_bytes, int world, int first, cudaStream_t st);
 int mt_gather_segments(const void* const* peer_shards, void* full, long chunk_bytes, long seg_bytes, int world, int* seg_flags, int ctas,
                        cudaStream_t st);
 int mt_gemm_bf16_ag(const void* a, void* c, int M, int N, int K, int64_t lda, int64_t ldc, const void* const* peer_shards, void* full,
@@ -84,6 +85,12 @@ void rs_sumsq_mc(int64_t mc_ptr, int64_t offset, int64_t n, torch::Tensor& dst, 
                              partials.data_ptr<float>(), sumsq_out ? sumsq_out->data_ptr<float>() : nullptr, (int)ctas, cur()) == 0,
               "mt_rs_sumsq_mc failed");
   mt_count_launches(sumsq_out ? 2 : 1);
+}
+
+void gather_dma(const std::vector<int64_t>& peer_ptrs, torch::Tensor& full, int64_t chunk_bytes, int64_t first) {
+  std::vector<long long> p(peer_ptrs.begin(), peer_ptrs.end());
+  TORCH_CHECK((int64_t)p.size() * chunk_bytes <= (int64_t)full.numel() * full.element_size(), "gather_dma: destination too small");
+  TORCH_CHECK(mt_gather_dma(p.data(), full.data_ptr(), chunk_bytes, (int)p.size(), (int)first, cur()) == 0, "mt_gather_dma failed");
 }
 
 void gather_segments(const torch::Tensor& peer_shards, torch::Tensor& full, int64_t chunk_bytes, int64_t seg_bytes, int64_t world,
@@ -174,5 +181,6 @@ void register_comm(pybind11::module_& m) {
   m.def("comm_wait", &comm_wait);
   m.def("rs_sumsq", &rs_sumsq);
   m.def("gather_segments", &gather_segments);
+  m.def("gather_dma", &gather_dma);
   m.def("gemm_ag", &gemm_ag);
 }

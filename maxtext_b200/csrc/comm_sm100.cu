@@ -265,3 +265,14 @@ extern "C" int mt_gather_segments(const void* const* peer_shards, void* full, lo
                                                seg_vec, spc, spc * world, 0, seg_flags);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// The same all-gather issued to the copy engines: one peer-to-local DMA per rank on `st`, no SM time. `peer_ptrs` are host values.
+extern "C" int mt_gather_dma(const long long* peer_ptrs, void* full, long chunk_bytes, int world, int first, cudaStream_t st) {
+  for (int k = 0; k < world; ++k) {
+    const int r = (first + k) % world;               // start at a different peer on every rank so the links are used evenly
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(full) + (long)r * chunk_bytes, reinterpret_cast<const void*>(peer_ptrs[r]), (size_t)chunk_bytes,
+                                    cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return -2;
+  }
+  return 0;
+}

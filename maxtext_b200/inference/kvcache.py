@@ -133,6 +133,10 @@ def make_caches(model, slots: int, max_len: int, device, quantize: bool = False)
     for blk in layer.blocks:
       if blk.plan.attention == "mla":
         per_layer.append(MlaLayerCache(slots, max_len, c.kv_lora_rank, c.qk_rope_head_dim, dt, device))
+      elif blk.plan.attention == "gdn":
+        from ..layers.gdn import GDNState
+        a = blk.attn
+        per_layer.append(GDNState(slots, a.conv_dim, a.K, a.hv, a.dk, a.dv, device))
       else:
         a = blk.attn
         per_layer.append(LayerKVCache(slots, max_len, a.hkv_l, a.dh, a.dh, dt, device, quant))

@@ -125,6 +125,9 @@ class MaxEngine:
         for name in ("k", "v", "ks", "vs", "latent", "k_rope"):
           if hasattr(s, name) and hasattr(d, name):
             getattr(d, name)[slot, :n] = getattr(s, name)[0, :n]
+        for name in ("conv", "rec"):                 # fixed-size recurrent state (gated delta layers)
+          if hasattr(s, name) and hasattr(d, name):
+            getattr(d, name)[slot] = getattr(s, name)[0]
     state.tokens[slot] = prefix.first_token.reshape(-1)[0]
     state.next_pos[slot] = n
     state.active[slot] = True

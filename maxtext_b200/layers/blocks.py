@@ -198,7 +198,8 @@ class Norm:
                kind: str = "rms", axes=("norm",)):
     self.eps, self.offset, self.kind = eps, offset, kind
     nb = b.sub(name)
-    self.scale = nb.vector("scale", dim, axes) if with_scale else None
+    # a scale applied as (offset + scale) starts at zero, so that the effective factor starts at one
+    self.scale = nb.vector("scale", dim, axes, init="zeros" if offset else "ones") if with_scale else None
     self.bias = nb.vector("bias", dim, axes, init="zeros") if kind == "layernorm" else None
 
   def __call__(self, x):
@@ -214,7 +215,7 @@ class Attention:
 
   def __init__(self, b: Builder, config, name="self_attention", window: int = 0, rope_inv_ts=None, interleaved=False,
                use_rope=True, qk_norm=False, query_scalar: float | None = None, soft_cap: float = 0.0, bias=False,
-               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0, out_bias=None, global_qk_norm=False):
+               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0, out_bias=None, global_qk_norm=False, gated=False, qk_norm_offset=0.0):
     c = config
     self.config = c
     self.hq, self.hkv, self.dh, self.d = c.num_query_heads, c.num_kv_heads, c.head_dim, c.emb_dim
@@ -229,18 +230,21 @@ class Attention:
     self.logit_scale = 1.0
     if use_rope and getattr(c, "rope_attention_scaling", False) and str(c.rope_type).lower() == "yarn" and c.rope_factor > 1:
       self.logit_scale = (0.1 * math.log(float(c.rope_factor)) + 1.0) ** 2
-    ab = b.sub(name)
+    # qwen3-next (src/maxtext/layers/attentions.py:685-686,1266-1270,1360-1362): the query projection is twice as wide,
+    # per head [query | gate], and sigmoid(gate) multiplies the attention output before the output projection
+    self.gated = bool(gated)
+    ab = b.sub(*name.split("/"))
     depth_scale = 1.0 if (qk_norm or (query_scalar is not None and query_scalar != 1.0)) else 1.0 / math.sqrt(self.dh)
     kv_tp = "col" if self.hkv >= tp else None
-    self.q = ab.sub("query").linear("kernel", (self.d,), (self.hq, self.dh), ("embed", "q_heads", "kv"), "fan_in_normal",
-                                    depth_scale, tp="col")
+    self.q = ab.sub("query").linear("kernel", (self.d,), (self.hq, self.dh * (2 if self.gated else 1)), ("embed", "q_heads", "kv"),
+                                    "fan_in_normal", depth_scale, tp="col")
     self.k = ab.sub("key").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
                                   "fan_in_normal", tp=kv_tp)
     self.v = ab.sub("value").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
                                     "fan_in_normal", tp=kv_tp)
     self.o = ab.sub("out").linear("kernel", (self.hq, self.dh), (self.d,), ("heads", "kv", "embed"), "fan_in_normal",
                                   tp="row")
-    self.qkv = FusedParam([self.q, self.k, self.v]) if FusedParam.possible([self.q, self.k, self.v]) else None
+    self.qkv = FusedParam([self.q, self.k, self.v]) if (not self.gated and FusedParam.possible([self.q, self.k, self.v])) else None
     self.bq = self.bk = self.bv = None
     if bias:
       self.bq = ab.sub("query").vector("bias", self.hq * self.dh, ("q_heads",), init="zeros", tp=True)
@@ -256,8 +260,8 @@ class Attention:
       self.qn = Norm(ab, "query_norm", self.hq * self.dh, c.normalization_layer_epsilon, axes=("norm",))
       self.kn = Norm(ab, "key_norm", self.hkv * self.dh, c.normalization_layer_epsilon, axes=("norm",))
     elif qk_norm:
-      self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
-      self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, axes=("norm",))
+      self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
+      self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
     self.sinks = ab.vector("sinks", self.hq, ("q_heads",), init="zeros", tp=True) if sinks else None
 
   def _project(self, x, ctx, tp_rt=None):
@@ -273,7 +277,7 @@ class Attention:
     q = ctx.keep("query_proj", F.linear(x, self.q, ctx.reuse("query_proj"), self.bq))
     k = ctx.keep("key_proj", F.linear(x, self.k, ctx.reuse("key_proj"), self.bk))
     v = ctx.keep("value_proj", F.linear(x, self.v, ctx.reuse("value_proj"), self.bv))
-    return None, (q.view(B, S, hq, dh), k.view(B, S, hkv, dh), v.view(B, S, hkv, dh))
+    return None, (q.view(B, S, hq, -1), k.view(B, S, hkv, dh), v.view(B, S, hkv, dh))
 
   def __call__(self, x, ctx):
     B, S, _ = x.shape
@@ -283,7 +287,7 @@ class Attention:
     if not fuse_in:
       x = tp_enter(x, ctx)
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
-    plain = (not self.qk_norm and self.sinks is None and ctx.cache is None and ctx.cp_size == 1
+    plain = (not self.qk_norm and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
@@ -298,6 +302,9 @@ class Attention:
         q, k, v = packed[:, :, :self.hq_l], packed[:, :, self.hq_l:self.hq_l + self.hkv_l], packed[:, :, self.hq_l + self.hkv_l:]
       else:
         q, k, v = sep
+      gate = None
+      if self.gated:
+        q, gate = q[..., :self.dh], q[..., self.dh:].reshape(B, S, -1)
       if self.global_qk_norm:
         q = self.qn(q.reshape(B, S, -1)).view(B, S, self.hq_l, self.dh)
         k = self.kn(k.reshape(B, S, -1)).view(B, S, self.hkv_l, self.dh)
@@ -333,6 +340,8 @@ class Attention:
       else:
         out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window)
     ctx.keep("context", out)
+    if self.gated:
+      out = (out.reshape(B, S, -1).float() * torch.sigmoid(gate.float())).to(out.dtype)
     if tp_rt is not None and ctx.reuse("out_proj") is None and self.bo is None:
       y = F.linear(out.reshape(B, S, -1), self.o, tp_reduce=tp_rt)
     else:

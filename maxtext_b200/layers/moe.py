@@ -244,6 +244,14 @@ class RoutedAndSharedMoE:
 
   def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0", style: str = ""):
     mb = b.sub(name)
+    self.shared_gate = None
+    if style == "qwen3_next":
+      # src/maxtext/models/qwen3.py:1107-1193: softmax top-k router, one shared expert whose output is scaled per token by
+      # sigmoid(x . w_gate)
+      self.routed = RoutedMoE(mb, config, "routed_experts", deepseek_style=False, style="")
+      self.shared = MLP(mb, config, "shared_expert", hidden=config.moe_mlp_dim)
+      self.shared_gate = mb.sub("shared_expert_gate").linear("kernel", (config.emb_dim,), (1,), ("embed", None))
+      return
     self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=(style == ""), style=style)
     self.shared = MLP(mb, config, "shared_experts", hidden=config.shared_experts * config.moe_mlp_dim) \
         if config.shared_experts > 0 else None
@@ -251,5 +259,9 @@ class RoutedAndSharedMoE:
   def __call__(self, x, ctx):
     y = self.routed(x, ctx)
     if self.shared is not None:
-      y = y + self.shared(x, ctx)
+      sh = self.shared(x, ctx)
+      if self.shared_gate is not None:
+        gate = torch.nn.functional.linear(x.float(), self.shared_gate.leaf().float())
+        sh = (sh.float() * torch.sigmoid(gate)).to(sh.dtype)
+      y = y + sh
     return y

@@ -27,6 +27,8 @@ def describe(c) -> Family:
   # src/maxtext/checkpoint_conversion/utils/param_mapping.py:498-508)
   if blk == "gpt3":
     return Family(norm_kind="layernorm")
+  if blk == "qwen3_next":
+    return Family(norm_offset=1.0)           # every RMS scale is stored zero-centred and applied as (1 + scale)
   return Family()
 
 
@@ -100,6 +102,20 @@ def layer_plans(c) -> list[LayerPlan]:
   if blk in ("qwen3_moe", "qwen3_custom_moe"):
     return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="moe_block", query_scalar=c.head_dim ** -0.5)])
             for _ in range(n)]
+  if blk == "qwen3_next":
+    # src/maxtext/models/qwen3.py:1196-1420: cycles of inhomogeneous_layer_cycle_interval layers form one scanned block with
+    # sub-trees layer_0 .. layer_{n-1}; the last layer of a cycle is gated full attention (partial RoPE, zero-centred
+    # per-head q/k norms), the others are gated delta networks; every layer has the routed + gated shared expert MLP
+    cyc = max(1, int(c.inhomogeneous_layer_cycle_interval))
+    assert n % cyc == 0, "qwen3_next layers must be a multiple of inhomogeneous_layer_cycle_interval"
+    blocks = []
+    for j in range(cyc):
+      full = (j + 1) % cyc == 0
+      blocks.append(BlockPlan(prefix=f"layer_{j}", pre_attn_norm="input_layernorm", pre_mlp_norm="post_attention_layernorm",
+                              attention="gqa" if full else "gdn", attn_name="attention/attention" if full else "attention",
+                              gated_attn=full, qk_norm=full, query_scalar=c.head_dim ** -0.5 if full else None, norm_offset=1.0,
+                              mlp="moe_shared", mlp_name="mlp", moe_style="qwen3_next"))
+    return [LayerPlan("layers", blocks) for _ in range(n // cyc)]
   if blk == "deepseek":
     nd = c.first_num_dense_layers
     dense = [LayerPlan("dense_layers", [_llama_like(c, attention=attn)]) for _ in range(nd)]
@@ -144,4 +160,4 @@ def layer_plans(c) -> list[LayerPlan]:
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, gpt3, gpt_oss, olmo3, llama4, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, gpt3, gpt_oss, olmo3, llama4, simple)")

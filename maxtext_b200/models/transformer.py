@@ -34,7 +34,8 @@ class BlockPlan:
   post_mlp_norm: str | None = None
   attn_name: str = "self_attention"
   mlp_name: str = "mlp"
-  attention: str = "gqa"                 # gqa | mla
+  attention: str = "gqa"                 # gqa | mla | gdn (gated delta network, qwen3-next)
+  gated_attn: bool = False               # qwen3-next full attention: sigmoid output gate from a widened query projection
   window: int = 0
   rope: str = "default"                  # key into Transformer.rope_tables
   use_rope: bool = True
@@ -74,14 +75,18 @@ class DecoderBlock:
     mk = lambda n: L.Norm(b, n + s, c.emb_dim, eps, plan.norm_offset, kind=plan.norm_kind)  # noqa: E731
     self.n1 = mk(plan.pre_attn_norm) if plan.pre_attn_norm else None
     inv_ts, interleaved = rope_tables[plan.rope]
+    rot = int(c.head_dim * c.partial_rotary_factor) if 0 < c.partial_rotary_factor < 1.0 else None
     if plan.attention == "mla":
       self.attn = L.MLA(b, c, inv_ts, interleaved, plan.attn_name + s)
+    elif plan.attention == "gdn":
+      from ..layers.gdn import GatedDeltaNet
+      self.attn = GatedDeltaNet(b, c, plan.attn_name + s)
     else:
       self.attn = L.Attention(b, c, plan.attn_name + s, plan.window, inv_ts, interleaved, plan.use_rope, plan.qk_norm,
                               plan.query_scalar, plan.soft_cap, plan.attn_bias,
-                              rotary_dim=None, sinks=plan.sinks, l2_qk_norm=plan.l2_qk_norm,
+                              rotary_dim=rot, sinks=plan.sinks, l2_qk_norm=plan.l2_qk_norm,
                               temperature_tuning=plan.temperature_tuning, chunk=plan.chunk, out_bias=plan.attn_out_bias,
-                              global_qk_norm=plan.global_qk_norm)
+                              global_qk_norm=plan.global_qk_norm, gated=plan.gated_attn, qk_norm_offset=plan.norm_offset)
     self.n1b = mk(plan.post_attn_norm) if plan.post_attn_norm else None
     self.n2 = mk(plan.pre_mlp_norm) if plan.pre_mlp_norm else None
     if plan.mlp == "moe":

@@ -55,7 +55,7 @@ class ParamDef:
   logical_axes: tuple            # logical names of the reference dims
   kind: str = "linear"           # "linear": ref [in..,out..] <-> internal [out,in]; "same": identical layout
   n_in_dims: int = 1             # for kind=linear: how many leading ref dims are "in"
-  init: str = "fan_in_trunc"     # fan_in_trunc | fan_in_normal | embed | ones | zeros | normal
+  init: str = "fan_in_trunc"     # fan_in_trunc | fan_in_normal | embed | ones | zeros | normal | log_uniform_16
   init_scale: float = 1.0
   layer: int | None = None       # index along the stacked layer axis
   stack: str | None = None       # name of the stacked collection in the reference tree ("layers", "dense_layers"...)
@@ -191,6 +191,10 @@ def init_full_tensor(pdef: ParamDef, device, base_seed: int, mode: str = "refere
     return torch.ones(pdef.shape, dtype=torch.float32, device=device)
   if pdef.init == "zeros":
     return torch.zeros(pdef.shape, dtype=torch.float32, device=device)
+  if pdef.init == "log_uniform_16":
+    # decay rates of the gated delta network: log of U(0, 16) (src/maxtext/models/qwen3.py:547-552)
+    t = torch.empty(pdef.global_shape(), dtype=torch.float32, device=device).uniform_(1e-9, 16.0, generator=gen)
+    return pdef.local_slice(torch.log(t)).contiguous()
   # draw the whole tensor, then keep this rank's tensor/expert-parallel slice: values do not depend on the mesh
   t = torch.empty(pdef.global_shape(), dtype=torch.float32, device=device)
   if mode == "normal" or pdef.init == "normal":
@@ -402,7 +406,7 @@ class ParamStore:
       buf = self.acquire_full(u)
       u.full, u.resident = buf, True
       self._views_into(u, buf, "data")
-      if self.ag_mode == "prefetch":
+      if self.ag_mode in ("prefetch", "dma"):
         # gather now, on the gather stream: it may start as soon as the compute stream no longer reads this pooled buffer
         from ..ops import backend
         # order after everything already enqueued on the compute stream: the previous user of this pooled buffer and, at the
@@ -411,7 +415,12 @@ class ParamStore:
         self.ag_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.ag_stream):
           esz = u.full.element_size()
-          backend.ext().gather_segments(self.peer_table(u), u.full, u.chunk * esz, self.seg_elems * esz, u.group_size, 32)
+          if self.ag_mode == "dma":
+            # copy engines instead of SMs: one peer-to-local copy per rank, the compute kernels keep every SM
+            ptrs = [int(a) + u.shard_offset * esz for a in self._cs.ptrs]
+            backend.ext().gather_dma(ptrs, u.full, u.chunk * esz, (self.symm.rank + 1) % u.group_size)
+          else:
+            backend.ext().gather_segments(self.peer_table(u), u.full, u.chunk * esz, self.seg_elems * esz, u.group_size, 32)
           done = torch.cuda.Event()
           done.record(self.ag_stream)
         if not async_op:

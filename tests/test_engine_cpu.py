@@ -29,7 +29,8 @@ def test_family_trains_and_gradient_matches_directional_derivative(model):
   assert torch.isfinite(g).all()
   v = torch.randn_like(g)
   v = v / v.norm()
-  eps = 5e-3 if model.startswith(("llama4", "qwen3-30b")) else 2e-2     # routed models: a larger step crosses routing flips (the loss jumps)
+  # routed models: a larger step crosses routing flips (the loss jumps)
+  eps = 1e-3 if model.startswith("qwen3-next") else 5e-3 if model.startswith(("llama4", "qwen3-30b")) else 2e-2
   w0 = store.master.clone()
   store.master.copy_(w0 + eps * v)
   store.sync_compute_from_master()

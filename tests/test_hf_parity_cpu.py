@@ -3,7 +3,7 @@
 A randomly initialised tiny HF model is converted with `checkpoint_conversion.hf.to_maxtext` and both models score
 the same tokens in fp32; the logits must agree to rounding. This is the CPU analogue of MaxText's golden-logit
 check (tests/utils/forward_pass_logit_checker.py) and covers, per family, the attention variant (GQA / MLA / sinks /
-sliding and chunked windows / per-head, all-head and scale-free q-k norms), the rotary variant (plain, llama-3.1
+sliding and chunked windows / per-head, all-head and scale-free q-k norms / gated delta network with gated full attention), the rotary variant (plain, llama-3.1
 and linear scaling, YaRN with attention scaling, adjacent-pair lanes), the router (softmax top-k, sigmoid with
 groups and bias, top-1 sigmoid, biased logits) and the expert tensor layouts of the converter.
 """
@@ -132,7 +132,18 @@ def _llama4(_):
   return cfg, transformers.Llama4ForCausalLM, hc
 
 
-CASES = {"gemma": _gemma, "gemma2": _gemma2, "gemma3": _gemma3, "qwen2": _qwen2, "qwen3": _qwen3, "qwen3_moe": _qwen3_moe,
+def _qwen3_next(_):
+  cfg = _tiny("qwen3-next-80b-a3b", ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32",
+                                     "gdn_key_head_dim=8", "gdn_value_head_dim=8", "gdn_num_key_heads=2", "gdn_num_value_heads=4",
+                                     "gdn_chunk_size=8"])
+  hc = transformers.Qwen3NextConfig(**_common(
+      cfg, num_hidden_layers=4, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+      linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4,
+      rope_parameters={"rope_theta": float(cfg.rope_max_timescale), "partial_rotary_factor": 0.25, "rope_type": "default"}))
+  return cfg, transformers.Qwen3NextForCausalLM, hc
+
+
+CASES = {"qwen3_next": _qwen3_next, "gemma": _gemma, "gemma2": _gemma2, "gemma3": _gemma3, "qwen2": _qwen2, "qwen3": _qwen3, "qwen3_moe": _qwen3_moe,
          "mistral": _mistral, "deepseek3": _deepseek3, "gpt_oss": _gpt_oss, "olmo3": _olmo3, "llama4": _llama4}
 
 
@@ -141,7 +152,9 @@ def _randomise(hf):
   give all of them values that a wrong mapping cannot reproduce by accident."""
   g = torch.Generator().manual_seed(1)
   for n, p in hf.named_parameters():
-    if "norm" in n:
+    if "conv1d" in n or "dt_bias" in n:
+      p.data = 0.5 + 0.2 * torch.randn(p.shape, generator=g)
+    elif "norm" in n:
       p.data = 1.0 + 0.1 * torch.randn(p.shape, generator=g)
     elif "bias" in n or "sinks" in n:
       p.data = 0.1 * torch.randn(p.shape, generator=g)
