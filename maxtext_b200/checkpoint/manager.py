@@ -345,6 +345,9 @@ def _restore_tree(io: TreeIO, items: str, engine, full_state: bool):
       missing.append(p.name)
       continue
     store.load_full(p.name, t.to(store.device))
+  if not full_state:
+    # a base-model checkpoint loaded under LoRA has no adapter tensors: those keep their initial value
+    missing = [n for n in missing if not n.endswith(("_lora_a", "_lora_b"))]
   if missing:
     raise KeyError(f"checkpoint {items} lacks {len(missing)} parameters, e.g. {missing[:4]}")
   store.sync_compute_from_master()

@@ -20,6 +20,41 @@ from ..parallel.param_store import Param, ParamDef, ALIGN
 
 
 # ------------------------------------------------------------------------------------------ param helpers
+class LoraSpec:
+  """Which linears get a low-rank adapter (`lora: {enable_lora, lora_rank, lora_alpha, lora_module_path}`,
+  src/maxtext/configs/types.py:1575-1600). `lora_module_path` is a regular expression searched in the module path,
+  e.g. `layers/.*(self_attention/(query|out)|mlp/(wi_0|wo))`; empty selects the attention and dense-MLP projections."""
+
+  DEFAULT = r"(self_attention|attention)/(query|key|value|out)|mlp/(wi_0|wi_1|wo)"
+
+  def __init__(self, d: dict):
+    import re
+    self.rank = int(d.get("lora_rank", 0))
+    self.alpha = float(d.get("lora_alpha", 0.0)) or float(self.rank)
+    self.pattern = re.compile(d.get("lora_module_path") or self.DEFAULT)
+    assert self.rank > 0, "enable_lora needs lora_rank > 0"
+
+  def matches(self, b: "Builder", leaf: str) -> bool:
+    if leaf != "kernel" or b.layer is None:
+      return False
+    path = "/".join((str(b.stack),) + tuple(b.prefix))
+    return self.pattern.search(path) is not None
+
+
+def lora_spec(config) -> LoraSpec | None:
+  d = getattr(config, "lora", None) or {}
+  if not isinstance(d, dict) or not d.get("enable_lora"):
+    return None
+  s = getattr(config, "_lora_spec", None)
+  if s is None:
+    s = LoraSpec(d)
+    try:
+      object.__setattr__(config, "_lora_spec", s)
+    except Exception:  # pylint: disable=broad-except
+      pass
+  return s
+
+
 class Builder:
   """Collects ParamDefs for one unit while layers are constructed."""
 
@@ -57,8 +92,19 @@ class Builder:
     elif tp == "row" and self.tp_size > 1:
       assert in_shape[0] % self.tp_size == 0
       li, tp_dim = n_in // self.tp_size, 1
-    return self._add(leaf, shape=(lo, li), ref_shape=in_shape + out_shape, logical_axes=tuple(axes), kind="linear",
-                     n_in_dims=len(in_shape), init=init, init_scale=init_scale, tp_dim=tp_dim)
+    p = self._add(leaf, shape=(lo, li), ref_shape=in_shape + out_shape, logical_axes=tuple(axes), kind="linear",
+                  n_in_dims=len(in_shape), init=init, init_scale=init_scale, tp_dim=tp_dim)
+    spec = lora_spec(self.config)
+    if spec is not None and spec.matches(self, leaf):
+      # W x + (alpha / r) B (A x): A [r, in] drawn like a dense kernel, B [out, r] zero, so training starts at the base model
+      assert self.tp_size == 1, "LoRA adapters are not split over the tensor axis"
+      r = spec.rank
+      a = self._add(leaf + "_lora_a", shape=(r, li), ref_shape=in_shape + (r,), logical_axes=tuple(axes[:len(in_shape)]) + (None,),
+                    kind="linear", n_in_dims=len(in_shape), init="fan_in_normal")
+      b = self._add(leaf + "_lora_b", shape=(lo, r), ref_shape=(r,) + out_shape, logical_axes=(None,) + tuple(axes[len(in_shape):]),
+                    kind="linear", n_in_dims=1, init="zeros")
+      p.lora = (a, b, spec.alpha / r)
+    return p
 
   def vector(self, leaf, n, axes=("norm",), init="ones", tp=False) -> Param:
     ln = n // self.tp_size if tp and self.tp_size > 1 else n
@@ -92,7 +138,13 @@ class FusedParam:
   @staticmethod
   def possible(parts: list[Param]) -> bool:
     cols = parts[0].shape[-1]
+    if any(p.lora is not None for p in parts) or len({p.pdef.frozen for p in parts}) > 1:
+      return False                           # adapters are per projection; a run is trained or frozen as a whole
     return all(len(p.shape) == 2 and p.shape[1] == cols and p.pdef.numel % ALIGN == 0 for p in parts)
+
+  @property
+  def frozen(self):
+    return self.parts[0].pdef.frozen
 
   def _span(self, attr):
     first = getattr(self.parts[0], attr)

@@ -223,6 +223,11 @@ class Transformer:
       self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
                                                                    ("embed_vocab", "vocab"))
     self.head_params = hb.params if self.has_head else []
+    if L.lora_spec(c) is not None:
+      # LoRA fine-tuning: everything but the adapters keeps its value (no gradient, no weight decay)
+      for p in self.all_params():
+        if not p.pdef.name.endswith(("_lora_a", "_lora_b")):
+          p.pdef.frozen = True
     self.store: ParamStore | None = None
     if build_store:
       self.store = ParamStore(self.all_params(), mesh or _SingleMesh(), c, self.device)

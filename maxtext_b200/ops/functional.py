@@ -93,7 +93,7 @@ class _LinearFn(torch.autograd.Function):
     if not dy2.is_contiguous():
       dy2 = dy2.contiguous()
     if getattr(ctx, "fp8", False) and ctx.tp_reduce_dx is None and _quant.supported(dy2, w):
-      go = pv.main_grad.view(w.shape) if (pv is not None and pv.main_grad is not None) else None
+      go = pv.main_grad.view(w.shape) if (pv is not None and pv.main_grad is not None and not getattr(pv, "frozen", False)) else None
       dx = _quant.linear_bwd(dy2, x2, w, bool(ctx.needs_input_grad[0]), go, bool(pv.grad_written) if go is not None else False, pv,
                              getattr(ctx, "fp8_saved", None))
       ctx.fp8_saved = None
@@ -107,7 +107,7 @@ class _LinearFn(torch.autograd.Function):
       dx = ctx.tp_reduce_dx.all_reduce_gemm(dy2, w, False)      # column-parallel input gradient: summed over the TP ranks in the GEMM
     else:
       dx = mm(dy2, w, False, False)
-    if pv is not None and pv.main_grad is not None:
+    if pv is not None and pv.main_grad is not None and not getattr(pv, "frozen", False):
       mm(dy2, x2, True, False, out=pv.main_grad.view(w.shape), accumulate=pv.grad_written)
       pv.grad_written = True
     dbias = dy2.float().sum(0) if ctx.has_bias else None
@@ -130,13 +130,28 @@ def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None,
     pre = tp_reduce.all_reduce_gemm(x2, p.data, True)
   elif pend is not None and saved_out is None and b is None:
     pre = pend.store.ag_linear(pend, p, x2)
+  lo = getattr(p, "lora", None)
   if not torch.is_grad_enabled():
     if saved_out is not None:
       return saved_out
     y = (pre if pre is not None else (_quant.linear_fwd(x2, p.data, p) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
+    if lo is not None:
+      y = y + _lora_delta(x2, lo).to(y.dtype)
     y = y.view(*x.shape[:-1], p.shape[0])
     return y + b.to(y.dtype) if b is not None else y
-  return _LinearFn.apply(x2, p.data, p, saved_out, b, pre, tp_reduce_dx).view(*x.shape[:-1], p.shape[0])
+  y = _LinearFn.apply(x2, p.data, p, saved_out, b, pre, tp_reduce_dx)
+  if lo is not None:
+    d = _lora_delta(x2, lo).to(y.dtype)
+    # a kept output already contains the adapter's contribution: add only its gradient path
+    y = y + (d - d.detach() if saved_out is not None else d)
+  return y.view(*x.shape[:-1], p.shape[0])
+
+
+def _lora_delta(x2: torch.Tensor, lo) -> torch.Tensor:
+  """scale * (x A^T) B^T for a low-rank adapter (A [r, in], B [out, r]); both products go through `linear`, so the
+  adapters' gradients land in their fp32 accumulators like any other weight's."""
+  a, b, scale = lo
+  return linear(linear(x2, a), b) * scale
 
 
 # =============================================================================== RMSNorm

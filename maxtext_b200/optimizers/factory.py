@@ -34,8 +34,18 @@ class AdamW(_Base):
 
   def step(self, grad_scale, lr, step, **kw):
     c, s = self.c, self.store
+    wd = c.adam_weight_decay
+    trainable = s.trainable_slices()
+    if trainable is not None:
+      # some parameters are frozen (LoRA): their gradient is exactly zero, so with no decay term the fused update leaves them
+      # untouched; the decoupled decay w <- w (1 - lr wd) is applied to the trainable ranges first, which gives the same result
+      # as the fused form w - lr (u + wd w)
+      if wd:
+        for a, b in trainable:
+          s.master[a:b].mul_(1.0 - lr * wd)
+      wd = 0.0
     F.adamw_flat(s.master, s.grad_shard, s.exp_avg, s.exp_avg_sq, s.compute_shard, lr, c.adam_b1, c.adam_b2, c.adam_eps,
-                 c.adam_eps_root, c.adam_weight_decay, step, grad_scale, pax=self.pax)
+                 c.adam_eps_root, wd, step, grad_scale, pax=self.pax)
     return {}
 
   def state_arrays(self):

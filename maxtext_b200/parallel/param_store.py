@@ -60,6 +60,7 @@ class ParamDef:
   layer: int | None = None       # index along the stacked layer axis
   stack: str | None = None       # name of the stacked collection in the reference tree ("layers", "dense_layers"...)
   weight_decay: bool = True
+  frozen: bool = False           # never trained (base weights under LoRA): gradient forced to zero, no weight decay
   tp_dim: int | None = None      # internal dim split over tensor axes (already applied to `shape`)
   ep_dim: int | None = None      # internal dim split over the expert axis (already applied)
   fsdp_axes: tuple = ()          # mesh axes of the flat shard group (filled by the store)
@@ -96,7 +97,7 @@ class Param:
   """Handle given to layer code. `.data` is the compute-dtype tensor (valid while the unit is
   resident), `.main_grad` the fp32 gradient accumulator view (valid during backward)."""
 
-  __slots__ = ("pdef", "_data", "main_grad", "grad_written", "_leaf", "unit")
+  __slots__ = ("pdef", "_data", "main_grad", "grad_written", "_leaf", "unit", "lora")
 
   def __init__(self, pdef: ParamDef):
     self.pdef = pdef
@@ -105,6 +106,7 @@ class Param:
     self.grad_written = False
     self._leaf = None
     self.unit = None          # set by the store
+    self.lora = None          # (A, B, scale) low-rank adapter params of a linear, see layers.blocks.Builder.linear
 
   @property
   def data(self):
@@ -128,19 +130,25 @@ class Param:
     return self.pdef.name
 
   @property
+  def frozen(self):
+    return self.pdef.frozen
+
+  @property
   def shape(self):
     return self.pdef.shape
 
   def leaf(self) -> torch.Tensor:
     """An autograd leaf aliasing `.data` for ops that rely on plain PyTorch differentiation; its
     `.grad` is folded into `main_grad` by `collect_leaf_grads` after the unit's backward."""
-    if not torch.is_grad_enabled():
+    if not torch.is_grad_enabled() or self.pdef.frozen:
       return self.data
     if self._leaf is None or self._leaf.data_ptr() != self.data.data_ptr():
       self._leaf = self.data.detach().requires_grad_(True)
     return self._leaf
 
   def accumulate_grad(self, g: torch.Tensor):
+    if self.pdef.frozen:
+      return
     if self.grad_written:
       self.main_grad.add_(g.reshape(self.main_grad.shape))
     else:
@@ -340,6 +348,23 @@ class ParamStore:
         u.resident = True
         self._views_into(u, u.full, "data")
 
+  def trainable_slices(self):
+    """None when every parameter trains; else the [a, b) ranges of this rank's flat shard that belong to trainable ones."""
+    cached = getattr(self, "_trainable", False)
+    if cached is not False:
+      return cached
+    out = None
+    if any(p.pdef.frozen for u in self.units.values() for p in u.params):
+      out = []
+      for u in self.units.values():
+        lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+        for p, off in zip(u.params, u.offsets):
+          a, b = max(off, lo), min(off + p.pdef.numel, hi)
+          if not p.pdef.frozen and a < b:
+            out.append((u.shard_offset + a - lo, u.shard_offset + b - lo))
+    self._trainable = out
+    return out
+
   def shard_view(self, u: Unit, flat: torch.Tensor) -> torch.Tensor:
     return flat[u.shard_offset: u.shard_offset + u.chunk]
 
@@ -497,7 +522,7 @@ class ParamStore:
   def _fused_reduce_scatter(self, u: Unit, accumulate: bool):
     from ..ops import backend
     for p in u.params:
-      if not p.grad_written:
+      if not p.grad_written or p.pdef.frozen:
         p.main_grad.zero_()
     b = u.grad_slot
     dst = self.shard_view(u, self.grad_shard)
@@ -566,8 +591,8 @@ class ParamStore:
       return
     if self.fused:
       return self._fused_reduce_scatter(u, accumulate)
-    for p in u.params:              # parameters never touched this step contribute zeros
-      if not p.grad_written:
+    for p in u.params:              # parameters never touched this step, and frozen ones, contribute zeros
+      if not p.grad_written or p.pdef.frozen:
         p.main_grad.zero_()
     dst = self.shard_view(u, self.grad_shard)
     full = u.full_grad
@@ -620,7 +645,7 @@ class ParamStore:
     for u in self.units.values():
       if u.group_size == 1:
         for p in u.params:
-          if not p.grad_written:
+          if not p.grad_written or p.pdef.frozen:
             p.main_grad.zero_()
             p.grad_written = True
 

@@ -92,6 +92,14 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
       start_step = restored
   elif c.load_parameters_path:
     ckpt_lib.load_params_only(c.load_parameters_path, engine)
+  lora_cfg = getattr(c, "lora", None) or {}
+  lora_on = isinstance(lora_cfg, dict) and bool(lora_cfg.get("enable_lora"))
+  if lora_on and start_step == 0:
+    # adapters from an earlier run (PEFT directory); ignored when this run resumes from its own checkpoint
+    adapter_dir = lora_cfg.get("lora_restore_path") or c.hf_lora_adapter_path
+    if adapter_dir:
+      from ..utils import lora_utils
+      lora_utils.load_adapter(adapter_dir, engine.store, c)
   engine.step_count = start_step
   is_cuda = engine.device.type == "cuda"
   stepper = engine
@@ -136,6 +144,17 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
       if clean and c.save_checkpoint_on_completion:
         ckpt.save(engine.step_count - 1, data_iterator, force=True)
       ckpt.wait_until_finished()
+    if lora_on and clean:
+      from ..utils import lora_utils
+      state, acfg = lora_utils.to_peft(engine.store, c)            # collective: every rank takes part in the gathers
+      if rank == 0 and c.base_output_directory:
+        import json
+        from safetensors.torch import save_file
+        out_dir = os.path.join(c.base_output_directory, c.run_name, "lora_adapter")
+        os.makedirs(out_dir, exist_ok=True)
+        save_file(state, os.path.join(out_dir, "adapter_model.safetensors"))
+        with open(os.path.join(out_dir, "adapter_config.json"), "w") as fh:
+          json.dump(acfg, fh, indent=1)
     logger.close()
     prof.close()
     recorder.close()
