@@ -66,10 +66,40 @@ def _locate(pdef, cfg) -> tuple[str, int | None]:
 _EXPERT_PART = {"wi_0": "gate", "wi_1": "up", "wo": "down", "wi_0_bias": "gate_bias", "wi_1_bias": "up_bias", "wo_bias": "down_bias"}
 
 
+def _vision_name(path: str) -> tuple[str, str] | None:
+  """Gemma-3 vision tower and projector (HF: SigLIP under model.vision_tower, model.multi_modal_projector)."""
+  import re
+  vt = "model.vision_tower.vision_model."
+  if path.startswith("vision_encoder/VisionEmbedder_0/"):
+    return {"mm_soft_embedding_norm/scale": ("model.multi_modal_projector.mm_soft_emb_norm.weight", "norm"),
+            "mm_input_projection/w": ("model.multi_modal_projector.mm_input_projection_weight", "linear_io")}.get(path.split("/", 2)[2])
+  rest = path.split("/", 2)[2]
+  top = {"embedding/kernel": (vt + "embeddings.patch_embedding.weight", "patch"),
+         "embedding/bias": (vt + "embeddings.patch_embedding.bias", "vec"),
+         "pos_embedding": (vt + "embeddings.position_embedding.weight", "vec"),
+         "Transformer/encoder_norm/scale": (vt + "post_layernorm.weight", "vec"),
+         "Transformer/encoder_norm/bias": (vt + "post_layernorm.bias", "vec")}
+  if rest in top:
+    return top[rest]
+  m = re.match(r"Transformer/encoderblock_(\d+)/(.+)", rest)
+  if not m:
+    return None
+  pre = f"{vt}encoder.layers.{m.group(1)}."
+  sub = {"LayerNorm_0": "layer_norm1", "LayerNorm_1": "layer_norm2", "MultiHeadDotProductAttention_0/query": "self_attn.q_proj",
+         "MultiHeadDotProductAttention_0/key": "self_attn.k_proj", "MultiHeadDotProductAttention_0/value": "self_attn.v_proj",
+         "MultiHeadDotProductAttention_0/out": "self_attn.out_proj", "MlpBlockViT_0/Dense_0": "mlp.fc1", "MlpBlockViT_0/Dense_1": "mlp.fc2"}
+  mod, leaf = m.group(2).rsplit("/", 1)
+  if mod not in sub:
+    return None
+  return pre + sub[mod] + (".bias" if leaf == "bias" else ".weight"), ("linear" if leaf == "kernel" else "vec")
+
+
 def _hf_name(pdef, cfg) -> tuple[str, str] | None:
   """(hf key, kind) for one of our parameters. Kinds: linear, vec, norm, embed, q, k, qbias, kbias, and
   experts:<part> for stacked expert tensors (the key is then the HF layer prefix)."""
   path, L = _locate(pdef, cfg)
+  if path.startswith("vision_encoder/"):
+    return _vision_name(path)
   pre = f"model.layers.{L}." if L is not None else ""
   blk = cfg.decoder_block
   sandwich = blk in ("gemma2", "gemma3")
@@ -274,6 +304,8 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
         continue
       store.load_full(name, p.pdef.local_slice(w.contiguous().reshape(p.pdef.global_shape())))
       continue
+    if key not in hf_state and key.startswith("model.") and "model.language_model." + key[6:] in hf_state:
+      key = "model.language_model." + key[6:]          # multimodal checkpoints nest the text model one level deeper
     if key not in hf_state:
       for a, b_ in _ALIASES:
         if a in key and key.replace(a, b_) in hf_state:
@@ -301,6 +333,10 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       w = w * _embed_scale(cfg)
     elif kind == "conv":
       w = w.permute(2, 1, 0)               # HF depthwise filter [channels, 1, kernel] -> [kernel, 1, channels]
+    elif kind == "patch":
+      w = w.permute(0, 2, 3, 1)            # HF conv [out, C, P, P] -> rows ordered (py, px, C) like the patch cutter
+    elif kind == "linear_io":
+      w = w.t()                            # stored [in, out] on the HF side
     store.load_full(name, p.pdef.local_slice(w.reshape(p.pdef.global_shape())))
   store.sync_compute_from_master()
   return missing
@@ -337,6 +373,13 @@ def to_hf(store, cfg) -> dict:
       w = w / _embed_scale(cfg)
     elif kind == "conv":
       w = w.permute(2, 1, 0)
+    elif kind == "patch":
+      P = cfg.patch_size_for_vit
+      w = w.view(w.shape[0], P, P, -1).permute(0, 3, 1, 2)
+    elif kind == "linear_io":
+      w = w.t()
+    elif key.endswith("position_embedding.weight"):
+      w = w.reshape(-1, w.shape[-1])
     out[key] = w.contiguous()
   return out
 

@@ -18,10 +18,20 @@ def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -
     eng.load_params()
   tok = build_tokenizer(config)
   ids = tok.encode(prompt if prompt is not None else config.prompt, add_bos=bool(config.add_bos))
+  mm_kw = {}
+  if bool(getattr(config, "use_multimodal", False)) and str(getattr(config, "image_path", "") or ""):
+    # one <start_of_image> in the prompt per file of image_path; each grows to 260 positions (256 of them soft tokens)
+    from ..multimodal import processor_gemma3 as pg
+    paths = [p for p in str(config.image_path).split(",") if p]
+    if ids.count(pg.BEGIN_IMAGE_TOKEN) < len(paths):
+      ids = ids + [pg.BEGIN_IMAGE_TOKEN] * (len(paths) - ids.count(pg.BEGIN_IMAGE_TOKEN))
+    t_ids, mask, pix = pg.prepare(ids, paths, int(config.image_size_for_vit))
+    ids = t_ids.tolist()
+    mm_kw = dict(images=pix, image_mask=torch.nn.functional.pad(mask, (0, max(0, int(config.max_prefill_predict_length) - len(ids)))))
   ids = [i % config.vocab_size for i in ids][: int(config.max_prefill_predict_length)]
   n = len(ids)
   padded = torch.tensor(ids + [0] * (int(config.max_prefill_predict_length) - n), dtype=torch.long)
-  prefix, first = eng.prefill(padded, n)
+  prefix, first = eng.prefill(padded, n, **mm_kw)
   state = eng.insert(prefix, eng.init_decode_state(1), 0)
   out = [int(first.data[0, 0])]
   for _ in range(n, int(config.max_target_length) - 1):

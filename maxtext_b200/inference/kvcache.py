@@ -93,6 +93,11 @@ class LayerKVCache:
     mask = ref.attention_mask(pos, kv_pos, None, None, True, window) & (kv_pos < valid_len)[:, None, None, :]
     if ctx.segment_ids is not None and ctx.mode == "prefill":
       mask = mask & (ctx.segment_ids[:, None, :, None] != 0)
+    if getattr(ctx, "bidir", None) is not None and ctx.bidir.shape[-2] == S and ctx.bidir.shape[-1] <= upto:
+      # multimodal prefill from an empty cache: the soft tokens of one image see each other in both directions
+      extra = torch.zeros_like(mask)
+      extra[..., : ctx.bidir.shape[-1]] = ctx.bidir
+      mask = mask | (extra & (kv_pos < valid_len)[:, None, None, :])
     return ref.attention(q, K, V, mask, 1.0, soft_cap, sinks=sinks.data if sinks is not None else None)
 
 

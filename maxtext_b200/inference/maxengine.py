@@ -87,14 +87,18 @@ class MaxEngine:
 
   # ------------------------------------------------------------------ prefill / insert / generate
   @torch.no_grad()
-  def prefill(self, padded_tokens: torch.Tensor, true_length: int, params=None) -> tuple[Prefix, ResultTokens]:
-    """padded_tokens [P] (right padded); only the first `true_length` enter the cache."""
+  def prefill(self, padded_tokens: torch.Tensor, true_length: int, params=None, images=None, image_mask=None) -> tuple[Prefix, ResultTokens]:
+    """padded_tokens [P] (right padded); only the first `true_length` enter the cache. `images` [N, 3, H, W] with
+    `image_mask` [P] (True at the soft-token positions of the prompt) makes the prompt multimodal."""
     dev = self.device
     toks = padded_tokens[:true_length].to(dev).long()[None]
     caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, true_length), dev)
     self._bind(caches, torch.zeros(1, dtype=torch.long, device=dev), torch.zeros(1, dtype=torch.long, device=dev))
     pos = torch.arange(true_length, device=dev)[None]
-    logits = self.model.forward(toks, pos, None, mode="prefill", caches=caches)[:, -1]
+    mm_kw = {}
+    if images is not None:
+      mm_kw = dict(images=images[None].to(dev), image_mask=image_mask[:true_length][None].to(dev))
+    logits = self.model.forward(toks, pos, None, mode="prefill", caches=caches, **mm_kw)[:, -1]
     tok = self._sample(logits)
     lp = inference_utils.log_prob_of(logits, tok) if self.config.return_log_prob else None
     res = ResultTokens(torch.tensor([[int(tok), 1, 1]], device=dev), lp)

@@ -223,6 +223,17 @@ class Transformer:
       self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
                                                                    ("embed_vocab", "vocab"))
     self.head_params = hb.params if self.has_head else []
+    # multimodal: the vision tower is a unit of its own; it is frozen unless freeze_vision_encoder_params is off
+    self.vision, self.vision_params = None, []
+    if bool(getattr(c, "use_multimodal", False)) and self.has_embed:
+      if (getattr(c, "vision_encoder_block", "") or c.decoder_block) != "gemma3":
+        raise NotImplementedError("use_multimodal is implemented for the Gemma-3 vision tower")
+      from .vision import Gemma3Vision
+      self.vision = Gemma3Vision(c, self.par)
+      self.vision_params = self.vision.params
+      if bool(getattr(c, "freeze_vision_encoder_params", True)):
+        for p in self.vision_params:
+          p.pdef.frozen = True
     if L.lora_spec(c) is not None:
       # LoRA fine-tuning: everything but the adapters keeps its value (no gradient, no weight decay)
       for p in self.all_params():
@@ -239,6 +250,7 @@ class Transformer:
       out.extend(l.params)
     out.extend(self.mtp_params)
     out.extend(self.head_params)
+    out.extend(self.vision_params)
     return out
 
   def units_in_order(self) -> list[str]:
@@ -263,9 +275,17 @@ class Transformer:
     return ctx
 
   # ------------------------------------------------------------------ pieces run by the engine
-  def embed(self, tokens, positions):
+  def encode_images(self, images, image_mask):
+    """images [B, N, 3, H, W] -> (soft tokens [B, N*K, D], mask [B, S]) as `embed(..., mm=...)` takes them."""
+    soft = self.vision(images.to(self.embedding.data.device))
+    return soft.reshape(soft.shape[0], -1, soft.shape[-1]), image_mask.to(soft.device).bool()
+
+  def embed(self, tokens, positions, mm=None):
     c = self.config
     x = F.embedding(tokens, self.embedding)
+    if mm is not None:
+      from ..multimodal.utils import merge_mm_embeddings
+      x = merge_mm_embeddings(x, mm[0], mm[1])
     if self.family.scale_embedding:
       x = (x.float() * math.sqrt(c.emb_dim)).to(x.dtype)
     if self.pos_embedding is not None:
@@ -287,13 +307,19 @@ class Transformer:
 
   # ------------------------------------------------------------------ plain forward (eval / inference / tests)
   @torch.no_grad()
-  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None):
-    """Full logits [B,S,V] in fp32; every unit must be resident (single rank or gathered by the caller)."""
+  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None, images=None, image_mask=None):
+    """Full logits [B,S,V] in fp32; every unit must be resident (single rank or gathered by the caller).
+    `images` [B, N, 3, H, W] with `image_mask` [B, S] (True at the soft-token positions) makes the prompt multimodal."""
     B, S = tokens.shape
     if positions is None:
       positions = torch.arange(S, device=tokens.device)[None].expand(B, S)
     ctx = self.make_ctx(positions, segment_ids, mode, tokens)
-    x = self.embed(tokens, positions)
+    mm = None
+    if images is not None:
+      from ..multimodal.utils import bidirectional_block_mask
+      mm = self.encode_images(images, image_mask)
+      ctx.bidir = bidirectional_block_mask(mm[1])
+    x = self.embed(tokens, positions, mm)
     for i, layer in enumerate(self.layers):
       ctx.layer_index = i
       ctx.cache = caches[i] if caches is not None else None

@@ -306,16 +306,19 @@ class ParamStore:
       max_chunk = max(u.chunk for u in sharded)
       self.seg_flags = torch.zeros(world * (-(-max_chunk // self.seg_elems)), dtype=torch.int32, device=dev)
       self.comm_ctas = int(getattr(config, "fsdp_comm_ctas", 8))
-      # How a unit's all-gather runs. "prefetch" (default): the peer-load gather kernel on its own stream, issued one unit ahead,
-      # so it overlaps the previous unit's compute (measured 5 % faster per step than the in-GEMM form at 2 GPUs once the GEMMs
-      # moved to CTA pairs). "gemm": copier CTAs inside the first GEMM of the unit. "inline": gather kernel on the compute stream.
-      self.ag_mode = os.environ.get("MAXTEXT_B200_AG_MODE", "prefetch")
+      # How a unit's all-gather runs, one unit ahead of its first use and on its own stream in both default forms.
+      # "dma": one peer-to-local copy per rank on the copy engines (no SM time); "prefetch": a peer-load kernel (32 CTAs).
+      # "gemm": copier CTAs inside the first GEMM of the unit. "inline": the gather kernel on the compute stream at first use.
+      # Measured on 8 GPUs (Llama-3-8B step): prefetch 1228 ms, dma 1156 ms; with in-switch reduction of the gradient
+      # reduce-scatter 1188 and 1125 ms. On 2 GPUs: prefetch 1148 ms, dma 1140 ms, and plain peer loads beat the in-switch
+      # reduction (1135 vs 1150 ms), which is therefore used from four ranks up.
+      big = world >= 4
+      self.ag_mode = os.environ.get("MAXTEXT_B200_AG_MODE", "dma")
       self.ag_in_gemm = self.ag_mode == "gemm"
       self.ag_stream = torch.cuda.Stream(device=dev)
-      # in-switch (NVLS) reduction of the gradient reduce-scatter when the buffers have a multicast address. Off unless
-      # MAXTEXT_B200_RS_NVLS=1: at two ranks the plain peer loads measured faster (1135 vs 1150 ms per step); larger groups,
-      # where the switch saves seven of eight loads, are the intended use.
-      self.rs_nvls = os.environ.get("MAXTEXT_B200_RS_NVLS", "0") == "1"
+      # in-switch (NVLS) reduction of the gradient reduce-scatter when the buffers have a multicast address: the switch adds the
+      # copies (`multimem.ld_reduce`), so each rank receives one chunk instead of `world` of them
+      self.rs_nvls = os.environ.get("MAXTEXT_B200_RS_NVLS", "1" if big else "0") == "1"
       self.comm_stream = torch.cuda.Stream(device=dev)
       self._gbufs = None
       self._gslot_pending = [None, None]

@@ -142,7 +142,8 @@ class TrainEngine:
     # ---- forward
     self._gather(0, async_op=False)
     self._gather(1)
-    x = self._run_embed(tokens, positions, grad=False)
+    mm = self._encode_images(batch, tokens, ctx)
+    x = self._run_embed(tokens, positions, grad=False, mm=mm)
     self._release(0) if self._units[0] and self._units[0][0].group_size > 1 and not c.logits_via_embedding else None
     ckpts = []
     for i, layer in enumerate(model.layers):
@@ -221,7 +222,7 @@ class TrainEngine:
     if not c.logits_via_embedding:
       for u in emb_units:
         store.acquire_full_grad(u)
-    self._run_embed(tokens, positions, grad=True, dx=dx)
+    self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm)
     for r_tokens, r_pos, d_emb in mtp_embed_grads:          # embeddings of the tokens further ahead, used by the MTP modules
       self._run_embed(r_tokens, r_pos, grad=True, dx=d_emb)
     self._finish_unit_grads(0, accumulate_rs)
@@ -283,13 +284,32 @@ class TrainEngine:
       return t
     return total_w
 
-  def _run_embed(self, tokens, positions, grad: bool, dx=None):
+  def _encode_images(self, batch: dict, tokens, ctx):
+    """Multimodal batches (`images` [B, N, 3, H, W] + `image_mask` [B, S]): run the frozen vision tower once, without
+    gradient, and let the tokens of each image attend to each other in both directions."""
+    if batch.get("images") is None or self.model.vision is None:
+      return None
+    if not bool(getattr(self.config, "freeze_vision_encoder_params", True)):
+      raise NotImplementedError("training the vision tower (freeze_vision_encoder_params=false) is not implemented")
+    from ..multimodal.utils import bidirectional_block_mask
+    units = [u for k, u in self.store.units.items() if k == "vision" or k.startswith("vision#")]
+    for u in units:
+      if u.group_size > 1 and not u.resident:
+        self.store.gather_unit(u, async_op=False)
+    with torch.no_grad():
+      mm = self.model.encode_images(batch["images"].to(self.device), batch["image_mask"].to(self.device))
+    for u in units:
+      self.store.release_full(u)
+    ctx.bidir = bidirectional_block_mask(mm[1])
+    return mm
+
+  def _run_embed(self, tokens, positions, grad: bool, dx=None, mm=None):
     model = self.model
     if not grad:
       with torch.no_grad():
-        return model.embed(tokens, positions)
+        return model.embed(tokens, positions, mm)
     with torch.enable_grad():
-      x = model.embed(tokens, positions)
+      x = model.embed(tokens, positions, mm)
     torch.autograd.backward([x], [dx])
     for p in model.embed_params:
       p.collect_leaf_grad()
