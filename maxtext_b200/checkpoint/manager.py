@@ -117,16 +117,13 @@ class TreeIO:
     scan = bool(self.c.scan_layers)
     stack_sizes = self.engine.model.stack_sizes
     written_meta = set()
-    writes_tp = self.tp_size > 1 or self.ep_size > 1
     for i, p in enumerate(self.store.params.values()):
       d = p.pdef
       t = self._full_from_flat(p, flat)           # collective over the unit's shard group
       # one writer per distinct (tp, ep) slice: the first rank of each shard group
       u = self.store.unit_of(p)
-      if u.group_rank != 0:
+      if not self._is_writer(p, u):
         continue
-      if not writes_tp and self.rank != self._writer_rank(i, u):
-        pass
       ref_local = ps.to_ref_layout(_LocalView(d, self._local_ref_shape(d)[0]), t)
       arr = _to_numpy(ref_local.to(dtype) if dtype is not None else ref_local)
       key, axis = leaf_key(d, scan)
@@ -161,8 +158,26 @@ class TreeIO:
         written_meta.add(adir)
       futures.append(pool.submit(zarr3.write_chunk, adir, tuple(index), block))
 
-  def _writer_rank(self, i, u):
-    return 0
+  def _is_writer(self, p, u) -> bool:
+    """Exactly one rank writes each distinct chunk: the first rank of the unit's shard group, and among the ranks that hold
+    identical copies (data-parallel replicas, tensor / expert ranks for parameters those axes do not split) the one at
+    index 0 of every such axis. Pipeline stages hold different parameters, so every stage writes its own."""
+    if u.group_rank != 0:
+      return False
+    m = self.mesh
+    if m is None:
+      return True
+    d = p.pdef
+    for a in m.axis_names:
+      if m.shape[a] <= 1 or a in u.fsdp_axes or a == "stage":
+        continue
+      if a in ("tensor", "tensor_sequence") and d.tp_dim is not None:
+        continue
+      if a == "expert" and d.ep_dim is not None:
+        continue
+      if m.axis_index(a) != 0:
+        return False
+    return True
 
   def _is_meta_writer(self, d):
     first_layer = d.layer in (None, 0)

@@ -57,7 +57,7 @@ def chunk_path(path: str, index) -> str:
 def write_chunk(path: str, index, data: np.ndarray):
   p = chunk_path(path, index)
   os.makedirs(os.path.dirname(p), exist_ok=True)
-  tmp = p + ".tmp"
+  tmp = f"{p}.tmp{os.getpid()}"           # unique per writer: a stray second writer must not break the rename
   with open(tmp, "wb") as fh:
     fh.write(np.ascontiguousarray(data).tobytes())
   os.replace(tmp, p)

@@ -186,3 +186,35 @@ def test_ring_of_experts_matches_single(tmp_path):
                   str(tmp_path), "roe2")
   _close(got["loss"], ref["loss"], 5e-4)
   _close(got["grad_norm"], ref["grad_norm"], 5e-3)
+
+
+def _run_cli(world, overrides):
+  """`python -m maxtext_b200.train.train` on `world` gloo ranks; returns rank 0's per-step losses."""
+  import re
+  port = _free_port()
+  procs = []
+  for r in range(world):
+    env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+               OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    procs.append(subprocess.Popen([sys.executable, "-m", "maxtext_b200.train.train", os.path.join(ROOT, "maxtext_b200/configs/base.yml")]
+                                  + _merge(BASE, overrides), cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+  outs = [p.communicate(timeout=300)[0].decode(errors="replace") for p in procs]
+  for p, o in zip(procs, outs):
+    assert p.returncode == 0, o[-3000:]
+  return [float(x) for x in re.findall(r"completed step: \d+.*?loss: ([0-9.]+)", outs[0])]
+
+
+@pytest.mark.parametrize("layout", ["pp2", "fsdp2", "fsdp2tp2"])
+def test_checkpoint_resume_reproduces_uninterrupted_run(tmp_path, layout):
+  """Save under a sharded layout, stop, resume: the remaining steps equal those of a run that never stopped. Under pipeline
+  parallelism every stage writes the layers it owns into the one shared tree; replicated tensors have exactly one writer."""
+  par = {"pp2": (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2"]),
+         "fsdp2": (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=2"]),
+         "fsdp2tp2": (4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_tensor_parallelism=2"])}[layout]
+  world, over = par
+  common = over + ["learning_rate_schedule_steps=6", f"base_output_directory={tmp_path}", "async_checkpointing=false"]
+  full = _run_cli(world, common + ["steps=6", "run_name=full", "enable_checkpointing=false"])
+  first = _run_cli(world, common + ["steps=4", "run_name=res", "enable_checkpointing=true", "checkpoint_period=2"])
+  rest = _run_cli(world, common + ["steps=6", "run_name=res", "enable_checkpointing=true", "checkpoint_period=2"])
+  assert first == full[:4] and len(rest) == 2, (full, first, rest)
+  _close(rest, full[4:], 2e-4)
