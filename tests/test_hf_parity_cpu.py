@@ -106,6 +106,22 @@ def _deepseek3(_):
   return cfg, transformers.DeepseekV3ForCausalLM, hc
 
 
+def _deepseek2(_):
+  # HF's DeepSeek-V2 port leaves the YaRN mscale^2 factor out of the softmax scale (its V3 port and MaxText's MLA,
+  # src/maxtext/layers/attention_mla.py:890-893, apply it), so the comparison runs with mscale = 0, where the factor is one
+  cfg = _tiny("deepseek2-16b", ["num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "base_num_decoder_layers=3", "kv_lora_rank=32",
+                                "qk_nope_head_dim=16", "qk_rope_head_dim=8", "v_head_dim=16", "shared_experts=1", "base_num_kv_heads=4",
+                                "first_num_dense_layers=1", "mscale=0.0"])
+  rp = dict(_yarn(cfg), mscale=0.707, mscale_all_dim=0.707)
+  rp.pop("truncate")
+  hc = transformers.DeepseekV2Config(**{k: v for k, v in _common(
+      cfg, moe_intermediate_size=32, n_routed_experts=4, num_experts_per_tok=2, num_hidden_layers=3, num_key_value_heads=4, kv_lora_rank=32,
+      q_lora_rank=None, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, n_group=1, topk_group=1, first_k_dense_replace=1,
+      n_shared_experts=1, routed_scaling_factor=cfg.routed_scaling_factor, topk_method="greedy", norm_topk_prob=False, rope_parameters=rp,
+      max_position_embeddings=S).items() if k != "head_dim"})
+  return cfg, transformers.DeepseekV2ForCausalLM, hc
+
+
 def _gpt_oss(_):
   cfg = _tiny("gpt-oss-20b", ["num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "sliding_window_size=8"])
   hc = transformers.GptOssConfig(**_common(cfg, intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
@@ -144,7 +160,7 @@ def _qwen3_next(_):
 
 
 CASES = {"qwen3_next": _qwen3_next, "gemma": _gemma, "gemma2": _gemma2, "gemma3": _gemma3, "qwen2": _qwen2, "qwen3": _qwen3, "qwen3_moe": _qwen3_moe,
-         "mistral": _mistral, "deepseek3": _deepseek3, "gpt_oss": _gpt_oss, "olmo3": _olmo3, "llama4": _llama4}
+         "mistral": _mistral, "deepseek2": _deepseek2, "deepseek3": _deepseek3, "gpt_oss": _gpt_oss, "olmo3": _olmo3, "llama4": _llama4}
 
 
 def _randomise(hf):
