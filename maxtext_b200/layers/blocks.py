@@ -314,6 +314,10 @@ class Attention:
     elif qk_norm:
       self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
       self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
+    if tp > 1 and not self.global_qk_norm:
+      for n_ in (self.qn, self.kn):
+        if n_ is not None and n_.scale is not None:
+          n_.scale.pdef.tp_partial = True        # every rank normalises its own heads with the shared per-lane scale
     self.sinks = ab.vector("sinks", self.hq, ("q_heads",), init="zeros", tp=True) if sinks else None
 
   def _project(self, x, ctx, tp_rt=None):

@@ -60,6 +60,7 @@ class ParamDef:
   layer: int | None = None       # index along the stacked layer axis
   stack: str | None = None       # name of the stacked collection in the reference tree ("layers", "dense_layers"...)
   weight_decay: bool = True
+  tp_partial: bool = False       # replicated over the tensor axes but fed rank-local data: its gradient is a partial sum
   frozen: bool = False           # never trained (base weights under LoRA): gradient forced to zero, no weight decay
   tp_dim: int | None = None      # internal dim split over tensor axes (already applied to `shape`)
   ep_dim: int | None = None      # internal dim split over the expert axis (already applied)

@@ -378,6 +378,11 @@ class TrainEngine:
     if self.inner_world > 1:
       dist.all_reduce(stats, group=self.inner_group)
       stats[3] /= self.inner_world
+      # ranks along the tensor axes score the same tokens: count each token once (the gradient itself is summed over the
+      # data axes only, so without this the normaliser, and with it the clipping threshold, would be off by the TP degree)
+      dup = self.mesh.axis_size(("tensor", "tensor_sequence")) if self.mesh is not None else 1
+      if dup > 1:
+        stats[[0, 1, 2, 4]] /= dup
     loss_sum, z_sum, total_w, aux, mtp_sum = stats[0], stats[1], stats[2], stats[3], stats[4]
     aux = aux / max(1, acc["micro"]) / max(1, self.n_moe_layers)
     inv_w = 1.0 / (total_w + EPS)
@@ -472,6 +477,16 @@ class TrainEngine:
         g = mesh.group(axes)
         if g is not None:
           dist.all_reduce(store.shard_view(u, store.grad_shard), group=g)
+    tp_axes = ("tensor", "tensor_sequence")
+    if mesh.axis_size(tp_axes) > 1:
+      # parameters every tensor rank holds whole but applies to its own heads only (per-head q/k norm scales)
+      tg = mesh.group(tp_axes)
+      for u in store.units.values():
+        for p, off in zip(u.params, u.offsets):
+          if p.pdef.tp_partial:
+            assert u.group_size == 1, "tensor-partial parameters live in replicated units"
+            a = u.shard_offset + off
+            dist.all_reduce(store.grad_shard[a: a + p.pdef.numel], group=tg)
 
   def _grad_sumsq(self):
     """Sum of squares of the (un-normalised) global gradient: local shards, de-duplicated, all-reduced."""
@@ -485,20 +500,28 @@ class TrainEngine:
     for u in store.units.values():
       if fused_sq and u.group_size > 1:
         continue
+      mixed = u.group_size == 1 and len({(p.pdef.tp_dim is None, p.pdef.ep_dim is None) for p in u.params}) > 1
+      if mixed:
+        # an unsharded unit that holds both split and replicated tensors: weigh each tensor by its own multiplicity
+        for p, off in zip(u.params, u.offsets):
+          a = u.shard_offset + off
+          total = total + F.sum_of_squares(store.grad_shard[a: a + p.pdef.numel]) / self._replication(u, [p])
+        continue
       sq = F.sum_of_squares(store.shard_view(u, store.grad_shard))
       total = total + sq / self._replication(u)
     dist.all_reduce(total, group=self.inner_group)
     return total
 
-  def _replication(self, u) -> float:
-    """How many ranks hold an identical copy of this unit's gradient shard."""
+  def _replication(self, u, params=None) -> float:
+    """How many ranks hold an identical copy of this unit's gradient shard (or of the given tensors of it)."""
     mesh = self.mesh
+    params = u.params if params is None else params
     distinct = u.group_size
     tp = mesh.axis_size(("tensor", "tensor_sequence"))
-    if tp > 1 and any(p.pdef.tp_dim is not None for p in u.params):
+    if tp > 1 and any(p.pdef.tp_dim is not None for p in params):
       distinct *= tp
     ep = mesh.axis_size("expert")
-    if ep > 1 and any(p.pdef.ep_dim is not None for p in u.params):
+    if ep > 1 and any(p.pdef.ep_dim is not None for p in params):
       distinct *= ep
     return max(1.0, self.inner_world / distinct)
 

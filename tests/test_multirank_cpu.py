@@ -218,3 +218,15 @@ def test_checkpoint_resume_reproduces_uninterrupted_run(tmp_path, layout):
   rest = _run_cli(world, common + ["steps=6", "run_name=res", "enable_checkpointing=true", "checkpoint_period=2"])
   assert first == full[:4] and len(rest) == 2, (full, first, rest)
   _close(rest, full[4:], 2e-4)
+
+
+@pytest.mark.parametrize("model", ["llama3-8b", "qwen3-8b"])
+def test_tp2_matches_single_including_grad_norm(tmp_path, model):
+  """Pure tensor parallelism: the same tokens are scored on both ranks (count them once), per-head q/k norm scales see
+  only the local heads (their gradients are summed over the tensor ranks), and replicated tensors enter the global
+  gradient norm once. A wrong norm changes the clipping factor, so the curves are compared at a large learning rate."""
+  q = [f"model_name={model}", "override_model_config=true", "steps=4", "learning_rate=1e-2"]
+  one = run_ranks(1, q + ["per_device_batch_size=4"], str(tmp_path), "one")
+  two = run_ranks(2, q + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"], str(tmp_path), "tp2")
+  _close(two["loss"], one["loss"], 2e-5)
+  _close(two["grad_norm"], one["grad_norm"], 2e-4)
