@@ -193,10 +193,17 @@ class RoutedMoE:
       assert self.k == 1, "llama4 routing scales the expert input by its single score"
       x2 = (x2.float() * torch.sigmoid(wts)).to(x2.dtype)
       wts = torch.ones_like(wts)
+    if ctx.tp_size > 1:
+      # the experts' hidden dim is split over the tensor ranks: what flows back into the tokens and into the combine weights
+      # is a partial sum on every rank (the router itself runs replicated and stays outside). The fused paths combine before
+      # the all-reduce of the output, the generic path after it, where the combine already sees complete expert outputs.
+      x2, wts_fused = tp_enter(x2, ctx), tp_enter(wts, ctx)
+    else:
+      wts_fused = wts
     plain_ffn = self.b0 is None and self.style != "gpt_oss"
     if plain_ffn and ctx.ep_size == 1 and self.act in F._ACT_CODE and moe_ops.padded_path_supported(x2, D, self.wi_0.data.shape[1], self.E):
       # GPU path: device-side stable sort into 128-row-padded expert groups, grouped tcgen05 GEMMs, no host synchronisation
-      out = moe_ops.moe_ffn_padded(x2, wts, idx, self.wi_0, self.wi_1, self.wo, self.E, self.act)
+      out = moe_ops.moe_ffn_padded(x2, wts_fused, idx, self.wi_0, self.wi_1, self.wo, self.E, self.act)
       if ctx.tp_size > 1:
         out = tp_exit(out, ctx)
       return out.view(B, S, D)
@@ -204,17 +211,14 @@ class RoutedMoE:
       from . import moe_ep
       if moe_ep.supported(x2, self, ctx):
         # dispatch / return through the peers' symmetric buffers (this repository's kernels); the NCCL path below is the fallback
-        out = moe_ep.expert_parallel_ffn(x2, wts, idx, self, ctx)
+        out = moe_ep.expert_parallel_ffn(x2, wts_fused, idx, self, ctx)
         if ctx.tp_size > 1:
           out = tp_exit(out, ctx)
         return out.view(B, S, D)
     rows, order, sizes = moe_ops.permute(x2, idx, self.E)          # rows sorted by global expert id
-    if ctx.ep_size > 1:
-      y = self._expert_parallel(rows, sizes, ctx)
-    else:
-      y = self.experts_ffn(rows, sizes)
-      if ctx.tp_size > 1:
-        y = tp_exit(y, ctx)
+    y = self._expert_parallel(rows, sizes, ctx) if ctx.ep_size > 1 else self.experts_ffn(rows, sizes)
+    if ctx.tp_size > 1:
+      y = tp_exit(y, ctx)           # the experts' hidden dim is split over the tensor ranks: sum the partial outputs
     out = moe_ops.unpermute_combine(y, order, wts, B * S, self.k, fp32_sum=self.c.float32_weight_sum)
     return out.view(B, S, D).to(x.dtype)
 

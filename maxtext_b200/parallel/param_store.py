@@ -654,11 +654,11 @@ class ParamStore:
             p.grad_written = True
 
   # ------------------------------------------------------------------ replica (data-parallel) reduction
-  def replica_axes(self, u: Unit) -> tuple:
-    """Mesh axes over which this unit's parameters are replicated while the batch is split."""
+  def replica_axes(self, u: Unit, params=None) -> tuple:
+    """Mesh axes over which this unit's parameters (or the given ones of it) are replicated while the batch is split."""
     batch_axes = ("data", "fsdp", "fsdp_transpose", "expert", "context", "context_usp_ulysses", "stage")
     used = set(u.fsdp_axes)
-    for p in u.params:
+    for p in (u.params if params is None else params):
       used.update(self.specs[p.name].all_axes)
     return tuple(a for a in self.mesh.axis_names if a in batch_axes and self.mesh.shape[a] > 1 and a not in used
                  and a != "stage")

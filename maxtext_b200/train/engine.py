@@ -190,7 +190,9 @@ class TrainEngine:
     # ---- backward through the layers
     aux_scale = None
     if self.n_moe_layers and c.load_balance_loss_weight > 0:
-      aux_scale = self._global_weight(total_w) / self.n_moe_layers
+      # the update divides every gradient by the global token weight; the balance loss is a mean over each rank's own rows,
+      # and the ranks' gradients are summed, so it is seeded with weight / (layers x data shards)
+      aux_scale = self._global_weight(total_w) / self.n_moe_layers / self._data_shards()
     self._gather(len(model.layers) - 1)  # unit index of layer L-2 is L-1
     for i in reversed(range(len(model.layers))):
       ui = i + 1
@@ -278,11 +280,19 @@ class TrainEngine:
     return dx_main + x_in.grad, [(tk, ps, e.grad) for tk, ps, e in embs]
 
   def _global_weight(self, total_w):
-    if self.world > 1:
+    """Token weight of the whole (inner) job, every token counted once."""
+    if self.inner_world > 1:
       t = total_w.clone()
-      dist.all_reduce(t)
-      return t
+      dist.all_reduce(t, group=self.inner_group)
+      dup = self.mesh.axis_size(("tensor", "tensor_sequence")) if self.mesh is not None else 1
+      return t / dup if dup > 1 else t
     return total_w
+
+  def _data_shards(self) -> int:
+    """Ranks of the (inner) job that see different tokens: the product of the batch and sequence axes."""
+    if self.mesh is None:
+      return 1
+    return max(1, self.mesh.axis_size(("data", "fsdp", "fsdp_transpose", "expert", "context", "context_usp_ulysses")))
 
   def _encode_images(self, batch: dict, tokens, ctx):
     """Multimodal batches (`images` [B, N, 3, H, W] + `image_mask` [B, S]): run the frozen vision tower once, without
@@ -472,7 +482,18 @@ class TrainEngine:
     if mesh is None or self.inner_world == 1:
       return
     for u in store.units.values():
-      axes = store.replica_axes(u)
+      per_param = [store.replica_axes(u, [p]) for p in u.params]
+      if len(set(per_param)) > 1:
+        # an unsharded unit that mixes tensors split over a batch axis (experts over `expert`) with replicated ones (norm
+        # scales): reduce each tensor over the axes it is replicated on
+        assert u.group_size == 1, "mixed replication is only laid out in unsharded units"
+        for p, off, axes in zip(u.params, u.offsets, per_param):
+          g = mesh.group(axes) if axes else None
+          if g is not None:
+            a = u.shard_offset + off
+            dist.all_reduce(store.grad_shard[a: a + p.pdef.numel], group=g)
+        continue
+      axes = per_param[0] if per_param else ()
       if axes:
         g = mesh.group(axes)
         if g is not None:
@@ -500,12 +521,16 @@ class TrainEngine:
     for u in store.units.values():
       if fused_sq and u.group_size > 1:
         continue
-      mixed = u.group_size == 1 and len({(p.pdef.tp_dim is None, p.pdef.ep_dim is None) for p in u.params}) > 1
-      if mixed:
-        # an unsharded unit that holds both split and replicated tensors: weigh each tensor by its own multiplicity
+      if len({(p.pdef.tp_dim is None, p.pdef.ep_dim is None) for p in u.params}) > 1:
+        # a unit that holds both split and replicated tensors (e.g. attention kernels next to the router): weigh the part
+        # of each tensor that lies in this rank's shard by that tensor's own multiplicity
+        lo = u.group_rank * u.chunk if u.group_size > 1 else 0
+        hi = lo + (u.chunk if u.group_size > 1 else u.numel)
         for p, off in zip(u.params, u.offsets):
-          a = u.shard_offset + off
-          total = total + F.sum_of_squares(store.grad_shard[a: a + p.pdef.numel]) / self._replication(u, [p])
+          a, b = max(off, lo), min(off + p.pdef.numel, hi)
+          if a < b:
+            piece = store.grad_shard[u.shard_offset + a - lo: u.shard_offset + b - lo]
+            total = total + F.sum_of_squares(piece) / self._replication(u, [p])
         continue
       sq = F.sum_of_squares(store.shard_view(u, store.grad_shard))
       total = total + sq / self._replication(u)

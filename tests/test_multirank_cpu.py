@@ -230,3 +230,28 @@ def test_tp2_matches_single_including_grad_norm(tmp_path, model):
   two = run_ranks(2, q + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"], str(tmp_path), "tp2")
   _close(two["loss"], one["loss"], 2e-5)
   _close(two["grad_norm"], one["grad_norm"], 2e-4)
+
+
+@pytest.fixture(scope="module")
+def moe_single(tmp_path_factory):
+  return run_ranks(1, MOE_HOT + ["per_device_batch_size=4"], str(tmp_path_factory.mktemp("moe_single")), "single")
+
+
+MOE_HOT = ["model_name=mixtral-8x7b", "override_model_config=true", "num_experts=4", "base_moe_mlp_dim=64", "load_balance_loss_weight=0.01",
+           "steps=4", "learning_rate=1e-2"]
+
+
+@pytest.mark.parametrize("layout", ["fsdp2", "ep2", "tp2", "ep2tp2"])
+def test_moe_layouts_match_single_including_grad_norm(moe_single, tmp_path, layout):
+  """Routed experts with the load-balance loss under FSDP, EP, TP and EP x TP: the balance loss is a per-rank mean (seeded
+  with 1 / data shards), expert outputs are partial sums over the tensor ranks in every path, the tokens' and combine
+  weights' gradients are summed over them where the combine precedes the reduction, and tensors that share a unit with
+  differently replicated ones (router next to attention kernels, norm scales next to experts) are reduced and normed each
+  with their own multiplicity."""
+  world, par = {"fsdp2": (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=2"]),
+                "ep2": (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_expert_parallelism=2"]),
+                "tp2": (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"]),
+                "ep2tp2": (4, ["per_device_batch_size=1", "ici_fsdp_parallelism=1", "ici_expert_parallelism=2", "ici_tensor_parallelism=2"])}[layout]
+  got = run_ranks(world, MOE_HOT + par, str(tmp_path), layout)
+  _close(got["loss"], moe_single["loss"], 2e-5)
+  _close(got["grad_norm"], moe_single["grad_norm"], 2e-4)
