@@ -230,13 +230,24 @@ class _ReduceFromTP(torch.autograd.Function):
     return dy, None
 
 
+def sp_enabled(config) -> bool:
+  """True when the mesh has a `tensor_sequence` axis: tensor parallelism with a sequence-split residual stream."""
+  return int(getattr(config, "ici_tensor_sequence_parallelism", 1)) * int(getattr(config, "dcn_tensor_sequence_parallelism", 1)) > 1
+
+
 def tp_enter(x, ctx):
+  if ctx.tp_size > 1 and ctx.sp:
+    from ..parallel import sequence_parallel as sp
+    return sp.gather(x, ctx.tp_group)
   return _CopyToTP.apply(x, ctx.tp_group) if ctx.tp_size > 1 and torch.is_grad_enabled() else x
 
 
 def tp_exit(x, ctx):
   if ctx.tp_size <= 1:
     return x
+  if ctx.sp and x.dim() == 3:
+    from ..parallel import sequence_parallel as sp
+    return sp.reduce_scatter(x, ctx.tp_group)
   if torch.is_grad_enabled():
     return _ReduceFromTP.apply(x, ctx.tp_group)
   x = x.contiguous()
@@ -304,6 +315,8 @@ class Attention:
       self.bv = ab.sub("value").vector("bias", self.hkv * self.dh, ("kv_heads",), init="zeros", tp=kv_tp is not None)
     # the output projection carries a bias whenever q/k/v do, except for qwen2 (src/maxtext/layers/attentions.py:833)
     self.bo = ab.sub("out").vector("bias", self.d, ("embed",), init="zeros") if (bias if out_bias is None else out_bias) else None
+    if self.bo is not None and tp > 1 and sp_enabled(c):
+      self.bo.pdef.tp_partial = True           # added after the reduce-scatter: each rank sees its own tokens
     self.qn = self.kn = None
     self.global_qk_norm = bool(global_qk_norm) and qk_norm
     if self.global_qk_norm:
@@ -342,6 +355,7 @@ class Attention:
     fuse_in = tp_rt is not None and self.qkv is not None and self.bq is None and self.qkv.fusable()
     if not fuse_in:
       x = tp_enter(x, ctx)
+      B, S, _ = x.shape                      # sequence parallelism: the gathered length
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
     plain = (not self.qk_norm and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
@@ -455,8 +469,8 @@ class MLA:
 
   def __call__(self, x, ctx):
     c = self.c
-    B, S, _ = x.shape
     x = tp_enter(x, ctx)
+    B, S, _ = x.shape
     if self.query is not None:
       q = F.linear(x, self.query)
     else:
@@ -515,6 +529,8 @@ class MLP:
     self.wi = FusedParam([self.wi_0, self.wi_1]) if self.gated and FusedParam.possible([self.wi_0, self.wi_1]) else None
     self.bi = mb.sub("wi_0" if self.gated else "wi").vector("bias", f, ("mlp",), init="zeros", tp=True) if bias else None
     self.bo = mb.sub("wo").vector("bias", d, ("embed",), init="zeros") if bias else None
+    if self.bo is not None and b.tp_size > 1 and sp_enabled(c):
+      self.bo.pdef.tp_partial = True
 
   def __call__(self, x, ctx):
     tp_rt = tp_fused.runtime_for(ctx, x, x.shape[-1]) if ctx.tp_size > 1 else None

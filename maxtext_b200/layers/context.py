@@ -67,6 +67,7 @@ class LayerCtx:
   metrics: dict = field(default_factory=dict)
   cache: object = None               # inference KV cache for the current layer
   tokens: torch.Tensor | None = None
+  sp: bool = False                   # residual stream split along the sequence over the tensor ranks (parallel.sequence_parallel)
   bidir: torch.Tensor | None = None  # [B, 1, S, S] extra allowed (query, key) pairs: tokens of one image see each other
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
 

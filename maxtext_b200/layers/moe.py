@@ -175,6 +175,16 @@ class RoutedMoE:
     return red
 
   def __call__(self, x, ctx):
+    if ctx.sp and ctx.tp_size > 1:
+      # sequence-parallel residual stream: routing needs every token, so the block runs the plain tensor-parallel form on
+      # the gathered sequence (which returns complete outputs and complete input gradients on every rank) and keeps its part
+      from ..parallel import sequence_parallel as sp
+      ctx.sp = False
+      try:
+        out = self(sp.gather_whole(x, ctx.tp_group), ctx)
+      finally:
+        ctx.sp = True
+      return sp.slice_local(out, ctx.tp_group)
     B, S, D = x.shape
     x2 = x.reshape(B * S, D)
     if ctx.ep_size > 1 and self.c.use_ring_of_experts and self.style != "llama4":

@@ -96,6 +96,12 @@ class DecoderBlock:
     else:
       self.mlp = L.MLP(b, c, plan.mlp_name + s, plan.mlp_hidden, bias=plan.mlp_bias)
     self.n2b = mk(plan.post_mlp_norm) if plan.post_mlp_norm else None
+    if b.tp_size > 1 and L.sp_enabled(c):
+      # sequence-parallel residual stream: these norms see this rank's tokens only, their scale gradients are partial sums
+      for n_ in (self.n1, self.n1b, self.n2, self.n2b):
+        for v_ in ((n_.scale, n_.bias) if n_ is not None else ()):
+          if v_ is not None:
+            v_.pdef.tp_partial = True
 
   def __call__(self, x, ctx: LayerCtx):
     a = self.attn(self.n1(x) if self.n1 is not None else x, ctx)

@@ -75,7 +75,7 @@ class TPReduceRuntime:
 def runtime_for(ctx, x: torch.Tensor, n: int):
   """The fused all-reduce runtime for activations shaped like `x` (rows = all leading dims), or None if not applicable."""
   c = ctx.config
-  if ctx.tp_size <= 1 or not x.is_cuda or x.dtype != torch.bfloat16 or not bool(getattr(c, "use_fused_comm_kernels", False)):
+  if ctx.tp_size <= 1 or getattr(ctx, "sp", False) or not x.is_cuda or x.dtype != torch.bfloat16 or not bool(getattr(c, "use_fused_comm_kernels", False)):
     return None
   rows = x.numel() // x.shape[-1]
   if ctx.tp_size > int(getattr(c, "tp_fused_max_ranks", 2)):

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.transformer import Transformer
+from ..layers.blocks import sp_enabled as L_sp_enabled
 from ..ops import functional as F
 from ..optimizers import factory as opt_factory
 from ..optimizers.schedules import make_schedule
@@ -144,6 +145,14 @@ class TrainEngine:
     self._gather(1)
     mm = self._encode_images(batch, tokens, ctx)
     x = self._run_embed(tokens, positions, grad=False, mm=mm)
+    # tensor-sequence parallelism: between blocks every tensor rank holds its part of the sequence only
+    sp_on = ctx.tp_size > 1 and L_sp_enabled(c) and ctx.cp_size == 1
+    if sp_on:
+      from ..parallel import sequence_parallel as sp
+      assert S % ctx.tp_size == 0, "the sequence must divide by the tensor-sequence degree"
+      assert not model.mtp_layers, "multi-token prediction is not implemented under tensor-sequence parallelism"
+      ctx.sp = True
+      x = sp.local_seq(x, ctx.tp_group)
     self._release(0) if self._units[0] and self._units[0][0].group_size > 1 and not c.logits_via_embedding else None
     ckpts = []
     for i, layer in enumerate(model.layers):
@@ -174,7 +183,11 @@ class TrainEngine:
     if compute_grads:
       for u in head_units:
         store.acquire_full_grad(u)
+    if sp_on:
+      x = sp.all_gather_seq(x, ctx.tp_group)               # the head scores every token on every tensor rank, as without SP
     loss_sum, z_sum, dx = self._run_head(x, targets.reshape(-1), w_flat, compute_grads)
+    if sp_on and dx is not None:
+      dx = sp.local_seq(dx.view(B, S, -1), ctx.tp_group)
     acc["loss_sum"] += loss_sum
     acc["z_sum"] += z_sum
     acc["weights"] += total_w
@@ -224,6 +237,8 @@ class TrainEngine:
     if not c.logits_via_embedding:
       for u in emb_units:
         store.acquire_full_grad(u)
+    if sp_on:
+      dx = sp.all_gather_seq(dx, ctx.tp_group)
     self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm)
     for r_tokens, r_pos, d_emb in mtp_embed_grads:          # embeddings of the tokens further ahead, used by the MTP modules
       self._run_embed(r_tokens, r_pos, grad=True, dx=d_emb)

@@ -255,3 +255,21 @@ def test_moe_layouts_match_single_including_grad_norm(moe_single, tmp_path, layo
   got = run_ranks(world, MOE_HOT + par, str(tmp_path), layout)
   _close(got["loss"], moe_single["loss"], 2e-5)
   _close(got["grad_norm"], moe_single["grad_norm"], 2e-4)
+
+
+@pytest.mark.parametrize("case", ["llama", "qwen3", "gpt3", "moe", "fsdp2xsp2"])
+def test_tensor_sequence_parallel_matches_single(tmp_path, case):
+  """`ici_tensor_sequence_parallelism`: tensor parallelism whose residual stream, norms and recompute checkpoints are split
+  along the sequence (all-gather into a block, reduce-scatter out of it). Norm scales and post-reduction biases then see
+  a part of the tokens only, so their gradients are summed over the tensor ranks; routed experts run on the gathered tokens."""
+  hot = ["steps=4", "learning_rate=1e-2"]
+  base = {"llama": [], "fsdp2xsp2": [], "qwen3": ["model_name=qwen3-8b", "override_model_config=true"],
+          "gpt3": ["model_name=gpt3-6b", "override_model_config=true", "trainable_position_size=32"],
+          "moe": ["model_name=mixtral-8x7b", "override_model_config=true", "num_experts=4", "base_moe_mlp_dim=64",
+                  "load_balance_loss_weight=0.01"]}[case]
+  world, par = (4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_tensor_sequence_parallelism=2"]) if case == "fsdp2xsp2" else \
+      (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_sequence_parallelism=2"])
+  one = run_ranks(1, base + hot + ["per_device_batch_size=4"], str(tmp_path), "one")
+  got = run_ranks(world, base + hot + par, str(tmp_path), "sp")
+  _close(got["loss"], one["loss"], 2e-5)
+  _close(got["grad_norm"], one["grad_norm"], 2e-4)
