@@ -80,3 +80,25 @@ def test_checkpoint_cli_roundtrip(tmp_path):
   for k, v in hf.state_dict().items():
     assert torch.allclose(back[k], v.float(), atol=1e-5), k
 
+
+
+def test_vllm_weight_stream_has_hf_names_and_values():
+  """What an RL loop pushes into a vLLM rollout engine: one (HF name, tensor) pair per parameter, equal to the export."""
+  from maxtext_b200.integration import vllm as mv
+  from helpers import tiny_config, make_engine
+  cfg = tiny_config("mixtral-8x7b", ["num_experts=4", "base_moe_mlp_dim=64"])
+  eng = make_engine(cfg)
+  want = conv.to_hf(eng.store, cfg)
+  got = dict(mv.weights_iterator(eng.store, cfg))
+  assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
+  assert "model.layers.0.self_attn.q_proj.weight" in got and "model.layers.1.block_sparse_moe.experts.3.w2.weight" in got
+
+  class FakeModel:
+    def load_weights(self, it):
+      self.names = [k for k, v in it if v.dtype == torch.bfloat16]
+  fake = type("LLM", (), {})()
+  fake.llm_engine = type("E", (), {})()
+  fake.llm_engine.model_executor = type("X", (), {})()
+  fake.llm_engine.model_executor.driver_worker = type("W", (), {})()
+  fake.llm_engine.model_executor.driver_worker.model_runner = type("R", (), {"model": FakeModel()})()
+  assert mv.sync_weights(fake, eng.store, cfg) == len(want)
