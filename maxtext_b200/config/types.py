@@ -44,7 +44,7 @@ QUANTIZATIONS = (
 OPT_TYPES = ("adamw", "adam_pax", "sgd", "muon")
 ATTENTION_KERNELS = ("autoselected", "dot_product", "flash", "cudnn_flash_te", "cudnn_flash_jax", "paged", "vllm_rpa")
 ATTENTION_TYPES = ("global", "local_sliding", "chunk", "mla", "full", "compressed", "block_diffusion")
-DATASET_TYPES = ("synthetic", "hf", "grain", "tfds", "c4_mlperf", "olmo_grain")
+DATASET_TYPES = ("synthetic", "hf", "grain", "tfds", "c4_mlperf", "olmo_grain", "tokens")
 CP_STRATEGIES = ("all_gather", "ring", "ulysses", "usp")
 ROPE_TYPES = ("default", "llama3.1", "yarn")
 HARDWARE = ("tpu", "gpu", "gpu_multiprocess", "cpu")

@@ -34,6 +34,21 @@ def build_extension(verbose: bool = True):
   return mod
 
 
+HOST_DIR = os.path.join(HERE, "host")
+HOST_BUILD_DIR = os.path.join(HERE, "build_host")
+HOST_EXT_NAME = "maxtext_b200_host"
+
+
+def build_host_extension(verbose: bool = True):
+  """The host-side runtime library (no CUDA): `csrc/host/*.cpp` -> `csrc/build_host/maxtext_b200_host.so`."""
+  from torch.utils import cpp_extension
+  os.makedirs(HOST_BUILD_DIR, exist_ok=True)
+  return cpp_extension.load(name=HOST_EXT_NAME, sources=sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp"))),
+                            extra_cflags=["-O2", "-std=c++17"], extra_ldflags=["-lpthread"], build_directory=HOST_BUILD_DIR,
+                            with_cuda=False, verbose=verbose)
+
+
 if __name__ == "__main__":
+  build_host_extension(verbose="-q" not in sys.argv)
   build_extension(verbose="-q" not in sys.argv)
   print("built", os.path.join(BUILD_DIR, EXT_NAME + ".so"))

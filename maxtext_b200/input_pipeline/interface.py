@@ -17,6 +17,19 @@ def _create(config, data_rank: int = 0, data_world: int = 1, split: str = "train
   if t in ("hf", "grain", "tfds", "c4_mlperf", "olmo_grain"):
     from .file_pipeline import create_file_iterator
     return create_file_iterator(config, data_rank, data_world, split)
+  if t == "tokens":
+    # pre-tokenized int32 streams (.bin / .npy), packed and prefetched by the native loader (csrc/host/data_loader.cpp)
+    from .file_pipeline import _expand
+    from .native_loader import NativeTokenIterator
+    from .tokenizer import build_tokenizer
+    pats = (config.grain_train_files or config.hf_train_files or config.dataset_path) if split == "train" else \
+        (config.grain_eval_files or config.hf_eval_files or config.dataset_path)
+    files = [f for f in _expand(pats) if f.endswith((".bin", ".npy"))]
+    if not files:
+      raise FileNotFoundError(f"dataset_type=tokens: no .bin / .npy files match {pats!r}")
+    gb = int(config.global_batch_size_to_load if split == "train" else config.global_batch_size_to_load_eval)
+    eos = getattr(build_tokenizer(config), "eos_id", None)
+    return NativeTokenIterator(files, int(config.max_target_length), gb // data_world, int(eos if eos is not None else 1), data_rank, data_world)
   raise ValueError(f"unknown dataset_type {t}")
 
 
