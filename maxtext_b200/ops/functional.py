@@ -77,7 +77,10 @@ class _LinearFn(torch.autograd.Function):
       return saved_out.reshape(-1, w.shape[0]).clone()
     ctx.fp8 = _quant.supported(x2, w)
     ctx.fp8_saved = None
-    if ctx.fp8:
+    ctx.int8 = _quant.int8_on()
+    if ctx.int8:
+      y = _quant.int8_linear_fwd(x2, w)
+    elif ctx.fp8:
       y, ctx.fp8_saved = _quant.linear_fwd(x2, w, pv, keep_for_bwd=True)     # this forward will be differentiated: quantise once for both passes
     else:
       y = mm(x2, w, False, True)
@@ -103,6 +106,8 @@ class _LinearFn(torch.autograd.Function):
       return dx, None, None, None, dbias, None, None
     if not ctx.needs_input_grad[0]:
       dx = None
+    elif getattr(ctx, "int8", False) and ctx.tp_reduce_dx is None:
+      dx = _quant.int8_linear_dx(dy2, w)
     elif ctx.tp_reduce_dx is not None:
       dx = ctx.tp_reduce_dx.all_reduce_gemm(dy2, w, False)      # column-parallel input gradient: summed over the TP ranks in the GEMM
     else:
@@ -134,7 +139,8 @@ def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None,
   if not torch.is_grad_enabled():
     if saved_out is not None:
       return saved_out
-    y = (pre if pre is not None else (_quant.linear_fwd(x2, p.data, p) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
+    y = (pre if pre is not None else _quant.int8_linear_fwd(x2, p.data) if _quant.int8_on() else
+         (_quant.linear_fwd(x2, p.data, p) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
     if lo is not None:
       y = y + _lora_delta(x2, lo).to(y.dtype)
     y = y.view(*x.shape[:-1], p.shape[0])

@@ -24,9 +24,10 @@ _HISTORY: dict = {}       # (owner id, role) -> [ring tensor [n], write position
 
 
 def set_mode(mode: str):
-  """'' (bf16), 'fp8' (all three products in 8 bit). Set once by the engine from config.quantization."""
+  """'' (bf16), 'fp8' (all three products in 8 bit), 'int8' (forward and input-gradient products on int8 operands).
+  Set once by the engine from config.quantization."""
   global _MODE
-  _MODE = "fp8" if mode in ("fp8", "fp8_full", "fp8_gpu", "nanoo_fp8", "fp8_nanoo") else ""
+  _MODE = "fp8" if mode in ("fp8", "fp8_full", "fp8_gpu", "nanoo_fp8", "fp8_nanoo") else "int8" if mode in ("int8", "intmp") else ""
 
 
 def mode() -> str:
@@ -104,3 +105,42 @@ def linear_bwd(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, need_dx: bo
     _, xt, sx = _quantize(x2, E4M3, False, True, (k, "x") if k else None)            # x^T [in, tokens]
     E.gemm_fp8(dyt, xt, grad_out, E5M2, E4M3, sdy, sx, accumulate)
   return dx
+
+
+# ------------------------------------------------------------------------------------------------------------- int8
+# `quantization=int8` (src/maxtext/layers/quantizations.py:144-224 `AqtQuantization`, AQT config_v3 with fwd_bits = 8,
+# dlhs_bits = 8, drhs_bits = None): the forward product and the input-gradient product take symmetric int8 operands with one
+# scale per contraction-free channel (per token for activations and gradients, per output or input feature for the
+# weight); the weight-gradient product stays in the compute dtype. Rounding is to nearest; gradients pass straight through
+# the rounding. The integer product itself is a library call on the GPU (`torch._int_mm`) and an exact float emulation
+# elsewhere; there is no tcgen05 kind::i8 kernel in this repository yet.
+def int8_on() -> bool:
+  return _MODE == "int8"
+
+
+def _q8(t: torch.Tensor, dim: int):
+  """Symmetric int8 along `dim` (the contraction dim): returns (int8 values, fp32 scale with `dim` kept as size 1)."""
+  amax = t.abs().amax(dim=dim, keepdim=True).float().clamp_(min=1e-12)
+  scale = amax / 127.0
+  return torch.clamp(torch.round(t.float() / scale), -127, 127).to(torch.int8), scale
+
+
+def _imm(a8: torch.Tensor, b8t: torch.Tensor) -> torch.Tensor:
+  """a8 [M, K] x b8t [N, K]^T -> fp32 [M, N] holding the exact integer products."""
+  M, K = a8.shape
+  N = b8t.shape[0]
+  if a8.is_cuda and M > 16 and K % 8 == 0 and N % 8 == 0:
+    return torch._int_mm(a8, b8t.t()).float()   # pylint: disable=protected-access
+  return a8.float() @ b8t.float().t()          # |sum| <= K * 127^2: exact in fp32 up to K = 1040, rounded beyond
+
+
+def int8_linear_fwd(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+  xq, sx = _q8(x2, 1)          # per token
+  wq, sw = _q8(w, 1)           # per output feature
+  return (_imm(xq, wq) * sx * sw.t()).to(x2.dtype)
+
+
+def int8_linear_dx(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+  gq, sg = _q8(dy2, 1)         # per token
+  wq, sw = _q8(w, 0)           # per input feature (the contraction now runs over the output features)
+  return (_imm(gq, wq.t().contiguous()) * sg * sw).to(dy2.dtype)

@@ -134,3 +134,32 @@ def test_adam_pax_matches_praxis_formula():
     rv = (1 - d2) * g * g + d2 * rv
     rp = rp - lr * (rm / (torch.sqrt(rv + epsr) + eps) + wd * rp)
     assert torch.allclose(p, rp, atol=1e-6)
+
+
+def test_int8_quantization_numerics_and_training():
+  """quantization=int8: forward and input-gradient products on symmetric per-channel int8 operands, weight gradient in the
+  compute dtype; checked against the definition and by a short training run."""
+  import torch
+  from helpers import tiny_config, make_engine, batch_of
+  from maxtext_b200.ops import quantization as Q
+  torch.manual_seed(0)
+  x, w = torch.randn(12, 32), torch.randn(20, 32) * 0.3
+  sx, sw = x.abs().amax(1, keepdim=True) / 127, w.abs().amax(1, keepdim=True) / 127
+  want = (torch.round(x / sx).clamp(-127, 127) * sx) @ (torch.round(w / sw).clamp(-127, 127) * sw).t()
+  got = Q.int8_linear_fwd(x, w)
+  assert (got - want).abs().max() < 1e-4 and 1e-4 < (got - x @ w.t()).abs().max() < 0.2      # quantised, and close to the exact product
+  dy = torch.randn(12, 20)
+  dx = Q.int8_linear_dx(dy, w)
+  assert (dx - dy @ w).abs().max() < 0.3 and (dx - dy @ w).abs().max() > 1e-5
+  try:
+    eng = make_engine(tiny_config("llama3-8b", ["quantization=int8"]))
+    assert Q.mode() == "int8"
+    b = batch_of(eng.config)
+    losses = [float(eng.train_step(b)["learning/loss"]) for _ in range(5)]
+    assert losses[-1] < losses[0], losses
+    ref = make_engine(tiny_config("llama3-8b"))          # resets the mode
+    assert Q.mode() == ""
+    l0 = float(ref.train_step(b)["learning/loss"])
+    assert abs(l0 - losses[0]) < 0.05 and l0 != losses[0]
+  finally:
+    Q.set_mode("")
