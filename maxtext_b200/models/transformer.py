@@ -245,6 +245,17 @@ class Transformer:
       for p in self.all_params():
         if not p.pdef.name.endswith(("_lora_a", "_lora_b")):
           p.pdef.frozen = True
+    import re
+    pats = [re.compile(x) for x in (getattr(c, "trainable_parameters_mask", None) or [])]
+    if pats:
+      # whitelist (src/maxtext/optimizers/optimizers.py:236-250): everything no pattern matches keeps its value
+      for p in self.all_params():
+        if not any(r.search(p.pdef.name) or r.search("/".join(p.pdef.ref_path)) for r in pats):
+          p.pdef.frozen = True
+    nodecay = [re.compile(x) for x in (getattr(c, "adamw_mask", None) or [])]
+    for p in self.all_params() if nodecay else ():
+      if any(r.search(p.pdef.name) or r.search("/".join(p.pdef.ref_path)) for r in nodecay):
+        p.pdef.weight_decay = False             # src/maxtext/optimizers/optimizers.py:47-49: matched parameters are not decayed
     self.store: ParamStore | None = None
     if build_store:
       self.store = ParamStore(self.all_params(), mesh or _SingleMesh(), c, self.device)

@@ -35,11 +35,11 @@ class AdamW(_Base):
   def step(self, grad_scale, lr, step, **kw):
     c, s = self.c, self.store
     wd = c.adam_weight_decay
-    trainable = s.trainable_slices()
+    trainable = s.decay_slices()
     if trainable is not None:
-      # some parameters are frozen (LoRA): their gradient is exactly zero, so with no decay term the fused update leaves them
-      # untouched; the decoupled decay w <- w (1 - lr wd) is applied to the trainable ranges first, which gives the same result
-      # as the fused form w - lr (u + wd w)
+      # some parameters are frozen (LoRA, trainable_parameters_mask) or excluded from decay (adamw_mask). A frozen one has an
+      # exactly zero gradient, so with no decay term the fused update leaves it untouched; the decoupled decay
+      # w <- w (1 - lr wd) is applied to the decayed ranges first, which gives the same result as the fused w - lr (u + wd w)
       if wd:
         for a, b in trainable:
           s.master[a:b].mul_(1.0 - lr * wd)

@@ -352,6 +352,24 @@ class ParamStore:
         u.resident = True
         self._views_into(u, u.full, "data")
 
+  def decay_slices(self):
+    """None when weight decay applies to the whole shard; else the [a, b) ranges of this rank's flat shard that are decayed
+    (trainable parameters that `adamw_mask` does not exclude)."""
+    cached = getattr(self, "_decay", False)
+    if cached is not False:
+      return cached
+    out = None
+    if any(p.pdef.frozen or not p.pdef.weight_decay for u in self.units.values() for p in u.params):
+      out = []
+      for u in self.units.values():
+        lo, hi = u.group_rank * u.chunk, (u.group_rank + 1) * u.chunk
+        for p, off in zip(u.params, u.offsets):
+          a, b = max(off, lo), min(off + p.pdef.numel, hi)
+          if not p.pdef.frozen and p.pdef.weight_decay and a < b:
+            out.append((u.shard_offset + a - lo, u.shard_offset + b - lo))
+    self._decay = out
+    return out
+
   def trainable_slices(self):
     """None when every parameter trains; else the [a, b) ranges of this rank's flat shard that belong to trainable ones."""
     cached = getattr(self, "_trainable", False)

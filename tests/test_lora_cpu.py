@@ -136,3 +136,26 @@ def test_cli_lora_run_from_base_checkpoint_writes_peft_adapter(tmp_path):
   _, hist2 = T.main(["train", BASE_YML] + base + ["steps=1", "enable_checkpointing=false", "run_name=lora2", f"load_parameters_path={ck}",
                                                   "lora={enable_lora: true, lora_rank: 4, lora_alpha: 8.0, lora_restore_path: " + d + "}"])
   assert hist2[0]["learning/loss"] < hist[0]["learning/loss"]
+
+
+def test_trainable_parameters_mask_and_adamw_mask():
+  """`trainable_parameters_mask`: only matching parameters change. `adamw_mask`: matching parameters get no weight decay
+  (with a zero learning-rate-independent check: under pure decay, lr > 0 and zero gradients they must stay put)."""
+  cfg = tiny_config("llama3-8b", ["trainable_parameters_mask=['.*mlp/wo.*','decoder_norm']"])
+  eng = make_engine(cfg)
+  before = {n: eng.store.full_master(p).clone() for n, p in eng.store.params.items()}
+  b = batch_of(cfg)
+  for _ in range(3):
+    eng.train_step(b)
+  changed = {n for n, p in eng.store.params.items() if not torch.equal(before[n], eng.store.full_master(p))}
+  assert changed == {n for n in before if "mlp/wo" in n or "decoder_norm" in n}, sorted(changed)
+  # decay mask: zero gradients (all-padding batch has zero loss weight), so the update is decay only
+  cfg2 = tiny_config("llama3-8b", ["adamw_mask=['.*norm.*','.*embedding.*']", "adam_weight_decay=0.5", "learning_rate=0.1"])
+  eng2 = make_engine(cfg2)
+  before = {n: eng2.store.full_master(p).clone() for n, p in eng2.store.params.items()}
+  b2 = dict(batch_of(cfg2))
+  b2["targets_segmentation"] = torch.zeros_like(b2["targets"])
+  eng2.train_step(b2)
+  for n, p in eng2.store.params.items():
+    same = torch.equal(before[n], eng2.store.full_master(p))
+    assert same == ("norm" in n or "embedding" in n), n
