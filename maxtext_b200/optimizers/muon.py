@@ -32,10 +32,19 @@ def newton_schulz(x: torch.Tensor, steps: int = 5, coeffs=NS_COEFFS, eps: float 
   if transposed:
     x = x.transpose(-1, -2)
   x = x / (x.norm(dim=(-2, -1), keepdim=True) + eps)
-  for _ in range(steps):
-    A = x @ x.transpose(-1, -2)
-    B = b * A + c * (A @ A)
-    x = a * x + B @ x
+  if x.is_cuda and x.dim() == 2:
+    # bf16 iterations on this repository's GEMM (nt, then two nn products per step), as the reference runs them in bf16
+    xb = x.to(torch.bfloat16).contiguous()
+    for _ in range(steps):
+      A = F.mm(xb, xb, False, True)
+      B = (b * A + c * F.mm(A, A, False, False)).to(torch.bfloat16)
+      xb = (a * xb + F.mm(B, xb, False, False)).to(torch.bfloat16)
+    x = xb.to(x.dtype)
+  else:
+    for _ in range(steps):
+      A = x @ x.transpose(-1, -2)
+      B = b * A + c * (A @ A)
+      x = a * x + B @ x
   return x.transpose(-1, -2) if transposed else x
 
 

@@ -163,3 +163,18 @@ def test_int8_quantization_numerics_and_training():
     assert abs(l0 - losses[0]) < 0.05 and l0 != losses[0]
   finally:
     Q.set_mode("")
+
+
+def test_muon_newton_schulz_and_training():
+  import torch
+  from helpers import tiny_config, make_engine, batch_of
+  from maxtext_b200.optimizers.muon import newton_schulz
+  torch.manual_seed(0)
+  for shape in ((32, 64), (64, 32), (3, 16, 24)):
+    o = newton_schulz(torch.randn(*shape), steps=8)
+    sv = torch.linalg.svdvals(o)
+    assert o.shape == shape and float(sv.max()) < 1.3 and float(sv.min()) > 0.5, (shape, sv.min(), sv.max())
+  eng = make_engine(tiny_config("llama3-8b", ["opt_type=muon"]))
+  b = batch_of(eng.config)
+  losses = [float(eng.train_step(b)["learning/loss"]) for _ in range(5)]
+  assert losses[-1] < losses[0], losses

@@ -117,3 +117,17 @@ def test_embedding():
   E.embedding_bwd(tok, dy, dt)
   want = torch.zeros(V, D, device="cuda").index_add_(0, tok.long(), dy.float())
   assert (dt - want).abs().max() <= 1e-3
+
+
+@pytest.mark.gpu
+def test_muon_newton_schulz_on_the_repository_gemm():
+  """The GPU path runs the iteration in bf16 on this repository's GEMM; it must orthogonalise like the fp32 definition."""
+  from maxtext_b200.optimizers.muon import newton_schulz
+  torch.manual_seed(0)
+  for shape in ((256, 512), (512, 256)):
+    x = torch.randn(*shape)
+    want = newton_schulz(x, steps=5)
+    got = newton_schulz(x.cuda(), steps=5).float().cpu()
+    assert (got - want).abs().max() < 0.05 * want.abs().max() + 0.02, (got - want).abs().max()
+    sv = torch.linalg.svdvals(got)
+    assert float(sv.max()) < 1.3 and float(sv.min()) > 0.4
