@@ -66,9 +66,40 @@ def _locate(pdef, cfg) -> tuple[str, int | None]:
 _EXPERT_PART = {"wi_0": "gate", "wi_1": "up", "wo": "down", "wi_0_bias": "gate_bias", "wi_1_bias": "up_bias", "wo_bias": "down_bias"}
 
 
+def _llama4_vision_name(path: str) -> tuple[str, str] | None:
+  """Llama-4 vision tower (HF: `vision_model.*`, `multi_modal_projector.linear_1`)."""
+  import re
+  vm = "vision_model."
+  rest = path.split("/", 2)[2] if path.count("/") >= 2 else ""
+  if path.startswith("vision_encoder/Llama4MultiModalProjector_0/"):
+    return "multi_modal_projector.linear_1.weight", "linear"
+  top = {"Llama4UnfoldConvolution_0/vit_unfold_linear/kernel": (vm + "patch_embedding.linear.weight", "linear"),
+         "class_embedding": (vm + "class_embedding", "vec"), "positional_embedding_vlm": (vm + "positional_embedding_vlm", "vec"),
+         "layernorm_pre/scale": (vm + "layernorm_pre.weight", "vec"), "layernorm_pre/bias": (vm + "layernorm_pre.bias", "vec"),
+         "layernorm_post/scale": (vm + "layernorm_post.weight", "vec"), "layernorm_post/bias": (vm + "layernorm_post.bias", "vec"),
+         "Llama4VisionPixelShuffleMLP_0/pixel_shuffle_mlp/vit_pixel_shuffle_mlp_fc1/kernel": (vm + "vision_adapter.mlp.fc1.weight", "linear"),
+         "Llama4VisionPixelShuffleMLP_0/pixel_shuffle_mlp/vit_pixel_shuffle_mlp_fc2/kernel": (vm + "vision_adapter.mlp.fc2.weight", "linear")}
+  if rest in top:
+    return top[rest]
+  m = re.match(r"Llama4VisionEncoder_0/layers_(\d+)/(.+)", rest)
+  if not m:
+    return None
+  pre = f"{vm}model.layers.{m.group(1)}."
+  sub = {"input_layer_norm": "input_layernorm", "post_attention_layer_norm": "post_attention_layernorm",
+         "self_attention_vision/query": "self_attn.q_proj", "self_attention_vision/key": "self_attn.k_proj",
+         "self_attention_vision/value": "self_attn.v_proj", "self_attention_vision/out": "self_attn.o_proj",
+         "Llama4VisionMLP_0/vit_encoder_layer_mlp_fc1": "mlp.fc1", "Llama4VisionMLP_0/vit_encoder_layer_mlp_fc2": "mlp.fc2"}
+  mod, leaf = m.group(2).rsplit("/", 1)
+  if mod not in sub:
+    return None
+  return pre + sub[mod] + (".bias" if leaf == "bias" else ".weight"), ("linear" if leaf == "kernel" else "vec")
+
+
 def _vision_name(path: str) -> tuple[str, str] | None:
   """Gemma-3 vision tower and projector (HF: SigLIP under model.vision_tower, model.multi_modal_projector)."""
   import re
+  if path.startswith(("vision_encoder/Llama4VisionModel_0/", "vision_encoder/Llama4MultiModalProjector_0/")):
+    return _llama4_vision_name(path)
   vt = "model.vision_tower.vision_model."
   if path.startswith("vision_encoder/VisionEmbedder_0/"):
     return {"mm_soft_embedding_norm/scale": ("model.multi_modal_projector.mm_soft_emb_norm.weight", "norm"),
@@ -298,7 +329,11 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       continue
     key, kind = m
     if kind.startswith("experts:"):
-      w = _load_experts(hf_state, key, kind.split(":")[1], cfg)
+      w = None
+      for pre_ in (key, "language_model." + key, "model.language_model." + key[6:]):      # multimodal checkpoints nest the text model
+        w = _load_experts(hf_state, pre_, kind.split(":")[1], cfg)
+        if w is not None:
+          break
       if w is None:
         missing.append(name)
         continue
@@ -306,6 +341,8 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
       continue
     if key not in hf_state and key.startswith("model.") and "model.language_model." + key[6:] in hf_state:
       key = "model.language_model." + key[6:]          # multimodal checkpoints nest the text model one level deeper
+    if key not in hf_state and "language_model." + key in hf_state:
+      key = "language_model." + key                    # Llama-4 multimodal checkpoints
     if key not in hf_state:
       for a, b_ in _ALIASES:
         if a in key and key.replace(a, b_) in hf_state:

@@ -232,10 +232,11 @@ class Transformer:
     # multimodal: the vision tower is a unit of its own; it is frozen unless freeze_vision_encoder_params is off
     self.vision, self.vision_params = None, []
     if bool(getattr(c, "use_multimodal", False)) and self.has_embed:
-      if (getattr(c, "vision_encoder_block", "") or c.decoder_block) != "gemma3":
-        raise NotImplementedError("use_multimodal is implemented for the Gemma-3 vision tower")
-      from .vision import Gemma3Vision
-      self.vision = Gemma3Vision(c, self.par)
+      kind = getattr(c, "vision_encoder_block", "") or c.decoder_block
+      if kind not in ("gemma3", "llama4"):
+        raise NotImplementedError("use_multimodal is implemented for the Gemma-3 and Llama-4 vision towers")
+      from .vision import Gemma3Vision, Llama4Vision
+      self.vision = (Gemma3Vision if kind == "gemma3" else Llama4Vision)(c, self.par)
       self.vision_params = self.vision.params
       if bool(getattr(c, "freeze_vision_encoder_params", True)):
         for p in self.vision_params:
@@ -335,7 +336,8 @@ class Transformer:
     if images is not None:
       from ..multimodal.utils import bidirectional_block_mask
       mm = self.encode_images(images, image_mask)
-      ctx.bidir = bidirectional_block_mask(mm[1])
+      if self.vision.__class__.__name__ == "Gemma3Vision":      # Llama-4 keeps plain causal attention over image tokens
+        ctx.bidir = bidirectional_block_mask(mm[1])
     x = self.embed(tokens, positions, mm)
     for i, layer in enumerate(self.layers):
       ctx.layer_index = i

@@ -103,3 +103,125 @@ class Gemma3Vision:
       x = tF.avg_pool2d(x.view(B * N, g, g, -1).permute(0, 3, 1, 2).float(), g // out_w).permute(0, 2, 3, 1).reshape(B * N, out_w * out_w, -1).to(dt)
     x = F.linear(self.soft_norm(x), self.proj)
     return x.view(B, N, x.shape[1], -1)
+
+
+# =============================================================================================== Llama-4
+def _rope_2d_angles(grid: int, head_dim: int, theta: float, device) -> torch.Tensor:
+  """Angles [grid*grid + 1, head_dim/2] of the Llama-4 vision rotary embedding: the first half of a head's lane pairs
+  rotates with the patch column (x + 1), the second half with the patch row (y + 1); the class token (last) is not rotated."""
+  n = grid * grid
+  idx = torch.arange(n, device=device)
+  x, y = (idx % grid).float() + 1.0, (idx // grid).float() + 1.0
+  fd = head_dim // 2
+  freq = 1.0 / (theta ** (torch.arange(0, fd, 2, device=device)[: fd // 2].float() / fd))      # [head_dim/4]
+  ang = torch.cat([x[:, None] * freq[None], y[:, None] * freq[None]], dim=-1)                   # [n, head_dim/2]
+  return torch.cat([ang, torch.zeros(1, ang.shape[1], device=device)], dim=0)
+
+
+def _rotate_pairs(t: torch.Tensor, ang: torch.Tensor) -> torch.Tensor:
+  """t [B, S, H, Dh] with adjacent lane pairs (re, im); ang [S, Dh/2]."""
+  tf = t.float()
+  re, im = tf[..., 0::2], tf[..., 1::2]
+  c, s = torch.cos(ang)[None, :, None, :], torch.sin(ang)[None, :, None, :]
+  return torch.stack([re * c - im * s, re * s + im * c], dim=-1).flatten(-2).to(t.dtype)
+
+
+class _Llama4EncoderLayer:
+  def __init__(self, b: L.Builder, c, i: int):
+    d, h = c.hidden_size_for_vit, c.num_attention_heads_for_vit
+    self.h, self.dh = h, d // h
+    lb = b.sub("Llama4VisionEncoder_0", f"layers_{i}")
+    eps = 1e-5
+    self.ln0 = L.Norm(lb, "input_layer_norm", d, eps, kind="layernorm")
+    ab = lb.sub("self_attention_vision")
+    mk = lambda n: ab.sub(n).linear("kernel", (d,), (h, self.dh), ("embed", "heads", "kv"))  # noqa: E731
+    self.q, self.k, self.v = mk("query"), mk("key"), mk("value")
+    self.o = ab.sub("out").linear("kernel", (h, self.dh), (d,), ("heads", "kv", "embed"))
+    self.bq, self.bk, self.bv = (ab.sub(n).vector("bias", d, ("heads",), init="zeros") for n in ("query", "key", "value"))
+    self.bo = ab.sub("out").vector("bias", d, ("embed",), init="zeros")
+    self.ln1 = L.Norm(lb, "post_attention_layer_norm", d, eps, kind="layernorm")
+    mb = lb.sub("Llama4VisionMLP_0")
+    f = c.intermediate_size_for_vit
+    self.w1 = mb.sub("vit_encoder_layer_mlp_fc1").linear("kernel", (d,), (f,), ("embed", "mlp"))
+    self.b1 = mb.sub("vit_encoder_layer_mlp_fc1").vector("bias", f, ("mlp",), init="zeros")
+    self.w2 = mb.sub("vit_encoder_layer_mlp_fc2").linear("kernel", (f,), (d,), ("mlp", "embed"))
+    self.b2 = mb.sub("vit_encoder_layer_mlp_fc2").vector("bias", d, ("embed",), init="zeros")
+
+  def __call__(self, x, ang):
+    B, S, _ = x.shape
+    y = self.ln0(x)
+    q = _rotate_pairs(F.linear(y, self.q, bias=self.bq).view(B, S, self.h, self.dh), ang)
+    k = _rotate_pairs(F.linear(y, self.k, bias=self.bk).view(B, S, self.h, self.dh), ang)
+    v = F.linear(y, self.v, bias=self.bv).view(B, S, self.h, self.dh)
+    a = ref.attention(q, k, v, None, 1.0 / math.sqrt(self.dh)).to(x.dtype)
+    x = x + F.linear(a.reshape(B, S, -1), self.o, bias=self.bo)
+    y = F.linear(self.ln1(x), self.w1, bias=self.b1)
+    y = tF.gelu(y.float()).to(x.dtype)
+    return x + F.linear(y, self.w2, bias=self.b2)
+
+
+class Llama4Vision:
+  """Llama-4 vision tower, pixel-shuffle adapter and projector (src/maxtext/models/llama4.py:44-300, 623-825).
+
+  Tiles [M, 3, H, W] -> unfolded patches -> linear -> + class token (appended last) -> + positions -> LayerNorm ->
+  encoder layers with the two-dimensional rotary embedding -> LayerNorm -> class token dropped -> pixel shuffle (each
+  2 x 2 block of patches becomes one token with four times the channels) -> two GELU linears -> projection to the language
+  model width. `__call__(tiles [B, N, 3, H, W]) -> [B, N, tokens, emb_dim]`."""
+
+  def __init__(self, config, par: dict):
+    c = self.c = config
+    b = L.Builder(c, "vision", None, None, **par)
+    vb = b.sub("vision_encoder", "Llama4VisionModel_0")
+    P, C, d = c.patch_size_for_vit, c.num_channels_for_vit, c.hidden_size_for_vit
+    tile = int(getattr(c, "tile_size_for_vit", 0) or c.image_size_for_vit)
+    self.tile, self.grid = tile, tile // P
+    # HF / reference unfold order: (channel, row, column) inside a patch
+    self.patch = vb.sub("Llama4UnfoldConvolution_0", "vit_unfold_linear").linear("kernel", (C, P, P), (d,), (None, None, None, "embed"))
+    self.cls = vb.vector("class_embedding", d, ("embed",), init="zeros")
+    self.pos = vb.table("positional_embedding_vlm", (self.grid * self.grid + 1, d), (None, "embed"), init="fan_in_normal")
+    self.ln_pre = L.Norm(vb, "layernorm_pre", d, 1e-5, kind="layernorm")
+    self.ln_post = L.Norm(vb, "layernorm_post", d, 1e-5, kind="layernorm")
+    self.layers = [_Llama4EncoderLayer(vb, c, i) for i in range(c.num_hidden_layers_for_vit)]
+    r = float(c.pixel_shuffle_ratio_for_vit)
+    self.ratio = r
+    shuffled = int(d / (r * r))
+    pin, pout = int(c.projector_input_dim_for_vit), int(c.projector_output_dim_for_vit)
+    sb = vb.sub("Llama4VisionPixelShuffleMLP_0", "pixel_shuffle_mlp")
+    self.fc1 = sb.sub("vit_pixel_shuffle_mlp_fc1").linear("kernel", (shuffled,), (pin,), ("embed", "mlp"))
+    self.fc2 = sb.sub("vit_pixel_shuffle_mlp_fc2").linear("kernel", (pin,), (pout,), ("mlp", "embed"))
+    self.proj = b.sub("vision_encoder", "Llama4MultiModalProjector_0", "vit_multi_modal_projector").linear(
+        "kernel", (int(c.vision_output_dim_for_vit),), (c.emb_dim,), ("embed", "embed_out"))
+    self.theta = float(c.rope_theta_for_vit)
+    self.params = b.params
+
+  def _pixel_shuffle(self, x):
+    """[M, g*g, d] -> [M, (g r)^2, d / r^2]: fold neighbouring columns, then neighbouring rows, into the channel dim."""
+    M, n, d = x.shape
+    g, r = self.grid, self.ratio
+    x = x.view(M, g, g, d)
+    x = x.view(M, g, int(g * r), int(d / r))
+    x = x.permute(0, 2, 1, 3).contiguous()
+    x = x.view(M, int(g * r), int(g * r), int(d / (r * r)))
+    x = x.permute(0, 2, 1, 3).contiguous()
+    return x.view(M, -1, x.shape[-1])
+
+  def __call__(self, tiles: torch.Tensor) -> torch.Tensor:
+    B, N = tiles.shape[:2]
+    dt = self.patch.data.dtype
+    img = tiles.reshape(B * N, *tiles.shape[2:]).to(dt)
+    M, C, H, W = img.shape
+    P, g = self.c.patch_size_for_vit, self.grid
+    assert H == W == g * P, f"tiles must be {g * P} x {g * P}"
+    patches = img.view(M, C, g, P, g, P).permute(0, 2, 4, 1, 3, 5).reshape(M, g * g, C * P * P)
+    x = F.linear(patches, self.patch)
+    x = torch.cat([x, self.cls.leaf().to(dt)[None, None].expand(M, 1, -1)], dim=1) + self.pos.leaf().to(dt)[None]
+    x = self.ln_pre(x)
+    ang = _rope_2d_angles(g, self.layers[0].dh, self.theta, x.device)
+    for lyr in self.layers:
+      x = lyr(x, ang)
+    x = self.ln_post(x)[:, :-1]
+    x = self._pixel_shuffle(x)
+    x = tF.gelu(F.linear(x, self.fc1).float()).to(dt)
+    x = tF.gelu(F.linear(x, self.fc2).float()).to(dt)
+    x = F.linear(x, self.proj)
+    return x.view(B, N, x.shape[1], -1)

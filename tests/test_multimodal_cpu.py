@@ -91,3 +91,65 @@ def test_multimodal_training_and_generation():
   prefix, _ = me.prefill(prompt, 270, images=b["images"][0], image_mask=mask[0])
   full = eng.model.forward(prompt[None], images=b["images"][:1], image_mask=mask[:1, :270])[:, -1]
   assert (prefix.logits - full).abs().max() < 1e-4
+
+
+def test_llama4_multimodal_logits_match_hf():
+  transformers = pytest.importorskip("transformers")
+  from maxtext_b200.checkpoint_conversion import hf as conv
+  cfg = tiny_config("llama4-17b-16e", [
+      "base_num_decoder_layers=4", "num_experts=4", "base_moe_mlp_dim=32", "chunk_attn_window_size=16", "nope_layer_interval=2",
+      "interleave_moe_layer_step=2", "use_multimodal=true", "hidden_size_for_vit=32", "intermediate_size_for_vit=128",
+      "num_hidden_layers_for_vit=2", "num_attention_heads_for_vit=4", "image_size_for_vit=32", "tile_size_for_vit=32", "patch_size_for_vit=4",
+      "projector_input_dim_for_vit=48", "projector_output_dim_for_vit=48", "vision_output_dim_for_vit=48", "pixel_shuffle_ratio_for_vit=0.5",
+      "rope_theta_for_vit=10000", "vocab_size=128", "max_target_length=64", "rope_max_timescale=10000", "weight_init=normal"])
+  vc = dict(hidden_size=32, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=32, patch_size=4, num_channels=3,
+            projector_input_dim=48, projector_output_dim=48, vision_output_dim=48, pixel_shuffle_ratio=0.5, projector_dropout=0.0,
+            rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+  tc = dict(hidden_size=64, intermediate_size=32, intermediate_size_mlp=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+            head_dim=16, vocab_size=128, num_local_experts=4, num_experts_per_tok=1, interleave_moe_layer_step=2, no_rope_layers=[1, 0, 1, 0],
+            attention_chunk_size=16, use_qk_norm=True, attn_temperature_tuning=True, floor_scale=8192, attn_scale=0.1,
+            rms_norm_eps=cfg.normalization_layer_epsilon, tie_word_embeddings=False, max_position_embeddings=64,
+            rope_parameters={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192, "rope_theta": 10000.0})
+  try:
+    hc = transformers.Llama4Config(text_config=tc, vision_config=vc, image_token_index=100, boi_token_index=101, eoi_token_index=102)
+  except TypeError as e:
+    pytest.skip(str(e))
+  for c_ in (hc, hc.text_config, hc.vision_config):
+    c_._attn_implementation = "eager"
+  torch.manual_seed(0)
+  hf = transformers.Llama4ForConditionalGeneration(hc).float().eval()
+  g = torch.Generator().manual_seed(5)
+  for n, p in hf.named_parameters():
+    if n.startswith(("vision_model", "multi_modal_projector")) or "experts" in n:
+      p.data = 0.15 * torch.randn(p.shape, generator=g) + (1.0 if ("norm" in n and n.endswith("weight")) else 0.0)
+  eng = make_engine(cfg)
+  assert not conv.to_maxtext(hf.state_dict(), eng.store, cfg)
+  toks = torch.randint(0, 100, (1, 48))
+  toks[0, 3], toks[0, 4:20], toks[0, 20], toks[0, 21:37], toks[0, 37] = 101, 100, 100, 100, 102      # two tiles of 16 soft tokens
+  mask = torch.zeros(1, 48, dtype=torch.bool)
+  mask[0, 4:20] = mask[0, 21:37] = True
+  toks[0, 20] = 7
+  tiles = torch.randn(2, 3, 32, 32)
+  ids = toks.clone()
+  ids[mask] = 100
+  with torch.no_grad():
+    want = hf(input_ids=ids, pixel_values=tiles, attention_mask=torch.ones_like(ids)).logits
+  got = eng.model.forward(torch.where(mask, torch.zeros_like(toks), toks), images=tiles[None], image_mask=mask)
+  assert (got - want).abs().max() < 5e-5 * max(1.0, float(want.abs().max())), (got - want).abs().max()
+  assert (eng.model.forward(torch.where(mask, torch.zeros_like(toks), toks), images=tiles[None] * 0, image_mask=mask) - got).abs().max() > 1e-3
+
+
+def test_llama4_processor_tiles_and_tokens():
+  from maxtext_b200.multimodal import processor_llama4 as pl
+  assert pl.best_grid(336, 336) == (1, 1) and pl.best_grid(336, 700) == (1, 2) and pl.best_grid(1000, 340) == (3, 1)
+  assert pl.tokens_per_tile() == 144 and max(h * w for h, w in pl.supported_grids()) == 16
+  rng = np.random.default_rng(0)
+  tiles, grid = pl.preprocess_image(rng.integers(0, 255, (60, 130, 3), dtype=np.uint8), tile=32, max_tiles=4)
+  assert grid == (2, 4) or grid[0] * grid[1] <= 4
+  assert tiles.shape[1:] == (3, 32, 32) and tiles.shape[0] == grid[0] * grid[1] + (1 if grid[0] * grid[1] > 1 else 0)
+  seq = pl.image_tokens((2, 2), 4)
+  assert len(seq) == 27 and seq[0] == pl.BEGIN_IMAGE_TOKEN and seq[-1] == pl.END_IMAGE_TOKEN and seq.count(pl.PATCH_TOKEN) == 20
+  assert seq.count(pl.TILE_X_SEPARATOR_TOKEN) == 2 and seq.count(pl.TILE_Y_SEPARATOR_TOKEN) == 2 and seq[-6] == pl.IMAGE_TOKEN
+  ids, mask, pix = pl.prepare([5, pl.IMAGE_TOKEN, 6], [rng.integers(0, 255, (32, 64, 3), dtype=np.uint8)], tile=32, patch=4, max_tiles=4)
+  assert pix.shape[0] == 3 and int(mask.sum()) == 3 * pl.tokens_per_tile(32, 4) and ids[0] == 5 and ids[-1] == 6
