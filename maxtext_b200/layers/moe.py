@@ -66,6 +66,23 @@ class _ReduceScatterRows(torch.autograd.Function):
     return out, None
 
 
+class _AllReduceMean(torch.autograd.Function):
+  """Mean over a group of equally weighted partial means; every rank uses the result in an identical loss term, so the
+  gradient of a rank's part is the mean of the ranks' output gradients."""
+  @staticmethod
+  def forward(ctx, x, group, n):
+    ctx.group, ctx.n = group, n
+    y = x.contiguous().clone()
+    dist.all_reduce(y, group=group)
+    return y / n
+
+  @staticmethod
+  def backward(ctx, dy):
+    g = dy.contiguous().clone()
+    dist.all_reduce(g, group=ctx.group)
+    return g / ctx.n, None, None
+
+
 class RoutedMoE:
   def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False, style: str = ""):
     """style: "llama4" (raw top-k logits, sigmoid score applied to the expert input, unit combine weights;
@@ -92,7 +109,7 @@ class RoutedMoE:
       self.bo = mb.table("wo_bias", (self.E, d), ("exp", "activation_embed"), init="zeros")
 
   # ---- routing
-  def route(self, x2, B, S):
+  def route(self, x2, B, S, ctx=None):
     c = self.c
     xg = x2.float() if c.float32_gate_logits else x2
     w = self.gate.leaf()
@@ -129,6 +146,12 @@ class RoutedMoE:
           1, idx, torch.ones_like(idx, dtype=torch.float32))
       density = onehot.view(B, S, self.E).mean(1)
       density_prob = probs.view(B, S, self.E).mean(1)
+      if ctx is not None and ctx.cp_size > 1:
+        # context parallelism: the two means run over the whole sequence, of which this rank holds a part
+        cp_axes = ("context", "context_usp_ulysses")
+        g = ctx.mesh.group(cp_axes) if ctx.mesh is not None else ctx.cp_group
+        density = _AllReduceMean.apply(density, g, ctx.cp_size)
+        density_prob = _AllReduceMean.apply(density_prob, g, ctx.cp_size)
       aux = (density * density_prob).mean() * (self.E ** 2) * c.load_balance_loss_weight
     return wts, idx, aux
 
@@ -192,7 +215,7 @@ class RoutedMoE:
       if ctx.tp_size > 1:
         out = tp_exit(out, ctx)
       return out.view(B, S, D)
-    wts, idx, aux = self.route(x2, B, S)
+    wts, idx, aux = self.route(x2, B, S, ctx)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))
     if (self.gate_bias is not None and self.deepseek and self.c.routed_bias_update_rate > 0 and ctx.expert_counts is not None

@@ -59,7 +59,9 @@ class TrainEngine:
     self.inner_world = self.world // n_rep
     self._accum = None
     self._units = self._ordered_units()
-    self.n_moe_layers = sum(1 for l in self.model.layers for b in l.plan.blocks if b.mlp in ("moe", "moe_shared"))
+    from ..models import families as _fam
+    # all MoE blocks of the model, also those that live on other pipeline stages (the balance loss is averaged over them)
+    self.n_moe_layers = sum(1 for pl in _fam.layer_plans(c) for b in pl.blocks if b.mlp in ("moe", "moe_shared"))
     self.all_group = None  # WORLD
 
   # ------------------------------------------------------------------ unit bookkeeping
@@ -299,7 +301,8 @@ class TrainEngine:
     if self.inner_world > 1:
       t = total_w.clone()
       dist.all_reduce(t, group=self.inner_group)
-      dup = self.mesh.axis_size(("tensor", "tensor_sequence")) if self.mesh is not None else 1
+      # tensor ranks and pipeline stages see the same tokens
+      dup = self.mesh.axis_size(("tensor", "tensor_sequence", "stage")) if self.mesh is not None else 1
       return t / dup if dup > 1 else t
     return total_w
 
@@ -403,7 +406,9 @@ class TrainEngine:
     stats = torch.stack([acc["loss_sum"], acc["z_sum"], acc["weights"], acc["aux"], acc.get("mtp", torch.zeros((), device=self.device))])
     if self.inner_world > 1:
       dist.all_reduce(stats, group=self.inner_group)
-      stats[3] /= self.inner_world
+      # the balance loss: summed over pipeline stages (each holds some of the layers), averaged over the ranks that hold the
+      # same layers (data shards and tensor ranks)
+      stats[3] /= max(1, self.inner_world // (self.mesh.axis_size("stage") if self.mesh is not None else 1))
       # ranks along the tensor axes score the same tokens: count each token once (the gradient itself is summed over the
       # data axes only, so without this the normaliser, and with it the clipping threshold, would be off by the TP degree)
       dup = self.mesh.axis_size(("tensor", "tensor_sequence")) if self.mesh is not None else 1

@@ -46,8 +46,8 @@ class PipelineEngine(TrainEngine):
     self._pending = []
 
   # ---- plumbing
-  def _replication(self, u) -> float:
-    return max(1.0, super()._replication(u) / self.P)        # every stage holds different parameters
+  def _replication(self, u, params=None) -> float:
+    return max(1.0, super()._replication(u, params) / self.P)        # every stage holds different parameters
 
   def _send(self, t, dst):
     self._pending.append((dist.isend(t.contiguous(), dst), t))
@@ -99,6 +99,10 @@ class PipelineEngine(TrainEngine):
     act_dtype = torch.bfloat16 if c.dtype == "bfloat16" else torch.float32
     sl = lambda t, m: None if t is None else t[m * mb:(m + 1) * mb]  # noqa: E731
     ctxs = [model.make_ctx(sl(positions, m), sl(seg, m), "train", sl(tokens, m)) for m in range(M)]
+    aux_scale = None
+    if self.n_moe_layers and c.load_balance_loss_weight > 0:
+      # as in the base engine, and every micro-batch's balance loss is a mean over its own rows
+      aux_scale = self._global_weight(weights.sum()) / self.n_moe_layers / self._data_shards() / M
     saved = {}          # (r, m) -> list of (layer, input, remat-saved tensors)
     final = {}          # m -> hidden state entering the head (last stage)
     # ---------------- forward
@@ -115,6 +119,8 @@ class PipelineEngine(TrainEngine):
           ctx.saved, ctx.recompute, ctx.layer_index, ctx.aux_losses = keep, False, layer.index, []
           with torch.no_grad():
             y = layer(x, ctx)
+          if ctx.aux_losses:
+            acc["aux"] += sum(a for _, a in ctx.aux_losses).detach().float() / M
           steps.append((layer, x, keep))
           x = y
         saved[(r, m)] = steps
@@ -153,7 +159,12 @@ class PipelineEngine(TrainEngine):
           ctx.saved, ctx.recompute, ctx.layer_index, ctx.aux_losses = keep, True, layer.index, []
           with torch.enable_grad():
             y = layer(x_in, ctx)
-          torch.autograd.backward([y], [dx])
+            outs, gr = [y], [dx]
+            if aux_scale is not None and ctx.aux_losses:
+              for _, a in ctx.aux_losses:
+                outs.append(a)
+                gr.append(aux_scale.to(a.dtype))
+          torch.autograd.backward(outs, gr)
           dx = x_in.grad
           for p in layer.params:
             p.collect_leaf_grad()

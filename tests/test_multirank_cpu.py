@@ -273,3 +273,22 @@ def test_tensor_sequence_parallel_matches_single(tmp_path, case):
   got = run_ranks(world, base + hot + par, str(tmp_path), "sp")
   _close(got["loss"], one["loss"], 2e-5)
   _close(got["grad_norm"], one["grad_norm"], 2e-4)
+
+
+@pytest.mark.parametrize("layout", ["pp2xtp2", "cp2xtp2", "moe_pp2", "moe_cp2"])
+def test_combined_layouts_match_single_including_grad_norm(single, moe_single, tmp_path, layout):
+  """Pipeline x tensor and context x tensor meshes, and the load-balance loss under pipeline parallelism (each stage adds the
+  loss of its own layers, seeded per micro-batch) and under context parallelism (the per-sequence routing statistics are
+  means over the whole sequence, of which a rank holds a part)."""
+  hot = ["steps=4", "learning_rate=1e-2"]
+  world, base, par = {
+      "pp2xtp2": (4, [], ["per_device_batch_size=1", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2", "ici_tensor_parallelism=2"]),
+      "cp2xtp2": (4, [], ["per_device_batch_size=1", "ici_fsdp_parallelism=1", "ici_context_parallelism=2", "ici_tensor_parallelism=2",
+                          "context_parallel_strategy=all_gather"]),
+      "moe_pp2": (2, MOE_HOT, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2"]),
+      "moe_cp2": (2, MOE_HOT, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_context_parallelism=2",
+                               "context_parallel_strategy=all_gather"])}[layout]
+  want = moe_single if base else run_ranks(1, hot + ["per_device_batch_size=4"], str(tmp_path), "one")
+  got = run_ranks(world, base + hot + par, str(tmp_path), layout)
+  _close(got["loss"], want["loss"], 2e-5)
+  _close(got["grad_norm"], want["grad_norm"], 2e-4)
