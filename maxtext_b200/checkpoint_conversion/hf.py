@@ -45,7 +45,7 @@ def _locate(pdef, cfg) -> tuple[str, int | None]:
     parts = parts[1:]
     if parts[0] == "attention":
       parts[0] = "self_attention"
-  elif blk == "qwen3_next" and parts[0].startswith("layer_"):
+  elif blk in ("qwen3_next", "qwen3_5") and parts[0].startswith("layer_"):
     cyc = max(1, int(cfg.inhomogeneous_layer_cycle_interval))
     L = L * cyc + int(parts[0].split("_")[1])
     parts = parts[1:]
@@ -302,7 +302,7 @@ def _embed_scale(cfg) -> float:
 def _q_scale(cfg) -> float:
   """Factor folded into the stored query projection: 1/sqrt(head_dim) unless the family scales at run time."""
   if cfg.use_qk_norm or cfg.attention_type == "mla" or cfg.decoder_block in ("gemma3", "qwen3", "qwen3_moe", "qwen3_custom_moe", "olmo3",
-                                                                              "llama4", "gpt_oss", "qwen3_next"):
+                                                                              "llama4", "gpt_oss", "qwen3_next", "qwen3_5"):
     return 1.0
   return 1.0 / math.sqrt(cfg.head_dim)
 
@@ -316,6 +316,46 @@ def _interleaved(cfg) -> bool:
 
 
 _ALIASES = (("block_sparse_moe.gate", "mlp.gate"),)
+
+
+def _gdn_dims(cfg):
+  hk, hv, dk, dv = int(cfg.gdn_num_key_heads), int(cfg.gdn_num_value_heads), int(cfg.gdn_key_head_dim), int(cfg.gdn_value_head_dim)
+  return hk, hv, dk, dv, hv // hk
+
+
+def _qwen35_pack(hf_state: dict, key: str, cfg) -> torch.Tensor | None:
+  """Qwen3.5 stores the gated-delta input projections flat and separate (in_proj_qkv = [q | k | v], in_proj_z, in_proj_b,
+  in_proj_a); the layer here (like Qwen3-Next) wants them grouped per key head: [q_h | k_h | v of its value heads | z of
+  them] and [b | a]."""
+  hk, hv, dk, dv, r = _gdn_dims(cfg)
+  base = key.rsplit(".", 2)[0] + "."
+  if key.endswith("in_proj_qkvz.weight"):
+    qkv, z = hf_state.get(base + "in_proj_qkv.weight"), hf_state.get(base + "in_proj_z.weight")
+    if qkv is None or z is None:
+      return None
+    qkv, z = qkv.float(), z.float()
+    d = qkv.shape[1]
+    q, k, v = qkv[:hk * dk].view(hk, dk, d), qkv[hk * dk:2 * hk * dk].view(hk, dk, d), qkv[2 * hk * dk:].view(hk, r * dv, d)
+    return torch.cat([q, k, v, z.view(hk, r * dv, d)], dim=1).reshape(-1, d)
+  b, a = hf_state.get(base + "in_proj_b.weight"), hf_state.get(base + "in_proj_a.weight")
+  if b is None or a is None:
+    return None
+  d = b.shape[1]
+  return torch.cat([b.float().view(hk, r, d), a.float().view(hk, r, d)], dim=1).reshape(-1, d)
+
+
+def _qwen35_unpack(out: dict, key: str, w: torch.Tensor, cfg):
+  hk, hv, dk, dv, r = _gdn_dims(cfg)
+  base = key.rsplit(".", 2)[0] + "."
+  d = w.shape[1]
+  if key.endswith("in_proj_qkvz.weight"):
+    g = w.view(hk, 2 * dk + 2 * r * dv, d)
+    q, k, v, z = g[:, :dk], g[:, dk:2 * dk], g[:, 2 * dk:2 * dk + r * dv], g[:, 2 * dk + r * dv:]
+    out[base + "in_proj_qkv.weight"] = torch.cat([q.reshape(-1, d), k.reshape(-1, d), v.reshape(-1, d)]).contiguous()
+    out[base + "in_proj_z.weight"] = z.reshape(-1, d).contiguous()
+  else:
+    g = w.view(hk, 2 * r, d)
+    out[base + "in_proj_b.weight"], out[base + "in_proj_a.weight"] = g[:, :r].reshape(-1, d).contiguous(), g[:, r:].reshape(-1, d).contiguous()
 
 
 def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
@@ -338,6 +378,13 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
         missing.append(name)
         continue
       store.load_full(name, p.pdef.local_slice(w.contiguous().reshape(p.pdef.global_shape())))
+      continue
+    if cfg.decoder_block == "qwen3_5" and key.endswith(("in_proj_qkvz.weight", "in_proj_ba.weight")) and key not in hf_state:
+      w = _qwen35_pack(hf_state, key, cfg)
+      if w is None:
+        missing.append(name)
+        continue
+      store.load_full(name, p.pdef.local_slice(w.reshape(p.pdef.global_shape())))
       continue
     if key not in hf_state and key.startswith("model.") and "model.language_model." + key[6:] in hf_state:
       key = "model.language_model." + key[6:]          # multimodal checkpoints nest the text model one level deeper
@@ -391,6 +438,9 @@ def to_hf(store, cfg) -> dict:
     w = store.full_master(p).float().clone()
     if kind.startswith("experts:"):
       _store_experts(out, key, kind.split(":")[1], w, cfg)
+      continue
+    if cfg.decoder_block == "qwen3_5" and key.endswith(("in_proj_qkvz.weight", "in_proj_ba.weight")):
+      _qwen35_unpack(out, key, w, cfg)
       continue
     if kind == "q":
       w = w / _q_scale(cfg)

@@ -27,7 +27,7 @@ def describe(c) -> Family:
   # src/maxtext/checkpoint_conversion/utils/param_mapping.py:498-508)
   if blk == "gpt3":
     return Family(norm_kind="layernorm")
-  if blk == "qwen3_next":
+  if blk in ("qwen3_next", "qwen3_5"):
     return Family(norm_offset=1.0)           # every RMS scale is stored zero-centred and applied as (1 + scale)
   return Family()
 
@@ -102,7 +102,8 @@ def layer_plans(c) -> list[LayerPlan]:
   if blk in ("qwen3_moe", "qwen3_custom_moe"):
     return [LayerPlan("layers", [_llama_like(c, mlp="moe", mlp_name="moe_block", query_scalar=c.head_dim ** -0.5)])
             for _ in range(n)]
-  if blk == "qwen3_next":
+  if blk in ("qwen3_next", "qwen3_5"):
+    # qwen3_5 reuses the qwen3-next layers unchanged (src/maxtext/models/qwen3_5.py)
     # src/maxtext/models/qwen3.py:1196-1420: cycles of inhomogeneous_layer_cycle_interval layers form one scanned block with
     # sub-trees layer_0 .. layer_{n-1}; the last layer of a cycle is gated full attention (partial RoPE, zero-centred
     # per-head q/k norms), the others are gated delta networks; every layer has the routed + gated shared expert MLP
@@ -160,4 +161,4 @@ def layer_plans(c) -> list[LayerPlan]:
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, gpt3, gpt_oss, olmo3, llama4, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, simple)")

@@ -31,6 +31,8 @@ FAMILIES = {
     "llama4-17b-16e": ["base_num_decoder_layers=4", "num_experts=4", "base_moe_mlp_dim=32", "chunk_attn_window_size=16", "nope_layer_interval=2"],
     "qwen3-next-80b-a3b": ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "gdn_key_head_dim=8",
                            "gdn_value_head_dim=8", "gdn_num_key_heads=2", "gdn_num_value_heads=4", "gdn_chunk_size=8"],
+    "qwen3.5-35b-a3b": ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "gdn_key_head_dim=8",
+                        "gdn_value_head_dim=8", "gdn_num_key_heads=2", "gdn_num_value_heads=4", "gdn_chunk_size=8"],
     "gpt-oss-20b": ["base_num_decoder_layers=2", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "sliding_window_size=8"],
 }
 

@@ -159,7 +159,19 @@ def _qwen3_next(_):
   return cfg, transformers.Qwen3NextForCausalLM, hc
 
 
-CASES = {"qwen3_next": _qwen3_next, "gemma": _gemma, "gemma2": _gemma2, "gemma3": _gemma3, "qwen2": _qwen2, "qwen3": _qwen3, "qwen3_moe": _qwen3_moe,
+def _qwen3_5(_):
+  cfg = _tiny("qwen3.5-35b-a3b", ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32",
+                                  "gdn_key_head_dim=8", "gdn_value_head_dim=8", "gdn_num_key_heads=2", "gdn_num_value_heads=4",
+                                  "gdn_chunk_size=8"])
+  hc = transformers.Qwen3_5MoeTextConfig(**_common(
+      cfg, num_hidden_layers=4, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+      linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2, linear_num_value_heads=4,
+      rope_parameters={"rope_theta": float(cfg.rope_max_timescale), "partial_rotary_factor": 0.25, "rope_type": "default",
+                       "mrope_section": [1, 1, 0], "mrope_interleaved": True}))
+  return cfg, transformers.Qwen3_5MoeForCausalLM, hc
+
+
+CASES = {"qwen3_next": _qwen3_next, "qwen3_5": _qwen3_5, "gemma": _gemma, "gemma2": _gemma2, "gemma3": _gemma3, "qwen2": _qwen2, "qwen3": _qwen3, "qwen3_moe": _qwen3_moe,
          "mistral": _mistral, "deepseek2": _deepseek2, "deepseek3": _deepseek3, "gpt_oss": _gpt_oss, "olmo3": _olmo3, "llama4": _llama4}
 
 
