@@ -1,6 +1,6 @@
 """Symmetric memory over NVLink: buffers that every rank of a node can address, plus epoch flags.
 
-MaxText has no communication code of its own: XLA lowers collectives to NCCL (SURVEY §2.7). Here, next to the
+MaxText has no communication code of its own: XLA lowers collectives to NCCL. Here, next to the
 NCCL process groups of `parallel.mesh`, each shard group owns a *symmetric heap*: every rank allocates the same
 buffers and exchanges handles, so a kernel running on one GPU can load from (or store to) the same offset of a
 peer's buffer with plain memory instructions. The fused kernels of `csrc/comm_sm100.cu` and the all-gather GEMM

@@ -2,7 +2,7 @@
 
 A row-parallel linear (attention output, MLP down projection) yields partial sums that must be added over the tensor-parallel
 ranks; so does the input gradient of a column-parallel linear. The reference leaves both to XLA's all-reduce /
-collective-matmul passes ("TP"). Here the GEMM kernel's epilogue adds every finished output tile straight
+collective-matmul passes. Here the GEMM kernel's epilogue adds every finished output tile straight
 into the fp32 accumulation buffer of the rank that owns those rows (a TMA reduce-add into peer memory over NVLink, tile by
 tile while later tiles are still being computed), and one more kernel reads the owners' reduced chunks back, converting to
 bf16 (the all-gather half). Epoch-flag barriers separate the phases; see TPReduceRuntime for the two variants (staged
