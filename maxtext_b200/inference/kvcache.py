@@ -93,6 +93,9 @@ class LayerKVCache:
     mask = ref.attention_mask(pos, kv_pos, None, None, True, window) & (kv_pos < valid_len)[:, None, None, :]
     if ctx.segment_ids is not None and ctx.mode == "prefill":
       mask = mask & (ctx.segment_ids[:, None, :, None] != 0)
+      if ctx.segment_ids.shape[1] == upto:
+        # several prompts packed into one prefill pass (prefill_concat): a token sees its own prompt only
+        mask = mask & (ctx.segment_ids[:, None, :, None] == ctx.segment_ids[:, None, None, :])
     if getattr(ctx, "bidir", None) is not None and ctx.bidir.shape[-2] == S and ctx.bidir.shape[-1] <= upto:
       # multimodal prefill from an empty cache: the soft tokens of one image see each other in both directions
       extra = torch.zeros_like(mask)
@@ -124,6 +127,8 @@ class MlaLayerCache(LayerKVCache):
     v = kv[..., mla.nope:]
     kv_pos = torch.arange(upto, device=q.device)[None].expand(B, upto)
     mask = ref.attention_mask(pos, kv_pos) & (kv_pos < (self.lengths + S)[:, None])[:, None, None, :]
+    if ctx.segment_ids is not None and ctx.mode == "prefill" and ctx.segment_ids.shape[1] == upto:
+      mask = mask & (ctx.segment_ids[:, None, :, None] == ctx.segment_ids[:, None, None, :])      # packed prompts (prefill_concat)
     return ref.attention(q, k, v, mask, 1.0)
 
 

@@ -104,6 +104,57 @@ class MaxEngine:
     res = ResultTokens(torch.tensor([[int(tok), 1, 1]], device=dev), lp)
     return Prefix(caches, true_length, tok, logits, lp), res
 
+  @torch.no_grad()
+  def prefill_multisampling(self, padded_tokens: torch.Tensor, true_length: int, num_samples: int):
+    """One prefill pass, `num_samples` independently sampled first tokens (src/maxtext/inference/maxengine/maxengine.py:998-1180):
+    the prefixes share the cached prompt and differ in their first token, e.g. for best-of-n or GRPO-style rollouts."""
+    prefix, _ = self.prefill(padded_tokens, true_length)
+    out = []
+    for _ in range(int(num_samples)):
+      tok = self._sample(prefix.logits)
+      lp = inference_utils.log_prob_of(prefix.logits, tok) if self.config.return_log_prob else None
+      out.append(Prefix(prefix.caches, prefix.length, tok, prefix.logits, lp))
+    return out
+
+  @torch.no_grad()
+  def prefill_concat(self, prompts: list[torch.Tensor]) -> list[Prefix]:
+    """Several short prompts in one prefill pass (maxengine.py:1180 `prefill_concat`): the prompts are packed into one row
+    with segment ids and per-prompt positions, and the cached keys / values of each segment become that prompt's prefix.
+    Layers with a recurrent state (gated delta networks) cannot be packed this way; such models prefill one by one."""
+    dev = self.device
+    lens = [int(p.numel()) for p in prompts]
+    total = sum(lens)
+    packable = total <= self.max_len and not any(b.plan.attention == "gdn" for l in self.model.layers for b in l.blocks)
+    if not packable or len(prompts) == 1:
+      return [self.prefill(p, n)[0] for p, n in zip(prompts, lens)]
+    toks = torch.cat([p.to(dev).long() for p in prompts])[None]
+    seg = torch.cat([torch.full((n,), i + 1, dtype=torch.int32, device=dev) for i, n in enumerate(lens)])[None]
+    pos = torch.cat([torch.arange(n, device=dev) for n in lens])[None]
+    packed = kvcache.make_caches(self.model, 1, total, dev)
+    zero = torch.zeros(1, dtype=torch.long, device=dev)
+    self._bind(packed, zero, zero)
+    logits = self.model.forward(toks, pos, seg, mode="prefill", caches=packed)[0]
+    out, start = [], 0
+    for n in lens:
+      caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, n), dev)
+      for dst_layer, src_layer in zip(caches, packed):
+        for d, s_ in zip(dst_layer, src_layer):
+          for name in ("k", "v", "ks", "vs", "latent", "k_rope"):
+            if hasattr(s_, name) and hasattr(d, name):
+              getattr(d, name)[0, :n] = getattr(s_, name)[0, start:start + n]
+      lg = logits[start + n - 1][None]
+      tok = self._sample(lg)
+      out.append(Prefix(caches, n, tok, lg, inference_utils.log_prob_of(lg, tok) if self.config.return_log_prob else None))
+      start += n
+    return out
+
+  @torch.no_grad()
+  def bulk_insert(self, prefix: Prefix, state: DecodeState, slots: list[int]) -> DecodeState:
+    """The same prefix into several slots (maxengine.py:1477), e.g. the prefixes of `prefill_multisampling` share a prompt."""
+    for s in slots:
+      state = self.insert(prefix, state, int(s))
+    return state
+
   def prefill_chunked(self, tokens: torch.Tensor, chunk: int | None = None) -> tuple[Prefix, ResultTokens]:
     """Chunked prefill (src/maxtext/inference/kvcache.py:609-712): the prompt enters the cache `chunk` tokens at a time."""
     dev = self.device

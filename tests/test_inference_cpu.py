@@ -121,3 +121,29 @@ def test_serving_loop_batches_concurrent_requests():
   assert out[0]["usage"]["prompt_tokens"] == 4 and loop.served == 2
   app = create_app(loop)
   assert {r.path for r in app.routes} >= {"/v1/health", "/v1/completions"}
+
+
+@pytest.mark.parametrize("model", ["llama3-8b", "deepseek2-16b"])
+def test_prefill_concat_and_multisampling_match_single_prefills(model):
+  from helpers import tiny_config
+  from maxtext_b200.inference.maxengine import MaxEngine
+  cfg = tiny_config(model, ["max_prefill_predict_length=16", "max_target_length=48"])
+  eng = MaxEngine(cfg)
+  eng.load_params()
+  torch.manual_seed(0)
+  prompts = [torch.randint(1, cfg.vocab_size, (n,)) for n in (5, 9, 3)]
+  packed = eng.prefill_concat(prompts)
+  state = eng.init_decode_state(slots=3)
+  state2 = eng.init_decode_state(slots=3)
+  for i, (p, pre) in enumerate(zip(prompts, packed)):
+    single, _ = eng.prefill(torch.nn.functional.pad(p, (0, 16 - p.numel())), p.numel())
+    assert (pre.logits - single.logits).abs().max() < 1e-4 and int(pre.first_token) == int(single.first_token)
+    state, state2 = eng.insert(pre, state, i), eng.insert(single, state2, i)
+  for _ in range(4):                                  # the packed prefixes decode like the single ones
+    state, r1 = eng.generate(state)
+    state2, r2 = eng.generate(state2)
+    assert torch.equal(r1.data[:, 0], r2.data[:, 0])
+  many = eng.prefill_multisampling(torch.nn.functional.pad(prompts[0], (0, 11)), 5, 3)
+  assert len(many) == 3 and all(m.length == 5 and m.caches is many[0].caches for m in many)
+  st = eng.bulk_insert(many[0], eng.init_decode_state(slots=3), [0, 2])
+  assert st.active.tolist() == [True, False, True] and st.next_pos.tolist()[0] == 5
