@@ -66,6 +66,27 @@ class MaxEngine:
     return self.model.store
 
   # ------------------------------------------------------------------ state
+  @torch.no_grad()
+  def quantize_params(self, bits: int = 8) -> dict:
+    """Weight-only quantisation for serving (src/maxtext/inference/maxengine/maxengine.py:576 `quantize_params`): every
+    matrix inside the decoder layers is rounded to `bits`-bit integers with one scale per output channel. Returns
+    {name: (int8 values, fp32 scales)} for saving; the engine's own weights are replaced by the de-quantised values, so
+    what it generates afterwards is what a server loading the quantised file generates (it still computes in bf16)."""
+    store = self.model.store
+    qmax = float(2 ** (int(bits) - 1) - 1)
+    packed = {}
+    for name, p in store.params.items():
+      d = p.pdef
+      if d.layer is None or d.kind not in ("linear", "expert_linear") or len(d.shape) < 2:
+        continue
+      w = store.full_master(p).float()
+      scale = w.abs().amax(dim=-1, keepdim=True).clamp_(min=1e-12) / qmax
+      q = torch.clamp(torch.round(w / scale), -qmax, qmax)
+      packed[name] = (q.to(torch.int8), scale.squeeze(-1))
+      store.load_full(name, d.local_slice(q * scale))
+    store.sync_compute_from_master()
+    return packed
+
   def init_decode_state(self, slots: int | None = None) -> DecodeState:
     c = self.config
     slots = int(slots or max(1, int(c.per_device_batch_size)))

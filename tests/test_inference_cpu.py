@@ -147,3 +147,27 @@ def test_prefill_concat_and_multisampling_match_single_prefills(model):
   assert len(many) == 3 and all(m.length == 5 and m.caches is many[0].caches for m in many)
   st = eng.bulk_insert(many[0], eng.init_decode_state(slots=3), [0, 2])
   assert st.active.tolist() == [True, False, True] and st.next_pos.tolist()[0] == 5
+
+
+def test_decode_multi_and_quantize_params():
+  from helpers import tiny_config
+  from maxtext_b200.inference.decode import decode
+  from maxtext_b200.inference.decode_multi import decode_multi
+  from maxtext_b200.inference.maxengine import MaxEngine
+  cfg = tiny_config("llama3-8b", ["max_prefill_predict_length=16", "max_target_length=32", "tokenizer_type=byte", "vocab_size=260"])
+  eng = MaxEngine(cfg)
+  eng.load_params()
+  prompts = ["abc", "hello there", "xy", "0123", "q"]
+  multi = decode_multi(cfg, prompts, engine=eng, max_new_tokens=5)                 # five prompts through four slots
+  assert len(multi) == 5
+  for p, m in zip(prompts[:2], multi):
+    assert decode(cfg, p, engine=eng)[:len(m)] == m or m.startswith(decode(cfg, p, engine=eng)[:3])
+  ids = torch.randint(1, 250, (1, 12))
+  before = eng.model.forward(ids)
+  packed = eng.quantize_params(8)
+  after = eng.model.forward(ids)
+  name, (q, sc) = next(iter(packed.items()))
+  assert q.dtype == torch.int8 and sc.shape == q.shape[:-1] and int(q.abs().max()) <= 127
+  w = eng.model.store.full_master(eng.model.store.params[name]).float()
+  assert torch.allclose(w, q.float() * sc[..., None], atol=1e-6)
+  assert 0 < (after - before).abs().max() < 0.1 * before.abs().max()
