@@ -53,6 +53,21 @@ def grpo_weights(token_losses, old_token_losses, advantages, mask, clip: float =
   return surrogate, A * ratio * active * mask
 
 
+def gspo_weights(token_losses, old_token_losses, advantages, mask, clip: float = 0.2):
+  """GSPO-token (`loss_algo: gspo-token`, src/maxtext/configs/post_train/rl.yml:52): the importance ratio is one number per
+  sequence, s_i = exp(mean_t(log pi - log pi_old)), used (and clipped) for all of its tokens; the gradient still flows
+  through each token's own probability, d s_it / d log pi_t = s_i. Returns (surrogate loss, per-token weights)."""
+  n = mask.sum(1).clamp_min(1)
+  s = torch.exp(((old_token_losses - token_losses) * mask).sum(1) / n)[:, None]          # [N, 1]
+  A = advantages[:, None]
+  unclipped = s * A
+  clipped = s.clamp(1 - clip, 1 + clip) * A
+  per_tok = torch.minimum(unclipped, clipped).expand_as(mask)
+  surrogate = -(per_tok * mask).sum() / mask.sum().clamp_min(1)
+  active = (unclipped <= clipped).float()
+  return surrogate, (A * s * active).expand_as(mask) * mask
+
+
 def distillation_loss(student_logits, teacher_logits, targets, mask, alpha: float = 0.5, temperature: float = 1.0):
   """alpha * CE(targets) + (1 - alpha) * T^2 * KL(teacher_T || student_T), mean over masked tokens
   (src/maxtext/trainers/post_train/distillation/distillation_utils.py)."""

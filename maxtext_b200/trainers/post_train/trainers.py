@@ -75,8 +75,11 @@ class DPOTrainer:
 class GRPOTrainer:
   """Sample `group_size` completions per prompt with the decode engine, score them, take one clipped policy step."""
 
-  def __init__(self, engine: TrainEngine, reward_fn, group_size: int = 4, clip: float = 0.2, max_new_tokens: int = 8):
+  def __init__(self, engine: TrainEngine, reward_fn, group_size: int = 4, clip: float = 0.2, max_new_tokens: int = 8,
+               loss_algo: str = "grpo"):
     self.eng, self.reward_fn, self.G, self.clip, self.max_new = engine, reward_fn, group_size, clip, max_new_tokens
+    assert loss_algo in ("grpo", "gspo-token"), loss_algo
+    self.loss_algo = loss_algo
     icfg = engine.config.replace(decode_sampling_strategy="weighted")
     self.sampler = MaxEngine(icfg, device=engine.device, model=engine.model)
 
@@ -101,7 +104,8 @@ class GRPOTrainer:
     batch, total = make_lm_batch([p + c for p, c in zip(ps, cs)], S)
     mask = O.sft_mask(torch.tensor([len(p) for p in ps]), total, S)
     old = self.eng.token_losses(batch).cpu()
-    surrogate, w = O.grpo_weights(old, old, adv, mask, self.clip)       # on-policy: ratio = 1 at the first step
+    weights_fn = O.gspo_weights if self.loss_algo == "gspo-token" else O.grpo_weights
+    surrogate, w = weights_fn(old, old, adv, mask, self.clip)           # on-policy: ratio = 1 at the first step
     batch["loss_weights"], batch["loss_normalizer"] = w, float(mask.sum().clamp_min(1))
     m = self.eng.train_step(batch)
     m["rl/mean_reward"], m["rl/surrogate"] = rewards.mean(), surrogate

@@ -76,3 +76,25 @@ def test_distillation_step_pulls_student_towards_teacher():
   batch = {"inputs": torch.randint(0, 256, (2, 32)).int(), "targets": torch.randint(0, 256, (2, 32)).int()}
   losses = [float(T.distill_step(student, teacher, batch)["learning/loss"]) for _ in range(6)]
   assert losses[-1] < losses[0]
+
+
+def test_gspo_token_weights_equal_autograd_and_trainer_runs():
+  torch.manual_seed(2)
+  N, S = 4, 6
+  old = torch.randn(N, S)
+  new = (old + 0.3 * torch.randn(N, S)).requires_grad_(True)
+  adv = O.grpo_advantages(torch.tensor([1.0, 0.0, 3.0, 2.0]), 2)
+  mask = torch.ones(N, S)
+  mask[1, 4:] = 0
+  # GSPO-token: s_it = sg[s_i] * pi_t / sg[pi_t], with s_i the length-normalised sequence ratio
+  logr = (old - new) * mask
+  s_i = torch.exp(logr.sum(1) / mask.sum(1))[:, None]
+  s_it = s_i.detach() * torch.exp((old - new) - (old - new).detach())
+  sur = -(torch.minimum(s_it * adv[:, None], s_it.clamp(0.8, 1.2) * adv[:, None]) * mask).sum() / mask.sum()
+  sur.backward()
+  val, w = O.gspo_weights(new.detach(), old, adv, mask, 0.2)
+  assert torch.allclose(new.grad * mask.sum(), w, atol=1e-5) and abs(float(val) - float(sur)) < 1e-6
+  cfg = tiny_config("llama3-8b", ["learning_rate=5e-3", "vocab_size=32", "max_prefill_predict_length=8"])
+  tr = T.GRPOTrainer(make_engine(cfg), lambda p, c: float(c[0] % 2 == 0), group_size=2, max_new_tokens=3, loss_algo="gspo-token")
+  m = tr.step([[1, 2, 3]])
+  assert torch.isfinite(torch.as_tensor(m["learning/loss"]))
