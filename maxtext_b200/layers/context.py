@@ -67,9 +67,21 @@ class LayerCtx:
   metrics: dict = field(default_factory=dict)
   cache: object = None               # inference KV cache for the current layer
   tokens: torch.Tensor | None = None
+  dropout_seed: int | None = None    # training with dropout_rate > 0: base of the per-site mask seeds of this micro-batch
   sp: bool = False                   # residual stream split along the sequence over the tensor ranks (parallel.sequence_parallel)
   bidir: torch.Tensor | None = None  # [B, 1, S, S] extra allowed (query, key) pairs: tokens of one image see each other
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
+
+  def dropout(self, t: torch.Tensor, site: int) -> torch.Tensor:
+    """Inverted dropout whose mask depends only on (seed of the micro-batch, layer, block, site): the recompute pass of a
+    rematerialised layer draws the same mask as the first pass, and tensor-parallel ranks (same seed) agree on it."""
+    rate = float(getattr(self.config, "dropout_rate", 0.0) or 0.0)
+    if self.dropout_seed is None or rate <= 0.0 or self.mode != "train":
+      return t
+    g = torch.Generator(device=t.device)
+    g.manual_seed((self.dropout_seed * 1000003 + self.layer_index * 1009 + (hash(self.name_prefix) % 97) * 31 + site) % (2 ** 62))
+    keep = (torch.rand(t.shape, generator=g, device=t.device) >= rate).to(t.dtype)
+    return t * keep / (1.0 - rate)
 
   def wants(self, name: str) -> bool:
     """True in the first forward of a rematerialised layer when the policy keeps `name`."""

@@ -107,11 +107,11 @@ class DecoderBlock:
     a = self.attn(self.n1(x) if self.n1 is not None else x, ctx)
     if self.n1b is not None:
       a = self.n1b(a)
-    x = x + a
+    x = x + ctx.dropout(a, 0)                 # src/maxtext/models/llama2.py: dropout on each residual branch
     m = self.mlp(self.n2(x) if self.n2 is not None else x, ctx)
     if self.n2b is not None:
       m = self.n2b(m)
-    return x + m
+    return x + ctx.dropout(m, 1)
 
 
 class DecoderLayer:

@@ -136,6 +136,10 @@ class TrainEngine:
 
     n_units = len(self._units)
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    if float(c.dropout_rate) > 0 and bool(c.enable_dropout) and compute_grads:
+      # one seed per micro-batch and data shard; tensor ranks of a shard share it (they hold the same activations)
+      shard = self.mesh.axis_index(("data", "fsdp", "fsdp_transpose", "expert", "context", "context_usp_ulysses")) if self.mesh is not None else 0
+      ctx.dropout_seed = (int(c.init_weights_seed) * 7919 + self.step_count * 613 + acc["micro"]) * 4099 + shard
     if c.use_qk_clip:
       self._max_logits = getattr(self, "_max_logits", None) or {}
       ctx.max_logits = self._max_logits

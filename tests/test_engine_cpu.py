@@ -229,3 +229,38 @@ def test_deepseek_routed_bias_moves_against_load():
   want = torch.sign(counts.sum() / counts.numel() - counts) * 0.01
   assert torch.allclose(after - before, want, atol=1e-7)
   assert (after - before).abs().max() > 0
+
+
+def test_dropout_is_replayed_by_recompute_and_off_in_eval():
+  """dropout_rate > 0: masks are a function of (step, micro-batch, layer, site), so the recompute pass of a rematerialised
+  layer sees the mask of the first pass (otherwise the analytic gradient would not match finite differences)."""
+  torch.manual_seed(0)
+  cfg = tiny_config("llama3-8b", ["dropout_rate=0.2", "enable_dropout=true", "gradient_clipping_threshold=0", "remat_policy=full"])
+  eng = make_engine(cfg)
+  batch = batch_of(cfg)
+  store = eng.store
+  eng.fwd_bwd(batch)
+  store.finish_resident_grads()
+  acc, eng._accum = eng._accum, None
+  g = store.grad_shard.clone() / float(acc["weights"])
+  train_loss = float(acc["loss_sum"] / acc["weights"])
+  v = torch.randn_like(g)
+  v = v / v.norm()
+  w0, eps = store.master.clone(), 2e-2
+
+  def loss_at(w):
+    store.master.copy_(w)
+    store.sync_compute_from_master()
+    a = eng.fwd_bwd(batch)                    # same step count and micro-batch index: same masks
+    eng._accum = None
+    return float(a["loss_sum"] / a["weights"])
+  fd = (loss_at(w0 + eps * v) - loss_at(w0 - eps * v)) / (2 * eps)
+  an = float((g * v).sum())
+  assert abs(fd - an) <= 0.05 * max(abs(fd), abs(an)) + 2e-4, (fd, an)
+  store.master.copy_(w0)
+  store.sync_compute_from_master()
+  ev = eng.eval_step(batch)
+  eval_loss = float(ev["evaluation/total_loss"] / ev["evaluation/total_weights"])
+  assert abs(eval_loss - train_loss) > 1e-4          # evaluation runs without dropout
+  losses = [float(eng.train_step(batch)["learning/loss"]) for _ in range(5)]
+  assert losses[-1] < losses[0]
