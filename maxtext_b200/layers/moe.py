@@ -9,6 +9,8 @@ a variable-size all-to-all whose split sizes come from an exchanged count matrix
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.distributed as dist
 
@@ -140,6 +142,19 @@ class RoutedMoE:
       if c.norm_topk_prob:
         wts = wts / wts.sum(-1, keepdim=True)
       probs = torch.softmax(logits.float(), -1)
+    if bool(getattr(c, "use_random_routing", False)) and not self.deepseek:
+      # debugging aid (src/maxtext/layers/moe.py `random_routing`): uniformly random experts, weights from their logits
+      idx = torch.rand(logits.shape, device=logits.device).topk(self.k, dim=-1).indices
+      vals = logits.gather(-1, idx)
+      wts = vals.float() if self.style == "llama4" else torch.softmax(vals.float(), -1)
+    cf = float(getattr(c, "capacity_factor", -1.0) or -1.0)
+    if cf > 0:
+      # token dropping (moe.py `generate_masks`): per sequence, assignments are counted per expert in (token, choice)
+      # order and those beyond the expert's capacity get weight zero
+      cap = int(max(math.ceil(S * self.k / self.E) * cf, cf))
+      onehot_k = torch.nn.functional.one_hot(idx.view(B, S * self.k), self.E)                  # [B, S*k, E]
+      rank_in_expert = (onehot_k.cumsum(1) * onehot_k).sum(-1)                                # 1-based arrival order
+      wts = wts * (rank_in_expert <= cap).view(B * S, self.k).to(wts.dtype)
     aux = None
     if c.load_balance_loss_weight > 0:
       onehot = torch.zeros(B * S, self.E, dtype=torch.float32, device=x2.device).scatter_add_(

@@ -178,3 +178,34 @@ def test_muon_newton_schulz_and_training():
   b = batch_of(eng.config)
   losses = [float(eng.train_step(b)["learning/loss"]) for _ in range(5)]
   assert losses[-1] < losses[0], losses
+
+
+def test_moe_capacity_factor_drops_overflow_and_random_routing_runs():
+  import torch
+  from helpers import tiny_config, make_engine, batch_of
+  from maxtext_b200.models.transformer import Transformer
+  base = ["num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=64", "weight_init=normal"]
+  full = Transformer(tiny_config("mixtral-8x7b", base), None, "cpu")
+  tight = Transformer(tiny_config("mixtral-8x7b", base + ["capacity_factor=0.5"]), None, "cpu")
+  loose = Transformer(tiny_config("mixtral-8x7b", base + ["capacity_factor=8.0"]), None, "cpu")
+  for m_ in (full, tight, loose):
+    m_.store.initialize(seed=0)
+  toks = torch.randint(0, 256, (2, 32))
+  a, b, c = full.forward(toks), tight.forward(toks), loose.forward(toks)
+  assert torch.allclose(a, c, atol=1e-6)                        # capacity above the load: nothing dropped
+  assert (a - b).abs().max() > 1e-4                            # half the fair share: some assignments dropped
+  # the mask itself: capacity = ceil(S k / E) * cf per sequence, arrival order over (token, choice)
+  moe = tight.layers[0].blocks[0].mlp
+  x2 = torch.randn(2 * 32, 64)
+  wts, idx, _ = moe.route(x2, 2, 32)
+  cap = int(max(-(-32 * 2 // 4) * 0.5, 0.5))
+  for row in range(2):
+    cnt = {}
+    for t in range(32):
+      for j in range(2):
+        e = int(idx[row * 32 + t, j])
+        cnt[e] = cnt.get(e, 0) + 1
+        assert (float(wts[row * 32 + t, j]) == 0.0) == (cnt[e] > cap)
+  eng = make_engine(tiny_config("mixtral-8x7b", base + ["use_random_routing=true", "capacity_factor=1.0"]))
+  bt = batch_of(eng.config)
+  assert torch.isfinite(torch.as_tensor(float(eng.train_step(bt)["learning/loss"])))
