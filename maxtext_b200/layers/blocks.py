@@ -268,6 +268,9 @@ class Norm:
   def __call__(self, x):
     if self.kind == "layernorm":
       return ref.layernorm(x, self.scale.leaf(), self.bias.leaf(), self.eps)
+    if self.scale is None:
+      xf = x.float()
+      return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
     return F.rmsnorm(x, self.scale, self.eps, self.offset)
 
 
@@ -325,8 +328,9 @@ class Attention:
       self.qn = Norm(ab, "query_norm", self.hq * self.dh, c.normalization_layer_epsilon, axes=("norm",))
       self.kn = Norm(ab, "key_norm", self.hkv * self.dh, c.normalization_layer_epsilon, axes=("norm",))
     elif qk_norm:
-      self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
-      self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, axes=("norm",))
+      ws = bool(getattr(c, "qk_norm_with_scale", True))         # false: plain RMS normalisation without a learned scale
+      self.qn = Norm(ab, "query_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, with_scale=ws, axes=("norm",))
+      self.kn = Norm(ab, "key_norm", self.dh, c.normalization_layer_epsilon, qk_norm_offset, with_scale=ws, axes=("norm",))
     if tp > 1 and not self.global_qk_norm:
       for n_ in (self.qn, self.kn):
         if n_ is not None and n_.scale is not None:

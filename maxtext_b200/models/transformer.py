@@ -306,6 +306,12 @@ class Transformer:
       x = merge_mm_embeddings(x, mm[0], mm[1])
     if self.family.scale_embedding:
       x = (x.float() * math.sqrt(c.emb_dim)).to(x.dtype)
+    if bool(getattr(c, "use_untrainable_positional_embedding", False)):
+      # fixed sinusoids [sin | cos] with geometric wavelengths up to 10 000 (src/maxtext/layers/embeddings.py:1055-1120)
+      half = c.emb_dim // 2
+      inv = torch.exp(torch.arange(half, device=x.device, dtype=torch.float32) * -(math.log(10000.0) / max(half - 1, 1)))
+      ang = positions.float()[..., None] * inv
+      x = x + torch.cat([torch.sin(ang), torch.cos(ang)], dim=-1).to(x.dtype)
     if self.pos_embedding is not None:
       x = x + self.pos_embedding.leaf()[positions.long()].to(x.dtype)
     return x

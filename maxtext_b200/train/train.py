@@ -115,7 +115,10 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
       prof.maybe_start(step)
       t0 = time.perf_counter()
       with recorder.span("DATA_LOADING", step):
-        batch = next(data_iterator)
+        if int(getattr(c, "reuse_example_batch", 0) or 0) > 0 and step > start_step:
+          pass                                   # performance testing: the first batch is fed again at every step
+        else:
+          batch = next(data_iterator)
       with recorder.span("STEP", step):
         metrics = stepper.train_step(batch)
         if is_cuda and (c.profile_cleanly or True):

@@ -209,3 +209,28 @@ def test_moe_capacity_factor_drops_overflow_and_random_routing_runs():
   eng = make_engine(tiny_config("mixtral-8x7b", base + ["use_random_routing=true", "capacity_factor=1.0"]))
   bt = batch_of(eng.config)
   assert torch.isfinite(torch.as_tensor(float(eng.train_step(bt)["learning/loss"])))
+
+
+def test_small_config_switches():
+  """use_untrainable_positional_embedding, qk_norm_with_scale=false, reuse_example_batch."""
+  import torch
+  from helpers import tiny_config, make_engine, batch_of, TINY, BASE_YML
+  from maxtext_b200.train import train as T
+  eng = make_engine(tiny_config("llama3-8b", ["use_untrainable_positional_embedding=true"]))
+  ref_ = make_engine(tiny_config("llama3-8b"))
+  toks = torch.randint(0, 256, (1, 8))
+  pos = torch.arange(8)[None]
+  d = eng.model.embed(toks, pos) - ref_.model.embed(toks, pos)
+  half = 32
+  inv = torch.exp(torch.arange(half).float() * -(torch.log(torch.tensor(10000.0)) / (half - 1)))
+  want = torch.cat([torch.sin(pos.float()[..., None] * inv), torch.cos(pos.float()[..., None] * inv)], -1)
+  assert torch.allclose(d, want, atol=1e-5)
+  q = make_engine(tiny_config("qwen3-8b", ["qk_norm_with_scale=false"]))
+  assert not any("query_norm" in n or "key_norm" in n for n in q.store.params)
+  b = batch_of(q.config)
+  ls = [float(q.train_step(b)["learning/loss"]) for _ in range(4)]
+  assert ls[-1] < ls[0]
+  args = [a for a in TINY if not a.startswith("steps")] + ["model_name=llama3-8b", "steps=4", "reuse_example_batch=1"]
+  _, hist = T.main(["train", BASE_YML] + args)
+  losses = [h["learning/loss"] for h in hist]
+  assert all(b_ < a_ for a_, b_ in zip(losses, losses[1:])), losses        # the same batch every step: monotone at this size
