@@ -40,7 +40,13 @@ def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -
     out.append(t)
     if t == getattr(tok, "eos_id", -1) or not bool(state.active[0]):
       break
+    stops = [x for x in (getattr(config, "stop_strings", None) or []) if x]
+    if stops and any(x in tok.decode(out) for x in stops):
+      break                                                   # `stop_strings`: generation ends once one of them appears
   text = tok.decode(out)
+  for x in (getattr(config, "stop_strings", None) or []):
+    if x and x in text:
+      text = text[: text.index(x)]
   if config.autoregressive_decode_assert:
     assert text.startswith(config.autoregressive_decode_assert), f"generated {text!r}, expected prefix {config.autoregressive_decode_assert!r}"
   return text

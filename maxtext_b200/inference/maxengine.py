@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import os
+
 import torch
 
 from ..models.transformer import Transformer
@@ -63,7 +65,36 @@ class MaxEngine:
       ckpt.load_params_only(path, _EngineView(self), self.model.mesh)
     else:
       self.model.store.initialize(seed=self.config.init_weights_seed if seed is None else seed)
+    c = self.config
+    if bool(getattr(c, "checkpoint_is_quantized", False)) and path and os.path.isfile(os.path.join(path, "quantized_params.safetensors")):
+      self.load_quantized_params(os.path.join(path, "quantized_params.safetensors"))
+    elif str(getattr(c, "quantization", "") or "") in ("int8", "int4") and str(getattr(c, "save_quantized_params_path", "") or ""):
+      # serving flow of the reference (maxengine.py:576-620): quantise the loaded weights once and write them out
+      self.save_quantized_params(c.save_quantized_params_path, 8 if c.quantization == "int8" else 4)
     return self.model.store
+
+  def save_quantized_params(self, directory: str, bits: int = 8) -> str:
+    from safetensors.torch import save_file
+    packed = self.quantize_params(bits)
+    flat = {}
+    for n, (q, sc) in packed.items():
+      flat[n + "/q"], flat[n + "/scale"] = q.contiguous(), sc.contiguous()
+    os.makedirs(directory, exist_ok=True)
+    out = os.path.join(directory, "quantized_params.safetensors")
+    save_file(flat, out)
+    return out
+
+  @torch.no_grad()
+  def load_quantized_params(self, file: str):
+    """`checkpoint_is_quantized`: matrices come from (int values, per-channel scales); the rest keeps its loaded value."""
+    from safetensors.torch import load_file
+    flat = load_file(file)
+    store = self.model.store
+    for name, p in store.params.items():
+      if name + "/q" in flat:
+        w = flat[name + "/q"].float() * flat[name + "/scale"].float()[..., None]
+        store.load_full(name, p.pdef.local_slice(w))
+    store.sync_compute_from_master()
 
   # ------------------------------------------------------------------ state
   @torch.no_grad()

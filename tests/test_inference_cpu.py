@@ -171,3 +171,29 @@ def test_decode_multi_and_quantize_params():
   w = eng.model.store.full_master(eng.model.store.params[name]).float()
   assert torch.allclose(w, q.float() * sc[..., None], atol=1e-6)
   assert 0 < (after - before).abs().max() < 0.1 * before.abs().max()
+
+
+def test_quantized_params_file_round_trip_and_stop_strings(tmp_path):
+  from helpers import tiny_config
+  from maxtext_b200.inference.decode import decode
+  from maxtext_b200.inference.maxengine import MaxEngine
+  base = ["max_prefill_predict_length=16", "max_target_length=32", "tokenizer_type=byte", "vocab_size=260"]
+  eng = MaxEngine(tiny_config("llama3-8b", base))
+  eng.load_params()
+  f = eng.save_quantized_params(str(tmp_path / "q"), 8)
+  ids = torch.randint(1, 250, (1, 10))
+  want = eng.model.forward(ids)                           # the engine now holds the de-quantised weights
+  other = MaxEngine(tiny_config("llama3-8b", base + ["init_weights_seed=7"]))
+  other.load_params()
+  for n in ("token_embedder/embedding", "decoder/decoder_norm/scale", "decoder/logits_dense/kernel"):
+    other.model.store.load_full(n, eng.model.store.full_master(eng.model.store.params[n]))
+  for n, p in eng.model.store.params.items():
+    if "norm" in n:
+      other.model.store.load_full(n, eng.model.store.full_master(p))
+  other.load_quantized_params(f)
+  assert (other.model.forward(ids) - want).abs().max() < 1e-5
+  text = decode(tiny_config("llama3-8b", base), "hello", engine=eng)
+  if len(text) > 3:
+    stop = text[2:4]
+    cut = decode(tiny_config("llama3-8b", base + [f"stop_strings=[{stop!r}]"]), "hello", engine=eng)
+    assert stop not in cut and text.startswith(cut)
