@@ -59,7 +59,8 @@ class FileDataIterator:
     self.files = _expand(pats)
     if not self.files:
       raise FileNotFoundError(f"dataset_type={c.dataset_type}: no files match {pats!r}")
-    self.column = (c.train_data_columns if split == "train" else c.eval_data_columns)[0]
+    self.columns = list(c.train_data_columns if split == "train" else c.eval_data_columns)
+    self.column = self.columns[0]
     self.tok = build_tokenizer(c)
     self.rank, self.world = data_rank, data_world
     gb = int(c.global_batch_size_to_load if split == "train" else c.global_batch_size_to_load_eval)
@@ -84,6 +85,14 @@ class FileDataIterator:
                 arr = np.asarray(ex["__tokens__"]).reshape(-1)
                 for s in range(0, len(arr) - 1, self.S + 1):
                   yield arr[s:s + self.S + 1].astype(np.int32)
+              elif bool(getattr(c, "use_sft", False)) and len(self.columns) >= 2 and self.columns[1] in ex:
+                # supervised fine-tuning (`use_sft`, src/maxtext/input_pipeline/input_pipeline_utils.py): prompt + completion in
+                # one sequence; with sft_train_on_completion_only the prompt tokens carry no loss
+                pr = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[0]]), add_bos=bool(c.add_bos), add_eos=False)]
+                co = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[1]]), add_bos=False, add_eos=bool(c.add_eos))]
+                if bool(getattr(c, "sft_train_on_completion_only", False)):
+                  pr = [-(t + 1) for t in pr]
+                yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
               else:
                 text = ex[self.column]
                 ids = self.tok.encode(text, add_bos=bool(c.add_bos), add_eos=bool(c.add_eos)) if c.tokenize_train_data else list(text)

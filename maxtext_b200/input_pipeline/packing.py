@@ -60,5 +60,10 @@ def shift_for_lm(row: dict, seq_len_plus_1: bool = True) -> dict:
   masked (segmentation 0) where it crosses into another segment or padding."""
   t, s, p = row["tokens"], row["segmentation"], row["position"]
   tgt_seg = np.where(s[1:] == s[:-1], s[1:], 0)
+  if (t < 0).any():
+    # supervised fine-tuning on completions only: prompt tokens travel through packing as -(id + 1) and are never targets
+    prompt = t < 0
+    t = np.where(prompt, -t - 1, t).astype(np.int32)
+    tgt_seg = np.where(prompt[1:], 0, tgt_seg)
   return {"inputs": t[:-1], "targets": t[1:], "inputs_segmentation": s[:-1], "targets_segmentation": tgt_seg.astype(np.int32),
           "inputs_position": p[:-1], "targets_position": p[:-1]}

@@ -87,3 +87,25 @@ def test_rampup_trains_end_to_end():
   _, hist = train_lib.train_loop(cfg)
   toks = [int(h["learning/total_weights"]) for h in hist]
   assert toks[0] == 2 * cfg.max_target_length and toks[-1] == 4 * cfg.max_target_length
+
+
+def test_use_sft_masks_prompt_tokens_through_packing(tmp_path):
+  """`use_sft` with prompt / completion columns: one packed row holds several examples, and only completion tokens (and
+  the end-of-sequence token) are targets when sft_train_on_completion_only is set."""
+  import json
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  p = tmp_path / "sft.jsonl"
+  recs = [{"prompt": "abcd", "completion": "XY"}, {"prompt": "ef", "completion": "ZZZ"}, {"prompt": "ghi", "completion": "W"}] * 4
+  p.write_text("\n".join(json.dumps(r) for r in recs))
+  base = ["dataset_type=hf", f"hf_train_files={p}", "train_data_columns=['prompt','completion']", "tokenizer_type=byte", "vocab_size=260",
+          "use_sft=true", "packing=true", "max_target_length=32", "per_device_batch_size=1", "add_bos=false", "add_eos=false"]
+  b = next(create_data_iterator(tiny_config("llama3-8b", base + ["sft_train_on_completion_only=true"])))
+  inp, tgt, tseg = b["inputs"][0].tolist(), b["targets"][0].tolist(), b["targets_segmentation"][0].tolist()
+  text = bytes(t for t in inp if 0 < t < 256).decode()
+  assert text.startswith("abcdXYefZZZghiW"[: len(text)]) or "abcdX" in text
+  trained = bytes(t for t, s in zip(tgt, tseg) if s != 0 and 0 < t < 256).decode()
+  assert set(trained) <= set("XYZW") and "Y" in trained and not set(trained) & set("abcdefghi")
+  b2 = next(create_data_iterator(tiny_config("llama3-8b", base + ["sft_train_on_completion_only=false"])))
+  trained2 = bytes(t for t, s in zip(b2["targets"][0].tolist(), b2["targets_segmentation"][0].tolist()) if s != 0 and 0 < t < 256).decode()
+  assert set(trained2) & set("abcdefghi")
