@@ -62,7 +62,7 @@ class FileDataIterator:
     self.columns = list(c.train_data_columns if split == "train" else c.eval_data_columns)
     self.column = self.columns[0]
     self.tok = build_tokenizer(c)
-    self.rank, self.world = data_rank, data_world
+    self.rank, self.world, self.split = data_rank, data_world, split
     gb = int(c.global_batch_size_to_load if split == "train" else c.global_batch_size_to_load_eval)
     assert gb % data_world == 0
     self.batch = gb // data_world
@@ -71,13 +71,41 @@ class FileDataIterator:
     self.pack = bool(c.packing)
     self._rows = self._row_stream()
 
+  def _examples(self):
+    """The epoch's examples in training order. With `enable_data_shuffling` the file order is permuted per epoch and the
+    examples are permuted inside consecutive windows of 4096, both as pure functions of (data_shuffle_seed, epoch, window),
+    so every rank derives the same order and a resumed run continues in it."""
+    c = self.c
+    shuffle = self.split == "train" and bool(getattr(c, "enable_data_shuffling", False))
+    files = list(self.files)
+    if not shuffle:
+      for f in files:
+        yield from _read_examples(f, self.column)
+      return
+    seed = int(getattr(c, "data_shuffle_seed", 0) or 0)
+    rng = np.random.default_rng([seed, self.epoch])
+    files = [files[j] for j in rng.permutation(len(files))]
+    window, w_id = [], 0
+
+    def flush():
+      order = np.random.default_rng([seed, self.epoch, w_id + 1]).permutation(len(window))
+      return [window[j] for j in order]
+    for f in files:
+      for ex in _read_examples(f, self.column):
+        window.append(ex)
+        if len(window) == 4096:
+          yield from flush()
+          window, w_id = [], w_id + 1
+    if window:
+      yield from flush()
+
   def _token_stream(self):
     """All ranks walk the same example sequence; rank r keeps examples with index % world == r."""
     c = self.c
     while c.num_epoch <= 0 or self.epoch < max(1, int(c.num_epoch)):
       i = 0
-      for f in self.files:
-        for ex in _read_examples(f, self.column):
+      for _once in (0,):
+        for ex in self._examples():
           if i >= self.index:
             self.index = i + 1
             if i % self.world == self.rank:

@@ -9,7 +9,7 @@ BASE_YML = os.path.join(ROOT, "maxtext_b200", "configs", "base.yml")
 TINY = ["override_model_config=true", "base_emb_dim=64", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=16",
         "base_mlp_dim=128", "base_num_decoder_layers=2", "vocab_size=256", "max_target_length=32", "per_device_batch_size=2",
         "dataset_type=synthetic", "dtype=float32", "hardware=cpu", "enable_checkpointing=false", "log_config=false", "steps=3",
-        "learning_rate=1e-3", "warmup_steps_fraction=0.0"]
+        "learning_rate=1e-3", "warmup_steps_fraction=0.0", "enable_data_shuffling=false"]
 
 FAMILIES = {
     "llama3-8b": [],

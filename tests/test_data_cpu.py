@@ -109,3 +109,34 @@ def test_use_sft_masks_prompt_tokens_through_packing(tmp_path):
   b2 = next(create_data_iterator(tiny_config("llama3-8b", base + ["sft_train_on_completion_only=false"])))
   trained2 = bytes(t for t, s in zip(b2["targets"][0].tolist(), b2["targets_segmentation"][0].tolist()) if s != 0 and 0 < t < 256).decode()
   assert set(trained2) & set("abcdefghi")
+
+
+def test_data_shuffling_is_deterministic_resumable_and_complete(tmp_path):
+  import json
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  p = tmp_path / "d.jsonl"
+  p.write_text("\n".join(json.dumps({"text": f"doc {i:03d}"}) for i in range(40)))
+  base = ["dataset_type=hf", f"hf_train_files={p}", "tokenizer_type=byte", "vocab_size=260", "packing=false", "max_target_length=16",
+          "per_device_batch_size=4", "enable_data_shuffling=true", "num_epoch=1"]
+
+  def docs(it, n):
+    out = []
+    for _ in range(n):
+      b = next(it)
+      out += [bytes(t for t in row if 0 < t < 256).decode()[:7] for row in b["inputs"].tolist()]
+    return out
+  a = docs(create_data_iterator(tiny_config("llama3-8b", base)), 10)
+  assert sorted(a) == [f"doc {i:03d}" for i in range(40)] and a != sorted(a)             # a permutation, not the file order
+  assert a == docs(create_data_iterator(tiny_config("llama3-8b", base)), 10)              # same seed, same order
+  assert a != docs(create_data_iterator(tiny_config("llama3-8b", base + ["data_shuffle_seed=5"])), 10)
+  it = create_data_iterator(tiny_config("llama3-8b", base))
+  first = docs(it, 3)
+  st = it.state()
+  it2 = create_data_iterator(tiny_config("llama3-8b", base))
+  it2.load_state(st)
+  assert first + docs(it2, 7) == a                                                         # resume continues the shuffled order
+  # two data shards see disjoint halves of the same order
+  r0 = docs(create_data_iterator(tiny_config("llama3-8b", base + ["per_device_batch_size=2"], num_devices=2), 0, 2), 10)
+  r1 = docs(create_data_iterator(tiny_config("llama3-8b", base + ["per_device_batch_size=2"], num_devices=2), 1, 2), 10)
+  assert sorted(r0 + r1) == sorted(a) and not set(r0) & set(r1)
