@@ -72,25 +72,52 @@ __device__ __forceinline__ float rs_block_sum(float v, float* sh) {
 }
 
 // dst[i] (+)= scale * sum_r peer[r][offset + i];  partials[block] = sum of squares of what was written this call.
+// A thread keeps RS_UNROLL independent 16-byte loads in flight per peer: with one load per thread the kernel is bound by the
+// NVLink round trip (measured 183 GB/s at two ranks), not by the links. Ranks are added in rank order for every element, so the
+// result does not depend on the unrolling.
+constexpr int RS_UNROLL = 8;
+
+__device__ __forceinline__ void rs_finish(float4& s, float scale, int accumulate, float4* dst, long i, float& acc) {
+  s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+  if (accumulate) {
+    const float4 o = dst[i];
+    s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+  }
+  dst[i] = s;
+  acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+}
+
 __global__ void __launch_bounds__(RS_THREADS)
 rs_sumsq_kernel(const float* const* __restrict__ peer, long offset, long n, float* __restrict__ dst, int accumulate, float scale,
                 int world, float* __restrict__ partials) {
   __shared__ float sh[32];
   float acc = 0.f;
   const long n4 = n / 4;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+  const long stride = (long)gridDim.x * blockDim.x;
+  float4* dst4 = reinterpret_cast<float4*>(dst);
+  long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  for (; i + (RS_UNROLL - 1) * stride < n4; i += RS_UNROLL * stride) {
+    float4 s[RS_UNROLL];
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4* src = reinterpret_cast<const float4*>(peer[r] + offset);
+      float4 v[RS_UNROLL];
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < RS_UNROLL; ++u) { s[u].x += v[u].x; s[u].y += v[u].y; s[u].z += v[u].z; s[u].w += v[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) rs_finish(s[u], scale, accumulate, dst4, i + u * stride, acc);
+  }
+  for (; i < n4; i += stride) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
       const float4 v = reinterpret_cast<const float4*>(peer[r] + offset)[i];
       s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
     }
-    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
-    if (accumulate) {
-      const float4 o = reinterpret_cast<const float4*>(dst)[i];
-      s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
-    }
-    reinterpret_cast<float4*>(dst)[i] = s;
-    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    rs_finish(s, scale, accumulate, dst4, i, acc);
   }
   const float t = rs_block_sum(acc, sh);
   if (threadIdx.x == 0 && partials) partials[blockIdx.x] = t;
@@ -98,27 +125,36 @@ rs_sumsq_kernel(const float* const* __restrict__ peer, long offset, long n, floa
 
 // The same reduce-scatter with the sum done inside the NVSwitch: `mc` is the multicast address of the symmetric gradient
 // buffer, and one multimem.ld_reduce returns the element-wise sum of every rank's copy, so each element costs this SM one
-// load instead of `world` loads (and the reduction traffic never enters the GPU).
+// load instead of `world` loads (and the reduction traffic never enters the GPU). RS_UNROLL of them are in flight per thread.
+__device__ __forceinline__ float4 mc_ld_reduce(const float* p) {
+  float4 s;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w)
+               : "l"(p)
+               : "memory");
+  return s;
+}
+
 __global__ void __launch_bounds__(RS_THREADS)
 rs_sumsq_mc_kernel(const float* __restrict__ mc, long offset, long n, float* __restrict__ dst, int accumulate, float scale,
                    float* __restrict__ partials) {
   __shared__ float sh[32];
   float acc = 0.f;
   const long n4 = n / 4;
+  const long stride = (long)gridDim.x * blockDim.x;
   const float* base = mc + offset;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
-    float4 s;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(s.x), "=f"(s.y), "=f"(s.z), "=f"(s.w)
-                 : "l"(base + 4 * i)
-                 : "memory");
-    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
-    if (accumulate) {
-      const float4 o = reinterpret_cast<const float4*>(dst)[i];
-      s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
-    }
-    reinterpret_cast<float4*>(dst)[i] = s;
-    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  float4* dst4 = reinterpret_cast<float4*>(dst);
+  long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  for (; i + (RS_UNROLL - 1) * stride < n4; i += RS_UNROLL * stride) {
+    float4 s[RS_UNROLL];
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) s[u] = mc_ld_reduce(base + 4 * (i + u * stride));
+#pragma unroll
+    for (int u = 0; u < RS_UNROLL; ++u) rs_finish(s[u], scale, accumulate, dst4, i + u * stride, acc);
+  }
+  for (; i < n4; i += stride) {
+    float4 s = mc_ld_reduce(base + 4 * i);
+    rs_finish(s, scale, accumulate, dst4, i, acc);
   }
   const float t = rs_block_sum(acc, sh);
   if (threadIdx.x == 0 && partials) partials[blockIdx.x] = t;
