@@ -106,6 +106,12 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
   if c.enable_diloco:
     from ..trainers.diloco import DiLoCoTrainer
     stepper = DiLoCoTrainer(engine, c, mesh)
+  if bool(getattr(c, "use_dpo", False)):
+    # preference optimisation through the same loop: batches of prompt / chosen / rejected, frozen copy of the start weights
+    from ..trainers.post_train.trainers import DPODataIterator, DPOStepper
+    stepper = DPOStepper(engine)
+    if not (isinstance(data_iterator, DPODataIterator)):
+      data_iterator = DPODataIterator(c, *data_shard(mesh))
   clean = False     # a failed attempt must not try a collective save on its way out
   try:
     for step in range(start_step, int(c.steps)):

@@ -71,6 +71,61 @@ class DPOTrainer:
     return m
 
 
+class DPODataIterator:
+  """`use_dpo` input (src/maxtext/input_pipeline, dpo_utils.py): JSON-lines records with prompt / chosen / rejected text
+  (columns from `train_data_columns`, default those three names), tokenised and cut to fit, `batch` records at a time,
+  dealt round-robin to the data shards; loops over the files."""
+
+  def __init__(self, config, data_rank: int = 0, data_world: int = 1):
+    import json
+    from ...input_pipeline.file_pipeline import _expand
+    from ...input_pipeline.tokenizer import build_tokenizer
+    c = self.c = config
+    cols = list(c.train_data_columns)
+    self.cols = cols if len(cols) >= 3 else ["prompt", "chosen", "rejected"]
+    tok = build_tokenizer(c)
+    S = int(c.max_target_length)
+    self.records = []
+    for f in _expand(c.hf_train_files or c.grain_train_files or c.dataset_path):
+      with open(f, "r", encoding="utf-8") as fh:
+        for i, line in enumerate(l for l in fh if l.strip()):
+          if i % data_world != data_rank:
+            continue
+          r = json.loads(line)
+          enc = lambda t, bos: [x % c.vocab_size for x in tok.encode(str(t), add_bos=bos and bool(c.add_bos), add_eos=False)]  # noqa: E731
+          p = enc(r[self.cols[0]], True)[: S // 2]
+          self.records.append((p, enc(r[self.cols[1]], False)[: S - len(p)], enc(r[self.cols[2]], False)[: S - len(p)]))
+    if not self.records:
+      raise FileNotFoundError("use_dpo: no prompt / chosen / rejected records found")
+    self.batch = max(1, int(c.global_batch_size_to_load) // data_world)
+    self.pos = 0
+
+  def __iter__(self):
+    return self
+
+  def __next__(self):
+    rows = [self.records[(self.pos + i) % len(self.records)] for i in range(self.batch)]
+    self.pos += self.batch
+    return {"prompts": [r[0] for r in rows], "chosen": [r[1] for r in rows], "rejected": [r[2] for r in rows]}
+
+  def state(self):
+    return {"pos": self.pos}
+
+  def load_state(self, st):
+    self.pos = int(st.get("pos", 0))
+
+
+class DPOStepper:
+  """Adapter that lets the pre-training loop drive `DPOTrainer` (`use_dpo=true`)."""
+
+  def __init__(self, engine: TrainEngine):
+    c = engine.config
+    self.trainer = DPOTrainer(engine, float(getattr(c, "dpo_beta", 0.1)), float(getattr(c, "dpo_label_smoothing", 0.0)))
+
+  def train_step(self, batch: dict) -> dict:
+    return self.trainer.step(batch["prompts"], batch["chosen"], batch["rejected"])
+
+
 # ------------------------------------------------------------------------------------------------ GRPO
 class GRPOTrainer:
   """Sample `group_size` completions per prompt with the decode engine, score them, take one clipped policy step."""

@@ -98,3 +98,18 @@ def test_gspo_token_weights_equal_autograd_and_trainer_runs():
   tr = T.GRPOTrainer(make_engine(cfg), lambda p, c: float(c[0] % 2 == 0), group_size=2, max_new_tokens=3, loss_algo="gspo-token")
   m = tr.step([[1, 2, 3]])
   assert torch.isfinite(torch.as_tensor(m["learning/loss"]))
+
+
+def test_use_dpo_through_the_train_cli(tmp_path):
+  import json
+  from helpers import TINY, BASE_YML
+  from maxtext_b200.train import train as TR
+  p = tmp_path / "pref.jsonl"
+  p.write_text("\n".join(json.dumps({"prompt": f"q{i} ", "chosen": "yes yes", "rejected": "no no no"}) for i in range(8)))
+  args = [a for a in TINY if not a.startswith(("steps", "dataset_type", "learning_rate=", "vocab_size", "per_device_batch_size"))] + [
+      "model_name=llama3-8b", "steps=6", "use_dpo=true", "dataset_type=hf", f"hf_train_files={p}", "tokenizer_type=byte", "vocab_size=260",
+      "per_device_batch_size=4", "learning_rate=5e-3", f"base_output_directory={tmp_path}", "run_name=dpo"]
+  _, hist = TR.main(["train", BASE_YML] + args)
+  acc = [float(h["dpo/reward_accuracy"]) for h in hist]
+  loss = [float(h["dpo/loss"]) for h in hist]
+  assert loss[-1] < loss[0] and acc[-1] >= acc[0] and abs(loss[0] - 0.6931) < 1e-3        # starts at log 2: policy = reference
