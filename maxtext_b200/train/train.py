@@ -175,7 +175,11 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
 
 
 def run_eval(config, engine, mesh) -> float:
-  it = create_data_iterator(config, mesh)
+  from ..input_pipeline import interface
+  has_eval_files = bool(getattr(config, "hf_eval_files", "") or getattr(config, "grain_eval_files", ""))
+  # the held-out split when one is configured (hf_eval_files / grain_eval_files), else fresh batches of the training stream
+  it = interface.create_data_iterator(config, *data_shard(mesh), split="eval") if has_eval_files and config.dataset_type != "synthetic" \
+      else create_data_iterator(config, mesh)
   tot, w = 0.0, 0.0
   n = config.eval_steps if config.eval_steps > 0 else 1
   for _ in range(n):

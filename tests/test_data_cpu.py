@@ -140,3 +140,22 @@ def test_data_shuffling_is_deterministic_resumable_and_complete(tmp_path):
   r0 = docs(create_data_iterator(tiny_config("llama3-8b", base + ["per_device_batch_size=2"], num_devices=2), 0, 2), 10)
   r1 = docs(create_data_iterator(tiny_config("llama3-8b", base + ["per_device_batch_size=2"], num_devices=2), 1, 2), 10)
   assert sorted(r0 + r1) == sorted(a) and not set(r0) & set(r1)
+
+
+def test_eval_uses_the_eval_files(tmp_path):
+  import json
+  from helpers import tiny_config, make_engine
+  from maxtext_b200.train import train as T
+  tr, ev = tmp_path / "train.jsonl", tmp_path / "eval.jsonl"
+  tr.write_text("\n".join(json.dumps({"text": "aaaa bbbb cccc dddd"}) for _ in range(8)))
+  ev.write_text("\n".join(json.dumps({"text": "zzzz yyyy xxxx wwww"}) for _ in range(8)))
+  base = ["dataset_type=hf", f"hf_train_files={tr}", "tokenizer_type=byte", "vocab_size=260", "max_target_length=16", "per_device_batch_size=2",
+          "eval_steps=1", "learning_rate=2e-2", "num_epoch=100"]
+  cfg = tiny_config("llama3-8b", base + [f"hf_eval_files={ev}"])
+  eng = make_engine(cfg)
+  it = T.create_data_iterator(cfg, None)
+  for _ in range(12):
+    eng.train_step(next(it))                                  # memorise the training text
+  held_out = T.run_eval(cfg, eng, None)
+  on_train = T.run_eval(tiny_config("llama3-8b", base), eng, None)
+  assert held_out > on_train + 0.5, (held_out, on_train)
