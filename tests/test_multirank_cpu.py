@@ -292,3 +292,15 @@ def test_combined_layouts_match_single_including_grad_norm(single, moe_single, t
   got = run_ranks(world, base + hot + par, str(tmp_path), layout)
   _close(got["loss"], want["loss"], 2e-5)
   _close(got["grad_norm"], want["grad_norm"], 2e-4)
+
+
+@pytest.mark.parametrize("case", ["lora", "masks"])
+def test_frozen_parameters_under_fsdp_match_single(tmp_path, case):
+  """LoRA and `trainable_parameters_mask` / `adamw_mask` with flat sharded optimizer state: frozen ranges get zero gradient
+  and no decay on every shard, trained ranges are decayed on the shard that owns them."""
+  over = {"lora": ["lora={enable_lora: true, lora_rank: 4, lora_alpha: 8.0}"],
+          "masks": ["trainable_parameters_mask=['.*mlp.*']", "adamw_mask=['.*wo.*']"]}[case] + ["steps=4", "learning_rate=1e-2"]
+  one = run_ranks(1, over + ["per_device_batch_size=4"], str(tmp_path), "one")
+  two = run_ranks(2, over + ["per_device_batch_size=2", "ici_fsdp_parallelism=2"], str(tmp_path), "two")
+  _close(two["loss"], one["loss"], 2e-5)
+  _close(two["grad_norm"], one["grad_norm"], 2e-4)
