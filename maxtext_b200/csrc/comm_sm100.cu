@@ -11,6 +11,7 @@
 //     publishes one flag per segment; the GEMM in gemm_sm100.cu runs the same loop in spare CTAs of its own
 //     launch so that tiles start as soon as their rows have arrived.
 // No kernel here uses bulk-tensor copies from peer memory: remote data is read with ld.global by the copying CTA.
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -125,7 +126,7 @@ rs_sumsq_kernel(const float* const* __restrict__ peer, long offset, long n, floa
 
 // The same reduce-scatter with the sum done inside the NVSwitch: `mc` is the multicast address of the symmetric gradient
 // buffer, and one multimem.ld_reduce returns the element-wise sum of every rank's copy, so each element costs this SM one
-// load instead of `world` loads (and the reduction traffic never enters the GPU). RS_UNROLL of them are in flight per thread.
+// load instead of `world` loads (and the reduction traffic never enters the GPU). U of them are in flight per thread.
 __device__ __forceinline__ float4 mc_ld_reduce(const float* p) {
   float4 s;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -135,6 +136,7 @@ __device__ __forceinline__ float4 mc_ld_reduce(const float* p) {
   return s;
 }
 
+template <int U>
 __global__ void __launch_bounds__(RS_THREADS)
 rs_sumsq_mc_kernel(const float* __restrict__ mc, long offset, long n, float* __restrict__ dst, int accumulate, float scale,
                    float* __restrict__ partials) {
@@ -145,12 +147,12 @@ rs_sumsq_mc_kernel(const float* __restrict__ mc, long offset, long n, float* __r
   const float* base = mc + offset;
   float4* dst4 = reinterpret_cast<float4*>(dst);
   long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
-  for (; i + (RS_UNROLL - 1) * stride < n4; i += RS_UNROLL * stride) {
-    float4 s[RS_UNROLL];
+  for (; i + (U - 1) * stride < n4; i += U * stride) {
+    float4 s[U];
 #pragma unroll
-    for (int u = 0; u < RS_UNROLL; ++u) s[u] = mc_ld_reduce(base + 4 * (i + u * stride));
+    for (int u = 0; u < U; ++u) s[u] = mc_ld_reduce(base + 4 * (i + u * stride));
 #pragma unroll
-    for (int u = 0; u < RS_UNROLL; ++u) rs_finish(s[u], scale, accumulate, dst4, i + u * stride, acc);
+    for (int u = 0; u < U; ++u) rs_finish(s[u], scale, accumulate, dst4, i + u * stride, acc);
   }
   for (; i < n4; i += stride) {
     float4 s = mc_ld_reduce(base + 4 * i);
@@ -286,7 +288,11 @@ extern "C" int mt_rs_sumsq_mc(const float* mc, long offset, long n, float* dst, 
   if (n % 4 || offset % 4 || !mc) return -1;
   if (n == 0) return 0;
   const int parts = mt_rs_num_partials(n, ctas);
-  rs_sumsq_mc_kernel<<<parts, RS_THREADS, 0, st>>>(mc, offset, n, dst, accumulate, scale, partials);
+  // In-switch loads in flight per thread: 1 is the form every multi-GPU step time of this repository was measured with; 8
+  // (MAXTEXT_B200_RS_MC_UNROLL=8) is 2.9x faster in isolation at two ranks but has no same-box step measurement at 4 / 8 ranks.
+  static const int unroll = [] { const char* e = getenv("MAXTEXT_B200_RS_MC_UNROLL"); return (e && atoi(e) == 8) ? 8 : 1; }();
+  if (unroll == 8) rs_sumsq_mc_kernel<8><<<parts, RS_THREADS, 0, st>>>(mc, offset, n, dst, accumulate, scale, partials);
+  else rs_sumsq_mc_kernel<1><<<parts, RS_THREADS, 0, st>>>(mc, offset, n, dst, accumulate, scale, partials);
   if (sumsq_out && partials) rs_stage2_kernel<<<1, RS_THREADS, 0, st>>>(partials, parts, sumsq_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
