@@ -37,7 +37,9 @@ def test_dataset_field_mapping(tmp_path):
 def backend():
   from maxtext_b200.inference.maxengine import MaxEngine
   cfg = tiny_config("llama3-8b", ["max_prefill_predict_length=16", "max_target_length=32", "tokenizer_type=byte", "vocab_size=260"])
-  return ev.LocalBackend(cfg, engine=MaxEngine(cfg), slots=2)
+  eng = MaxEngine(cfg)
+  eng.load_params()                                  # random weights: the scores must depend on the text
+  return ev.LocalBackend(cfg, engine=eng, slots=2)
 
 
 def test_three_task_kinds_in_process(backend, tmp_path):
@@ -90,3 +92,14 @@ def test_server_backend_against_the_serving_app(backend):
     server.should_exit = True
     th.join(timeout=10)
     loop.stop()
+
+
+def test_harness_adapter_methods(backend):
+  from maxtext_b200.eval.harness import MaxTextLM
+  lm = MaxTextLM(backend, max_gen_toks=4)
+  (ll, greedy), (ll2, _) = lm.loglikelihood([("2+2 =", " 4"), ("2+2 =", " 5")])
+  want, n = backend.loglikelihood("2+2 =", " 4")
+  assert ll == pytest.approx(want, rel=1e-5) and isinstance(greedy, bool) and ll != ll2
+  assert lm.loglikelihood_rolling([("some text here",)])[0] < 0
+  gen = lm.generate_until([("repeat: abc", {"until": ["\n"], "max_gen_toks": 3})])
+  assert isinstance(gen[0], str) and "\n" not in gen[0]
