@@ -187,6 +187,12 @@ def derive_and_validate(raw: dict, num_devices: int = 1) -> dict:
 
   # ---- mesh degrees in mesh-axis order
   axes = list(t["mesh_axes"])
+  for prefix in ("ici", "dcn"):
+    # the legacy `sequence` axis is no mesh axis any more: its degree is folded into `context` (base.yml:663,676)
+    seq = int(t.get(f"{prefix}_sequence_parallelism", 1) or 1)
+    if seq > 1 and "sequence" not in axes and "context" in axes:
+      t[f"{prefix}_context_parallelism"] = max(1, int(t.get(f"{prefix}_context_parallelism", 1))) * seq
+      t[f"{prefix}_sequence_parallelism"] = 1
   def degree(prefix, axis):
     key = f"{prefix}_{AXIS_TO_KEY.get(axis, axis)}_parallelism"
     return int(t.get(key, 1))

@@ -111,3 +111,10 @@ def test_yaml_base_config_chain(tmp_path):
   grand.write_text(f"base_config: {child}\nsteps: 12\n")
   c = pyconfig.initialize(["t", str(grand), "log_config=false"], num_devices=1)
   assert c.steps == 12 and c.emb_dim == 4096
+
+
+def test_legacy_sequence_degree_folds_into_context():
+  from helpers import tiny_config
+  c = tiny_config("llama3-8b", ["ici_sequence_parallelism=2", "ici_fsdp_parallelism=2"], num_devices=4)
+  shape = dict(zip(c.mesh_axes, c.mesh_shape))
+  assert shape["context"] == 2 and shape["fsdp"] == 2 and "sequence" not in shape
