@@ -304,3 +304,20 @@ def test_frozen_parameters_under_fsdp_match_single(tmp_path, case):
   two = run_ranks(2, over + ["per_device_batch_size=2", "ici_fsdp_parallelism=2"], str(tmp_path), "two")
   _close(two["loss"], one["loss"], 2e-5)
   _close(two["grad_norm"], one["grad_norm"], 2e-4)
+
+
+def test_checkpoint_written_under_one_layout_resumes_under_another(tmp_path):
+  """Resharding on restore: a run saved by 2 FSDP ranks continues on 2 tensor-parallel ranks and on a single rank, and the
+  remaining steps equal those of an uninterrupted single-rank run (the tree on disk does not depend on the mesh)."""
+  common = ["learning_rate_schedule_steps=6", f"base_output_directory={tmp_path}", "async_checkpointing=false"]
+  full = _run_cli(1, common + ["per_device_batch_size=4", "steps=6", "run_name=full", "enable_checkpointing=false"])
+  ck = ["enable_checkpointing=true", "checkpoint_period=2"]
+  first = _run_cli(2, common + ck + ["per_device_batch_size=2", "ici_fsdp_parallelism=2", "steps=4", "run_name=a"])
+  _close(first, full[:4], 2e-5)
+  import shutil
+  shutil.copytree(os.path.join(tmp_path, "a"), os.path.join(tmp_path, "b"))
+  rest_tp = _run_cli(2, common + ck + ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_parallelism=2", "steps=6", "run_name=a"])
+  rest_one = _run_cli(1, common + ck + ["per_device_batch_size=4", "steps=6", "run_name=b"])
+  assert len(rest_tp) == 2 and len(rest_one) == 2
+  _close(rest_tp, full[4:], 2e-4)
+  _close(rest_one, full[4:], 2e-4)
