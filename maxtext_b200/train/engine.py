@@ -42,6 +42,13 @@ class TrainEngine:
       device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and c.hardware != "cpu" \
           else torch.device("cpu")
     self.device = torch.device(device)
+    if mesh is not None and L_sp_enabled(c) and mesh.axis_size(("tensor", "tensor_sequence")) > 1:
+      # the sequence-split residual stream is implemented for the plain layer loop only; a silent fallback would leave the
+      # norm-scale gradients flagged as partial sums although they are complete
+      if mesh.axis_size(("context", "context_usp_ulysses")) > 1 or mesh.axis_size("stage") > 1:
+        raise NotImplementedError("tensor_sequence parallelism cannot be combined with context or pipeline parallelism yet")
+      if int(getattr(c, "mtp_num_layers", 0) or 0) > 0:
+        raise NotImplementedError("multi-token prediction is not implemented under tensor_sequence parallelism")
     self.model = model or Transformer(c, mesh, self.device)
     from ..ops import quantization as _quant
     _quant.set_mode(str(c.quantization or ""))
@@ -156,7 +163,6 @@ class TrainEngine:
     if sp_on:
       from ..parallel import sequence_parallel as sp
       assert S % ctx.tp_size == 0, "the sequence must divide by the tensor-sequence degree"
-      assert not model.mtp_layers, "multi-token prediction is not implemented under tensor-sequence parallelism"
       ctx.sp = True
       x = sp.local_seq(x, ctx.tp_group)
     self._release(0) if self._units[0] and self._units[0][0].group_size > 1 and not c.logits_via_embedding else None

@@ -264,3 +264,12 @@ def test_dropout_is_replayed_by_recompute_and_off_in_eval():
   assert abs(eval_loss - train_loss) > 1e-4          # evaluation runs without dropout
   losses = [float(eng.train_step(batch)["learning/loss"]) for _ in range(5)]
   assert losses[-1] < losses[0]
+
+
+def test_unsupported_tensor_sequence_combinations_are_rejected():
+  from maxtext_b200.parallel.mesh import Mesh
+  from maxtext_b200.train.engine import TrainEngine
+  cfg = tiny_config("llama3-8b", ["ici_tensor_sequence_parallelism=2", "ici_context_parallelism=2", "ici_fsdp_parallelism=1"], num_devices=4)
+  mesh = Mesh(list(cfg.mesh_axes), list(cfg.mesh_shape), rank=0, world=4)
+  with pytest.raises(NotImplementedError):
+    TrainEngine(cfg, mesh, torch.device("cpu"))
