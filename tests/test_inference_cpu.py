@@ -205,18 +205,11 @@ def test_tensor_parallel_decode_matches_single_rank(tmp_path):
   import os
   import subprocess
   import sys
-  from test_multirank_cpu import BASE, ROOT, _free_port, _merge
+  from test_multirank_cpu import BASE, ROOT, _launch_with_retry, _merge
 
   def run(world, over, tag):
-    out, port, procs = str(tmp_path / f"{tag}.json"), _free_port(), []
-    for r in range(world):
-      env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                 MAXTEXT_B200_QUIET="1", OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
-      procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "inference_tp_worker.py"), out] + _merge(BASE, over),
-                                    cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
-    logs = [p.communicate(timeout=300)[0].decode(errors="replace") for p in procs]
-    for p, l in zip(procs, logs):
-      assert p.returncode == 0, l[-2500:]
+    out = str(tmp_path / f"{tag}.json")
+    _launch_with_retry(world, [sys.executable, os.path.join(ROOT, "tests", "inference_tp_worker.py"), out] + _merge(BASE, over))
     return json.load(open(out))
   base = ["max_prefill_predict_length=16", "max_target_length=32", "per_device_batch_size=1"]
   one = run(1, base, "one")
