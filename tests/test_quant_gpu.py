@@ -96,3 +96,17 @@ def test_delayed_scaling_uses_history_maximum():
   finally:
     Q.set_delayed_scaling(0)
 
+
+@pytest.mark.skip(reason="written without a GPU at hand: run once on a B200, then remove this mark")
+@pytest.mark.gpu
+def test_int8_products_on_gpu_match_the_definition():
+  """quantization=int8 on the GPU (integer product through the library) against the float emulation of the same integers."""
+  from maxtext_b200.ops import quantization as Q
+  torch.manual_seed(0)
+  x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+  w = (torch.randn(384, 512, device="cuda") * 0.1).bfloat16()
+  dy = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+  y, dx = Q.int8_linear_fwd(x, w), Q.int8_linear_dx(dy, w)
+  y_ref, dx_ref = Q.int8_linear_fwd(x.cpu().float(), w.cpu().float()), Q.int8_linear_dx(dy.cpu().float(), w.cpu().float())
+  assert (y.float().cpu() - y_ref).abs().max() < 0.02 * y_ref.abs().max() + 0.05
+  assert (dx.float().cpu() - dx_ref).abs().max() < 0.02 * dx_ref.abs().max() + 0.05
