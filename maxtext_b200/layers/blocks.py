@@ -361,7 +361,8 @@ class Attention:
       x = tp_enter(x, ctx)
       B, S, _ = x.shape                      # sequence parallelism: the gathered length
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
-    plain = (not self.qk_norm and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and ctx.cache is None and ctx.cp_size == 1
+    moba = bool(getattr(self.config, "moba", False)) and ctx.cache is None and ctx.cp_size == 1
+    plain = (not self.qk_norm and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and not moba and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
@@ -400,7 +401,13 @@ class Attention:
         sc = torch.log(torch.floor((ctx.positions.float() + 1.0) / float(getattr(c_, "temperature_tuning_floor_scale", 8192.0))) + 1.0) \
             * float(getattr(c_, "temperature_tuning_scale", 0.1)) + 1.0
         q = (q.float() * sc[:, :, None, None]).to(q.dtype)
-      if ctx.cache is None and ctx.bidir is not None and ctx.cp_size == 1:
+      if moba:
+        # mixture-of-block attention: each query attends its own block and the best `moba_topk` earlier key blocks
+        seg = None
+        if ctx.segment_ids is not None:
+          seg = (ctx.segment_ids[:, None, :, None] == ctx.segment_ids[:, None, None, :]) & (ctx.segment_ids[:, None, None, :] != 0)
+        out = ref.moba_attention(q, k, v, ctx.positions, int(self.config.moba_chunk_size), int(self.config.moba_topk), 1.0, seg)
+      elif ctx.cache is None and ctx.bidir is not None and ctx.cp_size == 1:
         # multimodal prompt: causal (and windowed) as usual, plus both directions inside each image's block of soft tokens
         m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window) | ctx.bidir
         out = ref.attention(q, k, v, m, 1.0, self.soft_cap).to(q.dtype)

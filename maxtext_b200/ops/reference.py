@@ -244,3 +244,47 @@ def grouped_matmul(x: torch.Tensor, w: torch.Tensor, group_sizes: torch.Tensor) 
   if start < x.shape[0]:
     out[start:] = 0
   return out
+
+
+def moba_block_mask(q, k, q_pos, chunk: int, topk: int):
+  """Mixture-of-block attention gate (src/maxtext/layers/attention_op.py:1149-1259): keys are grouped into blocks of `chunk`
+  positions, each query scores a block by its dot product with the block's mean key, blocks in the future are excluded, the
+  query's own block always counts, and only the `topk` best blocks are attended (within them, causally).
+
+  q [B,Sq,Hq,D], k [B,Skv,Hkv,D], q_pos [B,Sq] -> bool [B,Hkv,g,Sq,Skv] (True = attend)."""
+  B, Sq, Hq, D = q.shape
+  Skv, Hkv = k.shape[1], k.shape[2]
+  g = Hq // Hkv
+  nb = -(-Skv // chunk)
+  kf = k.float()
+  pad = nb * chunk - Skv
+  kp = F.pad(kf, (0, 0, 0, 0, 0, pad)) if pad else kf
+  cnt = torch.full((nb,), float(chunk), device=k.device)
+  if pad:
+    cnt[-1] = chunk - pad
+  kmean = kp.view(B, nb, chunk, Hkv, D).sum(2) / cnt[None, :, None, None]                      # [B,nb,Hkv,D]
+  gate = torch.einsum("bskgd,bnkd->bkgsn", q.float().view(B, Sq, Hkv, g, D), kmean)            # [B,Hkv,g,Sq,nb]
+  qb = (q_pos // chunk)[:, None, None, :, None]
+  blocks = torch.arange(nb, device=q.device)[None, None, None, None, :]
+  gate = torch.where(qb > blocks, gate, torch.full_like(gate, float("-inf")))
+  gate = torch.where(qb == blocks, torch.full_like(gate, float("inf")), gate)
+  kk = min(int(topk), nb)
+  top_val, top_idx = gate.topk(kk, dim=-1)
+  chosen = torch.zeros_like(gate, dtype=torch.bool).scatter_(-1, top_idx, True) & (gate >= top_val.min(-1, keepdim=True).values)
+  kblock = torch.arange(Skv, device=q.device) // chunk
+  token = chosen[..., kblock]                                                                   # [B,Hkv,g,Sq,Skv]
+  causal = q_pos[:, None, None, :, None] >= torch.arange(Skv, device=q.device)[None, None, None, None, :]
+  return token & causal
+
+
+def moba_attention(q, k, v, q_pos, chunk: int, topk: int, scale: float = 1.0, extra_mask=None):
+  """Softmax attention restricted by `moba_block_mask` (and by `extra_mask` [B,1,Sq,Skv], e.g. segments)."""
+  B, Sq, Hq, D = q.shape
+  Hkv = k.shape[2]
+  g = Hq // Hkv
+  m = moba_block_mask(q, k, q_pos, chunk, topk)
+  if extra_mask is not None:
+    m = m & extra_mask[:, :, None]
+  logits = torch.einsum("bqhgd,bkhd->bhgqk", q.float().view(B, Sq, Hkv, g, D), k.float()) * scale
+  p = torch.softmax(logits.masked_fill(~m, -1e30), dim=-1)
+  return torch.einsum("bhgqk,bkhd->bqhgd", p, v.float()).reshape(B, Sq, Hq, v.shape[-1]).to(q.dtype)

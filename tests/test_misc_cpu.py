@@ -234,3 +234,40 @@ def test_small_config_switches():
   _, hist = T.main(["train", BASE_YML] + args)
   losses = [h["learning/loss"] for h in hist]
   assert all(b_ < a_ for a_, b_ in zip(losses, losses[1:])), losses        # the same batch every step: monotone at this size
+
+
+def test_moba_mask_matches_a_per_query_restatement_and_trains():
+  import torch
+  from helpers import tiny_config, make_engine, batch_of
+  from maxtext_b200.ops import reference as ref
+  torch.manual_seed(0)
+  B, S, Hq, Hkv, D, chunk, topk = 1, 22, 4, 2, 8, 4, 2
+  q, k = torch.randn(B, S, Hq, D), torch.randn(B, S, Hkv, D)
+  pos = torch.arange(S)[None]
+  m = ref.moba_block_mask(q, k, pos, chunk, topk)
+  g, nb = Hq // Hkv, -(-S // chunk)
+  for h in range(Hq):
+    kv = h // g
+    for t in range(S):
+      scores = []
+      for n in range(nb):
+        blk = k[0, n * chunk:(n + 1) * chunk, kv].float().mean(0)
+        sc = float(q[0, t, h].float() @ blk)
+        if n > t // chunk:
+          sc = float("-inf")
+        if n == t // chunk:
+          sc = float("inf")
+        scores.append(sc)
+      best = sorted(range(nb), key=lambda n: -scores[n])[: min(topk, nb)]
+      best = [n for n in best if scores[n] > float("-inf")]
+      want = torch.tensor([(j // chunk in best) and j <= t for j in range(S)])
+      assert torch.equal(m[0, kv, h % g, t], want), (h, t)
+  # with top-k covering all blocks the result is plain causal attention
+  v = torch.randn(B, S, Hkv, D)
+  full = ref.moba_attention(q, k, v, pos, chunk, nb, 0.3)
+  causal = ref.attention(q, k, v, ref.attention_mask(pos, pos), 0.3)
+  assert torch.allclose(full, causal.to(full.dtype), atol=1e-5)
+  eng = make_engine(tiny_config("llama3-8b", ["moba=true", "moba_chunk_size=8", "moba_topk=2"]))
+  b = batch_of(eng.config)
+  ls = [float(eng.train_step(b)["learning/loss"]) for _ in range(4)]
+  assert ls[-1] < ls[0]
