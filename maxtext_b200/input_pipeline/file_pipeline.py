@@ -113,6 +113,17 @@ class FileDataIterator:
                 arr = np.asarray(ex["__tokens__"]).reshape(-1)
                 for s in range(0, len(arr) - 1, self.S + 1):
                   yield arr[s:s + self.S + 1].astype(np.int32)
+              elif bool(getattr(c, "use_sft", False)) and isinstance(ex.get(self.columns[0]), list):
+                # chat data: a `messages` column; rendered with the chat template, trained on the last assistant turn
+                from . import chat
+                if not hasattr(self, "_chat_template"):
+                  self._chat_template = chat.load_template(c)
+                ptxt, ctxt = chat.split_for_sft(ex[self.columns[0]], self._chat_template)
+                pr = [t % c.vocab_size for t in self.tok.encode(ptxt, add_bos=bool(c.add_bos), add_eos=False)]
+                co = [t % c.vocab_size for t in self.tok.encode(ctxt, add_bos=False, add_eos=bool(c.add_eos))]
+                if bool(getattr(c, "sft_train_on_completion_only", False)):
+                  pr = [-(t + 1) for t in pr]
+                yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
               elif bool(getattr(c, "use_sft", False)) and len(self.columns) >= 2 and self.columns[1] in ex:
                 # supervised fine-tuning (`use_sft`, src/maxtext/input_pipeline/input_pipeline_utils.py): prompt + completion in
                 # one sequence; with sft_train_on_completion_only the prompt tokens carry no loss

@@ -159,3 +159,27 @@ def test_eval_uses_the_eval_files(tmp_path):
   held_out = T.run_eval(cfg, eng, None)
   on_train = T.run_eval(tiny_config("llama3-8b", base), eng, None)
   assert held_out > on_train + 0.5, (held_out, on_train)
+
+
+def test_chat_template_rendering_and_sft_on_messages(tmp_path):
+  import json
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline import chat
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "YO"}]
+  assert chat.render(msgs[:2], chat.DEFAULT_TEMPLATE, True) == "system: be brief\nuser: hi\nassistant: "
+  tpl = "{{ bos_token }}{% for m in messages %}<{{ m['role'] }}>{{ m['content'] }}</s>{% endfor %}{% if add_generation_prompt %}<assistant>{% endif %}"
+  assert chat.split_for_sft(msgs, tpl) == ("<system>be brief</s><user>hi</s><assistant>", "YO")
+  tf = tmp_path / "tpl.json"
+  tf.write_text(json.dumps({"chat_template": tpl}))
+  p = tmp_path / "chat.jsonl"
+  p.write_text("\n".join(json.dumps({"messages": msgs}) for _ in range(4)))
+  cfg = tiny_config("llama3-8b", ["dataset_type=hf", f"hf_train_files={p}", "train_data_columns=['messages']", "tokenizer_type=byte",
+                                  "vocab_size=260", "use_sft=true", "sft_train_on_completion_only=true", "packing=false",
+                                  "max_target_length=64", "per_device_batch_size=1", "add_bos=false", "add_eos=false",
+                                  f"chat_template_path={tf}"])
+  b = next(create_data_iterator(cfg))
+  text = bytes(t for t in b["inputs"][0].tolist() if 0 < t < 256).decode()
+  assert text.startswith("<system>be brief</s><user>hi</s><assistant>Y")
+  trained = bytes(t for t, s in zip(b["targets"][0].tolist(), b["targets_segmentation"][0].tolist()) if s != 0 and 0 < t < 256).decode()
+  assert trained == "YO"
