@@ -17,7 +17,12 @@ def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -
   if engine is None:
     eng.load_params()
   tok = build_tokenizer(config)
-  ids = tok.encode(prompt if prompt is not None else config.prompt, add_bos=bool(config.add_bos))
+  text_in = prompt if prompt is not None else config.prompt
+  if bool(getattr(config, "use_chat_template", False)):
+    # the prompt is one user turn; the template appends the header of the assistant's answer
+    from ..input_pipeline import chat
+    text_in = chat.render([{"role": "user", "content": text_in}], chat.load_template(config), add_generation_prompt=True)
+  ids = tok.encode(text_in, add_bos=bool(config.add_bos))
   mm_kw = {}
   if bool(getattr(config, "use_multimodal", False)) and str(getattr(config, "image_path", "") or ""):
     # one <start_of_image> in the prompt per file of image_path; each grows to 260 positions (256 of them soft tokens)
