@@ -183,3 +183,20 @@ def test_chat_template_rendering_and_sft_on_messages(tmp_path):
   assert text.startswith("<system>be brief</s><user>hi</s><assistant>Y")
   trained = bytes(t for t, s in zip(b["targets"][0].tolist(), b["targets_segmentation"][0].tolist()) if s != 0 and 0 < t < 256).decode()
   assert trained == "YO"
+
+
+def test_decode_wraps_prompt_with_chat_template(monkeypatch):
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline import tokenizer as tk
+  from maxtext_b200.inference import decode as dec
+  seen = []
+  orig = tk.ByteTokenizer.encode
+
+  def spy(self, text, *a, **k):
+    seen.append(text)
+    return orig(self, text, *a, **k)
+  monkeypatch.setattr(tk.ByteTokenizer, "encode", spy)
+  cfg = tiny_config("llama3-8b", ["tokenizer_type=byte", "vocab_size=260", "use_chat_template=true", "prompt=hi", "max_target_length=32",
+                                  "max_prefill_predict_length=16", "per_device_batch_size=1", "chat_template=[{{ messages[0]['content'] }}]>"])
+  dec.decode(cfg)
+  assert seen and seen[0] == "[hi]>"
