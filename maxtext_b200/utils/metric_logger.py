@@ -1,4 +1,4 @@
-"""Step metrics: console line, JSONL file, optional TensorBoard.
+"""Step metrics: console line, JSONL file, optional TensorBoard, optional Prometheus endpoint (`prometheus_port`).
 
 Follows src/maxtext/common/metric_logger.py:91-510: the metrics of step n are written while step
 n+1 runs (the device tensors are read one step late, so logging never stalls the GPU), the console
@@ -40,6 +40,23 @@ class MetricLogger:
       except Exception:  # tensorboard is optional
         self.tb = None
     self.history = []
+    self.prom = None
+    port = int(getattr(config, "prometheus_port", 0) or 0)
+    if is_writer and port > 0:
+      # one gauge per metric (slashes are not legal in Prometheus names), served from a daemon thread on `port`
+      import prometheus_client
+      self.prom_registry = prometheus_client.CollectorRegistry()
+      prometheus_client.start_http_server(port, registry=self.prom_registry)
+      self.prom = {}
+
+  def _export(self, scal):
+    import prometheus_client
+    for k, v in scal.items():
+      name = "maxtext_" + "".join(ch if ch.isalnum() else "_" for ch in k)
+      g = self.prom.get(name)
+      if g is None:
+        g = self.prom[name] = prometheus_client.Gauge(name, k, registry=self.prom_registry)
+      g.set(v)
 
   def record(self, step: int, metrics: dict, step_time_s: float):
     """Buffer this step's (device) metrics; write the previous step's."""
@@ -77,6 +94,8 @@ class MetricLogger:
           f"total_weights: {int(scal.get('learning/total_weights', 0))}, loss: {scal.get('learning/loss', float('nan')):.3f}")
       if self.file:
         self.file.write(json.dumps(scal) + "\n")
+      if self.prom is not None:
+        self._export(scal)
       if self.tb and step % max(1, self.c.log_period) == 0:
         for k, v in scal.items():
           self.tb.add_scalar(k, v, step)

@@ -271,3 +271,19 @@ def test_moba_mask_matches_a_per_query_restatement_and_trains():
   b = batch_of(eng.config)
   ls = [float(eng.train_step(b)["learning/loss"]) for _ in range(4)]
   assert ls[-1] < ls[0]
+
+
+def test_prometheus_endpoint_serves_step_metrics():
+  import socket
+  import urllib.request
+  from helpers import tiny_config
+  from maxtext_b200.utils.metric_logger import MetricLogger
+  with socket.socket() as s:
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+  ml = MetricLogger(tiny_config("llama3-8b", [f"prometheus_port={port}"]))
+  ml.record(0, {"learning/loss": 2.5}, 0.1)
+  ml.flush()
+  body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
+  assert "maxtext_learning_loss 2.5" in body and "maxtext_perf_step_time_seconds" in body
+  ml.close()
