@@ -3,6 +3,8 @@
 Rollouts for RL come from this repository's decode engine instead of an external vLLM / Tunix cluster."""
 from __future__ import annotations
 
+import math
+
 import copy
 
 import torch
@@ -168,10 +170,31 @@ class GRPOTrainer:
 
 
 # ------------------------------------------------------------------------------------------------ distillation
-def distill_step(student: TrainEngine, teacher: TrainEngine, batch: dict, alpha: float | None = None, temperature: float | None = None):
+def scheduled(step: int, max_steps: int, start: float, end, kind: str) -> float:
+  """A loss weight that moves from `start` to `end` over the run: `constant`, `linear` or `cosine` in step / max_steps
+  (`distill_{alpha,temperature,beta}_schedule` and `_end`; distillation_utils.py:165 `compute_schedule`)."""
+  if end is None or str(end) in ("None", "") or kind == "constant":
+    return float(start)
+  start, end = float(start), float(end)
+  prog = min(max(step / max(1, max_steps), 0.0), 1.0)
+  if kind == "linear":
+    return start + (end - start) * prog
+  if kind == "cosine":
+    return end + (start - end) * 0.5 * (1.0 + math.cos(math.pi * prog))
+  raise ValueError(f"unsupported schedule {kind!r}: constant, linear or cosine")
+
+
+def distill_step(student: TrainEngine, teacher: TrainEngine, batch: dict, alpha: float | None = None, temperature: float | None = None,
+                 step: int | None = None):
   """Online distillation on small models: full logits of both models, loss by autograd through the student's head and
-  the engine's layer schedule (the hidden-state gradient is injected with `fwd_bwd_from_hidden_grad`)."""
+  the engine's layer schedule (the hidden-state gradient is injected with `fwd_bwd_from_hidden_grad`). With `step`
+  given, alpha and the temperature follow their configured schedules over `steps`."""
   c = student.config
+  if step is not None:
+    if alpha is None:
+      alpha = scheduled(step, c.steps, c.distill_alpha, c.distill_alpha_end, str(c.distill_alpha_schedule))
+    if temperature is None:
+      temperature = scheduled(step, c.steps, c.distill_temperature, c.distill_temperature_end, str(c.distill_temperature_schedule))
   alpha = float(c.distill_alpha if alpha is None else alpha)
   temperature = float(c.distill_temperature if temperature is None else temperature)
   with torch.no_grad():

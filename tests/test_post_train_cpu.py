@@ -113,3 +113,16 @@ def test_use_dpo_through_the_train_cli(tmp_path):
   acc = [float(h["dpo/reward_accuracy"]) for h in hist]
   loss = [float(h["dpo/loss"]) for h in hist]
   assert loss[-1] < loss[0] and acc[-1] >= acc[0] and abs(loss[0] - 0.6931) < 1e-3        # starts at log 2: policy = reference
+
+
+def test_distillation_weight_schedules():
+  import math
+  from maxtext_b200.trainers.post_train.trainers import scheduled
+  assert scheduled(5, 10, 0.5, None, "linear") == 0.5
+  assert scheduled(5, 10, 0.5, 0.1, "constant") == 0.5
+  assert abs(scheduled(5, 10, 0.5, 0.1, "linear") - 0.3) < 1e-9
+  assert abs(scheduled(20, 10, 0.5, 0.1, "linear") - 0.1) < 1e-9
+  assert abs(scheduled(5, 10, 2.0, 1.0, "cosine") - 1.5) < 1e-9 and abs(scheduled(0, 10, 2.0, 1.0, "cosine") - 2.0) < 1e-9
+  import pytest
+  with pytest.raises(ValueError):
+    scheduled(1, 10, 1.0, 0.0, "step")
