@@ -51,12 +51,13 @@ def _from_numpy(a: np.ndarray) -> torch.Tensor:
   return torch.from_numpy(np.ascontiguousarray(a))
 
 
-def leaf_key(pdef, scan_layers: bool) -> tuple[tuple, int | None]:
-  """Tree path of the array holding this parameter and the index of the layer axis (None if unstacked)."""
+def leaf_key(pdef, scan_layers: bool, scan_axis: int = 1) -> tuple[tuple, int | None]:
+  """Tree path of the array holding this parameter and the index of the layer axis (None if unstacked). With scanned layers
+  the stacked layer axis sits at `param_scan_axis` of the array (src/maxtext/configs/base.yml `param_scan_axis`, default 1)."""
   if pdef.layer is None:
     return tuple(pdef.ref_path), None
   if scan_layers:
-    return ("decoder", pdef.stack) + tuple(pdef.ref_path), 1
+    return ("decoder", pdef.stack) + tuple(pdef.ref_path), int(scan_axis)
   return ("decoder", f"{pdef.stack}_{pdef.layer}") + tuple(pdef.ref_path), None
 
 
@@ -126,7 +127,7 @@ class TreeIO:
         continue
       ref_local = ps.to_ref_layout(_LocalView(d, self._local_ref_shape(d)[0]), t)
       arr = _to_numpy(ref_local.to(dtype) if dtype is not None else ref_local)
-      key, axis = leaf_key(d, scan)
+      key, axis = leaf_key(d, scan, int(self.c.param_scan_axis))
       adir = self._array_dir(root, prefix, key)
       shape = list(d.ref_shape)
       _, sl = self._local_ref_shape(d)
@@ -183,11 +184,24 @@ class TreeIO:
     first_layer = d.layer in (None, 0)
     return first_layer and self.tp_rank == 0 and self.ep_rank == 0 or (not self.c.scan_layers and self.tp_rank == 0 and self.ep_rank == 0)
 
+  def _scan_axis_of(self, root: str) -> int:
+    """The layer axis recorded by the writer of the tree under `root` (falls back to this run's `param_scan_axis`)."""
+    cache = self.__dict__.setdefault("_scan_axis_cache", {})
+    if root not in cache:
+      ax = int(self.c.param_scan_axis)
+      try:
+        with open(os.path.join(root, "_METADATA"), "r", encoding="utf-8") as fh:
+          ax = int(json.load(fh).get("custom_metadata", {}).get("param_scan_axis", ax))
+      except (OSError, ValueError):
+        pass
+      cache[root] = ax
+    return cache[root]
+
   def read_param(self, root: str, prefix: tuple, p) -> torch.Tensor | None:
     """Internal-layout tensor for parameter p from the tree under `root`, or None when absent."""
     d = p.pdef
     for scan in (bool(self.c.scan_layers), not bool(self.c.scan_layers)):
-      key, axis = leaf_key(d, scan)
+      key, axis = leaf_key(d, scan, self._scan_axis_of(root))
       adir = self._array_dir(root, prefix, key)
       if os.path.isfile(os.path.join(adir, "zarr.json")):
         break
@@ -284,17 +298,19 @@ class CheckpointManager:
     for name, flat in opt.items():
       self.io.write_tree(items, ("opt_state", "0", name, "params"), flat, self.pool, futures)
     if self.rank == 0:
-      zarr3.write_array(os.path.join(items, "step"), np.asarray(step, dtype=np.int32))
+      # the `step` leaf counts completed steps, as the reference's TrainState.step does after the step that is saved
+      zarr3.write_array(os.path.join(items, "step"), np.asarray(step + 1, dtype=np.int32))
       zarr3.write_array(os.path.join(items, "opt_state.0.count"), np.asarray(self.engine.step_count, dtype=np.int32))
       meta = {"custom_metadata": {"scan_layers": bool(self.c.scan_layers), "param_scan_axis": int(self.c.param_scan_axis),
                                   "format": "zarr3", "use_ocdbt": False, "model_name": self.c.model_name},
               "tree_metadata": sorted(os.listdir(items)), "timestamp": time.time()}
       with open(os.path.join(items, "_METADATA"), "w", encoding="utf-8") as fh:
         json.dump(meta, fh)
-      if data_iterator is not None and hasattr(data_iterator, "state"):
-        os.makedirs(os.path.join(sdir, "iter"), exist_ok=True)
-        with open(os.path.join(sdir, "iter", f"process_{self.rank}.json"), "w", encoding="utf-8") as fh:
-          json.dump(data_iterator.state(), fh)
+    if data_iterator is not None and hasattr(data_iterator, "state"):
+      # every rank records its own reader position: ranks of different data shards are at different places in the stream
+      os.makedirs(os.path.join(sdir, "iter"), exist_ok=True)
+      with open(os.path.join(sdir, "iter", f"process_{self.rank}.json"), "w", encoding="utf-8") as fh:
+        json.dump(data_iterator.state(), fh)
     self._inflight = (step, futures, sdir)
     if not self.c.async_checkpointing or force:
       self.wait_until_finished()
@@ -345,10 +361,16 @@ class CheckpointManager:
   def restore(self, step_dir: str, full_state: bool = True, data_iterator=None):
     items = os.path.join(step_dir, "items") if os.path.isdir(os.path.join(step_dir, "items")) else step_dir
     _restore_tree(self.io, items, self.engine, full_state)
-    it_file = os.path.join(step_dir, "iter", f"process_{self.rank}.json")
-    if data_iterator is not None and os.path.isfile(it_file) and hasattr(data_iterator, "load_state"):
-      with open(it_file, "r", encoding="utf-8") as fh:
-        data_iterator.load_state(json.load(fh))
+    if data_iterator is not None and hasattr(data_iterator, "load_state"):
+      it_file = os.path.join(step_dir, "iter", f"process_{self.rank}.json")
+      if os.path.isfile(it_file):
+        with open(it_file, "r", encoding="utf-8") as fh:
+          data_iterator.load_state(json.load(fh))
+      elif os.path.isfile(os.path.join(step_dir, "iter", "process_0.json")):
+        # written by a run with fewer ranks: rank 0's position is the closest known one (exact only without packing windows)
+        max_logging.log(f"warning: {step_dir} has no data-iterator state for rank {self.rank}; resuming from rank 0's position")
+        with open(os.path.join(step_dir, "iter", "process_0.json"), "r", encoding="utf-8") as fh:
+          data_iterator.load_state(json.load(fh))
 
 
 def _restore_tree(io: TreeIO, items: str, engine, full_state: bool):

@@ -67,7 +67,8 @@ class FileDataIterator:
     assert gb % data_world == 0
     self.batch = gb // data_world
     self.S = int(c.max_target_length)
-    self.epoch, self.index = 0, 0       # index = examples consumed (globally) in this epoch
+    self.epoch, self.index, self.sub = 0, 0, 0       # next array to read: chunk `sub` of example `index` (global numbering) of `epoch`
+    self._sync, self._used = self._pos(), 0
     self.pack = bool(c.packing)
     self._rows = self._row_stream()
 
@@ -99,65 +100,99 @@ class FileDataIterator:
     if window:
       yield from flush()
 
+  def _encode(self, ex):
+    """Token arrays of one example: one array, or consecutive S+1 chunks of a pre-tokenized .npy file."""
+    c = self.c
+    if "__tokens__" in ex:
+      arr = np.asarray(ex["__tokens__"]).reshape(-1)
+      for s in range(0, len(arr) - 1, self.S + 1):
+        yield arr[s:s + self.S + 1].astype(np.int32)
+    elif bool(getattr(c, "use_sft", False)) and isinstance(ex.get(self.columns[0]), list):
+      # chat data: a `messages` column; rendered with the chat template, trained on the last assistant turn
+      from . import chat
+      if not hasattr(self, "_chat_template"):
+        self._chat_template = chat.load_template(c)
+      ptxt, ctxt = chat.split_for_sft(ex[self.columns[0]], self._chat_template)
+      pr = [t % c.vocab_size for t in self.tok.encode(ptxt, add_bos=bool(c.add_bos), add_eos=False)]
+      co = [t % c.vocab_size for t in self.tok.encode(ctxt, add_bos=False, add_eos=bool(c.add_eos))]
+      if bool(getattr(c, "sft_train_on_completion_only", False)):
+        pr = [-(t + 1) for t in pr]
+      yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
+    elif bool(getattr(c, "use_sft", False)) and len(self.columns) >= 2 and self.columns[1] in ex:
+      # supervised fine-tuning (`use_sft`, src/maxtext/input_pipeline/input_pipeline_utils.py): prompt + completion in
+      # one sequence; with sft_train_on_completion_only the prompt tokens carry no loss
+      pr = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[0]]), add_bos=bool(c.add_bos), add_eos=False)]
+      co = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[1]]), add_bos=False, add_eos=bool(c.add_eos))]
+      if bool(getattr(c, "sft_train_on_completion_only", False)):
+        pr = [-(t + 1) for t in pr]
+      yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
+    else:
+      text = ex[self.column]
+      ids = self.tok.encode(text, add_bos=bool(c.add_bos), add_eos=bool(c.add_eos)) if c.tokenize_train_data else list(text)
+      ids = [t % c.vocab_size for t in ids]
+      yield np.asarray(ids[: self.S + 1] if c.use_truncation else ids, dtype=np.int32)
+
   def _token_stream(self):
-    """All ranks walk the same example sequence; rank r keeps examples with index % world == r."""
+    """All ranks walk the same example sequence; rank r keeps examples with index % world == r. The reader position is
+    (epoch, index, sub): the next array to produce is chunk `sub` of example `index` of that epoch."""
     c = self.c
     while c.num_epoch <= 0 or self.epoch < max(1, int(c.num_epoch)):
-      i = 0
-      for _once in (0,):
-        for ex in self._examples():
-          if i >= self.index:
-            self.index = i + 1
-            if i % self.world == self.rank:
-              if "__tokens__" in ex:
-                arr = np.asarray(ex["__tokens__"]).reshape(-1)
-                for s in range(0, len(arr) - 1, self.S + 1):
-                  yield arr[s:s + self.S + 1].astype(np.int32)
-              elif bool(getattr(c, "use_sft", False)) and isinstance(ex.get(self.columns[0]), list):
-                # chat data: a `messages` column; rendered with the chat template, trained on the last assistant turn
-                from . import chat
-                if not hasattr(self, "_chat_template"):
-                  self._chat_template = chat.load_template(c)
-                ptxt, ctxt = chat.split_for_sft(ex[self.columns[0]], self._chat_template)
-                pr = [t % c.vocab_size for t in self.tok.encode(ptxt, add_bos=bool(c.add_bos), add_eos=False)]
-                co = [t % c.vocab_size for t in self.tok.encode(ctxt, add_bos=False, add_eos=bool(c.add_eos))]
-                if bool(getattr(c, "sft_train_on_completion_only", False)):
-                  pr = [-(t + 1) for t in pr]
-                yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
-              elif bool(getattr(c, "use_sft", False)) and len(self.columns) >= 2 and self.columns[1] in ex:
-                # supervised fine-tuning (`use_sft`, src/maxtext/input_pipeline/input_pipeline_utils.py): prompt + completion in
-                # one sequence; with sft_train_on_completion_only the prompt tokens carry no loss
-                pr = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[0]]), add_bos=bool(c.add_bos), add_eos=False)]
-                co = [t % c.vocab_size for t in self.tok.encode(str(ex[self.columns[1]]), add_bos=False, add_eos=bool(c.add_eos))]
-                if bool(getattr(c, "sft_train_on_completion_only", False)):
-                  pr = [-(t + 1) for t in pr]
-                yield np.asarray((pr + co)[: self.S + 1], dtype=np.int32)
-              else:
-                text = ex[self.column]
-                ids = self.tok.encode(text, add_bos=bool(c.add_bos), add_eos=bool(c.add_eos)) if c.tokenize_train_data else list(text)
-                ids = [t % c.vocab_size for t in ids]
-                yield np.asarray(ids[: self.S + 1] if c.use_truncation else ids, dtype=np.int32)
-          i += 1
+      start_i, start_sub = self.index, self.sub
+      for i, ex in enumerate(self._examples()):
+        if i < start_i:
+          continue
+        if i % self.world == self.rank:
+          for j, ids in enumerate(self._encode(ex)):
+            if i == start_i and j < start_sub:
+              continue
+            self.index, self.sub = i, j + 1
+            yield ids
+        self.index, self.sub = i + 1, 0
       self.epoch += 1
-      self.index = 0
+      self.index, self.sub = 0, 0
 
-  def _row_stream(self):
+  def _pos(self):
+    return {"epoch": self.epoch, "index": self.index, "sub": self.sub}
+
+  def _group_stream(self):
+    """Yields (reader position before the group, rows of the group). A group is what one packing window produces (or the
+    single row of one array without packing): the smallest unit that can be rebuilt from a reader position alone."""
     S1 = self.S + 1
-    if self.pack:
-      window = []
-      for ids in self._token_stream():
+    ts = self._token_stream()
+    if not self.pack:
+      while True:
+        pos = self._pos()
+        try:
+          ids = next(ts)
+        except StopIteration:
+          return
+        yield pos, [packing._emit([ids[:S1]], S1)]
+    mode = self.c.grain_packing_type
+    while True:
+      pos, window = self._pos(), []
+      for ids in ts:
         window.append(ids)
         if len(window) >= 8 * self.batch:
-          mode = self.c.grain_packing_type
-          rows = packing.concat_then_split(window, S1) if mode == "concat_then_split" else \
-              packing.pack_first_fit(window, S1, int(self.c.max_segments_per_seq), "best_fit" if mode == "best_fit" else "first_fit")
-          yield from rows
-          window = []
-      if window:
-        yield from packing.pack_first_fit(window, S1, int(self.c.max_segments_per_seq))
-    else:
-      for ids in self._token_stream():
-        yield packing._emit([ids[:S1]], S1)
+          break
+      if not window:
+        return
+      last = len(window) < 8 * self.batch
+      if mode == "concat_then_split":
+        rows = list(packing.concat_then_split(window, S1))
+      else:
+        rows = list(packing.pack_first_fit(window, S1, int(self.c.max_segments_per_seq), "best_fit" if mode == "best_fit" and not last else "first_fit"))
+      yield pos, rows
+      if last:
+        return
+
+  def _row_stream(self, skip: int = 0):
+    for pos, rows in self._group_stream():
+      self._sync, self._used = pos, 0
+      for r in rows:
+        self._used += 1
+        if self._used > skip:
+          yield r
+      skip = 0
 
   def __iter__(self):
     return self
@@ -174,11 +209,15 @@ class FileDataIterator:
     return {k: torch.from_numpy(np.stack([r[k] for r in rows]).astype(np.int32)) for k in rows[0]}
 
   def state(self) -> dict:
-    return {"epoch": self.epoch, "index": self.index}
+    """Position of the last delivered row: the reader position at which the current group began plus the number of its
+    rows already handed out. Rebuilding that group and dropping those rows continues exactly where the run stopped, although
+    the reader itself runs up to a packing window ahead of what was delivered."""
+    return {**self._sync, "used": self._used}
 
   def load_state(self, st: dict):
-    self.epoch, self.index = int(st.get("epoch", 0)), int(st.get("index", 0))
-    self._rows = self._row_stream()
+    self.epoch, self.index, self.sub = int(st.get("epoch", 0)), int(st.get("index", 0)), int(st.get("sub", 0))
+    self._sync, self._used = self._pos(), 0
+    self._rows = self._row_stream(skip=int(st.get("used", 0)))
 
 
 def create_file_iterator(config, data_rank=0, data_world=1, split="train"):

@@ -51,6 +51,7 @@ class RampupIterator:
     self.buf = None
     self.start = 0
     self.active = self.cur < self.full
+    self._before_buf = None      # the wrapped iterator's state just before `buf` was read from it
 
   def __iter__(self):
     return self
@@ -59,22 +60,26 @@ class RampupIterator:
     import torch
     return {k: (v[lo:hi] if torch.is_tensor(v) else v) for k, v in batch.items()}
 
+  def _pull(self):
+    self._before_buf = self.inner.state() if hasattr(self.inner, "state") else None
+    return next(self.inner)
+
   def __next__(self):
     import torch
     if not self.active:
       if self.buf is not None and self.start > 0:       # finish the partially used buffer first
         rest = self._slice(self.buf, self.start, self.full)
-        nxt = next(self.inner)
+        nxt = self._pull()
         out = {k: (torch.cat([rest[k], v[: self.start]]) if torch.is_tensor(v) else v) for k, v in nxt.items()}
         self.buf = nxt
         return out
       self.buf = None
       return next(self.inner)
     if self.buf is None:
-      self.buf, self.start = next(self.inner), 0
+      self.buf, self.start = self._pull(), 0
     lo, hi = self.start, self.start + self.cur
     if hi > self.full:
-      old, self.buf = self.buf, next(self.inner)
+      old, self.buf = self.buf, self._pull()
       a, b = self._slice(old, lo, self.full), self._slice(self.buf, 0, hi - self.full)
       out = {k: (torch.cat([a[k], b[k]]) if torch.is_tensor(v) else v) for k, v in old.items()}
       self.start = hi - self.full
@@ -90,11 +95,20 @@ class RampupIterator:
     return out
 
   def state(self):
-    s = self.inner.state() if hasattr(self.inner, "state") else {}
-    return {"inner": s, "cur": self.cur, "consumed": self.consumed, "start": self.start, "active": self.active}
+    """With a partly used buffer the wrapped iterator is recorded as it was before that buffer was read, so that a resumed
+    run reads the same buffer again and continues at row `start` of it."""
+    held = self.buf is not None and (self.active or self.start > 0)
+    if held and self._before_buf is not None:
+      inner = self._before_buf
+    else:
+      inner = self.inner.state() if hasattr(self.inner, "state") else {}
+    return {"inner": inner, "cur": self.cur, "consumed": self.consumed, "start": self.start if held else 0, "active": self.active,
+            "held": held}
 
   def load_state(self, s):
     if hasattr(self.inner, "load_state"):
       self.inner.load_state(s.get("inner", {}))
-    self.cur, self.consumed, self.start, self.active = s["cur"], s["consumed"], 0, s["active"]
-    self.buf = None
+    self.cur, self.consumed, self.active = s["cur"], s["consumed"], s["active"]
+    self.buf, self.start = None, 0
+    if s.get("held"):
+      self.buf, self.start = self._pull(), int(s.get("start", 0))

@@ -48,7 +48,7 @@ def test_tree_layout_matches_reference_names_and_shapes(tmp_path):
   assert shape("params.params.decoder.logits_dense.kernel") == [D, V]
   assert shape("params.params.decoder.decoder_norm.scale") == [D]
   assert shape("opt_state.0.mu.params.decoder.layers.mlp.wi_0.kernel") == [D, L, F]
-  assert int(zarr3.read_array(os.path.join(items, "step"))) == 0
+  assert int(zarr3.read_array(os.path.join(items, "step"))) == 1     # steps completed, like TrainState.step after step 0
   # the stored query kernel of layer 1 is the transpose of the internal [out, in] matrix
   q = zarr3.read_array(os.path.join(items, "params.params.decoder.layers.self_attention.query.kernel"))
   internal = eng.store.params["layers_1/self_attention/query/kernel"].data

@@ -200,3 +200,58 @@ def test_decode_wraps_prompt_with_chat_template(monkeypatch):
                                   "max_prefill_predict_length=16", "per_device_batch_size=1", "chat_template=[{{ messages[0]['content'] }}]>"])
   dec.decode(cfg)
   assert seen and seen[0] == "[hi]>"
+
+
+def _drain(it, n):
+  return [next(it)["inputs"].numpy().copy() for _ in range(n)]
+
+
+def test_resume_is_sample_exact_inside_a_packing_window_and_inside_a_token_file(tmp_path):
+  """The reader runs up to a packing window ahead of what was delivered, and a .npy file is one example of many rows:
+  the saved position must be that of the last delivered row in both cases."""
+  f = tmp_path / "d.jsonl"
+  with open(f, "w") as fh:
+    for i in range(300):
+      fh.write(json.dumps({"text": f"doc {i} " + "y" * (3 + (i * 7) % 23)}) + "\n")
+  base = ["dataset_type=hf", f"hf_train_files={f}", "per_device_batch_size=2", "max_target_length=32", "vocab_size=300", "num_epoch=2"]
+  for extra in (["packing=true"], ["packing=true", "grain_packing_type=concat_then_split"], ["packing=false"]):
+    c = tiny_config("llama3-8b", base + extra, num_devices=2)
+    for rank in (0, 1):
+      ref = _drain(FileDataIterator(c, rank, 2), 9)
+      it = FileDataIterator(c, rank, 2)
+      _drain(it, 4)
+      st = json.loads(json.dumps(it.state()))
+      it2 = FileDataIterator(c, rank, 2)
+      it2.load_state(st)
+      got = _drain(it2, 5)
+      assert all(np.array_equal(a, b) for a, b in zip(got, ref[4:])), (extra, rank)
+  npy = tmp_path / "t.npy"
+  np.save(npy, (np.arange(33 * 10 + 5) % 250).astype(np.int32))
+  c = tiny_config("llama3-8b", ["dataset_type=olmo_grain", f"grain_train_files={npy}", "per_device_batch_size=2", "max_target_length=32",
+                               "vocab_size=300", "packing=false", "num_epoch=1"], num_devices=1)
+  ref = _drain(FileDataIterator(c), 4)
+  it = FileDataIterator(c)
+  _drain(it, 2)
+  it2 = FileDataIterator(c)
+  it2.load_state(it.state())
+  assert all(np.array_equal(a, b) for a, b in zip(_drain(it2, 2), ref[2:]))
+
+
+def test_rampup_resume_keeps_the_partially_used_buffer(tmp_path):
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  f = tmp_path / "d.jsonl"
+  with open(f, "w") as fh:
+    for i in range(400):
+      fh.write(json.dumps({"text": f"doc {i} " + "z" * (i % 11)}) + "\n")
+  c = tiny_config("llama3-8b", ["dataset_type=hf", f"hf_train_files={f}", "per_device_batch_size=8", "max_target_length=16", "vocab_size=300",
+                               "packing=false", "enable_rampup_batch_size=true", "per_device_batch_size_start=2",
+                               "per_device_batch_size_increment=3", "global_rampup_samples=20"], num_devices=1)
+  ref = _drain(create_data_iterator(c), 12)
+  for stop in (1, 3, 7, 9):
+    it = create_data_iterator(c)
+    _drain(it, stop)
+    st = json.loads(json.dumps(it.state()))
+    it2 = create_data_iterator(c)
+    it2.load_state(st)
+    got = _drain(it2, 12 - stop)
+    assert all(a.shape == b.shape and np.array_equal(a, b) for a, b in zip(got, ref[stop:])), stop

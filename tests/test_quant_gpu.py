@@ -97,7 +97,6 @@ def test_delayed_scaling_uses_history_maximum():
     Q.set_delayed_scaling(0)
 
 
-@pytest.mark.skip(reason="written without a GPU at hand: run once on a B200, then remove this mark")
 @pytest.mark.gpu
 def test_int8_products_on_gpu_match_the_definition():
   """quantization=int8 on the GPU (integer product through the library) against the float emulation of the same integers."""

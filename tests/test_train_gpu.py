@@ -38,7 +38,6 @@ def test_graft_smoke():
   g.smoke()
 
 
-@pytest.mark.skip(reason="written without a GPU at hand: run once on a B200, then remove this mark")
 @pytest.mark.parametrize("model,extra", [
     ("qwen3-next-80b-a3b", ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=256", "gdn_key_head_dim=64",
                             "gdn_value_head_dim=64", "gdn_num_key_heads=2", "gdn_num_value_heads=4", "gdn_chunk_size=64"]),
