@@ -36,15 +36,12 @@ def main():
   ap.add_argument("--dim", type=int, default=128)
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--small", action="store_true")
-  ap.add_argument("--fwd-variant", type=int, default=0, help="tuning: 1 = one CTA per SM, 2 = two CTAs per SM (0 = library default)")
   ap.add_argument("--no-lib", action="store_true")
   a = ap.parse_args()
   if a.small:
     a.batch, a.seq, a.hq, a.hkv, a.iters = 2, 4096, 32, 8, 3     # 160 MB of q, k, v, out: larger than L2, small enough to profile
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
-  if a.fwd_variant:
-    E.flash_fwd_set_variant(a.fwd_variant)
   B, S, Hq, Hkv, D = a.batch, a.seq, a.hq, a.hkv, a.dim
   qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
   q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
@@ -54,7 +51,7 @@ def main():
   dqkv = torch.empty_like(qkv)
   dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
   fwd_flops = 4.0 * B * S * S * Hq * D / 2
-  ms_f = timeit(lambda: E.flash_fwd(q, k, v, out, lse, None, 1.0, 0), a.iters)
+  ms_f = timeit(lambda: E.flash_fwd(q, k, v, out, lse, None, None, None, None, None, 1.0, 0.0, True, 0, 0, 0), a.iters)
   ms_b = timeit(lambda: E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, None, 1.0, 0), a.iters)
   row = {"B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9, "bwd_ms": ms_b,
          "bwd_tflops": 2.5 * fwd_flops / ms_b / 1e9, "kernel_status": E.kernel_status(True)}

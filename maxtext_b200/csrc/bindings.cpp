@@ -10,8 +10,9 @@ extern "C" {
 int mt_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn, int b_mn,
                  int out_f32, int accumulate, int* status, int num_sms, cudaStream_t stream);
 int mt_rmsnorm_fwd(const void* x, const void* scale, float eps, float offset, void* y, float* rstd, int rows, int D, cudaStream_t st);
-int mt_rmsnorm_bwd(const void* dy, const void* x, const void* scale, const float* rstd, float offset, void* dx, float* dscale, int rows,
-                   int D, int sms, cudaStream_t st);
+int mt_rmsnorm_bwd(const void* dy, const void* x, const void* scale, const float* rstd, float offset, void* dx, float* dscale,
+                   float* partial, int rows, int D, int sms, cudaStream_t st);
+int mt_rmsnorm_bwd_partial_rows(int rows, int D, int sms);
 int mt_rope(void* x, const int* pos, const float* inv_ts, long tokens, int heads, int dh, int n_rot, int rot_dim, int interleaved,
             int inverse, cudaStream_t st);
 int mt_gated_act_fwd(const void* gu, void* out, long rows, int F, int code, int sms, cudaStream_t st);
@@ -191,9 +192,12 @@ void rmsnorm_bwd(const torch::Tensor& dy, const torch::Tensor& x, const c10::opt
                  double offset, torch::Tensor& dx, const c10::optional<torch::Tensor>& dscale) {
   TORCH_CHECK(x.is_contiguous() && dy.is_contiguous() && dx.is_contiguous());
   c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor partial;
+  if (dscale) partial = torch::empty({mt_rmsnorm_bwd_partial_rows((int)x.size(0), (int)x.size(1), num_sms()), x.size(1)},
+                                     torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
   check(mt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), scale ? scale->data_ptr() : nullptr, rstd.data_ptr<float>(), (float)offset,
-                       dx.data_ptr(), dscale ? dscale->data_ptr<float>() : nullptr, (int)x.size(0), (int)x.size(1), num_sms(),
-                       cur_stream()),
+                       dx.data_ptr(), dscale ? dscale->data_ptr<float>() : nullptr, dscale ? partial.data_ptr<float>() : nullptr,
+                       (int)x.size(0), (int)x.size(1), num_sms(), cur_stream()),
         "mt_rmsnorm_bwd");
 }
 

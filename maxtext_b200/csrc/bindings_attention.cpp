@@ -5,8 +5,12 @@
 #include <cuda_runtime.h>
 
 extern "C" {
-int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* seg, int B, int S, int Hq, int Hkv, int D,
-                 long ldq, long ldk, long ldv, long ldo, float scale, int window, int* status, cudaStream_t st);
+int mt_flash_fwd_supported(int Dqk, int Dv);
+long mt_flash_fwd_tile_ints(int B, int Sq, int Skv, int Dqk);
+int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* seg_q, const int* seg_k, const int* pos_q,
+                 const int* pos_k, int* tiles, const float* sinks, int B, int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, long ldq, long bsq,
+                 long ldk, long bsk, long ldv, long bsv, long ldo, long bso, float scale, float softcap, int causal, int window, int chunk,
+                 int q_off, int* status, cudaStream_t st);
 int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, void* dq,
                  void* dk, void* dv, const int* seg, int B, int S, int Hq, int Hkv, int D, long ldq, long ldk, long ldv, long lddq,
                  long lddk, long lddv, float scale, int window, int* status, cudaStream_t st);
@@ -16,7 +20,6 @@ extern "C" int mt_decode_attention(const void* q, const void* k_cache, const voi
                                    int max_len, int Hq, int Hkv, int D, int window, float scale, float soft_cap, int splits, float* part,
                                    void* out, cudaStream_t st);
 
-extern "C" int mt_flash_fwd_set_variant(int v);
 
 int* mt_status_ptr();          // defined in bindings.cpp
 void mt_count_launches(int n); // defined in bindings.cpp
@@ -38,16 +41,47 @@ bool flash_supported(const torch::Tensor& q, const torch::Tensor& k, const torch
   return true;
 }
 
+// [B,S,H,D] view usable as a {H*D, S, B} TMA tensor: unit inner stride, heads adjacent, 16-byte aligned row / batch strides
+bool tma_view(const torch::Tensor& t) {
+  return t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(1) % 8 == 0 && t.stride(0) % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0 && t.scalar_type() == torch::kBFloat16;
+}
+
+// forward-only shape check: q [B,Sq,Hq,Dqk], k [B,Skv,Hkv,Dqk], v [B,Skv,Hkv,Dv]; any Sq / Skv
+bool flash_fwd_supported(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v) {
+  if (!q.is_cuda() || !tma_view(q) || !tma_view(k) || !tma_view(v)) return false;
+  if (!mt_flash_fwd_supported((int)q.size(3), (int)v.size(3)) || k.size(3) != q.size(3)) return false;
+  if (k.size(0) != q.size(0) || v.size(0) != q.size(0) || k.size(1) != v.size(1)) return false;
+  return k.size(2) == v.size(2) && q.size(2) % k.size(2) == 0;
+}
+
+const int* opt_int(const c10::optional<torch::Tensor>& t, int64_t numel, const char* what) {
+  if (!t) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == torch::kInt32 && t->numel() == numel, what, ": int32 contiguous tensor of ",
+              numel, " elements expected");
+  return t->data_ptr<int>();
+}
+
 void flash_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, torch::Tensor& out, torch::Tensor& lse,
-               const c10::optional<torch::Tensor>& seg, double scale, int64_t window) {
-  TORCH_CHECK(flash_supported(q, k, v) && token_major(out) && lse.is_contiguous() && lse.scalar_type() == torch::kFloat32);
-  if (seg) TORCH_CHECK(seg->is_contiguous() && seg->scalar_type() == torch::kInt32);
+               const c10::optional<torch::Tensor>& seg_q, const c10::optional<torch::Tensor>& seg_k, const c10::optional<torch::Tensor>& pos_q,
+               const c10::optional<torch::Tensor>& pos_k, const c10::optional<torch::Tensor>& sinks, double scale, double softcap, bool causal,
+               int64_t window, int64_t chunk, int64_t q_off) {
+  TORCH_CHECK(flash_fwd_supported(q, k, v) && tma_view(out) && lse.is_contiguous() && lse.scalar_type() == torch::kFloat32);
+  const int B = (int)q.size(0), Sq = (int)q.size(1), Skv = (int)k.size(1), Hq = (int)q.size(2);
+  TORCH_CHECK(out.size(0) == B && out.size(1) == Sq && out.size(2) == Hq && out.size(3) == v.size(3) && lse.numel() == (int64_t)B * Hq * Sq);
+  TORCH_CHECK(bool(seg_q) == bool(seg_k) && bool(pos_q) == bool(pos_k), "segment ids / positions must be given for queries and keys together");
+  if (sinks) TORCH_CHECK(sinks->is_cuda() && sinks->is_contiguous() && sinks->scalar_type() == torch::kFloat32 && sinks->numel() == Hq);
   c10::cuda::CUDAGuard guard(q.device());
-  int rc = mt_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), seg ? seg->data_ptr<int>() : nullptr,
-                        (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)k.size(2), (int)q.size(3), q.stride(1), k.stride(1),
-                        v.stride(1), out.stride(1), (float)scale, (int)window, mt_status_ptr(), at::cuda::getCurrentCUDAStream().stream());
+  torch::Tensor tiles;
+  if (pos_q) tiles = torch::empty({mt_flash_fwd_tile_ints(B, Sq, Skv, (int)q.size(3))}, torch::dtype(torch::kInt32).device(q.device()));
+  int rc = mt_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), opt_int(seg_q, (int64_t)B * Sq, "seg_q"),
+                        opt_int(seg_k, (int64_t)B * Skv, "seg_k"), opt_int(pos_q, (int64_t)B * Sq, "pos_q"), opt_int(pos_k, (int64_t)B * Skv, "pos_k"),
+                        pos_q ? tiles.data_ptr<int>() : nullptr, sinks ? sinks->data_ptr<float>() : nullptr, B, Sq, Skv, Hq, (int)k.size(2),
+                        (int)q.size(3), (int)v.size(3), q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+                        out.stride(1), out.stride(0), (float)scale, (float)softcap, causal ? 1 : 0, (int)window, (int)chunk, (int)q_off,
+                        mt_status_ptr(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "mt_flash_fwd failed with code ", rc);
-  mt_count_launches(1);
+  mt_count_launches(pos_q ? 3 : 1);
 }
 
 void flash_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
@@ -88,8 +122,8 @@ void decode_attention(const torch::Tensor& q, const torch::Tensor& k_cache, cons
 
 void register_attention(pybind11::module_& m) {
   m.def("decode_attention", &decode_attention);
-  m.def("flash_fwd_set_variant", [](int64_t v) { TORCH_CHECK(mt_flash_fwd_set_variant((int)v) == 0, "variant must be 1 or 2"); });
   m.def("flash_supported", &flash_supported);
+  m.def("flash_fwd_supported", &flash_fwd_supported);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

@@ -92,11 +92,13 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
 
 // ------------------------------------------------------------------------------------------------ RMSNorm backward
 // dx = rstd * (g - xhat * mean(g * xhat)), g = dy * (scale + offset);  dscale += sum_rows dy * xhat.
-// Blocks stride over rows and keep per-column dscale partials in registers; one fp32 atomicAdd per column per block.
+// Blocks stride over rows and keep per-column dscale partials in registers; each (block, row slot) writes its partial row
+// into `partial`, and rms_dscale_reduce_kernel adds the rows up in index order: no atomics, so the result is bitwise
+// reproducible.
 template <int TPR, int VPT>
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ scale, const float* __restrict__ rstd_in, float offset,
-                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dscale, int rows, int D) {
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int D) {
   __shared__ float red[8];
   const int rows_per_block = blockDim.x / TPR;
   const int r_in_block = threadIdx.x / TPR;
@@ -153,16 +155,33 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
       }
     }
   }
-  if (dscale) {
+  if (partial) {
+    float* prow = partial + ((long)blockIdx.x * rows_per_block + r_in_block) * D;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int col = (i * TPR + tid) * 8;
       if (col < D) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) atomicAdd(dscale + col + e, ds[i][e]);
+        *reinterpret_cast<float4*>(prow + col) = make_float4(ds[i][0], ds[i][1], ds[i][2], ds[i][3]);
+        *reinterpret_cast<float4*>(prow + col + 4) = make_float4(ds[i][4], ds[i][5], ds[i][6], ds[i][7]);
       }
     }
   }
+}
+
+// dscale[c] += sum over partial rows (fixed order); four independent accumulators keep the loads in flight
+__global__ void rms_dscale_reduce_kernel(const float* __restrict__ partial, int nrows, int D, float* __restrict__ dscale) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int r = 0;
+  for (; r + 3 < nrows; r += 4) {
+    a0 += partial[(long)r * D + c];
+    a1 += partial[(long)(r + 1) * D + c];
+    a2 += partial[(long)(r + 2) * D + c];
+    a3 += partial[(long)(r + 3) * D + c];
+  }
+  for (; r < nrows; ++r) a0 += partial[(long)r * D + c];
+  dscale[c] += (a0 + a1) + (a2 + a3);
 }
 
 // ------------------------------------------------------------------------------------------------ rotary embedding
@@ -294,27 +313,41 @@ extern "C" int mt_rmsnorm_fwd(const void* x, const void* scale, float eps, float
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-template <int TPR>
-static void launch_rms_bwd(const void* dy, const void* x, const void* scale, const float* rstd, float offset, void* dx, float* dscale,
-                           int rows, int D, int sms, cudaStream_t st) {
-  const int vpt = (D / 8 + TPR - 1) / TPR;
-  const int threads = 256;
-  const int rpb = threads / TPR;
+static int rms_bwd_grid(int rows, int tpr, int sms) {
+  const int rpb = 256 / tpr;
   long groups = ((long)rows + rpb - 1) / rpb;
   int grid = (int)(groups < (long)sms * 4 ? groups : (long)sms * 4);
-  if (grid < 1) grid = 1;
-#define L(V) rmsnorm_bwd_kernel<TPR, V><<<grid, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,                 \
-                                                                  (const __nv_bfloat16*)scale, rstd, offset, (__nv_bfloat16*)dx,    \
-                                                                  dscale, rows, D)
-  if (vpt <= 1) L(1); else if (vpt <= 2) L(2); else if (vpt <= 4) L(4); else L(8);
-#undef L
+  return grid < 1 ? 1 : grid;
 }
 
+template <int TPR>
+static void launch_rms_bwd(const void* dy, const void* x, const void* scale, const float* rstd, float offset, void* dx, float* dscale,
+                           float* partial, int rows, int D, int sms, cudaStream_t st) {
+  const int vpt = (D / 8 + TPR - 1) / TPR;
+  const int threads = 256;
+  const int grid = rms_bwd_grid(rows, TPR, sms);
+  float* part = dscale ? partial : nullptr;
+#define L(V) rmsnorm_bwd_kernel<TPR, V><<<grid, threads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,                 \
+                                                                  (const __nv_bfloat16*)scale, rstd, offset, (__nv_bfloat16*)dx,    \
+                                                                  part, rows, D)
+  if (vpt <= 1) L(1); else if (vpt <= 2) L(2); else if (vpt <= 4) L(4); else L(8);
+#undef L
+  if (part) rms_dscale_reduce_kernel<<<(D + 127) / 128, 128, 0, st>>>(part, grid * (threads / TPR), D, dscale);
+}
+
+// number of fp32 rows of length D that `partial` must hold for mt_rmsnorm_bwd with a scale gradient
+extern "C" int mt_rmsnorm_bwd_partial_rows(int rows, int D, int sms) {
+  const int tpr = D <= 512 ? 32 : 256;
+  return rms_bwd_grid(rows, tpr, sms) * (256 / tpr);
+}
+
+// `partial`: scratch of mt_rmsnorm_bwd_partial_rows(rows, D, sms) x D floats (needed only when dscale is given); rows of a
+// block that saw no input row are written as zeros by the kernel, so the scratch needs no clearing.
 extern "C" int mt_rmsnorm_bwd(const void* dy, const void* x, const void* scale, const float* rstd, float offset, void* dx,
-                              float* dscale, int rows, int D, int sms, cudaStream_t st) {
-  if (D % 8 || D > 8 * 256 * 8) return -1;
-  if (D <= 512) launch_rms_bwd<32>(dy, x, scale, rstd, offset, dx, dscale, rows, D, sms, st);
-  else launch_rms_bwd<256>(dy, x, scale, rstd, offset, dx, dscale, rows, D, sms, st);
+                              float* dscale, float* partial, int rows, int D, int sms, cudaStream_t st) {
+  if (D % 8 || D > 8 * 256 * 8 || (dscale && !partial)) return -1;
+  if (D <= 512) launch_rms_bwd<32>(dy, x, scale, rstd, offset, dx, dscale, partial, rows, D, sms, st);
+  else launch_rms_bwd<256>(dy, x, scale, rstd, offset, dx, dscale, partial, rows, D, sms, st);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

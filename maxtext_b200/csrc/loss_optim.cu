@@ -50,20 +50,20 @@ __global__ void __launch_bounds__(1024) xent_kernel(__nv_bfloat16* __restrict__ 
     const float nm = fmaxf(m, lm);
     float acc = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc += __expf(f[e] - nm);
-    s = s * __expf(m - nm) + acc;
+    for (int e = 0; e < 8; ++e) acc += expf(f[e] - nm);
+    s = s * expf(m - nm) + acc;
     m = nm;
   }
   for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {   // tail when V % 8 != 0
     const float f = __bfloat162float(lrow[i]);
     const float nm = fmaxf(m, f);
-    s = s * __expf(m - nm) + __expf(f - nm);
+    s = s * expf(m - nm) + expf(f - nm);
     m = nm;
   }
   // block reduce (max, sum)
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   float wm = warp_max(m);
-  float ws = warp_sum2(s * ((m == -INFINITY) ? 0.f : __expf(m - wm)));
+  float ws = warp_sum2(s * ((m == -INFINITY) ? 0.f : expf(m - wm)));
   if (l == 0) { s_m[w] = wm; s_s[w] = ws; }
   __syncthreads();
   if (w == 0) {
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(1024) xent_kernel(__nv_bfloat16* __restrict__ 
     float mm = (l < nw) ? s_m[l] : -INFINITY;
     float ss = (l < nw) ? s_s[l] : 0.f;
     const float gm = warp_max(mm);
-    const float gs = warp_sum2(ss * ((mm == -INFINITY) ? 0.f : __expf(mm - gm)));
+    const float gs = warp_sum2(ss * ((mm == -INFINITY) ? 0.f : expf(mm - gm)));
     if (l == 0) {
       const float lse = gm + logf(gs);
       s_lse = lse;
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(1024) xent_kernel(__nv_bfloat16* __restrict__ 
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float2 t = __bfloat1622float2(p.v[e]);
-      float a = coef * __expf(t.x - lse), b = coef * __expf(t.y - lse);
+      float a = coef * expf(t.x - lse), b = coef * expf(t.y - lse);
       const int c0 = i * 8 + 2 * e;
       if (c0 == tgt) a -= wgt;
       if (c0 + 1 == tgt) b -= wgt;
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(1024) xent_kernel(__nv_bfloat16* __restrict__ 
     *reinterpret_cast<bf16x8*>(lrow + i * 8) = o;
   }
   for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
-    float a = coef * __expf(__bfloat162float(lrow[i]) - lse);
+    float a = coef * expf(__bfloat162float(lrow[i]) - lse);
     if (i == tgt) a -= wgt;
     lrow[i] = __float2bfloat16_rn(a);
   }

@@ -23,11 +23,14 @@ extern "C" {
 //   x      device pointer to n floats (16-byte aligned), out  device pointer to one float.
 // Returns 0 on success; a negative code otherwise (mt_sumsq_noalloc_strerror explains it):
 //   -1 bad argument, -2 n exceeds MT_SUMSQ_NOALLOC_MAX_ELEMS, -3 the device needs more partials than the built-in
-//   scratch holds, -4 the scratch address could not be obtained, -5 kernel launch failed.
+//   scratch holds, -4 the scratch address could not be obtained, -5 kernel launch failed, -6 the current device's
+//   ordinal is 64 or more (set-up state is kept for ordinals 0..63).
 // It calls no cudaMalloc / cudaFree and no allocating library routine.
 //
 // The first call on each device looks up the device address of the scratch array (cudaGetSymbolAddress with that
-// device current) and caches it. Make that first call before starting any stream capture on the device.
+// device current) and caches it. Make that first call before starting any stream capture on the device. The set-up
+// is guarded by a per-device lock and published with release / acquire ordering, so host threads may make their
+// first calls at the same time; the lock is taken only until the set-up has succeeded once.
 // All calls on a device share the one scratch array. Nothing in it has to start at zero (stage 1 overwrites every
 // slot it later reads), but two calls that overlap on the GPU (different streams, no ordering between them) race
 // on it and return garbage: order them on one stream or with events.

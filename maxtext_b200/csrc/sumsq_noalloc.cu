@@ -4,6 +4,8 @@
 // mt_sumsq in loss_optim.cu, so both entry points return the same value on the same device.
 #include "no_alloc.h"
 #include <stdint.h>
+#include <atomic>
+#include <mutex>
 
 extern "C" int mt_sumsq_num_partials(long n, int sms);   // loss_optim.cu: grid size of stage 1
 
@@ -54,8 +56,16 @@ __global__ void __launch_bounds__(NA_THREADS) na_stage2(const float* __restrict_
 }
 
 constexpr int NA_MAX_DEVICES = 64;
-float* g_scratch_ptr[NA_MAX_DEVICES] = {nullptr};
-int g_sm_count[NA_MAX_DEVICES] = {0};
+
+// Per-device set-up result, published once: `ready` is stored with release order after the other two fields, and
+// read with acquire order, so a host thread that sees ready != 0 also sees the pointer and the SM count.
+struct NaDevice {
+  std::atomic<int> ready{0};
+  float* scratch = nullptr;
+  int sms = 0;
+  std::mutex init;
+};
+NaDevice g_dev[NA_MAX_DEVICES];
 
 }  // namespace
 
@@ -67,6 +77,7 @@ extern "C" const char* mt_sumsq_noalloc_strerror(int code) {
     case -3: return "this device needs more stage-1 partials than the built-in scratch (MT_SUMSQ_NOALLOC_MAX_PARTIALS) holds";
     case -4: return "could not obtain the device address of the built-in scratch (cudaGetSymbolAddress failed)";
     case -5: return "kernel launch failed";
+    case -6: return "device ordinal beyond the 64 devices this entry point keeps set-up state for (or no current device)";
     default: return "unknown error code";
   }
 }
@@ -75,21 +86,34 @@ extern "C" int mt_sumsq_noalloc(const float* x, long long n, float* out, cudaStr
   if (!x || !out || n < 0 || (reinterpret_cast<uintptr_t>(x) & 15u)) return -1;
   if (n > MT_SUMSQ_NOALLOC_MAX_ELEMS) return -2;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) return -4;
-  if (!g_scratch_ptr[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) return -6;
+  NaDevice& d = g_dev[dev];
+  if (!d.ready.load(std::memory_order_acquire)) {
     // one-time set-up for this device (it is current): resolve the device address of the scratch symbol
-    float* ptr = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_partials) != cudaSuccess || !ptr) return -4;
-    int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -4;
-    g_sm_count[dev] = sms;
-    g_scratch_ptr[dev] = ptr;
+    std::lock_guard<std::mutex> lock(d.init);
+    if (!d.ready.load(std::memory_order_relaxed)) {
+      float* ptr = nullptr;
+      if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_partials) != cudaSuccess || !ptr) return -4;
+      int sms = 0;
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return -4;
+      d.sms = sms;
+      d.scratch = ptr;
+      d.ready.store(1, std::memory_order_release);
+    }
   }
   if (n == 0) return 0;
-  const int parts = mt_sumsq_num_partials((long)n, g_sm_count[dev]);
+  const int parts = mt_sumsq_num_partials((long)n, d.sms);
   if (parts > MT_SUMSQ_NOALLOC_MAX_PARTIALS) return -3;
-  float* scratch = g_scratch_ptr[dev];
-  na_stage1<<<parts, NA_THREADS, 0, stream>>>(x, n, scratch);
-  na_stage2<<<1, NA_THREADS, 0, stream>>>(scratch, parts, out);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  float* scratch = d.scratch;
+  // each launch's own return code is read (cudaLaunchKernel), so an earlier, unrelated error of the caller is neither
+  // reported as ours nor cleared
+  long long n_arg = n;
+  int parts_arg = parts;
+  const float* x_arg = x;
+  void* a1[] = {(void*)&x_arg, (void*)&n_arg, (void*)&scratch};
+  if (cudaLaunchKernel((const void*)na_stage1, dim3(parts), dim3(NA_THREADS), a1, 0, stream) != cudaSuccess) return -5;
+  const float* sc = scratch;
+  void* a2[] = {(void*)&sc, (void*)&parts_arg, (void*)&out};
+  if (cudaLaunchKernel((const void*)na_stage2, dim3(1), dim3(NA_THREADS), a2, 0, stream) != cudaSuccess) return -5;
+  return 0;
 }

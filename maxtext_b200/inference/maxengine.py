@@ -52,6 +52,10 @@ class MaxEngine:
     self.model = model or Transformer(c, mesh, self.device)
     self.max_len = int(c.max_target_length)
     self.max_prefill = int(c.max_prefill_predict_length)
+    if self.max_prefill >= int(c.max_target_length):
+      # src/maxtext/inference/offline_engine.py:950 makes the same demand
+      raise ValueError(f"max_prefill_predict_length ({self.max_prefill}) must be smaller than max_target_length ({int(c.max_target_length)}): "
+                       "a full prompt leaves no room to generate")
     self.generator = torch.Generator(device=self.device)
     self.generator.manual_seed(int(c.init_weights_seed))
     self._graphs: dict = {}          # id(state) -> (CUDAGraph, static result tensors) when cuda_graphs is on
@@ -132,6 +136,13 @@ class MaxEngine:
       for cch in per_layer:
         cch.bind(slot_ids, lengths)
 
+  def _check_length(self, n: int, what: str):
+    """A prompt must leave room for at least one generated token: a prefix of max_target_length tokens would make the next
+    decode step write its key / value one row past the end of the slot's cache."""
+    n = int(n)
+    if n < 1 or n >= self.max_len:
+      raise ValueError(f"{what}: length {n} is outside [1, max_target_length - 1 = {self.max_len - 1}]")
+
   def _sample(self, logits):
     c = self.config
     return inference_utils.sampling(logits, c.decode_sampling_strategy, int(c.decode_sampling_top_k), float(c.decode_sampling_nucleus_p),
@@ -143,6 +154,9 @@ class MaxEngine:
     """padded_tokens [P] (right padded); only the first `true_length` enter the cache. `images` [N, 3, H, W] with
     `image_mask` [P] (True at the soft-token positions of the prompt) makes the prompt multimodal."""
     dev = self.device
+    self._check_length(true_length, "prefill")
+    if int(true_length) > int(padded_tokens.numel()):
+      raise ValueError(f"prefill: true_length {true_length} exceeds the {int(padded_tokens.numel())} tokens given")
     toks = padded_tokens[:true_length].to(dev).long()[None]
     caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, true_length), dev)
     self._bind(caches, torch.zeros(1, dtype=torch.long, device=dev), torch.zeros(1, dtype=torch.long, device=dev))
@@ -175,6 +189,8 @@ class MaxEngine:
     Layers with a recurrent state (gated delta networks) cannot be packed this way; such models prefill one by one."""
     dev = self.device
     lens = [int(p.numel()) for p in prompts]
+    for n in lens:
+      self._check_length(n, "prefill_concat")
     total = sum(lens)
     packable = total <= self.max_len and not any(b.plan.attention == "gdn" for l in self.model.layers for b in l.blocks)
     if not packable or len(prompts) == 1:
@@ -212,6 +228,7 @@ class MaxEngine:
     dev = self.device
     chunk = int(chunk or self.config.prefill_chunk_size)
     n = int(tokens.numel())
+    self._check_length(n, "prefill_chunked")
     caches = kvcache.make_caches(self.model, 1, max(self.max_prefill, n), dev)
     slot = torch.zeros(1, dtype=torch.long, device=dev)
     logits = None
@@ -227,6 +244,9 @@ class MaxEngine:
   @torch.no_grad()
   def insert(self, prefix: Prefix, state: DecodeState, slot: int) -> DecodeState:
     n = prefix.length
+    self._check_length(n, "insert")
+    if not 0 <= int(slot) < int(state.tokens.shape[0]):
+      raise ValueError(f"insert: slot {slot} is outside [0, {int(state.tokens.shape[0])})")
     for dst_layer, src_layer in zip(state.caches, prefix.caches):
       for d, s in zip(dst_layer, src_layer):
         for name in ("k", "v", "ks", "vs", "latent", "k_rope"):

@@ -412,16 +412,15 @@ class Attention:
         m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window) | ctx.bidir
         out = ref.attention(q, k, v, m, 1.0, self.soft_cap).to(q.dtype)
       elif ctx.cache is None and self.chunk and S > self.chunk and ctx.cp_size == 1:
-        m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window, chunk=self.chunk)
-        out = ref.attention(q, k, v, m, 1.0, self.soft_cap)
+        out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window, chunk=self.chunk,
+                          sinks=self.sinks.leaf() if self.sinks is not None else None)
       elif ctx.cache is not None:
         out = ctx.cache.attend(q, k, v, ctx, window=self.window, soft_cap=self.soft_cap, sinks=self.sinks)
       elif ctx.cp_size > 1:
         from ..parallel.context_parallel import context_attention
         out = context_attention(q, k, v, ctx.positions, ctx.segment_ids, ctx, 1.0, self.soft_cap, self.window)
       elif self.sinks is not None:
-        m = ref.attention_mask(ctx.positions, ctx.positions, ctx.segment_ids, ctx.segment_ids, True, self.window)
-        out = ref.attention(q, k, v, m, 1.0, self.soft_cap, sinks=self.sinks.leaf())
+        out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window, sinks=self.sinks.leaf())
       else:
         out = F.attention(q, k, v, ctx.positions, ctx.segment_ids, 1.0, self.soft_cap, self.window)
     ctx.keep("context", out)

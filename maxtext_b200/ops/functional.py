@@ -21,6 +21,14 @@ _ATTN_IMPL = os.environ.get("MAXTEXT_B200_ATTN", "auto")
 
 
 # =============================================================================== GEMM
+_GEMM_FALLBACKS = 0
+
+
+def gemm_fallbacks() -> int:
+  """How many matrix products on a GPU went to the library because the tcgen05 kernels do not cover their shape."""
+  return _GEMM_FALLBACKS
+
+
 def _gemm_supported(M, N, K, a, b):
   return a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and M % 8 == 0 and K >= 16
 
@@ -43,8 +51,11 @@ def mm(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out: torch.Tensor |
     if _GEMM_IMPL == "tcgen05" and _gemm_supported(M, N, K, a, b) and E.gemm_supported(a, b, out, ta, tb):
       E.gemm(a, b, out, ta, tb, accumulate)
       return out
-    if _GEMM_IMPL == "tcgen05" and os.environ.get("MAXTEXT_B200_STRICT_GEMM"):
-      raise RuntimeError(f"tcgen05 GEMM does not cover M={M} N={N} K={K} {a.dtype}")
+    if _GEMM_IMPL == "tcgen05":
+      global _GEMM_FALLBACKS
+      _GEMM_FALLBACKS += 1
+      if os.environ.get("MAXTEXT_B200_STRICT_GEMM") == "1":
+        raise RuntimeError(f"tcgen05 GEMM does not cover M={M} N={N} K={K} {a.dtype} (strides {a.stride()}, {b.stride()})")
   opa, opb = (a.t() if ta else a), (b.t() if tb else b)
   if accumulate:
     if out.dtype == a.dtype:
@@ -328,32 +339,50 @@ def _flash_ok(q, k, v, soft_cap):
   return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == v.shape[-1] and q.shape[-1] in (64, 128) and not soft_cap
 
 
+def _i32(t):
+  return None if t is None else t.to(torch.int32).contiguous()
+
+
 def attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal=True, kv_positions=None,
-                  kv_segment_ids=None):
-  """Returns (out [B,Sq,Hq,Dv], lse [B,Hq,Sq] fp32). Strided q/k/v views are accepted."""
+                  kv_segment_ids=None, chunk=0, sinks=None):
+  """Returns (out [B,Sq,Hq,Dv], lse [B,Hq,Sq] fp32). Strided q/k/v views are accepted.
+
+  On a GPU this is the tcgen05 flash kernel for every mask form the models use: causal or not, sliding window, chunked
+  attention, segment ids, logit soft-cap, per-head sink logits, Dqk != Dv (MLA), any sequence length, and keys that are
+  a block of a longer sequence (`kv_positions` / `kv_segment_ids`, context parallelism). `positions` are only consulted
+  when the mask cannot be derived from token indices: with kv_positions, or chunked attention over packed rows."""
   if backend.use_cuda_kernels(q):
     E = backend.ext()
-    if hasattr(E, "flash_fwd") and _flash_ok(q, k, v, soft_cap) and kv_positions is None and causal \
-        and E.flash_supported(q, k, v):
+    if q.dtype == torch.bfloat16 and _ATTN_IMPL != "sdpa" and E.flash_fwd_supported(q, k, v):
       out = torch.empty(q.shape[0], q.shape[1], q.shape[2], v.shape[-1], dtype=q.dtype, device=q.device)
       lse = torch.empty(q.shape[0], q.shape[2], q.shape[1], dtype=torch.float32, device=q.device)
-      seg = segment_ids.to(torch.int32).contiguous() if segment_ids is not None else None
-      E.flash_fwd(q, k, v, out, lse, seg, float(scale), int(window))
+      seg_q = _i32(segment_ids)
+      seg_k = _i32(kv_segment_ids) if kv_segment_ids is not None else seg_q
+      if seg_q is None:
+        seg_k = None
+      by_arrays = kv_positions is not None or (chunk and segment_ids is not None)
+      pos_q = _i32(positions) if by_arrays else None
+      pos_k = _i32(kv_positions if kv_positions is not None else positions) if by_arrays else None
+      sk = sinks.detach().float().contiguous() if sinks is not None else None
+      E.flash_fwd(q, k, v, out, lse, seg_q, seg_k, pos_q, pos_k, sk, float(scale), float(soft_cap or 0.0), bool(causal), int(window or 0),
+                  int(chunk or 0), int(k.shape[1] - q.shape[1]) if not by_arrays else 0)
       return out, lse
   mask_args = dict(q_pos=positions, kv_pos=kv_positions if kv_positions is not None else positions, q_seg=segment_ids,
                    kv_seg=kv_segment_ids if kv_segment_ids is not None else segment_ids, causal=causal,
-                   sliding_window=window)
+                   sliding_window=window, chunk=chunk)
   if q.is_cuda:
-    if _ATTN_IMPL == "sdpa" and segment_ids is None and not window and not soft_cap and causal and kv_positions is None:
+    if _ATTN_IMPL == "sdpa" and segment_ids is None and not window and not soft_cap and causal and kv_positions is None and not chunk \
+        and sinks is None:
       # comparison arm only (library attention); the product path is the flash kernel above
       o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
                                                            is_causal=True, scale=scale, enable_gqa=q.shape[2] != k.shape[2])
       return o.transpose(1, 2).contiguous(), None
-    return _attention_chunked(q, k, v, mask_args, scale, soft_cap)
-  return _sdpa_reference(q, k, v, mask_args, scale, soft_cap)
+    return _attention_chunked(q, k, v, mask_args, scale, soft_cap, sinks=sinks)
+  m = ref.attention_mask(**mask_args)
+  return ref.attention(q, k, v, m, scale, soft_cap, sinks=sinks, return_lse=True)
 
 
-def _attention_chunked(q, k, v, mask_args, scale, soft_cap, chunk=1024):
+def _attention_chunked(q, k, v, mask_args, scale, soft_cap, chunk=1024, sinks=None):
   """Memory-bounded evaluation of the reference attention on GPU (query chunks)."""
   outs, lses = [], []
   Sq = q.shape[1]
@@ -362,23 +391,28 @@ def _attention_chunked(q, k, v, mask_args, scale, soft_cap, chunk=1024):
     ma["q_pos"] = mask_args["q_pos"][:, s:s + chunk]
     if ma.get("q_seg") is not None:
       ma["q_seg"] = mask_args["q_seg"][:, s:s + chunk]
-    o, l = ref.attention(q[:, s:s + chunk], k, v, ref.attention_mask(**ma), scale, soft_cap, return_lse=True)
+    o, l = ref.attention(q[:, s:s + chunk], k, v, ref.attention_mask(**ma), scale, soft_cap, sinks=sinks, return_lse=True)
     outs.append(o)
     lses.append(l)
   return torch.cat(outs, 1), torch.cat(lses, 2)
 
 
 def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal=True,
-                  kv_positions=None, kv_segment_ids=None):
+                  kv_positions=None, kv_segment_ids=None, chunk=0, sinks=None):
   """Gradients of attention given the forward's `out` and `lse`. With kv_positions the keys are a block of a longer
   (context-parallel) sequence: `out`/`lse` are then the merged global results and the returned dq/dk/dv are this
-  block's exact contributions."""
-  if backend.use_cuda_kernels(q) and kv_positions is None:
+  block's exact contributions. Returns the gradient of the sink logits (or None)."""
+  dsinks = None
+  if sinks is not None and lse is not None:
+    # d loss / d sink_h = -sum_{b,q} p_sink * delta, with p_sink = exp(sink - lse) and delta = rowsum(dO * O)
+    delta = (dout.float() * out.float()).sum(-1).permute(0, 2, 1)                 # [B, Hq, Sq]
+    dsinks = -(torch.exp(sinks.detach().float()[None, :, None] - lse) * delta).sum((0, 2)).to(sinks.dtype)
+  if backend.use_cuda_kernels(q) and kv_positions is None and not chunk:
     E = backend.ext()
-    if hasattr(E, "flash_bwd") and _flash_ok(q, k, v, soft_cap) and causal and E.flash_supported(q, k, v):
+    if hasattr(E, "flash_bwd") and _flash_ok(q, k, v, soft_cap) and causal and lse is not None and E.flash_supported(q, k, v):
       seg = segment_ids.to(torch.int32).contiguous() if segment_ids is not None else None
       E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, float(scale), int(window))
-      return
+      return dsinks
   kpos = kv_positions if kv_positions is not None else positions
   kseg = kv_segment_ids if kv_segment_ids is not None else segment_ids
   if lse is None:
@@ -391,7 +425,7 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
     dq.copy_(gq)
     dk.copy_(gk)
     dv.copy_(gv)
-    return
+    return dsinks
   # reference: recompute probabilities from lse, chunked over queries
   B, Sq, Hq, D = q.shape
   Hkv = k.shape[2]
@@ -399,12 +433,12 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
   kf, vf = k.float(), v.float()
   dkf = torch.zeros(B, k.shape[1], Hkv, D, dtype=torch.float32, device=q.device)
   dvf = torch.zeros(B, v.shape[1], Hkv, v.shape[-1], dtype=torch.float32, device=q.device)
-  chunk = 1024 if q.is_cuda else Sq
-  for s in range(0, Sq, chunk):
-    e = min(Sq, s + chunk)
+  step = 1024 if q.is_cuda else Sq
+  for s in range(0, Sq, step):
+    e = min(Sq, s + step)
     qf = q[:, s:e].float().reshape(B, e - s, Hkv, g, D)
     mask = ref.attention_mask(positions[:, s:e], kpos, segment_ids[:, s:e] if segment_ids is not None else None,
-                              kseg, causal, window)
+                              kseg, causal, window, chunk)
     raw = torch.einsum("bqhgd,bkhd->bhgqk", qf, kf) * scale
     if soft_cap and soft_cap > 0:
       t = torch.tanh(raw / soft_cap)
@@ -426,32 +460,37 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
     dkf += torch.einsum("bhgqk,bqhgd->bkhd", ds, qf)
   dk.copy_(dkf.to(dk.dtype))
   dv.copy_(dvf.to(dv.dtype))
+  return dsinks
 
 
 class _AttnFn(torch.autograd.Function):
   """Attention over separate q/k/v tensors (used when q/k need per-head norms or differ in width)."""
 
   @staticmethod
-  def forward(ctx, q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions=None, kv_segment_ids=None):
-    out, lse = attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)
-    ctx.save_for_backward(q, k, v, out, lse, positions, segment_ids, kv_positions, kv_segment_ids)
-    ctx.cfg = (scale, soft_cap, window, causal)
+  def forward(ctx, q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions=None, kv_segment_ids=None, chunk=0,
+              sinks=None):
+    out, lse = attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids, chunk, sinks)
+    ctx.save_for_backward(q, k, v, out, lse, positions, segment_ids, kv_positions, kv_segment_ids, sinks)
+    ctx.cfg = (scale, soft_cap, window, causal, chunk)
     return out
 
   @staticmethod
   def backward(ctx, dout):
-    q, k, v, out, lse, positions, segment_ids, kpos, kseg = ctx.saved_tensors
-    scale, soft_cap, window, causal = ctx.cfg
+    q, k, v, out, lse, positions, segment_ids, kpos, kseg, sinks = ctx.saved_tensors
+    scale, soft_cap, window, causal, chunk = ctx.cfg
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    attention_bwd(dout.contiguous(), q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal, kpos, kseg)
-    return dq, dk, dv, None, None, None, None, None, None, None, None
+    dsinks = attention_bwd(dout.contiguous(), q, k, v, out, lse, positions, segment_ids, scale, soft_cap, window, dq, dk, dv, causal, kpos,
+                           kseg, chunk, sinks)
+    return dq, dk, dv, None, None, None, None, None, None, None, None, None, dsinks
 
 
-def attention(q, k, v, positions, segment_ids, scale=1.0, soft_cap=0.0, window=0, causal=True, kv_positions=None, kv_segment_ids=None):
-  """kv_positions / kv_segment_ids describe keys that are not the queries' own tokens (context parallelism)."""
+def attention(q, k, v, positions, segment_ids, scale=1.0, soft_cap=0.0, window=0, causal=True, kv_positions=None, kv_segment_ids=None,
+              chunk=0, sinks=None):
+  """kv_positions / kv_segment_ids describe keys that are not the queries' own tokens (context parallelism); `chunk` restricts
+  attention to blocks of that many positions; `sinks` [Hq] are per-head logits that only enter the softmax denominator."""
   if not torch.is_grad_enabled():
-    return attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)[0]
-  return _AttnFn.apply(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids)
+    return attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids, chunk, sinks)[0]
+  return _AttnFn.apply(q, k, v, positions, segment_ids, scale, soft_cap, window, causal, kv_positions, kv_segment_ids, chunk, sinks)
 
 
 class _RopeFn(torch.autograd.Function):

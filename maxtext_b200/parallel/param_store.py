@@ -16,7 +16,7 @@ explicit and laid out for NVLink collectives:
 * fp32 master weights, AdamW moments and fp32 gradient shards are single contiguous arrays over all
   units, so the optimizer is one kernel launch over the local shard;
 * the compute-dtype copy of a unit is materialised into a small pool of gather buffers, prefetched
-  one unit ahead by `parallel.fsdp.FsdpSchedule`.
+  one unit ahead by the step schedule of `train.engine.TrainEngine`.
 
 Internal linear layout is `[out, in]`; the reference layout (`[in..., out...]`, layer axis stacked
 at `param_scan_axis`) is produced by `to_reference_tree` for checkpoints.
@@ -427,7 +427,7 @@ class ParamStore:
       self.compute_shard.copy_(self.master)
 
   # ------------------------------------------------------------------ gather / scatter (synchronous forms; the
-  # overlapped schedule lives in parallel.fsdp)
+  # overlapped schedule is driven by train.engine.TrainEngine through prefetch / release)
   def max_unit_numel(self) -> int:
     return max((u.numel for u in self.units.values() if u.group_size > 1), default=0)
 

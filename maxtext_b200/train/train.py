@@ -79,7 +79,7 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
   start_step = 0
   own_watcher = preemption is None
   preemption = preemption or elastic.PreemptionWatcher(_default_store())
-  injector = elastic.FaultInjector(rank=rank)
+  injector = elastic.FaultInjector(rank=rank, guard=elastic.peer_memory_guard(engine))
   heartbeat = None
   if c.elastic_enabled and _default_store() is not None:
     heartbeat = elastic.Heartbeat(_default_store(), rank, mesh.world if mesh is not None else 1,
@@ -129,6 +129,9 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
         metrics = stepper.train_step(batch)
         if is_cuda and (c.profile_cleanly or True):
           torch.cuda.synchronize()
+          # a bounded device wait that ran out left incomplete tiles or gradients behind: stop before this step is logged
+          # or checkpointed; the elastic supervisor treats the error as retryable
+          check_kernel_status(engine.device, rank)
       dt = time.perf_counter() - t0
       logger.record(step, metrics, dt)
       if ckpt is not None:
@@ -172,6 +175,20 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
     if own_watcher:
       preemption.close()
   return engine, logger.history
+
+
+def check_kernel_status(device, rank: int = 0, ext=None):
+  """Raises CommTimeoutError when any kernel of this process recorded a timed-out wait since the last check (the status
+  word is read and cleared). Called after the per-step synchronize, before logging and saving."""
+  from ..ops import backend
+  from ..parallel.symm import CommTimeoutError
+  E = ext if ext is not None else backend.ext()
+  if E is None:
+    return
+  st = int(E.kernel_status(True))
+  if st != 0:
+    what = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue / softmax", 4: "peer flag"}.get(st, "unknown")
+    raise CommTimeoutError(f"rank {rank} on {device}: a bounded device wait ran out (status {st}: {what}); the step's results are incomplete")
 
 
 def run_eval(config, engine, mesh) -> float:

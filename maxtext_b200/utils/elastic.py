@@ -22,6 +22,25 @@ class ScaleUpSignal(Exception):
   """Raised between steps when more ranks became available: the supervisor re-initialises with the larger world."""
 
 
+class FaultInjectionRefused(RuntimeError):
+  """An injected rank departure was refused because it is unsafe in the current set-up (not retryable)."""
+
+
+def peer_memory_guard(engine):
+  """For FaultInjector: a reason string when `engine` holds peer-mapped GPU memory, else ''."""
+  def guard():
+    dev = getattr(engine, "device", None)
+    if dev is None or getattr(dev, "type", "cpu") != "cuda":
+      return ""
+    store = getattr(engine, "store", None)
+    if store is not None and (getattr(store, "fused", False) or getattr(store, "rs_nvls", False) or getattr(store, "symm", None) is not None):
+      return "this rank's gradient / parameter buffers are symmetric memory mapped by its peers (fused communication is on)"
+    if os.environ.get("NCCL_NVLS_ENABLE", "") != "0":
+      return "NCCL may have bound this rank's buffers to an NVLS multicast object (set NCCL_NVLS_ENABLE=0)"
+    return ""
+  return guard
+
+
 class RankFailure(RuntimeError):
   """A peer stopped answering (heartbeat) or a collective / device wait gave up."""
 
@@ -215,9 +234,15 @@ class FaultInjector:
   Spec `"<kind>@<step>[:rank]"`, kinds: `raise` (RankFailure out of the step loop), `sigterm` (preemption notice to
   this process), `exit` (the rank leaves between steps, exit code 17), `stall` (stops heartbeats and sleeps).
   Reads MAXTEXT_B200_INJECT_FAULT when no spec is given. Nothing here touches a device.
+
+  `exit` and `stall` take a rank away while its peers keep running. They refuse to fire (FaultInjectionRefused) when
+  `guard()` says the process holds peer-mapped device memory (symmetric buffers of the fused communication path, which may
+  be bound to an NVSwitch multicast object): a rank that disappears with such mappings alive raises NVLink faults on the
+  other GPUs. Use them with gloo ranks on CPU, or with `use_fused_comm_kernels=false` and NVLS off.
   """
 
-  def __init__(self, spec: str | None = None, rank: int = 0):
+  def __init__(self, spec: str | None = None, rank: int = 0, guard=None):
+    self.guard = guard
     spec = spec if spec is not None else os.environ.get("MAXTEXT_B200_INJECT_FAULT", "")
     self.kind, self.step, self.fired = None, -1, False
     if spec:
@@ -229,6 +254,10 @@ class FaultInjector:
   def maybe_fire(self, step: int, attempt: int = 0, heartbeat: Heartbeat | None = None):
     if self.kind is None or self.fired or attempt > 0 or step != self.step:
       return
+    if self.kind in ("exit", "stall") and self.guard is not None:
+      why = self.guard()
+      if why:
+        raise FaultInjectionRefused(f"fault '{self.kind}' not injected: {why}")
     self.fired = True
     if self.kind == "raise":
       raise RankFailure(f"injected failure at step {step}")

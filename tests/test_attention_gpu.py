@@ -40,7 +40,7 @@ def _case(B, S, Hq, Hkv, D, seg_mode=None, window=0, scale=1.0, packed=True, see
   assert E.flash_supported(q, k, v)
   out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
   lse = torch.empty(B, Hq, S, device="cuda")
-  E.flash_fwd(q, k, v, out, lse, seg, scale, window)
+  E.flash_fwd(q, k, v, out, lse, seg, seg, None, None, None, scale, 0.0, True, window, 0, 0)
   torch.cuda.synchronize()
   assert E.kernel_status(True) == 0, "bounded wait timed out in the forward kernel"
   qf, kf, vf, ro, rl = _reference(q, k, v, seg, window, scale)
@@ -141,26 +141,96 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, window):
       assert (out[b].float() - want.float()).abs().max() < 2e-2, (b, splits)
 
 
-def test_flash_forward_two_ctas_per_sm_variant_matches_default():
-  """The experimental forward variant (two co-resident CTAs per SM, single score buffer) gives the default kernel's result."""
-  from maxtext_b200.ops import backend
-  E = backend.ext(required=True)
-  torch.manual_seed(0)
-  B, S, Hq, Hkv, D = 2, 512, 8, 2, 128
-  qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
-  q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
-  seg = torch.ones(B, S, device="cuda", dtype=torch.int32)
-  seg[:, 300:] = 2
+def _fwd_general(B, Sq, Skv, Hq, Hkv, Dqk, Dv, *, causal=True, window=0, chunk=0, softcap=0.0, sinks=False, seg=False, arrays=False,
+                 scale=0.25, seed=0):
+  """Forward kernel against the fp32 definition for the general mask / shape forms (the public op of ops.functional)."""
+  from maxtext_b200.ops import functional as F
+  E = _E()
+  g = torch.Generator(device="cuda").manual_seed(seed)
+  q = (torch.randn(B, Sq, Hq, Dqk, device="cuda", generator=g)).bfloat16()
+  k = (torch.randn(B, Skv, Hkv, Dqk, device="cuda", generator=g)).bfloat16()
+  v = (torch.randn(B, Skv, Hkv, Dv, device="cuda", generator=g)).bfloat16()
+  off = Skv - Sq
+  pos_q = (torch.arange(Sq, device="cuda") + off)[None].expand(B, Sq).contiguous()
+  pos_k = torch.arange(Skv, device="cuda")[None].expand(B, Skv).contiguous()
+  seg_q = seg_k = None
+  if seg:
+    seg_k = torch.ones(B, Skv, dtype=torch.int32, device="cuda")
+    seg_k[:, Skv // 3:] = 2
+    seg_k[:, (2 * Skv) // 3 + 7:] = 3
+    seg_k[-1, -9:] = 0
+    seg_q = seg_k[:, off:].contiguous()
+  sk = (torch.randn(Hq, device="cuda", generator=g) * 2.0) if sinks else None
+  kw = {}
+  if arrays:
+    # keys are a shuffled-block view of a longer sequence: positions come from arrays (as under context parallelism)
+    perm = torch.cat([torch.arange(Skv // 2, Skv), torch.arange(0, Skv // 2)]).cuda()
+    k, v, pos_k = k[:, perm].contiguous(), v[:, perm].contiguous(), pos_k[:, perm].contiguous()
+    if seg:
+      seg_k = seg_k[:, perm].contiguous()
+    kw = dict(kv_positions=pos_k, kv_segment_ids=seg_k)
+  out, lse = F.attention_fwd(q, k, v, pos_q, seg_q, scale, softcap, window, causal, chunk=chunk, sinks=sk, **kw)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0
+  assert E.flash_fwd_supported(q, k, v)
+  mask = ref.attention_mask(pos_q, pos_k, seg_q, seg_k, causal, window, chunk)
+  ro, rl = ref.attention(q.float(), k.float(), v.float(), mask, scale, softcap, sinks=sk, return_lse=True)
+  rows = mask.any(-1)[:, 0]                                    # rows with at least one visible key
+  if sinks:
+    rows = torch.ones_like(rows)
+  err = (out.float() - ro)[rows].abs().max().item()
+  assert err <= 2e-2, f"forward max err {err}"
+  lerr = (lse.transpose(1, 2)[rows] - rl.transpose(1, 2)[rows]).abs().max().item()
+  assert lerr <= 2e-2, f"lse max err {lerr}"
+  if not sinks and (~rows).any():
+    assert out.float()[~rows].abs().max().item() == 0.0        # fully masked rows give zeros, not NaN
+
+
+def test_fwd_ragged_lengths_not_multiples_of_the_tile():
+  _fwd_general(2, 333, 333, 4, 2, 128, 128)
+  _fwd_general(1, 130, 130, 2, 2, 64, 64)
+  _fwd_general(1, 100, 100, 2, 1, 128, 128, causal=False)
+
+
+def test_fwd_more_keys_than_queries_bottom_right_causal():
+  _fwd_general(2, 200, 712, 4, 2, 128, 128)
+  _fwd_general(1, 256, 1024, 2, 2, 128, 128, window=300)
+
+
+def test_fwd_mla_shape_192_128():
+  _fwd_general(2, 384, 384, 4, 4, 192, 128, scale=0.07)
+  _fwd_general(1, 257, 257, 2, 2, 192, 128, scale=0.07, seg=True)
+
+
+def test_fwd_logit_softcap():
+  _fwd_general(2, 384, 384, 4, 2, 128, 128, softcap=5.0, scale=0.5)
+
+
+def test_fwd_sinks():
+  _fwd_general(2, 300, 300, 4, 2, 64, 64, sinks=True, window=128)
+
+
+def test_fwd_chunked_attention():
+  _fwd_general(2, 640, 640, 4, 2, 128, 128, chunk=256)
+  _fwd_general(1, 500, 500, 2, 2, 128, 128, chunk=192)
+  _fwd_general(1, 512, 512, 2, 2, 128, 128, chunk=128, seg=True)       # packed rows: positions come from arrays
+
+
+def test_fwd_key_positions_from_arrays_with_tile_skipping():
+  _fwd_general(2, 512, 512, 4, 2, 128, 128, arrays=True)
+  _fwd_general(1, 640, 640, 2, 2, 128, 128, arrays=True, seg=True, window=200)
+  _fwd_general(1, 384, 384, 2, 1, 128, 128, arrays=True, causal=False)
+
+
+def test_fwd_bitwise_repeatable():
+  E = _E()
+  torch.manual_seed(3)
+  q, k, v = ((0.5 * torch.randn(2, 1024, 4, 128, device="cuda")).bfloat16() for _ in range(3))
   outs = []
-  try:
-    for variant in (1, 2):
-      E.flash_fwd_set_variant(variant)
-      out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
-      lse = torch.empty(B, Hq, S, device="cuda")
-      E.flash_fwd(q, k, v, out, lse, seg, 1.0, 64)
-      outs.append((out.float(), lse))
-  finally:
-    E.flash_fwd_set_variant(1)
-  assert (outs[0][0] - outs[1][0]).abs().max() < 2e-2
-  assert (outs[0][1] - outs[1][1]).abs().max() < 1e-3
+  for _ in range(2):
+    out = torch.empty_like(q)
+    lse = torch.empty(2, 4, 1024, device="cuda")
+    E.flash_fwd(q, k, v, out, lse, None, None, None, None, None, 1.0, 0.0, True, 0, 0, 0)
+    outs.append((out, lse))
+  assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
   assert E.kernel_status(True) == 0

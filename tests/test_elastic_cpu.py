@@ -127,3 +127,50 @@ def test_rank_departure_between_steps_is_seen_by_peers(tmp_path):
   assert procs[1].returncode == 17, outs[1][-2000:]
   assert procs[0].returncode == 0, outs[0][-2000:]
   assert "RANK_FAILURE_SEEN" in outs[0], outs[0][-2000:]
+
+
+def test_rank_departure_faults_are_refused_while_peers_map_this_ranks_gpu_memory():
+  """`exit` / `stall` must not take a rank away while its device buffers are mapped by peers; `raise` stays allowed."""
+  import types
+  import pytest
+  from maxtext_b200.utils import elastic
+  cuda_fused = types.SimpleNamespace(device=types.SimpleNamespace(type="cuda"), store=types.SimpleNamespace(fused=True, rs_nvls=True, symm=object()))
+  cpu = types.SimpleNamespace(device=types.SimpleNamespace(type="cpu"), store=types.SimpleNamespace(fused=False, rs_nvls=False, symm=None))
+  assert elastic.peer_memory_guard(cpu)() == ""
+  assert "symmetric" in elastic.peer_memory_guard(cuda_fused)()
+  for kind in ("exit", "stall"):
+    inj = elastic.FaultInjector(f"{kind}@2", guard=elastic.peer_memory_guard(cuda_fused))
+    inj.maybe_fire(1)
+    with pytest.raises(elastic.FaultInjectionRefused):
+      inj.maybe_fire(2)
+    assert not elastic.retryable(elastic.FaultInjectionRefused("x"))
+  inj = elastic.FaultInjector("raise@2", guard=elastic.peer_memory_guard(cuda_fused))
+  with pytest.raises(elastic.RankFailure):
+    inj.maybe_fire(2)
+
+
+def test_timed_out_device_wait_becomes_a_retryable_error_before_the_step_is_saved():
+  """The train loop reads the kernels' status word after each step's synchronize; a non-zero word (here from a stand-in
+  extension) raises CommTimeoutError, which the supervisor retries."""
+  import pytest
+  from maxtext_b200.parallel.symm import CommTimeoutError
+  from maxtext_b200.train.train import check_kernel_status
+  from maxtext_b200.utils import elastic
+
+  class FakeExt:
+    def __init__(self, st):
+      self.st, self.cleared = st, False
+
+    def kernel_status(self, clear):
+      st, self.cleared = self.st, bool(clear)
+      if clear:
+        self.st = 0
+      return st
+  ok = FakeExt(0)
+  check_kernel_status("cuda:0", 0, ext=ok)
+  bad = FakeExt(4)
+  with pytest.raises(CommTimeoutError) as e:
+    check_kernel_status("cuda:0", 3, ext=bad)
+  assert "peer flag" in str(e.value) and "rank 3" in str(e.value) and bad.cleared
+  assert elastic.retryable(e.value)
+  check_kernel_status("cuda:0", 3, ext=bad)      # the word was cleared by the failed check

@@ -216,3 +216,31 @@ def test_tensor_parallel_decode_matches_single_rank(tmp_path):
   two = run(2, base + ["ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"], "tp2")
   assert one["tokens"] == two["tokens"]
   assert all(abs(a - b) < 1e-5 for a, b in zip(one["logits"], two["logits"]))
+
+
+def test_prompt_lengths_that_would_overrun_the_cache_are_rejected_on_the_host():
+  """A prefix of max_target_length tokens would make the next decode step write one row past the slot's cache: prefill,
+  insert, prefill_concat and the config layer refuse such lengths before any device work."""
+  import pytest
+  import torch
+  from helpers import tiny_config
+  from maxtext_b200.inference.maxengine import MaxEngine, Prefix
+  cfg = tiny_config(extra=["max_target_length=32", "max_prefill_predict_length=16", "per_device_batch_size=2"])
+  eng = MaxEngine(cfg, device=torch.device("cpu"))
+  eng.load_params()
+  toks = torch.arange(40) % 50
+  with pytest.raises(ValueError):
+    eng.prefill(toks, 32)
+  with pytest.raises(ValueError):
+    eng.prefill(toks[:8], 12)
+  with pytest.raises(ValueError):
+    eng.prefill_concat([toks[:4], toks[:35]])
+  prefix, _ = eng.prefill(toks, 8)
+  state = eng.init_decode_state()
+  with pytest.raises(ValueError):
+    eng.insert(Prefix(prefix.caches, 32, prefix.first_token, prefix.logits), state, 0)
+  with pytest.raises(ValueError):
+    eng.insert(prefix, state, 2)
+  eng.insert(prefix, state, 1)
+  with pytest.raises(ValueError):
+    MaxEngine(tiny_config(extra=["max_target_length=32", "max_prefill_predict_length=32"]), device=torch.device("cpu"))

@@ -7,11 +7,14 @@ pytestmark = pytest.mark.gpu
 
 def _cfg(extra=()):
   from maxtext_b200.config import pyconfig
-  return pyconfig.initialize(
-      ["t", "maxtext_b200/configs/base.yml", "base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128",
-       "base_mlp_dim=1024", "base_num_decoder_layers=2", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
-       "dataset_type=synthetic", "enable_checkpointing=false", "weight_init=normal", "log_config=false", "steps=4",
-       "learning_rate=1e-3", "warmup_steps_fraction=0.0", *extra], num_devices=1)
+  base = ["base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128",
+          "base_mlp_dim=1024", "base_num_decoder_layers=2", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
+          "dataset_type=synthetic", "enable_checkpointing=false", "weight_init=normal", "log_config=false", "steps=4",
+          "learning_rate=1e-3", "warmup_steps_fraction=0.0"]
+  merged = {}
+  for kv in list(base) + list(extra):
+    merged[kv.split("=")[0]] = kv          # a later entry replaces an earlier one with the same key
+  return pyconfig.initialize(["t", "maxtext_b200/configs/base.yml", *merged.values()], num_devices=1)
 
 
 def _losses(cfg, device, steps=4):
