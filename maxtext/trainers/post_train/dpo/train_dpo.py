@@ -7,7 +7,7 @@ from maxtext_b200.train.train import main as _train_main
 
 def main(argv=None):
   argv = list(sys.argv if argv is None else argv)
-  return _train_main(argv + ["use_dpo=true"])
+  return _train_main(argv + ["use_dpo=true"] + ([] if any(a.startswith("packing=") for a in argv) else ["packing=false"]))
 
 
 if __name__ == "__main__":

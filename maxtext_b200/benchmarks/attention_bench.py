@@ -52,7 +52,7 @@ def main():
   dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
   fwd_flops = 4.0 * B * S * S * Hq * D / 2
   ms_f = timeit(lambda: E.flash_fwd(q, k, v, out, lse, None, None, None, None, None, 1.0, 0.0, True, 0, 0, 0), a.iters)
-  ms_b = timeit(lambda: E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, None, 1.0, 0), a.iters)
+  ms_b = timeit(lambda: E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, None, None, None, None, 1.0, 0.0, True, 0, 0, 0), a.iters)
   row = {"B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9, "bwd_ms": ms_b,
          "bwd_tflops": 2.5 * fwd_flops / ms_b / 1e9, "kernel_status": E.kernel_status(True)}
   if not a.no_lib:

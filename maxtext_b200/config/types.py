@@ -53,8 +53,7 @@ DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp3
           "float16": "float16", "fp16": "float16", "float8_e4m3fn": "float8_e4m3fn"}
 
 
-class ConfigValueError(ValueError):
-  pass
+from .validators import ConfigValueError, run_all as _run_validators  # noqa: E402
 
 
 def detect_num_devices(table: dict) -> int:
@@ -273,8 +272,6 @@ def derive_and_validate(raw: dict, num_devices: int = 1) -> dict:
     raise ConfigValueError("num_vocab_tiling must be >= 1")
   if t["attention_type"] == "mla" and t["share_kv_projections"]:
     raise ConfigValueError("share_kv_projections is not compatible with attention_type=mla")
-  if t["use_dpo"] and t["packing"]:
-    t["packing"] = False
 
   # custom remat: collect the named tensors (src/maxtext/configs/types.py:3538-3563)
   names = ("context", "mlpwi", "mlpwi_0", "mlpwi_1", "mlpwo", "moe_mlpwi_0", "moe_mlpwi_1", "moe_mlpwo", "query_proj",
@@ -285,4 +282,5 @@ def derive_and_validate(raw: dict, num_devices: int = 1) -> dict:
 
   # expert / context axis helpers
   t["ep_enabled"] = t.get("expert_mesh_size", 1) > 1
+  _run_validators(t)
   return t

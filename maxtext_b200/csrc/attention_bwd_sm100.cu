@@ -2,7 +2,7 @@
 //
 //   delta = rowsum(dO * O)                                  (small pre-pass)
 //   kernel A, CTA = 128 keys of one kv head, K and V resident in shared memory. It walks the query heads
-//     of its GQA group and the 128-query tiles at or after its keys (Q / dO tiles double buffered):
+//     of its GQA group and the 128-query tiles that can see its keys (Q / dO tiles double buffered):
 //        S^T = K Q^T, dP^T = V dO^T  (128 x 128 fp32 in TMEM)
 //        P^T = exp(S^T - lse), dS^T = scale * P^T * (dP^T - delta)  -> bf16, written back into TMEM
 //        dV += P^T dO, dK += dS^T Q  (TMEM operands, accumulators stay in TMEM until the end)
@@ -10,8 +10,11 @@
 //     tensor core work at the same time.
 //   kernel B, CTA = 128 queries of one head, Q and dO resident, K / V tiles double buffered:
 //        S = Q K^T, dP = dO V^T, dS = scale * P * (dP - delta) -> TMEM, dQ += dS K.
-// P is recomputed from the saved log-sum-exp in both kernels. Masks follow the forward kernel (causal by
-// token index, sliding window, segment ids). All waits are bounded; a timeout sets the status word.
+// P is recomputed from the saved log-sum-exp in both kernels (sink logits only enter through it). Masks are those of
+// the forward kernel (attention_mask.cuh): causal, sliding window, chunks, segment ids, positions from indices or arrays,
+// ragged sequence lengths (TMA zero-fills loads and clips stores), different query and key lengths; a logit soft-cap
+// multiplies dS by 1 - tanh^2. All waits are bounded; a timeout sets the status word.
+#include "attention_mask.cuh"
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 
@@ -23,20 +26,19 @@ constexpr int SM_THREADS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Params {
-  int B, S, Hq, Hkv, D;
-  int window;
+  int B, Hq, Hkv;
+  attn::Mask mk;
   float scale;
-  const int* seg;
-  const float* lse;
-  const float* delta;
+  float softcap;         // 0 = none
+  const float* lse;      // [B,Hq,Sq]
+  const float* delta;    // [B,Hq,Sq]
   int* status;
 };
 
-__device__ __forceinline__ bool valid(int qg, int kg, int window, bool has_seg, int sq, int sk) {
-  bool v = kg <= qg;
-  if (window > 0) v = v && (qg - kg < window);
-  if (has_seg) v = v && (sq == sk) && (sk != 0);
-  return v;
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // [128 x D] tile held as D/64 boxes {64 cols, 128 rows} (16 KB each)
@@ -69,8 +71,18 @@ __device__ __forceinline__ void stage_rows_bf16(uint32_t tmem_addr, uint32_t box
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
   }
 }
+// zeros in place of stage_rows_bf16 (a tile whose accumulator was never written)
+__device__ __forceinline__ void stage_rows_zero(uint32_t box, int row, int c) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int chunk = (c & 1) * 4 + j;
+    const uint32_t dst = box + row * 128 + ((chunk ^ (row & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+  }
+}
 
 // ================================================================================================ delta
+// delta[b,h,s] = sum_d dout[b,s,h,d] * out[b,s,h,d] for contiguous [B,S,H,D] tensors; one warp per (b,s,h)
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ delta,
                              int B, int S, int H, int D) {
   const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
@@ -96,11 +108,31 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_
 // Issue order of the MMA warp in steady state:  dV_i | S^T_{i+1} | dK_i | dP^T_{i+1}
 // so the tensor core computes S^T of the next tile while the softmax threads turn dP^T_i into dS^T_i, and
 // dP^T of the next tile while they turn S^T_{i+1} into P^T_{i+1}.
+//
+// The work list of a CTA is the sequence of (query head of the group, query tile) pairs whose tile pair is not fully
+// masked, in a fixed order that the producer, the MMA issuer and the softmax threads each derive for themselves.
+struct QueryWalk {
+  const attn::Mask& mk;
+  attn::Span ks;
+  int b, G, qt_lo, qt_hi, g, qt;
+  __device__ QueryWalk(const attn::Mask& m, const attn::Span& k, int b_, int G_, int lo, int hi)
+      : mk(m), ks(k), b(b_), G(G_), qt_lo(lo), qt_hi(hi), g(0), qt(lo - 1) {}
+  // advances to the next pair that takes part; returns its class (1 unmasked, 2 mixed) or 0 at the end
+  __device__ __forceinline__ int next() {
+    if (qt_hi <= qt_lo) return 0;
+    for (;;) {
+      if (++qt >= qt_hi) { qt = qt_lo; if (++g >= G) return 0; }
+      const int c = attn::classify(mk, attn::q_span(mk, b, qt), ks);
+      if (c) return c;
+    }
+  }
+};
+
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
            const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
-           Params p) {
+           const __grid_constant__ Params p) {
   constexpr int BIG = 128 * D * 2;
   constexpr int NBOX = D / 64;
   constexpr uint32_t TMEM_COLS = 512;
@@ -109,24 +141,25 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sK = base, sV = base + BIG, sStage = base + 2 * BIG;          // stage s: Q at +s*2*BIG, dO right after it
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + (base - smem_u32(smem_raw)) + 6 * BIG);
-  float* s_lse = reinterpret_cast<float*>(ctl + 1);      // [2][128], pre-multiplied by log2(e)
+  float* s_lse = reinterpret_cast<float*>(ctl + 1);      // [2][128], pre-multiplied by log2(e); +inf for queries beyond Sq
   float* s_delta = s_lse + 256;                          // [2][128]
-  int* s_seg = reinterpret_cast<int*>(s_delta + 256);    // [2][128]
+  int* s_seg = reinterpret_cast<int*>(s_delta + 256);    // [2][128] query segment ids
+  int* s_pos = s_seg + 256;                              // [2][128] query positions (array mode)
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   enum { KV_FULL = 0, Q_FULL0, Q_FULL1, Q_EMPTY0, Q_EMPTY1, ST_FULL, DP_FULL, P_READY, DS_READY, ACC_FULL };
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
+  const attn::Mask& mk = p.mk;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_t = p.S / 128;
-  const int kt = blockIdx.x;
-  const int hk = blockIdx.y, b = blockIdx.z;
+  // Head-major order: the CTAs that run at the same time work on few (batch, head) pairs, so the Q / dO tiles they all
+  // stream stay in L2. Within a head the key tiles ascend: under a causal mask the first ones see the most queries.
+  const int kt = (int)(blockIdx.x % mk.n_kt);
+  const int hk = (int)(blockIdx.x / mk.n_kt) % p.Hkv, b = (int)(blockIdx.x / mk.n_kt) / p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int k0 = kt * 128;
-  const int row_base = b * p.S;
-  int qt_hi = n_t - 1;
-  if (p.window > 0) { const int hi = (k0 + 127 + p.window - 1) / 128; qt_hi = hi < n_t - 1 ? hi : n_t - 1; }
-  const int n_qt = qt_hi - kt + 1;
-  const int n_iter = n_qt * G;
+  const attn::Span ks = attn::k_span(mk, b, kt);
+  int qt_lo, qt_hi;
+  attn::q_tiles_for(mk, ks, qt_lo, qt_hi);
 
   if (threadIdx.x == 0) {
     ctl->abort_flag = 0;
@@ -151,21 +184,22 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       mbar_arrive_expect_tx(bar(KV_FULL), 2 * BIG);
 #pragma unroll
       for (int j = 0; j < NBOX; ++j) {
-        tma_load_2d(sK + j * 16384, &map_k, bar(KV_FULL), hk * D + j * 64, row_base + k0);
-        tma_load_2d(sV + j * 16384, &map_v, bar(KV_FULL), hk * D + j * 64, row_base + k0);
+        tma_load_3d(sK + j * 16384, &map_k, bar(KV_FULL), hk * D + j * 64, k0, b);
+        tma_load_3d(sV + j * 16384, &map_v, bar(KV_FULL), hk * D + j * 64, k0, b);
       }
-      for (int it = 0; it < n_iter; ++it) {
+      QueryWalk w(mk, ks, b, G, qt_lo, qt_hi);
+      for (int it = 0; w.next(); ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        const int h = hk * G + it / n_qt;
-        const int q0 = (kt + it % n_qt) * 128;
+        const int h = hk * G + w.g;
+        const int q0 = w.qt * 128;
         if (!mbar_wait(bar(Q_EMPTY0 + s), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) break;
         mbar_arrive_expect_tx(bar(Q_FULL0 + s), 2 * BIG);
         const uint32_t sq = sStage + s * 2 * BIG, sdo = sq + BIG;
 #pragma unroll
         for (int j = 0; j < NBOX; ++j) {
-          tma_load_2d(sq + j * 16384, &map_q, bar(Q_FULL0 + s), h * D + j * 64, row_base + q0);
-          tma_load_2d(sdo + j * 16384, &map_do, bar(Q_FULL0 + s), h * D + j * 64, row_base + q0);
+          tma_load_3d(sq + j * 16384, &map_q, bar(Q_FULL0 + s), h * D + j * 64, q0, b);
+          tma_load_3d(sdo + j * 16384, &map_do, bar(Q_FULL0 + s), h * D + j * 64, q0, b);
         }
       }
     }
@@ -184,19 +218,22 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int k = 0; k < D / 16; ++k) umma_f16_ss(tmem + COL_DPT, big_kmajor(sV, k), big_kmajor(stage_q(it) + BIG, k), idesc_nt, k != 0);
         umma_commit(bar(DP_FULL));
       };
+      QueryWalk w(mk, ks, b, G, qt_lo, qt_hi);
+      bool more = w.next() != 0;
       bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
-      if (ok && n_iter > 0) {
+      if (ok && more) {
         ok = mbar_wait(bar(Q_FULL0), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
         if (ok) { tc_fence_after(); issue_st(0); issue_dpt(0); }
       }
-      for (int it = 0; it < n_iter && ok; ++it) {
+      for (int it = 0; more && ok; ++it) {
         const uint32_t ph = it & 1;
+        const bool next = w.next() != 0;
         if (!mbar_wait(bar(P_READY), ph, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_f16_ts(tmem + COL_DV, tmem + COL_ST + tmem_a_col(k), big_mnmajor(stage_q(it) + BIG, k), idesc_acc, (it | k) != 0);
-        if (it + 1 < n_iter) {
+        if (next) {
           if (!mbar_wait(bar(Q_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
           tc_fence_after();
           issue_st(it + 1);        // overwrites P^T_it only after dV_it (issued above) has consumed it: MMAs retire in order
@@ -207,8 +244,9 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         for (int k = 0; k < 8; ++k)
           umma_f16_ts(tmem + COL_DK, tmem + COL_DPT + tmem_a_col(k), big_mnmajor(stage_q(it), k), idesc_acc, (it | k) != 0);
         umma_commit(bar(Q_EMPTY0 + (it & 1)));
-        if (it + 1 < n_iter) issue_dpt(it + 1);
+        if (next) issue_dpt(it + 1);
         else umma_commit(bar(ACC_FULL));
+        more = next;
       }
     }
   } else {
@@ -219,32 +257,53 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     const int row = qd * 32 + lane;             // key row
     const int et = threadIdx.x - 64;            // 0..255
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-    const float a = p.scale * LOG2E;
-    const bool has_seg = p.seg != nullptr;
+    const bool cap = p.softcap > 0.f;
+    const float a = cap ? p.softcap * LOG2E : p.scale * LOG2E;
+    const float pre = cap ? p.scale / p.softcap : 1.f;
+    const bool has_seg = mk.seg_q != nullptr;
+    const bool arrays = mk.pos_q != nullptr;
     const int kg = k0 + row;
-    const int my_seg = has_seg ? p.seg[b * p.S + kg] : 0;
+    const bool key_ok = row < ks.rows;
+    const int my_seg = has_seg ? (key_ok ? mk.seg_k[(long)b * mk.Skv + kg] : 0) : 1;
+    const int kpos = arrays ? (key_ok ? mk.pos_k[(long)b * mk.Skv + kg] : 0) : kg;
+    // query positions that may attend to this key, as a closed interval
+    int lo_p, hi_p;
+    attn::query_interval(mk, kpos, lo_p, hi_p);
+    const uint32_t span = (uint32_t)hi_p - (uint32_t)lo_p;
+    const bool none = hi_p < lo_p || !key_ok;
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
+    int n_done = 0;
+    QueryWalk w(mk, ks, b, G, qt_lo, qt_hi);
+    for (int it = 0;; ++it) {
+      const int cls = w.next();
+      if (!cls) break;
+      n_done = it + 1;
       const int s = it & 1;
       const uint32_t ph = it & 1;
-      const int h = hk * G + it / n_qt;
-      const int q0 = (kt + it % n_qt) * 128;
+      const int h = hk * G + w.g;
+      const int q0 = w.qt * 128;
       if (et < 128) {
-        const long idx = ((long)b * p.Hq + h) * p.S + q0 + et;
-        s_lse[s * 128 + et] = p.lse[idx] * LOG2E;
-        s_delta[s * 128 + et] = p.delta[idx];
-        if (has_seg) s_seg[s * 128 + et] = p.seg[b * p.S + q0 + et];
+        const int qi = q0 + et;
+        const bool q_ok = qi < mk.Sq;
+        const long idx = ((long)b * p.Hq + h) * mk.Sq + qi;
+        s_lse[s * 128 + et] = q_ok ? p.lse[idx] * LOG2E : INFINITY;     // queries beyond the sequence get probability 0
+        s_delta[s * 128 + et] = q_ok ? p.delta[idx] : 0.f;
+        if (has_seg) s_seg[s * 128 + et] = q_ok ? mk.seg_q[(long)b * mk.Sq + qi] : 0;
+        if (arrays) s_pos[s * 128 + et] = q_ok ? mk.pos_q[(long)b * mk.Sq + qi] : INT_MAX;
       }
       // One thread waits for the MMAs; its verdict is sticky. A failed CTA keeps meeting at the named barriers
       // (so nobody is left waiting there) but does no further tensor-memory work.
       if (et == 128 && !mbar_wait(bar(ST_FULL), ph, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
       named_bar_sync(1, SM_THREADS);
       if (*reinterpret_cast<volatile int*>(&ctl->ok_flag) == 0) ok = false;
-      const bool need_mask = (q0 == k0) || p.window > 0 || has_seg;
+      const bool need_mask = cls == 2;
       const float* lse_s = s_lse + s * 128 + half * 64;
       const float* del_s = s_delta + s * 128 + half * 64;
       const int* seg_s = s_seg + s * 128 + half * 64;
-      float pr[64];
+      const int* pos_s = s_pos + s * 128 + half * 64;
+      // index mode: query column e of this half has position q0 + half*64 + e + q_off
+      const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)(q0 + half * 64 + mk.q_off);
+      float pr[64];      // what multiplies (dP - delta): P, or P * (1 - tanh^2) under a soft-cap
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -252,16 +311,25 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem + lane_off + COL_ST + half * 64 + c * 32, r);
           tmem_ld_wait();
-          uint32_t pk[16];
+          float pv[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int col = c * 32 + e;
-            float v = fast_exp2(fmaf(a, __uint_as_float(r[e]), -lse_s[col]));
-            if (need_mask && !valid(q0 + half * 64 + col, kg, p.window, has_seg, has_seg ? seg_s[col] : 0, my_seg)) v = 0.f;
-            pr[col] = v;
+            float sv = __uint_as_float(r[e]);
+            float dt = 1.f;
+            if (cap) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
+            float v = fast_exp2(fmaf(a, sv, -lse_s[col]));
+            if (need_mask) {
+              bool keep = arrays ? ((uint32_t)pos_s[col] - (uint32_t)lo_p <= span) : ((uint32_t)col - e_lo <= span);
+              if (has_seg) keep = keep && seg_s[col] == my_seg && my_seg != 0;
+              if (!keep || none) v = 0.f;
+            }
+            pv[e] = v;
+            pr[col] = v * dt;
           }
+          uint32_t pk[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pr[c * 32 + 2 * e], pr[c * 32 + 2 * e + 1]);
+          for (int e = 0; e < 16; ++e) pk[e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
           // P^T of this thread's 64 queries: 32 packed columns at the start of its own 64 score columns, so the two
           // halves never write over each other's unread scores
           tmem_st_32x32b_x16(tmem + lane_off + COL_ST + half * 64 + c * 16, pk);
@@ -294,27 +362,32 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       tc_fence_before();
       mbar_arrive(bar(DS_READY));
     }
-    if (et == 0 && ok && !mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
+    if (et == 0 && ok && !mbar_wait(bar(n_done > 0 ? ACC_FULL : KV_FULL), 0, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
     named_bar_sync(1, SM_THREADS);
     ok = *reinterpret_cast<volatile int*>(&ctl->ok_flag) != 0;
-    if (ok && n_iter > 0) {
+    if (ok && ks.rows > 0) {
       tc_fence_after();
-      // all MMAs have retired: the Q/dO stages become the staging area, dV first then dK
+      // all MMAs have retired: the Q/dO stages become the staging area, dV first then dK (zeros when no query sees these keys)
       for (int c = half; c < D / 32; c += 2) {
-        stage_rows_bf16(tmem + lane_off + COL_DV + c * 32, sStage + (c >> 1) * 16384, row, c);
-        stage_rows_bf16(tmem + lane_off + COL_DK + c * 32, sStage + NBOX * 16384 + (c >> 1) * 16384, row, c);
+        if (n_done > 0) {
+          stage_rows_bf16(tmem + lane_off + COL_DV + c * 32, sStage + (c >> 1) * 16384, row, c);
+          stage_rows_bf16(tmem + lane_off + COL_DK + c * 32, sStage + NBOX * 16384 + (c >> 1) * 16384, row, c);
+        } else {
+          stage_rows_zero(sStage + (c >> 1) * 16384, row, c);
+          stage_rows_zero(sStage + NBOX * 16384 + (c >> 1) * 16384, row, c);
+        }
       }
       fence_proxy_async_smem();
-      named_bar_sync(2, SM_THREADS);
-      if (et == 0) {
+    }
+    named_bar_sync(2, SM_THREADS);
+    if (ok && ks.rows > 0 && et == 0) {
 #pragma unroll
-        for (int j = 0; j < NBOX; ++j) {
-          tma_store_2d(&map_dv, sStage + j * 16384, hk * D + j * 64, row_base + k0);
-          tma_store_2d(&map_dk, sStage + NBOX * 16384 + j * 16384, hk * D + j * 64, row_base + k0);
-        }
-        tma_commit_group();
-        tma_wait_group<0>();
+      for (int j = 0; j < NBOX; ++j) {
+        tma_store_3d(&map_dv, sStage + j * 16384, hk * D + j * 64, k0, b);
+        tma_store_3d(&map_dk, sStage + NBOX * 16384 + j * 16384, hk * D + j * 64, k0, b);
       }
+      tma_commit_group();
+      tma_wait_group<0>();
     }
   }
   if (*abort_flag) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 200000ull) { } }
@@ -326,10 +399,25 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
 // ================================================================================================ kernel B: dQ
 // Issue order of the MMA warp in steady state:  S_{i+1} | dQ_i | dP_{i+1}: the next tile's scores are computed while
 // the softmax threads turn dP_i into dS_i.
+struct KeyWalk {
+  const attn::Mask& mk;
+  attn::Span qs;
+  int b, kt_hi, kt;
+  __device__ KeyWalk(const attn::Mask& m, const attn::Span& q, int b_, int lo, int hi) : mk(m), qs(q), b(b_), kt_hi(hi), kt(lo - 1) {}
+  // advances to the next key tile that takes part; returns its class (1 unmasked, 2 mixed) or 0 at the end
+  __device__ __forceinline__ int next() {
+    while (++kt < kt_hi) {
+      const int c = attn::classify(mk, qs, attn::k_span(mk, b, kt));
+      if (c) return c;
+    }
+    return 0;
+  }
+};
+
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-          const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq, Params p) {
+          const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ Params p) {
   constexpr int BIG = 128 * D * 2;
   constexpr int NBOX = D / 64;
   constexpr uint32_t TMEM_COLS = 512;
@@ -338,21 +426,23 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sQ = base, sDO = base + BIG, sStage = base + 2 * BIG;         // stage s: K at +s*2*BIG, V right after it
   Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + (base - smem_u32(smem_raw)) + 6 * BIG);
-  int* s_seg = reinterpret_cast<int*>(ctl + 1);          // [2][128]
+  int* s_seg = reinterpret_cast<int*>(ctl + 1);          // [2][128] key segment ids
+  int* s_pos = s_seg + 256;                              // [2][128] key positions (array mode)
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   enum { Q_FULL = 0, KV_FULL0, KV_FULL1, KV_EMPTY0, KV_EMPTY1, S_FULL, DP_FULL, S_DONE, DS_READY, ACC_FULL };
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
+  const attn::Mask& mk = p.mk;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_t = p.S / 128;
-  const int qt = n_t - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Head-major order (the K / V tiles that concurrent CTAs stream stay in L2); within a head the heaviest query tiles
+  // first: under a causal mask the last ones see the most keys.
+  const int qt = mk.n_qt - 1 - (int)(blockIdx.x % mk.n_qt);
+  const int h = (int)(blockIdx.x / mk.n_qt) % p.Hq, b = (int)(blockIdx.x / mk.n_qt) / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qt * 128;
-  const int row_base = b * p.S;
-  int kt_lo = 0;
-  if (p.window > 0) { const int lo = q0 - p.window + 1; kt_lo = lo > 0 ? lo / 128 : 0; }
-  const int n_kt = qt - kt_lo + 1;
+  const attn::Span qs = attn::q_span(mk, b, qt);
+  int kt_lo, kt_hi;
+  attn::k_tiles_for(mk, qs, kt_lo, kt_hi);
 
   if (threadIdx.x == 0) {
     ctl->abort_flag = 0;
@@ -377,20 +467,21 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       mbar_arrive_expect_tx(bar(Q_FULL), 2 * BIG);
 #pragma unroll
       for (int j = 0; j < NBOX; ++j) {
-        tma_load_2d(sQ + j * 16384, &map_q, bar(Q_FULL), h * D + j * 64, row_base + q0);
-        tma_load_2d(sDO + j * 16384, &map_do, bar(Q_FULL), h * D + j * 64, row_base + q0);
+        tma_load_3d(sQ + j * 16384, &map_q, bar(Q_FULL), h * D + j * 64, q0, b);
+        tma_load_3d(sDO + j * 16384, &map_do, bar(Q_FULL), h * D + j * 64, q0, b);
       }
-      for (int it = 0; it < n_kt; ++it) {
+      KeyWalk w(mk, qs, b, kt_lo, kt_hi);
+      for (int it = 0; w.next(); ++it) {
         const int s = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        const int kk = (kt_lo + it) * 128;
+        const int kk = w.kt * 128;
         if (!mbar_wait(bar(KV_EMPTY0 + s), ph ^ 1, abort_flag, p.status, ST_TIMEOUT_PRODUCER)) break;
         mbar_arrive_expect_tx(bar(KV_FULL0 + s), 2 * BIG);
         const uint32_t sk = sStage + s * 2 * BIG, sv = sk + BIG;
 #pragma unroll
         for (int j = 0; j < NBOX; ++j) {
-          tma_load_2d(sk + j * 16384, &map_k, bar(KV_FULL0 + s), hk * D + j * 64, row_base + kk);
-          tma_load_2d(sv + j * 16384, &map_v, bar(KV_FULL0 + s), hk * D + j * 64, row_base + kk);
+          tma_load_3d(sk + j * 16384, &map_k, bar(KV_FULL0 + s), hk * D + j * 64, kk, b);
+          tma_load_3d(sv + j * 16384, &map_v, bar(KV_FULL0 + s), hk * D + j * 64, kk, b);
         }
       }
     }
@@ -409,14 +500,17 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         for (int k = 0; k < D / 16; ++k) umma_f16_ss(tmem + COL_DP, big_kmajor(sDO, k), big_kmajor(stage_k(it) + BIG, k), idesc_nt, k != 0);
         umma_commit(bar(DP_FULL));
       };
+      KeyWalk w(mk, qs, b, kt_lo, kt_hi);
+      bool more = w.next() != 0;
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
-      if (ok) {
+      if (ok && more) {
         ok = mbar_wait(bar(KV_FULL0), 0, abort_flag, p.status, ST_TIMEOUT_MMA);
         if (ok) { tc_fence_after(); issue_s(0); issue_dp(0); }
       }
-      for (int it = 0; it < n_kt && ok; ++it) {
+      for (int it = 0; more && ok; ++it) {
         const uint32_t ph = it & 1;
-        if (it + 1 < n_kt) {
+        const bool next = w.next() != 0;
+        if (next) {
           // the score buffer is free as soon as the softmax threads have read it
           if (!mbar_wait(bar(S_DONE), ph, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
           if (!mbar_wait(bar(KV_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_MMA)) break;
@@ -429,8 +523,9 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
         for (int k = 0; k < 8; ++k)
           umma_f16_ts(tmem + COL_DQ, tmem + COL_DP + tmem_a_col(k), big_mnmajor(stage_k(it), k), idesc_acc, (it | k) != 0);
         umma_commit(bar(KV_EMPTY0 + (it & 1)));
-        if (it + 1 < n_kt) issue_dp(it + 1);
+        if (next) issue_dp(it + 1);
         else umma_commit(bar(ACC_FULL));
+        more = next;
       }
     }
   } else {
@@ -440,25 +535,45 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
     const int row = qd * 32 + lane;             // query row
     const int et = threadIdx.x - 64;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-    const float a = p.scale * LOG2E;
-    const bool has_seg = p.seg != nullptr;
+    const bool cap = p.softcap > 0.f;
+    const float a = cap ? p.softcap * LOG2E : p.scale * LOG2E;
+    const float pre = cap ? p.scale / p.softcap : 1.f;
+    const bool has_seg = mk.seg_q != nullptr;
+    const bool arrays = mk.pos_k != nullptr;
     const int qg = q0 + row;
-    const int my_seg = has_seg ? p.seg[b * p.S + qg] : 0;
-    const long sidx = ((long)b * p.Hq + h) * p.S + qg;
-    const float my_lse = p.lse[sidx] * LOG2E;
-    const float my_delta = p.delta[sidx];
+    const bool row_ok = row < qs.rows;
+    const int my_seg = has_seg ? (row_ok ? mk.seg_q[(long)b * mk.Sq + qg] : 0) : 1;
+    const int qpos = mk.pos_q ? (row_ok ? mk.pos_q[(long)b * mk.Sq + qg] : 0) : qg + mk.q_off;
+    int lo_p, hi_p;
+    attn::key_interval(mk, qpos, lo_p, hi_p);
+    const uint32_t span = (uint32_t)hi_p - (uint32_t)lo_p;
+    const bool none = hi_p < lo_p;
+    const long sidx = ((long)b * p.Hq + h) * mk.Sq + qg;
+    const float my_lse = row_ok ? p.lse[sidx] * LOG2E : INFINITY;      // rows beyond the sequence get probability 0
+    const float my_delta = row_ok ? p.delta[sidx] : 0.f;
     bool ok = true;
-    for (int it = 0; it < n_kt; ++it) {
+    int n_done = 0;
+    KeyWalk w(mk, qs, b, kt_lo, kt_hi);
+    for (int it = 0;; ++it) {
+      const int cls = w.next();
+      if (!cls) break;
+      n_done = it + 1;
       const int s = it & 1;
       const uint32_t ph = it & 1;
-      const int kk = (kt_lo + it) * 128;
-      if (has_seg && et < 128) s_seg[s * 128 + et] = p.seg[b * p.S + kk + et];
+      const int kk = w.kt * 128;
+      if (et < 128 && cls == 2) {
+        const int ki = kk + et;
+        if (has_seg) s_seg[s * 128 + et] = ki < mk.Skv ? mk.seg_k[(long)b * mk.Skv + ki] : 0;
+        if (arrays) s_pos[s * 128 + et] = ki < mk.Skv ? mk.pos_k[(long)b * mk.Skv + ki] : INT_MAX;
+      }
       if (et == 128 && !mbar_wait(bar(S_FULL), ph, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
       named_bar_sync(1, SM_THREADS);
       if (*reinterpret_cast<volatile int*>(&ctl->ok_flag) == 0) ok = false;
-      const bool need_mask = (kk == q0) || p.window > 0 || has_seg;
+      const bool need_mask = cls == 2;
       const int* seg_s = s_seg + s * 128 + half * 64;
-      float pr[64];
+      const int* pos_s = s_pos + s * 128 + half * 64;
+      const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)(kk + half * 64);     // index mode: key column e of this half has position kk + half*64 + e
+      float pr[64];      // what multiplies (dP - delta): P, or P * (1 - tanh^2) under a soft-cap
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -469,8 +584,15 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int col = c * 32 + e;
-            float v = fast_exp2(fmaf(a, __uint_as_float(r[e]), -my_lse));
-            if (need_mask && !valid(qg, kk + half * 64 + col, p.window, has_seg, my_seg, has_seg ? seg_s[col] : 0)) v = 0.f;
+            float sv = __uint_as_float(r[e]);
+            float dt = 1.f;
+            if (cap) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
+            float v = fast_exp2(fmaf(a, sv, -my_lse)) * dt;
+            if (need_mask) {
+              bool keep = arrays ? ((uint32_t)pos_s[col] - (uint32_t)lo_p <= span) : ((uint32_t)col - e_lo <= span);
+              if (has_seg) keep = keep && seg_s[col] == my_seg && my_seg != 0;
+              if (!keep || none) v = 0.f;
+            }
             pr[col] = v;
           }
         }
@@ -500,20 +622,23 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       tc_fence_before();
       mbar_arrive(bar(DS_READY));
     }
-    if (et == 0 && ok && !mbar_wait(bar(ACC_FULL), 0, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
+    if (et == 0 && ok && !mbar_wait(bar(n_done > 0 ? ACC_FULL : Q_FULL), 0, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ctl->ok_flag = 0;
     named_bar_sync(1, SM_THREADS);
     ok = *reinterpret_cast<volatile int*>(&ctl->ok_flag) != 0;
-    if (ok) {
+    if (ok && qs.rows > 0) {
       tc_fence_after();
-      for (int c = half; c < D / 32; c += 2) stage_rows_bf16(tmem + lane_off + COL_DQ + c * 32, sStage + (c >> 1) * 16384, row, c);
-      fence_proxy_async_smem();
-      named_bar_sync(2, SM_THREADS);
-      if (et == 0) {
-#pragma unroll
-        for (int j = 0; j < NBOX; ++j) tma_store_2d(&map_dq, sStage + j * 16384, h * D + j * 64, row_base + q0);
-        tma_commit_group();
-        tma_wait_group<0>();
+      for (int c = half; c < D / 32; c += 2) {
+        if (n_done > 0) stage_rows_bf16(tmem + lane_off + COL_DQ + c * 32, sStage + (c >> 1) * 16384, row, c);
+        else stage_rows_zero(sStage + (c >> 1) * 16384, row, c);          // no key is visible from these queries
       }
+      fence_proxy_async_smem();
+    }
+    named_bar_sync(2, SM_THREADS);
+    if (ok && qs.rows > 0 && et == 0) {
+#pragma unroll
+      for (int j = 0; j < NBOX; ++j) tma_store_3d(&map_dq, sStage + j * 16384, h * D + j * 64, q0, b);
+      tma_commit_group();
+      tma_wait_group<0>();
     }
   }
   if (*abort_flag) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 200000ull) { } }
@@ -537,15 +662,16 @@ static EncodeFn encode_fn() {
   return fn;
 }
 
-// tokens x (heads*D) view, row stride `ld` elements; box {64 columns, box_rows rows}
-static int tok_map(CUtensorMap* m, const void* ptr, long rows, long cols, long ld, int box_rows) {
+// {heads*D, tokens, batch} view with row stride `ld` and batch stride `bs` (elements); box {64 columns, 128 rows, 1}
+static int tok_map(CUtensorMap* m, const void* ptr, long batch, long tokens, long cols, long ld, long bs) {
   EncodeFn enc = encode_fn();
   if (!enc) return -1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t es[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (batch == 1) bs = tokens * ld;      // a one-batch view may carry any batch stride
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)tokens, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)bs * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
@@ -556,44 +682,62 @@ static int set_smem(K kern, int bytes) {
 }
 
 template <int D>
-static int run(const CUtensorMap& q64, const CUtensorMap& q128, const CUtensorMap& k64, const CUtensorMap& k128, const CUtensorMap& v64,
-               const CUtensorMap& v128, const CUtensorMap& do64, const CUtensorMap& do128, const CUtensorMap& mdq, const CUtensorMap& mdk,
-               const CUtensorMap& mdv, const Params& p, cudaStream_t st) {
+static int run(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo, const CUtensorMap& mdq,
+               const CUtensorMap& mdk, const CUtensorMap& mdv, const Params& p, cudaStream_t st) {
   const int smem = 6 * 128 * D * 2 + (int)sizeof(Ctl) + 4096 + 1024;
   static bool cfg = false;
   if (!cfg) {
     if (set_smem(dkv_kernel<D>, smem) || set_smem(dq_kernel<D>, smem)) return -2;
     cfg = true;
   }
-  dkv_kernel<D><<<dim3(p.S / 128, p.Hkv, p.B), THREADS, smem, st>>>(q128, k128, v128, do128, mdk, mdv, p);
-  dq_kernel<D><<<dim3(p.S / 128, p.Hq, p.B), THREADS, smem, st>>>(q128, k128, v128, do128, mdq, p);
+  dkv_kernel<D><<<(unsigned)((long)p.mk.n_kt * p.Hkv * p.B), THREADS, smem, st>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  dq_kernel<D><<<(unsigned)((long)p.mk.n_qt * p.Hq * p.B), THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace bwd
 }  // namespace mt
 
-// dout/out: contiguous [B,S,Hq,D]; delta: scratch [B,Hq,S] fp32; dq/dk/dv: token-major views with their own row strides.
+extern "C" void mt_attn_tile_minmax(const int* pos, int B, int S, int* out, cudaStream_t st);      // attention_fwd_sm100.cu
+
+// Shapes the backward kernels cover: Dqk = Dv in {64, 128}.
+extern "C" int mt_flash_bwd_supported(int Dqk, int Dv) { return Dqk == Dv && (Dqk == 64 || Dqk == 128); }
+
+// dout/out: contiguous [B,Sq,Hq,D]; delta: scratch [B,Hq,Sq] fp32; q/k/v and dq/dk/dv: token-major views with their own row (ld*) and
+// batch (bs*) strides in elements. seg_*, pos_* may be null (pos_* need `tiles`, mt_attn_tile_ints ints of scratch).
 extern "C" int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta,
-                            void* dq, void* dk, void* dv, const int* seg, int B, int S, int Hq, int Hkv, int D, long ldq, long ldk,
-                            long ldv, long lddq, long lddk, long lddv, float scale, int window, int* status, cudaStream_t st) {
+                            void* dq, void* dk, void* dv, const int* seg_q, const int* seg_k, const int* pos_q, const int* pos_k, int* tiles,
+                            int B, int Sq, int Skv, int Hq, int Hkv, int D, long ldq, long bsq, long ldk, long bsk, long ldv, long bsv, long lddq,
+                            long bsdq, long lddk, long bsdk, long lddv, long bsdv, float scale, float softcap, int causal, int window, int chunk,
+                            int q_off, int* status, cudaStream_t st) {
   using namespace mt::bwd;
-  if ((D != 128 && D != 64) || S % 128 || Hq % Hkv) return -1;
-  const long rows = (long)B * S;
+  if (!mt_flash_bwd_supported(D, D) || Hq % Hkv || Sq < 1 || Skv < 1 || (pos_q == nullptr) != (pos_k == nullptr) ||
+      (seg_q == nullptr) != (seg_k == nullptr) || (pos_q && !tiles))
+    return -1;
   {
-    const long warps = rows * Hq;
+    const long warps = (long)B * Sq * Hq;
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
-    delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, D);
+    delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, Sq, Hq, D);
   }
-  CUtensorMap q64, q128, k64, k128, v64, v128, do64, do128, mdq, mdk, mdv;
+  CUtensorMap mq, mkk, mv, mdo, mdq, mdk, mdv;
   const long cq = (long)Hq * D, ck = (long)Hkv * D;
-  if (tok_map(&q64, q, rows, cq, ldq, 64) || tok_map(&q128, q, rows, cq, ldq, 128) || tok_map(&k64, k, rows, ck, ldk, 64) ||
-      tok_map(&k128, k, rows, ck, ldk, 128) || tok_map(&v64, v, rows, ck, ldv, 64) || tok_map(&v128, v, rows, ck, ldv, 128) ||
-      tok_map(&do64, dout, rows, cq, cq, 64) || tok_map(&do128, dout, rows, cq, cq, 128) || tok_map(&mdq, dq, rows, cq, lddq, 128) ||
-      tok_map(&mdk, dk, rows, ck, lddk, 128) || tok_map(&mdv, dv, rows, ck, lddv, 128))
+  if (tok_map(&mq, q, B, Sq, cq, ldq, bsq) || tok_map(&mkk, k, B, Skv, ck, ldk, bsk) || tok_map(&mv, v, B, Skv, ck, ldv, bsv) ||
+      tok_map(&mdo, dout, B, Sq, cq, cq, (long)Sq * cq) || tok_map(&mdq, dq, B, Sq, cq, lddq, bsdq) ||
+      tok_map(&mdk, dk, B, Skv, ck, lddk, bsdk) || tok_map(&mdv, dv, B, Skv, ck, lddv, bsdv))
     return -3;
-  Params p{B, S, Hq, Hkv, D, window, scale, seg, lse, delta, status};
-  if (D == 128) return run<128>(q64, q128, k64, k128, v64, v128, do64, do128, mdq, mdk, mdv, p, st);
-  return run<64>(q64, q128, k64, k128, v64, v128, do64, do128, mdq, mdk, mdv, p, st);
+  Params p{};
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.scale = scale; p.softcap = softcap; p.lse = lse; p.delta = delta; p.status = status;
+  mt::attn::Mask& m = p.mk;
+  m.Sq = Sq; m.Skv = Skv; m.n_qt = (Sq + 127) / 128; m.n_kt = (Skv + 127) / 128;
+  m.q_off = q_off; m.causal = causal; m.window = window; m.chunk = chunk;
+  m.seg_q = seg_q; m.seg_k = seg_k; m.pos_q = pos_q; m.pos_k = pos_k;
+  if (pos_q) {
+    mt_attn_tile_minmax(pos_q, B, Sq, tiles, st);
+    mt_attn_tile_minmax(pos_k, B, Skv, tiles + 2l * B * m.n_qt, st);
+    m.tile_q = tiles;
+    m.tile_k = tiles + 2l * B * m.n_qt;
+  }
+  if (D == 128) return run<128>(mq, mkk, mv, mdo, mdq, mdk, mdv, p, st);
+  return run<64>(mq, mkk, mv, mdo, mdq, mdk, mdv, p, st);
 }

@@ -12,18 +12,23 @@
 // The tensor core alternates between the two query tiles:  P0 V -> S0(next) -> P1 V -> S1(next) -> ...  so while the
 // softmax threads of one tile turn scores into probabilities the other tile's products run. S_i lives in its own 128
 // TMEM columns; P_i (bf16) is written over the first 64 of them and consumed by tcgen05.mma as the TMEM operand; O_i
-// stays in TMEM for the whole key loop. A row's reference maximum is only moved when the new maximum exceeds it by
-// more than 2^8 (probabilities then stay below 256, exact in the final normalisation), so rescaling O is rare and is
-// done by the row's own softmax thread once the previous P V product has retired.
+// stays in TMEM for the whole key loop. A softmax thread walks its 128 score columns twice, 32 at a time with the next
+// tensor-memory load in flight (maximum, then probabilities with packed two-float arithmetic), so no score is spilled;
+// the first 64 probabilities are announced as soon as they are written and the P V product starts on them. A row's
+// reference maximum is only moved when the new maximum exceeds it by more than 2^8 (probabilities then stay below 256,
+// exact in the final normalisation), so rescaling O is rare and is done by the row's own softmax thread once the
+// previous P V product has retired.
 //
 // Masks: causal on positions, sliding window, chunked (block-local) attention, segment ids, keys beyond Skv. Positions
 // are token indices (queries offset by q_off) or come from arrays (context parallelism: the keys are a block of a
 // longer sequence); with arrays, per-tile (min, max) tables let every role skip fully masked key tiles. Optional logit
 // soft-cap and per-head sink logits. Every wait is bounded; a timeout records a status code and the CTA drains and exits.
 // The backward lives in attention_bwd_sm100.cu.
+#include "attention_mask.cuh"
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
-#include <limits.h>
+#include <type_traits>
+#include <stdlib.h>
 
 namespace mt {
 namespace fwd {
@@ -33,19 +38,12 @@ constexpr float LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.f;     // log2 units
 
 struct Params {
-  int B, Sq, Skv, Hq, Hkv;
-  int n_pairs;           // ceil(Sq / 256)
-  int n_kt;              // ceil(Skv / 128)
-  int q_off;             // index mode: position of query row i is i + q_off, of key row j is j
-  int causal, window, chunk;
+  int B, Hq, Hkv;
+  int n_pairs;           // CTAs per (batch, head): ceil(Sq / (128 * query tiles per CTA))
+  int head_major;        // CTA order: 1 = all query pairs of a head together, 0 = heaviest pairs of all heads first
+  attn::Mask mk;
   float scale;           // logits = scale * q.k
   float softcap;         // 0 = none; logits = softcap * tanh(scale * q.k / softcap)
-  const int* seg_q;      // [B,Sq]  segment ids (0 = padding) or nullptr
-  const int* seg_k;      // [B,Skv]
-  const int* pos_q;      // [B,Sq]  positions or nullptr (index mode)
-  const int* pos_k;      // [B,Skv]
-  const int* tile_q;     // [B, 2*n_pairs, 2] (min, max) position per 128-row query tile (array mode)
-  const int* tile_k;     // [B, n_kt, 2]
   const float* sinks;    // [Hq] or nullptr
   float* lse;            // [B,Hq,Sq]
   int* status;
@@ -73,53 +71,6 @@ struct alignas(8) Ctl {
   int pad[2];
 };
 
-// What one query tile sees of the key range: position bounds used to classify key tiles.
-struct QTile {
-  int q0;          // first query row
-  int rows;        // valid rows (0: the tile lies beyond Sq)
-  int pmin, pmax;  // smallest / largest query position in the tile
-};
-
-// 0: every (query, key) pair of the tile pair is masked -> skipped by all roles; 1: no pair is masked; 2: mixed.
-__device__ __forceinline__ int classify(const Params& p, const QTile& t, int b, int kt) {
-  if (t.rows == 0) return 0;
-  int kmin, kmax;
-  const int k0 = kt * 128;
-  const bool tail = k0 + 128 > p.Skv;
-  if (p.pos_k) {
-    kmin = p.tile_k[((long)b * p.n_kt + kt) * 2];
-    kmax = p.tile_k[((long)b * p.n_kt + kt) * 2 + 1];
-  } else {
-    kmin = k0;
-    kmax = tail ? p.Skv - 1 : k0 + 127;
-  }
-  if (p.causal && kmin > t.pmax) return 0;
-  if (p.window > 0 && t.pmin - kmax >= p.window) return 0;
-  bool full = !tail && !p.seg_q;
-  if (p.causal && kmax > t.pmin) full = false;
-  if (p.window > 0 && t.pmax - kmin >= p.window) full = false;
-  if (p.chunk > 0) {
-    const int c0 = t.pmin / p.chunk;
-    if (kmax < c0 * p.chunk && t.pmax / p.chunk == c0) return 0;        // keys end before the queries' chunk begins
-    if (!(t.pmax / p.chunk == c0 && kmin / p.chunk == c0 && kmax / p.chunk == c0)) full = false;
-  }
-  return full ? 1 : 2;
-}
-
-#define MT_TMEM_LD32(addr, arr, o)                                                                                         \
-  asm volatile(                                                                                                            \
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                            \
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                            \
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                            \
-      : "=r"(arr[o + 0]), "=r"(arr[o + 1]), "=r"(arr[o + 2]), "=r"(arr[o + 3]), "=r"(arr[o + 4]), "=r"(arr[o + 5]),        \
-        "=r"(arr[o + 6]), "=r"(arr[o + 7]), "=r"(arr[o + 8]), "=r"(arr[o + 9]), "=r"(arr[o + 10]), "=r"(arr[o + 11]),      \
-        "=r"(arr[o + 12]), "=r"(arr[o + 13]), "=r"(arr[o + 14]), "=r"(arr[o + 15]), "=r"(arr[o + 16]), "=r"(arr[o + 17]),  \
-        "=r"(arr[o + 18]), "=r"(arr[o + 19]), "=r"(arr[o + 20]), "=r"(arr[o + 21]), "=r"(arr[o + 22]), "=r"(arr[o + 23]),  \
-        "=r"(arr[o + 24]), "=r"(arr[o + 25]), "=r"(arr[o + 26]), "=r"(arr[o + 27]), "=r"(arr[o + 28]), "=r"(arr[o + 29]),  \
-        "=r"(arr[o + 30]), "=r"(arr[o + 31])                                                                               \
-      : "r"(addr)                                                                                                          \
-      : "memory")
-
 template <int DQK, int DV, int NQ>
 __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
                                                const CUtensorMap& map_o, const Params& p) {
@@ -138,51 +89,38 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
   int* sk_pos = reinterpret_cast<int*>(ctl + 1);         // [tile i][parity][128]
   int* sk_seg = sk_pos + 2 * 2 * 128;                    // [tile i][parity][128]
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
-  enum { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1, S_FULL0, S_FULL1, P_READY0, P_READY1,
-         PV_DONE0, PV_DONE1 };
+  enum { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1, S_FULL0, S_FULL1, PA_READY0, PA_READY1,
+         PV_DONE0, PV_DONE1, PB_READY0, PB_READY1 };
   auto bar = [&](int i) { return bar0 + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heaviest CTAs first: for causal masks the last query pairs see the most keys
   const int hb = p.Hq * p.B;
-  const int pair = p.n_pairs - 1 - (int)(blockIdx.x / hb);
-  const int h = (int)(blockIdx.x % hb) % p.Hq, b = (int)(blockIdx.x % hb) / p.Hq;
+  int pair, h, b;
+  if (p.head_major) {
+    pair = p.n_pairs - 1 - (int)(blockIdx.x % p.n_pairs);
+    h = (int)(blockIdx.x / p.n_pairs) % p.Hq; b = (int)(blockIdx.x / p.n_pairs) / p.Hq;
+  } else {
+    pair = p.n_pairs - 1 - (int)(blockIdx.x / hb);
+    h = (int)(blockIdx.x % hb) % p.Hq; b = (int)(blockIdx.x % hb) / p.Hq;
+  }
   const int hk = h / (p.Hq / p.Hkv);
 
-  QTile qt[NQ];
+  const attn::Mask& mk = p.mk;
+  attn::Span qt[NQ];
+  int q0s[NQ];
+  // key tiles [kt_lo, kt_hi) that any query tile of this CTA may need (exact in index mode, everything in array mode)
+  int kt_lo = INT_MAX, kt_hi = 0;
 #pragma unroll
   for (int i = 0; i < NQ; ++i) {
-    QTile& t = qt[i];
-    t.q0 = (pair * NQ + i) * 128;
-    t.rows = t.q0 >= p.Sq ? 0 : (p.Sq - t.q0 < 128 ? p.Sq - t.q0 : 128);
-    if (p.pos_q && t.rows) {
-      t.pmin = p.tile_q[((long)b * (p.n_pairs * NQ) + pair * NQ + i) * 2];
-      t.pmax = p.tile_q[((long)b * (p.n_pairs * NQ) + pair * NQ + i) * 2 + 1];
-    } else {
-      t.pmin = t.q0 + p.q_off;
-      t.pmax = t.q0 + (t.rows ? t.rows - 1 : 0) + p.q_off;
-    }
+    q0s[i] = (pair * NQ + i) * 128;
+    qt[i] = attn::q_span(mk, b, pair * NQ + i);
+    int lo, hi;
+    attn::k_tiles_for(mk, qt[i], lo, hi);
+    if (qt[i].rows) { kt_lo = lo < kt_lo ? lo : kt_lo; kt_hi = hi > kt_hi ? hi : kt_hi; }
   }
-  // key tiles [kt_lo, kt_hi) that any query tile of this CTA may need (exact in index mode, everything in array mode)
-  int kt_lo = 0, kt_hi = p.n_kt;
-  if (!p.pos_q) {
-    int lo = INT_MAX, hi = 0;
-#pragma unroll
-    for (int i = 0; i < NQ; ++i) {
-      if (!qt[i].rows) continue;
-      int l = 0, hh = p.n_kt;
-      if (p.causal) { hh = qt[i].pmax < 0 ? 0 : (qt[i].pmax / 128 + 1 < p.n_kt ? qt[i].pmax / 128 + 1 : p.n_kt); }
-      int lp = INT_MIN;
-      if (p.window > 0) lp = qt[i].pmin - p.window + 1;
-      if (p.chunk > 0 && qt[i].pmin >= 0) { const int c = (qt[i].pmin / p.chunk) * p.chunk; lp = lp > c ? lp : c; }
-      if (lp > 0) l = lp / 128;
-      lo = l < lo ? l : lo;
-      hi = hh > hi ? hh : hi;
-    }
-    kt_lo = lo == INT_MAX ? 0 : lo;
-    kt_hi = hi;
-    if (kt_hi < kt_lo) kt_hi = kt_lo;
-  }
+  if (kt_lo == INT_MAX) kt_lo = 0;
+  if (kt_hi < kt_lo) kt_hi = kt_lo;
   const int n_u = kt_hi - kt_lo;
 
   if (threadIdx.x == 0) {
@@ -190,7 +128,8 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
     mbar_init(bar(Q_FULL), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(K_FULL0 + s), 1); mbar_init(bar(V_FULL0 + s), 1); mbar_init(bar(K_EMPTY0 + s), 1); mbar_init(bar(V_EMPTY0 + s), 1);
-      mbar_init(bar(S_FULL0 + s), 1); mbar_init(bar(P_READY0 + s), 128); mbar_init(bar(PV_DONE0 + s), 1);
+      mbar_init(bar(S_FULL0 + s), 1); mbar_init(bar(PV_DONE0 + s), 1);
+      mbar_init(bar(PA_READY0 + s), 4); mbar_init(bar(PB_READY0 + s), 4);          // one arrival per softmax warp
     }
     fence_barrier_init();
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v); prefetch_tensormap(&map_o);
@@ -209,7 +148,7 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
 #pragma unroll
       for (int i = 0; i < NQ; ++i)
 #pragma unroll
-        for (int j = 0; j < NBQ; ++j) tma_load_3d(sQ + i * QT + j * 16384, &map_q, bar(Q_FULL), h * DQK + j * 64, qt[i].q0, b);
+        for (int j = 0; j < NBQ; ++j) tma_load_3d(sQ + i * QT + j * 16384, &map_q, bar(Q_FULL), h * DQK + j * 64, q0s[i], b);
       for (int u = 0; u < n_u; ++u) {
         const int s = u & 1;
         const uint32_t ph = (u >> 1) & 1;
@@ -233,7 +172,7 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
 #pragma unroll
       for (int i = 0; i < NQ; ++i) cnt[i] = 0;
       auto issue_s = [&](int i, int u) {
-        if (classify(p, qt[i], b, kt_lo + u) == 0) return;
+        if (attn::classify(mk, qt[i], attn::k_span(mk, b, kt_lo + u)) == 0) return;
         const uint32_t sk = sK + (u & 1) * QT;
 #pragma unroll
         for (int k = 0; k < DQK / 16; ++k) umma_f16_ss(tmem + COL_S + i * 128, kmajor(sQ + i * QT, k), kmajor(sk, k), idesc_qk, k != 0);
@@ -255,12 +194,18 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
         const uint32_t sv = sV + s * VT;
 #pragma unroll
         for (int i = 0; i < NQ; ++i) {
-          if (classify(p, qt[i], b, kt_lo + u) != 0) {
-            if (!mbar_wait(bar(P_READY0 + i), cnt[i] & 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          if (attn::classify(mk, qt[i], attn::k_span(mk, b, kt_lo + u)) != 0) {
+            // the probabilities arrive in two halves of 64 keys; the product starts on the first while the second is computed
+            if (!mbar_wait(bar(PA_READY0 + i), cnt[i] & 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
+            for (int k = 0; k < 4; ++k)
               umma_f16_ts(tmem + COL_O + i * 128, tmem + COL_S + i * 128 + k * 8, mnmajor(sv, k), idesc_pv, (cnt[i] | k) != 0);
+            if (!mbar_wait(bar(PB_READY0 + i), cnt[i] & 1, abort_flag, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int k = 4; k < 8; ++k)
+              umma_f16_ts(tmem + COL_O + i * 128, tmem + COL_S + i * 128 + k * 8, mnmajor(sv, k), idesc_pv, 1);
             umma_commit(bar(PV_DONE0 + i));
             ++cnt[i];
           }
@@ -285,122 +230,174 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     const uint32_t tS = tmem + lane_off + COL_S + i * 128;
     const uint32_t tO = tmem + lane_off + COL_O + i * 128;
-    const QTile t = qt[i];
-    const int qg = t.q0 + row;
+    const attn::Span t = qt[i];
+    const int tq0 = q0s[i];
+    const int qg = tq0 + row;
     const bool row_ok = row < t.rows;
-    const bool has_seg = p.seg_q != nullptr;
-    const bool arrays = p.pos_k != nullptr;
-    const int qpos = p.pos_q ? (row_ok ? p.pos_q[(long)b * p.Sq + qg] : 0) : qg + p.q_off;
-    const int my_seg = has_seg ? (row_ok ? p.seg_q[(long)b * p.Sq + qg] : 0) : 1;
-    // keys this row may attend to, as a closed position interval
-    int lo_p = INT_MIN, hi_p = INT_MAX - 1;
-    if (p.causal) hi_p = qpos;
-    if (p.window > 0) lo_p = qpos - p.window + 1;
-    if (p.chunk > 0) {
-      const int c = (qpos / p.chunk) * p.chunk;
-      lo_p = lo_p > c ? lo_p : c;
-      hi_p = hi_p < c + p.chunk - 1 ? hi_p : c + p.chunk - 1;
-    }
-    if (!arrays && hi_p > p.Skv - 1) hi_p = p.Skv - 1;
+    const bool has_seg = mk.seg_q != nullptr;
+    const bool arrays = mk.pos_k != nullptr;
     const bool cap = p.softcap > 0.f;
     const float a = cap ? p.softcap * LOG2E : p.scale * LOG2E;     // y = a * s' is the logit in log2 units
-    const float pre = cap ? p.scale / p.softcap : 1.f;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f;                                  // reference maximum (log2 units) and row sum
     int cnt = 0;
     bool ok = true;
-    for (int u = 0; u < n_u; ++u) {
-      const int kt = kt_lo + u;
-      const int cls = classify(p, t, b, kt);
-      if (cls == 0) continue;
-      const int k0 = kt * 128;
-      const int par = cnt & 1;
-      if (cls == 2 && (arrays || has_seg)) {
-        const int kg = k0 + wt;
-        if (arrays) sk_pos[(i * 2 + par) * 128 + wt] = kg < p.Skv ? p.pos_k[(long)b * p.Skv + kg] : INT_MAX;
-        if (has_seg) sk_seg[(i * 2 + par) * 128 + wt] = kg < p.Skv ? p.seg_k[(long)b * p.Skv + kg] : 0;
-        named_bar_sync(1 + i, 128);
+
+    auto max32 = [](const uint32_t (&r)[32]) {
+      float v0 = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+      float v1 = fmax3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
+#pragma unroll
+      for (int e = 6; e < 30; e += 4) {
+        v0 = fmax3(v0, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+        v1 = fmax3(v1, __uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
       }
-      if (ok && !mbar_wait(bar(S_FULL0 + i), cnt & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ok = false;
-      if (!ok) { ++cnt; continue; }
-      tc_fence_after();
-      uint32_t sr[128];
-      MT_TMEM_LD32(tS, sr, 0);
-      MT_TMEM_LD32(tS + 32, sr, 32);
-      MT_TMEM_LD32(tS + 64, sr, 64);
-      MT_TMEM_LD32(tS + 96, sr, 96);
-      tmem_ld_wait();
-      if (cap) {
-#pragma unroll
-        for (int e = 0; e < 128; ++e) sr[e] = __float_as_uint(fast_tanh(__uint_as_float(sr[e]) * pre));
+      return fmax3(v0, v1, fmaxf(__uint_as_float(r[30]), __uint_as_float(r[31])));
+    };
+
+    // One key tile of this row in two passes over its 128 score columns (maximum, then probabilities), 32 columns at a time so
+    // that a row never holds more than two chunks in registers. MASKED tiles (and soft-capped logits) take the same route with
+    // the mask state derived here, so the unmasked fast path carries none of it.
+    auto tile = [&](auto masked_t, int k0, int par) {
+      constexpr bool MASKED = decltype(masked_t)::value;
+      int lo_p = 0, my_seg = 1;
+      uint32_t span = 0;
+      bool none = false;
+      [[maybe_unused]] const bool has_seg = MASKED && mk.seg_q != nullptr;
+      [[maybe_unused]] const bool arrays = MASKED && mk.pos_k != nullptr;
+      float pre = 1.f;
+      if constexpr (MASKED) {
+        const int qpos = mk.pos_q ? (row_ok ? mk.pos_q[(long)b * mk.Sq + qg] : 0) : qg + mk.q_off;
+        if (has_seg) my_seg = row_ok ? mk.seg_q[(long)b * mk.Sq + qg] : 0;
+        int hi_p;
+        attn::key_interval(mk, qpos, lo_p, hi_p);                   // keys this row may attend to, as a closed position interval
+        span = (uint32_t)hi_p - (uint32_t)lo_p;                     // lo_p <= position <= hi_p as one unsigned comparison
+        none = hi_p < lo_p;
+        if (cap) pre = p.scale / p.softcap;
       }
-      if (cls == 2) {
-        // lo_p <= key position <= hi_p as one unsigned comparison (wrap-around arithmetic)
-        const uint32_t span = (uint32_t)hi_p - (uint32_t)lo_p;
-        const bool none = hi_p < lo_p;
-        if (arrays) {
-          const int* kp = sk_pos + (i * 2 + par) * 128;
+      // soft-cap and mask of 32 score columns starting at column c0 of the tile
+      auto prepare = [&](uint32_t (&r)[32], int c0) {
+        if constexpr (MASKED) {
+          if (cap) {
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
-            if ((uint32_t)kp[e] - (uint32_t)lo_p > span || none) sr[e] = 0xff800000u;
-        } else {
-          const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)k0;
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(fast_tanh(__uint_as_float(r[e]) * pre));
+          }
+          if (arrays) {
+            const int* kp = sk_pos + (i * 2 + par) * 128 + c0;
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
-            if ((uint32_t)e - e_lo > span || none) sr[e] = 0xff800000u;
+            for (int e = 0; e < 32; ++e)
+              if ((uint32_t)kp[e] - (uint32_t)lo_p > span || none) r[e] = 0xff800000u;
+          } else {
+            const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)(k0 + c0);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((uint32_t)e - e_lo > span || none) r[e] = 0xff800000u;
+          }
+          if (has_seg) {
+            const int* ks = sk_seg + (i * 2 + par) * 128 + c0;
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (ks[e] != my_seg || my_seg == 0) r[e] = 0xff800000u;
+          }
         }
-        if (has_seg) {
-          const int* ks = sk_seg + (i * 2 + par) * 128;
-#pragma unroll
-          for (int e = 0; e < 128; ++e)
-            if (ks[e] != my_seg || my_seg == 0) sr[e] = 0xff800000u;
-        }
-      }
-      float mx[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float v = fmax3(__uint_as_float(sr[32 * j]), __uint_as_float(sr[32 * j + 1]), __uint_as_float(sr[32 * j + 2]));
-#pragma unroll
-        for (int e = 3; e < 31; e += 2) v = fmax3(v, __uint_as_float(sr[32 * j + e]), __uint_as_float(sr[32 * j + e + 1]));
-        mx[j] = fmaxf(v, __uint_as_float(sr[32 * j + 31]));
-      }
-      const float mt_ = a * fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));      // -inf when the whole row is masked
-      const bool grow = mt_ > m + RESCALE_THRESHOLD;                              // m = -inf: any finite maximum grows it
+      };
+      // pass 1: exact row maximum of the tile; the loads run one 32-column chunk ahead of the arithmetic
+      uint32_t r0[32], r1[32];
+      float tmax;
+      tmem_ld_32x32b_x32(tS, r0);
+      tmem_ld_wait_dep(r0);
+      tmem_ld_32x32b_x32(tS + 32, r1);
+      prepare(r0, 0);
+      tmax = max32(r0);
+      tmem_ld_wait_dep(r1);
+      tmem_ld_32x32b_x32(tS + 64, r0);
+      prepare(r1, 32);
+      tmax = fmaxf(tmax, max32(r1));
+      tmem_ld_wait_dep(r0);
+      tmem_ld_32x32b_x32(tS + 96, r1);
+      prepare(r0, 64);
+      tmax = fmaxf(tmax, max32(r0));
+      tmem_ld_wait_dep(r1);
+      tmem_ld_32x32b_x32(tS, r0);              // first chunk of pass 2
+      prepare(r1, 96);
+      tmax = fmaxf(tmax, max32(r1));
+      const float mt_ = a * tmax;                                    // -inf when the whole row is masked
+      const bool grow = mt_ > m + RESCALE_THRESHOLD;                 // m = -inf: any finite maximum grows it
       if (__any_sync(0xffffffffu, grow)) {
         const float alpha = grow ? fast_exp2(m - mt_) : 1.f;
         if (cnt > 0) {
           // O may only be touched once the previous P V product of this tile has retired
-          if (!mbar_wait(bar(PV_DONE0 + i), (cnt - 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; ++cnt; continue; }
+          if (!mbar_wait(bar(PV_DONE0 + i), (cnt - 1) & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; return; }
           tc_fence_after();
+          tmem_ld_wait_dep(r0);
 #pragma unroll 1
           for (int c = 0; c < DV / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tO + c * 32, r);
-            tmem_ld_wait();
+            tmem_ld_32x32b_x32(tO + c * 32, r1);
+            tmem_ld_wait_dep(r1);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-            tmem_st_32x32b_x32(tO + c * 32, r);
+            for (int e = 0; e < 32; ++e) r1[e] = __float_as_uint(__uint_as_float(r1[e]) * alpha);
+            tmem_st_32x32b_x32(tO + c * 32, r1);
           }
         }
         if (grow) { l *= alpha; m = mt_; }
       }
+      // pass 2: probabilities, written over the row's own (already read) score columns chunk by chunk
       const float neg = (m == -INFINITY) ? 0.f : -m;
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      // packed two-float arithmetic (fma.f32x2 / add.f32x2): half the issue slots of the scale-and-shift and of the row sum
+      const float2 a2 = make_float2(a, a), neg2 = make_float2(neg, neg);
+      float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
+      auto exps = [&](uint32_t (&r)[32], int c) {
+        prepare(r, c * 32);
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = fast_exp2(fmaf(a, __uint_as_float(sr[c * 32 + 2 * e]), neg));
-          const float p1 = fast_exp2(fmaf(a, __uint_as_float(sr[c * 32 + 2 * e + 1]), neg));
-          rs[e & 3] += p0 + p1;
-          pk[e] = pack_bf16(p0, p1);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])), a2, neg2);
+          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          if (e & 1) rsb = __fadd2_rn(rsb, pp); else rsa = __fadd2_rn(rsa, pp);
+          pk[e] = pack_bf16(pp.x, pp.y);
         }
-        tmem_st_32x32b_x16(tS + c * 16, pk);       // P over this row's own (already read) score columns
-      }
-      l += (rs[0] + rs[1]) + (rs[2] + rs[3]);
+        tmem_st_32x32b_x16(tS + c * 16, pk);
+      };
+      tmem_ld_wait_dep(r0);
+      tmem_ld_32x32b_x32(tS + 32, r1);
+      exps(r0, 0);
+      tmem_ld_wait_dep(r1);
+      tmem_ld_32x32b_x32(tS + 64, r0);
+      exps(r1, 1);
+      tmem_ld_wait_dep(r0);
+      tmem_ld_32x32b_x32(tS + 96, r1);
+      // the first 64 keys' probabilities are in place: the P V product may start on them
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(P_READY0 + i));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PA_READY0 + i));
+      exps(r0, 2);
+      tmem_ld_wait_dep(r1);
+      exps(r1, 3);
+      l += (rsa.x + rsa.y) + (rsb.x + rsb.y);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PB_READY0 + i));
+    };
+
+    for (int u = 0; u < n_u; ++u) {
+      const int kt = kt_lo + u;
+      const int cls = attn::classify(mk, t, attn::k_span(mk, b, kt));
+      if (cls == 0) continue;
+      const int k0 = kt * 128;
+      const int par = cnt & 1;
+      const bool masked = cls == 2 || cap;
+      if (masked && (mk.pos_k != nullptr || mk.seg_q != nullptr)) {
+        const int kg = k0 + wt;
+        if (mk.pos_k) sk_pos[(i * 2 + par) * 128 + wt] = kg < mk.Skv ? mk.pos_k[(long)b * mk.Skv + kg] : INT_MAX;
+        if (mk.seg_q) sk_seg[(i * 2 + par) * 128 + wt] = kg < mk.Skv ? mk.seg_k[(long)b * mk.Skv + kg] : 0;
+        named_bar_sync(1 + i, 128);
+      }
+      if (ok && !mbar_wait(bar(S_FULL0 + i), cnt & 1, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) ok = false;
+      if (ok) {
+        tc_fence_after();
+        if (masked) tile(std::true_type{}, k0, par);
+        else tile(std::false_type{}, k0, par);
+      }
       ++cnt;
     }
     // ---------------------------------------------------------------- epilogue of this query tile
@@ -438,13 +435,13 @@ __device__ __forceinline__ void flash_fwd_body(const CUtensorMap& map_q, const C
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o4[0]), "r"(o4[1]), "r"(o4[2]), "r"(o4[3]) : "memory");
           }
         }
-        if (row_ok && p.lse) p.lse[((long)b * p.Hq + h) * p.Sq + qg] = (lt > 0.f) ? (m + log2f(lt)) * LN2 : -INFINITY;
+        if (row_ok && p.lse) p.lse[((long)b * p.Hq + h) * mk.Sq + qg] = (lt > 0.f) ? (m + log2f(lt)) * LN2 : -INFINITY;
         fence_proxy_async_smem();
       }
       named_bar_sync(1 + i, 128);
       if (wt == 0 && *abort_flag == 0) {
 #pragma unroll
-        for (int j = 0; j < NBV; ++j) tma_store_3d(&map_o, sQ + i * QT + j * 16384, h * DV + j * 64, t.q0, b);
+        for (int j = 0; j < NBV; ++j) tma_store_3d(&map_o, sQ + i * QT + j * 16384, h * DV + j * 64, tq0, b);
         tma_commit_group();
         tma_wait_group<0>();
       }
@@ -534,11 +531,13 @@ extern "C" {
 // Shapes this kernel covers: (Dqk, Dv) in {(64,64), (128,128), (192,128)}.
 int mt_flash_fwd_supported(int Dqk, int Dv) { return (Dqk == 64 && Dv == 64) || (Dqk == 128 && Dv == 128) || (Dqk == 192 && Dv == 128); }
 
-// ints of scratch (`tiles`) that mt_flash_fwd needs when position arrays are given
-long mt_flash_fwd_tile_ints(int B, int Sq, int Skv, int Dqk) {
-  const int nq = Dqk == 192 ? 1 : 2;
-  const long n_pairs = (Sq + 128 * nq - 1) / (128 * nq);
-  return 2l * B * (n_pairs * nq + (Skv + 127) / 128);
+// ints of scratch (`tiles`) that the attention kernels need when position arrays are given
+long mt_attn_tile_ints(int B, int Sq, int Skv) { return 2l * B * ((Sq + 127) / 128 + (Skv + 127) / 128); }
+
+// (min, max) position of every 128-token tile of pos [B, S] -> out [B, ceil(S/128), 2]
+void mt_attn_tile_minmax(const int* pos, int B, int S, int* out, cudaStream_t st) {
+  const int nt = (S + 127) / 128;
+  mt::fwd::tile_minmax_kernel<<<(B * nt * 32 + 255) / 256, 256, 0, st>>>(pos, B, S, nt, out);
 }
 
 // q/k/v/out: token-major views; ld* = row stride, bs* = batch stride (elements). seg_q/seg_k, pos_q/pos_k, sinks may be null;
@@ -557,19 +556,19 @@ int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
     return -3;
   const int nq = Dqk == 192 ? 1 : 2;
   Params p{};
-  p.B = B; p.Sq = Sq; p.Skv = Skv; p.Hq = Hq; p.Hkv = Hkv;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv;
   p.n_pairs = (Sq + 128 * nq - 1) / (128 * nq);
-  p.n_kt = (Skv + 127) / 128;
-  p.q_off = q_off; p.causal = causal; p.window = window; p.chunk = chunk;
-  p.scale = scale; p.softcap = softcap;
-  p.seg_q = seg_q; p.seg_k = seg_k; p.pos_q = pos_q; p.pos_k = pos_k; p.sinks = sinks; p.lse = lse; p.status = status;
+  p.scale = scale; p.softcap = softcap; p.sinks = sinks; p.lse = lse; p.status = status;
+  p.head_major = getenv("MT_ATTN_HEAD_MAJOR") ? 1 : 0;
+  mt::attn::Mask& msk = p.mk;
+  msk.Sq = Sq; msk.Skv = Skv; msk.n_qt = (Sq + 127) / 128; msk.n_kt = (Skv + 127) / 128;
+  msk.q_off = q_off; msk.causal = causal; msk.window = window; msk.chunk = chunk;
+  msk.seg_q = seg_q; msk.seg_k = seg_k; msk.pos_q = pos_q; msk.pos_k = pos_k;
   if (pos_q) {
-    const int ntq = p.n_pairs * nq;
-    int* tq = tiles;
-    int* tk = tiles + 2l * B * ntq;
-    tile_minmax_kernel<<<(B * ntq * 32 + 255) / 256, 256, 0, st>>>(pos_q, B, Sq, ntq, tq);
-    tile_minmax_kernel<<<(B * p.n_kt * 32 + 255) / 256, 256, 0, st>>>(pos_k, B, Skv, p.n_kt, tk);
-    p.tile_q = tq; p.tile_k = tk;
+    mt_attn_tile_minmax(pos_q, B, Sq, tiles, st);
+    mt_attn_tile_minmax(pos_k, B, Skv, tiles + 2l * B * msk.n_qt, st);
+    msk.tile_q = tiles;
+    msk.tile_k = tiles + 2l * B * msk.n_qt;
   }
   if (Dqk == 128) return run<128, 128, 2>(mq, mk, mv, mo, p, st);
   if (Dqk == 64) return run<64, 64, 2>(mq, mk, mv, mo, p, st);

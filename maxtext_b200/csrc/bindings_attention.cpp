@@ -6,14 +6,16 @@
 
 extern "C" {
 int mt_flash_fwd_supported(int Dqk, int Dv);
-long mt_flash_fwd_tile_ints(int B, int Sq, int Skv, int Dqk);
+long mt_attn_tile_ints(int B, int Sq, int Skv);
 int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* seg_q, const int* seg_k, const int* pos_q,
                  const int* pos_k, int* tiles, const float* sinks, int B, int Sq, int Skv, int Hq, int Hkv, int Dqk, int Dv, long ldq, long bsq,
                  long ldk, long bsk, long ldv, long bsv, long ldo, long bso, float scale, float softcap, int causal, int window, int chunk,
                  int q_off, int* status, cudaStream_t st);
+int mt_flash_bwd_supported(int Dqk, int Dv);
 int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, void* dq,
-                 void* dk, void* dv, const int* seg, int B, int S, int Hq, int Hkv, int D, long ldq, long ldk, long ldv, long lddq,
-                 long lddk, long lddv, float scale, int window, int* status, cudaStream_t st);
+                 void* dk, void* dv, const int* seg_q, const int* seg_k, const int* pos_q, const int* pos_k, int* tiles, int B, int Sq, int Skv,
+                 int Hq, int Hkv, int D, long ldq, long bsq, long ldk, long bsk, long ldv, long bsv, long lddq, long bsdq, long lddk, long bsdk,
+                 long lddv, long bsdv, float scale, float softcap, int causal, int window, int chunk, int q_off, int* status, cudaStream_t st);
 }
 
 extern "C" int mt_decode_attention(const void* q, const void* k_cache, const void* v_cache, const int* slot_ids, const int* lengths, int B,
@@ -25,21 +27,6 @@ int* mt_status_ptr();          // defined in bindings.cpp
 void mt_count_launches(int n); // defined in bindings.cpp
 
 namespace {
-
-// [B,S,H,D] view whose tokens are consecutive rows of one 2-D tensor: strides (S*ld, ld, D, 1)
-bool token_major(const torch::Tensor& t) {
-  return t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(0) == t.size(1) * t.stride(1) &&
-         t.stride(1) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0 && t.scalar_type() == torch::kBFloat16;
-}
-
-bool flash_supported(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v) {
-  if (!q.is_cuda() || !token_major(q) || !token_major(k) || !token_major(v)) return false;
-  const int64_t D = q.size(3);
-  if ((D != 128 && D != 64) || k.size(3) != D || v.size(3) != D) return false;
-  if (q.size(1) % 128 || k.size(1) != q.size(1) || v.size(1) != q.size(1)) return false;
-  if (k.size(2) != v.size(2) || q.size(2) % k.size(2)) return false;
-  return true;
-}
 
 // [B,S,H,D] view usable as a {H*D, S, B} TMA tensor: unit inner stride, heads adjacent, 16-byte aligned row / batch strides
 bool tma_view(const torch::Tensor& t) {
@@ -73,7 +60,7 @@ void flash_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tens
   if (sinks) TORCH_CHECK(sinks->is_cuda() && sinks->is_contiguous() && sinks->scalar_type() == torch::kFloat32 && sinks->numel() == Hq);
   c10::cuda::CUDAGuard guard(q.device());
   torch::Tensor tiles;
-  if (pos_q) tiles = torch::empty({mt_flash_fwd_tile_ints(B, Sq, Skv, (int)q.size(3))}, torch::dtype(torch::kInt32).device(q.device()));
+  if (pos_q) tiles = torch::empty({mt_attn_tile_ints(B, Sq, Skv)}, torch::dtype(torch::kInt32).device(q.device()));
   int rc = mt_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), opt_int(seg_q, (int64_t)B * Sq, "seg_q"),
                         opt_int(seg_k, (int64_t)B * Skv, "seg_k"), opt_int(pos_q, (int64_t)B * Sq, "pos_q"), opt_int(pos_k, (int64_t)B * Skv, "pos_k"),
                         pos_q ? tiles.data_ptr<int>() : nullptr, sinks ? sinks->data_ptr<float>() : nullptr, B, Sq, Skv, Hq, (int)k.size(2),
@@ -84,20 +71,33 @@ void flash_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tens
   mt_count_launches(pos_q ? 3 : 1);
 }
 
+bool flash_bwd_supported(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v) {
+  return flash_fwd_supported(q, k, v) && mt_flash_bwd_supported((int)q.size(3), (int)v.size(3));
+}
+
 void flash_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& out,
-               const torch::Tensor& lse, torch::Tensor& dq, torch::Tensor& dk, torch::Tensor& dv, const c10::optional<torch::Tensor>& seg,
-               double scale, int64_t window) {
-  TORCH_CHECK(flash_supported(q, k, v) && token_major(dq) && token_major(dk) && token_major(dv));
-  TORCH_CHECK(dout.is_contiguous() && out.is_contiguous() && lse.is_contiguous());
+               const torch::Tensor& lse, torch::Tensor& dq, torch::Tensor& dk, torch::Tensor& dv, const c10::optional<torch::Tensor>& seg_q,
+               const c10::optional<torch::Tensor>& seg_k, const c10::optional<torch::Tensor>& pos_q, const c10::optional<torch::Tensor>& pos_k,
+               double scale, double softcap, bool causal, int64_t window, int64_t chunk, int64_t q_off) {
+  TORCH_CHECK(flash_bwd_supported(q, k, v) && tma_view(dq) && tma_view(dk) && tma_view(dv));
+  TORCH_CHECK(dq.sizes() == q.sizes() && dk.sizes() == k.sizes() && dv.sizes() == v.sizes());
+  TORCH_CHECK(dout.is_contiguous() && out.is_contiguous() && lse.is_contiguous() && dout.sizes() == out.sizes() &&
+              dout.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kBFloat16 && lse.scalar_type() == torch::kFloat32);
+  TORCH_CHECK(bool(seg_q) == bool(seg_k) && bool(pos_q) == bool(pos_k), "segment ids / positions must be given for queries and keys together");
+  const int B = (int)q.size(0), Sq = (int)q.size(1), Skv = (int)k.size(1), Hq = (int)q.size(2);
+  TORCH_CHECK(lse.numel() == (int64_t)B * Hq * Sq && out.size(0) == B && out.size(1) == Sq && out.size(2) == Hq && out.size(3) == v.size(3));
   c10::cuda::CUDAGuard guard(q.device());
-  auto delta = torch::empty({q.size(0), q.size(2), q.size(1)}, lse.options());
-  int rc = mt_flash_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(),
-                        delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), seg ? seg->data_ptr<int>() : nullptr,
-                        (int)q.size(0), (int)q.size(1), (int)q.size(2), (int)k.size(2), (int)q.size(3), q.stride(1), k.stride(1),
-                        v.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), (float)scale, (int)window, mt_status_ptr(),
-                        at::cuda::getCurrentCUDAStream().stream());
+  auto delta = torch::empty({B, Hq, Sq}, lse.options());
+  torch::Tensor tiles;
+  if (pos_q) tiles = torch::empty({mt_attn_tile_ints(B, Sq, Skv)}, torch::dtype(torch::kInt32).device(q.device()));
+  int rc = mt_flash_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), opt_int(seg_q, (int64_t)B * Sq, "seg_q"), opt_int(seg_k, (int64_t)B * Skv, "seg_k"),
+                        opt_int(pos_q, (int64_t)B * Sq, "pos_q"), opt_int(pos_k, (int64_t)B * Skv, "pos_k"), pos_q ? tiles.data_ptr<int>() : nullptr,
+                        B, Sq, Skv, Hq, (int)k.size(2), (int)q.size(3), q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+                        dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), (float)scale, (float)softcap,
+                        causal ? 1 : 0, (int)window, (int)chunk, (int)q_off, mt_status_ptr(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "mt_flash_bwd failed with code ", rc);
-  mt_count_launches(3);
+  mt_count_launches(pos_q ? 5 : 3);
 }
 
 // q [B, Hq, D], caches [slots, max_len, Hkv, D] (bf16), slot_ids / lengths int32 [B] (lengths include the new token); out [B, Hq, D].
@@ -122,8 +122,8 @@ void decode_attention(const torch::Tensor& q, const torch::Tensor& k_cache, cons
 
 void register_attention(pybind11::module_& m) {
   m.def("decode_attention", &decode_attention);
-  m.def("flash_supported", &flash_supported);
   m.def("flash_fwd_supported", &flash_fwd_supported);
+  m.def("flash_bwd_supported", &flash_bwd_supported);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
 }

@@ -407,11 +407,19 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
     # d loss / d sink_h = -sum_{b,q} p_sink * delta, with p_sink = exp(sink - lse) and delta = rowsum(dO * O)
     delta = (dout.float() * out.float()).sum(-1).permute(0, 2, 1)                 # [B, Hq, Sq]
     dsinks = -(torch.exp(sinks.detach().float()[None, :, None] - lse) * delta).sum((0, 2)).to(sinks.dtype)
-  if backend.use_cuda_kernels(q) and kv_positions is None and not chunk:
+  if backend.use_cuda_kernels(q) and lse is not None and q.dtype == torch.bfloat16:
     E = backend.ext()
-    if hasattr(E, "flash_bwd") and _flash_ok(q, k, v, soft_cap) and causal and lse is not None and E.flash_supported(q, k, v):
-      seg = segment_ids.to(torch.int32).contiguous() if segment_ids is not None else None
-      E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, float(scale), int(window))
+    if E.flash_bwd_supported(q, k, v) and E.flash_fwd_supported(dq, dk, dv):
+      seg_q = _i32(segment_ids)
+      seg_k = _i32(kv_segment_ids) if kv_segment_ids is not None else seg_q
+      if seg_q is None:
+        seg_k = None
+      by_arrays = kv_positions is not None or (chunk and segment_ids is not None)
+      pos_q = _i32(positions) if by_arrays else None
+      pos_k = _i32(kv_positions if kv_positions is not None else positions) if by_arrays else None
+      E.flash_bwd(dout if dout.is_contiguous() else dout.contiguous(), q, k, v, out if out.is_contiguous() else out.contiguous(), lse, dq, dk, dv,
+                  seg_q, seg_k, pos_q, pos_k, float(scale), float(soft_cap or 0.0), bool(causal), int(window or 0), int(chunk or 0),
+                  int(k.shape[1] - q.shape[1]) if not by_arrays else 0)
       return dsinks
   kpos = kv_positions if kv_positions is not None else positions
   kseg = kv_segment_ids if kv_segment_ids is not None else segment_ids

@@ -37,7 +37,7 @@ def _case(B, S, Hq, Hkv, D, seg_mode=None, window=0, scale=1.0, packed=True, see
     seg[:, S // 3:] = 2
     seg[:, (2 * S) // 3 + 5:] = 3
     seg[1, -17:] = 0     # padding tail
-  assert E.flash_supported(q, k, v)
+  assert E.flash_bwd_supported(q, k, v)
   out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
   lse = torch.empty(B, Hq, S, device="cuda")
   E.flash_fwd(q, k, v, out, lse, seg, seg, None, None, None, scale, 0.0, True, window, 0, 0)
@@ -58,7 +58,7 @@ def _case(B, S, Hq, Hkv, D, seg_mode=None, window=0, scale=1.0, packed=True, see
     dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
   else:
     dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
-  E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, scale, window)
+  E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, seg, seg, None, None, scale, 0.0, True, window, 0, 0)
   torch.cuda.synchronize()
   assert E.kernel_status(True) == 0, "bounded wait timed out in a backward kernel"
   for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
@@ -142,7 +142,7 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, window):
 
 
 def _fwd_general(B, Sq, Skv, Hq, Hkv, Dqk, Dv, *, causal=True, window=0, chunk=0, softcap=0.0, sinks=False, seg=False, arrays=False,
-                 scale=0.25, seed=0):
+                 scale=0.25, seed=0, grads=True):
   """Forward kernel against the fp32 definition for the general mask / shape forms (the public op of ops.functional)."""
   from maxtext_b200.ops import functional as F
   E = _E()
@@ -184,6 +184,24 @@ def _fwd_general(B, Sq, Skv, Hq, Hkv, Dqk, Dv, *, causal=True, window=0, chunk=0
   assert lerr <= 2e-2, f"lse max err {lerr}"
   if not sinks and (~rows).any():
     assert out.float()[~rows].abs().max().item() == 0.0        # fully masked rows give zeros, not NaN
+  if not grads:
+    return
+  # backward through the public op (kernels where they cover the shape) against autograd of the fp32 definition
+  dout = torch.randn(B, Sq, Hq, Dv, device="cuda", generator=g).bfloat16() * rows[:, :, None, None]
+  ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+  skl = sk.detach().clone().requires_grad_(True) if sinks else None
+  o2 = F.attention(ql, kl, vl, pos_q, seg_q, scale, softcap, window, causal, chunk=chunk, sinks=skl, **kw)
+  o2.backward(dout)
+  torch.cuda.synchronize()
+  assert E.kernel_status(True) == 0
+  qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+  skf = sk.detach().clone().requires_grad_(True) if sinks else None
+  ref.attention(qf, kf, vf, mask, scale, softcap, sinks=skf).backward(dout.float())
+  pairs = [("dq", ql.grad, qf.grad), ("dk", kl.grad, kf.grad), ("dv", vl.grad, vf.grad)] + ([("dsinks", skl.grad, skf.grad)] if sinks else [])
+  for name, got, want in pairs:
+    e = (got.float() - want).abs().max().item()
+    sc = want.abs().max().item()
+    assert e <= 3e-2 * max(1.0, sc), f"{name}: max err {e} (scale {sc})"
 
 
 def test_fwd_ragged_lengths_not_multiples_of_the_tile():

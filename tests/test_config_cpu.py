@@ -118,3 +118,64 @@ def test_legacy_sequence_degree_folds_into_context():
   c = tiny_config("llama3-8b", ["ici_sequence_parallelism=2", "ici_fsdp_parallelism=2"], num_devices=4)
   shape = dict(zip(c.mesh_axes, c.mesh_shape))
   assert shape["context"] == 2 and shape["fsdp"] == 2 and "sequence" not in shape
+
+
+REJECTED = [
+    (["load_parameters_path=/a", "load_full_state_path=/b"], "At most one of"),
+    (["enable_emergency_checkpoint=true"], "local_checkpoint_directory"),
+    (["enable_emergency_checkpoint=true", "local_checkpoint_directory=/tmp/x", "local_checkpoint_period=0"], "local_checkpoint_period"),
+    (["attention_type=chunk", "chunk_attn_window_size=0"], "chunk_attn_window_size"),
+    (["attention_type=local_sliding", "sliding_window_size=0"], "sliding_window_size"),
+    (["mla_qk_head_chunk_size=3"], "mla_qk_head_chunk_size"),
+    (["use_indexer=true"], "attention_type='mla'"),
+    (["use_qk_clip=true"], "QK-Clip is only supported"),
+    (["share_kv_projections=true", "fused_qkv=true"], "fused_qkv"),
+    (["num_kv_shared_layers=1", "fused_qkv=true"], "num_kv_shared_layers"),
+    (["quantize_kvcache=true", "kv_quant_axis="], "kv_quant_axis"),
+    (["attention_type=block_diffusion", "packing=true"], "does not support packing"),
+    (["training_objective=block_diffusion", "packing=false"], "requires `attention_type='block_diffusion'`"),
+    (["training_objective=block_diffusion", "attention_type=block_diffusion", "packing=false", "block_diffusion_mask_id=999999"], "block_diffusion_mask_id"),
+    (["quantization=fp8", "gradient_accumulation_steps=2"], "gradient accumulation"),
+    (["use_batch_split_schedule=true", "quantization=int8"], "fp8_full"),
+    (["use_manual_quantization=true"], "use_batch_split_schedule"),
+    (["num_experts=4", "num_experts_per_tok=2", "routed_bias=true", "routed_bias_update_rate=0.1"], "Loss-free load balancing"),
+    (["num_experts=4", "num_experts_per_tok=2", "num_moe_token_chunks=3", "max_target_length=32"], "num_moe_token_chunks"),
+    (["decoder_block=llama4", "num_experts=4", "num_experts_per_tok=2"], "top-1 routing"),
+    (["decoder_block=llama4", "num_experts=4", "num_experts_per_tok=1", "capacity_factor=1.0"], "capacity_factor"),
+    (["partial_rotary_factor=0.5"], "partial_rotary_factor"),
+    (["decoder_block=qwen3_next", "gdn_num_value_heads=3", "gdn_num_key_heads=2"], "gdn_num_value_heads"),
+    (["use_multimodal=true"], "Multimodal is only supported"),
+    (["use_sft=true", "use_dpo=true", "packing=false"], "Only one of"),
+    (["use_dpo=true", "packing=true"], "DPO does not support packing"),
+    (["num_vocab_tiling=7"], "vocab tiles"),
+    (["ring_scan_unroll=2", "context_parallel_strategy=all_gather"], "ring_scan_unroll"),
+    (["dcn_data_parallelism=2"], "dcn degrees"),
+    (["enable_streaming_diloco=true", "scan_layers=false"], "scan_layers=True"),
+]
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("overrides,fragment", REJECTED, ids=[r[1][:28].replace(" ", "_") for r in REJECTED])
+def test_illegal_combinations_are_rejected_at_parse_time(overrides, fragment):
+  """One case per cross-field rule: the config layer refuses the combination and names the offending keys."""
+  from helpers import tiny_config
+  from maxtext_b200.config.types import ConfigValueError
+  with pytest.raises((ConfigValueError, ValueError)) as e:
+    tiny_config(extra=list(overrides))
+  assert fragment in str(e.value), str(e.value)
+
+
+def test_multi_device_rules_are_rejected_at_parse_time():
+  from helpers import tiny_config
+  from maxtext_b200.config.types import ConfigValueError
+  for over, frag, n in [
+      (["ici_tensor_parallelism=4", "ici_fsdp_parallelism=1", "base_num_query_heads=6", "base_num_kv_heads=2"], "num_query_heads", 4),
+      (["ici_expert_parallelism=4", "ici_fsdp_parallelism=1", "num_experts=6", "num_experts_per_tok=2"], "num_experts", 4),
+      (["ici_tensor_sequence_parallelism=2", "ici_context_parallelism=2", "ici_fsdp_parallelism=1"], "tensor_sequence parallelism cannot", 4),
+      (["ici_context_parallelism=2", "ici_fsdp_parallelism=1", "context_parallel_strategy=ulysses", "base_num_kv_heads=1", "base_num_query_heads=4"], "MQA", 2),
+  ]:
+    with pytest.raises((ConfigValueError, ValueError)) as e:
+      tiny_config(extra=over, num_devices=n)
+    assert frag in str(e.value), (over, str(e.value))

@@ -107,7 +107,7 @@ def test_use_dpo_through_the_train_cli(tmp_path):
   p = tmp_path / "pref.jsonl"
   p.write_text("\n".join(json.dumps({"prompt": f"q{i} ", "chosen": "yes yes", "rejected": "no no no"}) for i in range(8)))
   args = [a for a in TINY if not a.startswith(("steps", "dataset_type", "learning_rate=", "vocab_size", "per_device_batch_size"))] + [
-      "model_name=llama3-8b", "steps=6", "use_dpo=true", "dataset_type=hf", f"hf_train_files={p}", "tokenizer_type=byte", "vocab_size=260",
+      "model_name=llama3-8b", "steps=6", "use_dpo=true", "packing=false", "dataset_type=hf", f"hf_train_files={p}", "tokenizer_type=byte", "vocab_size=260",
       "per_device_batch_size=4", "learning_rate=5e-3", f"base_output_directory={tmp_path}", "run_name=dpo"]
   _, hist = TR.main(["train", BASE_YML] + args)
   acc = [float(h["dpo/reward_accuracy"]) for h in hist]
@@ -126,3 +126,157 @@ def test_distillation_weight_schedules():
   import pytest
   with pytest.raises(ValueError):
     scheduled(1, 10, 1.0, 0.0, "step")
+
+
+def test_hooked_loop_calls_callbacks_in_order_and_stops_at_target_eval_loss():
+  """The shared post-training loop: data hooks feed batches, training hooks see start / step / eval / end in order, and
+  the run ends early once the evaluation loss reaches `target_eval_loss`."""
+  from helpers import batch_of, make_engine, tiny_config
+  from maxtext_b200.trainers.post_train import hooks as H
+  cfg = tiny_config(extra=["steps=6", "eval_interval=2", "eval_steps=1", "target_eval_loss=100.0", "learning_rate=1e-3"])
+  eng = make_engine(cfg)
+  calls = []
+
+  class Spy(H.MetricTrainingHooks):
+    def on_train_start(self, loop):
+      calls.append("start")
+      super().on_train_start(loop)
+
+    def on_train_step_end(self, loop, step, metrics, step_time):
+      calls.append(f"step{step}")
+      super().on_train_step_end(loop, step, metrics, step_time)
+
+    def on_eval_step_end(self, loop, loss_sum, weights):
+      calls.append("eval")
+      super().on_eval_step_end(loop, loss_sum, weights)
+
+    def on_train_end(self, loop):
+      calls.append("end")
+      super().on_train_end(loop)
+
+  class OneBatch:
+    def __iter__(self):
+      return self
+
+    def __next__(self):
+      return batch_of(cfg)
+  data = H.DataHooks(cfg, train_iterator=OneBatch(), eval_iterator=OneBatch())
+
+  def eval_fn(batch):
+    m = eng.eval_step(batch)
+    return float(m["evaluation/total_loss"]), float(m["evaluation/total_weights"])
+  hooks = Spy(cfg, is_writer=False)
+  done = H.run_with_hooks(cfg, eng, hooks, data, eval_fn)
+  # the evaluation after step 1 meets the (generous) target, which ends the run
+  assert calls == ["start", "step0", "step1", "eval", "end"] and done == 2
+  step_rows = [m for _, m in hooks.history if "learning/loss" in m]
+  assert step_rows[0]["learning/total_weights"] > 0 and step_rows[0]["learning/perplexity"] > 1.0
+  assert any("eval/avg_perplexity" in m for _, m in hooks.history)
+
+
+def _rl_cfg(tmp_path, extra=()):
+  from helpers import tiny_config
+  return tiny_config(extra=["max_target_length=64", "max_prefill_predict_length=40", "per_device_batch_size=2", "steps=2", "vocab_size=300",
+                            "tokenizer_type=byte", "learning_rate=1e-3", "decode_sampling_temperature=1.0", "eval_interval=1", "eval_steps=2",
+                            "reasoning_start_token=<r>", "reasoning_end_token=</r>", "solution_start_token=<a>", "solution_end_token=</a>",
+                            "reward_exact_format_match=0.5", "reward_partial_format_match=0.25", "penalty_incorrect_format=-0.25",
+                            "reward_exact_answer=3.0", "reward_white_space_format_match=1.5", "penalty_incorrect_answer=-1.0", *extra])
+
+
+def test_reward_functions_and_answer_extraction(tmp_path):
+  """Format rewards follow the tag structure; the answer reward accepts exact text, white-space variants and numerically
+  equal forms (through the verification workers), and penalises wrong or missing answers."""
+  from maxtext_b200.trainers.post_train.rl import math_verify_pool as mvp, rewards as R
+  c = _rl_cfg(tmp_path)
+  good = "<r>2+2 is 4</r><a>\\boxed{4}</a>"
+  assert R.extract_answer(good, c) == "4" and R.extract_answer("<a> 7 </a>", c) == "7" and R.extract_answer("nothing", c) == R.FALLBACK_ANSWER
+  assert R.extract_answer("<a>\\boxed{\\frac{1}{2}}</a>", c) == "\\frac{1}{2}"
+  assert R.extract_hash_answer("so the total is 18\n#### 18") == "18"
+  assert R.match_format_exactly([""], [good, "4"], c) == [0.5, 0.0]
+  assert R.match_format_approximately([""], [good, "<a>4"], c) == [1.0, -0.25 * 3 + 0.25]
+  comps = [good, "<r>x</r><a>4.0</a>", "<r>x</r><a>5</a>", "no tags at all", "<a>1/2</a>", "<a>50%</a>"]
+  ans = ['["4"]', '["4"]', '["4"]', '["4"]', '["0.5"]', '["0.5"]']
+  assert R.check_numbers([""] * 6, comps, c, answer=ans, question=[""] * 6) == [3.0, 3.0, -0.25, -1.0, 3.0, 3.0]
+  assert mvp.are_equal("\\boxed{1,000}", "1000") and not mvp.are_equal("12", "21")
+  # the pooled path: more items than the in-process short cut takes, verified in spawned workers
+  items = [(i, ["\\boxed{%d}" % i], ["\\boxed{%d.0}" % (i if i % 2 else i + 1)]) for i in range(6)]
+  assert mvp.math_verify_pool(items, [0.0] * 6, reward=2.0, timeout=60.0, num_procs=2) == [0.0, 2.0, 0.0, 2.0, 0.0, 2.0]
+  fns = R.build_reward_fns(c)
+  assert [f.__name__ for f in fns] == ["match_format_exactly", "match_format_approximately", "check_numbers"]
+  assert R.total_reward(fns, [""], [good], c, answer=['["4"]'], question=[""]) == [0.5 + 1.0 + 3.0]
+
+
+def test_rl_train_loop_rolls_out_scores_and_updates(tmp_path):
+  """`train_rl` end to end on a tiny model: rollouts from the policy's own weights, rewards from a user function named in
+  the config, GRPO updates with a KL term to the starting policy, and the greedy evaluation pass."""
+  import json
+  from maxtext_b200.trainers.post_train.rl import train_rl
+  data = tmp_path / "q.jsonl"
+  with open(data, "w") as fh:
+    for i in range(6):
+      fh.write(json.dumps({"question": f"What is {i} + 1?", "answer": f"it is #### {i + 1}"}) + "\n")
+  user = tmp_path / "my_rewards.py"
+  user.write_text("def length_reward(prompts, completions, config, **kw):\n  return [float(len(c) % 5) for c in completions]\n")
+  cfg = _rl_cfg(tmp_path, [f"hf_train_files={data}", f"hf_eval_files={data}", f"reward_functions_path={user}", "reward_functions=length_reward"])
+  cfg = cfg.replace(rl={"num_generations": 2, "num_iterations": 2, "grpo_beta": 0.05, "grpo_epsilon": 0.2, "loss_algo": "grpo"})
+  rows = train_rl.load_questions(str(data))
+  assert rows[2] == {"question": "What is 2 + 1?", "answer": '["3"]'}
+  trainer, hist = train_rl.rl_train(cfg)
+  assert len(hist) == 2 and all("rl/mean_reward" in h and "rl/kl" in h and "learning/loss" in h for h in hist)
+  assert all(h["eval/num_questions"] == 2 and 0.0 <= h["eval/accuracy"] <= 1.0 for h in hist)
+  assert hist[0]["rl/kl"] >= 0.0 and hist[0]["rl/completion_tokens"] >= 1.0
+  assert not torch.equal(trainer.ref_master, trainer.eng.store.master)          # the policy moved away from its start
+
+
+def test_distillation_online_offline_and_learn_to_init(tmp_path):
+  """Teacher top-k logits are written in resumable shards; the student trains from them (KL over the top-k support) and
+  from an online teacher; learn-to-init copies the teacher's matching tensors, picking teacher layers for the student's."""
+  import json
+  import os
+  from helpers import batch_of, make_engine, tiny_config
+  from maxtext_b200.trainers.post_train.distillation import save_top_k_teacher_logits as S, train_distill as D
+  t_cfg = tiny_config(extra=["base_num_decoder_layers=4", "steps=5"])
+  s_cfg = tiny_config(extra=["base_num_decoder_layers=2", "steps=3", "learning_rate=2e-3", "distill_alpha=0.3", "distill_temperature=2.0",
+                             "distill_temperature_end=1.0", "distill_temperature_schedule=linear"])
+  teacher = make_engine(t_cfg)
+
+  class Batches:
+    def __init__(self):
+      self.n = 0
+
+    def __iter__(self):
+      return self
+
+    def __next__(self):
+      self.n += 1
+      b = batch_of(t_cfg)
+      return {k: (v + self.n) % t_cfg.vocab_size if k in ("inputs", "targets") else v for k, v in b.items()}
+  out = str(tmp_path / "topk")
+  man = S.generate_and_save(t_cfg, teacher, Batches(), top_k=8, output_dir=out, shard_batches=2, max_batches=3)
+  assert man["shards"] == ["shard_00000.npz", "shard_00001.npz"] and man["batches_done"] == 3
+  man = S.generate_and_save(t_cfg, teacher, Batches(), top_k=8, output_dir=out, shard_batches=2, max_batches=5)   # resumes after batch 3
+  assert man["batches_done"] == 5 and len(man["shards"]) == 3 and len(os.listdir(out)) == 4
+  it = S.TopKShardIterator(out, batch=int(s_cfg.global_batch_size_to_load))
+  b0 = next(it)
+  vals, idx = S.teacher_top_k(teacher, {"inputs": b0["inputs"]}, 8)
+  assert torch.equal(idx.cpu(), b0["top_k_indices"]) and torch.allclose(vals.cpu(), b0["top_k_logits"].float(), atol=0.05, rtol=0.02)
+  # offline: the student's loss on a fixed shard batch falls
+  student = make_engine(s_cfg)
+
+  class Fixed:
+    def __iter__(self):
+      return self
+
+    def __next__(self):
+      return b0
+  _, hist = D.train_distill(s_cfg.replace(offline_data_dir=out), student=student, data_iterator=Fixed())
+  assert len(hist) == 3 and hist[-1]["learning/loss"] < hist[0]["learning/loss"]
+  assert hist[0]["distill/temperature"] == 2.0 and 1.0 < hist[1]["distill/temperature"] < 2.0
+  # online teacher + learn-to-init: student layers 0, 1 take teacher layers 0, 3
+  student2 = make_engine(s_cfg)
+  n = D.init_student_from_teacher(student2, teacher, [0, 3])
+  assert n > 0
+  name_s, name_t = "layers_1/mlp/wo/kernel", "layers_3/mlp/wo/kernel"
+  assert torch.equal(student2.store.full_master(student2.store.params[name_s]), teacher.store.full_master(teacher.store.params[name_t]))
+  _, hist2 = D.train_distill(s_cfg, student=student2, teacher=teacher, data_iterator=Fixed())
+  assert hist2[-1]["learning/loss"] < hist2[0]["learning/loss"]

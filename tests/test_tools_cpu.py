@@ -43,3 +43,26 @@ def test_get_flops_llama3_8b(capsys):
   # 6 * params(non-embedding) * tokens + attention: the number behind the bench's TFLOP/s/device figure
   assert 800 < out["total_tflops_per_device_per_step"] < 900
   assert out["tokens_per_device_per_step"] == 2 * 8192
+
+
+def test_tokenizer_trainer_writes_a_loadable_sentencepiece_model(tmp_path):
+  """The vocabulary trainer samples a jsonl corpus, trains a small unigram model and the data pipeline can load it."""
+  import json
+  import pytest
+  pytest.importorskip("sentencepiece")
+  from maxtext_b200.input_pipeline.tokenizer import build_tokenizer
+  from maxtext_b200.trainers.tokenizer import train_tokenizer as tt
+  words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "lambda", "omega"]
+  for j in range(2):
+    with open(tmp_path / f"c{j}.jsonl", "w") as fh:
+      for i in range(400):
+        fh.write(json.dumps({"text": " ".join(words[(i * 7 + k * 3 + j) % len(words)] for k in range(12))}) + "\n")
+  assert len(list(tt.example_texts(str(tmp_path / "*.jsonl")))) == 800
+  tt.main([f"--train_files={tmp_path}/*.jsonl", "--file_type=jsonl", "--vocab_size=64", "--max_corpus_chars=20000",
+           f"--assets_path={tmp_path}/assets", "--vocab_model_name=tok.model"])
+  model = tmp_path / "assets" / "tok.model"
+  assert model.is_file()
+  cfg = tiny_config(extra=["tokenizer_type=sentencepiece", f"tokenizer_path={model}"])
+  tok = build_tokenizer(cfg)
+  ids = tok.encode("alpha beta omega", add_bos=False, add_eos=True)
+  assert ids[-1] == 1 and "alpha" in tok.decode(ids)
