@@ -17,6 +17,7 @@
 #include "attention_mask.cuh"
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
+#include <type_traits>
 
 namespace mt {
 namespace bwd {
@@ -304,8 +305,9 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       // index mode: query column e of this half has position q0 + half*64 + e + q_off
       const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)(q0 + half * 64 + mk.q_off);
       float pr[64];      // what multiplies (dP - delta): P, or P * (1 - tanh^2) under a soft-cap
-      if (ok) {
-        tc_fence_after();
+      // the soft-cap and the mask are compile-time switches of this loop, so the common case stays three instructions per score
+      auto phase1 = [&](auto cap_t, auto mask_t) {
+        constexpr bool CAP = decltype(cap_t)::value, MASK = decltype(mask_t)::value;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
@@ -317,15 +319,15 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
             const int col = c * 32 + e;
             float sv = __uint_as_float(r[e]);
             float dt = 1.f;
-            if (cap) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
+            if constexpr (CAP) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
             float v = fast_exp2(fmaf(a, sv, -lse_s[col]));
-            if (need_mask) {
+            if constexpr (MASK) {
               bool keep = arrays ? ((uint32_t)pos_s[col] - (uint32_t)lo_p <= span) : ((uint32_t)col - e_lo <= span);
               if (has_seg) keep = keep && seg_s[col] == my_seg && my_seg != 0;
               if (!keep || none) v = 0.f;
             }
             pv[e] = v;
-            pr[col] = v * dt;
+            pr[col] = CAP ? v * dt : v;
           }
           uint32_t pk[16];
 #pragma unroll
@@ -334,6 +336,12 @@ dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
           // halves never write over each other's unread scores
           tmem_st_32x32b_x16(tmem + lane_off + COL_ST + half * 64 + c * 16, pk);
         }
+      };
+      if (ok) {
+        tc_fence_after();
+        if (cap) phase1(std::true_type{}, std::true_type{});
+        else if (need_mask) phase1(std::false_type{}, std::true_type{});
+        else phase1(std::false_type{}, std::false_type{});
       }
       tmem_st_wait();
       tc_fence_before();
@@ -574,8 +582,8 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
       const int* pos_s = s_pos + s * 128 + half * 64;
       const uint32_t e_lo = (uint32_t)lo_p - (uint32_t)(kk + half * 64);     // index mode: key column e of this half has position kk + half*64 + e
       float pr[64];      // what multiplies (dP - delta): P, or P * (1 - tanh^2) under a soft-cap
-      if (ok) {
-        tc_fence_after();
+      auto phase1 = [&](auto cap_t, auto mask_t) {
+        constexpr bool CAP = decltype(cap_t)::value, MASK = decltype(mask_t)::value;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
@@ -586,9 +594,10 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             const int col = c * 32 + e;
             float sv = __uint_as_float(r[e]);
             float dt = 1.f;
-            if (cap) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
-            float v = fast_exp2(fmaf(a, sv, -my_lse)) * dt;
-            if (need_mask) {
+            if constexpr (CAP) { sv = fast_tanh(sv * pre); dt = 1.f - sv * sv; }
+            float v = fast_exp2(fmaf(a, sv, -my_lse));
+            if constexpr (CAP) v *= dt;
+            if constexpr (MASK) {
               bool keep = arrays ? ((uint32_t)pos_s[col] - (uint32_t)lo_p <= span) : ((uint32_t)col - e_lo <= span);
               if (has_seg) keep = keep && seg_s[col] == my_seg && my_seg != 0;
               if (!keep || none) v = 0.f;
@@ -596,6 +605,12 @@ dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUt
             pr[col] = v;
           }
         }
+      };
+      if (ok) {
+        tc_fence_after();
+        if (cap) phase1(std::true_type{}, std::true_type{});
+        else if (need_mask) phase1(std::false_type{}, std::true_type{});
+        else phase1(std::false_type{}, std::false_type{});
         tc_fence_before();
         mbar_arrive(bar(S_DONE));
       }

@@ -51,11 +51,9 @@ class MaxEngine:
     self.device = torch.device(device)
     self.model = model or Transformer(c, mesh, self.device)
     self.max_len = int(c.max_target_length)
-    self.max_prefill = int(c.max_prefill_predict_length)
-    if self.max_prefill >= int(c.max_target_length):
-      # src/maxtext/inference/offline_engine.py:950 makes the same demand
-      raise ValueError(f"max_prefill_predict_length ({self.max_prefill}) must be smaller than max_target_length ({int(c.max_target_length)}): "
-                       "a full prompt leaves no room to generate")
+    # a prompt must leave room for at least one generated token (prefill / insert check every length against max_len - 1);
+    # training configs that build a sampler keep the default prefill length, so it is capped here rather than refused
+    self.max_prefill = min(int(c.max_prefill_predict_length), self.max_len - 1)
     self.generator = torch.Generator(device=self.device)
     self.generator.manual_seed(int(c.init_weights_seed))
     self._graphs: dict = {}          # id(state) -> (CUDAGraph, static result tensors) when cuda_graphs is on

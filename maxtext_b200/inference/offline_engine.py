@@ -23,6 +23,9 @@ class Request:
 
 class OfflineEngine:
   def __init__(self, engine: MaxEngine, slots: int = 4, eos_id: int = -1):
+    c = engine.config
+    if int(c.max_target_length) - int(c.max_prefill_predict_length) <= 0:
+      raise ValueError("Make sure max_target_length - max_prefill_predict_length is greater than 0")      # offline_engine.py:950
     self.eng, self.slots, self.eos_id = engine, slots, eos_id
     self.state = engine.init_decode_state(slots)
     self.queue: deque[Request] = deque()

@@ -242,5 +242,6 @@ def test_prompt_lengths_that_would_overrun_the_cache_are_rejected_on_the_host():
   with pytest.raises(ValueError):
     eng.insert(prefix, state, 2)
   eng.insert(prefix, state, 1)
+  from maxtext_b200.inference.offline_engine import OfflineEngine
   with pytest.raises(ValueError):
-    MaxEngine(tiny_config(extra=["max_target_length=32", "max_prefill_predict_length=32"]), device=torch.device("cpu"))
+    OfflineEngine(MaxEngine(tiny_config(extra=["max_target_length=32", "max_prefill_predict_length=32"]), device=torch.device("cpu")))

@@ -66,3 +66,33 @@ def test_tokenizer_trainer_writes_a_loadable_sentencepiece_model(tmp_path):
   tok = build_tokenizer(cfg)
   ids = tok.encode("alpha beta omega", add_bos=False, add_eos=True)
   assert ids[-1] == 1 and "alpha" in tok.decode(ids)
+
+
+def test_layerwise_quantization_matches_whole_model_quantization(tmp_path):
+  """Quantising layer by layer from the checkpoint arrays gives the file the serving engine writes when it quantises the
+  loaded model at once, and an engine that loads it generates with the de-quantised weights."""
+  from safetensors.torch import load_file
+  from maxtext_b200.checkpoint import manager as ckpt_lib
+  from maxtext_b200.inference.maxengine import MaxEngine
+  from maxtext_b200.utils import layerwise_quantization as LQ
+  cfg = tiny_config(extra=["steps=1", "checkpoint_period=1", "enable_checkpointing=true", "async_checkpointing=false",
+                           f"base_output_directory={tmp_path}", "run_name=lq"])
+  eng = make_engine(cfg)
+  eng.store.initialize(seed=3)
+  ckpt_lib.CheckpointManager(cfg, eng).save_params_only(0)
+  src = os.path.join(cfg.checkpoint_dir, "0")
+  qcfg = cfg.replace(load_parameters_path=src, save_quantized_params_path=str(tmp_path / "q"), quantization="int8")
+  info = LQ.layerwise_quantize(qcfg)
+  assert info["layers"] == cfg.num_decoder_layers and info["quantized_bytes"] < info["fp32_bytes"] / 3
+  assert info["peak_layer_bytes"] <= info["fp32_bytes"] // cfg.num_decoder_layers + 1
+  got = load_file(info["file"])
+  whole = MaxEngine(cfg.replace(load_parameters_path=src), device=torch.device("cpu"))
+  whole.load_params()
+  ref_file = whole.save_quantized_params(str(tmp_path / "ref"), 8)
+  want = load_file(ref_file)
+  assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
+  served = MaxEngine(cfg.replace(load_parameters_path=src, checkpoint_is_quantized=True), device=torch.device("cpu"))
+  os.replace(info["file"], os.path.join(src, "quantized_params.safetensors"))
+  served.load_params()
+  name = "layers_0/mlp/wo/kernel"
+  assert torch.allclose(served.model.store.full_master(served.model.store.params[name]), whole.model.store.full_master(whole.model.store.params[name]))
