@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 
 extern "C" {
+int mt_router_topk(const void* logits, int is_bf16, const float* bias, long tokens, int E, int k, int mode, int sigmoid_scores, int raw_weights,
+                   float scaling, int* idx, float* wts, float* probs, int* counts, cudaStream_t st);
 int mt_moe_sort(const int* idx, int n, int E, int rows_max, int* sizes, int* offs, int* blk_expert, int* dest, int* row_pair, cudaStream_t st);
 int mt_moe_gather(const void* x, const int* row_pair, const int* offs, int E, int k, int D, int rows_max, void* rows, int sms, cudaStream_t st);
 int mt_moe_combine(const void* y, const int* dest, const float* w, int T, int k, int D, void* out, int sms, cudaStream_t st);
@@ -36,6 +38,26 @@ bool bf16_rows(const torch::Tensor& t) {
 }
 
 // idx [n] int32 -> fills sizes [E], offs [E+1], blk_expert [rows_max/128], dest [n], row_pair [rows_max]
+// logits [T,E] fp32 / bf16 -> (idx [T,k] int32, wts [T,k] fp32, probs [T,E] fp32, counts [E] int32), see router_sm100.cu
+std::vector<torch::Tensor> router_topk(const torch::Tensor& logits, const c10::optional<torch::Tensor>& bias, int64_t k, int64_t mode,
+                                       bool sigmoid_scores, bool raw_weights, double scaling) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() &&
+              (logits.scalar_type() == torch::kFloat32 || logits.scalar_type() == torch::kBFloat16));
+  const int64_t T = logits.size(0), E = logits.size(1);
+  if (bias) TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->scalar_type() == torch::kFloat32 && bias->numel() == E);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto oi = torch::TensorOptions().dtype(torch::kInt32).device(logits.device());
+  auto of = torch::TensorOptions().dtype(torch::kFloat32).device(logits.device());
+  auto idx = torch::empty({T, k}, oi), counts = torch::zeros({E}, oi);
+  auto wts = torch::empty({T, k}, of), probs = torch::empty({T, E}, of);
+  int rc = mt_router_topk(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16 ? 1 : 0, bias ? bias->data_ptr<float>() : nullptr, T, (int)E,
+                          (int)k, (int)mode, sigmoid_scores ? 1 : 0, raw_weights ? 1 : 0, (float)scaling, idx.data_ptr<int>(),
+                          wts.data_ptr<float>(), probs.data_ptr<float>(), counts.data_ptr<int>(), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "mt_router_topk failed with code ", rc);
+  mt_count_launches(1);
+  return {idx, wts, probs, counts};
+}
+
 void moe_sort(const torch::Tensor& idx, int64_t E, torch::Tensor& sizes, torch::Tensor& offs, torch::Tensor& blk_expert, torch::Tensor& dest,
               torch::Tensor& row_pair) {
   TORCH_CHECK(i32(idx) && i32(sizes) && i32(offs) && i32(blk_expert) && i32(dest) && i32(row_pair));
@@ -179,6 +201,7 @@ void register_moe(pybind11::module_& m) {
   m.def("ep_push", &ep_push);
   m.def("ep_pull", &ep_pull);
   m.def("ep_zero_pads", &ep_zero_pads);
+  m.def("router_topk", &router_topk);
   m.def("moe_sort", &moe_sort);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);

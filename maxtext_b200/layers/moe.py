@@ -116,8 +116,20 @@ class RoutedMoE:
     xg = x2.float() if c.float32_gate_logits else x2
     w = self.gate.leaf()
     logits = torch.nn.functional.linear(xg, w.to(xg.dtype))
-    if self.deepseek:
-      func = c.routed_score_func or "softmax"
+    grouped = self.deepseek and c.n_routing_groups > 0 and c.topk_routing_group > 0
+    func = (c.routed_score_func or "softmax") if self.deepseek else "softmax"
+    if (moe_ops.router_kernel_ok(logits, self.E, self.k) and not grouped and func in ("softmax", "sigmoid")
+        and not bool(getattr(c, "use_random_routing", False))):
+      # one launch: scores, top-k, routing weights (csrc/router_sm100.cu); the bias only steers the selection and is not trained
+      bias = self.gate_bias.leaf() if self.gate_bias is not None else None
+      if self.deepseek:
+        idx, wts, probs, _ = moe_ops.router_topk(logits, bias, self.k, 1, func == "sigmoid", False, float(c.routed_scaling_factor))
+      else:
+        lg = logits + bias.to(logits.dtype) if bias is not None else logits      # here the bias is part of the logits (and trained)
+        idx, wts, probs, _ = moe_ops.router_topk(lg, None, self.k, 0, False, self.style == "llama4", 1.0)
+        if c.norm_topk_prob:
+          wts = wts / wts.sum(-1, keepdim=True)
+    elif self.deepseek:
       lf = logits.float()
       scores = torch.softmax(lf, -1) if func == "softmax" else torch.sigmoid(lf) if func == "sigmoid" else lf
       sel = scores + self.gate_bias.leaf().float() if self.gate_bias is not None else scores

@@ -22,6 +22,12 @@ _ATTN_IMPL = os.environ.get("MAXTEXT_B200_ATTN", "auto")
 
 # =============================================================================== GEMM
 _GEMM_FALLBACKS = 0
+_ATTN_FALLBACKS = 0
+
+
+def attention_fallbacks() -> int:
+  """How many attention forward / backward calls on a GPU were evaluated by PyTorch ops instead of the flash kernels."""
+  return _ATTN_FALLBACKS
 
 
 def gemm_fallbacks() -> int:
@@ -371,6 +377,8 @@ def attention_fwd(q, k, v, positions, segment_ids, scale, soft_cap, window, caus
                    kv_seg=kv_segment_ids if kv_segment_ids is not None else segment_ids, causal=causal,
                    sliding_window=window, chunk=chunk)
   if q.is_cuda:
+    global _ATTN_FALLBACKS
+    _ATTN_FALLBACKS += 1
     if _ATTN_IMPL == "sdpa" and segment_ids is None and not window and not soft_cap and causal and kv_positions is None and not chunk \
         and sinks is None:
       # comparison arm only (library attention); the product path is the flash kernel above
@@ -423,6 +431,9 @@ def attention_bwd(dout, q, k, v, out, lse, positions, segment_ids, scale, soft_c
       return dsinks
   kpos = kv_positions if kv_positions is not None else positions
   kseg = kv_segment_ids if kv_segment_ids is not None else segment_ids
+  if q.is_cuda:
+    global _ATTN_FALLBACKS
+    _ATTN_FALLBACKS += 1
   if lse is None:
     # comparison arm (library attention): differentiate the library call
     with torch.enable_grad():

@@ -246,3 +246,63 @@ def moe_ffn_padded(x2, weights, expert_idx, p_wi0, p_wi1, p_wo, num_experts: int
   rows = _GatherRowsFn.forward(F._Dummy(), x2, plan)
   y = _ExpertsFFNFn.forward(F._Dummy(), rows, w0, w1, wo, None, None, None, plan, act)
   return _CombineFn.forward(F._Dummy(), y, weights, plan)
+
+
+# =============================================================================== router (softmax / sigmoid + top-k in one launch)
+class _RouterFn(torch.autograd.Function):
+  """Scores, top-k indices and routing weights of the MoE router from one kernel (`csrc/router_sm100.cu`); the gradient of
+  these few [T, E] / [T, k] tensors is assembled here from the saved outputs."""
+
+  @staticmethod
+  def forward(ctx, logits, bias, k, mode, sigmoid_scores, raw_weights, scaling):
+    idx, wts, probs, counts = backend.ext().router_topk(logits.contiguous(), bias, int(k), int(mode), bool(sigmoid_scores), bool(raw_weights),
+                                                        float(scaling))
+    ctx.save_for_backward(idx, wts, probs)
+    ctx.cfg = (int(mode), bool(sigmoid_scores), bool(raw_weights), float(scaling), logits.dtype)
+    ctx.mark_non_differentiable(idx, counts)
+    return idx, wts, probs, counts
+
+  @staticmethod
+  def backward(ctx, _didx, dwts, dprobs, _dcounts):
+    idx, wts, probs = ctx.saved_tensors
+    mode, sig, raw, scaling, dtype = ctx.cfg
+    li = idx.long()
+    dscore = dprobs.clone() if dprobs is not None else torch.zeros_like(probs)       # gradient w.r.t. the scores (mode 1) / probs
+    dlogits = torch.zeros_like(probs)
+    if dwts is not None:
+      if mode == 1:
+        sel = probs.gather(1, li)
+        if sig:
+          tot = sel.sum(-1, keepdim=True) + 1e-20
+          w = sel / tot                                                              # wts / scaling
+          g = dwts * scaling
+          dsel = (g - (g * w).sum(-1, keepdim=True)) / tot
+        else:
+          dsel = dwts * scaling
+        dscore.scatter_add_(1, li, dsel)
+      elif raw:
+        dlogits.scatter_add_(1, li, dwts)
+      else:
+        dv = wts * (dwts - (dwts * wts).sum(-1, keepdim=True))                        # softmax over the k selected logits
+        dlogits.scatter_add_(1, li, dv)
+    if mode == 1 and sig:
+      dlogits += dscore * probs * (1.0 - probs)
+    else:
+      dlogits += probs * (dscore - (dscore * probs).sum(-1, keepdim=True))            # softmax over all experts
+    return dlogits.to(dtype), None, None, None, None, None, None
+
+
+def router_topk(logits: torch.Tensor, bias, k: int, mode: int = 0, sigmoid_scores: bool = False, raw_weights: bool = False,
+                scaling: float = 1.0):
+  """(idx [T,k] int64, wts [T,k] fp32, probs [T,E] fp32, counts [E] int32) on a GPU; see `_RouterFn`."""
+  b = bias.detach().float().contiguous() if bias is not None else None
+  if torch.is_grad_enabled() and logits.requires_grad:
+    idx, wts, probs, counts = _RouterFn.apply(logits, b, k, mode, sigmoid_scores, raw_weights, scaling)
+  else:
+    idx, wts, probs, counts = backend.ext().router_topk(logits.contiguous(), b, int(k), int(mode), bool(sigmoid_scores), bool(raw_weights),
+                                                        float(scaling))
+  return idx.long(), wts, probs, counts
+
+
+def router_kernel_ok(logits: torch.Tensor, E: int, k: int) -> bool:
+  return backend.use_cuda_kernels(logits) and logits.dtype in (torch.float32, torch.bfloat16) and E <= 512 and k <= 32 and k <= E

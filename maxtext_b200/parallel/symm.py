@@ -14,6 +14,8 @@ peers reached it, with a time limit after which the kernel records a status code
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -53,14 +55,16 @@ class SymmTensor:
 class SymmGroup:
   N_SLOTS = 16
 
-  def __init__(self, group, device, wait_limit_ms: float = 20000.0):
+  def __init__(self, group, device, wait_limit_ms: float | None = None):
     import torch.distributed._symmetric_memory as sm
     self._sm = sm
     self.group = group if group is not None else dist.group.WORLD
     self.device = torch.device(device)
     self.rank = dist.get_rank(self.group)
     self.world = dist.get_world_size(self.group)
-    self.wait_limit_ms = wait_limit_ms
+    # how long a device-side flag wait may spin before it records a status code and returns (MAXTEXT_B200_WAIT_LIMIT_MS overrides:
+    # tests use a few seconds so that a rank that lost its peer leaves on its own instead of being killed)
+    self.wait_limit_ms = float(wait_limit_ms if wait_limit_ms is not None else os.environ.get("MAXTEXT_B200_WAIT_LIMIT_MS", 20000.0))
     self._handles = []
     self.flags = self.alloc(self.N_SLOTS * self.world, torch.int32, zero=True)
     self.epochs = [0] * self.N_SLOTS

@@ -64,7 +64,9 @@ def plan(config, world: int | None = None, part: str = "b200") -> dict:
   mem = {}
   mem["master_weights"] = local * wbytes
   mem["compute_shard_bf16"] = 0 if (wbytes == 2 and c.dtype == "bfloat16") else local * 2
-  mem["optimizer_state"] = local * 4 * opt_states
+  mu_bytes = 2 if str(getattr(c, "mu_dtype", "") or c.weight_dtype) in ("bfloat16", "float16") else 4
+  # first moment in mu_dtype, second moment always fp32
+  mem["optimizer_state"] = local * (mu_bytes + 4 * (opt_states - 1)) if opt_states >= 1 else 0
   mem["grad_shard_fp32"] = local * 4
   sharded = [u for u in st.units.values() if u.group_size > 1]
   max_unit = max((u.numel for u in sharded), default=0)

@@ -108,6 +108,34 @@ def train_tp(rank, world, dev, fused):
   return out
 
 
+def train_cp(rank, world, dev, strategy):
+  """Context parallelism over all ranks (None: one rank alone on the whole batch). Every strategy must land on the flash
+  kernels: the ring and all-gather forms attend to foreign key blocks through the kernels' position arrays."""
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.ops import functional as F
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as T
+  from maxtext_b200.train.engine import TrainEngine
+  n = 1 if strategy is None else world
+  par = [] if strategy is None else [f"ici_context_parallelism={world}", "ici_fsdp_parallelism=1", f"context_parallel_strategy={strategy}"]
+  cfg = pyconfig.initialize(
+      ["w", "maxtext_b200/configs/base.yml", "base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128",
+       "base_mlp_dim=1024", "base_num_decoder_layers=2", "vocab_size=4096", "max_target_length=1024",
+       f"per_device_batch_size={2 * world if strategy is None else 2}",
+       "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal", "log_config=false", "steps=3",
+       "learning_rate=1e-3", "warmup_steps_fraction=0.0", "use_fused_comm_kernels=false"] + par, num_devices=n)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world) if strategy is not None else None
+  eng = TrainEngine(cfg, mesh, dev)
+  it = T.create_data_iterator(cfg, mesh)
+  before = F.attention_fallbacks()
+  out = []
+  for _ in range(3):
+    m = eng.train_step(next(it))
+    out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  assert F.attention_fallbacks() == before, f"{strategy}: attention fell back to PyTorch ops {F.attention_fallbacks() - before} times"
+  return out
+
+
 def train(rank, world, dev, fused):
   from maxtext_b200.config import pyconfig
   from maxtext_b200.parallel import mesh as mesh_lib
@@ -138,6 +166,15 @@ def main():
     if mode == "kernels":
       kernels(rank, world, dev)
       msg = "ok"
+    elif mode == "cp":
+      ref = train_cp(rank, world, dev, None)
+      got = {s: train_cp(rank, world, dev, s) for s in ("ring", "all_gather", "ulysses")}
+      for s, vals in got.items():
+        for (la, na), (lb, nb) in zip(ref, vals):
+          assert abs(la - lb) < 3e-2 and abs(na - nb) < 5e-2 * max(1.0, na), (s, ref, vals)
+      from maxtext_b200.ops import backend
+      assert backend.ext().kernel_status(True) == 0
+      msg = "ok " + repr((ref, got))
     else:
       fn = {"moe_ep": train_moe_ep, "tp": train_tp}.get(mode, train)
       a = fn(rank, world, dev, fused=False)

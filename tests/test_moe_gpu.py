@@ -149,3 +149,38 @@ def test_routed_moe_layer_matches_per_expert_loop():
   for n, w in (("wi_0", W0), ("wi_1", W1), ("wo", Wo)):
     err = (got_dw[n] - w.grad).abs().max() / (w.grad.abs().max() + 1e-6)
     assert err < 3e-2, (n, float(err))
+
+
+@pytest.mark.parametrize("E,k,mode,sig,raw,use_bias", [(8, 2, 0, False, False, False), (128, 8, 0, False, False, True), (16, 1, 0, False, True, False),
+                                                      (64, 6, 1, False, False, True), (64, 6, 1, True, False, True), (160, 6, 1, True, False, False)])
+def test_router_kernel_matches_pytorch_forward_and_backward(E, k, mode, sig, raw, use_bias):
+  """Scores, top-k, routing weights and the expert histogram from one launch; gradients w.r.t. the logits through both
+  outputs (weights and full probabilities) against autograd of the plain PyTorch formulas."""
+  from maxtext_b200.ops import moe_ops
+  torch.manual_seed(E + k)
+  T = 777
+  logits = (torch.randn(T, E, device="cuda") * 2.0).requires_grad_(True)
+  bias = (torch.randn(E, device="cuda") * 0.5) if use_bias else None
+  scaling = 2.5 if mode == 1 else 1.0
+  idx, wts, probs, counts = moe_ops.router_topk(logits, bias, k, mode, sig, raw, scaling)
+  ref_l = logits.detach().clone().requires_grad_(True)
+  if mode == 1:
+    scores = torch.sigmoid(ref_l) if sig else torch.softmax(ref_l, -1)
+    sel = scores + bias if bias is not None else scores
+    ridx = sel.topk(k, -1).indices
+    rw = scores.gather(-1, ridx)
+    if sig:
+      rw = rw / (rw.sum(-1, keepdim=True) + 1e-20)
+    rw, rp = rw * scaling, scores
+  else:
+    lg = ref_l + bias if bias is not None else ref_l
+    vals, ridx = lg.topk(k, -1)
+    rw = vals if raw else torch.softmax(vals, -1)
+    rp = torch.softmax(lg, -1)
+  assert torch.equal(idx, ridx)
+  assert torch.allclose(wts, rw, atol=1e-5, rtol=1e-4) and torch.allclose(probs, rp, atol=1e-6, rtol=1e-4)
+  assert torch.equal(counts.long(), torch.bincount(ridx.reshape(-1), minlength=E))
+  gw, gp = torch.randn_like(wts), torch.randn_like(probs)
+  ((wts * gw).sum() + (probs * gp).sum()).backward()
+  ((rw * gw).sum() + (rp * gp).sum()).backward()
+  assert torch.allclose(logits.grad, ref_l.grad, atol=2e-5, rtol=1e-3), (logits.grad - ref_l.grad).abs().max()

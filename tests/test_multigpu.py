@@ -23,17 +23,20 @@ def _run(mode, tmp_path, world=2):
   procs = []
   for r in range(world):
     env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-               MAXTEXT_B200_QUIET="1")
+               MAXTEXT_B200_QUIET="1", MAXTEXT_B200_WAIT_LIMIT_MS="5000")
     procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multigpu_worker.py"), mode, res], cwd=ROOT, env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
   outs = []
   for p in procs:
     try:
-      o, _ = p.communicate(timeout=420)
+      o, _ = p.communicate(timeout=600)
     except subprocess.TimeoutExpired:
-      for q in procs:
-        q.kill()
-      raise
+      # Device waits are bounded (5 s here) and the process group has a 120 s timeout, so a rank that lost its peer ends by
+      # itself; ranks are never killed while their buffers may be mapped by a peer. Give them that time, then report.
+      try:
+        o, _ = p.communicate(timeout=180)
+      except subprocess.TimeoutExpired:
+        pytest.fail("a rank is still running after its bounded waits should have ended it; it is left to finish on its own")
     outs.append(o.decode(errors="replace"))
   for r in range(world):
     path = f"{res}.{r}"
@@ -56,3 +59,7 @@ def test_expert_parallel_peer_dispatch_matches_nccl(tmp_path):
 
 def test_tensor_parallel_gemm_reduce_scatter_matches_nccl(tmp_path):
   _run("tp", tmp_path)
+
+
+def test_context_parallel_strategies_on_the_flash_kernels_match_one_gpu(tmp_path):
+  _run("cp", tmp_path)
