@@ -35,7 +35,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 PRESETS = {
     "llama3_8b": dict(model="llama3-8b", seq=8192, pdbs=2.0, ep=1, tp=1, quantization="", extra=[]),
     "mixtral_ep8": dict(model="mixtral-8x7b", seq=4096, pdbs=1.0, ep=8, tp=1, quantization="", extra=[]),
-    "deepseek16b_fp8_ep8": dict(model="deepseek2-16b", seq=4096, pdbs=2.0, ep=8, tp=1, quantization="fp8", extra=[]),
+    "deepseek16b_fp8_ep8": dict(model="deepseek2-16b", seq=4096, pdbs=2.0, ep=8, tp=1, quantization="fp8", extra=["fp8_block_scaling=true"]),
     # fp32 master + second moment, bf16 first moment: 14 bytes per parameter so that 70.6 B parameters fit 8 x 180 GB
     "llama70b_fsdp4_tp2": dict(model="llama3-70b", seq=4096, pdbs=1.0, ep=1, tp=2, quantization="", extra=["mu_dtype=bfloat16"]),
 }

@@ -28,7 +28,6 @@
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 #include <type_traits>
-#include <stdlib.h>
 
 namespace mt {
 namespace fwd {
@@ -559,7 +558,7 @@ int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
   p.B = B; p.Hq = Hq; p.Hkv = Hkv;
   p.n_pairs = (Sq + 128 * nq - 1) / (128 * nq);
   p.scale = scale; p.softcap = softcap; p.sinks = sinks; p.lse = lse; p.status = status;
-  p.head_major = getenv("MT_ATTN_HEAD_MAJOR") ? 1 : 0;
+  p.head_major = 0;                       // tile-major: longest query tiles of every head first
   mt::attn::Mask& msk = p.mk;
   msk.Sq = Sq; msk.Skv = Skv; msk.n_qt = (Sq + 127) / 128; msk.n_kt = (Skv + 127) / 128;
   msk.q_off = q_off; msk.causal = causal; msk.window = window; msk.chunk = chunk;

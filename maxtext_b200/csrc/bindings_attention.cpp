@@ -23,6 +23,9 @@ extern "C" int mt_decode_attention(const void* q, const void* k_cache, const voi
                                    void* out, cudaStream_t st);
 
 
+extern "C" int mt_sample(const void* logits, int is_bf16, const float* uniform, long rows, long V, int topk, float nucleus_p, float temperature,
+                         int greedy, long long* out, cudaStream_t st);
+
 int* mt_status_ptr();          // defined in bindings.cpp
 void mt_count_launches(int n); // defined in bindings.cpp
 
@@ -118,9 +121,27 @@ void decode_attention(const torch::Tensor& q, const torch::Tensor& k_cache, cons
   mt_count_launches(2);
 }
 
+// logits [rows, V] fp32 / bf16 -> token ids [rows] int64; `uniform` [rows] fp32 in [0,1) drives the draw (unused when greedy)
+torch::Tensor sample_tokens(const torch::Tensor& logits, const c10::optional<torch::Tensor>& uniform, int64_t topk, double nucleus_p,
+                            double temperature, bool greedy) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() &&
+              (logits.scalar_type() == torch::kFloat32 || logits.scalar_type() == torch::kBFloat16));
+  if (!greedy) TORCH_CHECK(uniform && uniform->is_cuda() && uniform->is_contiguous() && uniform->scalar_type() == torch::kFloat32 &&
+                           uniform->numel() == logits.size(0), "one uniform number per row is needed");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto out = torch::empty({logits.size(0)}, torch::dtype(torch::kInt64).device(logits.device()));
+  int rc = mt_sample(logits.data_ptr(), logits.scalar_type() == torch::kBFloat16 ? 1 : 0, greedy ? nullptr : uniform->data_ptr<float>(),
+                     logits.size(0), logits.size(1), (int)topk, (float)nucleus_p, (float)temperature, greedy ? 1 : 0,
+                     reinterpret_cast<long long*>(out.data_ptr<int64_t>()), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "mt_sample failed with code ", rc);
+  mt_count_launches(1);
+  return out;
+}
+
 }  // namespace
 
 void register_attention(pybind11::module_& m) {
+  m.def("sample_tokens", &sample_tokens);
   m.def("decode_attention", &decode_attention);
   m.def("flash_fwd_supported", &flash_fwd_supported);
   m.def("flash_bwd_supported", &flash_bwd_supported);

@@ -5,6 +5,11 @@
 #include <cuda_runtime.h>
 
 extern "C" {
+int mt_quant_fp8_rows(const void* x, long R, int C, long ldx, void* q, float* scales_t, cudaStream_t st);
+int mt_quant_fp8_blocks(const void* w, int G, int R, int C, void* q, void* qt, float* scales, cudaStream_t st);
+int mt_gemm_fp8_block(const void* aq, const void* bq, void* c, int M, int N, int K, long lda, long ldb, long ldc, const float* sa, const float* sb,
+                      long sb_e, long sb_n, long sb_k, int experts, const int* x_offs, const int* blk_expert, int* status, int num_sms,
+                      cudaStream_t st);
 int mt_router_topk(const void* logits, int is_bf16, const float* bias, long tokens, int E, int k, int mode, int sigmoid_scores, int raw_weights,
                    float scaling, int* idx, float* wts, float* probs, int* counts, cudaStream_t st);
 int mt_moe_sort(const int* idx, int n, int E, int rows_max, int* sizes, int* offs, int* blk_expert, int* dest, int* row_pair, cudaStream_t st);
@@ -38,6 +43,65 @@ bool bf16_rows(const torch::Tensor& t) {
 }
 
 // idx [n] int32 -> fills sizes [E], offs [E+1], blk_expert [rows_max/128], dest [n], row_pair [rows_max]
+// ---- block-scaled FP8 (gemm_fp8_block_sm100.cu)
+// x [R, C] bf16 -> (q [R, C] uint8 holding e4m3, scales_t [ceil(C/128), R] fp32)
+std::vector<torch::Tensor> quant_fp8_rows(const torch::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 4 == 0 && x.scalar_type() == torch::kBFloat16 && x.size(1) % 16 == 0 &&
+              (reinterpret_cast<uintptr_t>(x.data_ptr()) % 8) == 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto q = torch::empty({x.size(0), x.size(1)}, torch::dtype(torch::kUInt8).device(x.device()));
+  auto s = torch::empty({(x.size(1) + 127) / 128, x.size(0)}, torch::dtype(torch::kFloat32).device(x.device()));
+  int rc = mt_quant_fp8_rows(x.data_ptr(), x.size(0), (int)x.size(1), x.stride(0), q.data_ptr(), s.data_ptr<float>(), cur());
+  TORCH_CHECK(rc == 0, "mt_quant_fp8_rows failed with code ", rc);
+  mt_count_launches(1);
+  return {q, s};
+}
+
+// w [R, C] or [G, R, C] bf16 -> (q or None, qt [.., C, R] or None, scales [G, ceil(R/128), ceil(C/128)])
+std::vector<c10::optional<torch::Tensor>> quant_fp8_blocks(const torch::Tensor& w, bool want_q, bool want_t) {
+  TORCH_CHECK(w.is_cuda() && (w.dim() == 2 || w.dim() == 3) && w.is_contiguous() && w.scalar_type() == torch::kBFloat16);
+  const int64_t G = w.dim() == 3 ? w.size(0) : 1, R = w.size(w.dim() - 2), C = w.size(w.dim() - 1);
+  TORCH_CHECK(R % 16 == 0 && C % 16 == 0, "quant_fp8_blocks: dims must be multiples of 16");
+  c10::cuda::CUDAGuard guard(w.device());
+  auto o8 = torch::dtype(torch::kUInt8).device(w.device());
+  c10::optional<torch::Tensor> q, qt;
+  if (want_q) q = torch::empty({G, R, C}, o8);
+  if (want_t) qt = torch::empty({G, C, R}, o8);
+  auto s = torch::empty({G, (R + 127) / 128, (C + 127) / 128}, torch::dtype(torch::kFloat32).device(w.device()));
+  int rc = mt_quant_fp8_blocks(w.data_ptr(), (int)G, (int)R, (int)C, q ? q->data_ptr() : nullptr, qt ? qt->data_ptr() : nullptr,
+                               s.data_ptr<float>(), cur());
+  TORCH_CHECK(rc == 0, "mt_quant_fp8_blocks failed with code ", rc);
+  mt_count_launches(1);
+  return {q, qt, s};
+}
+
+// out [M, N] bf16 = aq [M, K] (e4m3, scales sa [KB, M]) x bq [G, N, K]^T (e4m3, scales sb [G, NB', KB'] read as element
+// (e, nb, kb) = sb[e][nb][kb], or with `sb_transposed` as sb[e][kb][nb]: the table of the un-transposed weight). Grouped when
+// offs / blk_expert are given (rows grouped by expert, padded to 128 per group).
+void gemm_fp8_block(const torch::Tensor& aq, const torch::Tensor& sa, const torch::Tensor& bq, const torch::Tensor& sb, bool sb_transposed,
+                    torch::Tensor& out, const c10::optional<torch::Tensor>& offs, const c10::optional<torch::Tensor>& blk_expert) {
+  TORCH_CHECK(aq.is_cuda() && aq.dim() == 2 && aq.scalar_type() == torch::kUInt8 && aq.stride(1) == 1 && bq.dim() == 3 && bq.is_contiguous() &&
+              bq.scalar_type() == torch::kUInt8 && sb.dim() == 3 && sb.is_contiguous() && sa.is_contiguous() && sa.scalar_type() == torch::kFloat32 &&
+              sb.scalar_type() == torch::kFloat32 && out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == torch::kBFloat16);
+  const int64_t M = aq.size(0), K = aq.size(1), G = bq.size(0), N = bq.size(1);
+  TORCH_CHECK(bq.size(2) == K && out.size(0) == M && out.size(1) == N && sa.size(0) == (K + 127) / 128 && sa.size(1) == M);
+  const bool grouped = offs.has_value();
+  if (grouped) {
+    TORCH_CHECK(i32(*offs) && blk_expert && i32(*blk_expert) && offs->numel() == G + 1 && blk_expert->numel() * 128 == M);
+  } else {
+    TORCH_CHECK(G == 1);
+  }
+  const int64_t NB = (N + 127) / 128, KB = (K + 127) / 128;
+  TORCH_CHECK(sb.size(0) == G && sb.size(1) == (sb_transposed ? KB : NB) && sb.size(2) == (sb_transposed ? NB : KB));
+  c10::cuda::CUDAGuard guard(aq.device());
+  int rc = mt_gemm_fp8_block(aq.data_ptr(), bq.data_ptr(), out.data_ptr(), (int)M, (int)N, (int)K, aq.stride(0), K, out.stride(0),
+                             sa.data_ptr<float>(), sb.data_ptr<float>(), sb.stride(0), sb_transposed ? 1 : sb.stride(1),
+                             sb_transposed ? sb.stride(1) : 1, grouped ? (int)G : 0, grouped ? offs->data_ptr<int>() : nullptr,
+                             grouped ? blk_expert->data_ptr<int>() : nullptr, mt_status_ptr(), mt_num_sms(), cur());
+  TORCH_CHECK(rc == 0, "mt_gemm_fp8_block failed with code ", rc);
+  mt_count_launches(1);
+}
+
 // logits [T,E] fp32 / bf16 -> (idx [T,k] int32, wts [T,k] fp32, probs [T,E] fp32, counts [E] int32), see router_sm100.cu
 std::vector<torch::Tensor> router_topk(const torch::Tensor& logits, const c10::optional<torch::Tensor>& bias, int64_t k, int64_t mode,
                                        bool sigmoid_scores, bool raw_weights, double scaling) {
@@ -202,6 +266,9 @@ void register_moe(pybind11::module_& m) {
   m.def("ep_pull", &ep_pull);
   m.def("ep_zero_pads", &ep_zero_pads);
   m.def("router_topk", &router_topk);
+  m.def("quant_fp8_rows", &quant_fp8_rows);
+  m.def("quant_fp8_blocks", &quant_fp8_blocks);
+  m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("moe_sort", &moe_sort);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);

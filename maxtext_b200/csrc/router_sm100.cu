@@ -47,7 +47,7 @@ __global__ void router_topk_kernel(const T* __restrict__ logits, const float* __
 #pragma unroll
   for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
     const int e = lane + 32 * j;
-    x[j] = (j < per && e < E) ? to_f<T>(logits[tok * E + e]) : -INFINITY;
+    x[j] = (j < per && e < E) ? to_f<T>(logits[tok * E + e]) + ((mode == 0 && bias) ? bias[e] : 0.f) : -INFINITY;      // mode 0: the bias is part of the logits
     mx = fmaxf(mx, x[j]);
   }
   mx = warp_max(mx);
@@ -73,8 +73,8 @@ __global__ void router_topk_kernel(const T* __restrict__ logits, const float* __
     const int e = lane + 32 * j;
     const bool live = j < per && e < E;
     if (live && probs_out) probs_out[tok * E + e] = sc[j];
-    const float b = (bias && live) ? bias[e] : 0.f;
-    sel[j] = !live ? -INFINITY : (mode == 1 ? sc[j] + b : x[j] + b);
+    const float b = (mode == 1 && bias && live) ? bias[e] : 0.f;              // mode 1: the bias only steers the selection
+    sel[j] = !live ? -INFINITY : (mode == 1 ? sc[j] + b : x[j]);
   }
   // k rounds of arg-max; the winner's lane keeps its value for the weight computation
   float wsel = 0.f;      // lane r (r < k) ends up holding the r-th winner: its selection value, score and expert
@@ -101,7 +101,7 @@ __global__ void router_topk_kernel(const T* __restrict__ logits, const float* __
       const int j = e >> 5;
 #pragma unroll
       for (int jj = 0; jj < ROUTER_MAX_PER_LANE; ++jj)
-        if (jj == j) { s_owner = (mode == 1) ? sc[jj] : x[jj] + (bias ? bias[e] : 0.f); sel[jj] = -INFINITY; }
+        if (jj == j) { s_owner = (mode == 1) ? sc[jj] : x[jj]; sel[jj] = -INFINITY; }
     }
     s_owner = __shfl_sync(0xffffffffu, s_owner, e & 31);
     if (lane == r) { wsel = v; wscore = s_owner; wexp = e; }

@@ -25,7 +25,20 @@ def _mask_nucleus(logits, p):
 
 def sampling(logits: torch.Tensor, strategy: str = "greedy", topk: int = 0, nucleus_p: float = -1.0, temperature: float = 1.0,
              generator: torch.Generator | None = None) -> torch.Tensor:
-  """logits [..., V] -> token ids [...]."""
+  """logits [..., V] -> token ids [...]. On a GPU every strategy is one launch of the sampling kernel (`csrc/sampling_sm100.cu`:
+  radix select for top-k, mass select for the nucleus, inverse CDF against one uniform number per row)."""
+  if strategy not in ("greedy", "weighted", "topk", "nucleus", "composite"):
+    raise ValueError(f"unknown decode_sampling_strategy {strategy}")
+  if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16):
+    from ..ops import backend
+    E = backend.ext(required=True)
+    flat = logits.reshape(-1, logits.shape[-1])
+    flat = flat if flat.is_contiguous() else flat.contiguous()
+    greedy = strategy == "greedy"
+    u = None if greedy else torch.rand(flat.shape[0], device=flat.device, generator=generator)
+    k = int(topk) if strategy in ("topk", "composite") else 0
+    p = float(nucleus_p) if strategy in ("nucleus", "composite") else -1.0
+    return E.sample_tokens(flat, u, k, p, float(temperature), greedy).reshape(logits.shape[:-1])
   lf = logits.float()
   if strategy == "greedy":
     return lf.argmax(-1)

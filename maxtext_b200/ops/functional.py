@@ -92,10 +92,13 @@ class _LinearFn(torch.autograd.Function):
     if saved_out is not None:
       # a copy: callers may transform the projection in place (rotary embedding on the packed q|k|v)
       return saved_out.reshape(-1, w.shape[0]).clone()
-    ctx.fp8 = _quant.supported(x2, w)
+    ctx.fp8b = _quant.block_supported(x2, w)
+    ctx.fp8 = not ctx.fp8b and _quant.supported(x2, w)
     ctx.fp8_saved = None
     ctx.int8 = _quant.int8_on()
-    if ctx.int8:
+    if ctx.fp8b:
+      y = _quant.block_linear_fwd(x2, w)
+    elif ctx.int8:
       y = _quant.int8_linear_fwd(x2, w)
     elif ctx.fp8:
       y, ctx.fp8_saved = _quant.linear_fwd(x2, w, pv, keep_for_bwd=True)     # this forward will be differentiated: quantise once for both passes
@@ -123,6 +126,8 @@ class _LinearFn(torch.autograd.Function):
       return dx, None, None, None, dbias, None, None
     if not ctx.needs_input_grad[0]:
       dx = None
+    elif getattr(ctx, "fp8b", False) and ctx.tp_reduce_dx is None and _quant.block_supported(dy2, w):
+      dx = _quant.block_linear_dx(dy2, w)
     elif getattr(ctx, "int8", False) and ctx.tp_reduce_dx is None:
       dx = _quant.int8_linear_dx(dy2, w)
     elif ctx.tp_reduce_dx is not None:
@@ -156,7 +161,8 @@ def linear(x: torch.Tensor, p, saved_out: torch.Tensor | None = None, bias=None,
   if not torch.is_grad_enabled():
     if saved_out is not None:
       return saved_out
-    y = (pre if pre is not None else _quant.int8_linear_fwd(x2, p.data) if _quant.int8_on() else
+    y = (pre if pre is not None else _quant.block_linear_fwd(x2, p.data) if _quant.block_supported(x2, p.data) else
+         _quant.int8_linear_fwd(x2, p.data) if _quant.int8_on() else
          (_quant.linear_fwd(x2, p.data, p) if _quant.supported(x2, p.data) else mm(x2, p.data, False, True)))
     if lo is not None:
       y = y + _lora_delta(x2, lo).to(y.dtype)

@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import backend
+from . import quantization as _quant
 from . import functional as F
 
 
@@ -199,12 +200,23 @@ class _ExpertsFFNFn(torch.autograd.Function):
     E_ = backend.ext()
     Fdim = w0.shape[1]
     gu = torch.empty(plan.rows_max, 2 * Fdim, dtype=rows.dtype, device=rows.device)
-    E_.grouped_gemm(1, rows, w0, gu[:, :Fdim], plan.offs, plan.blk_expert, False)
-    E_.grouped_gemm(1, rows, w1, gu[:, Fdim:], plan.offs, plan.blk_expert, False)
+    f8 = _quant.block_on() and Fdim % 16 == 0 and rows.shape[1] % 16 == 0      # block-scaled 8-bit forward / input-gradient products
+    ctx.f8 = f8
     h = torch.empty(plan.rows_max, Fdim, dtype=rows.dtype, device=rows.device)
-    E_.gated_act_fwd(gu, h, F._ACT_CODE[act])
     y = torch.empty(plan.rows_max, wo.shape[1], dtype=rows.dtype, device=rows.device)
-    E_.grouped_gemm(1, h, wo, y, plan.offs, plan.blk_expert, False)
+    if f8:
+      E8 = backend.ext()
+      rq, sr = E8.quant_fp8_rows(rows)                                         # one quantisation of the rows feeds both up-projections
+      for w_, dst in ((w0, gu[:, :Fdim]), (w1, gu[:, Fdim:])):
+        wq, _, sw = E8.quant_fp8_blocks(w_, True, False)
+        E8.gemm_fp8_block(rq, sr, wq, sw, False, dst, plan.offs, plan.blk_expert)
+      E_.gated_act_fwd(gu, h, F._ACT_CODE[act])
+      _quant.block_grouped_fwd(h, wo, plan.offs, plan.blk_expert, y)
+    else:
+      E_.grouped_gemm(1, rows, w0, gu[:, :Fdim], plan.offs, plan.blk_expert, False)
+      E_.grouped_gemm(1, rows, w1, gu[:, Fdim:], plan.offs, plan.blk_expert, False)
+      E_.gated_act_fwd(gu, h, F._ACT_CODE[act])
+      E_.grouped_gemm(1, h, wo, y, plan.offs, plan.blk_expert, False)
     ctx.save_for_backward(rows, gu, w0, w1, wo)
     ctx.misc = (p0, p1, po, plan, act)
     return y
@@ -219,17 +231,25 @@ class _ExpertsFFNFn(torch.autograd.Function):
     h = torch.empty(plan.rows_max, Fdim, dtype=rows.dtype, device=rows.device)
     E_.gated_act_fwd(gu, h, F._ACT_CODE[act])                     # recomputed: cheaper than keeping it
     g_o = _dw_into(po, dy, h, plan, wo.shape)
+    f8 = getattr(ctx, "f8", False)
     dh = h                                                          # reuse the buffer
-    E_.grouped_gemm(2, dy, wo, dh, plan.offs, plan.blk_expert, False)
+    if f8:
+      _quant.block_grouped_dx(dy, wo, plan.offs, plan.blk_expert, dh)
+    else:
+      E_.grouped_gemm(2, dy, wo, dh, plan.offs, plan.blk_expert, False)
     dgu = torch.empty_like(gu)
     E_.gated_act_bwd(dh, gu, dgu, F._ACT_CODE[act])
     d0, d1 = dgu[:, :Fdim], dgu[:, Fdim:]
     g_0 = _dw_into(p0, d0, rows, plan, w0.shape)
     g_1 = _dw_into(p1, d1, rows, plan, w1.shape)
     drows = torch.empty_like(rows)
-    E_.grouped_gemm(2, d0, w0, drows, plan.offs, plan.blk_expert, False)
     tmp = torch.empty_like(rows)
-    E_.grouped_gemm(2, d1, w1, tmp, plan.offs, plan.blk_expert, False)
+    if f8:
+      _quant.block_grouped_dx(d0, w0, plan.offs, plan.blk_expert, drows)
+      _quant.block_grouped_dx(d1, w1, plan.offs, plan.blk_expert, tmp)
+    else:
+      E_.grouped_gemm(2, d0, w0, drows, plan.offs, plan.blk_expert, False)
+      E_.grouped_gemm(2, d1, w1, tmp, plan.offs, plan.blk_expert, False)
     drows.add_(tmp)
     return drows, g_0, g_1, g_o, None, None, None, None, None
 

@@ -144,3 +144,64 @@ def int8_linear_dx(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
   gq, sg = _q8(dy2, 1)         # per token
   wq, sw = _q8(w, 0)           # per input feature (the contraction now runs over the output features)
   return (_imm(gq, wq.t().contiguous()) * sg * sw).to(dy2.dtype)
+
+
+# ------------------------------------------------------------------------------------------------------- block-scaled fp8
+# `quantization=fp8` with `fp8_block_scaling=true`: E4M3 operands with one fp32 scale per 1 x 128 block of the contraction
+# dimension for activations / gradients and one per 128 x 128 block for weights (the recipe of DeepSeek-V3 style training;
+# the reference reaches block-scaled formats through src/maxtext/layers/quantizations.py:1022-1043 and quantises around the
+# expert collectives in src/maxtext/models/deepseek_batchsplit_fp8.py:42-98). The forward and the input-gradient products
+# run on `csrc/gemm_fp8_block_sm100.cu`; the weight-gradient product stays in bf16 with fp32 accumulation into the store.
+_BLOCK = False
+
+
+def set_block_scaling(on: bool):
+  global _BLOCK
+  _BLOCK = bool(on)
+
+
+def block_on() -> bool:
+  return _MODE == "fp8" and _BLOCK
+
+
+def block_supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
+  return (block_on() and backend.use_cuda_kernels(x2) and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
+          and x2.shape[1] % 16 == 0 and w.shape[0] % 16 == 0 and w.is_contiguous() and hasattr(backend.ext(), "gemm_fp8_block"))
+
+
+def block_linear_fwd(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+  """y = x W^T: x quantised 1 x 128 along `in`, W [out, in] in 128 x 128 blocks."""
+  E = backend.ext()
+  xq, sx = E.quant_fp8_rows(x2)
+  wq, _, sw = E.quant_fp8_blocks(w, True, False)
+  y = torch.empty(x2.shape[0], w.shape[0], dtype=torch.bfloat16, device=x2.device)
+  E.gemm_fp8_block(xq, sx, wq, sw, False, y, None, None)
+  return y
+
+
+def block_linear_dx(dy2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+  """dx = dy W: dy quantised 1 x 128 along `out`; the operand is the transposed 8-bit copy of W with the same block scales."""
+  E = backend.ext()
+  gq, sg = E.quant_fp8_rows(dy2)
+  _, wt, sw = E.quant_fp8_blocks(w, False, True)            # wt [1, in, out]; sw [1, out/128, in/128] is read transposed
+  dx = torch.empty(dy2.shape[0], w.shape[1], dtype=torch.bfloat16, device=dy2.device)
+  E.gemm_fp8_block(gq, sg, wt, sw, True, dx, None, None)
+  return dx
+
+
+def block_grouped_fwd(rows: torch.Tensor, w: torch.Tensor, offs, blk_expert, out: torch.Tensor):
+  """out = rows W_e^T over padded expert groups (W [E, out, in])."""
+  E = backend.ext()
+  rq, sr = E.quant_fp8_rows(rows)
+  wq, _, sw = E.quant_fp8_blocks(w, True, False)
+  E.gemm_fp8_block(rq, sr, wq, sw, False, out, offs, blk_expert)
+  return out
+
+
+def block_grouped_dx(dy: torch.Tensor, w: torch.Tensor, offs, blk_expert, out: torch.Tensor):
+  """out = dy W_e over padded expert groups."""
+  E = backend.ext()
+  gq, sg = E.quant_fp8_rows(dy)
+  _, wt, sw = E.quant_fp8_blocks(w, False, True)
+  E.gemm_fp8_block(gq, sg, wt, sw, True, out, offs, blk_expert)
+  return out

@@ -53,6 +53,7 @@ class TrainEngine:
     from ..ops import quantization as _quant
     _quant.set_mode(str(c.quantization or ""))
     _quant.set_delayed_scaling(int(getattr(c, "fp8_amax_history_len", 0)))
+    _quant.set_block_scaling(bool(getattr(c, "fp8_block_scaling", False)))
     self.store = self.model.store
     if init:
       self.store.initialize(seed=c.init_weights_seed)
