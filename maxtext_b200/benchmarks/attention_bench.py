@@ -34,6 +34,7 @@ def main():
   ap.add_argument("--hq", type=int, default=32)
   ap.add_argument("--hkv", type=int, default=8)
   ap.add_argument("--dim", type=int, default=128)
+  ap.add_argument("--dim-v", type=int, default=0, help="head dim of V / O when it differs (multi-head latent attention: --dim 192 --dim-v 128)")
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--small", action="store_true")
   ap.add_argument("--no-lib", action="store_true")
@@ -43,17 +44,25 @@ def main():
   from maxtext_b200.ops import backend
   E = backend.ext(required=True)
   B, S, Hq, Hkv, D = a.batch, a.seq, a.hq, a.hkv, a.dim
-  qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
-  q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
-  out = torch.empty(B, S, Hq, D, device="cuda", dtype=torch.bfloat16)
+  Dv = a.dim_v or D
+  if Dv == D:
+    qkv = (0.3 * torch.randn(B, S, Hq + 2 * Hkv, D, device="cuda")).bfloat16()
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
+  else:
+    q = (0.3 * torch.randn(B, S, Hq, D, device="cuda")).bfloat16()
+    k = (0.3 * torch.randn(B, S, Hkv, D, device="cuda")).bfloat16()
+    v = (0.3 * torch.randn(B, S, Hkv, Dv, device="cuda")).bfloat16()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    a.no_lib = True
+  out = torch.empty(B, S, Hq, Dv, device="cuda", dtype=torch.bfloat16)
   lse = torch.empty(B, Hq, S, device="cuda")
   dout = torch.randn_like(out)
-  dqkv = torch.empty_like(qkv)
-  dq, dk, dv = dqkv[:, :, :Hq], dqkv[:, :, Hq:Hq + Hkv], dqkv[:, :, Hq + Hkv:]
-  fwd_flops = 4.0 * B * S * S * Hq * D / 2
+  fwd_flops = 2.0 * B * S * S * Hq * (D + Dv) / 2
   ms_f = timeit(lambda: E.flash_fwd(q, k, v, out, lse, None, None, None, None, None, 1.0, 0.0, True, 0, 0, 0), a.iters)
   ms_b = timeit(lambda: E.flash_bwd(dout, q, k, v, out, lse, dq, dk, dv, None, None, None, None, 1.0, 0.0, True, 0, 0, 0), a.iters)
-  row = {"B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9, "bwd_ms": ms_b,
+  row = {"B": B, "S": S, "Hq": Hq, "Hkv": Hkv, "D": D, "Dv": Dv, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9, "bwd_ms": ms_b,
          "bwd_tflops": 2.5 * fwd_flops / ms_b / 1e9, "kernel_status": E.kernel_status(True)}
   if not a.no_lib:
     qh, kh, vh = (t.transpose(1, 2).contiguous().requires_grad_(True) for t in (q, k, v))

@@ -81,6 +81,14 @@ def main():
       ref = torch.mm(sets[1][0].float()[:256], sets[1][1].float().t())
       E.gemm_fp8(q[1][0][0], q[1][1][0], out, 0, 0, q[1][0][2], q[1][1][2], False)
       row.update(fp8_rel_err=float((out[:256].float() - ref).abs().max() / ref.abs().max()))
+      # block-scaled form (1 x 128 activation, 128 x 128 weight scales): the product alone, then with both quantisations
+      qb = [(E.quant_fp8_rows(a), E.quant_fp8_blocks(b, True, False)) for a, b in sets]
+      msb = time_fn(lambda i: E.gemm_fp8_block(qb[i & 1][0][0], qb[i & 1][0][1], qb[i & 1][1][0], qb[i & 1][1][2], False, out, None, None),
+                    args.iters)
+      msq = time_fn(lambda i: (E.quant_fp8_rows(sets[i & 1][0]), E.quant_fp8_blocks(sets[i & 1][1], True, False)), args.iters)
+      E.gemm_fp8_block(qb[1][0][0], qb[1][0][1], qb[1][1][0], qb[1][1][2], False, out, None, None)
+      row.update(fp8_block_ms=msb, fp8_block_tflops=2.0 * M * N * K / msb / 1e9, fp8_block_quant_ms=msq,
+                 fp8_block_rel_err=float((out[:256].float() - ref).abs().max() / ref.abs().max()))
     rows.append(row)
     print(json.dumps(row), flush=True)
     del sets, out

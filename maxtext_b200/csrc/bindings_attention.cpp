@@ -14,7 +14,7 @@ int mt_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
 int mt_flash_bwd_supported(int Dqk, int Dv);
 int mt_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, void* dq,
                  void* dk, void* dv, const int* seg_q, const int* seg_k, const int* pos_q, const int* pos_k, int* tiles, int B, int Sq, int Skv,
-                 int Hq, int Hkv, int D, long ldq, long bsq, long ldk, long bsk, long ldv, long bsv, long lddq, long bsdq, long lddk, long bsdk,
+                 int Hq, int Hkv, int D, int Dv, long ldq, long bsq, long ldk, long bsk, long ldv, long bsv, long lddq, long bsdq, long lddk, long bsdk,
                  long lddv, long bsdv, float scale, float softcap, int causal, int window, int chunk, int q_off, int* status, cudaStream_t st);
 }
 
@@ -96,7 +96,7 @@ void flash_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::T
   int rc = mt_flash_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
                         dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), opt_int(seg_q, (int64_t)B * Sq, "seg_q"), opt_int(seg_k, (int64_t)B * Skv, "seg_k"),
                         opt_int(pos_q, (int64_t)B * Sq, "pos_q"), opt_int(pos_k, (int64_t)B * Skv, "pos_k"), pos_q ? tiles.data_ptr<int>() : nullptr,
-                        B, Sq, Skv, Hq, (int)k.size(2), (int)q.size(3), q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+                        B, Sq, Skv, Hq, (int)k.size(2), (int)q.size(3), (int)v.size(3), q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
                         dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), (float)scale, (float)softcap,
                         causal ? 1 : 0, (int)window, (int)chunk, (int)q_off, mt_status_ptr(), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "mt_flash_bwd failed with code ", rc);

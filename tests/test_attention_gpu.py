@@ -190,10 +190,12 @@ def _fwd_general(B, Sq, Skv, Hq, Hkv, Dqk, Dv, *, causal=True, window=0, chunk=0
   dout = torch.randn(B, Sq, Hq, Dv, device="cuda", generator=g).bfloat16() * rows[:, :, None, None]
   ql, kl, vl = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
   skl = sk.detach().clone().requires_grad_(True) if sinks else None
+  before = F.attention_fallbacks()
   o2 = F.attention(ql, kl, vl, pos_q, seg_q, scale, softcap, window, causal, chunk=chunk, sinks=skl, **kw)
   o2.backward(dout)
   torch.cuda.synchronize()
   assert E.kernel_status(True) == 0
+  assert F.attention_fallbacks() == before, "the backward left the kernels"
   qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
   skf = sk.detach().clone().requires_grad_(True) if sinks else None
   ref.attention(qf, kf, vf, mask, scale, softcap, sinks=skf).backward(dout.float())
@@ -218,6 +220,8 @@ def test_fwd_more_keys_than_queries_bottom_right_causal():
 def test_fwd_mla_shape_192_128():
   _fwd_general(2, 384, 384, 4, 4, 192, 128, scale=0.07)
   _fwd_general(1, 257, 257, 2, 2, 192, 128, scale=0.07, seg=True)
+  _fwd_general(1, 200, 600, 4, 2, 192, 128, scale=0.07, window=250)
+  _fwd_general(1, 512, 512, 2, 1, 192, 128, scale=0.07, arrays=True)
 
 
 def test_fwd_logit_softcap():
