@@ -3,10 +3,11 @@
 //
 //   C[m, n] = sum_kb  sa[kb, m] * sb[n / 128, kb] * sum_{k in block kb} Aq[m, k] * Bq[n, k]
 //
-// The tensor core (tcgen05 kind::f8f6f4) forms the inner sum of one 128-wide K block in tensor memory; the four epilogue warps
+// The tensor core (tcgen05 kind::f8f6f4) forms the inner sum of one 128-wide K block in tensor memory; sixteen epilogue warps
 // read that partial product, multiply it by the two scales of the block and add it to fp32 accumulators that live in their
-// registers for the whole K loop (a thread owns one row of the 128 x 128 output tile). Two TMEM buffers alternate, so the
-// tensor core works on block kb + 1 while block kb is being promoted. The same kernel serves mixture-of-experts layers: rows
+// registers for the whole K loop (a thread owns 32 columns of one row of the 128 x 128 output tile; four warps per scheduler hide
+// the latency of the tensor-memory loads). Four TMEM buffers rotate, so
+// the tensor core runs up to three K blocks ahead of the promotion. The same kernel serves mixture-of-experts layers: rows
 // grouped by expert and padded to 128 per group, one weight matrix (and one scale table) per expert.
 //
 // The two quantisation kernels that produce the operands are here as well: 1 x 128 for activations / gradients (scales stored
@@ -15,6 +16,7 @@
 #include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <stdlib.h>
 
 namespace mt {
 namespace f8b {
@@ -24,8 +26,10 @@ constexpr int STAGES = 5;
 constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_BYTES = 2 * BM * 128;            // two 64-column bf16 staging buffers
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 256 + 1024;
-constexpr int THREADS = 192;
-constexpr uint32_t TMEM_COLS = 256;
+constexpr int THREADS = 576;                       // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..17: promotion / epilogue
+constexpr int EPI_THREADS = 512;
+constexpr int NACC = 4;
+constexpr uint32_t TMEM_COLS = NACC * BN;
 
 struct Params {
   int M, N, K;
@@ -50,11 +54,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-  auto tempty = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  auto tempty = [&](int a) { return bars + 8u * (2 * STAGES + NACC + a); };
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (bars - base) + 8 * (2 * STAGES + 4));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (bars - base) + 8 * (2 * STAGES + 2 * NACC));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  volatile int* epi_ok = abort_flag + 1;      // two slots, alternating per K block: a late reader never sees the next block's verdict
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_blocks = p.experts ? p.x_offs[p.experts] / BM : (p.M + BM - 1) / BM;
@@ -65,7 +68,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 128); }
+    for (int a = 0; a < NACC; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), EPI_THREADS); }
     fence_barrier_init();
     prefetch_tensormap(&map_a); prefetch_tensormap(&map_b); prefetch_tensormap(&map_c);
   }
@@ -118,66 +121,66 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           umma_commit(empty(s));
           umma_commit(tfull(acc));
           if (++s == STAGES) { s = 0; ph ^= 1; }
-          if (++acc == 2) { acc = 0; aph ^= 1; }
+          if (++acc == NACC) { acc = 0; aph ^= 1; }
         }
       }
     }
   } else {
-    const int q = warp & 3, row = q * 32 + lane, et = threadIdx.x - 64;
-    int acc = 0, buf = 0;
+    // A thread owns columns [cg * 32, cg * 32 + 32) of row `row` of the tile. Every thread waits on the barriers itself; one
+    // that gave up (ok = false) keeps meeting the others at the named barriers of the output stage but touches no tensor memory.
+    const int q = warp & 3, cg = (warp - 2) >> 2, row = q * 32 + lane, et = threadIdx.x - 64;
+    int acc = 0;
     uint32_t aph = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int mb, nb;
       coords(t, mb, nb);
       const int e = p.experts ? p.blk_expert[mb] : 0;
       const long m = (long)mb * BM + row;
       const bool row_ok = m < p.M;
+      const float* sap = p.sa + (row_ok ? m : 0);
       const float* sbp = p.sb + e * p.sb_e + nb * p.sb_n;
-      float c[BN];
+      float c[32];
 #pragma unroll
-      for (int j = 0; j < BN; ++j) c[j] = 0.f;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const float s = (row_ok ? p.sa[(long)kb * p.M + m] : 0.f) * sbp[kb * p.sb_k];
-        if (et == 0) epi_ok[kb & 1] = mbar_wait(tfull(acc), aph, abort_flag, p.status, ST_TIMEOUT_EPILOGUE) ? 1 : 0;
-        named_bar_sync(3, 128);
-        if (epi_ok[kb & 1] == 0) { ok = false; break; }
+      for (int j = 0; j < 32; ++j) c[j] = 0.f;
+      float s_next = row_ok ? sap[0] * sbp[0] : 0.f;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const float sc = s_next;
+        if (kb + 1 < num_kb) s_next = row_ok ? sap[(long)(kb + 1) * p.M] * sbp[(long)(kb + 1) * p.sb_k] : 0.f;   // in flight during the wait
+        if (!mbar_wait(tfull(acc), aph, abort_flag, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t ta = tmem + acc * BN + ((uint32_t)(q * 32) << 16);
-#pragma unroll
-        for (int ch = 0; ch < BN / 32; ++ch) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(ta + ch * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) c[ch * 32 + j] = fmaf(__uint_as_float(r[j]), s, c[ch * 32 + j]);
-        }
+        if (DUMMY == 0) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem + acc * BN + cg * 32 + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(tempty(acc));
-        if (++acc == 2) { acc = 0; aph ^= 1; }
+        mbar_arrive(tempty(acc));                       // the values are in registers: the tensor core may reuse the buffer
+#pragma unroll
+        for (int j = 0; j < 32; ++j) c[j] = fmaf(__uint_as_float(r[j]), sc, c[j]);
+        } else { c[0] += sc; tc_fence_before(); mbar_arrive(tempty(acc)); }
+        if (++acc == NACC) { acc = 0; aph ^= 1; }
       }
-      if (!ok) break;
-      // bf16 output through two 64-column staging buffers and TMA stores (rows beyond M are clipped by the tensor map)
+      // bf16 output: two 64-column staging boxes, each filled by two column groups; one thread stores both (rows beyond M are
+      // clipped by the map)
+      if (et == 0) tma_wait_group_read<0>();
+      named_bar_sync(1, EPI_THREADS);
+      const uint32_t sbuf = sEpi + (cg >> 1) * (BM * 128);
 #pragma unroll
-      for (int h = 0; h < BN / 64; ++h) {
-        if (et == 0) tma_wait_group_read<1>();
-        named_bar_sync(1, 128);
-        const uint32_t sbuf = sEpi + buf * (BM * 128);
+      for (int j = 0; j < 4; ++j) {
+        uint32_t pk[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t pk[4];
+        for (int x = 0; x < 4; ++x) pk[x] = pack_bf16(c[8 * j + 2 * x], c[8 * j + 2 * x + 1]);
+        const uint32_t dst = sbuf + row * 128 + ((((cg & 1) * 4 + j) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+      }
+      if (!ok) *abort_flag = 1;
+      fence_proxy_async_smem();
+      named_bar_sync(2, EPI_THREADS);
+      if (et == 0 && *abort_flag == 0) {
 #pragma unroll
-          for (int x = 0; x < 4; ++x) pk[x] = pack_bf16(c[h * 64 + 8 * j + 2 * x], c[h * 64 + 8 * j + 2 * x + 1]);
-          const uint32_t dst = sbuf + row * 128 + ((j ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
-        }
-        fence_proxy_async_smem();
-        named_bar_sync(2, 128);
-        if (et == 0) {
-          if (nb * BN + h * 64 < p.N) tma_store_2d(&map_c, sbuf, nb * BN + h * 64, mb * BM);
-          tma_commit_group();
-        }
-        buf ^= 1;
+        for (int h = 0; h < BN / 64; ++h)
+          if (nb * BN + h * 64 < p.N) tma_store_2d(&map_c, sEpi + h * (BM * 128), nb * BN + h * 64, mb * BM);
+        tma_commit_group();
       }
     }
     if (et == 0) tma_wait_group<0>();
@@ -355,6 +358,9 @@ int mt_gemm_fp8_block(const void* aq, const void* bq, void* c, int M, int N, int
   }
   const int tiles = (M / BM + (M % BM != 0)) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
+  static int probe = getenv("MT_F8B_PROBE") ? 1 : 0;
+  if (probe) { cudaFuncSetAttribute(gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); gemm_kernel<1><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, mc, p); }
+  else
   gemm_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, mc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

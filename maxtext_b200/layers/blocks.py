@@ -471,6 +471,12 @@ class MLA:
     self.wkv_b = ab.sub("wkv_b").linear("kernel", (c.kv_lora_rank,), (c.num_query_heads, self.nope + self.vd),
                                         ("kv_lora", "kv_heads", "kv_head_dim"), tp="col")
     self.o = ab.sub("out").linear("kernel", (c.num_query_heads, self.vd), (d,), ("heads", "kv", "embed"), tp="row")
+    self.indexer = None
+    if bool(getattr(c, "use_indexer", False)):
+      # src/maxtext/layers/attention_mla.py:735-750: DeepSeek-V3.2 sparse attention; shares the rotary table, not the layout
+      from .indexer import Indexer
+      assert b.tp_size == 1, "use_indexer is not split over the tensor axis"
+      self.indexer = Indexer(ab, c, rope_inv_ts)
     scale = self.qk ** -0.5
     if c.max_position_embeddings > c.original_max_position_embeddings and c.rope_type == "yarn":
       m = 0.1 * c.mscale * math.log(c.rope_factor) + 1.0
@@ -481,10 +487,12 @@ class MLA:
     c = self.c
     x = tp_enter(x, ctx)
     B, S, _ = x.shape
+    low_rank_q = None
     if self.query is not None:
       q = F.linear(x, self.query)
     else:
-      q = F.linear(self.q_norm(F.linear(x, self.wq_a)), self.wq_b)
+      low_rank_q = self.q_norm(F.linear(x, self.wq_a))
+      q = F.linear(low_rank_q, self.wq_b)
     q = q.view(B, S, self.h, self.qk)
     q_nope, q_rope = q[..., :self.nope], q[..., self.nope:]
     q_rope = F.rope(q_rope, ctx.positions, self.inv_ts, self.interleaved)
@@ -501,7 +509,16 @@ class MLA:
       v = kv[..., self.nope:]
       if c.use_qk_clip and ctx.mode == "train" and not ctx.recompute and ctx.max_logits is not None:
         ctx.max_logits[(ctx.layer_index, self)] = _max_logit_per_head(q, k, ctx.positions, ctx.segment_ids)
-      out = F.attention(q, k.contiguous(), v.contiguous(), ctx.positions, ctx.segment_ids, 1.0, 0.0, 0)
+      sparse = None
+      if self.indexer is not None:
+        sparse, score, allowed = self.indexer(x, low_rank_q, ctx.positions, ctx.segment_ids)
+        if sparse is not None and ctx.mode == "train" and float(c.indexer_loss_scaling_factor) > 0:
+          ctx.aux_losses.append(("indexer_loss", self.indexer.loss(score, q, k, allowed, sparse)))
+      if sparse is not None:
+        # a per-query key set is not a mask form of the flash kernels: this path is the fp32 definition with an explicit mask
+        out = ref.attention(q, k, v, sparse, 1.0)
+      else:
+        out = F.attention(q, k.contiguous(), v.contiguous(), ctx.positions, ctx.segment_ids, 1.0, 0.0, 0)
     y = F.linear(out.reshape(B, S, -1), self.o)
     return tp_exit(y, ctx)
 

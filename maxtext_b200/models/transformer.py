@@ -96,6 +96,12 @@ class DecoderBlock:
     else:
       self.mlp = L.MLP(b, c, plan.mlp_name + s, plan.mlp_hidden, bias=plan.mlp_bias)
     self.n2b = mk(plan.post_mlp_norm) if plan.post_mlp_norm else None
+    self.mhc_attn = self.mhc_mlp = None
+    if int(getattr(c, "mhc_expansion_rate", 1)) > 1:
+      # src/maxtext/models/deepseek.py:177-179: each branch of the block is wrapped by its own hyper-connection
+      from ..layers.mhc import HyperConnection
+      self.mhc_attn = HyperConnection(b, c, "mhc_attention", c.emb_dim)
+      self.mhc_mlp = HyperConnection(b, c, "mhc_mlp", c.emb_dim)
     if b.tp_size > 1 and L.sp_enabled(c):
       # sequence-parallel residual stream: these norms see this rank's tokens only, their scale gradients are partial sums
       for n_ in (self.n1, self.n1b, self.n2, self.n2b):
@@ -104,6 +110,9 @@ class DecoderBlock:
             v_.pdef.tp_partial = True
 
   def __call__(self, x, ctx: LayerCtx):
+    if self.mhc_attn is not None:               # x [B, S, k, D]: the residual adds live inside the hyper-connections
+      x = self.mhc_attn(self.n1, lambda h: self.attn(h, ctx), x)
+      return self.mhc_mlp(self.n2, lambda h: self.mlp(h, ctx), x)
     a = self.attn(self.n1(x) if self.n1 is not None else x, ctx)
     if self.n1b is not None:
       a = self.n1b(a)
@@ -134,6 +143,21 @@ class DecoderLayer:
     ctx.name_prefix = ""
     ctx.cache = caches
     return x
+
+
+class _CollapsingNorm:
+  """Final norm of a model with hyper-connections: the k residual streams are summed before the norm
+  (src/maxtext/layers/decoders.py:1279-1288)."""
+
+  def __init__(self, norm):
+    self.norm = norm
+    self.scale, self.bias = norm.scale, norm.bias
+
+  def __call__(self, x):
+    if x.dim() == 4:
+      from ..layers.mhc import reduce_streams
+      x = reduce_streams(x)
+    return self.norm(x)
 
 
 class MTPLayer:
@@ -202,6 +226,7 @@ class Transformer:
           "embedding", (c.trainable_position_size, c.emb_dim), (None, "embed"))
     self.embed_params = eb.params if self.has_embed else []
     # ---- layers
+    self.mhc_k = int(getattr(c, "mhc_expansion_rate", 1) or 1)
     self.layers: list[DecoderLayer] = []
     counters: dict[str, int] = {}
     for i, plan in enumerate(families.layer_plans(c)):
@@ -222,8 +247,9 @@ class Transformer:
       self.mtp_params = mb.params
     # ---- head unit
     hb = L.Builder(c, "head", None, None, **self.par)
-    self.final_norm = L.Norm(hb.sub("decoder"), "decoder_norm", c.emb_dim, c.normalization_layer_epsilon,
-                             self.family.norm_offset, kind=self.family.norm_kind)
+    norm = L.Norm(hb.sub("decoder"), "decoder_norm", c.emb_dim, c.normalization_layer_epsilon,
+                  self.family.norm_offset, kind=self.family.norm_kind)
+    self.final_norm = _CollapsingNorm(norm) if self.mhc_k > 1 else norm
     self.logits_dense = None
     if not c.logits_via_embedding:
       self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
@@ -314,6 +340,9 @@ class Transformer:
       x = x + torch.cat([torch.sin(ang), torch.cos(ang)], dim=-1).to(x.dtype)
     if self.pos_embedding is not None:
       x = x + self.pos_embedding.leaf()[positions.long()].to(x.dtype)
+    if self.mhc_k > 1:
+      from ..layers.mhc import expand_streams
+      x = expand_streams(x, self.mhc_k)        # src/maxtext/layers/decoders.py:880-883
     return x
 
   def head_param(self):

@@ -55,7 +55,7 @@ class ParamDef:
   logical_axes: tuple            # logical names of the reference dims
   kind: str = "linear"           # "linear": ref [in..,out..] <-> internal [out,in]; "same": identical layout
   n_in_dims: int = 1             # for kind=linear: how many leading ref dims are "in"
-  init: str = "fan_in_trunc"     # fan_in_trunc | fan_in_normal | embed | ones | zeros | normal | log_uniform_16
+  init: str = "fan_in_trunc"     # fan_in_trunc | fan_in_normal | embed | ones | zeros | const | normal | log_uniform_16
   init_scale: float = 1.0
   layer: int | None = None       # index along the stacked layer axis
   stack: str | None = None       # name of the stacked collection in the reference tree ("layers", "dense_layers"...)
@@ -200,6 +200,8 @@ def init_full_tensor(pdef: ParamDef, device, base_seed: int, mode: str = "refere
     return torch.ones(pdef.shape, dtype=torch.float32, device=device)
   if pdef.init == "zeros":
     return torch.zeros(pdef.shape, dtype=torch.float32, device=device)
+  if pdef.init == "const":
+    return torch.full(pdef.shape, float(pdef.init_scale), dtype=torch.float32, device=device)     # init_scale carries the constant
   if pdef.init == "log_uniform_16":
     # decay rates of the gated delta network: log of U(0, 16) (src/maxtext/models/qwen3.py:547-552)
     t = torch.empty(pdef.global_shape(), dtype=torch.float32, device=device).uniform_(1e-9, 16.0, generator=gen)

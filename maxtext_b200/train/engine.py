@@ -369,7 +369,7 @@ class TrainEngine:
 
   def _run_head(self, x, targets, weights, compute_grads):
     c, model = self.config, self.model
-    B, S, D = x.shape
+    B, S, D = x.shape[0], x.shape[1], x.shape[-1]      # x is [B, S, k, D] when hyper-connections widen the residual stream
     fn = getattr(self, "_custom_loss", None)
     if fn is not None and compute_grads:
       x_in = x.detach().requires_grad_(True)
