@@ -84,7 +84,8 @@ bool gemm_supported(const torch::Tensor& a, const torch::Tensor& b, const torch:
   if (!is2d_rowmajor(out, out.scalar_type() == torch::kFloat32 ? 4 : 8)) return false;
   const int64_t M = ta ? a.size(1) : a.size(0), K = ta ? a.size(0) : a.size(1), N = tb ? b.size(0) : b.size(1);
   if ((tb ? b.size(1) : b.size(0)) != K || out.size(0) != M || out.size(1) != N) return false;
-  return M >= 128 && N >= 128 && K >= 64 && M % 8 == 0 && N % 8 == 0 && K % 8 == 0;
+  // M is a contiguous dimension only of a transposed A; elsewhere TMA clips the ragged last row block
+  return M >= 128 && N >= 128 && K >= 64 && (!ta || M % 8 == 0) && N % 8 == 0 && K % 8 == 0;
 }
 
 // CTA-pair (cta_group::2) kernel for shapes it covers: measured 3-10 % faster than the single-CTA kernel under sustained load

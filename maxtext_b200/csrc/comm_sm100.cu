@@ -308,13 +308,47 @@ extern "C" int mt_gather_segments(const void* const* peer_shards, void* full, lo
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// The same all-gather issued to the copy engines: one peer-to-local DMA per rank on `st`, no SM time. `peer_ptrs` are host values.
+// The same all-gather issued to the copy engines: one peer-to-local DMA per rank, no SM time. `peer_ptrs` are host values.
+// The copies are spread over a few helper streams that fork from and join back into `st`, so several copy engines (and several
+// NVLink peers) work at once; issued back to back on one stream they run one after another.
+namespace {
+constexpr int kDmaLanes = 4;
+struct DmaLanes {
+  cudaStream_t s[kDmaLanes];
+  cudaEvent_t fork, join[kDmaLanes];
+  bool ok = false;
+};
+DmaLanes* dma_lanes() {
+  static DmaLanes lanes[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  DmaLanes& l = lanes[dev];
+  if (!l.ok) {
+    if (cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int i = 0; i < kDmaLanes; ++i)
+      if (cudaStreamCreateWithFlags(&l.s[i], cudaStreamNonBlocking) != cudaSuccess ||
+          cudaEventCreateWithFlags(&l.join[i], cudaEventDisableTiming) != cudaSuccess)
+        return nullptr;
+    l.ok = true;
+  }
+  return &l;
+}
+}  // namespace
+
 extern "C" int mt_gather_dma(const long long* peer_ptrs, void* full, long chunk_bytes, int world, int first, cudaStream_t st) {
+  DmaLanes* l = world > 2 ? dma_lanes() : nullptr;
+  if (l && cudaEventRecord(l->fork, st) != cudaSuccess) return -2;
+  const int lanes = l ? (world - 1 < kDmaLanes ? world - 1 : kDmaLanes) : 0;
+  for (int i = 0; i < lanes; ++i)
+    if (cudaStreamWaitEvent(l->s[i], l->fork, 0) != cudaSuccess) return -2;
   for (int k = 0; k < world; ++k) {
     const int r = (first + k) % world;               // start at a different peer on every rank so the links are used evenly
+    cudaStream_t on = lanes ? l->s[k % lanes] : st;
     cudaError_t e = cudaMemcpyAsync(static_cast<char*>(full) + (long)r * chunk_bytes, reinterpret_cast<const void*>(peer_ptrs[r]), (size_t)chunk_bytes,
-                                    cudaMemcpyDeviceToDevice, st);
+                                    cudaMemcpyDeviceToDevice, on);
     if (e != cudaSuccess) return -2;
   }
+  for (int i = 0; i < lanes; ++i)
+    if (cudaEventRecord(l->join[i], l->s[i]) != cudaSuccess || cudaStreamWaitEvent(st, l->join[i], 0) != cudaSuccess) return -2;
   return 0;
 }

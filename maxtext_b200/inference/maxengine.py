@@ -70,7 +70,7 @@ class MaxEngine:
     c = self.config
     if bool(getattr(c, "checkpoint_is_quantized", False)) and path and os.path.isfile(os.path.join(path, "quantized_params.safetensors")):
       self.load_quantized_params(os.path.join(path, "quantized_params.safetensors"))
-    elif str(getattr(c, "quantization", "") or "") in ("int8", "int4") and str(getattr(c, "save_quantized_params_path", "") or ""):
+    elif str(getattr(c, "quantization", "") or "") in ("int8", "int4", "intmp") and str(getattr(c, "save_quantized_params_path", "") or ""):
       # serving flow of the reference (maxengine.py:576-620): quantise the loaded weights once and write them out
       self.save_quantized_params(c.save_quantized_params_path, 8 if c.quantization == "int8" else 4)
     return self.model.store
@@ -94,29 +94,39 @@ class MaxEngine:
     store = self.model.store
     for name, p in store.params.items():
       if name + "/q" in flat:
-        w = flat[name + "/q"].float() * flat[name + "/scale"].float()[..., None]
+        q, sc = flat[name + "/q"].float(), flat[name + "/scale"].float()
+        if sc.dim() == q.dim():                  # sub-channel scales [..., out, tiles]: one per stretch of the contraction dim
+          sc = sc.repeat_interleave(q.shape[-1] // sc.shape[-1], dim=-1)
+          w = q * sc
+        else:
+          w = q * sc[..., None]
         store.load_full(name, p.pdef.local_slice(w))
     store.sync_compute_from_master()
 
   # ------------------------------------------------------------------ state
   @torch.no_grad()
-  def quantize_params(self, bits: int = 8) -> dict:
+  def quantize_params(self, bits: int = 8, mixed=None) -> dict:
     """Weight-only quantisation for serving (src/maxtext/inference/maxengine/maxengine.py:576 `quantize_params`): every
-    matrix inside the decoder layers is rounded to `bits`-bit integers with one scale per output channel. Returns
-    {name: (int8 values, fp32 scales)} for saving; the engine's own weights are replaced by the de-quantised values, so
-    what it generates afterwards is what a server loading the quantised file generates (it still computes in bf16)."""
+    matrix inside the decoder layers is rounded to `bits`-bit integers with one scale per output channel, or per matrix as a
+    mixed-precision map says (`mixed` = `mixed_precision.load_quant_map(path)`; `quantization=intmp` loads `quant_cfg_path`).
+    Returns {name: (int8 values, fp32 scales)} for saving; the engine's own weights are replaced by the de-quantised values,
+    so what it generates afterwards is what a server loading the quantised file generates (it still computes in bf16)."""
+    from . import mixed_precision as mp
     store = self.model.store
-    qmax = float(2 ** (int(bits) - 1) - 1)
+    c = self.config
+    if mixed is None and str(getattr(c, "quantization", "") or "") == "intmp":
+      if not str(getattr(c, "quant_cfg_path", "") or ""):
+        raise ValueError("quantization=intmp needs quant_cfg_path")
+      mixed = mp.load_quant_map(c.quant_cfg_path)
     packed = {}
     for name, p in store.params.items():
       d = p.pdef
       if d.layer is None or d.kind not in ("linear", "expert_linear") or len(d.shape) < 2:
         continue
-      w = store.full_master(p).float()
-      scale = w.abs().amax(dim=-1, keepdim=True).clamp_(min=1e-12) / qmax
-      q = torch.clamp(torch.round(w / scale), -qmax, qmax)
-      packed[name] = (q.to(torch.int8), scale.squeeze(-1))
-      store.load_full(name, d.local_slice(q * scale))
+      cfg = mp.settings_for(name, mixed) if mixed is not None else {"w_bits": int(bits), "tile_size": -1, "w_scale": 1.0}
+      q, scale, deq = mp.quantize_weight(store.full_master(p).float(), cfg)
+      packed[name] = (q, scale)
+      store.load_full(name, d.local_slice(deq))
     store.sync_compute_from_master()
     return packed
 

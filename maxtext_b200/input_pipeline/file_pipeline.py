@@ -1,8 +1,8 @@
 """File-backed input pipeline for dataset_type in {hf, grain, tfds, c4_mlperf, olmo_grain}.
 
 The reference wires Grain / HF datasets / TFDS readers (src/maxtext/input_pipeline/{grain,hf,tfds}_data_processing.py).
-Here one reader covers local files of the common formats (jsonl, txt, parquet, and .npy token arrays for the OLMo
-style): read -> tokenize -> (optionally) pack -> shift -> batch, sharded across data-parallel ranks by example index,
+Here one reader covers local files of the common formats (jsonl, txt, parquet, Arrow IPC, TFRecord shards of
+tf.train.Example, and .npy token arrays for the OLMo style): read -> tokenize -> (optionally) pack -> shift -> batch, sharded across data-parallel ranks by example index,
 with an iterator state (epoch, position) that checkpoints save and restore for sample-exact resume.
 File selection: `hf_train_files` / `grain_train_files` / `dataset_path` (glob patterns, comma separated)."""
 from __future__ import annotations
@@ -45,6 +45,18 @@ def _read_examples(path: str, column: str):
   elif path.endswith(".npy"):
     arr = np.load(path, mmap_mode="r")
     yield {"__tokens__": arr}
+  elif ".tfrecord" in os.path.basename(path):
+    # TFDS shards (c4-train.tfrecord-00000-of-01024): tf.train.Example records; token id features pass through as arrays
+    from .record_formats import read_tfrecord_examples
+    for row in read_tfrecord_examples(path, (column,)):
+      v = row.get(column)
+      if isinstance(v, np.ndarray):
+        yield {"__tokens__": v}
+      else:
+        yield row
+  elif path.endswith(".arrow"):
+    from .record_formats import read_arrow
+    yield from read_arrow(path)
   else:
     with open(path, "r", encoding="utf-8", errors="replace") as fh:
       for line in fh:

@@ -36,7 +36,7 @@ def gemm_fallbacks() -> int:
 
 
 def _gemm_supported(M, N, K, a, b):
-  return a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and M % 8 == 0 and K >= 16
+  return a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and K >= 16
 
 
 def mm(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out: torch.Tensor | None = None,

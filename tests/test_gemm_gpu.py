@@ -49,6 +49,15 @@ def test_gemm_ragged_and_large(M, N, K):
   _run(M, N, K, True, False, torch.float32)
 
 
+@pytest.mark.parametrize("M", [2526, 619, 131])
+def test_gemm_row_count_not_a_multiple_of_eight(M):
+  """Rows are the strided dimension of a non-transposed A and of the output: any count works (per-expert token groups)."""
+  _run(M, 1408, 2048, False, True, torch.bfloat16)
+  _run(M, 512, 256, False, False, torch.bfloat16)
+  if M >= 512:
+    _run(M, 512, 256, False, True, torch.bfloat16, pair=True)
+
+
 def test_gemm_accumulate_fp32():
   _run(640, 512, 384, True, False, torch.float32, accumulate=True)
   _run(384, 1024, 256, False, True, torch.float32, accumulate=True)

