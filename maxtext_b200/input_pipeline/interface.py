@@ -16,7 +16,10 @@ def _create(config, data_rank: int = 0, data_world: int = 1, split: str = "train
     return SyntheticDataIterator(config, data_rank, data_world)
   if t in ("hf", "grain", "tfds", "c4_mlperf", "olmo_grain"):
     from .file_pipeline import create_file_iterator
-    return create_file_iterator(config, data_rank, data_world, split)
+    it = create_file_iterator(config, data_rank, data_world, split)
+    depth = int(config.grain_worker_count if split == "train" else config.grain_worker_count_eval) * \
+        int(config.grain_per_worker_buffer_size if split == "train" else config.grain_per_worker_buffer_size_eval)
+    return PrefetchIterator(it, depth) if depth > 0 else it
   if t == "tokens":
     # pre-tokenized int32 streams (.bin / .npy), packed and prefetched by the native loader (csrc/host/data_loader.cpp)
     from .file_pipeline import _expand
@@ -31,6 +34,86 @@ def _create(config, data_rank: int = 0, data_world: int = 1, split: str = "train
     eos = getattr(build_tokenizer(config), "eos_id", None)
     return NativeTokenIterator(files, int(config.max_target_length), gb // data_world, int(eos if eos is not None else 1), data_rank, data_world)
   raise ValueError(f"unknown dataset_type {t}")
+
+
+class PrefetchIterator:
+  """Reads, tokenizes and packs batches on a background thread, `depth` batches ahead of the training loop (the role of Grain's
+  worker processes and per-worker buffers, src/maxtext/input_pipeline/grain_data_processing.py: `grain_worker_count` x
+  `grain_per_worker_buffer_size` batches in flight). Every queued batch carries the reader state taken right after it was
+  produced, so `state()` describes the last batch that was DELIVERED, whatever the thread has read ahead; `load_state`
+  stops the thread, repositions the reader and starts over."""
+
+  def __init__(self, inner, depth: int):
+    import queue
+    import threading
+    self.inner, self.depth = inner, max(1, int(depth))
+    self._queue_mod, self._threading = queue, threading
+    self._state = inner.state()
+    self._start()
+
+  def _start(self):
+    self._q = self._queue_mod.Queue(maxsize=self.depth)
+    self._stop = self._threading.Event()
+    self._thread = self._threading.Thread(target=self._work, args=(self._q, self._stop), daemon=True)
+    self._thread.start()
+
+  def _work(self, q, stop):
+    def put(item):
+      while not stop.is_set():
+        try:
+          q.put(item, timeout=0.1)
+          return True
+        except self._queue_mod.Full:
+          continue
+      return False
+    try:
+      while not stop.is_set():
+        try:
+          batch = next(self.inner)
+        except StopIteration:
+          put(("end", None, None))
+          return
+        if not put(("batch", batch, self.inner.state())):
+          return
+    except BaseException as e:  # pylint: disable=broad-except
+      put(("error", e, None))
+
+  def __iter__(self):
+    return self
+
+  def __next__(self):
+    kind, payload, st = self._q.get()
+    if kind == "end":
+      self._q.put(("end", None, None))         # stay exhausted
+      raise StopIteration
+    if kind == "error":
+      raise payload
+    self._state = st
+    return payload
+
+  def state(self):
+    return self._state
+
+  def _halt(self):
+    self._stop.set()
+    while self._thread.is_alive():
+      try:
+        self._q.get_nowait()
+      except self._queue_mod.Empty:
+        pass
+      self._thread.join(timeout=0.05)
+
+  def load_state(self, st):
+    self._halt()
+    self.inner.load_state(st)
+    self._state = self.inner.state()
+    self._start()
+
+  def close(self):
+    self._halt()
+
+  def __getattr__(self, name):
+    return getattr(self.inner, name)
 
 
 class RampupIterator:

@@ -15,6 +15,7 @@ peers reached it, with a time limit after which the kernel records a status code
 from __future__ import annotations
 
 import os
+import weakref
 
 import torch
 import torch.distributed as dist
@@ -52,6 +53,19 @@ class SymmTensor:
     return self.table + elem_offset * self.tensor.element_size()
 
 
+_LIVE: "weakref.WeakSet" = weakref.WeakSet()
+
+
+def verify_all_canaries() -> int:
+  """Checks the guard pages of every live group (no-op unless MAXTEXT_B200_CANARIES=1); returns how many buffers were checked."""
+  n = 0
+  for g in list(_LIVE):
+    if g.canaries:
+      g.verify_canaries()
+      n += len(g._guards)
+  return n
+
+
 class SymmGroup:
   N_SLOTS = 16
 
@@ -66,12 +80,21 @@ class SymmGroup:
     # tests use a few seconds so that a rank that lost its peer leaves on its own instead of being killed)
     self.wait_limit_ms = float(wait_limit_ms if wait_limit_ms is not None else os.environ.get("MAXTEXT_B200_WAIT_LIMIT_MS", 20000.0))
     self._handles = []
+    # MAXTEXT_B200_CANARIES=1 (tests): every allocation is framed by two guard pages holding a fixed pattern; `check()` verifies
+    # them, so a kernel (this rank's or a peer's) that wrote outside a symmetric buffer is caught at the next check
+    self.canaries = os.environ.get("MAXTEXT_B200_CANARIES") == "1"
+    self._guards: list[tuple[torch.Tensor, torch.Tensor]] = []
     self.flags = self.alloc(self.N_SLOTS * self.world, torch.int32, zero=True)
     self.epochs = [0] * self.N_SLOTS
+    _LIVE.add(self)
     dist.barrier(group=self.group)
 
+  GUARD_BYTES = 4096
+  GUARD_WORD = 0x5AC3A55A
+
   def alloc(self, numel: int, dtype: torch.dtype, zero: bool = False) -> SymmTensor:
-    t = self._sm.empty(int(numel), dtype=dtype, device=self.device)
+    guard = self.GUARD_BYTES // torch.empty((), dtype=dtype).element_size() if self.canaries else 0
+    t = self._sm.empty(int(numel) + 2 * guard, dtype=dtype, device=self.device)
     if zero:
       t.zero_()
       torch.cuda.synchronize(self.device)
@@ -89,7 +112,24 @@ class SymmGroup:
         mc += off
     except Exception:  # pylint: disable=broad-except
       mc = 0
+    if guard:
+      lo, hi = t[:guard].view(torch.int32), t[guard + int(numel):].view(torch.int32)
+      lo.fill_(self.GUARD_WORD)
+      hi.fill_(self.GUARD_WORD)
+      torch.cuda.synchronize(self.device)
+      self._guards.append((lo, hi))
+      ptrs = [p + self.GUARD_BYTES for p in ptrs]
+      mc = mc + self.GUARD_BYTES if mc else 0
+      t = t[guard:guard + int(numel)]
     return SymmTensor(t, ptrs, mc)
+
+  def verify_canaries(self):
+    """Raises if any guard word around a symmetric buffer of this rank changed."""
+    for i, (lo, hi) in enumerate(self._guards):
+      for side, g in (("below", lo), ("above", hi)):
+        if not bool((g == self.GUARD_WORD).all()):
+          bad = int((g != self.GUARD_WORD).nonzero()[0])
+          raise RuntimeError(f"rank {self.rank}: symmetric buffer #{i} was overrun ({side} it, guard word {bad} changed)")
 
   # ---- epoch flags (stream ordered)
   def signal(self, slot: int) -> int:
@@ -109,3 +149,5 @@ class SymmGroup:
     st = backend.ext().kernel_status(True)
     if st != 0:
       raise CommTimeoutError(f"a device-side wait timed out (status {st}) on rank {self.rank}")
+    if self.canaries:
+      self.verify_canaries()

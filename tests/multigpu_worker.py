@@ -60,6 +60,15 @@ def kernels(rank, world, dev):
   sg.check()
 
 
+def _canaries(fused):
+  """Guard pages around every symmetric buffer must be intact after the steps (the test driver switches them on)."""
+  from maxtext_b200.parallel import symm
+  torch.cuda.synchronize()
+  n = symm.verify_all_canaries()
+  if fused and os.environ.get("MAXTEXT_B200_CANARIES") == "1":
+    assert n > 0, "the fused path allocated no symmetric buffers"
+
+
 def train_moe_ep(rank, world, dev, fused):
   """Mixtral-style model with its experts spread over the `expert` axis: peer-memory dispatch vs the NCCL all-to-all path."""
   from maxtext_b200.config import pyconfig
@@ -80,6 +89,7 @@ def train_moe_ep(rank, world, dev, fused):
   for _ in range(3):
     m = eng.train_step(next(it))
     out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  _canaries(fused)
   return out
 
 
@@ -105,6 +115,7 @@ def train_tp(rank, world, dev, fused):
   if fused:
     from maxtext_b200.parallel import tp_fused
     assert tp_fused._RT and all(rt.use > 0 for rt in tp_fused._RT.values()), "fused TP path did not run"
+  _canaries(fused)
   return out
 
 
@@ -153,6 +164,7 @@ def train(rank, world, dev, fused):
   for _ in range(3):
     m = eng.train_step(next(it))
     out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  _canaries(fused)
   return out
 
 

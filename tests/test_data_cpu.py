@@ -255,3 +255,65 @@ def test_rampup_resume_keeps_the_partially_used_buffer(tmp_path):
     it2.load_state(st)
     got = _drain(it2, 12 - stop)
     assert all(a.shape == b.shape and np.array_equal(a, b) for a, b in zip(got, ref[stop:])), stop
+
+
+def test_tfrecord_example_and_arrow_readers(tmp_path):
+  """TFRecord framing with checksums, tf.train.Example wire format and Arrow IPC files, without TensorFlow."""
+  import numpy as np
+  import pyarrow as pa
+  import pytest
+  from maxtext_b200.input_pipeline import record_formats as rf
+  assert rf.crc32c(b"123456789") == 0xE3069283                        # the check value of CRC-32C
+  rows = [{"text": "hello world", "ids": [1, 2, 3, -4, 2 ** 40], "score": [0.5, 1.5]}, {"text": "zweite Zeile äöü", "ids": [7], "score": [2.0]}]
+  path = str(tmp_path / "c4-train.tfrecord-00000-of-00001")
+  rf.write_tfrecord(path, [rf.build_example(r) for r in rows])
+  back = list(rf.read_tfrecord_examples(path))
+  assert [b["text"] for b in back] == [r["text"] for r in rows]
+  assert back[0]["ids"].tolist() == rows[0]["ids"] and np.allclose(back[0]["score"], rows[0]["score"])
+  assert len(list(rf.read_tfrecord(path, verify_payload=True))) == 2
+  raw = bytearray(open(path, "rb").read())
+  raw[3] ^= 0xFF                                                       # damage the first length field
+  bad = str(tmp_path / "bad.tfrecord")
+  open(bad, "wb").write(bytes(raw))
+  with pytest.raises(IOError):
+    list(rf.read_tfrecord(bad))
+  raw = bytearray(open(path, "rb").read())
+  raw[20] ^= 0x01                                                      # damage a payload byte
+  open(bad, "wb").write(bytes(raw))
+  with pytest.raises(IOError):
+    list(rf.read_tfrecord(bad, verify_payload=True))
+  table = pa.table({"text": ["a b c", "d e"], "n": [1, 2]})
+  for kind in ("file", "stream"):
+    ap = str(tmp_path / f"data_{kind}.arrow")
+    with pa.OSFile(ap, "wb") as sink:
+      w = (pa.ipc.new_file if kind == "file" else pa.ipc.new_stream)(sink, table.schema)
+      w.write_table(table)
+      w.close()
+    assert list(rf.read_arrow(ap)) == [{"text": "a b c", "n": 1}, {"text": "d e", "n": 2}]
+
+
+def test_file_pipeline_reads_tfrecord_shards_and_prefetch_keeps_resume_exact(tmp_path):
+  import torch
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline import record_formats as rf
+  from maxtext_b200.input_pipeline.interface import PrefetchIterator, create_data_iterator
+  texts = [f"record number {i} " + "tok " * (3 + i % 7) for i in range(120)]
+  for sh in range(2):
+    rf.write_tfrecord(str(tmp_path / f"c4-train.tfrecord-0000{sh}-of-00002"), [rf.build_example({"text": t}) for t in texts[sh::2]])
+  base = ["dataset_type=tfds", f"dataset_path={tmp_path}/c4-train.tfrecord-*", "tokenizer_type=byte", "vocab_size=260", "max_target_length=32",
+          "per_device_batch_size=2", "packing=true", "num_epoch=1"]
+  plain = create_data_iterator(tiny_config("llama3-8b", base + ["grain_worker_count=0"]))
+  assert not isinstance(plain, PrefetchIterator)
+  want = [b["inputs"].clone() for b in plain]
+  assert len(want) > 6
+  it = create_data_iterator(tiny_config("llama3-8b", base + ["grain_worker_count=2", "grain_per_worker_buffer_size=2"]))
+  assert isinstance(it, PrefetchIterator)
+  got = [next(it)["inputs"] for _ in range(3)]
+  st = it.state()                                                      # the thread has read further ahead than three batches
+  got += [b["inputs"] for b in it]
+  assert len(got) == len(want) and all(torch.equal(a, b) for a, b in zip(got, want))
+  it2 = create_data_iterator(tiny_config("llama3-8b", base + ["grain_worker_count=2", "grain_per_worker_buffer_size=2"]))
+  it2.load_state(st)
+  rest = [b["inputs"] for b in it2]
+  assert len(rest) == len(want) - 3 and all(torch.equal(a, b) for a, b in zip(rest, want[3:]))
+  it.close(), it2.close()

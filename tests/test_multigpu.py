@@ -23,7 +23,7 @@ def _run(mode, tmp_path, world=2):
   procs = []
   for r in range(world):
     env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-               MAXTEXT_B200_QUIET="1", MAXTEXT_B200_WAIT_LIMIT_MS="5000")
+               MAXTEXT_B200_QUIET="1", MAXTEXT_B200_WAIT_LIMIT_MS="5000", MAXTEXT_B200_CANARIES="1")
     procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multigpu_worker.py"), mode, res], cwd=ROOT, env=env,
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
   outs = []
