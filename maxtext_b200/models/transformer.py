@@ -66,9 +66,16 @@ class LayerPlan:
 
 
 class DecoderBlock:
-  def __init__(self, b: L.Builder, config, plan: BlockPlan, rope_tables: dict):
+  def __init__(self, b: L.Builder, config, plan: BlockPlan, rope_tables: dict, layer_index: int | None = None, hash_mapping=None):
     c, s = config, plan.suffix
     self.plan = plan
+    self.engram = None
+    if hash_mapping is not None and layer_index in hash_mapping.layer_ids:
+      # src/maxtext/models/deepseek.py:105-137, 365-367: n-gram memory added to the layer input, before attention
+      from ..layers.engram import Engram
+      self.engram_norm = L.Norm(b, "engram_layer_norm", c.emb_dim, c.normalization_layer_epsilon)
+      self.engram = Engram(b, c, hash_mapping.vocab_sizes(layer_index))
+      self.engram_layer, self.hash_mapping = layer_index, hash_mapping
     if plan.prefix:
       b = b.sub(plan.prefix)
     eps = c.normalization_layer_epsilon
@@ -110,6 +117,9 @@ class DecoderBlock:
             v_.pdef.tp_partial = True
 
   def __call__(self, x, ctx: LayerCtx):
+    if self.engram is not None and ctx.tokens is not None:
+      ids = self.hash_mapping.hashes(self.hash_mapping.ct(ctx.tokens), self.engram_layer)
+      x = x + self.engram(self.engram_norm(x), ids)
     if self.mhc_attn is not None:               # x [B, S, k, D]: the residual adds live inside the hyper-connections
       x = self.mhc_attn(self.n1, lambda h: self.attn(h, ctx), x)
       return self.mhc_mlp(self.n2, lambda h: self.mlp(h, ctx), x)
@@ -126,11 +136,11 @@ class DecoderBlock:
 class DecoderLayer:
   """One schedulable unit: all parameters gathered / reduced together."""
 
-  def __init__(self, config, index: int, stack_index: int, plan: LayerPlan, rope_tables, par):
+  def __init__(self, config, index: int, stack_index: int, plan: LayerPlan, rope_tables, par, hash_mapping=None):
     self.index, self.plan = index, plan
     self.unit = f"layer_{index}"
     b = L.Builder(config, self.unit, stack_index, plan.stack, **par)
-    self.blocks = [DecoderBlock(b, config, bp, rope_tables) for bp in plan.blocks]
+    self.blocks = [DecoderBlock(b, config, bp, rope_tables, layer_index=index, hash_mapping=hash_mapping) for bp in plan.blocks]
     self.params = b.params
 
   def __call__(self, x, ctx: LayerCtx):
@@ -227,6 +237,13 @@ class Transformer:
     self.embed_params = eb.params if self.has_embed else []
     # ---- layers
     self.mhc_k = int(getattr(c, "mhc_expansion_rate", 1) or 1)
+    self.hash_mapping = None
+    if list(getattr(c, "engram_layers", []) or []):
+      from ..input_pipeline.tokenizer import build_tokenizer
+      from ..layers.engram import NgramHashMapping
+      tok = build_tokenizer(c)
+      self.hash_mapping = NgramHashMapping(c.engram_vocab_bases, c.engram_max_ngram_size, c.engram_num_heads, c.engram_layers, tok,
+                                           int(getattr(tok, "pad_id", 0) or 0), int(c.engram_seed))
     self.layers: list[DecoderLayer] = []
     counters: dict[str, int] = {}
     for i, plan in enumerate(families.layer_plans(c)):
@@ -234,7 +251,7 @@ class Transformer:
       counters[plan.stack] = si + 1
       if stage is not None and (i // max(1, int(c.num_layers_per_pipeline_stage))) % stage[1] != stage[0]:
         continue
-      self.layers.append(DecoderLayer(c, i, si, plan, self.rope_tables, self.par))
+      self.layers.append(DecoderLayer(c, i, si, plan, self.rope_tables, self.par, hash_mapping=self.hash_mapping))
     self.stack_sizes = counters
     # ---- multi-token prediction unit (training only; the last stage owns it)
     self.mtp_layers: list[MTPLayer] = []
