@@ -50,7 +50,7 @@ struct Params {
 
 template <int DUMMY = 0>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
             const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -355,12 +355,12 @@ int mt_gemm_fp8_block(const void* aq, const void* bq, void* c, int M, int N, int
   p.experts = experts; p.x_offs = x_offs; p.blk_expert = blk_expert; p.status = status;
   static bool cfg = false;
   if (!cfg) {
-    if (cudaFuncSetAttribute(gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(gemm_fp8_block_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
     cfg = true;
   }
   const int tiles = (M / BM + (M % BM != 0)) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, mc, p);
+  gemm_fp8_block_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, mc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
