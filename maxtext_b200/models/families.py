@@ -79,6 +79,20 @@ def layer_plans(c) -> list[LayerPlan]:
                         window=c.sliding_window_size if (j % 4) != 3 else 0, qk_norm=c.use_qk_norm, query_scalar=c.head_dim ** -0.5,
                         global_qk_norm=True, attn_bias=c.attention_bias) for j in range(cyc)]
     return [LayerPlan("layers", blocks) for _ in range(n // cyc)]
+  if blk == "envy":
+    # src/maxtext/models/envy.py: cycles of inhomogeneous_layer_cycle_interval layers (sub-trees layers_0 ..) form one scanned
+    # block; every interleave_moe_layer_step-th layer of a cycle has a routed MoE (MoeBlock_0), the others a dense MLP; the
+    # query is scaled by head_dim^-1/2 at run time; optional q/k norms and a norm on the feed-forward output
+    cyc = max(1, int(c.inhomogeneous_layer_cycle_interval))
+    assert n % cyc == 0, "envy layers must be a multiple of inhomogeneous_layer_cycle_interval"
+    step = max(1, int(c.interleave_moe_layer_step))
+    blocks = []
+    for j in range(cyc):
+      is_moe = c.num_experts > 1 and (j + 1) % step == 0
+      blocks.append(BlockPlan(prefix=f"layers_{j}", query_scalar=c.head_dim ** -0.5, qk_norm=bool(c.use_qk_norm),
+                              post_mlp_norm="post_ffw_norm" if c.use_post_ffw_norm else None,
+                              mlp="moe" if is_moe else "dense", mlp_name="MoeBlock_0" if is_moe else "mlp"))
+    return [LayerPlan("layers", blocks) for _ in range(n // cyc)]
   if blk == "llama4":
     # src/maxtext/models/llama4.py:267-420: every nope_layer_interval-th layer has no RoPE, global attention and the
     # temperature-tuned query; the others use RoPE, chunked attention and scale-free q/k normalisation; MoE layers
@@ -161,4 +175,4 @@ def layer_plans(c) -> list[LayerPlan]:
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, envy, simple)")

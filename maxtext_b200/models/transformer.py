@@ -152,6 +152,11 @@ class DecoderLayer:
       x = blk(x, ctx)
     ctx.name_prefix = ""
     ctx.cache = caches
+    ds = ctx.deepstack
+    if ds is not None and self.index < len(ds[1]) and x.shape[1] == ds[0].shape[1]:
+      # Qwen3-VL deepstack: intermediate vision features join the hidden states of the image positions after the first layers
+      from ..multimodal.utils import merge_mm_embeddings
+      x = x + merge_mm_embeddings(torch.zeros_like(x), ds[1][self.index], ds[0])
     return x
 
 
@@ -273,13 +278,14 @@ class Transformer:
                                                                    ("embed_vocab", "vocab"))
     self.head_params = hb.params if self.has_head else []
     # multimodal: the vision tower is a unit of its own; it is frozen unless freeze_vision_encoder_params is off
-    self.vision, self.vision_params = None, []
+    self.vision, self.vision_params, self._deepstack = None, [], None
     if bool(getattr(c, "use_multimodal", False)) and self.has_embed:
       kind = getattr(c, "vision_encoder_block", "") or c.decoder_block
-      if kind not in ("gemma3", "llama4"):
-        raise NotImplementedError("use_multimodal is implemented for the Gemma-3 and Llama-4 vision towers")
-      from .vision import Gemma3Vision, Llama4Vision
-      self.vision = (Gemma3Vision if kind == "gemma3" else Llama4Vision)(c, self.par)
+      qwen_vl = kind in ("qwen3", "qwen3_moe", "qwen3_5", "qwen3_next", "qwen3_vl", "qwen3_omni")
+      if kind not in ("gemma3", "llama4") and not qwen_vl:
+        raise NotImplementedError("use_multimodal is implemented for the Gemma-3, Llama-4 and Qwen3-VL / Omni vision towers")
+      from .vision import Gemma3Vision, Llama4Vision, Qwen3VLVision
+      self.vision = (Gemma3Vision if kind == "gemma3" else Llama4Vision if kind == "llama4" else Qwen3VLVision)(c, self.par)
       self.vision_params = self.vision.params
       if bool(getattr(c, "freeze_vision_encoder_params", True)):
         for p in self.vision_params:
@@ -339,7 +345,10 @@ class Transformer:
   def encode_images(self, images, image_mask):
     """images [B, N, 3, H, W] -> (soft tokens [B, N*K, D], mask [B, S]) as `embed(..., mm=...)` takes them."""
     soft = self.vision(images.to(self.embedding.data.device))
-    return soft.reshape(soft.shape[0], -1, soft.shape[-1]), image_mask.to(soft.device).bool()
+    mask = image_mask.to(soft.device).bool()
+    deep = getattr(self.vision, "deepstack", None)
+    self._deepstack = (mask, [d.reshape(d.shape[0], -1, d.shape[-1]) for d in deep]) if deep else None
+    return soft.reshape(soft.shape[0], -1, soft.shape[-1]), mask
 
   def embed(self, tokens, positions, mm=None):
     c = self.config
@@ -388,6 +397,7 @@ class Transformer:
     if images is not None:
       from ..multimodal.utils import bidirectional_block_mask
       mm = self.encode_images(images, image_mask)
+      ctx.deepstack = self._deepstack
       if self.vision.__class__.__name__ == "Gemma3Vision":      # Llama-4 keeps plain causal attention over image tokens
         ctx.bidir = bidirectional_block_mask(mm[1])
     x = self.embed(tokens, positions, mm)

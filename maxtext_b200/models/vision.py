@@ -225,3 +225,159 @@ class Llama4Vision:
     x = tF.gelu(F.linear(x, self.fc2).float()).to(dt)
     x = F.linear(x, self.proj)
     return x.view(B, N, x.shape[1], -1)
+
+
+# =============================================================================================== Qwen3-VL / Qwen3-Omni
+class _QwenMerger:
+  """Patch merger (src/maxtext/models/qwen3.py:1672-1786): groups of merge^2 neighbouring patches are concatenated, LayerNorm
+  (before or after the concatenation), Linear -> GELU -> Linear to the language model's width."""
+
+  def __init__(self, b: L.Builder, c, name: str, post_shuffle_norm: bool, eps: float):
+    d, m = c.hidden_size_for_vit, c.spatial_merge_size_for_vit ** 2
+    self.m, self.d, self.post = m, d, post_shuffle_norm
+    mb = b.sub(name)
+    self.ln = L.Norm(mb, "ln_q", d * m if post_shuffle_norm else d, eps, kind="layernorm")
+    self.w0 = mb.sub("mlp_0").linear("kernel", (d * m,), (d * m,), ("embed", "mlp"))
+    self.b0 = mb.sub("mlp_0").vector("bias", d * m, ("mlp",), init="zeros")
+    self.w2 = mb.sub("mlp_2").linear("kernel", (d * m,), (c.out_hidden_size_for_vit,), ("mlp", "embed"))
+    self.b2 = mb.sub("mlp_2").vector("bias", c.out_hidden_size_for_vit, ("embed",), init="zeros")
+
+  def __call__(self, x):
+    """x [M, S, d] in merge order (the merge^2 patches of a block are consecutive) -> [M, S / merge^2, out]."""
+    M, S, d = x.shape
+    if self.post:
+      x = self.ln(x.reshape(M, S // self.m, self.m * d))
+    else:
+      x = self.ln(x).reshape(M, S // self.m, self.m * d)
+    y = tF.gelu(F.linear(x, self.w0, bias=self.b0).float()).to(x.dtype)
+    return F.linear(y, self.w2, bias=self.b2)
+
+
+class _QwenVisionBlock:
+  def __init__(self, b: L.Builder, c, i: int, eps: float):
+    d, h = c.hidden_size_for_vit, c.num_attention_heads_for_vit
+    self.h, self.dh = h, d // h
+    bb = b.sub(f"blocks_{i}")
+    self.ln1, self.ln2 = L.Norm(bb, "ln1", d, eps, kind="layernorm"), L.Norm(bb, "ln2", d, eps, kind="layernorm")
+    ab = bb.sub("attn", "attn")
+    mk = lambda n: ab.sub(n).linear("kernel", (d,), (h, self.dh), ("embed", "heads", "kv"))  # noqa: E731
+    self.q, self.k, self.v = mk("query"), mk("key"), mk("value")
+    self.bq, self.bk, self.bv = (ab.sub(n).vector("bias", d, ("heads",), init="zeros") for n in ("query", "key", "value"))
+    self.o = ab.sub("out").linear("kernel", (h, self.dh), (d,), ("heads", "kv", "embed"))
+    self.bo = ab.sub("out").vector("bias", d, ("embed",), init="zeros")
+    f = c.intermediate_size_for_vit
+    self.w1 = bb.sub("mlp").linear("kernel", (d,), (f,), ("embed", "mlp"))
+    self.b1 = bb.sub("mlp").vector("bias", f, ("mlp",), init="zeros")
+    self.w2 = bb.sub("mlp_out").linear("kernel", (f,), (d,), ("mlp", "embed"))
+    self.b2 = bb.sub("mlp_out").vector("bias", d, ("embed",), init="zeros")
+
+  def __call__(self, x, cos, sin):
+    M, S, _ = x.shape
+    y = self.ln1(x)
+    q = F.linear(y, self.q, bias=self.bq).view(M, S, self.h, self.dh)
+    k = F.linear(y, self.k, bias=self.bk).view(M, S, self.h, self.dh)
+    v = F.linear(y, self.v, bias=self.bv).view(M, S, self.h, self.dh)
+
+    def rot(t):                                     # rotate-half with the (row, column) angle table
+      tf = t.float()
+      half = tf.shape[-1] // 2
+      r = torch.cat([-tf[..., half:], tf[..., :half]], dim=-1)
+      return (tf * cos + r * sin).to(t.dtype)
+    a = ref.attention(rot(q), rot(k), v, None, 1.0 / math.sqrt(self.dh)).to(x.dtype)      # bidirectional within one image
+    x = x + F.linear(a.reshape(M, S, -1), self.o, bias=self.bo)
+    y = F.linear(self.ln2(x), self.w1, bias=self.b1)
+    y = tF.gelu(y.float(), approximate="tanh").to(x.dtype)
+    return x + F.linear(y, self.w2, bias=self.b2)
+
+
+class Qwen3VLVision:
+  """Vision tower of Qwen3-VL / Qwen3-Omni (src/maxtext/models/qwen3.py:1672-2256, qwen3_vl_vision.py, qwen3_5_vision.py).
+
+  A frame pair [C, 2, H, W] is cut into patch_size x patch_size x temporal_patch_size patches (one linear map each, the
+  reference's 3-D convolution); a learned position grid of sqrt(num_position_embeddings)^2 entries is bilinearly interpolated
+  to the patch grid; blocks are pre-LayerNorm encoders with a 2-D rotary embedding (row angles on the first half of each
+  rotary half, column angles on the second); tokens are kept in MERGE ORDER (the merge x merge patches that the merger will
+  fuse are consecutive). The exit merger gives (H/P/merge) x (W/P/merge) soft tokens per image; the hidden states after the
+  blocks listed in `deepstack_visual_indexes_for_vit` go through mergers of their own and are added to the decoder's hidden
+  states at the image positions after its first layers ("deepstack").
+
+  `__call__(images [B, N, 3, H, W]) -> [B, N, K, out_hidden]`; the deepstack features of the last call are in `.deepstack`
+  (list of [B, N, K, out_hidden])."""
+
+  def __init__(self, config, par: dict):
+    c = self.c = config
+    b = L.Builder(c, "vision", None, None, **par)
+    vb = b.sub("vision_encoder")
+    self.P, self.TP, self.C, self.d = c.patch_size_for_vit, c.temporal_patch_size_for_vit, c.num_channels_for_vit, c.hidden_size_for_vit
+    self.merge = c.spatial_merge_size_for_vit
+    eps = 1e-6
+    # reference kernel layout of the 3-D patch convolution: [T, P, P, C, d]
+    self.patch = vb.sub("patch_embed", "proj").linear("kernel", (self.TP, self.P, self.P, self.C), (self.d,), (None, None, None, None, "embed"))
+    self.patch_bias = vb.sub("patch_embed", "proj").vector("bias", self.d, ("embed",), init="zeros")
+    self.side = int(math.isqrt(int(c.num_position_embeddings_for_vit)))
+    self.pos = vb.sub("pos_embed_interpolate").table("pos_embed", (self.side * self.side, self.d), (None, "embed"), init="fan_in_normal")
+    self.blocks = [_QwenVisionBlock(vb, c, i, eps) for i in range(c.num_hidden_layers_for_vit)]
+    self.deep_idx = [int(i) for i in (c.deepstack_visual_indexes_for_vit or [])]
+    self.deep_mergers = [_QwenMerger(vb, c, f"merger_{i}", True, eps) for i in range(len(self.deep_idx))]
+    self.merger = _QwenMerger(b.sub("vision_projector"), c, "merger", False, eps)
+    self.params = b.params
+    self.deepstack = []
+
+  # ---- token order and tables
+  def _merge_order(self, gh: int, gw: int, device):
+    """Patch (row, col) of every token, blocks of merge x merge patches consecutive: [gh*gw, 2]."""
+    m = self.merge
+    br, bc = torch.arange(gh // m, device=device), torch.arange(gw // m, device=device)
+    ir, ic = torch.arange(m, device=device), torch.arange(m, device=device)
+    rows = (br[:, None, None, None] * m + ir[None, None, :, None]).expand(gh // m, gw // m, m, m).reshape(-1)
+    cols = (bc[None, :, None, None] * m + ic[None, None, None, :]).expand(gh // m, gw // m, m, m).reshape(-1)
+    return torch.stack([rows, cols], -1)
+
+  def _pos_embed(self, rc, gh: int, gw: int):
+    """Bilinear interpolation of the learned side x side grid at the patch centres (corner aligned), for tokens at `rc`."""
+    s = self.side
+    tab = self.pos.leaf().float()
+    hi = torch.linspace(0, s - 1, gh, device=rc.device)[rc[:, 0]]
+    wi = torch.linspace(0, s - 1, gw, device=rc.device)[rc[:, 1]]
+    h0, w0 = hi.floor().long(), wi.floor().long()
+    h1, w1 = (h0 + 1).clamp(max=s - 1), (w0 + 1).clamp(max=s - 1)
+    dh, dw = (hi - h0)[:, None], (wi - w0)[:, None]
+    return (tab[h0 * s + w0] * (1 - dh) * (1 - dw) + tab[h0 * s + w1] * (1 - dh) * dw +
+            tab[h1 * s + w0] * dh * (1 - dw) + tab[h1 * s + w1] * dh * dw)
+
+  def _rope(self, rc):
+    """cos / sin [S, 1, head_dim]: angles = [row * f | col * f] repeated for the two rotate-half halves."""
+    dh = self.d // self.c.num_attention_heads_for_vit
+    inv = 1.0 / (float(self.c.rope_theta_for_vit) ** (torch.arange(0, dh // 2, 2, device=rc.device, dtype=torch.float32) / (dh // 2)))
+    ang = torch.cat([rc[:, :1].float() * inv, rc[:, 1:].float() * inv], -1)           # [S, dh/2]
+    ang = torch.cat([ang, ang], -1)[:, None]
+    return ang.cos(), ang.sin()
+
+  def patches(self, images: torch.Tensor) -> torch.Tensor:
+    """[M, C, H, W] (one frame, repeated over the temporal patch) -> [M, S, TP*P*P*C] in merge order, features ordered
+    (t, py, px, c) like the reference kernel."""
+    M, C, H, W = images.shape
+    P = self.P
+    gh, gw = H // P, W // P
+    assert H % (P * self.merge) == 0 and W % (P * self.merge) == 0, "image sides must be multiples of patch_size * spatial_merge_size"
+    rc = self._merge_order(gh, gw, images.device)
+    x = images.view(M, C, gh, P, gw, P).permute(0, 2, 4, 3, 5, 1)                     # M, gy, gx, py, px, C
+    x = x[:, rc[:, 0], rc[:, 1]]                                                      # M, S, py, px, C
+    x = x.unsqueeze(2).expand(M, x.shape[1], self.TP, P, P, C)
+    return x.reshape(M, x.shape[1], self.TP * P * P * C), rc, gh, gw
+
+  def __call__(self, images: torch.Tensor) -> torch.Tensor:
+    B, N = images.shape[:2]
+    dt = self.patch.data.dtype
+    x, rc, gh, gw = self.patches(images.reshape(B * N, *images.shape[2:]).to(dt))
+    x = F.linear(x, self.patch, bias=self.patch_bias)
+    x = x + self._pos_embed(rc, gh, gw).to(dt)
+    cos, sin = self._rope(rc)
+    deep = []
+    for i, blk in enumerate(self.blocks):
+      x = blk(x, cos, sin)
+      if i in self.deep_idx:
+        deep.append(self.deep_mergers[self.deep_idx.index(i)](x))
+    out = self.merger(x)
+    self.deepstack = [t.view(B, N, t.shape[1], -1) for t in deep]
+    return out.view(B, N, out.shape[1], -1)
