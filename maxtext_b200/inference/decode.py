@@ -26,11 +26,16 @@ def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -
   mm_kw = {}
   if bool(getattr(config, "use_multimodal", False)) and str(getattr(config, "image_path", "") or ""):
     # one <start_of_image> in the prompt per file of image_path; each grows to 260 positions (256 of them soft tokens)
-    from ..multimodal import processor_gemma3 as pg
     paths = [p for p in str(config.image_path).split(",") if p]
-    if ids.count(pg.BEGIN_IMAGE_TOKEN) < len(paths):
-      ids = ids + [pg.BEGIN_IMAGE_TOKEN] * (len(paths) - ids.count(pg.BEGIN_IMAGE_TOKEN))
-    t_ids, mask, pix = pg.prepare(ids, paths, int(config.image_size_for_vit))
+    if eng.model.vision.__class__.__name__ == "Qwen3VLVision":
+      # <|vision_start|> <|image_pad|> x K <|vision_end|> per image, K from the resized image's patch grid
+      from ..multimodal import processor_qwen3 as pq
+      t_ids, mask, pix = pq.prepare(ids, paths, config)
+    else:
+      from ..multimodal import processor_gemma3 as pg
+      if ids.count(pg.BEGIN_IMAGE_TOKEN) < len(paths):
+        ids = ids + [pg.BEGIN_IMAGE_TOKEN] * (len(paths) - ids.count(pg.BEGIN_IMAGE_TOKEN))
+      t_ids, mask, pix = pg.prepare(ids, paths, int(config.image_size_for_vit))
     ids = t_ids.tolist()
     mm_kw = dict(images=pix, image_mask=torch.nn.functional.pad(mask, (0, max(0, int(config.max_prefill_predict_length) - len(ids)))))
   ids = [i % config.vocab_size for i in ids][: int(config.max_prefill_predict_length)]

@@ -1,0 +1,92 @@
+"""Qwen3-VL / Qwen3-Omni / Qwen3.5 image conventions (src/maxtext/multimodal/processor_qwen3_omni.py:38-340, 720-857).
+
+An image is resized so that both sides are multiples of patch_size * spatial_merge_size, the pixel count stays inside
+[min_pixels, max_pixels] and the aspect ratio is kept as closely as that allows; pixels are scaled to [-1, 1]
+((x - 127.5) / 127.5). In the prompt every image is  <|vision_start|> <|image_pad|> x K <|vision_end|>  with
+K = (H / patch / merge) * (W / patch / merge); the pad positions receive the merged vision tokens. Video and audio inputs of
+the Omni model are not handled here."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from .processor import load_image
+
+TOKENS = {
+    "qwen3.5": dict(vision_start=248053, vision_end=248054, image_pad=248056),
+    "": dict(vision_start=151652, vision_end=151653, image_pad=151655),          # Qwen3-VL and Qwen3-Omni vocabularies
+}
+MAX_RATIO = 200
+
+
+def special_tokens(model_name: str) -> dict:
+  return next(v for k, v in TOKENS.items() if str(model_name or "").startswith(k))
+
+
+def smart_resize(height: int, width: int, factor: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
+  if max(height, width) / min(height, width) > MAX_RATIO:
+    raise ValueError(f"aspect ratio {max(height, width) / min(height, width):.0f} exceeds {MAX_RATIO}")
+  h, w = max(factor, round(height / factor) * factor), max(factor, round(width / factor) * factor)
+  if h * w > max_pixels:
+    beta = math.sqrt(height * width / max_pixels)
+    h, w = max(factor, math.floor(height / beta / factor) * factor), max(factor, math.floor(width / beta / factor) * factor)
+  elif h * w < min_pixels:
+    beta = math.sqrt(min_pixels / (height * width))
+    h, w = math.ceil(height * beta / factor) * factor, math.ceil(width * beta / factor) * factor
+  return h, w
+
+
+def preprocess_image(image, config, size: tuple[int, int] | None = None) -> torch.Tensor:
+  """path or HWC uint8 array -> [3, H, W] float32 in [-1, 1] with H, W multiples of patch * merge."""
+  if isinstance(image, str):
+    image = load_image(image)
+  arr = np.asarray(image)
+  if arr.ndim == 2:
+    arr = np.repeat(arr[:, :, None], 3, 2)
+  factor = int(config.patch_size_for_vit) * int(config.spatial_merge_size_for_vit)
+  h, w = size or smart_resize(arr.shape[0], arr.shape[1], factor, 4 * factor * factor, 16384 * factor * factor)
+  t = torch.as_tensor(arr).float().permute(2, 0, 1)[None]
+  if arr.dtype != np.uint8:
+    t = t * 255.0
+  if t.shape[-2:] != (h, w):
+    t = torch.nn.functional.interpolate(t, size=(h, w), mode="bicubic", antialias=True, align_corners=False).clamp_(0, 255)
+  return ((t - 127.5) / 127.5)[0]
+
+
+def tokens_per_image(h: int, w: int, config) -> int:
+  f = int(config.patch_size_for_vit) * int(config.spatial_merge_size_for_vit)
+  return (h // f) * (w // f)
+
+
+def prepare(tokens: list[int], images, config):
+  """Prompt ids (one <|image_pad|> or <|vision_start|> per image, or none: images are then appended) and raw images ->
+  (ids [S], image_mask [S], pixel values [N, 3, H, W]). All images of one prompt are brought to the size of the first."""
+  tk = special_tokens(getattr(config, "model_name", ""))
+  pix = []
+  for im in images:
+    pix.append(preprocess_image(im, config, size=tuple(pix[0].shape[-2:]) if pix else None))
+  pix = torch.stack(pix)
+  K = tokens_per_image(pix.shape[-2], pix.shape[-1], config)
+  block = [tk["vision_start"]] + [tk["image_pad"]] * K + [tk["vision_end"]]
+  out, used, i = [], 0, 0
+  toks = list(tokens)
+  while i < len(toks):
+    t = toks[i]
+    if t == tk["vision_start"] and used < len(images):
+      out.extend(block)
+      used += 1
+      while i + 1 < len(toks) and toks[i + 1] in (tk["image_pad"], tk["vision_end"]):    # drop the collapsed placeholder run
+        i += 1
+    elif t == tk["image_pad"] and used < len(images):
+      out.extend(block)
+      used += 1
+    else:
+      out.append(t)
+    i += 1
+  for _ in range(len(images) - used):
+    out.extend(block)
+  mask = [t == tk["image_pad"] for t in out]
+  assert sum(mask) == K * len(images)
+  return torch.tensor(out), torch.tensor(mask), pix

@@ -98,3 +98,22 @@ def test_deepstack_features_reach_the_decoder_at_image_positions():
   assert a.shape == (B, S, cfg.vocab_size) and torch.isfinite(a).all()
   assert not torch.allclose(a, b)
   assert torch.allclose(a[:, :3], b[:, :3], atol=1e-5)         # causal: positions before the image are untouched
+
+
+def test_processor_resizes_to_the_patch_grid_and_expands_placeholders():
+  import numpy as np
+  from maxtext_b200.multimodal import processor_qwen3 as pq
+  cfg = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=64"])
+  assert pq.smart_resize(100, 37, 8, 4 * 64, 10 ** 9) == (96, 40)
+  assert pq.smart_resize(1000, 1000, 8, 256, 64 * 64) == (64, 64)          # capped by max_pixels, still a multiple of 8
+  assert pq.smart_resize(3, 5, 8, 4 * 64, 10 ** 9)[0] % 8 == 0
+  img = (np.random.default_rng(0).random((30, 45, 3)) * 255).astype(np.uint8)
+  tk = pq.special_tokens("qwen3-vl-2b")
+  ids, mask, pix = pq.prepare([5, tk["vision_start"], tk["image_pad"], tk["vision_end"], 9], [img], cfg)
+  assert pix.shape == (1, 3, 32, 48) and float(pix.min()) >= -1.0 and float(pix.max()) <= 1.0
+  K = (32 // 8) * (48 // 8)
+  assert int(mask.sum()) == K and ids.tolist()[:2] == [5, tk["vision_start"]] and ids.tolist()[-2:] == [tk["vision_end"], 9]
+  assert len(ids) == 2 + K + 2
+  ids2, mask2, _ = pq.prepare([5, 9], [img, img], cfg)                      # no placeholder in the prompt: images are appended
+  assert int(mask2.sum()) == 2 * K
+  assert pq.special_tokens("qwen3.5-35b-a3b")["image_pad"] == 248056
