@@ -281,10 +281,13 @@ class Attention:
 
   def __init__(self, b: Builder, config, name="self_attention", window: int = 0, rope_inv_ts=None, interleaved=False,
                use_rope=True, qk_norm=False, query_scalar: float | None = None, soft_cap: float = 0.0, bias=False,
-               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0, out_bias=None, global_qk_norm=False, gated=False, qk_norm_offset=0.0):
+               rotary_dim=None, sinks=False, l2_qk_norm=False, temperature_tuning=False, chunk=0, out_bias=None, global_qk_norm=False, gated=False, qk_norm_offset=0.0,
+               head_dim: int | None = None, num_kv_heads: int | None = None, share_kv: bool = False, v_norm: str = ""):
     c = config
     self.config = c
-    self.hq, self.hkv, self.dh, self.d = c.num_query_heads, c.num_kv_heads, c.head_dim, c.emb_dim
+    # gemma4 global layers have their own head width and key/value head count (src/maxtext/models/gemma4.py:186-196)
+    self.hq, self.hkv, self.dh, self.d = c.num_query_heads, int(num_kv_heads or c.num_kv_heads), int(head_dim or c.head_dim), c.emb_dim
+    self.share_kv, self.v_norm = bool(share_kv), str(v_norm or "")
     tp = b.tp_size
     self.hq_l = self.hq // tp
     self.hkv_l = max(1, self.hkv // tp) if self.hkv >= tp else self.hkv
@@ -306,11 +309,13 @@ class Attention:
                                     "fan_in_normal", depth_scale, tp="col")
     self.k = ab.sub("key").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
                                   "fan_in_normal", tp=kv_tp)
-    self.v = ab.sub("value").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
-                                    "fan_in_normal", tp=kv_tp)
+    # share_kv_projections (src/maxtext/layers/attentions.py:289): the value is the (un-normalised, un-rotated) key projection
+    self.v = None if self.share_kv else ab.sub("value").linear("kernel", (self.d,), (self.hkv, self.dh), ("embed", "kv_heads", "kv_head_dim"),
+                                                               "fan_in_normal", tp=kv_tp)
     self.o = ab.sub("out").linear("kernel", (self.hq, self.dh), (self.d,), ("heads", "kv", "embed"), "fan_in_normal",
                                   tp="row")
-    self.qkv = FusedParam([self.q, self.k, self.v]) if (not self.gated and FusedParam.possible([self.q, self.k, self.v])) else None
+    self.qkv = FusedParam([self.q, self.k, self.v]) if (not self.gated and not self.share_kv and FusedParam.possible([self.q, self.k, self.v])) else None
+    self.vn = Norm(ab, "value_norm", self.dh, c.normalization_layer_epsilon, with_scale=(self.v_norm == "scale"), axes=("norm",)) if self.v_norm else None
     self.bq = self.bk = self.bv = None
     if bias:
       self.bq = ab.sub("query").vector("bias", self.hq * self.dh, ("q_heads",), init="zeros", tp=True)
@@ -349,7 +354,7 @@ class Attention:
       return qkv.view(B, S, hq + 2 * hkv, dh), None
     q = ctx.keep("query_proj", F.linear(x, self.q, ctx.reuse("query_proj"), self.bq))
     k = ctx.keep("key_proj", F.linear(x, self.k, ctx.reuse("key_proj"), self.bk))
-    v = ctx.keep("value_proj", F.linear(x, self.v, ctx.reuse("value_proj"), self.bv))
+    v = k if self.share_kv else ctx.keep("value_proj", F.linear(x, self.v, ctx.reuse("value_proj"), self.bv))
     return None, (q.view(B, S, hq, -1), k.view(B, S, hkv, dh), v.view(B, S, hkv, dh))
 
   def __call__(self, x, ctx):
@@ -362,7 +367,7 @@ class Attention:
       B, S, _ = x.shape                      # sequence parallelism: the gathered length
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
     moba = bool(getattr(self.config, "moba", False)) and ctx.cache is None and ctx.cp_size == 1
-    plain = (not self.qk_norm and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and not moba and ctx.cache is None and ctx.cp_size == 1
+    plain = (not self.qk_norm and self.vn is None and not self.share_kv and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and not moba and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
@@ -385,6 +390,8 @@ class Attention:
         k = self.kn(k.reshape(B, S, -1)).view(B, S, self.hkv_l, self.dh)
       elif self.qk_norm:
         q, k = self.qn(q), self.kn(k)
+      if self.vn is not None:
+        v = self.vn(v)
       if self.use_rope:
         q = F.rope(q, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
         k = F.rope(k, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)

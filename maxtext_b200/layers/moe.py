@@ -16,7 +16,7 @@ import torch.distributed as dist
 
 from ..ops import functional as F
 from ..ops import moe_ops
-from .blocks import Builder, FusedParam, MLP, tp_enter, tp_exit
+from .blocks import Builder, FusedParam, MLP, Norm, tp_enter, tp_exit
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -109,13 +109,25 @@ class RoutedMoE:
       self.b0 = mb.table("wi_0_bias", (self.E, f), ("exp", "activation_mlp"), init="zeros")
       self.b1 = mb.table("wi_1_bias", (self.E, f), ("exp", "activation_mlp"), init="zeros")
       self.bo = mb.table("wo_bias", (self.E, d), ("exp", "activation_embed"), init="zeros")
+    # gemma4 (src/maxtext/layers/moe.py:639-645,744-763): combine weights are the soft-max probabilities of the chosen experts,
+    # renormalised, times a learned scale per expert
+    self.per_expert_scale = mb.vector("per_expert_scale", self.E, ("exp",), init="ones") if style == "gemma4" else None
 
   # ---- routing
-  def route(self, x2, B, S, ctx=None):
+  def route(self, x2, B, S, ctx=None, gate_inputs=None):
     c = self.c
-    xg = x2.float() if c.float32_gate_logits else x2
+    src = x2 if gate_inputs is None else gate_inputs
+    xg = src.float() if c.float32_gate_logits else src
     w = self.gate.leaf()
     logits = torch.nn.functional.linear(xg, w.to(xg.dtype))
+    if self.style == "gemma4":
+      probs = torch.softmax(logits.float(), -1)
+      idx = logits.topk(self.k, dim=-1).indices
+      wts = probs.gather(-1, idx)
+      if c.norm_topk_prob:
+        wts = wts / wts.sum(-1, keepdim=True)
+      wts = wts * self.per_expert_scale.leaf().float()[idx]
+      return wts, idx, self._aux(probs, idx, B, S, ctx)
     grouped = self.deepseek and c.n_routing_groups > 0 and c.topk_routing_group > 0
     func = (c.routed_score_func or "softmax") if self.deepseek else "softmax"
     if (moe_ops.router_kernel_ok(logits, self.E, self.k) and not grouped and func in ("softmax", "sigmoid")
@@ -167,9 +179,13 @@ class RoutedMoE:
       onehot_k = torch.nn.functional.one_hot(idx.view(B, S * self.k), self.E)                  # [B, S*k, E]
       rank_in_expert = (onehot_k.cumsum(1) * onehot_k).sum(-1)                                # 1-based arrival order
       wts = wts * (rank_in_expert <= cap).view(B * S, self.k).to(wts.dtype)
+    return wts, idx, self._aux(probs, idx, B, S, ctx)
+
+  def _aux(self, probs, idx, B, S, ctx):
+    c = self.c
     aux = None
     if c.load_balance_loss_weight > 0:
-      onehot = torch.zeros(B * S, self.E, dtype=torch.float32, device=x2.device).scatter_add_(
+      onehot = torch.zeros(B * S, self.E, dtype=torch.float32, device=probs.device).scatter_add_(
           1, idx, torch.ones_like(idx, dtype=torch.float32))
       density = onehot.view(B, S, self.E).mean(1)
       density_prob = probs.view(B, S, self.E).mean(1)
@@ -180,7 +196,7 @@ class RoutedMoE:
         density = _AllReduceMean.apply(density, g, ctx.cp_size)
         density_prob = _AllReduceMean.apply(density_prob, g, ctx.cp_size)
       aux = (density * density_prob).mean() * (self.E ** 2) * c.load_balance_loss_weight
-    return wts, idx, aux
+    return aux
 
   # ---- expert FFN on rows grouped by (local) expert
   def experts_ffn(self, rows, sizes):
@@ -224,8 +240,9 @@ class RoutedMoE:
     red = _ReduceScatterRows.apply(out, ctx.ep_group) if torch.is_grad_enabled() else _ReduceScatterRows.forward(F._Dummy(), out, ctx.ep_group)
     return red
 
-  def __call__(self, x, ctx):
+  def __call__(self, x, ctx, gate_inputs=None):
     if ctx.sp and ctx.tp_size > 1:
+      assert gate_inputs is None, "a separate router input is not implemented under tensor-sequence parallelism"
       # sequence-parallel residual stream: routing needs every token, so the block runs the plain tensor-parallel form on
       # the gathered sequence (which returns complete outputs and complete input gradients on every rank) and keeps its part
       from ..parallel import sequence_parallel as sp
@@ -242,7 +259,7 @@ class RoutedMoE:
       if ctx.tp_size > 1:
         out = tp_exit(out, ctx)
       return out.view(B, S, D)
-    wts, idx, aux = self.route(x2, B, S, ctx)
+    wts, idx, aux = self.route(x2, B, S, ctx, gate_inputs.reshape(B * S, D) if gate_inputs is not None else None)
     if aux is not None:
       ctx.aux_losses.append(("moe_lb_loss", aux))
     if (self.gate_bias is not None and self.deepseek and self.c.routed_bias_update_rate > 0 and ctx.expert_counts is not None
@@ -301,6 +318,31 @@ class RoutedMoE:
     inv[local_order] = torch.arange(local_order.numel(), device=rows.device)
     y = y[inv]
     return _AllToAllRows.apply(y, recv_sizes, send_sizes, ctx.ep_group)
+
+
+class Gemma4MoE:
+  """Feed-forward block of the Gemma-4 MoE models (src/maxtext/models/gemma4.py:57-147): the dense MLP ("shared expert", width
+  mlp_dim) reads the pre-normed input; the routed experts read their own RMS norm of the un-normed residual stream; the router
+  reads a scale-free RMS norm of it times emb_dim^-1/2 times a learned per-channel scale; each branch has its own output norm."""
+
+  def __init__(self, b: Builder, config, name="mlp"):
+    c = config
+    mb = b.sub(name)
+    eps = c.normalization_layer_epsilon
+    self.routed = RoutedMoE(mb.sub("moe_block"), c, "MoeBlock_0", deepseek_style=False, style="gemma4")
+    self.shared = MLP(mb.sub("moe_block"), c, "shared_experts", hidden=max(1, int(c.shared_experts)) * c.mlp_dim)
+    self.router_scale = mb.vector("pre_forward_scale_2", c.emb_dim, ("embed",), init="ones")
+    self.pre2 = Norm(mb, "pre_feedforward_layernorm_2", c.emb_dim, eps)
+    self.post1 = Norm(mb, "post_feedforward_layernorm_1", c.emb_dim, eps)
+    self.post2 = Norm(mb, "post_feedforward_layernorm_2", c.emb_dim, eps)
+    self.eps, self.root = eps, c.emb_dim ** -0.5
+
+  def __call__(self, x, ctx, original):
+    shared = self.post1(self.shared(x, ctx))
+    of = original.float()
+    gate_in = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.eps) * self.root * self.router_scale.leaf().float()
+    routed = self.post2(self.routed(self.pre2(original), ctx, gate_inputs=gate_in if self.routed.c.float32_gate_logits else gate_in.to(x.dtype)))
+    return routed + shared
 
 
 class RoutedAndSharedMoE:

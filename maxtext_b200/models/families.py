@@ -50,6 +50,17 @@ def rope_tables(c, device) -> dict:
   local_max = c.local_rope_max_timescale if c.local_rope_max_timescale > 0 else c.rope_max_timescale
   # local (sliding-window) layers never use the long-context linear scaling (gemma3)
   tables["local"] = (ref.rope_inv_timescale(rot, c.rope_min_timescale, local_max, 1.0, "default").to(device), False)
+  if c.decoder_block == "gemma4":
+    # proportional rotary embedding (src/maxtext/models/gemma4.py:198-213): frequencies are spaced over the WHOLE head width and
+    # only the first `proportion` of the angle pairs rotate; the others keep frequency zero (identity)
+    def prop(head_dim, proportion, max_ts):
+      t = ref.rope_inv_timescale(head_dim, c.rope_min_timescale, max_ts, 1.0, "default")
+      t[int(proportion * head_dim // 2):] = 0.0
+      return t.to(device)
+    g_dim = int(c.global_head_dim or c.head_dim)
+    g_max = c.global_rope_max_timescale if c.global_rope_max_timescale > 0 else c.rope_max_timescale
+    tables["gemma4_global"] = (prop(g_dim, float(c.global_rope_proportion), g_max), False)
+    tables["gemma4_local"] = (prop(int(c.head_dim), float(c.local_rope_proportion), local_max), False)
   return tables
 
 
@@ -162,6 +173,25 @@ def layer_plans(c) -> list[LayerPlan]:
           window=c.sliding_window_size if local else 0, rope="local" if local else "default", qk_norm=True,
           query_scalar=qs, soft_cap=c.attn_logits_soft_cap)]))
     return plans
+  if blk == "gemma4":
+    # src/maxtext/models/gemma4.py:40-55,150-410: five sliding-window layers then one global layer; global layers may have their
+    # own head width / key-value head count and reuse the key projection as the value; q, k (scaled) and v (scale-free) are
+    # RMS-normalised, no 1/sqrt(d) factor; every layer output is multiplied by a learned scalar; MoE variants add routed
+    # experts next to the dense MLP (the "shared expert")
+    plans = []
+    for i in range(n):
+      glob = (i % 6) == 5
+      plans.append(LayerPlan("layers", [BlockPlan(
+          pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="pre_ffw_norm",
+          post_attn_norm="post_self_attention_norm" if c.use_post_attn_norm else None,
+          post_mlp_norm="post_ffw_norm" if c.use_post_ffw_norm else None,
+          window=0 if glob else c.sliding_window_size, rope="gemma4_global" if glob else "gemma4_local", qk_norm=True,
+          query_scalar=1.0, soft_cap=c.attn_logits_soft_cap, v_norm="scale" if c.v_norm_with_scale else "noscale",
+          head_dim=int(c.global_head_dim or c.head_dim) if glob else None,
+          kv_heads=int(c.global_num_kv_heads or c.num_kv_heads) if glob else None,
+          share_kv=bool(c.share_kv_projections) and glob, layer_scalar=True,
+          mlp="gemma4_moe" if c.num_experts > 1 else "dense")]))
+    return plans
   if blk == "gpt3":
     bp = BlockPlan(pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="post_self_attention_norm", use_rope=False,
                    attn_bias=True, mlp_bias=True, norm_kind="layernorm")
@@ -175,4 +205,4 @@ def layer_plans(c) -> list[LayerPlan]:
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, envy, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, envy, gemma4, simple)")

@@ -57,6 +57,11 @@ class BlockPlan:
   temperature_tuning: bool = False       # llama4 NoPE layers: position-dependent query scale
   chunk: int = 0                         # llama4 RoPE layers: attention restricted to chunks of this many tokens
   moe_style: str = ""                    # "" | "llama4" | "gpt_oss"
+  head_dim: int | None = None            # gemma4 global layers: own head width ...
+  kv_heads: int | None = None            # ... and key / value head count
+  share_kv: bool = False                 # value = key projection
+  v_norm: str = ""                       # "" | "noscale" | "scale": RMS normalisation of the value heads
+  layer_scalar: bool = False             # learned scalar on the layer output
 
 
 @dataclass
@@ -93,16 +98,21 @@ class DecoderBlock:
                               plan.query_scalar, plan.soft_cap, plan.attn_bias,
                               rotary_dim=rot, sinks=plan.sinks, l2_qk_norm=plan.l2_qk_norm,
                               temperature_tuning=plan.temperature_tuning, chunk=plan.chunk, out_bias=plan.attn_out_bias,
-                              global_qk_norm=plan.global_qk_norm, gated=plan.gated_attn, qk_norm_offset=plan.norm_offset)
+                              global_qk_norm=plan.global_qk_norm, gated=plan.gated_attn, qk_norm_offset=plan.norm_offset,
+                              head_dim=plan.head_dim, num_kv_heads=plan.kv_heads, share_kv=plan.share_kv, v_norm=plan.v_norm)
     self.n1b = mk(plan.post_attn_norm) if plan.post_attn_norm else None
     self.n2 = mk(plan.pre_mlp_norm) if plan.pre_mlp_norm else None
     if plan.mlp == "moe":
       self.mlp = M.RoutedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
     elif plan.mlp == "moe_shared":
       self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
+    elif plan.mlp == "gemma4_moe":
+      self.mlp = M.Gemma4MoE(b, c, plan.mlp_name + s)
     else:
       self.mlp = L.MLP(b, c, plan.mlp_name + s, plan.mlp_hidden, bias=plan.mlp_bias)
     self.n2b = mk(plan.post_mlp_norm) if plan.post_mlp_norm else None
+    self.layer_scalar = b._add("layer_scalar" + s, shape=(1,), ref_shape=(1,), logical_axes=(None,), kind="same", init="ones") \
+        if plan.layer_scalar else None
     self.mhc_attn = self.mhc_mlp = None
     if int(getattr(c, "mhc_expansion_rate", 1)) > 1:
       # src/maxtext/models/deepseek.py:177-179: each branch of the block is wrapped by its own hyper-connection
@@ -127,10 +137,14 @@ class DecoderBlock:
     if self.n1b is not None:
       a = self.n1b(a)
     x = x + ctx.dropout(a, 0)                 # src/maxtext/models/llama2.py: dropout on each residual branch
-    m = self.mlp(self.n2(x) if self.n2 is not None else x, ctx)
+    h = self.n2(x) if self.n2 is not None else x
+    m = self.mlp(h, ctx, original=x) if self.plan.mlp == "gemma4_moe" else self.mlp(h, ctx)
     if self.n2b is not None:
       m = self.n2b(m)
-    return x + ctx.dropout(m, 1)
+    x = x + ctx.dropout(m, 1)
+    if self.layer_scalar is not None:
+      x = x * self.layer_scalar.leaf().to(x.dtype)
+    return x
 
 
 class DecoderLayer:

@@ -1,0 +1,102 @@
+"""Gemma-4 text stack (dense and MoE) against the HuggingFace model with the same weights, fp32."""
+import math
+
+import pytest
+import torch
+
+from helpers import tiny_config
+
+D, H, HKV, DH, GDH, GKV, F, L, V = 48, 4, 2, 16, 32, 1, 64, 6, 128
+
+
+def _hf(moe: bool):
+  from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig
+  from transformers.models.gemma4.modeling_gemma4 import Gemma4ForCausalLM
+  cfg = Gemma4TextConfig(
+      vocab_size=V, hidden_size=D, intermediate_size=F, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=HKV, head_dim=DH,
+      global_head_dim=GDH, num_global_key_value_heads=GKV, attention_k_eq_v=True, sliding_window=8, max_position_embeddings=64,
+      layer_types=["sliding_attention"] * 5 + ["full_attention"], hidden_size_per_layer_input=0, vocab_size_per_layer_input=V,
+      final_logit_softcapping=30.0, rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                                      "full_attention": {"rope_type": "proportional", "rope_theta": 1000000.0, "partial_rotary_factor": 0.25}},
+      enable_moe_block=moe, num_experts=4 if moe else None, top_k_experts=2 if moe else None, moe_intermediate_size=24 if moe else None,
+      tie_word_embeddings=True)
+  cfg._attn_implementation = "eager"
+  torch.manual_seed(0)
+  m = Gemma4ForCausalLM(cfg).float().eval()
+  with torch.no_grad():
+    for n, p in m.named_parameters():
+      p.copy_(torch.randn_like(p) * (0.3 if p.dim() > 1 else 0.5) + (1.0 if "norm" in n or "scale" in n else 0.0))
+    for n, b in m.named_buffers():
+      if n.endswith("layer_scalar"):
+        b.copy_(torch.rand(1) + 0.5)
+  return m
+
+
+def _ours(moe: bool):
+  extra = ["num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=24", "shared_experts=1", "norm_topk_prob=true", "load_balance_loss_weight=0.0"] if moe \
+      else ["num_experts=1"]
+  cfg = tiny_config("gemma4-26b", [f"base_emb_dim={D}", f"base_num_query_heads={H}", f"base_num_kv_heads={HKV}", f"head_dim={DH}", f"global_head_dim={GDH}",
+                                   f"global_num_kv_heads={GKV}", f"base_mlp_dim={F}", f"base_num_decoder_layers={L}", f"vocab_size={V}", "sliding_window_size=8",
+                                   "max_target_length=16", "tokenizer_type=byte", "normalize_embedding_logits=true", "float32_gate_logits=true"] + extra)
+  from maxtext_b200.models.transformer import Transformer
+  model = Transformer(cfg, None, torch.device("cpu"))
+  model.store.initialize(seed=0)
+  return cfg, model
+
+
+def _load(model, hf, moe):
+  sd = {k: v.detach().float() for k, v in hf.state_dict().items()}
+  st = model.store
+
+  def put(name, t):
+    p = st.params[name]
+    assert tuple(p.pdef.shape) == tuple(t.shape), (name, tuple(p.pdef.shape), tuple(t.shape))
+    st.load_full(name, t.contiguous())
+  put("token_embedder/embedding", sd["model.embed_tokens.weight"] * math.sqrt(D))
+  put("decoder/decoder_norm/scale", sd["model.norm.weight"])
+  for i in range(L):
+    a, b = f"layers_{i}/", f"model.layers.{i}."
+    put(a + "pre_self_attention_norm/scale", sd[b + "input_layernorm.weight"])
+    put(a + "post_self_attention_norm/scale", sd[b + "post_attention_layernorm.weight"])
+    put(a + "pre_ffw_norm/scale", sd[b + "pre_feedforward_layernorm.weight"])
+    put(a + "post_ffw_norm/scale", sd[b + "post_feedforward_layernorm.weight"])
+    put(a + "layer_scalar", sd[b + "layer_scalar"])
+    put(a + "self_attention/query/kernel", sd[b + "self_attn.q_proj.weight"])
+    put(a + "self_attention/key/kernel", sd[b + "self_attn.k_proj.weight"])
+    if i % 6 != 5:
+      put(a + "self_attention/value/kernel", sd[b + "self_attn.v_proj.weight"])
+    put(a + "self_attention/out/kernel", sd[b + "self_attn.o_proj.weight"])
+    put(a + "self_attention/query_norm/scale", sd[b + "self_attn.q_norm.weight"])
+    put(a + "self_attention/key_norm/scale", sd[b + "self_attn.k_norm.weight"])
+    mlp = a + ("mlp/moe_block/shared_experts/" if moe else "mlp/")
+    put(mlp + "wi_0/kernel", sd[b + "mlp.gate_proj.weight"])
+    put(mlp + "wi_1/kernel", sd[b + "mlp.up_proj.weight"])
+    put(mlp + "wo/kernel", sd[b + "mlp.down_proj.weight"])
+    if moe:
+      r = a + "mlp/moe_block/MoeBlock_0/"
+      put(r + "gate/kernel", sd[b + "router.proj.weight"])
+      put(r + "per_expert_scale", sd[b + "router.per_expert_scale"])
+      gu = sd[b + "experts.gate_up_proj"]                                   # [E, 2F, D]
+      put(r + "wi_0", gu[:, :24])
+      put(r + "wi_1", gu[:, 24:])
+      put(r + "wo", sd[b + "experts.down_proj"])
+      put(a + "mlp/pre_forward_scale_2", sd[b + "router.scale"])
+      put(a + "mlp/pre_feedforward_layernorm_2/scale", sd[b + "pre_feedforward_layernorm_2.weight"])
+      put(a + "mlp/post_feedforward_layernorm_1/scale", sd[b + "post_feedforward_layernorm_1.weight"])
+      put(a + "mlp/post_feedforward_layernorm_2/scale", sd[b + "post_feedforward_layernorm_2.weight"])
+  st.sync_compute_from_master()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_logits_match_huggingface(moe):
+  pytest.importorskip("transformers")
+  hf = _hf(moe)
+  cfg, model = _ours(moe)
+  _load(model, hf, moe)
+  torch.manual_seed(1)
+  ids = torch.randint(0, V, (2, 14))                              # longer than the sliding window of 8
+  with torch.no_grad():
+    want = hf(input_ids=ids).logits.float()
+    got = model.forward(ids)
+  err = float((got - want).abs().max())
+  assert err < 2e-3 * max(1.0, float(want.abs().max())), err
