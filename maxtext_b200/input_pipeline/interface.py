@@ -54,29 +54,38 @@ class PrefetchIterator:
   def _start(self):
     self._q = self._queue_mod.Queue(maxsize=self.depth)
     self._stop = self._threading.Event()
-    self._thread = self._threading.Thread(target=self._work, args=(self._q, self._stop), daemon=True)
+    # the thread holds the reader, the queue and the stop flag, not this wrapper: dropping the wrapper ends the thread
+    self._thread = self._threading.Thread(target=PrefetchIterator._work, args=(self.inner, self._q, self._stop, self._queue_mod.Full),
+                                          daemon=True)
     self._thread.start()
 
-  def _work(self, q, stop):
+  @staticmethod
+  def _work(inner, q, stop, full_exc):
     def put(item):
       while not stop.is_set():
         try:
           q.put(item, timeout=0.1)
           return True
-        except self._queue_mod.Full:
+        except full_exc:
           continue
       return False
     try:
       while not stop.is_set():
         try:
-          batch = next(self.inner)
+          batch = next(inner)
         except StopIteration:
           put(("end", None, None))
           return
-        if not put(("batch", batch, self.inner.state())):
+        if not put(("batch", batch, inner.state())):
           return
     except BaseException as e:  # pylint: disable=broad-except
       put(("error", e, None))
+
+  def __del__(self):
+    try:
+      self._stop.set()
+    except Exception:  # pylint: disable=broad-except
+      pass
 
   def __iter__(self):
     return self

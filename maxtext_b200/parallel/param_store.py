@@ -284,18 +284,25 @@ class ParamStore:
     dev = self.device
     self.master = torch.zeros(total_local, dtype=self.weight_dtype, device=dev)
     self.alias_compute = self.compute_dtype == self.weight_dtype
-    # ---- fused communication (symmetric memory over NVLink): only for pure shard groups spanning every rank
+    # process groups (collective creation, deterministic order)
+    for u in self.units.values():
+      # planning runs build the store on the meta device for worlds that are not attached: no process groups there
+      u.group = mesh.group(u.fsdp_axes) if (u.group_size > 1 and self.device.type != "meta") else None
+    # ---- fused communication (symmetric memory over NVLink): when every sharded unit is sharded over the SAME group of ranks
+    # (the whole world for pure FSDP; the ranks of one tensor / expert / pipeline coordinate on mixed meshes)
     self.fused = False
     self.symm = None
     world = getattr(mesh, "world", 1)
     sharded = [u for u in self.units.values() if u.group_size > 1]
-    if (bool(getattr(config, "use_fused_comm_kernels", False)) and self.device.type == "cuda" and world > 1 and sharded
-        and all(u.group_size == world for u in sharded) and not self.alias_compute and self.compute_dtype == torch.bfloat16
+    one_group = bool(sharded) and len({(tuple(u.fsdp_axes), u.group_size) for u in sharded}) == 1
+    if (bool(getattr(config, "use_fused_comm_kernels", False)) and self.device.type == "cuda" and world > 1 and one_group
+        and not self.alias_compute and self.compute_dtype == torch.bfloat16
         and self.grad_dtype == torch.float32 and not bool(config.logits_via_embedding)):
       from . import symm as _symm
       if _symm.available():
         try:
-          self.symm = _symm.SymmGroup(None, self.device)
+          whole = sharded[0].group_size == world
+          self.symm = _symm.SymmGroup(None if whole else sharded[0].group, self.device)
           self.fused = True
         except Exception as e:  # pylint: disable=broad-except
           # no peer mapping on this platform (or the allocator refused): the NCCL composition below does the same job
@@ -307,7 +314,11 @@ class ParamStore:
       self.compute_shard = self._cs.tensor
       self.seg_elems = 512 * 1024
       max_chunk = max(u.chunk for u in sharded)
-      self.seg_flags = torch.zeros(world * (-(-max_chunk // self.seg_elems)), dtype=torch.int32, device=dev)
+      gsz = sharded[0].group_size
+      self.seg_flags = torch.zeros(gsz * (-(-max_chunk // self.seg_elems)), dtype=torch.int32, device=dev)
+      # on a mixed mesh some tensors of a unit are replicated over the other axes: the gradient norm then weighs every tensor by
+      # its multiplicity, which the partial sums emitted by the reduce-scatter kernels cannot do
+      self.gradsq_whole_world = gsz == world
       self.comm_ctas = int(getattr(config, "fsdp_comm_ctas", 8))
       # How a unit's all-gather runs, one unit ahead of its first use and on its own stream in both default forms.
       # "dma": one peer-to-local copy per rank on the copy engines (no SM time); "prefetch": a peer-load kernel (32 CTAs).
@@ -315,7 +326,7 @@ class ParamStore:
       # Measured on 8 GPUs (Llama-3-8B step): prefetch 1228 ms, dma 1156 ms; with in-switch reduction of the gradient
       # reduce-scatter 1188 and 1125 ms. On 2 GPUs: prefetch 1148 ms, dma 1140 ms, and plain peer loads beat the in-switch
       # reduction (1135 vs 1150 ms), which is therefore used from four ranks up.
-      big = world >= 4
+      big = gsz >= 4
       self.ag_mode = os.environ.get("MAXTEXT_B200_AG_MODE", "dma")
       self.ag_in_gemm = self.ag_mode == "gemm"
       self.ag_stream = torch.cuda.Stream(device=dev)
@@ -332,10 +343,6 @@ class ParamStore:
     self.grad_shard = None   # allocated on first backward (inference never needs it)
     self.exp_avg = None
     self.exp_avg_sq = None
-    # process groups (collective creation, deterministic order)
-    for u in self.units.values():
-      # planning runs build the store on the meta device for worlds that are not attached: no process groups there
-      u.group = mesh.group(u.fsdp_axes) if (u.group_size > 1 and self.device.type != "meta") else None
     self._pool: list[torch.Tensor] = []
     self._grad_pool: list[torch.Tensor] = []
     self._rs_inflight: list = []
@@ -660,7 +667,7 @@ class ParamStore:
     self.ensure_grad_buffers()
     if self.fused:
       self.gradsq.zero_()
-      self.gradsq_valid = int(self.config.gradient_accumulation_steps) == 1
+      self.gradsq_valid = int(self.config.gradient_accumulation_steps) == 1 and self.gradsq_whole_world
     for u in self.units.values():
       for p in u.params:
         p.grad_written = False

@@ -119,6 +119,33 @@ def train_tp(rank, world, dev, fused):
   return out
 
 
+def train_fsdp_tp(rank, world, dev, fused):
+  """fsdp (world / 2) x tensor 2: every sharded unit lives on the fsdp ranks of one tensor coordinate, a sub-group of the world.
+  The fused collectives (symmetric memory over that sub-group) against NCCL on the same sub-group."""
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.parallel import mesh as mesh_lib
+  from maxtext_b200.train import train as T
+  from maxtext_b200.train.engine import TrainEngine
+  cfg = pyconfig.initialize(
+      ["w", "maxtext_b200/configs/base.yml", "base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128",
+       "base_mlp_dim=1024", "base_num_decoder_layers=3", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
+       "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal", "log_config=false", "steps=3",
+       "learning_rate=1e-3", "warmup_steps_fraction=0.0", f"ici_fsdp_parallelism={world // 2}", "ici_tensor_parallelism=2",
+       f"use_fused_comm_kernels={'true' if fused else 'false'}"], num_devices=world)
+  mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world)
+  eng = TrainEngine(cfg, mesh, dev)
+  assert bool(eng.store.fused) == bool(fused), "the fused FSDP path should be on exactly when asked for"
+  if fused:
+    assert eng.store.symm.world == world // 2
+  it = T.create_data_iterator(cfg, mesh)
+  out = []
+  for _ in range(3):
+    m = eng.train_step(next(it))
+    out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
+  _canaries(fused)
+  return out
+
+
 def train_cp(rank, world, dev, strategy):
   """Context parallelism over all ranks (None: one rank alone on the whole batch). Every strategy must land on the flash
   kernels: the ring and all-gather forms attend to foreign key blocks through the kernels' position arrays."""
@@ -188,7 +215,7 @@ def main():
       assert backend.ext().kernel_status(True) == 0
       msg = "ok " + repr((ref, got))
     else:
-      fn = {"moe_ep": train_moe_ep, "tp": train_tp}.get(mode, train)
+      fn = {"moe_ep": train_moe_ep, "tp": train_tp, "fsdp_tp": train_fsdp_tp}.get(mode, train)
       a = fn(rank, world, dev, fused=False)
       b = fn(rank, world, dev, fused=True)
       for (la, na), (lb, nb) in zip(a, b):

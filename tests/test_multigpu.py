@@ -63,3 +63,8 @@ def test_tensor_parallel_gemm_reduce_scatter_matches_nccl(tmp_path):
 
 def test_context_parallel_strategies_on_the_flash_kernels_match_one_gpu(tmp_path):
   _run("cp", tmp_path)
+
+
+def test_fused_fsdp_on_a_shard_subgroup_matches_nccl(tmp_path):
+  """fsdp2 x tp2 on four GPUs: the fused gather / reduce-scatter run over the two fsdp ranks of each tensor coordinate."""
+  _run("fsdp_tp", tmp_path, world=4)
