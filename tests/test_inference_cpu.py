@@ -290,3 +290,39 @@ def test_mixed_precision_quantisation_maps(tmp_path):
   bad.write_text(json.dumps({".*": {"bits": 3}}))
   with pytest.raises(ValueError):
     mp.load_quant_map(str(bad))
+
+
+def test_mlperf_offline_harness_and_accuracy_log(tmp_path):
+  """Offline scenario driver: length buckets, per-bucket slots, LoadGen-format accuracy log, ROUGE against references."""
+  import json
+  from helpers import tiny_config
+  from maxtext_b200.inference.maxengine import MaxEngine
+  from maxtext_b200.inference.mlperf import evaluate_accuracy, offline_mode
+  from maxtext_b200.input_pipeline.tokenizer import build_tokenizer
+  cfg = tiny_config("llama3-8b", ["max_prefill_predict_length=32", "max_target_length=64", "tokenizer_type=byte", "vocab_size=260"])
+  eng = MaxEngine(cfg)
+  eng.load_params()
+  tok = build_tokenizer(cfg)
+  texts = ["short one", "a somewhat longer prompt here", "x", "the longest prompt of them all, yes"]
+  data = tmp_path / "data.jsonl"
+  data.write_text("\n".join(json.dumps({"tok_input": tok.encode(t), "tok_input_len": len(tok.encode(t)), "output": "reference text"}) for t in texts))
+  out = tmp_path / "logs"
+  args = offline_mode.parse_args(["--dataset_path", str(data), "--mlperf_test_mode", "accuracy", "--output_log_dir", str(out),
+                                  "--prefill_lengths_and_batch_sizes", "8,2|16,2|40,1", "--max_new_tokens", "5",
+                                  "--rename_dataset_cols", '{"tok_input_len": "tok_input_length"}'])
+  summary = offline_mode.run(args, engine=eng)
+  assert summary["samples"] == 4 and summary["generated_tokens"] > 0 and summary["samples_per_second"] > 0
+  assert summary["buckets"] == {"8": 1, "16": 1, "40": 2}
+  log = json.loads((out / "mlperf_log_accuracy.json").read_text())
+  assert [e["qsl_idx"] for e in log] == [0, 1, 2, 3] and all(len(bytes.fromhex(e["data"])) == 8 * e["token_count"] for e in log)
+  gen = evaluate_accuracy.decode_log(str(out / "mlperf_log_accuracy.json"))
+  # the harness generated what the engine generates for the same prompt on its own
+  from maxtext_b200.inference.offline_engine import OfflineEngine
+  want = OfflineEngine(eng, slots=1).batch_inference([tok.encode(texts[0])], max_new_tokens=5)[0]
+  assert gen[0] == want
+  res = evaluate_accuracy.evaluate(str(out / "mlperf_log_accuracy.json"), offline_mode.load_dataset(str(data)), tok)
+  assert set(res) >= {"rouge1", "rouge2", "rougeL", "gen_len", "gen_num"} and res["gen_num"] == 4
+  import pytest
+  with pytest.raises(ValueError):
+    offline_mode.classify([{"tok_input_length": 99}], [(8, 1)], allow_skip=False)
+  assert (out / "mlperf_log_summary.txt").read_text().startswith("=====")
