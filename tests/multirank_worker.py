@@ -18,7 +18,10 @@ def main():
   cfg = pyconfig.initialize(["w", "maxtext_b200/configs/base.yml"] + overrides, num_devices=world)
   mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world) if world > 1 else None
   from maxtext_b200.train.pipeline import make_engine
-  eng = make_engine(cfg, mesh, torch.device("cpu"))
+  # MAXTEXT_B200_TEST_DEVICE=cuda: the same worker on GPUs (one per rank, NCCL), used by the multi-GPU tier
+  on_gpu = os.environ.get("MAXTEXT_B200_TEST_DEVICE") == "cuda"
+  dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
+  eng = make_engine(cfg, mesh, dev)
   it = T.create_data_iterator(cfg, mesh)
   losses, norms = [], []
   stepper = eng
@@ -29,9 +32,14 @@ def main():
     m = stepper.train_step(next(it))
     losses.append(float(m["learning/loss"]))
     norms.append(float(m["learning/raw_grad_norm"]))
+  status = 0
+  if on_gpu:
+    from maxtext_b200.ops import backend
+    torch.cuda.synchronize()
+    status = int(backend.ext(required=True).kernel_status(True))
   if rank == 0:
     with open(out_path, "w") as fh:
-      json.dump({"loss": losses, "grad_norm": norms}, fh)
+      json.dump({"loss": losses, "grad_norm": norms, "kernel_status": status}, fh)
   if world > 1:
     torch.distributed.destroy_process_group()
 

@@ -68,3 +68,53 @@ def test_context_parallel_strategies_on_the_flash_kernels_match_one_gpu(tmp_path
 def test_fused_fsdp_on_a_shard_subgroup_matches_nccl(tmp_path):
   """fsdp2 x tp2 on four GPUs: the fused gather / reduce-scatter run over the two fsdp ranks of each tensor coordinate."""
   _run("fsdp_tp", tmp_path, world=4)
+
+
+# ---- layouts that the CPU tier checks on gloo ranks, here on GPUs in bf16 with this repository's kernels: two ranks against one GPU
+GPU_BASE = ["base_emb_dim=512", "base_num_query_heads=4", "base_num_kv_heads=2", "head_dim=128", "base_mlp_dim=1024", "base_num_decoder_layers=4",
+            "vocab_size=4096", "max_target_length=256", "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal",
+            "log_config=false", "steps=3", "learning_rate=1e-3", "warmup_steps_fraction=0.0", "dtype=bfloat16", "weight_dtype=float32",
+            "attention=flash", "enable_data_shuffling=false"]
+
+
+def _run_layout(world, overrides, tmp_path, tag):
+  import json
+  if torch.cuda.device_count() < world:
+    pytest.skip(f"needs {world} GPUs")
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  port = s.getsockname()[1]
+  s.close()
+  out = os.path.join(str(tmp_path), f"{tag}.json")
+  procs = []
+  for r in range(world):
+    env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+               MAXTEXT_B200_QUIET="1", MAXTEXT_B200_WAIT_LIMIT_MS="5000", MAXTEXT_B200_TEST_DEVICE="cuda")
+    procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multirank_worker.py"), out] + GPU_BASE + list(overrides), cwd=ROOT,
+                                  env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+  logs = []
+  for p in procs:
+    try:
+      o, _ = p.communicate(timeout=600)
+    except subprocess.TimeoutExpired:
+      pytest.fail("a rank is still running; it is left to finish on its own")
+    logs.append(o.decode(errors="replace"))
+  for p, l in zip(procs, logs):
+    assert p.returncode == 0, l[-3000:]
+  return json.load(open(out))
+
+
+@pytest.mark.parametrize("layout,overrides", [
+    ("pp2_gpipe", ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2"]),
+    ("pp2_circular", ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2", "num_layers_per_pipeline_stage=1",
+                      "num_pipeline_microbatches=4"]),
+    ("tensor_sequence2", ["per_device_batch_size=4", "ici_fsdp_parallelism=1", "ici_tensor_sequence_parallelism=2"]),
+])
+def test_layouts_on_two_gpus_match_one_gpu(layout, overrides, tmp_path):
+  one = _run_layout(1, ["per_device_batch_size=4"], tmp_path, "one")
+  two = _run_layout(2, overrides, tmp_path, layout)
+  assert one["kernel_status"] == 0 and two["kernel_status"] == 0
+  for a, b in zip(two["loss"], one["loss"]):
+    assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (layout, two, one)
+  for a, b in zip(two["grad_norm"], one["grad_norm"]):
+    assert abs(a - b) <= 6e-2 * max(1.0, abs(b)), (layout, two, one)

@@ -280,3 +280,47 @@ def test_distillation_online_offline_and_learn_to_init(tmp_path):
   assert torch.equal(student2.store.full_master(student2.store.params[name_s]), teacher.store.full_master(teacher.store.params[name_t]))
   _, hist2 = D.train_distill(s_cfg, student=student2, teacher=teacher, data_iterator=Fixed())
   assert hist2[-1]["learning/loss"] < hist2[0]["learning/loss"]
+
+
+def test_learn_to_init_maps_teacher_attention_into_a_narrower_student():
+  """Effective kernels follow the published contraction; training only the maps lowers the student's loss; collapsing writes them."""
+  import torch
+  from helpers import batch_of, make_engine, tiny_config
+  from maxtext_b200.trainers.post_train.distillation.learn_to_init import LearnToInit, effective_kernel
+  torch.manual_seed(0)
+  # the contraction, against explicit loops
+  C, A, B = torch.randn(5, 3, 4), torch.randn(3, 2), torch.randn(4, 6)
+  k = effective_kernel(C, A, B)
+  want = torch.zeros(5, 2, 6)
+  for b in range(5):
+    want[b] = A.t() @ C[b] @ B
+  assert torch.allclose(k, want, atol=1e-5)
+  Co, Ao, Bo = torch.randn(3, 4, 5), torch.randn(3, 2), torch.randn(6, 4)
+  ko = effective_kernel(Co, Ao, Bo, is_output=True)
+  assert ko.shape == (2, 6, 5) and torch.allclose(ko[..., 1], Ao.t() @ Co[..., 1] @ Bo.t(), atol=1e-5)
+  W = torch.randn(3, 4, 2, 6)
+  assert torch.allclose(effective_kernel(C, W=W), torch.einsum("bxy,xyuv->buv", C, W))
+  # a student with 2 query heads of width 8 initialised from a "teacher" with 4 heads of width 16
+  cfg = tiny_config("llama3-8b", ["base_num_query_heads=2", "base_num_kv_heads=2", "head_dim=8", "steps=8", "gradient_clipping_threshold=0"])
+  eng = make_engine(cfg)
+  D = cfg.emb_dim
+  teacher = {}
+  for i in range(cfg.num_decoder_layers):
+    for proj in ("query", "key", "value"):
+      teacher[f"layers_{i}/self_attention/{proj}/kernel"] = torch.randn(D, 4, 16) * 0.05
+    teacher[f"layers_{i}/self_attention/out/kernel"] = torch.randn(4, 16, D) * 0.05
+  lti = LearnToInit(eng, teacher, lr=2e-2, layer_indices=[0])
+  assert set(lti.maps) == {n for n in teacher if n.startswith("layers_0/")}            # layer 1 keeps its own weights
+  name = "layers_0/self_attention/query/kernel"
+  p = eng.store.params[name]
+  assert torch.allclose(eng.store.full_master(p).float(), lti._internal(name, lti.kernel(name)), atol=1e-6)
+  other = eng.store.full_master(eng.store.params["layers_0/mlp/wi_0/kernel"]).clone()
+  batch = batch_of(cfg)
+  losses = [lti.step(batch)["loss"] for _ in range(8)]
+  assert losses[-1] < losses[0]
+  assert torch.equal(eng.store.full_master(eng.store.params["layers_0/mlp/wi_0/kernel"]), other)   # only the maps moved
+  final = lti.collapse()
+  assert torch.allclose(eng.store.full_master(p).float(), lti._internal(name, final[name]), atol=1e-6)
+  g = LearnToInit(make_engine(cfg), teacher, general_map=True, layer_indices=[1])
+  assert g.maps["layers_1/self_attention/out/kernel"]["train"]["W"].shape == (4, 16, 2, 8)
+  assert g.step(batch)["loss"] > 0
