@@ -267,9 +267,7 @@ def test_dropout_is_replayed_by_recompute_and_off_in_eval():
 
 
 def test_unsupported_tensor_sequence_combinations_are_rejected():
-  from maxtext_b200.parallel.mesh import Mesh
-  from maxtext_b200.train.engine import TrainEngine
-  cfg = tiny_config("llama3-8b", ["ici_tensor_sequence_parallelism=2", "ici_context_parallelism=2", "ici_fsdp_parallelism=1"], num_devices=4)
-  mesh = Mesh(list(cfg.mesh_axes), list(cfg.mesh_shape), rank=0, world=4)
-  with pytest.raises(NotImplementedError):
-    TrainEngine(cfg, mesh, torch.device("cpu"))
+  # the combination is refused when the configuration is parsed, before any engine is built
+  from maxtext_b200.config.validators import ConfigValueError
+  with pytest.raises(ConfigValueError):
+    tiny_config("llama3-8b", ["ici_tensor_sequence_parallelism=2", "ici_context_parallelism=2", "ici_fsdp_parallelism=1"], num_devices=4)
