@@ -44,17 +44,35 @@ class PipelineEngine(TrainEngine):
     self.chunks = [[l for l in self.model.layers if (l.index // lps) // self.P == r] for r in range(self.R)]
     self._uidx = {name: i for i, name in enumerate(self.model.units_in_order())}
     self._pending = []
+    # NCCL runs the point-to-point operations of one communicator in issue order on one stream per peer. In the circular
+    # schedule a stage sends activations of later micro-batches forward while the wrap-around of earlier ones comes back from
+    # the same peer, and the two sides issue those in different orders: on one communicator that dead-locks. Every directed
+    # (source, destination) pair therefore gets a communicator of its own, separately for activations and for gradients.
+    self._p2p = {}
+    if dist.is_initialized() and dist.get_backend() == "nccl":
+      seen = set()
+      for r in range(mesh.world):                                  # collective: every rank creates every group, in one order
+        ring = tuple(mesh.ranks_along(("stage",), r))
+        if ring in seen:
+          continue
+        seen.add(ring)
+        for tag in ("act", "grad"):
+          for i in range(len(ring)):
+            src, dst = (ring[i], ring[(i + 1) % len(ring)]) if tag == "act" else (ring[(i + 1) % len(ring)], ring[i])
+            g = dist.new_group([src, dst]) if src != dst else None
+            if mesh.rank in (src, dst):
+              self._p2p[(src, dst, tag)] = g
 
   # ---- plumbing
   def _replication(self, u, params=None) -> float:
     return max(1.0, super()._replication(u, params) / self.P)        # every stage holds different parameters
 
-  def _send(self, t, dst):
-    self._pending.append((dist.isend(t.contiguous(), dst), t))
+  def _send(self, t, dst, tag="act"):
+    self._pending.append((dist.isend(t.contiguous(), dst, group=self._p2p.get((self.mesh.rank, dst, tag))), t))
 
-  def _recv(self, shape, dtype, src):
+  def _recv(self, shape, dtype, src, tag="act"):
     buf = torch.empty(shape, dtype=dtype, device=self.device)
-    dist.recv(buf, src)
+    dist.recv(buf, src, group=self._p2p.get((src, self.mesh.rank, tag)))
     return buf
 
   def _drain(self):
@@ -135,7 +153,7 @@ class PipelineEngine(TrainEngine):
       for m in range(M):
         accumulate = grads_started or m > 0 or r < self.R - 1
         if self._has_next(r):
-          dx = self._recv((mb, S, c.emb_dim), act_dtype, self.next_rank) if compute_grads else None
+          dx = self._recv((mb, S, c.emb_dim), act_dtype, self.next_rank, "grad") if compute_grads else None
         else:
           hi = self._uidx["head"]
           if compute_grads:
@@ -170,7 +188,7 @@ class PipelineEngine(TrainEngine):
             p.collect_leaf_grad()
           self._finish_unit_grads(ui, grads_started or m > 0)
         if self._has_prev(r):
-          self._send(dx, self.prev_rank)
+          self._send(dx, self.prev_rank, "grad")
         else:
           ei = self._uidx["embed"]
           for u in self._units[ei]:

@@ -20,6 +20,13 @@ def main():
   from maxtext_b200.train.pipeline import make_engine
   # MAXTEXT_B200_TEST_DEVICE=cuda: the same worker on GPUs (one per rank, NCCL), used by the multi-GPU tier
   on_gpu = os.environ.get("MAXTEXT_B200_TEST_DEVICE") == "cuda"
+  if on_gpu:
+    # a rank that is still here after three minutes is stuck in a collective whose partner never came: leave, so that the
+    # test ends with an error instead of holding the GPUs
+    import threading
+    t = threading.Timer(180.0, os._exit, (3,))
+    t.daemon = True
+    t.start()
   dev = torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu")
   eng = make_engine(cfg, mesh, dev)
   it = T.create_data_iterator(cfg, mesh)

@@ -95,7 +95,7 @@ def _run_layout(world, overrides, tmp_path, tag):
   logs = []
   for p in procs:
     try:
-      o, _ = p.communicate(timeout=600)
+      o, _ = p.communicate(timeout=240)          # a rank leaves by itself after 180 s
     except subprocess.TimeoutExpired:
       pytest.fail("a rank is still running; it is left to finish on its own")
     logs.append(o.decode(errors="replace"))
