@@ -86,7 +86,7 @@ class _AllReduceMean(torch.autograd.Function):
 
 
 class RoutedMoE:
-  def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False, style: str = ""):
+  def __init__(self, b: Builder, config, name="MoeBlock_0", deepseek_style=False, style: str = "", hash_routing: bool = False):
     """style: "llama4" (raw top-k logits, sigmoid score applied to the expert input, unit combine weights;
     src/maxtext/layers/moe.py:752,902-906,1051-1053) or "gpt_oss" (router bias on the logits, per-expert biases and the
     clamped x * sigmoid(1.702 x) * (up + 1) activation; moe.py:617-637,841-853,2239-2242)."""
@@ -112,6 +112,12 @@ class RoutedMoE:
     # gemma4 (src/maxtext/layers/moe.py:639-645,744-763): combine weights are the soft-max probabilities of the chosen experts,
     # renormalised, times a learned scale per expert
     self.per_expert_scale = mb.vector("per_expert_scale", self.E, ("exp",), init="ones") if style == "gemma4" else None
+    # DeepSeek-V4 prefix layers (src/maxtext/layers/moe.py:442-455,729-739): experts are chosen by a fixed table indexed with the
+    # TOKEN ID ([vocab, k], stored as floats in the checkpoint, never trained); the router only supplies the combine weights
+    self.tid2eid = None
+    if hash_routing:
+      self.tid2eid = mb.table("tid2eid", (c.vocab_size, self.k), (None, None), init="zeros")
+      self.tid2eid.pdef.frozen = True
 
   # ---- routing
   def route(self, x2, B, S, ctx=None, gate_inputs=None):
@@ -130,7 +136,7 @@ class RoutedMoE:
       return wts, idx, self._aux(probs, idx, B, S, ctx)
     grouped = self.deepseek and c.n_routing_groups > 0 and c.topk_routing_group > 0
     func = (c.routed_score_func or "softmax") if self.deepseek else "softmax"
-    if (moe_ops.router_kernel_ok(logits, self.E, self.k) and not grouped and func in ("softmax", "sigmoid")
+    if (self.tid2eid is None and moe_ops.router_kernel_ok(logits, self.E, self.k) and not grouped and func in ("softmax", "sigmoid")
         and not bool(getattr(c, "use_random_routing", False))):
       # one launch: scores, top-k, routing weights (csrc/router_sm100.cu); the bias only steers the selection and is not trained
       bias = self.gate_bias.leaf() if self.gate_bias is not None else None
@@ -145,14 +151,21 @@ class RoutedMoE:
       lf = logits.float()
       scores = torch.softmax(lf, -1) if func == "softmax" else torch.sigmoid(lf) if func == "sigmoid" else lf
       sel = scores + self.gate_bias.leaf().float() if self.gate_bias is not None else scores
-      if c.n_routing_groups > 0 and c.topk_routing_group > 0:
+      if self.tid2eid is not None:
+        if ctx is None or ctx.tokens is None:
+          raise ValueError("hash routing needs the token ids of the batch")
+        sel = None
+      if sel is not None and c.n_routing_groups > 0 and c.topk_routing_group > 0:
         G = c.n_routing_groups
         grp = sel.view(-1, G, self.E // G)
         gscore = grp.topk(2, dim=-1).values.sum(-1) if self.gate_bias is not None else grp.max(-1).values
         gidx = gscore.topk(c.topk_routing_group, dim=-1).indices
         gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0).bool()
         sel = sel.masked_fill(~gmask[:, :, None].expand_as(grp).reshape(sel.shape), float("-inf"))
-      idx = sel.topk(self.k, dim=-1).indices
+      if sel is None:
+        idx = self.tid2eid.data.detach()[ctx.tokens.reshape(-1).long()].long().clamp_(0, self.E - 1)
+      else:
+        idx = sel.topk(self.k, dim=-1).indices
       wts = scores.gather(-1, idx)
       if func in ("sigmoid", "sqrtsoftplus"):
         wts = wts / (wts.sum(-1, keepdim=True) + 1e-20)
@@ -348,7 +361,7 @@ class Gemma4MoE:
 class RoutedAndSharedMoE:
   """Routed experts plus always-on shared experts (src/maxtext/layers/moe.py:3259-3371)."""
 
-  def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0", style: str = ""):
+  def __init__(self, b: Builder, config, name="DeepSeekMoeBlock_0", style: str = "", hash_routing: bool = False):
     mb = b.sub(name)
     self.shared_gate = None
     if style == "qwen3_next":
@@ -358,7 +371,7 @@ class RoutedAndSharedMoE:
       self.shared = MLP(mb, config, "shared_expert", hidden=config.moe_mlp_dim)
       self.shared_gate = mb.sub("shared_expert_gate").linear("kernel", (config.emb_dim,), (1,), ("embed", None))
       return
-    self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=(style == ""), style=style)
+    self.routed = RoutedMoE(mb, config, "MoeBlock_0", deepseek_style=(style == ""), style=style, hash_routing=hash_routing)
     self.shared = MLP(mb, config, "shared_experts", hidden=config.shared_experts * config.moe_mlp_dim) \
         if config.shared_experts > 0 else None
 

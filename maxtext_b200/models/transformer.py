@@ -105,7 +105,8 @@ class DecoderBlock:
     if plan.mlp == "moe":
       self.mlp = M.RoutedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
     elif plan.mlp == "moe_shared":
-      self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s, style=plan.moe_style)
+      hashed = layer_index is not None and layer_index < int(getattr(c, "first_num_hash_layers", 0) or 0) and plan.moe_style == ""
+      self.mlp = M.RoutedAndSharedMoE(b, c, plan.mlp_name + s, style=plan.moe_style, hash_routing=hashed)
     elif plan.mlp == "gemma4_moe":
       self.mlp = M.Gemma4MoE(b, c, plan.mlp_name + s)
     else:

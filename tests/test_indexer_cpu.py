@@ -89,3 +89,28 @@ def test_model_trains_and_the_indexer_learns_only_from_its_own_loss():
   eng3 = make_engine(cfg)
   ref0 = {p.name: p.data.clone() for u in eng3.store.units.values() for p in u.params if "indexer/wq_b" in p.name}
   assert any(not torch.allclose(p.data, ref0[p.name], atol=1e-5) for p in moved)
+
+
+def test_hash_routed_prefix_layers_pick_experts_from_the_token_table():
+  """`first_num_hash_layers`: the experts of a token come from a frozen [vocab, k] table; the router supplies the weights only."""
+  cfg = tiny_config("deepseek3-tiny", ["first_num_hash_layers=2", "first_num_dense_layers=0", "n_routing_groups=0", "topk_routing_group=0", "steps=3"])
+  eng = make_engine(cfg)
+  tabs = [p for u in eng.store.units.values() for p in u.params if p.name.endswith("tid2eid")]
+  assert len(tabs) == 2 and all(p.pdef.frozen and p.pdef.shape == (cfg.vocab_size, 2) for p in tabs)       # layers 0 and 1 only
+  table = (torch.arange(cfg.vocab_size)[:, None] * 3 + torch.tensor([0, 5])) % cfg.num_experts
+  for p in tabs:
+    eng.store.load_full(p.name, table.float())
+  eng.store.sync_compute_from_master()
+  moe = eng.model.layers[0].blocks[0].mlp.routed
+  batch = batch_of(cfg)
+  tokens = batch["inputs"]
+  ctx = eng.model.make_ctx(torch.arange(tokens.shape[1])[None].expand_as(tokens), None, "train", tokens)
+  x2 = torch.randn(tokens.numel(), cfg.emb_dim)
+  with torch.no_grad():
+    wts, idx, _ = moe.route(x2, tokens.shape[0], tokens.shape[1], ctx)
+  assert torch.equal(idx, table[tokens.reshape(-1).long()])
+  assert wts.shape == idx.shape and bool((wts > 0).all())
+  before = eng.store.full_master(tabs[0]).clone()
+  losses = [float(eng.train_step(batch)["learning/loss"]) for _ in range(3)]
+  assert all(math.isfinite(v) for v in losses) and losses[-1] < losses[0]
+  assert torch.equal(eng.store.full_master(tabs[0]), before)                                                 # the table is not trained
