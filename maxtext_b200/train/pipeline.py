@@ -48,8 +48,10 @@ class PipelineEngine(TrainEngine):
     # schedule a stage sends activations of later micro-batches forward while the wrap-around of earlier ones comes back from
     # the same peer, and the two sides issue those in different orders: on one communicator that dead-locks. Every directed
     # (source, destination) pair therefore gets a communicator of its own, separately for activations and for gradients.
+    # The plain schedule (one repeat) only ever moves activations one way and gradients the other, in the same order on both
+    # sides, and stays on the default group.
     self._p2p = {}
-    if dist.is_initialized() and dist.get_backend() == "nccl":
+    if dist.is_initialized() and dist.get_backend() == "nccl" and self.R > 1:
       seen = set()
       for r in range(mesh.world):                                  # collective: every rank creates every group, in one order
         ring = tuple(mesh.ranks_along(("stage",), r))

@@ -106,8 +106,6 @@ def _run_layout(world, overrides, tmp_path, tag):
 
 @pytest.mark.parametrize("layout,overrides", [
     ("pp2_gpipe", ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2"]),
-    ("pp2_circular", ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_pipeline_parallelism=2", "num_layers_per_pipeline_stage=1",
-                      "num_pipeline_microbatches=4"]),
     ("tensor_sequence2", ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_sequence_parallelism=2"]),
 ])
 def test_layouts_on_two_gpus_match_one_gpu(layout, overrides, tmp_path):
