@@ -69,7 +69,12 @@ class FileDataIterator:
     c = self.c = config
     pats = (c.hf_train_files or c.grain_train_files or c.dataset_path) if split == "train" else (c.hf_eval_files or c.grain_eval_files or c.dataset_path)
     self.files = _expand(pats)
-    if not self.files:
+    # dataset_type=hf with hf_path set: the HuggingFace `datasets` library opens the source as a STREAMING dataset
+    # (src/maxtext/input_pipeline/hf_data_processing.py:206-240 `load_dataset(hf_path, data_dir, data_files, split, streaming=True)`);
+    # rows arrive one at a time, nothing is materialised. hf_path is a builder ("json", "parquet", "text", "csv", "arrow") for
+    # local files or a hub name when the machine has network access.
+    self.hf_stream = c.dataset_type == "hf" and bool(str(getattr(c, "hf_path", "") or ""))
+    if not self.files and not self.hf_stream:
       raise FileNotFoundError(f"dataset_type={c.dataset_type}: no files match {pats!r}")
     self.columns = list(c.train_data_columns if split == "train" else c.eval_data_columns)
     self.column = self.columns[0]
@@ -91,6 +96,9 @@ class FileDataIterator:
     c = self.c
     shuffle = self.split == "train" and bool(getattr(c, "enable_data_shuffling", False))
     files = list(self.files)
+    if self.hf_stream:
+      yield from self._hf_examples(shuffle)
+      return
     if not shuffle:
       for f in files:
         yield from _read_examples(f, self.column)
@@ -111,6 +119,26 @@ class FileDataIterator:
           window, w_id = [], w_id + 1
     if window:
       yield from flush()
+
+  def _hf_examples(self, shuffle: bool):
+    """Rows of a streaming HuggingFace dataset in training order; the shuffle is the library's buffered one, seeded by
+    (data_shuffle_seed, epoch) so that every rank and a resumed run see the same order."""
+    import datasets
+    c = self.c
+    split = (c.hf_eval_split or "validation") if self.split != "train" else (getattr(c, "hf_train_split", "") or "train")
+    kw = dict(split=split, streaming=True)
+    if str(c.hf_data_dir or ""):
+      kw["data_dir"] = c.hf_data_dir
+    if self.files:
+      kw["data_files"] = list(self.files)
+    if str(getattr(c, "hf_name", "") or ""):
+      kw["name"] = c.hf_name
+    if str(c.hf_access_token or ""):
+      kw["token"] = c.hf_access_token
+    ds = datasets.load_dataset(c.hf_path, **kw)
+    if shuffle:
+      ds = ds.shuffle(seed=int(getattr(c, "data_shuffle_seed", 0) or 0) + self.epoch, buffer_size=int(getattr(c, "hf_shuffle_buffer_size", 0) or 4096))
+    yield from ds
 
   def _encode(self, ex):
     """Token arrays of one example: one array, or consecutive S+1 chunks of a pre-tokenized .npy file."""

@@ -317,3 +317,25 @@ def test_file_pipeline_reads_tfrecord_shards_and_prefetch_keeps_resume_exact(tmp
   rest = [b["inputs"] for b in it2]
   assert len(rest) == len(want) - 3 and all(torch.equal(a, b) for a, b in zip(rest, want[3:]))
   it.close(), it2.close()
+
+
+def test_streaming_huggingface_dataset_backend(tmp_path):
+  """dataset_type=hf with hf_path: rows come from `datasets` in streaming mode; same batches as the plain file reader, and
+  the buffered shuffle is reproducible across iterators (ranks, resumed runs)."""
+  import json
+  import pytest
+  import torch
+  pytest.importorskip("datasets")
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  p = tmp_path / "corpus.jsonl"
+  p.write_text("\n".join(json.dumps({"text": f"document {i} " + "word " * (2 + i % 5)}) for i in range(60)))
+  base = ["dataset_type=hf", f"hf_train_files={p}", "tokenizer_type=byte", "vocab_size=260", "max_target_length=32", "per_device_batch_size=2",
+          "packing=true", "num_epoch=1", "grain_worker_count=0"]
+  plain = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", base))]
+  stream = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", base + ["hf_path=json"]))]
+  assert len(plain) == len(stream) > 3 and all(torch.equal(a, b) for a, b in zip(plain, stream))
+  sh = base + ["hf_path=json", "enable_data_shuffling=true", "data_shuffle_seed=3"]
+  a = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", sh))]
+  b2 = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", sh))]
+  assert all(torch.equal(x, y) for x, y in zip(a, b2)) and not all(torch.equal(x, y) for x, y in zip(a, plain))
