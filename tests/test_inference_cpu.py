@@ -326,3 +326,33 @@ def test_mlperf_offline_harness_and_accuracy_log(tmp_path):
   with pytest.raises(ValueError):
     offline_mode.classify([{"tok_input_length": 99}], [(8, 1)], allow_skip=False)
   assert (out / "mlperf_log_summary.txt").read_text().startswith("=====")
+
+
+def test_grpc_front_end_streams_the_tokens_of_the_serving_loop():
+  pytest.importorskip("grpc")
+  from helpers import tiny_config
+  from maxtext_b200.inference import grpc_server as gs
+  from maxtext_b200.inference.maxengine import MaxEngine
+  from maxtext_b200.inference.maxengine_server import ServingLoop
+  # message codec round trip
+  assert gs.decode_request(gs.encode_request("héllo", None, 7)) == {"max_tokens": 7, "text": "héllo", "token_ids": None}
+  assert gs.decode_request(gs.encode_request(None, [1, 300, 70000], 3))["token_ids"] == [1, 300, 70000]
+  assert gs.decode_response(gs.encode_response("ab", [5, 260])) == {"text": "ab", "token_ids": [5, 260]}
+  cfg = tiny_config("llama3-8b", ["max_prefill_predict_length=16", "max_target_length=32", "tokenizer_type=byte", "vocab_size=260", "per_device_batch_size=2"])
+  eng = MaxEngine(cfg)
+  eng.load_params()
+  loop = ServingLoop(cfg, engine=eng).start()
+  server, port = gs.serve(loop, 0)
+  try:
+    cl = gs.Client(f"127.0.0.1:{port}")
+    assert cl.healthy()
+    chunks = list(cl.decode(text="hello", max_tokens=6))
+    ids = [t for c in chunks for t in c["token_ids"]]
+    want = loop.complete({"prompt": "hello", "max_tokens": 6})["choices"][0]["tokens"]
+    assert ids == want and 1 <= len(chunks) <= 6
+    ids2 = [t for c in cl.decode(token_ids=loop.tok.encode("hello", add_bos=bool(cfg.add_bos)), max_tokens=6) for t in c["token_ids"]]
+    assert ids2 == want
+    cl.close()
+  finally:
+    server.stop(0)
+    loop.stop()
