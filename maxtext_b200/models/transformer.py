@@ -297,10 +297,10 @@ class Transformer:
     if bool(getattr(c, "use_multimodal", False)) and self.has_embed:
       kind = getattr(c, "vision_encoder_block", "") or c.decoder_block
       qwen_vl = kind in ("qwen3", "qwen3_moe", "qwen3_5", "qwen3_next", "qwen3_vl", "qwen3_omni")
-      if kind not in ("gemma3", "llama4") and not qwen_vl:
-        raise NotImplementedError("use_multimodal is implemented for the Gemma-3, Llama-4 and Qwen3-VL / Omni vision towers")
-      from .vision import Gemma3Vision, Llama4Vision, Qwen3VLVision
-      self.vision = (Gemma3Vision if kind == "gemma3" else Llama4Vision if kind == "llama4" else Qwen3VLVision)(c, self.par)
+      if kind not in ("gemma3", "gemma4", "llama4") and not qwen_vl:
+        raise NotImplementedError("use_multimodal is implemented for the Gemma-3, Gemma-4, Llama-4 and Qwen3-VL / Omni vision towers")
+      from .vision import Gemma3Vision, Gemma4Vision, Llama4Vision, Qwen3VLVision
+      self.vision = {"gemma3": Gemma3Vision, "gemma4": Gemma4Vision, "llama4": Llama4Vision}.get(kind, Qwen3VLVision)(c, self.par)
       self.vision_params = self.vision.params
       if bool(getattr(c, "freeze_vision_encoder_params", True)):
         for p in self.vision_params:
@@ -413,7 +413,7 @@ class Transformer:
       from ..multimodal.utils import bidirectional_block_mask
       mm = self.encode_images(images, image_mask)
       ctx.deepstack = self._deepstack
-      if self.vision.__class__.__name__ == "Gemma3Vision":      # Llama-4 keeps plain causal attention over image tokens
+      if self.vision.__class__.__name__ in ("Gemma3Vision", "Gemma4Vision"):      # Llama-4 keeps plain causal attention over image tokens
         ctx.bidir = bidirectional_block_mask(mm[1])
     x = self.embed(tokens, positions, mm)
     for i, layer in enumerate(self.layers):

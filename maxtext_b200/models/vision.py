@@ -381,3 +381,132 @@ class Qwen3VLVision:
     out = self.merger(x)
     self.deepstack = [t.view(B, N, t.shape[1], -1) for t in deep]
     return out.view(B, N, out.shape[1], -1)
+
+
+# =============================================================================================== Gemma-4
+class _Gemma4EncoderBlock:
+  """Sandwich-normed encoder block of the Gemma-4 tower (src/maxtext/models/gemma4_vision.py:422-533): RMS norms before and after
+  both branches, q / k norms with scale and a scale-free v norm, no 1/sqrt(d) factor, a 2-D rotary embedding whose two halves of
+  the head rotate by the patch's x and y coordinate, and a gated GELU MLP. The input / output clipping of the published
+  checkpoints' linears is not applied."""
+
+  def __init__(self, b: L.Builder, c, i: int):
+    d, h = c.hidden_size_for_vit, c.num_attention_heads_for_vit
+    self.h, self.dh, self.eps = h, d // h, c.normalization_layer_epsilon
+    eb = b.sub(f"layers_{i}")
+    mk = lambda n: L.Norm(eb, n, d, self.eps)  # noqa: E731
+    self.n_in, self.n_post_attn, self.n_pre_ffw, self.n_post_ffw = mk("pre_attention_norm"), mk("post_attention_norm"), mk("pre_ffw_norm"), mk("post_ffw_norm")
+    ab = eb.sub("attention")
+    lin = lambda n: ab.sub(n).linear("kernel", (d,), (h, self.dh), ("embed", "heads", "kv"))  # noqa: E731
+    self.q, self.k, self.v = lin("query"), lin("key"), lin("value")
+    self.o = ab.sub("out").linear("kernel", (h, self.dh), (d,), ("heads", "kv", "embed"))
+    self.qn = L.Norm(ab, "query_norm", self.dh, self.eps, axes=("norm",))
+    self.kn = L.Norm(ab, "key_norm", self.dh, self.eps, axes=("norm",))
+    f = c.intermediate_size_for_vit
+    mb = eb.sub("mlp")
+    self.w0 = mb.sub("wi_0").linear("kernel", (d,), (f,), ("embed", "mlp"))
+    self.w1 = mb.sub("wi_1").linear("kernel", (d,), (f,), ("embed", "mlp"))
+    self.wo = mb.sub("wo").linear("kernel", (f,), (d,), ("mlp", "embed"))
+
+  def __call__(self, x, cos, sin):
+    M, S, _ = x.shape
+    y = self.n_in(x)
+    q = self.qn(F.linear(y, self.q).view(M, S, self.h, self.dh))
+    k = self.kn(F.linear(y, self.k).view(M, S, self.h, self.dh))
+    v = F.linear(y, self.v).view(M, S, self.h, self.dh)
+    vf = v.float()
+    v = (vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + self.eps)).to(v.dtype)
+
+    def rot(t):                                     # each half of the head is rotated (rotate-half inside the half) by its own axis
+      tf = t.float()
+      a, b2 = tf[..., :self.dh // 2], tf[..., self.dh // 2:]
+
+      def rh(z):
+        q4 = z.shape[-1] // 2
+        return torch.cat([-z[..., q4:], z[..., :q4]], -1)
+      out = torch.cat([a, b2], -1) * cos + torch.cat([rh(a), rh(b2)], -1) * sin
+      return out.to(t.dtype)
+    a = ref.attention(rot(q), rot(k), v, None, 1.0).to(x.dtype)
+    x = x + self.n_post_attn(F.linear(a.reshape(M, S, -1), self.o))
+    y = self.n_pre_ffw(x)
+    g = tF.gelu(F.linear(y, self.w0).float(), approximate="tanh").to(x.dtype) * F.linear(y, self.w1)
+    return x + self.n_post_ffw(F.linear(g, self.wo))
+
+
+class Gemma4Vision:
+  """Vision tower of Gemma-4 (src/maxtext/models/gemma4_vision.py:88-650): a bias-free linear map of every patch_size^2 x 3
+  patch, learned x- and y-position tables that are ADDED (one row per coordinate), `num_hidden_layers_for_vit` encoder blocks,
+  k x k average pooling of the patch grid down to `vision_output_length` soft tokens, a sqrt(width) scale, a scale-free RMS
+  norm and the projection to the language model's width.
+
+  `__call__(images [B, N, 3, H, W]) -> [B, N, K, emb_dim]`, images already normalised to [-1, 1]."""
+
+  def __init__(self, config, par: dict):
+    c = self.c = config
+    b = L.Builder(c, "vision", None, None, **par)
+    vb = b.sub("vision_encoder")
+    self.P, self.d = int(c.patch_size_for_vit), int(c.hidden_size_for_vit)
+    self.patch = vb.sub("entry", "input_projection").linear("kernel", (self.P, self.P, int(c.num_channels_for_vit)), (self.d,), (None, None, None, "embed"))
+    self.pos_size = int(c.num_position_embeddings_for_vit)
+    self.pos = vb.sub("entry").table("pos_emb", (2, self.pos_size, self.d), (None, None, "embed"), init="fan_in_normal")
+    self.blocks = [_Gemma4EncoderBlock(vb, c, i) for i in range(c.num_hidden_layers_for_vit)]
+    pb = b.sub("vision_projector")
+    self.proj = pb.sub("projection").linear("kernel", (self.d,), (c.emb_dim,), ("embed", "embed_out"))
+    self.params = b.params
+
+  def _grid(self, H: int, W: int, device):
+    gh, gw = H // self.P, W // self.P
+    ys, xs = torch.meshgrid(torch.arange(gh, device=device), torch.arange(gw, device=device), indexing="ij")
+    return gh, gw, torch.stack([xs.reshape(-1), ys.reshape(-1)], -1)          # (x, y) per patch, row-major
+
+  def patches(self, images: torch.Tensor) -> torch.Tensor:
+    """[M, C, H, W] -> [M, gh*gw, P*P*C], features ordered (row, column, channel) like the reference kernel."""
+    M, C, H, W = images.shape
+    P = self.P
+    gh, gw = H // P, W // P
+    return images.view(M, C, gh, P, gw, P).permute(0, 2, 4, 3, 5, 1).reshape(M, gh * gw, P * P * C)
+
+  def rope(self, xy):
+    """cos / sin [S, 1, head_dim]: the first half of the head carries the x angles, the second the y angles."""
+    dh = self.d // int(self.c.num_attention_heads_for_vit)
+    sp = dh // 2
+    inv = 1.0 / (float(self.c.rope_theta_for_vit) ** (torch.arange(0, sp, 2, device=xy.device, dtype=torch.float32) / sp))
+    parts = []
+    for i in range(2):
+      f = xy[:, i:i + 1].float() * inv
+      parts.append(torch.cat([f, f], -1))
+    ang = torch.cat(parts, -1)[:, None]
+    return ang.cos(), ang.sin()
+
+  def encode(self, patches: torch.Tensor, xy: torch.Tensor, out_len: int) -> torch.Tensor:
+    """patches [M, S, P*P*C] with coordinates xy [S, 2] -> pooled soft tokens [M, out_len, d] (before the projector)."""
+    dt = self.patch.data.dtype
+    x = F.linear(patches.to(dt), self.patch)
+    tab = self.pos.leaf().to(dt)
+    x = x + tab[0][xy[:, 0]] + tab[1][xy[:, 1]]
+    cos, sin = self.rope(xy)
+    for blk in self.blocks:
+      x = blk(x, cos, sin)
+    S = x.shape[1]
+    if S != out_len:
+      k = int(math.isqrt(S // out_len))
+      assert k * k * out_len == S, f"cannot pool {S} patches to {out_len} tokens"
+      max_x = int(xy[:, 0].max()) + 1
+      cell = (xy[:, 0] // k) + (max_x // k) * (xy[:, 1] // k)
+      w = tF.one_hot(cell, out_len).float() / (k * k)                                   # [S, out_len]
+      x = torch.einsum("sl,msd->mld", w, x.float()).to(dt)
+    return x * math.sqrt(self.d)
+
+  def project(self, soft: torch.Tensor) -> torch.Tensor:
+    sf = soft.float()
+    normed = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + self.c.normalization_layer_epsilon)).to(soft.dtype)
+    return F.linear(normed, self.proj)
+
+  def __call__(self, images: torch.Tensor) -> torch.Tensor:
+    B, N = images.shape[:2]
+    H, W = images.shape[-2:]
+    gh, gw, xy = self._grid(H, W, images.device)
+    out_len = int(self.c.vision_output_length) if int(self.c.vision_output_length) > 0 else gh * gw
+    soft = self.encode(self.patches(images.reshape(B * N, *images.shape[2:])), xy, out_len)
+    out = self.project(soft)
+    return out.view(B, N, out.shape[1], -1)

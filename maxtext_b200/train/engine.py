@@ -340,7 +340,7 @@ class TrainEngine:
     for u in units:
       self.store.release_full(u)
     ctx.deepstack = getattr(self.model, "_deepstack", None)
-    if self.model.vision.__class__.__name__ == "Gemma3Vision":    # Llama-4 keeps plain causal attention over image tokens
+    if self.model.vision.__class__.__name__ in ("Gemma3Vision", "Gemma4Vision"):    # Llama-4 keeps plain causal attention over image tokens
       ctx.bidir = bidirectional_block_mask(mm[1])
     return mm
 

@@ -100,3 +100,55 @@ def test_logits_match_huggingface(moe):
     got = model.forward(ids)
   err = float((got - want).abs().max())
   assert err < 2e-3 * max(1.0, float(want.abs().max())), err
+
+
+def test_vision_tower_matches_huggingface():
+  pytest.importorskip("transformers")
+  from transformers.models.gemma4.configuration_gemma4 import Gemma4VisionConfig
+  from transformers.models.gemma4.modeling_gemma4 import Gemma4VisionModel
+  from maxtext_b200.models.vision import Gemma4Vision
+  d, h, f, P, depth = 32, 2, 48, 4, 2
+  hf_cfg = Gemma4VisionConfig(hidden_size=d, intermediate_size=f, num_hidden_layers=depth, num_attention_heads=h, num_key_value_heads=h, head_dim=d // h,
+                              patch_size=P, position_embedding_size=16, pooling_kernel_size=2, standardize=False, use_clipped_linears=False,
+                              rope_parameters={"rope_type": "default", "rope_theta": 100.0}, hidden_activation="gelu_pytorch_tanh", rms_norm_eps=1e-6)
+  hf_cfg._attn_implementation = "eager"
+  torch.manual_seed(0)
+  hf = Gemma4VisionModel(hf_cfg).float().eval()
+  with torch.no_grad():
+    for n, p in hf.named_parameters():
+      p.copy_(torch.randn_like(p) * 0.3 + (1.0 if "norm" in n else 0.0))
+  cfg = tiny_config("gemma4-26b", ["use_multimodal=true", f"hidden_size_for_vit={d}", f"num_attention_heads_for_vit={h}", f"intermediate_size_for_vit={f}",
+                                   f"num_hidden_layers_for_vit={depth}", f"patch_size_for_vit={P}", "num_position_embeddings_for_vit=16", "rope_theta_for_vit=100",
+                                   "vision_output_length=6", "image_size_for_vit=[16,24]", "num_experts=1", "tokenizer_type=byte"])
+  tower = Gemma4Vision(cfg, {})
+  sd = {k: v.detach().float() for k, v in hf.state_dict().items()}
+  Pm = {p.name: p for p in tower.params}
+
+  def put(name, t):
+    assert tuple(Pm[name].shape) == tuple(t.shape), (name, tuple(Pm[name].shape), tuple(t.shape))
+    Pm[name].data = t.clone()
+  put("vision_encoder/entry/input_projection/kernel", sd["patch_embedder.input_proj.weight"])
+  put("vision_encoder/entry/pos_emb", sd["patch_embedder.position_embedding_table"])
+  for i in range(depth):
+    a, b = f"vision_encoder/layers_{i}/", f"encoder.layers.{i}."
+    for ours, theirs in (("pre_attention_norm", "input_layernorm"), ("post_attention_norm", "post_attention_layernorm"),
+                         ("pre_ffw_norm", "pre_feedforward_layernorm"), ("post_ffw_norm", "post_feedforward_layernorm")):
+      put(a + ours + "/scale", sd[b + theirs + ".weight"])
+    for ours, theirs in (("query", "q_proj"), ("key", "k_proj"), ("value", "v_proj"), ("out", "o_proj")):
+      put(a + f"attention/{ours}/kernel", sd[b + f"self_attn.{theirs}.linear.weight"])
+    put(a + "attention/query_norm/scale", sd[b + "self_attn.q_norm.weight"])
+    put(a + "attention/key_norm/scale", sd[b + "self_attn.k_norm.weight"])
+    for ours, theirs in (("wi_0", "gate_proj"), ("wi_1", "up_proj"), ("wo", "down_proj")):
+      put(a + f"mlp/{ours}/kernel", sd[b + f"mlp.{theirs}.linear.weight"])
+  Pm["vision_projector/projection/kernel"].data = torch.randn(Pm["vision_projector/projection/kernel"].shape) * 0.1
+  H, W = 16, 24                                   # 4 x 6 patches, pooled 2 x 2 -> 6 soft tokens
+  images = torch.rand(2, 3, H, W) * 2 - 1         # already in [-1, 1]
+  with torch.no_grad():
+    gh, gw, xy = tower._grid(H, W, images.device)
+    patches = tower.patches(images)
+    got = tower.encode(patches, xy, 6)
+    # HuggingFace takes pixels in [0, 1] (it applies 2 (x - 0.5) itself) and one (x, y) pair per patch
+    want = hf(pixel_values=(patches + 1) / 2, pixel_position_ids=xy[None].expand(2, -1, -1)).last_hidden_state.view(2, 6, d)
+    out = tower(images[None])
+  assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+  assert out.shape == (1, 2, 6, cfg.emb_dim) and torch.isfinite(out).all()
