@@ -48,7 +48,40 @@ def build_host_extension(verbose: bool = True):
                             with_cuda=False, verbose=verbose)
 
 
+HOST_ASAN_BUILD_DIR = os.path.join(HERE, "build_host_asan")
+HOST_ASAN_EXT_NAME = "maxtext_b200_host_asan"
+
+
+def build_host_extension_sanitized(verbose: bool = True):
+  """The same host library under AddressSanitizer + UndefinedBehaviorSanitizer (`--sanitize`), as a module of its own
+  (`csrc/build_host_asan/maxtext_b200_host_asan.so`). It must be loaded into a Python that has libasan pre-loaded
+  (LD_PRELOAD=$(g++ -print-file-name=libasan.so), ASAN_OPTIONS=detect_leaks=0): `tests/test_native_loader_cpu.py` does that in
+  a child process."""
+  import subprocess
+  from torch.utils import cpp_extension
+  os.makedirs(HOST_ASAN_BUILD_DIR, exist_ok=True)
+  # the sanitizer runtimes ship with one particular compiler installation: build with a g++ that can find its own libasan
+  for cxx in (os.environ.get("CXX", ""), "g++", "/usr/bin/g++"):
+    if not cxx:
+      continue
+    try:
+      lib = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True, check=False).stdout.strip()
+    except OSError:
+      continue
+    if lib and os.path.isfile(lib):
+      os.environ["CXX"] = cxx
+      break
+  flags = ["-O1", "-g", "-std=c++17", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined"]
+  return cpp_extension.load(name=HOST_ASAN_EXT_NAME, sources=sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp"))), extra_cflags=flags,
+                            extra_ldflags=["-lpthread", "-fsanitize=address,undefined"], build_directory=HOST_ASAN_BUILD_DIR,
+                            with_cuda=False, verbose=verbose)
+
+
 if __name__ == "__main__":
+  if "--sanitize" in sys.argv:
+    build_host_extension_sanitized(verbose="-q" not in sys.argv)
+    print("built", os.path.join(HOST_ASAN_BUILD_DIR, HOST_ASAN_EXT_NAME + ".so"))
+    sys.exit(0)
   build_host_extension(verbose="-q" not in sys.argv)
   build_extension(verbose="-q" not in sys.argv)
   print("built", os.path.join(BUILD_DIR, EXT_NAME + ".so"))

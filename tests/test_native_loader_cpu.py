@@ -108,3 +108,42 @@ def test_train_cli_reads_token_files_through_the_native_loader(lib, tmp_path):
       "run_name=tok", "learning_rate=3e-3"]
   eng, hist = T.main(["train", BASE_YML] + args)
   assert len(hist) == 4 and hist[-1]["learning/loss"] < hist[0]["learning/loss"] + 0.5 and all(np.isfinite(h["learning/loss"]) for h in hist)
+
+
+def test_loader_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+  """The host library rebuilt with -fsanitize=address,undefined and driven in a child Python that pre-loads libasan: batches,
+  epoch wrap-around, seek and shutdown with a full queue must not trip either sanitizer."""
+  import os
+  import subprocess
+  import sys
+  asan = subprocess.run(["g++", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+  if not asan or not os.path.isfile(asan):
+    pytest.skip("libasan is not installed")
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  rng = np.random.default_rng(0)
+  toks = np.concatenate([np.asarray(d, dtype=np.int32) for d in _docs(rng, 40)])
+  f = tmp_path / "a.bin"
+  toks.tofile(f)
+  code = f"""
+import sys, torch
+sys.path.insert(0, {root!r})
+from maxtext_b200.csrc import build
+m = build.build_host_extension_sanitized(verbose=False)
+L = m.TokenLoader([{str(f)!r}], 16, 2, {EOS}, 0, 1, 3)
+bufs = [torch.zeros(2, 16, dtype=torch.int32) for _ in range(4)]
+seen = []
+for i in range(40):                      # several passes over the file
+  L.next(*bufs)
+  seen.append(bufs[0].clone())
+st = L.state()
+L.next(*bufs); a = bufs[0].clone()
+L.seek(list(st))
+L.next(*bufs)
+assert torch.equal(a, bufs[0]), "seek did not reproduce the batch"
+del L                                    # the worker is blocked on a full queue: the destructor must wake and join it
+print("sanitized-ok")
+"""
+  env = dict(os.environ, LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1", CUDA_VISIBLE_DEVICES="")
+  r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=900)
+  assert r.returncode == 0 and "sanitized-ok" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])
+  assert "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr, r.stderr[-3000:]
