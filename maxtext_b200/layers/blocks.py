@@ -367,7 +367,7 @@ class Attention:
       B, S, _ = x.shape                      # sequence parallelism: the gathered length
     packed, sep = self._project(x, ctx, tp_rt if fuse_in else None)
     moba = bool(getattr(self.config, "moba", False)) and ctx.cache is None and ctx.cp_size == 1
-    plain = (not self.qk_norm and self.vn is None and not self.share_kv and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and not moba and ctx.cache is None and ctx.cp_size == 1
+    plain = (ctx.positions3 is None and not self.qk_norm and self.vn is None and not self.share_kv and self.sinks is None and self.rotary_dim is None and not self.gated and ctx.bidir is None and not moba and ctx.cache is None and ctx.cp_size == 1
              and not self.l2_qk_norm and not self.temperature_tuning and not (self.chunk and S > self.chunk))
     saved_ctx = ctx.reuse("context")
     if saved_ctx is not None and packed is not None and plain:
@@ -392,7 +392,12 @@ class Attention:
         q, k = self.qn(q), self.kn(k)
       if self.vn is not None:
         v = self.vn(v)
-      if self.use_rope:
+      if self.use_rope and ctx.positions3 is not None and bool(getattr(self.config, "use_mrope", False)):
+        # multi-axis rotary embedding: image tokens carry (t, h, w) positions (src/maxtext/layers/embeddings.py:1791-1948)
+        sec = list(self.config.mrope_section)
+        q = ref.apply_mrope(q, ctx.positions3, self.inv_ts, sec, self.rotary_dim)
+        k = ref.apply_mrope(k, ctx.positions3, self.inv_ts, sec, self.rotary_dim)
+      elif self.use_rope:
         q = F.rope(q, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
         k = F.rope(k, ctx.positions, self.inv_ts, self.interleaved, self.rotary_dim)
       if self.l2_qk_norm:

@@ -70,6 +70,7 @@ class LayerCtx:
   dropout_seed: int | None = None    # training with dropout_rate > 0: base of the per-site mask seeds of this micro-batch
   sp: bool = False                   # residual stream split along the sequence over the tensor ranks (parallel.sequence_parallel)
   bidir: torch.Tensor | None = None  # [B, 1, S, S] extra allowed (query, key) pairs: tokens of one image see each other
+  positions3: torch.Tensor | None = None  # [B, S, 3] (temporal, height, width) positions of a multimodal prompt (`use_mrope`)
   deepstack: tuple | None = None     # (image mask [B, S], [features [B, N*K, D], ...]): feature i is added after decoder layer i
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
 

@@ -401,13 +401,14 @@ class Transformer:
 
   # ------------------------------------------------------------------ plain forward (eval / inference / tests)
   @torch.no_grad()
-  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None, images=None, image_mask=None):
+  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None, images=None, image_mask=None, positions3=None):
     """Full logits [B,S,V] in fp32; every unit must be resident (single rank or gathered by the caller).
     `images` [B, N, 3, H, W] with `image_mask` [B, S] (True at the soft-token positions) makes the prompt multimodal."""
     B, S = tokens.shape
     if positions is None:
       positions = torch.arange(S, device=tokens.device)[None].expand(B, S)
     ctx = self.make_ctx(positions, segment_ids, mode, tokens)
+    ctx.positions3 = positions3.to(tokens.device) if positions3 is not None else None
     mm = None
     if images is not None:
       from ..multimodal.utils import bidirectional_block_mask

@@ -90,3 +90,30 @@ def prepare(tokens: list[int], images, config):
   mask = [t == tk["image_pad"] for t in out]
   assert sum(mask) == K * len(images)
   return torch.tensor(out), torch.tensor(mask), pix
+
+
+def rope_index(image_mask, grids) -> torch.Tensor:
+  """(temporal, height, width) positions of a prompt with images (`use_mrope`; src/maxtext/multimodal/processor_qwen3_omni.py:1004-1288).
+
+  image_mask [S] marks the soft-token positions; `grids` lists (rows, columns) of merged tokens per image, in prompt order.
+  Text tokens count up with the same number on all three axes. The tokens of an image all carry the temporal position at
+  which the image starts, their row and column added to it on the other two axes; the text after an image continues at
+  start + max(rows, columns)."""
+  m = [bool(v) for v in (image_mask.tolist() if hasattr(image_mask, "tolist") else image_mask)]
+  out, cur, i, g = [], 0, 0, 0
+  while i < len(m):
+    if not m[i]:
+      out.append((cur, cur, cur))
+      cur += 1
+      i += 1
+      continue
+    rows, cols = grids[g]
+    g += 1
+    n = rows * cols
+    assert all(m[i:i + n]) and len(m[i:i + n]) == n, "an image's soft tokens must be one contiguous run of rows * columns positions"
+    for r in range(rows):
+      for c in range(cols):
+        out.append((cur, cur + r, cur + c))
+    cur += max(rows, cols)
+    i += n
+  return torch.tensor(out, dtype=torch.long)

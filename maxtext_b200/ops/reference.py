@@ -108,6 +108,31 @@ def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_ts: torch.Tensor, i
   return torch.cat([out, rest], dim=-1) if rest.shape[-1] else out
 
 
+def mrope_axis_of_frequency(n_freq: int, sections) -> torch.Tensor:
+  """Which position axis (0 temporal, 1 height, 2 width) drives each of the n_freq rotary frequencies under the interleaved
+  multi-axis layout of Qwen3-VL / Omni (src/maxtext/layers/embeddings.py:1861-1886): temporal everywhere, except that indices
+  1, 4, 7, ... below 3 * sections[1] use the height and indices 2, 5, 8, ... below 3 * sections[2] the width."""
+  axis = torch.zeros(n_freq, dtype=torch.long)
+  axis[1:3 * int(sections[1]):3] = 1
+  axis[2:3 * int(sections[2]):3] = 2
+  return axis
+
+
+def apply_mrope(x: torch.Tensor, positions3: torch.Tensor, inv_ts: torch.Tensor, sections, rotary_dim: int | None = None) -> torch.Tensor:
+  """Rotate-half rotary embedding whose angle for frequency i is positions3[b, s, axis(i)] * inv_ts[i]; x [B,S,H,Dh],
+  positions3 [B,S,3] (text tokens carry the same number on all three axes, which makes this the ordinary embedding)."""
+  d = x.shape[-1] if rotary_dim is None else rotary_dim
+  xr, rest = x[..., :d], x[..., d:]
+  axis = mrope_axis_of_frequency(d // 2, sections).to(x.device)
+  pos = positions3.float()[..., axis]                                     # [B, S, d/2]
+  ang = (pos * inv_ts.to(x.device).float())[:, :, None, :]
+  sin, cos = torch.sin(ang), torch.cos(ang)
+  xf = xr.float()
+  x1, x2 = xf[..., : d // 2], xf[..., d // 2:]
+  out = torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+  return torch.cat([out, rest], dim=-1) if rest.shape[-1] else out
+
+
 # ----------------------------------------------------------------------------- activations
 _ACTS = {
     "silu": F.silu, "swish": F.silu, "gelu": lambda t: F.gelu(t, approximate="tanh"), "gelu_exact": F.gelu,

@@ -144,6 +144,8 @@ class TrainEngine:
 
     n_units = len(self._units)
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    p3 = batch.get("inputs_position3")          # [B, S, 3] multi-axis rotary positions of multimodal rows (`use_mrope`)
+    ctx.positions3 = p3.to(self.device) if p3 is not None else None
     if float(c.dropout_rate) > 0 and bool(c.enable_dropout) and compute_grads:
       # one seed per micro-batch and data shard; tensor ranks of a shard share it (they hold the same activations)
       shard = self.mesh.axis_index(("data", "fsdp", "fsdp_transpose", "expert", "context", "context_usp_ulysses")) if self.mesh is not None else 0
@@ -609,6 +611,8 @@ class TrainEngine:
     seg = batch.get("inputs_segmentation")
     seg = seg.to(self.device) if seg is not None else None
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    p3 = batch.get("inputs_position3")          # [B, S, 3] multi-axis rotary positions of multimodal rows (`use_mrope`)
+    ctx.positions3 = p3.to(self.device) if p3 is not None else None
     for i in range(len(self._units)):
       self._gather(i, async_op=False)
     x = model.embed(tokens, positions)

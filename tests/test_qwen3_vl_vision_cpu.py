@@ -117,3 +117,44 @@ def test_processor_resizes_to_the_patch_grid_and_expands_placeholders():
   ids2, mask2, _ = pq.prepare([5, 9], [img, img], cfg)                      # no placeholder in the prompt: images are appended
   assert int(mask2.sum()) == 2 * K
   assert pq.special_tokens("qwen3.5-35b-a3b")["image_pad"] == 248056
+
+
+def test_multi_axis_rotary_positions_and_angles_match_huggingface():
+  pytest.importorskip("transformers")
+  from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLTextConfig
+  from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLTextRotaryEmbedding, apply_rotary_pos_emb
+  from maxtext_b200.multimodal.processor_qwen3 import rope_index
+  from maxtext_b200.ops import reference as ref
+  # positions: 3 text tokens, a 2 x 3 image, 2 text tokens
+  mask = [False] * 3 + [True] * 6 + [False] * 2
+  p3 = rope_index(mask, [(2, 3)])
+  assert p3.tolist() == [[0, 0, 0], [1, 1, 1], [2, 2, 2],
+                         [3, 3, 3], [3, 3, 4], [3, 3, 5], [3, 4, 3], [3, 4, 4], [3, 4, 5],
+                         [6, 6, 6], [7, 7, 7]]
+  # angles: against the HuggingFace rotary module with the same sections
+  D, sec = 32, [6, 5, 5]
+  hf_cfg = Qwen3VLTextConfig(hidden_size=64, num_attention_heads=2, num_key_value_heads=2, head_dim=D, num_hidden_layers=1, intermediate_size=64, vocab_size=64,
+                             rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": sec, "mrope_interleaved": True})
+  rot = Qwen3VLTextRotaryEmbedding(hf_cfg)
+  torch.manual_seed(0)
+  x = torch.randn(1, len(mask), 2, D)
+  pos_hf = p3.t()[:, None, :]                                              # [3, batch, seq]
+  cos, sin = rot(x, pos_hf)
+  want, _ = apply_rotary_pos_emb(x.transpose(1, 2), x.transpose(1, 2), cos, sin)
+  inv = ref.rope_inv_timescale(D, 1, 10000.0)
+  got = ref.apply_mrope(x, p3[None], inv, sec)
+  assert torch.allclose(got, want.transpose(1, 2), atol=1e-5)
+  # text-only positions reduce to the ordinary embedding
+  p = torch.arange(11)[None]
+  assert torch.allclose(ref.apply_mrope(x, p[..., None].expand(-1, -1, 3), inv, sec), ref.apply_rope(x, p, inv, False), atol=1e-6)
+  # and the model takes them: logits change when the image positions are supplied
+  from maxtext_b200.models.transformer import Transformer
+  cfg = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=64", "mrope_section=[4,2,2]"])
+  model = Transformer(cfg, None, torch.device("cpu"))
+  model.store.initialize(seed=0)
+  tokens = torch.randint(1, 200, (1, 11))
+  with torch.no_grad():
+    a = model.forward(tokens)
+    b = model.forward(tokens, positions3=p3[None])
+    c = model.forward(tokens, positions3=torch.arange(11)[None, :, None].expand(-1, -1, 3))
+  assert torch.allclose(a, c, atol=1e-4) and not torch.allclose(a, b, atol=1e-4)
