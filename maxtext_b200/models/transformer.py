@@ -305,6 +305,15 @@ class Transformer:
       if bool(getattr(c, "freeze_vision_encoder_params", True)):
         for p in self.vision_params:
           p.pdef.frozen = True
+    # Qwen3-Omni audio tower (frozen with the vision tower)
+    self.audio, self.audio_params = None, []
+    if bool(getattr(c, "use_multimodal", False)) and bool(getattr(c, "use_audio", False)) and self.has_embed:
+      from .audio import Qwen3OmniAudio
+      self.audio = Qwen3OmniAudio(c, self.par)
+      self.audio_params = self.audio.params
+      if bool(getattr(c, "freeze_vision_encoder_params", True)):
+        for p in self.audio_params:
+          p.pdef.frozen = True
     if L.lora_spec(c) is not None:
       # LoRA fine-tuning: everything but the adapters keeps its value (no gradient, no weight decay)
       for p in self.all_params():
@@ -333,6 +342,7 @@ class Transformer:
     out.extend(self.mtp_params)
     out.extend(self.head_params)
     out.extend(self.vision_params)
+    out.extend(self.audio_params)
     return out
 
   def units_in_order(self) -> list[str]:
@@ -365,12 +375,23 @@ class Transformer:
     self._deepstack = (mask, [d.reshape(d.shape[0], -1, d.shape[-1]) for d in deep]) if deep else None
     return soft.reshape(soft.shape[0], -1, soft.shape[-1]), mask
 
+  def encode_audio(self, audio, audio_mask):
+    """audio: [B, mel, frames] or a list of [mel, frames_i] clips (one per sequence) -> (soft tokens [B, K, D], mask [B, S]);
+    shorter clips are padded with zero rows that no mask position reaches."""
+    dev = self.embedding.data.device
+    clips = [self.audio(a.to(dev)) for a in audio]
+    K = max(x.shape[0] for x in clips)
+    soft = torch.stack([torch.nn.functional.pad(x, (0, 0, 0, K - x.shape[0])) for x in clips])
+    return soft, audio_mask.to(dev).bool()
+
   def embed(self, tokens, positions, mm=None):
+    """mm: (soft tokens, mask) of one modality, or a list of such pairs (images, audio) merged one after the other."""
     c = self.config
     x = F.embedding(tokens, self.embedding)
     if mm is not None:
       from ..multimodal.utils import merge_mm_embeddings
-      x = merge_mm_embeddings(x, mm[0], mm[1])
+      for soft, mask in ([mm] if isinstance(mm, tuple) else mm):
+        x = merge_mm_embeddings(x, soft, mask)
     if self.family.scale_embedding:
       x = (x.float() * math.sqrt(c.emb_dim)).to(x.dtype)
     if bool(getattr(c, "use_untrainable_positional_embedding", False)):
@@ -401,9 +422,11 @@ class Transformer:
 
   # ------------------------------------------------------------------ plain forward (eval / inference / tests)
   @torch.no_grad()
-  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None, images=None, image_mask=None, positions3=None):
+  def forward(self, tokens, positions=None, segment_ids=None, mode="train", caches=None, images=None, image_mask=None, positions3=None,
+              audio=None, audio_mask=None):
     """Full logits [B,S,V] in fp32; every unit must be resident (single rank or gathered by the caller).
-    `images` [B, N, 3, H, W] with `image_mask` [B, S] (True at the soft-token positions) makes the prompt multimodal."""
+    `images` [B, N, 3, H, W] with `image_mask` [B, S] (True at the soft-token positions) makes the prompt multimodal;
+    `audio` (mel spectrograms, one clip per sequence) with `audio_mask` [B, S] does the same for the audio tower."""
     B, S = tokens.shape
     if positions is None:
       positions = torch.arange(S, device=tokens.device)[None].expand(B, S)
@@ -416,6 +439,9 @@ class Transformer:
       ctx.deepstack = self._deepstack
       if self.vision.__class__.__name__ in ("Gemma3Vision", "Gemma4Vision"):      # Llama-4 keeps plain causal attention over image tokens
         ctx.bidir = bidirectional_block_mask(mm[1])
+    if audio is not None:
+      am = self.encode_audio(audio, audio_mask)
+      mm = am if mm is None else [mm, am]
     x = self.embed(tokens, positions, mm)
     for i, layer in enumerate(self.layers):
       ctx.layer_index = i

@@ -160,6 +160,9 @@ class TrainEngine:
     self._gather(0, async_op=False)
     self._gather(1)
     mm = self._encode_images(batch, tokens, ctx)
+    am = self._encode_audio(batch)
+    if am is not None:
+      mm = am if mm is None else [mm, am]
     x = self._run_embed(tokens, positions, grad=False, mm=mm)
     # tensor-sequence parallelism: between blocks every tensor rank holds its part of the sequence only
     sp_on = ctx.tp_size > 1 and L_sp_enabled(c) and ctx.cp_size == 1
@@ -345,6 +348,22 @@ class TrainEngine:
     if self.model.vision.__class__.__name__ in ("Gemma3Vision", "Gemma4Vision"):    # Llama-4 keeps plain causal attention over image tokens
       ctx.bidir = bidirectional_block_mask(mm[1])
     return mm
+
+  def _encode_audio(self, batch: dict):
+    """Batches with `audio` ([B, mel, frames] or a list of clips) + `audio_mask` [B, S]: run the frozen audio tower once."""
+    if batch.get("audio") is None or self.model.audio is None:
+      return None
+    if not bool(getattr(self.config, "freeze_vision_encoder_params", True)):
+      raise NotImplementedError("training the audio tower (freeze_vision_encoder_params=false) is not implemented")
+    units = [u for k, u in self.store.units.items() if k == "audio" or k.startswith("audio#")]
+    for u in units:
+      if u.group_size > 1 and not u.resident:
+        self.store.gather_unit(u, async_op=False)
+    with torch.no_grad():
+      am = self.model.encode_audio(batch["audio"], batch["audio_mask"].to(self.device))
+    for u in units:
+      self.store.release_full(u)
+    return am
 
   def _run_embed(self, tokens, positions, grad: bool, dx=None, mm=None):
     model = self.model
