@@ -4,6 +4,9 @@ from __future__ import annotations
 
 def create_data_iterator(config, data_rank: int = 0, data_world: int = 1, split: str = "train"):
   it = _create(config, data_rank, data_world, split)
+  if str(getattr(config, "training_objective", "causal_lm")) == "block_diffusion":
+    from ..diffusion.block_diffusion.batches import BlockDiffusionIterator
+    it = BlockDiffusionIterator(config, it, data_rank)
   if split == "train" and config.enable_rampup_batch_size:
     it = RampupIterator(config, it, data_world)
   return it

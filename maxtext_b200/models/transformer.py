@@ -432,6 +432,9 @@ class Transformer:
       positions = torch.arange(S, device=tokens.device)[None].expand(B, S)
     ctx = self.make_ctx(positions, segment_ids, mode, tokens)
     ctx.positions3 = positions3.to(tokens.device) if positions3 is not None else None
+    if str(getattr(self.config, "attention_type", "global")) == "block_diffusion" and caches is None:
+      from ..diffusion.block_diffusion import same_block_mask
+      ctx.bidir = same_block_mask(positions, int(self.config.causal_block_size), segment_ids)
     mm = None
     if images is not None:
       from ..multimodal.utils import bidirectional_block_mask

@@ -49,6 +49,12 @@ class TrainEngine:
         raise NotImplementedError("tensor_sequence parallelism cannot be combined with context or pipeline parallelism yet")
       if int(getattr(c, "mtp_num_layers", 0) or 0) > 0:
         raise NotImplementedError("multi-token prediction is not implemented under tensor_sequence parallelism")
+    if str(getattr(c, "attention_type", "global")) == "block_diffusion":
+      if str(getattr(c, "training_objective", "causal_lm")) != "block_diffusion":
+        # src/maxtext/trainers/pre_train/train.py:115-119: next-token labels would leak inside a bidirectional block
+        raise ValueError("block-diffusion attention requires training_objective=block_diffusion")
+      if mesh is not None and mesh.axis_size(("context", "context_usp_ulysses")) > 1:
+        raise NotImplementedError("block-diffusion attention is not implemented under context parallelism")
     self.model = model or Transformer(c, mesh, self.device)
     from ..ops import quantization as _quant
     _quant.set_mode(str(c.quantization or ""))
@@ -131,6 +137,18 @@ class TrainEngine:
       weights = batch["loss_weights"].to(self.device).float()
     if c.dataset_type == "synthetic" and not c.packing_in_synthetic:
       seg = None   # synthetic batches are one segment per row by construction: skip the mask work
+    diffusion = str(getattr(c, "training_objective", "causal_lm")) == "block_diffusion"
+    bd_index = None
+    if diffusion:
+      # block diffusion (src/maxtext/trainers/pre_train/train.py:114-142,201-228): the batch names its own targets
+      for k in ("corruption_mask", "targets_loss_mask"):
+        if batch.get(k) is None or tuple(batch[k].shape) != (B, S):
+          raise ValueError(f"block-diffusion loss needs the batch mask {k!r} with the shape of targets")
+      weights = weights * (batch["targets_loss_mask"].to(self.device) != 0).float()
+      from ..diffusion.block_diffusion import source_indices
+      tpos = batch.get("targets_position", batch.get("inputs_position"))
+      bd_index = source_indices(str(c.block_diffusion_logit_alignment), S, tpos.to(self.device) if tpos is not None else None,
+                                (tseg.to(self.device) != 0) if tseg is not None else None, B, self.device)
 
     first_micro = self._accum is None
     if first_micro:
@@ -144,6 +162,9 @@ class TrainEngine:
 
     n_units = len(self._units)
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    if str(getattr(c, "attention_type", "global")) == "block_diffusion":
+      from ..diffusion.block_diffusion import same_block_mask
+      ctx.bidir = same_block_mask(positions, int(c.causal_block_size), seg)
     p3 = batch.get("inputs_position3")          # [B, S, 3] multi-axis rotary positions of multimodal rows (`use_mrope`)
     ctx.positions3 = p3.to(self.device) if p3 is not None else None
     if float(c.dropout_rate) > 0 and bool(c.enable_dropout) and compute_grads:
@@ -203,7 +224,13 @@ class TrainEngine:
         store.acquire_full_grad(u)
     if sp_on:
       x = sp.all_gather_seq(x, ctx.tp_group)               # the head scores every token on every tensor rank, as without SP
-    loss_sum, z_sum, dx = self._run_head(x, targets.reshape(-1), w_flat, compute_grads)
+    if bd_index is not None:
+      # shifted alignment: target s is scored by the state of the slot holding the previous position
+      gi = bd_index[:, :, None].expand(B, S, x.shape[-1])
+      loss_sum, z_sum, dxa = self._run_head(x.gather(1, gi), targets.reshape(-1), w_flat, compute_grads)
+      dx = torch.zeros_like(x).scatter_add_(1, gi, dxa.view(B, S, -1)).view(dxa.shape) if dxa is not None else None
+    else:
+      loss_sum, z_sum, dx = self._run_head(x, targets.reshape(-1), w_flat, compute_grads)
     if sp_on and dx is not None:
       dx = sp.local_seq(dx.view(B, S, -1), ctx.tp_group)
     acc["loss_sum"] += loss_sum
