@@ -73,6 +73,23 @@ class LayerCtx:
   positions3: torch.Tensor | None = None  # [B, S, 3] (temporal, height, width) positions of a multimodal prompt (`use_mrope`)
   deepstack: tuple | None = None     # (image mask [B, S], [features [B, N*K, D], ...]): feature i is added after decoder layer i
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
+  batch_split: int = 1               # > 1: every decoder layer runs the batch as that many micro-batches on alternating streams
+  micro_slot: int = 0                # which micro-batch of a split layer this context describes
+
+  def micro(self, j: int, n: int) -> "LayerCtx":
+    """Context of micro-batch j of n: the per-row tensors are sliced, kept tensors go to a dictionary of their own, and
+    the lists / dictionaries that a layer appends to are private so that the caller can merge them afterwards."""
+    import dataclasses
+
+    def cut(t):
+      return None if t is None else t.chunk(n, 0)[j]
+    sub = dataclasses.replace(self, positions=cut(self.positions), segment_ids=cut(self.segment_ids), tokens=cut(self.tokens),
+                              bidir=cut(self.bidir), positions3=cut(self.positions3), batch_split=1, micro_slot=j, aux_losses=[],
+                              max_logits={} if self.max_logits is not None else None)
+    if self.deepstack is not None:
+      sub.deepstack = (cut(self.deepstack[0]), [cut(f) for f in self.deepstack[1]])
+    sub.saved = None if self.saved is None else self.saved.setdefault(f"mb{j}", {})
+    return sub
 
   def dropout(self, t: torch.Tensor, site: int) -> torch.Tensor:
     """Inverted dropout whose mask depends only on (seed of the micro-batch, layer, block, site): the recompute pass of a
@@ -81,7 +98,7 @@ class LayerCtx:
     if self.dropout_seed is None or rate <= 0.0 or self.mode != "train":
       return t
     g = torch.Generator(device=t.device)
-    g.manual_seed((self.dropout_seed * 1000003 + self.layer_index * 1009 + (hash(self.name_prefix) % 97) * 31 + site) % (2 ** 62))
+    g.manual_seed((self.dropout_seed * 1000003 + self.layer_index * 1009 + (hash(self.name_prefix) % 97) * 31 + site + 7 * self.micro_slot) % (2 ** 62))
     keep = (torch.rand(t.shape, generator=g, device=t.device) >= rate).to(t.dtype)
     return t * keep / (1.0 - rate)
 

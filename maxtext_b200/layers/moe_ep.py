@@ -87,8 +87,10 @@ class EPRuntime:
     return out
 
 
-def runtime(group, device, num_experts, d_model, pairs, factor) -> EPRuntime:
-  key = (id(group), num_experts, d_model, pairs)
+def runtime(group, device, num_experts, d_model, pairs, factor, slot: int = 0) -> EPRuntime:
+  """`slot` separates exchanges that may be in flight at the same time (the micro-batches of the batch-split schedule run
+  on different streams): each slot owns its buffers and its epoch flags."""
+  key = (id(group), num_experts, d_model, pairs, slot)
   if key not in _RUNTIMES:
     _RUNTIMES[key] = EPRuntime(group, device, num_experts, d_model, pairs, factor)
   return _RUNTIMES[key]
@@ -141,7 +143,7 @@ def supported(x2, moe, ctx) -> bool:
 def expert_parallel_ffn(x2, wts, idx, moe, ctx):
   """x2 [T, D] -> [T, D]: routed experts spread over the `expert` mesh axis."""
   T, k = idx.shape
-  rt = runtime(ctx.ep_group, x2.device, moe.E, x2.shape[1], T * k, float(getattr(moe.c, "ep_buffer_factor", 2.0)))
+  rt = runtime(ctx.ep_group, x2.device, moe.E, x2.shape[1], T * k, float(getattr(moe.c, "ep_buffer_factor", 2.0)), int(ctx.micro_slot) % 2)
   lp = moe_ops.GroupPlan(idx, moe.E)                 # this rank's pairs sorted by GLOBAL expert
   rp = _RecvPlan(rt, T * k)
   idx32 = idx.reshape(-1).to(torch.int32).contiguous()

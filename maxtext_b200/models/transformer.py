@@ -159,6 +159,46 @@ class DecoderLayer:
     self.params = b.params
 
   def __call__(self, x, ctx: LayerCtx):
+    n = int(ctx.batch_split)
+    if n > 1 and ctx.cache is None and x.shape[0] % n == 0:
+      return self._call_split(x, ctx, n)
+    return self._call_one(x, ctx)
+
+  def _call_split(self, x, ctx: LayerCtx, n: int):
+    """Batch-split schedule (the role of src/maxtext/models/deepseek_batchsplit.py:1939-2015 and its staggered layer body):
+    the batch runs through this layer as n micro-batches on alternating CUDA streams, so the expert-parallel exchange
+    (and any other collective) of one micro-batch overlaps the attention and GEMMs of the other. The backward pass of every
+    operation runs on the stream of its forward, so the overlap carries over. Results are the concatenation of the
+    micro-batch results; auxiliary losses are averaged, per-head logit maxima are merged by maximum."""
+    parts = x.chunk(n, 0)
+    lanes = _split_lanes(x.device, min(n, 2)) if x.is_cuda else None
+    main = torch.cuda.current_stream(x.device) if lanes else None
+    outs, subs = [], []
+    for j in range(n):
+      sub = ctx.micro(j, n)
+      subs.append(sub)
+      if lanes:
+        lane = lanes[j % len(lanes)]
+        lane.wait_stream(main)
+        with torch.cuda.stream(lane):
+          outs.append(self._call_one(parts[j], sub))
+      else:
+        outs.append(self._call_one(parts[j], sub))
+    if lanes:
+      for lane in lanes:
+        main.wait_stream(lane)
+      for o in outs:
+        o.record_stream(main)
+    names = [nm for nm, _ in subs[0].aux_losses]
+    for i, nm in enumerate(names):
+      ctx.aux_losses.append((nm, sum(s_.aux_losses[i][1] for s_ in subs) / n))
+    if ctx.max_logits is not None:
+      for s_ in subs:
+        for k_, v_ in s_.max_logits.items():
+          ctx.max_logits[k_] = torch.maximum(ctx.max_logits[k_], v_) if k_ in ctx.max_logits and s_ is not subs[0] else v_
+    return torch.cat(outs, 0)
+
+  def _call_one(self, x, ctx: LayerCtx):
     caches = ctx.cache                      # inference: one cache per block of this layer
     for i, blk in enumerate(self.blocks):
       ctx.name_prefix = f"b{i}/" if len(self.blocks) > 1 else ""
@@ -173,6 +213,17 @@ class DecoderLayer:
       from ..multimodal.utils import merge_mm_embeddings
       x = x + merge_mm_embeddings(torch.zeros_like(x), ds[1][self.index], ds[0])
     return x
+
+
+_LANES: dict = {}
+
+
+def _split_lanes(device, n: int):
+  """Side streams of the batch-split schedule, one set per device."""
+  key = (device.index if device.index is not None else torch.cuda.current_device(), n)
+  if key not in _LANES:
+    _LANES[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+  return _LANES[key]
 
 
 class _CollapsingNorm:

@@ -162,6 +162,8 @@ class TrainEngine:
 
     n_units = len(self._units)
     ctx = model.make_ctx(positions, seg, "train", tokens)
+    if bool(getattr(c, "use_batch_split_schedule", False)):
+      ctx.batch_split = max(2, int(getattr(c, "batch_split_factor", 1) or 1))
     if str(getattr(c, "attention_type", "global")) == "block_diffusion":
       from ..diffusion.block_diffusion import same_block_mask
       ctx.bidir = same_block_mask(positions, int(c.causal_block_size), seg)

@@ -63,3 +63,14 @@ def test_newer_families_train_on_gpu_and_track_cpu(model, extra):
   tol = 0.15 if model.startswith("llama4") else 0.08
   assert all(abs(a - b) < tol for a, b in zip(gpu, cpu)), (gpu, cpu)
   assert gpu[-1] < gpu[0]
+
+
+def test_batch_split_schedule_on_two_streams_matches_the_plain_step():
+  """The micro-batches of a split layer run on two side streams; the losses must follow the unsplit run."""
+  from maxtext_b200.ops import backend
+  E = backend.ext(required=True)
+  plain = _losses(_cfg(["hardware=gpu", "per_device_batch_size=4"]), "cuda")
+  split = _losses(_cfg(["hardware=gpu", "per_device_batch_size=4", "use_batch_split_schedule=true"]), "cuda")
+  assert E.kernel_status(True) == 0
+  for a, b in zip(plain, split):
+    assert abs(a - b) < 0.03, (plain, split)
