@@ -148,6 +148,22 @@ def layer_plans(c) -> list[LayerPlan]:
     moe = [LayerPlan("moe_layers", [_llama_like(c, attention=attn, mlp="moe_shared", mlp_name="DeepSeekMoeBlock_0")])
            for _ in range(n - nd)]
     return dense + moe
+  if blk == "deepseek4":
+    # src/maxtext/models/deepseek4.py + src/maxtext/layers/decoders.py:1554-1640: `first_num_hash_layers` prefix layers with
+    # their own compression ratios and hash routing, then pairs of (heavy, sparse) compressed-attention layers that form
+    # one scanned block (`scanned_blocks`, sub-trees layers_0 / layers_1). Every layer has a routed MoE with shared experts.
+    ratios = [int(r) for r in c.compress_ratios]
+    nh = int(c.first_num_hash_layers)
+    assert len(ratios) >= n, "compress_ratios must name every decoder layer"
+    assert (n - nh) % 2 == 0, "the layers after the hash-routed prefix come in (heavy, sparse) pairs"
+
+    def v4(ratio, prefix=""):
+      return _llama_like(c, attention="compressed", attn_name="self_attention", mlp="moe_shared", mlp_name="DeepSeekMoeBlock_0",
+                         compress_ratio=ratio, prefix=prefix)
+    plans = [LayerPlan("layers", [v4(ratios[i])]) for i in range(nh)]
+    for i in range(nh, n, 2):
+      plans.append(LayerPlan("scanned_blocks", [v4(ratios[i], "layers_0"), v4(ratios[i + 1], "layers_1")]))
+    return plans
   if blk == "gemma":
     bp = BlockPlan(pre_attn_norm="pre_self_attention_norm", pre_mlp_norm="pre_ffw_norm", soft_cap=c.attn_logits_soft_cap)
     return [LayerPlan("layers", [bp]) for _ in range(n)]
@@ -205,4 +221,4 @@ def layer_plans(c) -> list[LayerPlan]:
     return plans
   raise NotImplementedError(
       f"decoder_block={blk!r} parses but has no model implementation here yet (implemented: llama2, mistral, mixtral, "
-      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, envy, gemma4, simple)")
+      "deepseek, gemma, gemma2, gemma3, qwen2, qwen3, qwen3_moe, qwen3_next, qwen3_5, gpt3, gpt_oss, olmo3, llama4, envy, gemma4, deepseek4, simple)")

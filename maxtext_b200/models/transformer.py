@@ -62,6 +62,7 @@ class BlockPlan:
   share_kv: bool = False                 # value = key projection
   v_norm: str = ""                       # "" | "noscale" | "scale": RMS normalisation of the value heads
   layer_scalar: bool = False             # learned scalar on the layer output
+  compress_ratio: int = 0                # DeepSeek-V4 compressed attention: 0 (window only), 4 (sparse) or 128 (heavy)
 
 
 @dataclass
@@ -93,6 +94,9 @@ class DecoderBlock:
     elif plan.attention == "gdn":
       from ..layers.gdn import GatedDeltaNet
       self.attn = GatedDeltaNet(b, c, plan.attn_name + s)
+    elif plan.attention == "compressed":
+      from ..layers.attention_compressed import CompressedAttention
+      self.attn = CompressedAttention(b, c, plan.attn_name + s, plan.compress_ratio, int(c.sliding_window_size))
     else:
       self.attn = L.Attention(b, c, plan.attn_name + s, plan.window, inv_ts, interleaved, plan.use_rope, plan.qk_norm,
                               plan.query_scalar, plan.soft_cap, plan.attn_bias,
@@ -227,17 +231,17 @@ def _split_lanes(device, n: int):
 
 
 class _CollapsingNorm:
-  """Final norm of a model with hyper-connections: the k residual streams are summed before the norm
-  (src/maxtext/layers/decoders.py:1279-1288)."""
+  """Final norm of a model with hyper-connections: the k residual streams are summed before the norm, or, for DeepSeek-V4,
+  mixed by the learned gates of its hyper-head (src/maxtext/layers/decoders.py:1279-1288)."""
 
-  def __init__(self, norm):
-    self.norm = norm
+  def __init__(self, norm, hyper_head=None):
+    self.norm, self.hyper_head = norm, hyper_head
     self.scale, self.bias = norm.scale, norm.bias
 
   def __call__(self, x):
     if x.dim() == 4:
       from ..layers.mhc import reduce_streams
-      x = reduce_streams(x)
+      x = self.hyper_head(x) if self.hyper_head is not None else reduce_streams(x)
     return self.norm(x)
 
 
@@ -337,7 +341,11 @@ class Transformer:
     hb = L.Builder(c, "head", None, None, **self.par)
     norm = L.Norm(hb.sub("decoder"), "decoder_norm", c.emb_dim, c.normalization_layer_epsilon,
                   self.family.norm_offset, kind=self.family.norm_kind)
-    self.final_norm = _CollapsingNorm(norm) if self.mhc_k > 1 else norm
+    hyper_head = None
+    if self.mhc_k > 1 and c.decoder_block == "deepseek4":
+      from ..layers.mhc import HyperHead
+      hyper_head = HyperHead(hb.sub("decoder"), c, "hc_head")
+    self.final_norm = _CollapsingNorm(norm, hyper_head) if self.mhc_k > 1 else norm
     self.logits_dense = None
     if not c.logits_via_embedding:
       self.logits_dense = hb.sub("decoder", "logits_dense").linear("kernel", (c.emb_dim,), (c.vocab_size,),
