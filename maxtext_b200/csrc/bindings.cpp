@@ -88,6 +88,26 @@ bool gemm_supported(const torch::Tensor& a, const torch::Tensor& b, const torch:
   return M >= 128 && N >= 128 && K >= 64 && (!ta || M % 8 == 0) && N % 8 == 0 && K % 8 == 0;
 }
 
+extern "C" int mt_gemm_small_m_supported(int M, int N, int K, long ldx, long ldw, long ldo);
+extern "C" int mt_gemm_small_m(const void* x, const void* w, void* out, int M, int N, int K, long ldx, long ldw, long ldo, int num_sms, cudaStream_t stream);
+
+// out[M, N] = x[M, K] w[N, K]^T for M <= 64 (decode): the weight-streaming kernel of gemm_small_m.cu
+bool gemm_small_m_supported(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& out) {
+  if (!x.is_cuda() || x.scalar_type() != torch::kBFloat16 || w.scalar_type() != torch::kBFloat16 || out.scalar_type() != torch::kBFloat16) return false;
+  if (x.dim() != 2 || w.dim() != 2 || out.dim() != 2 || x.stride(1) != 1 || w.stride(1) != 1 || out.stride(1) != 1) return false;
+  if (x.size(1) != w.size(1) || out.size(0) != x.size(0) || out.size(1) != w.size(0)) return false;
+  if (reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 || reinterpret_cast<uintptr_t>(w.data_ptr()) % 16) return false;
+  return mt_gemm_small_m_supported((int)x.size(0), (int)w.size(0), (int)x.size(1), x.stride(0), w.stride(0), out.stride(0)) != 0;
+}
+
+void gemm_small_m(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out) {
+  TORCH_CHECK(gemm_small_m_supported(x, w, out), "gemm_small_m: unsupported operands");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(mt_gemm_small_m(x.data_ptr(), w.data_ptr(), out.data_ptr(), (int)x.size(0), (int)w.size(0), (int)x.size(1), x.stride(0), w.stride(0),
+                        out.stride(0), num_sms(), cur_stream()),
+        "mt_gemm_small_m");
+}
+
 // CTA-pair (cta_group::2) kernel for shapes it covers: measured 3-10 % faster than the single-CTA kernel under sustained load
 bool g_use_pair = true;
 
@@ -285,6 +305,8 @@ void register_comm(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_supported", &gemm_supported);
   m.def("gemm", &gemm);
+  m.def("gemm_small_m_supported", &gemm_small_m_supported);
+  m.def("gemm_small_m", &gemm_small_m);
   m.def("gemm_pair", &gemm_pair);
   m.def("gemm_use_pair", [](bool v) { g_use_pair = v; });
   m.def("gemm_set_raster", [](int64_t v) { mt_gemm_set_raster((int)v); });

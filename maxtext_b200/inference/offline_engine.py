@@ -22,7 +22,10 @@ class Request:
 
 
 class OfflineEngine:
-  def __init__(self, engine: MaxEngine, slots: int = 4, eos_id: int = -1):
+  def __init__(self, engine: MaxEngine, slots: int = 4, eos_id: int = -1, enable_batch_prefill: bool = False,
+               batch_prefill_max_batch_size: int = 16):
+    """`enable_batch_prefill` packs the prompts that wait for free slots into shared prefill passes
+    (src/maxtext/inference/offline_engine.py:749-780, prefill_packing.py)."""
     c = engine.config
     if int(c.max_target_length) - int(c.max_prefill_predict_length) <= 0:
       raise ValueError("Make sure max_target_length - max_prefill_predict_length is greater than 0")      # offline_engine.py:950
@@ -31,6 +34,10 @@ class OfflineEngine:
     self.queue: deque[Request] = deque()
     self.running: dict[int, Request] = {}
     self.steps = 0
+    self.batched = None
+    if enable_batch_prefill:
+      from .prefill_packing import BatchedPrefillProcessor
+      self.batched = BatchedPrefillProcessor(engine, batch_prefill_max_batch_size)
 
   def submit(self, tokens, max_new_tokens=32) -> Request:
     r = Request(len(self.queue) + len(self.running) + self.steps * 1000, list(tokens), max_new_tokens)
@@ -38,6 +45,8 @@ class OfflineEngine:
     return r
 
   def _fill_free_slots(self):
+    if self.batched is not None:
+      return self._fill_free_slots_packed()
     for s in range(self.slots):
       if s in self.running or not self.queue:
         continue
@@ -47,6 +56,26 @@ class OfflineEngine:
       self.state = self.eng.insert(prefix, self.state, s)
       r.output.append(int(first.data[0, 0]))
       self.running[s] = r
+      self._maybe_finish(s)
+
+  def _fill_free_slots_packed(self):
+    """All prompts that fit the free slots go through the packing processor; their first tokens arrive by callback."""
+    free = [s for s in range(self.slots) if s not in self.running]
+    cap = int(self.eng.config.max_prefill_predict_length)
+    placed = {}
+
+    def done(results, state):
+      for rid, first in results:
+        placed[rid].output.append(int(first.reshape(-1)[0]))
+    for s in free:
+      if not self.queue:
+        break
+      r = self.queue.popleft()
+      placed[r.rid] = r
+      self.running[s] = r
+      self.state = self.batched.process(self.state, s, r.rid, r.tokens, cap, done)
+    self.state = self.batched.flush(self.state, done)
+    for s in free:
       self._maybe_finish(s)
 
   def _maybe_finish(self, s):

@@ -35,6 +35,19 @@ def gemm_fallbacks() -> int:
   return _GEMM_FALLBACKS
 
 
+def _small_m_wins(M, N, K) -> bool:
+  """Shapes on which the weight-streaming kernel measured faster than the library's small-M kernels on a B200 (4096 x 4096
+  weights at M <= 32: 11.4 - 15.3 us against 15.6 - 17.1 us). Its mma.sync inner loop runs out of issue rate above M = 32, and
+  on wider or deeper weights the library's kernels are ahead, so those go to the library (and are counted as fallbacks).
+  MAXTEXT_B200_SMALL_M=all / none overrides the rule."""
+  mode = os.environ.get("MAXTEXT_B200_SMALL_M", "")
+  if mode == "none" or M > 64:
+    return False
+  if mode == "all":
+    return True
+  return M <= 32 and N <= 4096 and K <= 4096
+
+
 def _gemm_supported(M, N, K, a, b):
   return a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and K >= 16
 
@@ -54,6 +67,10 @@ def mm(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out: torch.Tensor |
     accumulate = False
   if a.is_cuda:
     E = backend.ext(required=True)
+    if (_GEMM_IMPL == "tcgen05" and not ta and tb and not accumulate and out.dtype == torch.bfloat16 and _small_m_wins(M, N, K)
+        and E.gemm_small_m_supported(a, b, out)):
+      E.gemm_small_m(a, b, out)            # decode-sized products stream the weight once (csrc/gemm_small_m.cu)
+      return out
     if _GEMM_IMPL == "tcgen05" and _gemm_supported(M, N, K, a, b) and E.gemm_supported(a, b, out, ta, tb):
       E.gemm(a, b, out, ta, tb, accumulate)
       return out

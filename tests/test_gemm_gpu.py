@@ -99,3 +99,43 @@ def test_gemm_pair_ragged_and_large(M, N, K):
 
 def test_gemm_pair_accumulate_fp32():
   _run(512, 512, 256, True, False, torch.float32, accumulate=True, pair=True)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(16, 64), (100, 192), (4096, 4096), (1000, 1024)])
+def test_small_m_weight_streaming_gemm(M, N, K):
+  """Decode-sized products (M <= 64): out = x @ W.T against an fp32 reference, all activation-tile counts, ragged N."""
+  E = _ext()
+  g = torch.Generator(device="cuda").manual_seed(M * 1000 + N)
+  x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+  w = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+  out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+  assert E.gemm_small_m_supported(x, w, out)
+  E.gemm_small_m(x, w, out)
+  torch.cuda.synchronize()
+  ref = x.float() @ w.float().t()
+  err = (out.float() - ref).abs().max().item()
+  assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), f"M={M} N={N} K={K}: max err {err}"
+
+
+def test_small_m_gemm_strided_views_and_dispatch():
+  """Row-strided activations / weights / outputs, and `functional.mm` routing M <= 64 to the streaming kernel (no library call)."""
+  from maxtext_b200.ops import functional as F
+  E = _ext()
+  g = torch.Generator(device="cuda").manual_seed(3)
+  xb = torch.randn(12, 640, device="cuda", generator=g).bfloat16()
+  wb = torch.randn(300, 640, device="cuda", generator=g).bfloat16()
+  ob = torch.zeros(12, 512, device="cuda", dtype=torch.bfloat16)
+  x, w, out = xb[:, 128:512], wb[:, 256:640], ob[:, :300]
+  assert E.gemm_small_m_supported(x, w, out)
+  E.gemm_small_m(x, w, out)
+  ref = x.float() @ w.float().t()
+  assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+  assert float(ob[:, 300:].abs().max()) == 0.0                 # nothing is written past N
+  before = F.gemm_fallbacks()
+  y = F.mm(xb, wb, False, True)
+  assert F.gemm_fallbacks() == before
+  ref2 = xb.float() @ wb.float().t()
+  assert (y.float() - ref2).abs().max().item() <= 2e-2 * ref2.abs().max().item()
+  # K not a multiple of 64 is not covered: the caller falls back and counts it
+  assert not E.gemm_small_m_supported(xb[:, :40].contiguous(), wb[:, :40].contiguous(), torch.empty(12, 300, device="cuda", dtype=torch.bfloat16))

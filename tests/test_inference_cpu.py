@@ -356,3 +356,35 @@ def test_grpc_front_end_streams_the_tokens_of_the_serving_loop():
   finally:
     server.stop(0)
     loop.stop()
+
+
+def test_prefill_packing_buckets_and_offline_engine_agree_with_single_prefills():
+  from maxtext_b200.inference.offline_engine import OfflineEngine
+  from maxtext_b200.inference.prefill_packing import BatchedPrefillProcessor, PrefillBucket, PrefillProcessor
+  b = PrefillBucket(10)
+  assert b.is_empty() and b.try_add(0, "a", [1, 2, 3, 4]) and b.try_add(1, "b", [5, 6, 7, 8, 9]) and b.unallocated() == 1
+  assert not b.try_add(2, "c", [1, 2]) and len(b) == 2
+  with pytest.raises(ValueError):
+    b.add(2, "c", [1, 2])
+  with pytest.raises(ValueError):
+    PrefillBucket(0)
+  eng, cfg = _engine(extra=["vocab_size=300"])
+  prompts = [[5, 6, 7], [9, 10, 11, 12], [3, 4], [8, 8, 8, 8, 8], [20, 21, 22, 23, 24, 25]]
+  plain = OfflineEngine(eng, slots=3).batch_inference(prompts, max_new_tokens=5)
+  packed_eng = OfflineEngine(eng, slots=3, enable_batch_prefill=True, batch_prefill_max_batch_size=2)
+  packed = packed_eng.batch_inference(prompts, max_new_tokens=5)
+  assert packed == plain
+  assert 0 < packed_eng.batched.passes < len(prompts)                   # fewer passes than prompts: some were packed together
+  # the processors by hand: three prompts, capacity for two of them -> two passes, results by callback
+  proc = BatchedPrefillProcessor(eng, max_batch_size=8)
+  state = eng.init_decode_state(3)
+  got = {}
+  done = lambda res, st: got.update({rid: int(tok.reshape(-1)[0]) for rid, tok in res})      # noqa: E731
+  for s, p in enumerate(prompts[:3]):
+    state = proc.process(state, s, f"r{s}", p, 8, done)
+  state = proc.flush(state, done)
+  assert proc.passes == 2 and set(got) == {"r0", "r1", "r2"}
+  first, _ = PrefillProcessor(eng).process(eng.init_decode_state(3), 0, prompts[1])
+  assert int(first.data[0, 0]) == got["r1"]
+  with pytest.raises(ValueError):
+    proc.process(state, 0, "big", list(range(9)), 8)
