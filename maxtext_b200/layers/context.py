@@ -75,6 +75,7 @@ class LayerCtx:
   name_prefix: str = ""              # disambiguates blocks that share a layer (gemma2 local/global)
   batch_split: int = 1               # > 1: every decoder layer runs the batch as that many micro-batches on alternating streams
   micro_slot: int = 0                # which micro-batch of a split layer this context describes
+  split_active: bool = False         # this context is one micro-batch of a split layer (its twin may run on another stream)
 
   def micro(self, j: int, n: int) -> "LayerCtx":
     """Context of micro-batch j of n: the per-row tensors are sliced, kept tensors go to a dictionary of their own, and
@@ -84,7 +85,7 @@ class LayerCtx:
     def cut(t):
       return None if t is None else t.chunk(n, 0)[j]
     sub = dataclasses.replace(self, positions=cut(self.positions), segment_ids=cut(self.segment_ids), tokens=cut(self.tokens),
-                              bidir=cut(self.bidir), positions3=cut(self.positions3), batch_split=1, micro_slot=j, aux_losses=[],
+                              bidir=cut(self.bidir), positions3=cut(self.positions3), batch_split=1, micro_slot=j, split_active=True, aux_losses=[],
                               max_logits={} if self.max_logits is not None else None)
     if self.deepstack is not None:
       sub.deepstack = (cut(self.deepstack[0]), [cut(f) for f in self.deepstack[1]])

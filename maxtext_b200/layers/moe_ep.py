@@ -13,6 +13,8 @@ Buffer discipline (one pair of symmetric buffers per EP group, shared by all lay
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -136,6 +138,11 @@ def _ident(lp):
 
 def supported(x2, moe, ctx) -> bool:
   c = moe.c
+  if getattr(ctx, "split_active", False) and os.environ.get("MAXTEXT_B200_SPLIT_FUSED_EP") != "1":
+    # two micro-batches of a split layer exchange at the same time on two streams. Each slot has its own buffers and flags
+    # (`runtime(slot=)`), but that combination has not run on GPUs yet: the exchange goes through the NCCL path, whose calls
+    # are issued in the same order on every rank
+    return False
   return (bool(getattr(c, "use_fused_comm_kernels", False)) and x2.dtype == torch.bfloat16 and moe.act in F._ACT_CODE
           and moe_ops.padded_path_supported(x2, x2.shape[1], moe.wi_0.data.shape[1], moe.E) and symm_lib.available())
 
