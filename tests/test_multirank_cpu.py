@@ -58,7 +58,11 @@ def _launch_with_retry(world, argv):
   """The rendezvous on a freshly picked local port can lose a race with another process once in a while: a launch whose
   ranks fail is repeated once on a new port; a real failure fails both times and is reported."""
   codes, logs = _launch(world, argv)
-  if any(c != 0 for c in codes):
+  rendezvous = ("Address already in use", "EADDRINUSE", "Connection refused", "Connection reset", "connect() timed out", "DistNetworkError",
+                "failed to connect", "Socket Timeout")
+  if any(c != 0 for c in codes) and any(pat in l for l in logs for pat in rendezvous):
+    # only a lost race for the port is repeated: a run that got further may have left checkpoints behind, and repeating it
+    # would resume from them and report different steps
     codes, logs = _launch(world, argv)
   for c, l in zip(codes, logs):
     assert c == 0, l[-3000:]
