@@ -149,7 +149,9 @@ class RoutedMoE:
           wts = wts / wts.sum(-1, keepdim=True)
     elif self.deepseek:
       lf = logits.float()
-      scores = torch.softmax(lf, -1) if func == "softmax" else torch.sigmoid(lf) if func == "sigmoid" else lf
+      # src/maxtext/layers/linears.py:40-56: the gate's score function; DeepSeek-V4 uses sqrt(softplus(logit))
+      scores = torch.softmax(lf, -1) if func == "softmax" else torch.sigmoid(lf) if func == "sigmoid" else \
+          torch.sqrt(torch.nn.functional.softplus(lf)) if func == "sqrtsoftplus" else lf
       sel = scores + self.gate_bias.leaf().float() if self.gate_bias is not None else scores
       if self.tid2eid is not None:
         if ctx is None or ctx.tokens is None:

@@ -189,3 +189,23 @@ def test_engine_trains_deepseek4():
   batch = next(SyntheticDataIterator(cfg, pin=False))
   losses = [float(eng.train_step(dict(batch))["learning/loss"]) for _ in range(5)]
   assert all(math.isfinite(v) for v in losses) and losses[-1] < losses[0], losses
+
+
+def test_sqrt_softplus_router_weights_are_positive_and_normalised():
+  from maxtext_b200.layers import blocks as L
+  from maxtext_b200.layers import moe as M
+  cfg = tiny_config("deepseek4-tiny", V4)
+  b = L.Builder(cfg, "u", None, None)
+  moe = M.RoutedMoE(b, cfg, "MoeBlock_0", deepseek_style=True)
+  g = torch.Generator().manual_seed(0)
+  for p in b.params:
+    p.data = torch.randn(p.shape, generator=g) * 0.5
+  x = torch.randn(2, 16, cfg.emb_dim)
+  x2 = x.reshape(-1, cfg.emb_dim)
+  logits = x2 @ moe.gate.data.t()
+  with torch.no_grad():
+    wts, idx, _ = moe.route(x2, 2, 16, None)
+  assert (wts > 0).all()
+  assert torch.allclose(wts.sum(-1), torch.full((32,), float(cfg.routed_scaling_factor)), atol=1e-5)
+  want = torch.sqrt(torch.nn.functional.softplus(logits.float())) + moe.gate_bias.data.float()
+  assert torch.equal(idx.sort(-1).values, want.topk(int(cfg.num_experts_per_tok), -1).indices.sort(-1).values)

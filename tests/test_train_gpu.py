@@ -49,6 +49,13 @@ def test_graft_smoke():
                         "interleave_moe_layer_step=2"]),
     ("olmo3-7b", ["base_num_decoder_layers=4", "sliding_window_size=64"]),
     ("gemma3-4b", ["base_num_decoder_layers=6", "sliding_window_size=64"]),
+    ("deepseek4-tiny", ["base_num_decoder_layers=5", "compress_ratios=[0,4,8,8,4]", "first_num_hash_layers=1", "sliding_window_size=64",
+                        "qk_rope_head_dim=64", "q_lora_rank=64", "o_groups=2", "o_lora_rank=64", "indexer_head_dim=64", "indexer_n_heads=2",
+                        "indexer_topk=8", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=256", "base_num_kv_heads=1",
+                        "mhc_expansion_rate=2"]),
+    ("gemma4-26b", ["base_num_decoder_layers=6", "sliding_window_size=64", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=256",
+                    "global_head_dim=128", "global_num_kv_heads=1"]),
+    ("envy-test", ["base_num_decoder_layers=4", "num_experts=4", "num_experts_per_tok=1", "base_moe_mlp_dim=256"]),
 ])
 def test_newer_families_train_on_gpu_and_track_cpu(model, extra):
   """bf16 on the GPU (this repository's kernels wherever they apply) against fp32 on the CPU for families whose blocks take the
@@ -60,7 +67,8 @@ def test_newer_families_train_on_gpu_and_track_cpu(model, extra):
   assert E.kernel_status(True) == 0
   cpu = _losses(_cfg(over + ["hardware=cpu", "dtype=float32"]), "cpu", 3)
   # top-1 routing (Llama-4) can flip an expert choice between bf16 and fp32, which moves the loss a little more
-  tol = 0.15 if model.startswith("llama4") else 0.08
+  # so can the sparse layers' top-k block choice and the routers of the small MoE variants below
+  tol = 0.15 if model.startswith(("llama4", "deepseek4", "gemma4", "envy")) else 0.08
   assert all(abs(a - b) < tol for a, b in zip(gpu, cpu)), (gpu, cpu)
   assert gpu[-1] < gpu[0]
 
