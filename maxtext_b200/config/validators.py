@@ -225,8 +225,74 @@ def check_parallelism(t):
             "when enable_streaming_diloco is True.")
 
 
+def _num(v):
+  """Optional numeric keys arrive as None, the string 'None', or a number."""
+  if v is None or (isinstance(v, str) and v.strip().lower() in ("none", "")):
+    return None
+  return float(v)
+
+
+def check_schedules_and_distillation(t):
+  """src/maxtext/configs/types.py:3310-3345: the distillation parameter schedules (the WSD phase check lives in `types.py`)."""
+  a_end, t_end, b_end = _num(t.get("distill_alpha_end")), _num(t.get("distill_temperature_end")), _num(t.get("distill_beta_end"))
+  if a_end is not None and not 0.0 <= a_end <= 1.0:
+    _fail(f"distill_alpha_end must be in [0, 1], got {a_end}")
+  if t_end is not None and t_end <= 0.0:
+    _fail(f"distill_temperature_end must be > 0, got {t_end}")
+  if b_end is not None and b_end < 0.0:
+    _fail(f"distill_beta_end must be >= 0, got {b_end}")
+  if float(_g(t, "distill_beta", 0.0)) == 0.0 and b_end is not None and b_end > 0.0:
+    _fail(f"distill_beta=0.0 but distill_beta_end={b_end}. Feature extraction is disabled when distill_beta starts at 0.0.")
+  for name, end in (("distill_alpha", a_end), ("distill_temperature", t_end), ("distill_beta", b_end)):
+    sched = str(_g(t, f"{name}_schedule", "constant"))
+    if sched != "constant" and end is None:
+      _fail(f"{name}_schedule is '{sched}' but {name}_end is None. Set {name}_end to a target value or use schedule='constant'.")
+
+
+def check_misc(t):
+  """Single-key ranges and pairings from src/maxtext/configs/types.py:3183-3197, 3356-3420, 3815-3818, 3884-3930, 4280-4330."""
+  if (_g(t, "load_parameters_path", "") or _g(t, "load_full_state_path", "")) and not _g(t, "enable_checkpointing", True):
+    _fail("You must set enable_checkpointing=True to load a checkpoint.")
+  if _g(t, "enable_multi_tier_checkpointing", False):
+    mins, steps = t.get("multi_tier_checkpointing_backup_interval_minutes"), t.get("multi_tier_checkpointing_backup_interval_steps")
+    if (_num(mins) is None) == (_num(steps) is None):
+      _fail("Exactly one of `multi_tier_checkpointing_backup_interval_minutes` or `multi_tier_checkpointing_backup_interval_steps` must be set.")
+    if _num(steps) is not None and _num(steps) <= 0:
+      _fail(f"`multi_tier_checkpointing_backup_interval_steps` ({steps}) must be > 0.")
+  if str(_g(t, "elastic_backup_kind", "snapshot")) not in ("snapshot", "checkpoint"):
+    _fail(f"elastic_backup_kind must be one of 'snapshot' or 'checkpoint', got '{t.get('elastic_backup_kind')}'.")
+  tol = float(_g(t, "sharding_tolerance", 0.02))
+  if tol > 1.0 or tol < 0.0:
+    _fail(f"sharding_tolerance must lie in [0, 1], got {tol}.")
+  if not _g(t, "use_indexer", False) and str(_g(t, "indexer_cutoff_threshold", "remat")) != "remat":
+    _fail(f"Setting `indexer_cutoff_threshold='{t.get('indexer_cutoff_threshold')}'` is only valid when `use_indexer=True`.")
+  chunk = int(_g(t, "mla_qk_head_chunk_size", 0) or 0)
+  if chunk > 0 and _g(t, "use_indexer", False) and int(_g(t, "indexer_n_heads", chunk)) % chunk != 0:
+    _fail(f"`mla_qk_head_chunk_size` ({chunk}) must divide `indexer_n_heads` ({t.get('indexer_n_heads')}).")
+  layers = list(_g(t, "engram_layers", []) or [])
+  if layers:
+    bases, n = list(_g(t, "engram_vocab_bases", []) or []), int(_g(t, "engram_max_ngram_size", 0))
+    if len(bases) != n - 1:
+      _fail(f"Engram vocab size mismatch: expected {n - 1} (max_ngram_size - 1), but got {bases}.")
+  if str(_g(t, "decoder_block", "")) == "deepseek4" and int(_g(t, "first_num_hash_layers", 0) or 0) > 0 and _g(t, "use_ring_of_experts", False):
+    _fail("DeepSeek V4 hash routing is currently not supported with ring of experts.")
+  ep = 1
+  for k in ("ici_expert_parallelism", "dcn_expert_parallelism"):
+    ep *= max(1, int(_g(t, k, 1) or 1))
+  if ep == 1 and not _g(t, "override_logical_axis_rules", False):
+    for flag, off in (("use_ring_of_experts", False),):            # random routing works on one rank here, the ring needs peers
+      if _g(t, flag, off) != off:
+        _fail(f"When EP rank is 1, {flag} must be {off} (was {t.get(flag)}).")
+  dpo = t.get("dpo") if isinstance(t.get("dpo"), dict) else None
+  if _g(t, "use_dpo", False) and dpo and dpo.get("max_prompt_length") is not None:
+    if int(dpo["max_prompt_length"]) >= int(t["max_target_length"]):
+      _fail(f"dpo.max_prompt_length ({dpo['max_prompt_length']}) must be less than max_target_length ({t['max_target_length']}).")
+  if str(_g(t, "dataset_type", "")) == "tfds" and not _g(t, "dataset_name", "") and not _g(t, "dataset_path", ""):
+    _fail("dataset_name can't be empty when dataset_type=tfds")
+
+
 ALL_CHECKS = (check_checkpointing, check_attention, check_block_diffusion, check_quantization, check_moe, check_families, check_post_training,
-              check_batch_and_vocab, check_parallelism)
+              check_batch_and_vocab, check_parallelism, check_schedules_and_distillation, check_misc)
 
 
 def run_all(t: dict) -> None:

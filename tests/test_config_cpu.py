@@ -151,6 +151,18 @@ REJECTED = [
     (["ring_scan_unroll=2", "context_parallel_strategy=all_gather"], "ring_scan_unroll"),
     (["dcn_data_parallelism=2"], "dcn degrees"),
     (["enable_streaming_diloco=true", "scan_layers=false"], "scan_layers=True"),
+    (["distill_alpha_end=1.5"], "distill_alpha_end must be in [0, 1]"),
+    (["distill_temperature_end=0"], "distill_temperature_end must be > 0"),
+    (["distill_beta=0.0", "distill_beta_end=0.5"], "distill_beta_end=0.5"),
+    (["distill_alpha_schedule=linear"], "distill_alpha_end is None"),
+    (["load_parameters_path=/tmp/none", "enable_checkpointing=false"], "enable_checkpointing=True to load"),
+    (["enable_multi_tier_checkpointing=true", "local_checkpoint_directory=/tmp/x", "local_checkpoint_period=2"], "Exactly one of"),
+    (["elastic_backup_kind=tape"], "elastic_backup_kind"),
+    (["context_parallel_strategy=spiral"], "context_parallel_strategy"),
+    (["sharding_tolerance=1.5"], "sharding_tolerance"),
+    (["indexer_cutoff_threshold=device"], "indexer_cutoff_threshold"),
+    (["engram_layers=[1]", "engram_vocab_bases=[50]", "engram_max_ngram_size=3", "tokenizer_type=byte"], "Engram vocab size mismatch"),
+    (["use_ring_of_experts=true", "num_experts=4", "num_experts_per_tok=2"], "When EP rank is 1"),
 ]
 
 
