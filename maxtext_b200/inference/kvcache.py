@@ -143,6 +143,8 @@ def make_caches(model, slots: int, max_len: int, device, quantize: bool = False)
     for blk in layer.blocks:
       if blk.plan.attention == "mla":
         per_layer.append(MlaLayerCache(slots, max_len, c.kv_lora_rank, c.qk_rope_head_dim, dt, device))
+      elif blk.plan.attention == "compressed":
+        per_layer.append(blk.attn.make_cache(slots, max_len, dt, device))
       elif blk.plan.attention == "gdn":
         from ..layers.gdn import GDNState
         a = blk.attn

@@ -200,7 +200,7 @@ class MaxEngine:
     for n in lens:
       self._check_length(n, "prefill_concat")
     total = sum(lens)
-    packable = total <= self.max_len and not any(b.plan.attention == "gdn" for l in self.model.layers for b in l.blocks)
+    packable = total <= self.max_len and not any(b.plan.attention in ("gdn", "compressed") for l in self.model.layers for b in l.blocks)
     if not packable or len(prompts) == 1:
       return [self.prefill(p, n)[0] for p, n in zip(prompts, lens)]
     toks = torch.cat([p.to(dev).long() for p in prompts])[None]
@@ -257,7 +257,7 @@ class MaxEngine:
       raise ValueError(f"insert: slot {slot} is outside [0, {int(state.tokens.shape[0])})")
     for dst_layer, src_layer in zip(state.caches, prefix.caches):
       for d, s in zip(dst_layer, src_layer):
-        for name in ("k", "v", "ks", "vs", "latent", "k_rope"):
+        for name in ("k", "v", "ks", "vs", "latent", "k_rope") + tuple(getattr(s, "token_buffers", ())):
           if hasattr(s, name) and hasattr(d, name):
             getattr(d, name)[slot, :n] = getattr(s, name)[0, :n]
         for name in ("conv", "rec"):                 # fixed-size recurrent state (gated delta layers)

@@ -14,9 +14,9 @@ two-step output projection (grouped low-rank map, then a dense map).
 Rotary embedding (src/maxtext/layers/embeddings.py:1985-2128): the trailing `qk_rope_head_dim` channels are rotated in
 adjacent pairs (2i, 2i + 1); layers with compression use `compressed_rope_max_timescale`, the others `rope_max_timescale`.
 
-Built for training and cache-free prefill: logits over [window keys | pooled entries] are formed per chunk of queries, so
-the work is O(S * (window + chunk + S / r)) and no [S, S] tensor exists. The autoregressive caches of the pooled entries are
-not built.
+Training and cache-free prefill form logits over [window keys | pooled entries] per chunk of queries, so the work is
+O(S * (window + chunk + S / r)) and no [S, S] tensor exists. Decoding keeps, per slot, the rotated key = value vectors and the
+per-token pooling projections (`CompressedLayerCache`) and rebuilds the pooled entries of complete blocks from them.
 """
 from __future__ import annotations
 
@@ -58,35 +58,45 @@ class _Pool:
     self.position_bias = b.table("position_bias", (self.r, mult * dim), (None, None), init="zeros")
     self.kv_norm = L.Norm(b, "kv_norm", dim, c.normalization_layer_epsilon)
 
-  def windows(self, x):
-    """x [B, S, D] -> kv, gate [B, n, r, mult * dim] in fp32 over the whole blocks of the sequence (gate with its slot bias)."""
-    B, S, _ = x.shape
+  def project(self, x):
+    """x [B, S, D] -> per-token (kv, gate) [B, S, mult * dim] in fp32 (the gate without its slot bias)."""
+    return F.linear(x, self.kv_proj).float(), F.linear(x, self.gate_proj).float()
+
+  def windows(self, kv_tok, gate_tok):
+    """Per-token projections -> kv, gate [B, n, r, mult * dim] over the whole blocks (gate with its slot bias)."""
+    B, S, _ = kv_tok.shape
     n = S // self.r
     use = n * self.r
-    kv = F.linear(x[:, :use], self.kv_proj).float().view(B, n, self.r, -1)
-    gate = F.linear(x[:, :use], self.gate_proj).float().view(B, n, self.r, -1) + self.position_bias.leaf().float()
+    kv = kv_tok[:, :use].reshape(B, n, self.r, -1)
+    gate = gate_tok[:, :use].reshape(B, n, self.r, -1) + self.position_bias.leaf().float()
     return kv, gate
 
   def closed(self, x, positions, theta, rope_dim):
-    """Non-overlapping pooling: [B, n, dim], rotated at each block's first position."""
-    kv, gate = self.windows(x)
-    if kv.shape[1] == 0:
-      return x.new_zeros(x.shape[0], 0, self.dim)
-    pooled = (kv * torch.softmax(gate, dim=2)).sum(2)
-    pooled = self.kv_norm(pooled.to(x.dtype))
-    return rope_pairs(pooled, positions[:, :kv.shape[1] * self.r:self.r], theta, rope_dim)
+    return self.closed_from(*self.project(x), positions, theta, rope_dim, x.dtype)
 
   def overlapping(self, x, positions, theta, rope_dim):
+    return self.overlapping_from(*self.project(x), positions, theta, rope_dim, x.dtype)
+
+  def closed_from(self, kv_tok, gate_tok, positions, theta, rope_dim, dtype):
+    """Non-overlapping pooling: [B, n, dim], rotated at each block's first position."""
+    kv, gate = self.windows(kv_tok, gate_tok)
+    if kv.shape[1] == 0:
+      return kv_tok.new_zeros(kv_tok.shape[0], 0, self.dim).to(dtype)
+    pooled = (kv * torch.softmax(gate, dim=2)).sum(2)
+    pooled = self.kv_norm(pooled.to(dtype))
+    return rope_pairs(pooled, positions[:, :kv.shape[1] * self.r:self.r], theta, rope_dim)
+
+  def overlapping_from(self, kv_tok, gate_tok, positions, theta, rope_dim, dtype):
     """Stride-r, width-2r pooling (csa_overlap_pooling, attention_compressed.py:60-161): the first half of the channels of
     block i - 1 and the second half of the channels of block i are gated together. A block that starts a new document
     (its first position does not continue the previous block) pools itself only."""
-    kv, gate = self.windows(x)
+    kv, gate = self.windows(kv_tok, gate_tok)
     B, n = kv.shape[:2]
     if n == 0:
-      return x.new_zeros(B, 0, self.dim)
+      return kv_tok.new_zeros(B, 0, self.dim).to(dtype)
     d = self.dim
     start = positions[:, :n * self.r:self.r]
-    cont = torch.ones(B, n, dtype=torch.bool, device=x.device)
+    cont = torch.ones(B, n, dtype=torch.bool, device=kv.device)
     cont[:, 0] = False                                                         # nothing precedes the first block
     cont[:, 1:] = start[:, 1:] == start[:, :-1] + self.r
     prev_kv = torch.cat([kv.new_zeros(B, 1, self.r, d), kv[:, :-1, :, :d]], 1)
@@ -96,7 +106,7 @@ class _Pool:
     both_kv = torch.cat([prev_kv, kv[..., d:]], 2)                             # [B, n, 2r, d]
     both_gate = torch.cat([prev_gate, gate[..., d:]], 2)
     pooled = (both_kv * torch.softmax(both_gate, dim=2)).sum(2)
-    pooled = self.kv_norm(pooled.to(x.dtype))
+    pooled = self.kv_norm(pooled.to(dtype))
     return rope_pairs(pooled, start, theta, rope_dim)
 
 
@@ -104,6 +114,12 @@ def block_visible(positions: torch.Tensor, n: int, r: int) -> torch.Tensor:
   """[B, S, n] bool: block j (first position p_j) is visible to a query at position p once p_j + r <= p + 1."""
   start = positions[:, :n * r:r]
   return (start[:, None, :] + r) <= (positions[:, :, None] + 1)
+
+
+def block_visible_at(query_positions: torch.Tensor, n: int, r: int) -> torch.Tensor:
+  """As `block_visible` for rows whose cached tokens sit at positions 0, 1, 2, ...: block j starts at j * r."""
+  start = torch.arange(n, device=query_positions.device) * r
+  return (start[None, None, :] + r) <= (query_positions[:, :, None] + 1)
 
 
 def block_segments(segment_ids: torch.Tensor | None, n: int, r: int):
@@ -125,23 +141,24 @@ class V4Indexer:
     self.pool = _Pool(b, c, ratio, self.d, 2)
     self.weights_proj = b.sub("weights_proj").linear("kernel", (c.emb_dim,), (self.h,), ("embed", "indexer_weights"))
 
-  def scores(self, x, q_latent, positions, theta, rope_dim):
-    """[B, S, n] fp32 relevance of every pooled block for every query (before masking)."""
+  def scores(self, x, q_latent, positions, theta, rope_dim, keys=None):
+    """[B, S, n] fp32 relevance of every pooled block for every query (before masking). `keys` [B, n, d]: pooled index
+    entries that the caller already has (decoding from a cache); by default they are pooled from x."""
     B, S, _ = x.shape
-    keys = self.pool.overlapping(x, positions, theta, rope_dim).float()                     # [B, n, d]
+    keys = (self.pool.overlapping(x, positions, theta, rope_dim) if keys is None else keys).float()       # [B, n, d]
     q = F.linear(q_latent, self.q_proj).view(B, S, self.h, self.d)
     q = rope_pairs(q, positions, theta, rope_dim).float()
     s = torch.relu(torch.einsum("bshd,bnd->bshn", q, keys)) * self.d ** -0.5
     w = F.linear(x, self.weights_proj).float() * self.h ** -0.5
     return torch.einsum("bshn,bsh->bsn", s, w)
 
-  def select(self, x, q_latent, positions, allowed, theta, rope_dim):
+  def select(self, x, q_latent, positions, allowed, theta, rope_dim, keys=None):
     """allowed [B, S, n] bool -> [B, S, n] bool: the (at most) top-k allowed blocks of every query."""
     n = allowed.shape[-1]
     if n == 0:
       return allowed
     with torch.no_grad():
-      sc = self.scores(x, q_latent, positions, theta, rope_dim).masked_fill(~allowed, -math.inf)
+      sc = self.scores(x, q_latent, positions, theta, rope_dim, keys).masked_fill(~allowed, -math.inf)
       k = min(self.topk, n)
       idx = sc.topk(k, dim=-1).indices
       chosen = torch.zeros_like(allowed).scatter_(-1, idx, True)
@@ -238,9 +255,58 @@ class CompressedAttention:
         outs.append(self._attend(q, kv, positions, segment_ids, ent, allowed, s0, s1))
     return outs[0] if len(outs) == 1 else torch.cat(outs, 1)
 
+  def make_cache(self, slots: int, max_len: int, dtype, device) -> "CompressedLayerCache":
+    return CompressedLayerCache(self, slots, max_len, dtype, device)
+
+  def _cached(self, x, ctx):
+    """Prefill into / decode from a `CompressedLayerCache`: the new tokens' rotated key = value vectors and their pooling
+    projections are appended at each row's length; pooled entries are rebuilt from the cached per-token projections of the
+    complete blocks, so a decoded token sees exactly what it would see in one full pass."""
+    cache = ctx.cache
+    if ctx.segment_ids is not None and ctx.mode == "prefill" and bool((ctx.segment_ids != ctx.segment_ids[:, :1]).any()):
+      raise NotImplementedError("several prompts packed into one prefill pass are not supported by compressed attention")
+    B, S, _ = x.shape
+    pos = cache.lengths[:, None] + torch.arange(S, device=x.device)[None]
+    q, kv, qn = self.project(x, pos)
+    rows = cache.slot_ids[:, None].expand(B, S)
+    cache.kv[rows, pos] = kv.to(cache.kv.dtype)
+    pool = self.hca if self.hca is not None else self.csa
+    if pool is not None:
+      pk, pg = pool.project(x)
+      cache.pool_kv[rows, pos], cache.pool_gate[rows, pos] = pk, pg
+    if self.indexer is not None:
+      ik, ig = self.indexer.pool.project(x)
+      cache.idx_kv[rows, pos], cache.idx_gate[rows, pos] = ik, ig
+    upto = int((cache.lengths.max() + S).item())
+    kv_all = cache.kv[cache.slot_ids, :upto]
+    kpos = torch.arange(upto, device=x.device)[None].expand(B, upto)
+    m = (kpos[:, None, :] <= pos[:, :, None]) & (kpos[:, None, :] < (cache.lengths + S)[:, None, None])
+    if self.window > 0:
+      m = m & (pos[:, :, None] - kpos[:, None, :] < self.window)
+    keys = kv_all
+    if pool is not None and upto // self.r > 0:
+      n = upto // self.r
+      sl = cache.slot_ids
+      ent = (pool.closed_from if self.hca is not None else pool.overlapping_from)(
+          cache.pool_kv[sl, :upto], cache.pool_gate[sl, :upto], kpos, self.theta, self.rope_dim, x.dtype)
+      allowed = block_visible_at(pos, n, self.r)
+      if self.indexer is not None:
+        ikeys = self.indexer.pool.overlapping_from(cache.idx_kv[sl, :upto], cache.idx_gate[sl, :upto], kpos, self.theta, self.rope_dim, x.dtype)
+        allowed = self.indexer.select(x, qn, pos, allowed, self.theta, self.rope_dim, keys=ikeys)
+      keys = torch.cat([kv_all, ent], 1)
+      m = torch.cat([m, allowed], -1)
+    qf, kf = q.float(), keys.float()
+    logits = torch.einsum("bshd,bkd->bhsk", qf, kf).masked_fill(~m[:, None], -1e30)
+    sink = self.sinks.leaf().float().view(1, -1, 1, 1).expand(B, -1, S, 1)
+    p = torch.softmax(torch.cat([logits, sink], -1), -1)[..., :-1].masked_fill(~m[:, None], 0.0)
+    out = torch.einsum("bhsk,bkd->bshd", p, kf).to(q.dtype)
+    out = rope_pairs(out, pos, self.theta, self.rope_dim, reverse=True)
+    grouped = torch.einsum("bsgi,gio->bsgo", out.reshape(B, S, self.g, self.per_group), self.o_a.leaf().to(out.dtype))
+    return F.linear(grouped.reshape(B, S, self.g * self.o_rank), self.o_b)
+
   def __call__(self, x, ctx):
     if ctx.cache is not None:
-      raise NotImplementedError("compressed attention has no decode cache; prefill / train only")
+      return self._cached(x, ctx)
     if ctx.cp_size > 1:
       raise NotImplementedError("compressed attention is not implemented under context parallelism")
     B, S, _ = x.shape
@@ -253,3 +319,30 @@ class CompressedAttention:
     ctx.keep("context", out)
     grouped = torch.einsum("bsgi,gio->bsgo", out.reshape(B, S, self.g, self.per_group), self.o_a.leaf().to(out.dtype))
     return F.linear(grouped.reshape(B, S, self.g * self.o_rank), self.o_b)
+
+
+class CompressedLayerCache:
+  """Per-slot cache of one compressed-attention layer: the rotated key = value vector of every token, and the per-token
+  pooling projections (kv and gate, for the layer's compressor and, in sparse layers, for the indexer) from which the pooled
+  entries of complete blocks are rebuilt. `token_buffers` names the [slots, max_len, ...] tensors an engine copies on insert."""
+
+  def __init__(self, attn: CompressedAttention, slots: int, max_len: int, dtype, device):
+    self.slots, self.max_len = slots, max_len
+    self.kv = torch.zeros(slots, max_len, attn.dh, dtype=dtype, device=device)
+    names = ["kv"]
+    pool = attn.hca if attn.hca is not None else attn.csa
+    if pool is not None:
+      w = pool.mult * pool.dim
+      self.pool_kv = torch.zeros(slots, max_len, w, dtype=torch.float32, device=device)
+      self.pool_gate = torch.zeros(slots, max_len, w, dtype=torch.float32, device=device)
+      names += ["pool_kv", "pool_gate"]
+    if attn.indexer is not None:
+      w = attn.indexer.pool.mult * attn.indexer.pool.dim
+      self.idx_kv = torch.zeros(slots, max_len, w, dtype=torch.float32, device=device)
+      self.idx_gate = torch.zeros(slots, max_len, w, dtype=torch.float32, device=device)
+      names += ["idx_kv", "idx_gate"]
+    self.token_buffers = tuple(names)
+    self.slot_ids = self.lengths = None
+
+  def bind(self, slot_ids, lengths):
+    self.slot_ids, self.lengths = slot_ids, lengths

@@ -35,6 +35,8 @@ FAMILIES = {
                         "gdn_value_head_dim=8", "gdn_num_key_heads=2", "gdn_num_value_heads=4", "gdn_chunk_size=8"],
     "gemma4-26b": ["base_num_decoder_layers=6", "sliding_window_size=8", "global_head_dim=32", "global_num_kv_heads=1", "num_experts=4",
                    "num_experts_per_tok=2", "base_moe_mlp_dim=32", "shared_experts=1", "tokenizer_type=byte"],
+    "deepseek4-tiny": ["base_num_decoder_layers=5", "compress_ratios=[0,4,8,8,4]", "first_num_hash_layers=1", "tokenizer_type=byte",
+                       "sliding_window_size=8", "qk_rope_head_dim=8", "indexer_head_dim=16", "indexer_topk=2"],
     "envy-test": ["num_experts=4", "num_experts_per_tok=1", "base_moe_mlp_dim=32", "base_num_decoder_layers=4", "tokenizer_type=byte"],
     "gpt-oss-20b": ["base_num_decoder_layers=2", "num_experts=4", "num_experts_per_tok=2", "base_moe_mlp_dim=32", "sliding_window_size=8"],
 }

@@ -15,7 +15,7 @@ def _engine(model="llama3-8b", extra=()):
 
 
 @pytest.mark.parametrize("model", ["llama3-8b", "gemma2-2b", "gemma3-4b", "deepseek2-16b", "deepseek3-tiny", "qwen3-8b", "mixtral-8x7b",
-                                   "gpt-oss-20b", "olmo3-7b", "llama4-17b-16e", "qwen2.5-7b", "qwen3-next-80b-a3b", "gemma4-26b", "envy-test"])
+                                   "gpt-oss-20b", "olmo3-7b", "llama4-17b-16e", "qwen2.5-7b", "qwen3-next-80b-a3b", "gemma4-26b", "envy-test", "deepseek4-tiny"])
 def test_greedy_decode_matches_full_forward(model):
   eng, cfg = _engine(model)
   torch.manual_seed(0)
