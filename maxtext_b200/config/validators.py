@@ -251,8 +251,9 @@ def check_schedules_and_distillation(t):
 
 def check_misc(t):
   """Single-key ranges and pairings from src/maxtext/configs/types.py:3183-3197, 3356-3420, 3815-3818, 3884-3930, 4280-4330."""
-  if (_g(t, "load_parameters_path", "") or _g(t, "load_full_state_path", "")) and not _g(t, "enable_checkpointing", True):
-    _fail("You must set enable_checkpointing=True to load a checkpoint.")
+  if _g(t, "load_full_state_path", "") and not _g(t, "enable_checkpointing", True):
+    # parameters alone (`load_parameters_path`) load without the checkpoint manager here; a full state needs it
+    _fail("You must set enable_checkpointing=True to load a full training state.")
   if _g(t, "enable_multi_tier_checkpointing", False):
     mins, steps = t.get("multi_tier_checkpointing_backup_interval_minutes"), t.get("multi_tier_checkpointing_backup_interval_steps")
     if (_num(mins) is None) == (_num(steps) is None):

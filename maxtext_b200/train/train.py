@@ -100,6 +100,11 @@ def train_loop(config, engine=None, mesh=None, data_iterator=None, recorder=None
     if adapter_dir:
       from ..utils import lora_utils
       lora_utils.load_adapter(adapter_dir, engine.store, c)
+  if lora_on and start_step == 0:
+    from ..utils import nf4
+    n_q = nf4.snap_store(engine.store, c)             # QLoRA: the frozen base weights take their 4-bit NormalFloat values
+    if n_q and rank == 0:
+      max_logging.log(f"QLoRA: {n_q} base weights rounded to nf4 (tile {lora_cfg.get('lora_tile_size') or nf4.DEFAULT_TILE})")
   engine.step_count = start_step
   is_cuda = engine.device.type == "cuda"
   stepper = engine

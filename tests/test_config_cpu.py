@@ -155,7 +155,7 @@ REJECTED = [
     (["distill_temperature_end=0"], "distill_temperature_end must be > 0"),
     (["distill_beta=0.0", "distill_beta_end=0.5"], "distill_beta_end=0.5"),
     (["distill_alpha_schedule=linear"], "distill_alpha_end is None"),
-    (["load_parameters_path=/tmp/none", "enable_checkpointing=false"], "enable_checkpointing=True to load"),
+    (["load_full_state_path=/tmp/none", "enable_checkpointing=false"], "enable_checkpointing=True to load"),
     (["enable_multi_tier_checkpointing=true", "local_checkpoint_directory=/tmp/x", "local_checkpoint_period=2"], "Exactly one of"),
     (["elastic_backup_kind=tape"], "elastic_backup_kind"),
     (["context_parallel_strategy=spiral"], "context_parallel_strategy"),

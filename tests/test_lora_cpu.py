@@ -159,3 +159,44 @@ def test_trainable_parameters_mask_and_adamw_mask():
   for n, p in eng2.store.params.items():
     same = torch.equal(before[n], eng2.store.full_master(p))
     assert same == ("norm" in n or "embedding" in n), n
+
+
+def test_nf4_codes_round_trip_and_error_is_bounded():
+  from maxtext_b200.utils import nf4
+  torch.manual_seed(0)
+  w = torch.randn(24, 128) * 0.05
+  codes, absmax = nf4.quantize(w, 64)
+  assert codes.dtype == torch.uint8 and int(codes.max()) <= 15 and absmax.shape == (48,)
+  assert torch.equal(nf4.unpack(nf4.pack(codes)), codes) and nf4.pack(codes).numel() == w.numel() // 2
+  back = nf4.dequantize(codes, absmax, w.shape, 64)
+  # every value lands on its nearest level: the error is at most half the widest gap (0.16 of the tile's maximum)
+  assert float(((back - w).abs() / absmax.repeat_interleave(64).view_as(w)).max()) <= 0.17
+  assert torch.equal(nf4.snap(back, 64), back)                    # the grid is a fixed point
+  # the extreme of every tile is kept exactly
+  t = w.view(-1, 64)
+  big = t.abs().argmax(1)
+  assert torch.allclose(back.view(-1, 64).gather(1, big[:, None]), t.gather(1, big[:, None]))
+  import pytest
+  with pytest.raises(ValueError):
+    nf4.quantize(torch.randn(4, 100), 64)
+
+
+def test_qlora_rounds_only_the_adapted_base_weights_and_still_trains():
+  from maxtext_b200.utils import nf4
+  q = ["lora={enable_lora: true, lora_rank: 4, lora_alpha: 8.0, lora_weight_qtype: nf4, lora_tile_size: 32}", "weight_init=normal"]
+  eng = make_engine(tiny_config("llama3-8b", q))
+  before = {n: eng.store.full_master(p).clone() for n, p in eng.store.params.items()}
+  n = nf4.snap_store(eng.store, eng.config)
+  adapted = {p.name for p, _, _, _ in lora_utils.adapted(eng.store)}
+  assert n == len(adapted) > 0
+  for name, p in eng.store.params.items():
+    now = eng.store.full_master(p)
+    if name in adapted:
+      assert not torch.equal(now, before[name]) and torch.equal(nf4.snap(now.float(), 32).view_as(now), now.float())
+      assert len(torch.unique((now.float().view(-1, 32) / now.float().view(-1, 32).abs().amax(1, keepdim=True)).round(decimals=4))) <= 16
+    else:
+      assert torch.equal(now, before[name])
+  batch = batch_of(eng.config)
+  losses = [float(eng.train_step(batch)["learning/loss"]) for _ in range(5)]
+  assert losses[-1] < losses[0]
+  assert nf4.snap_store(eng.store, tiny_config("llama3-8b", LORA)) == 0          # plain LoRA leaves the base alone
