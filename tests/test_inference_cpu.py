@@ -388,3 +388,30 @@ def test_prefill_packing_buckets_and_offline_engine_agree_with_single_prefills()
   assert int(first.data[0, 0]) == got["r1"]
   with pytest.raises(ValueError):
     proc.process(state, 0, "big", list(range(9)), 8)
+
+
+def test_mmlu_prompt_parsing_grouping_and_both_scoring_modes(tmp_path):
+  import json
+  from maxtext_b200.benchmarks.mmlu import mmlu_eval as M
+  from maxtext_b200.benchmarks.mmlu.subjects import AREA_OF, FIELD_OF
+  from maxtext_b200.input_pipeline.tokenizer import ByteTokenizer
+  assert len(FIELD_OF) == 57 and FIELD_OF["college_computer_science"] == "computer science" and AREA_OF["law"] == "humanities"
+  p = M.construct_prompt("high_school_physics", "What falls?", ["Up", "Apples", "Nothing", "Sky"])
+  assert "about high school physics." in p and "B. Apples" in p and p.endswith("Answer:")
+  assert M.parse_answer("Answer: c because") == "C" and M.parse_answer("so The answer is (B).") == "B" and M.parse_answer("no idea") is None
+  f = tmp_path / "mmlu.jsonl"
+  rows = [{"subject": "anatomy", "question": f"q{i}", "choices": ["a", "b", "c", "d"], "answer": "ABCD"[i % 4] if i % 2 else i % 4} for i in range(6)]
+  f.write_text("\n".join(json.dumps(r) for r in rows))
+  samples = M.load_samples(str(f), limit=5)
+  assert len(samples) == 5 and samples[1]["answer"] == 1 and samples[2]["answer"] == 2
+  eng, cfg = _engine(extra=["vocab_size=300", "max_prefill_predict_length=40", "max_target_length=64"])
+  tok = ByteTokenizer()
+  for mode in ("loglik", "generate"):
+    rep = M.evaluate(eng, tok, samples, mode=mode, max_new_tokens=3)
+    assert rep["total"] == 5 and 0.0 <= rep["accuracy"] <= 1.0 and set(rep["subject"]) == {"anatomy"} and set(rep["area"]) == {"other (business, health, misc.)"}
+  t = M.Tally()
+  t.add("astronomy", True)
+  t.add("astronomy", False)
+  t.add("jurisprudence", True)
+  r = t.report()
+  assert r["accuracy"] == 2 / 3 and r["subject"]["astronomy"] == 0.5 and r["area"] == {"STEM": 0.5, "humanities": 1.0}
