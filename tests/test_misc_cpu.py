@@ -287,3 +287,21 @@ def test_prometheus_endpoint_serves_step_metrics():
   body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
   assert "maxtext_learning_loss 2.5" in body and "maxtext_perf_step_time_seconds" in body
   ml.close()
+
+
+def test_convergence_recipe_resolves_samples_and_tokens_into_steps():
+  from maxtext_b200.benchmarks.convergence import C4_MLPERF, ConvergenceSpec, convergence_recipe
+  from maxtext_b200.benchmarks.recipes import RECIPES
+  spec = ConvergenceSpec(warmup_samples=1000, decay_end_samples=10000, total_tokens_to_train=64 * 8192 * 500, learning_rate_per_sample=1e-6,
+                         eval_interval_tokens=64 * 8192 * 50, target_eval_loss=2.7)
+  r = convergence_recipe(RECIPES["llama3_8b_8192_fsdp8"], C4_MLPERF, spec, gpus=8, global_batch=64)
+  t = r.tuning
+  assert t["steps"] == 500 and t["per_device_batch_size"] == 8.0 and abs(t["learning_rate"] - 6.4e-5) < 1e-12
+  assert t["learning_rate_schedule_steps"] == 157 and abs(t["warmup_steps_fraction"] - 16 / 157) < 1e-9
+  assert t["eval_interval"] == 50 and t["eval_steps"] == -(-24567 * 2048 // (64 * 8192)) and t["dataset_type"] == "c4_mlperf"
+  assert t["target_eval_loss"] == 2.7 and r.gpus == 8 and r.name.endswith("-c4mlperf")
+  over = r.overrides()
+  assert "steps=500" in over and "dataset_type=c4_mlperf" in over and "eval_split=validation_24567exp" in over
+  # the same specification on another machine size keeps the token budget
+  r2 = convergence_recipe(RECIPES["llama3_8b_8192_fsdp8"], C4_MLPERF, spec, gpus=4, global_batch=32)
+  assert r2.tuning["steps"] == 1000 and r2.tuning["per_device_batch_size"] == 8.0
