@@ -69,7 +69,7 @@ def _canaries(fused):
     assert n > 0, "the fused path allocated no symmetric buffers"
 
 
-def train_moe_ep(rank, world, dev, fused):
+def train_moe_ep(rank, world, dev, fused, extra=()):
   """Mixtral-style model with its experts spread over the `expert` axis: peer-memory dispatch vs the NCCL all-to-all path."""
   from maxtext_b200.config import pyconfig
   from maxtext_b200.parallel import mesh as mesh_lib
@@ -81,7 +81,7 @@ def train_moe_ep(rank, world, dev, fused):
        "num_experts_per_tok=2", "base_num_decoder_layers=2", "vocab_size=4096", "max_target_length=256", "per_device_batch_size=2",
        "dataset_type=synthetic", "enable_checkpointing=false", "hardware=gpu", "weight_init=normal", "log_config=false", "steps=3",
        "learning_rate=1e-3", "warmup_steps_fraction=0.0", "ici_fsdp_parallelism=1", f"ici_expert_parallelism={world}",
-       f"use_fused_comm_kernels={'true' if fused else 'false'}"], num_devices=world)
+       f"use_fused_comm_kernels={'true' if fused else 'false'}", *extra], num_devices=world)
   mesh = mesh_lib.mesh_from_config(cfg, rank=rank, world=world)
   eng = TrainEngine(cfg, mesh, dev)
   it = T.create_data_iterator(cfg, mesh)
@@ -91,6 +91,16 @@ def train_moe_ep(rank, world, dev, fused):
     out.append((float(m["learning/loss"]), float(m["learning/raw_grad_norm"])))
   _canaries(fused)
   return out
+
+
+def train_moe_ep_split(rank, world, dev, fused):
+  """The same model with every layer run as two micro-batches on two streams (`use_batch_split_schedule`); the expert exchange
+  of the split run goes through NCCL on both settings of `fused`. The balance loss is off so that the two runs agree exactly
+  up to bf16 rounding (it is not linear in the batch)."""
+  extra = ["load_balance_loss_weight=0.0"]
+  if not fused:
+    return train_moe_ep(rank, world, dev, False, extra)
+  return train_moe_ep(rank, world, dev, True, extra + ["use_batch_split_schedule=true"])
 
 
 def train_tp(rank, world, dev, fused):
@@ -215,7 +225,7 @@ def main():
       assert backend.ext().kernel_status(True) == 0
       msg = "ok " + repr((ref, got))
     else:
-      fn = {"moe_ep": train_moe_ep, "tp": train_tp, "fsdp_tp": train_fsdp_tp}.get(mode, train)
+      fn = {"moe_ep": train_moe_ep, "moe_ep_split": train_moe_ep_split, "tp": train_tp, "fsdp_tp": train_fsdp_tp}.get(mode, train)
       a = fn(rank, world, dev, fused=False)
       b = fn(rank, world, dev, fused=True)
       for (la, na), (lb, nb) in zip(a, b):

@@ -57,6 +57,11 @@ def test_expert_parallel_peer_dispatch_matches_nccl(tmp_path):
   _run("moe_ep", tmp_path)
 
 
+def test_batch_split_schedule_with_expert_parallelism_matches_the_plain_step(tmp_path):
+  """Two micro-batches per layer on two streams, experts on two GPUs: same losses and gradient norms as the unsplit NCCL run."""
+  _run("moe_ep_split", tmp_path)
+
+
 def test_tensor_parallel_gemm_reduce_scatter_matches_nccl(tmp_path):
   _run("tp", tmp_path)
 
