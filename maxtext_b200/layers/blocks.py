@@ -96,13 +96,21 @@ class Builder:
                   n_in_dims=len(in_shape), init=init, init_scale=init_scale, tp_dim=tp_dim)
     spec = lora_spec(self.config)
     if spec is not None and spec.matches(self, leaf):
-      # W x + (alpha / r) B (A x): A [r, in] drawn like a dense kernel, B [out, r] zero, so training starts at the base model
-      assert self.tp_size == 1, "LoRA adapters are not split over the tensor axis"
+      # W x + (alpha / r) B (A x): A [r, in] drawn like a dense kernel, B [out, r] zero, so training starts at the base model.
+      # Under tensor parallelism the adapter follows its weight: a column-split W (outputs divided) gets a whole A and a B split
+      # along the outputs; a row-split W (inputs divided) gets an A split along the inputs and a whole B, whose product is a
+      # partial sum that joins W's own all-reduce. The whole factor sees rank-local data, so its gradient is a partial sum.
       r = spec.rank
+      col = tp == "col" and self.tp_size > 1
+      row = tp == "row" and self.tp_size > 1
       a = self._add(leaf + "_lora_a", shape=(r, li), ref_shape=in_shape + (r,), logical_axes=tuple(axes[:len(in_shape)]) + (None,),
-                    kind="linear", n_in_dims=len(in_shape), init="fan_in_normal")
+                    kind="linear", n_in_dims=len(in_shape), init="fan_in_normal", tp_dim=1 if row else None)
       b = self._add(leaf + "_lora_b", shape=(lo, r), ref_shape=(r,) + out_shape, logical_axes=(None,) + tuple(axes[len(in_shape):]),
-                    kind="linear", n_in_dims=1, init="zeros")
+                    kind="linear", n_in_dims=1, init="zeros", tp_dim=0 if col else None)
+      if col:
+        a.pdef.tp_partial = True
+      if row:
+        b.pdef.tp_partial = True
       p.lora = (a, b, spec.alpha / r)
     return p
 
@@ -438,7 +446,7 @@ class Attention:
     ctx.keep("context", out)
     if self.gated:
       out = (out.reshape(B, S, -1).float() * torch.sigmoid(gate.float())).to(out.dtype)
-    if tp_rt is not None and ctx.reuse("out_proj") is None and self.bo is None:
+    if tp_rt is not None and ctx.reuse("out_proj") is None and self.bo is None and self.o.lora is None:
       y = F.linear(out.reshape(B, S, -1), self.o, tp_reduce=tp_rt)
     else:
       y = F.linear(out.reshape(B, S, -1), self.o, ctx.reuse("out_proj"), self.bo if ctx.tp_size == 1 else None)
@@ -587,7 +595,7 @@ class MLP:
     else:
       h = F.linear(x, self.wi_0, bias=self.bi)
       h = ref.act_fn(self.acts[0])(h.float()).to(x.dtype) if self.acts[0] != "linear" else h
-    if tp_rt is not None and ctx.reuse("mlpwo") is None and self.bo is None:
+    if tp_rt is not None and ctx.reuse("mlpwo") is None and self.bo is None and self.wo.lora is None:
       y = F.linear(h, self.wo, tp_reduce=tp_rt)
     else:
       y = F.linear(h, self.wo, ctx.reuse("mlpwo"), self.bo if ctx.tp_size == 1 else None)

@@ -587,10 +587,15 @@ class TrainEngine:
       tg = mesh.group(tp_axes)
       for u in store.units.values():
         for p, off in zip(u.params, u.offsets):
-          if p.pdef.tp_partial:
-            assert u.group_size == 1, "tensor-partial parameters live in replicated units"
-            a = u.shard_offset + off
-            dist.all_reduce(store.grad_shard[a: a + p.pdef.numel], group=tg)
+          if p.pdef.tp_partial and not p.pdef.frozen:
+            # the part of this tensor that lies in this rank's shard of the unit (all of it when the unit is not sharded); the
+            # tensor ranks that share a shard index hold the same part
+            lo_ = u.group_rank * u.chunk if u.group_size > 1 else 0
+            hi_ = lo_ + (u.chunk if u.group_size > 1 else u.numel)
+            s0, s1 = max(off, lo_), min(off + p.pdef.numel, hi_)
+            if s1 > s0:
+              a = u.shard_offset + (s0 - lo_)
+              dist.all_reduce(store.grad_shard[a: a + (s1 - s0)], group=tg)
 
   def _grad_sumsq(self):
     """Sum of squares of the (un-normalised) global gradient: local shards, de-duplicated, all-reduced."""

@@ -352,3 +352,18 @@ def test_checkpoint_written_under_one_layout_resumes_under_another(tmp_path):
   assert len(rest_tp) == 2 and len(rest_one) == 2
   _close(rest_tp, full[4:], 2e-4)
   _close(rest_one, full[4:], 2e-4)
+
+
+@pytest.mark.parametrize("layout", ["tp2", "fsdp2xtp2"])
+def test_lora_adapters_under_tensor_parallelism_match_single(tmp_path, layout):
+  """Adapters follow their weight's split (column: B split, row: A split); the whole factor's gradient is summed over the
+  tensor ranks, also when the unit is sharded over fsdp as well."""
+  lora = ["lora={enable_lora: true, lora_rank: 4, lora_alpha: 8.0}", "weight_init=normal", "learning_rate=1e-2"]
+  one = run_ranks(1, lora + ["per_device_batch_size=4"], str(tmp_path), "one")
+  # the global batch is per_device_batch_size x ranks, whatever the ranks are used for
+  world, par = (2, ["per_device_batch_size=2", "ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"]) if layout == "tp2" else \
+      (4, ["per_device_batch_size=1", "ici_fsdp_parallelism=2", "ici_tensor_parallelism=2"])
+  got = run_ranks(world, lora + par, str(tmp_path), layout)
+  _close(got["loss"], one["loss"], 2e-4)
+  _close(got["grad_norm"], one["grad_norm"], 2e-3)
+  assert one["loss"][-1] < one["loss"][0]
