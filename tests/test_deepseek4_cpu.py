@@ -117,7 +117,9 @@ def _naive_layer(att, x, positions, seg):
 def test_layer_matches_per_query_restatement(ratio, packed):
   cfg, att, LayerCtx = _layer(ratio)
   B, S = 2, 40
-  x = torch.randn(B, S, cfg.emb_dim)
+  # fixed inputs: with two index scores within rounding of each other the vectorised top-k and the per-query sort could pick
+  # different blocks, which is a legitimate tie, not an error
+  x = torch.randn(B, S, cfg.emb_dim, generator=torch.Generator().manual_seed(100 + ratio + int(packed)))
   if packed:
     # two documents per row; the boundary (18) cuts through a block of 4 and of 8
     seg = torch.cat([torch.ones(B, 18), torch.full((B, 22), 2.0)], 1).long()
@@ -134,7 +136,7 @@ def test_layer_matches_per_query_restatement(ratio, packed):
 def test_query_chunking_does_not_change_values_or_gradients(monkeypatch):
   from maxtext_b200.layers import attention_compressed as ac
   cfg, att, LayerCtx = _layer(4)
-  x = torch.randn(1, 48, cfg.emb_dim, requires_grad=True)
+  x = torch.randn(1, 48, cfg.emb_dim, generator=torch.Generator().manual_seed(7)).requires_grad_(True)
   pos = torch.arange(48)[None]
   a = att(x, LayerCtx(cfg, pos, None))
   ga, = torch.autograd.grad(a.sum(), x)
@@ -146,7 +148,7 @@ def test_query_chunking_does_not_change_values_or_gradients(monkeypatch):
 
 def test_sparse_layer_keeps_at_most_topk_blocks():
   cfg, att, LayerCtx = _layer(4)
-  x = torch.randn(2, 64, cfg.emb_dim)
+  x = torch.randn(2, 64, cfg.emb_dim, generator=torch.Generator().manual_seed(8))
   pos = torch.arange(64)[None].expand(2, 64)
   with torch.no_grad():
     _, _, qn = att.project(x, pos)

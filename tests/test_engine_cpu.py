@@ -30,7 +30,7 @@ def test_family_trains_and_gradient_matches_directional_derivative(model):
   v = torch.randn_like(g)
   v = v / v.norm()
   # routed models: a larger step crosses routing flips (the loss jumps)
-  eps = 1e-3 if model.startswith(("qwen3-next", "qwen3.5")) else 5e-3 if model.startswith(("llama4", "qwen3-30b")) else 1e-3 if model.startswith(("envy", "gemma4")) else 2e-2
+  eps = 1e-3 if model.startswith(("qwen3-next", "qwen3.5")) else 5e-3 if model.startswith(("llama4", "qwen3-30b")) else 1e-3 if model.startswith(("envy", "gemma4", "deepseek4")) else 2e-2
   w0 = store.master.clone()
   store.master.copy_(w0 + eps * v)
   store.sync_compute_from_master()
