@@ -367,3 +367,19 @@ def test_lora_adapters_under_tensor_parallelism_match_single(tmp_path, layout):
   _close(got["loss"], one["loss"], 2e-4)
   _close(got["grad_norm"], one["grad_norm"], 2e-3)
   assert one["loss"][-1] < one["loss"][0]
+
+
+def test_two_slices_data_parallel_over_dcn_and_fsdp_inside_match_single(single, tmp_path):
+  """num_slices=2: the `data` axis spans the slices (dcn), fsdp stays inside a slice (ici). Ranks of one slice are contiguous, the
+  gradient is reduce-scattered inside the slice and only the shards cross slices."""
+  from maxtext_b200.config import pyconfig
+  from maxtext_b200.parallel.mesh import Mesh
+  over = ["per_device_batch_size=1", "num_slices=2", "dcn_data_parallelism=2", "ici_fsdp_parallelism=2"]
+  cfg = pyconfig.initialize(["t", os.path.join(ROOT, "maxtext_b200/configs/base.yml")] + _merge(BASE, over), num_devices=4)
+  assert dict(zip(cfg.mesh_axes, cfg.mesh_shape))["data"] == 2 and dict(zip(cfg.mesh_axes, cfg.mesh_shape))["fsdp"] == 2
+  m = Mesh(list(cfg.mesh_axes), list(cfg.mesh_shape), rank=0, world=4)
+  assert m.ranks_along(("fsdp",), 0) == [0, 1] and m.ranks_along(("fsdp",), 2) == [2, 3]      # a slice = consecutive ranks
+  assert m.ranks_along(("data",), 0) == [0, 2]
+  got = run_ranks(4, over, str(tmp_path), "dcn2")
+  _close(got["loss"], single["loss"], 2e-4)
+  _close(got["grad_norm"], single["grad_norm"], 2e-3)
