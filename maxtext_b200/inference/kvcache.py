@@ -33,7 +33,15 @@ class KVQuant:
 class LayerKVCache:
   """Cache of one attention layer for `slots` concurrent sequences."""
 
-  def __init__(self, slots, max_len, kv_heads, head_dim, v_dim, dtype, device, quant: KVQuant | None = None):
+  def __init__(self, slots, max_len, kv_heads, head_dim, v_dim, dtype, device, quant: KVQuant | None = None, seq_group=None,
+               seq_rank: int = 0, seq_size: int = 1):
+    """`seq_size` > 1 (the `context_autoregressive` mesh axis, src/maxtext/configs/base.yml `ici_context_autoregressive_parallelism`):
+    the cache is split along the sequence, position p lives on rank p mod seq_size at row p div seq_size, every rank attends over
+    its own rows and the partial results are merged with their log-sum-exp."""
+    self.seq_group, self.seq_rank, self.seq_size = seq_group, int(seq_rank), int(seq_size)
+    self.global_len = max_len
+    if self.seq_size > 1:
+      max_len = -(-max_len // self.seq_size)
     self.slots, self.max_len, self.quant = slots, max_len, quant
     sd = quant.tdtype if quant else dtype
     self.dtype = dtype
@@ -47,6 +55,44 @@ class LayerKVCache:
 
   def bind(self, slot_ids, lengths):
     self.slot_ids, self.lengths = slot_ids, lengths
+
+  def rows_for(self, n: int) -> int:
+    """Rows of this rank's part that hold a prompt of n tokens."""
+    return n if self.seq_size == 1 else -(-n // self.seq_size)
+
+  def _attend_split(self, q, k, v, ctx, window, soft_cap, sinks):
+    """Sequence-split cache: write the new tokens this rank owns, attend over the local rows, merge over the ranks."""
+    import torch.distributed as dist
+    B, S = q.shape[:2]
+    N, r = self.seq_size, self.seq_rank
+    pos = self.lengths[:, None] + torch.arange(S, device=q.device)[None]
+    mine = (pos % N) == r
+    rows = self.slot_ids[:, None].expand(B, S)
+    for buf, sbuf, x in ((self.k, getattr(self, "ks", None), k), (self.v, getattr(self, "vs", None), v)):
+      if self.quant:
+        qx, sx = self.quant.quantize(x)
+        buf[rows[mine], (pos // N)[mine]] = qx[mine]
+        sbuf[rows[mine], (pos // N)[mine]] = sx[mine]
+      else:
+        buf[rows[mine], (pos // N)[mine]] = x[mine].to(buf.dtype)
+    upto = self.rows_for(int((self.lengths.max() + S).item()))
+    K, V = self._read(self.k, getattr(self, "ks", None), upto), self._read(self.v, getattr(self, "vs", None), upto)
+    kv_pos = (torch.arange(upto, device=q.device) * N + r)[None].expand(B, upto)
+    mask = ref.attention_mask(pos, kv_pos, None, None, True, window) & (kv_pos < (self.lengths + S)[:, None])[:, None, None, :]
+    if ctx.segment_ids is not None and ctx.mode == "prefill":
+      mask = mask & (ctx.segment_ids[:, None, :, None] != 0)
+    sk = sinks.data if (sinks is not None and r == 0) else None            # the sink joins the denominator once
+    out, lse = ref.attention(q, K, V, mask, 1.0, soft_cap, sinks=sk, return_lse=True)
+    empty = ~mask.any(-1)                                                  # [B, 1, S]: no key of this rank is visible
+    lse = lse.masked_fill(empty.expand_as(lse), float("-inf")) if sk is None else lse
+    outs = [torch.empty_like(out) for _ in range(N)]
+    lses = [torch.empty_like(lse) for _ in range(N)]
+    dist.all_gather(outs, out.contiguous(), group=self.seq_group)
+    dist.all_gather(lses, lse.contiguous(), group=self.seq_group)
+    L = torch.stack(lses)                                                  # [N, B, H, S]
+    w = torch.softmax(L, 0).nan_to_num(0.0)
+    O = torch.stack(outs).float()                                          # [N, B, S, H, D]
+    return (O * w.permute(0, 1, 3, 2)[..., None]).sum(0).to(q.dtype)
 
   def _write(self, buf, sbuf, x, pos):
     B, S = x.shape[:2]
@@ -75,6 +121,10 @@ class LayerKVCache:
   def attend(self, q, k, v, ctx, window=0, soft_cap=0.0, sinks=None):
     """Append k/v of the S new tokens at each row's current length, then attend over everything cached."""
     B, S = q.shape[:2]
+    if self.seq_size > 1:
+      if getattr(ctx, "bidir", None) is not None:
+        raise NotImplementedError("a sequence-split cache does not take bidirectional image blocks")
+      return self._attend_split(q, k, v, ctx, window, soft_cap, sinks)
     pos = self.lengths[:, None] + torch.arange(S, device=q.device)[None]           # absolute positions of the new tokens
     self._write(self.k, getattr(self, "ks", None), k, pos)
     self._write(self.v, getattr(self, "vs", None), v, pos)
@@ -137,10 +187,15 @@ def make_caches(model, slots: int, max_len: int, device, quantize: bool = False)
   c = model.config
   dt = model.store.compute_dtype
   quant = KVQuant(c.kv_quant_dtype) if (quantize or c.quantize_kvcache) else None
+  mesh = getattr(model, "mesh", None)
+  seq_size = mesh.axis_size("context_autoregressive") if mesh is not None else 1
+  seq = dict(seq_group=mesh.group("context_autoregressive"), seq_rank=mesh.axis_index("context_autoregressive"), seq_size=seq_size) if seq_size > 1 else {}
   out = []
   for layer in model.layers:
     per_layer = []
     for blk in layer.blocks:
+      if seq_size > 1 and blk.plan.attention in ("mla", "gdn", "compressed"):
+        raise NotImplementedError("context_autoregressive parallelism splits plain key / value caches only")
       if blk.plan.attention == "mla":
         per_layer.append(MlaLayerCache(slots, max_len, c.kv_lora_rank, c.qk_rope_head_dim, dt, device))
       elif blk.plan.attention == "compressed":
@@ -151,6 +206,6 @@ def make_caches(model, slots: int, max_len: int, device, quantize: bool = False)
         per_layer.append(GDNState(slots, a.conv_dim, a.K, a.hv, a.dk, a.dv, device))
       else:
         a = blk.attn
-        per_layer.append(LayerKVCache(slots, max_len, a.hkv_l, a.dh, a.dh, dt, device, quant))
+        per_layer.append(LayerKVCache(slots, max_len, a.hkv_l, a.dh, a.dh, dt, device, quant, **seq))
     out.append(per_layer)
   return out

@@ -257,9 +257,10 @@ class MaxEngine:
       raise ValueError(f"insert: slot {slot} is outside [0, {int(state.tokens.shape[0])})")
     for dst_layer, src_layer in zip(state.caches, prefix.caches):
       for d, s in zip(dst_layer, src_layer):
+        m = s.rows_for(n) if hasattr(s, "rows_for") else n          # rows of this rank's part of a sequence-split cache
         for name in ("k", "v", "ks", "vs", "latent", "k_rope") + tuple(getattr(s, "token_buffers", ())):
           if hasattr(s, name) and hasattr(d, name):
-            getattr(d, name)[slot, :n] = getattr(s, name)[0, :n]
+            getattr(d, name)[slot, :m] = getattr(s, name)[0, :m]
         for name in ("conv", "rec"):                 # fixed-size recurrent state (gated delta layers)
           if hasattr(s, name) and hasattr(d, name):
             getattr(d, name)[slot] = getattr(s, name)[0]

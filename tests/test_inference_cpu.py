@@ -216,6 +216,10 @@ def test_tensor_parallel_decode_matches_single_rank(tmp_path):
   two = run(2, base + ["ici_fsdp_parallelism=1", "ici_tensor_parallelism=2"], "tp2")
   assert one["tokens"] == two["tokens"]
   assert all(abs(a - b) < 1e-5 for a, b in zip(one["logits"], two["logits"]))
+  # the cache split along the sequence over two ranks (positions alternate between them), partial attention merged by log-sum-exp
+  seq = run(2, base + ["ici_fsdp_parallelism=1", "ici_context_autoregressive_parallelism=2"], "car2")
+  assert one["tokens"] == seq["tokens"]
+  assert all(abs(a - b) < 1e-4 for a, b in zip(one["logits"], seq["logits"]))
 
 
 def test_prompt_lengths_that_would_overrun_the_cache_are_rejected_on_the_host():
