@@ -5,8 +5,11 @@ small OpenAI-style HTTP server (benchmarks/api_server/). Here one process owns t
 loop (`OfflineEngine`) in a background thread; HTTP handlers only enqueue requests and wait for their result, so any number of
 clients share the decode slots.
 
-  POST /v1/completions   {"prompt": "...", "max_tokens": 32}      or {"prompt_tokens": [1, 2, 3], ...}
+  POST /v1/completions        {"prompt": "..." | ["...", "..."], "max_tokens": 32}      or {"prompt_tokens": [1, 2, 3], ...}
+  POST /v1/chat/completions   {"messages": [{"role": "user", "content": "..."}], "max_tokens": 32}   (benchmarks/api_server/maxtext_server.py:144-156)
   GET  /v1/health
+A list of prompts is served as one request with one choice per prompt; the prompts share the decode slots like any others.
+Chat messages are rendered with the configured chat template (`chat_template`, `chat_template_path`) and the generation prompt.
 """
 from __future__ import annotations
 
@@ -71,21 +74,47 @@ class ServingLoop:
           inflight.remove(it)
           self.served += 1
 
+  def _generate_many(self, token_lists, max_tokens: int, timeout: float):
+    """Submit every prompt at once (they share the slots), wait for all: [(prompt tokens, output tokens, token limit)]."""
+    items = []
+    for toks in token_lists:
+      toks = toks[-int(self.config.max_prefill_predict_length):] or [0]
+      max_new = max(1, min(int(max_tokens), int(self.config.max_target_length) - len(toks) - 1))
+      items.append((toks, max_new, self.submit(toks, max_new)))
+    deadline = time.perf_counter() + timeout
+    for _, _, it in items:
+      if not it["event"].wait(max(0.0, deadline - time.perf_counter())):
+        raise TimeoutError("generation timed out")
+    return [(toks, it["request"].output, max_new) for toks, max_new, it in items]
+
   def complete(self, body: dict, timeout: float = 600.0) -> dict:
     if "prompt_tokens" in body:
-      toks = [int(t) for t in body["prompt_tokens"]]
+      pt = body["prompt_tokens"]
+      prompts = [[int(t) for t in p] for p in pt] if pt and isinstance(pt[0], (list, tuple)) else [[int(t) for t in pt]]
     else:
-      toks = self.tok.encode(str(body.get("prompt", "")), add_bos=bool(self.config.add_bos))
-    toks = toks[-int(self.config.max_prefill_predict_length):] or [0]
-    max_new = int(body.get("max_tokens", 32))
-    max_new = max(1, min(max_new, int(self.config.max_target_length) - len(toks) - 1))
+      raw = body.get("prompt", "")
+      prompts = [self.tok.encode(str(p), add_bos=bool(self.config.add_bos)) for p in (raw if isinstance(raw, (list, tuple)) else [raw])]
     t0 = time.perf_counter()
-    item = self.submit(toks, max_new)
-    if not item["event"].wait(timeout):
-      raise TimeoutError("generation timed out")
-    out = item["request"].output
+    res = self._generate_many(prompts, int(body.get("max_tokens", 32)), timeout)
     return {"object": "text_completion", "model": self.config.model_name,
-            "choices": [{"index": 0, "text": self.tok.decode(out), "tokens": out, "finish_reason": "length" if len(out) >= max_new else "stop"}],
+            "choices": [{"index": i, "text": self.tok.decode(out), "tokens": out, "finish_reason": "length" if len(out) >= mx else "stop"}
+                        for i, (_, out, mx) in enumerate(res)],
+            "usage": {"prompt_tokens": sum(len(t) for t, _, _ in res), "completion_tokens": sum(len(o) for _, o, _ in res),
+                      "total_tokens": sum(len(t) + len(o) for t, o, _ in res)},
+            "latency_s": round(time.perf_counter() - t0, 4)}
+
+  def chat(self, body: dict, timeout: float = 600.0) -> dict:
+    """OpenAI-style chat completion: the messages are rendered with the chat template plus the generation prompt."""
+    from ..input_pipeline import chat as chat_lib
+    msgs = body.get("messages")
+    if not isinstance(msgs, list) or not msgs or not all(isinstance(m, dict) and "role" in m and "content" in m for m in msgs):
+      raise ValueError("`messages` must be a non-empty list of {role, content}")
+    text = chat_lib.render(msgs, chat_lib.load_template(self.config), add_generation_prompt=True)
+    t0 = time.perf_counter()
+    toks, out, mx = self._generate_many([self.tok.encode(text, add_bos=bool(self.config.add_bos))], int(body.get("max_tokens", 32)), timeout)[0]
+    return {"object": "chat.completion", "model": self.config.model_name,
+            "choices": [{"index": 0, "message": {"role": "assistant", "content": self.tok.decode(out)},
+                         "finish_reason": "length" if len(out) >= mx else "stop"}],
             "usage": {"prompt_tokens": len(toks), "completion_tokens": len(out), "total_tokens": len(toks) + len(out)},
             "latency_s": round(time.perf_counter() - t0, 4)}
 
@@ -102,6 +131,15 @@ def create_app(loop: ServingLoop):
   def completions(body: dict):
     try:
       return loop.complete(body)
+    except TimeoutError as e:
+      raise HTTPException(status_code=504, detail=str(e)) from e
+
+  @app.post("/v1/chat/completions")
+  def chat_completions(body: dict):
+    try:
+      return loop.chat(body)
+    except ValueError as e:
+      raise HTTPException(status_code=400, detail=str(e)) from e
     except TimeoutError as e:
       raise HTTPException(status_code=504, detail=str(e)) from e
 

@@ -116,11 +116,24 @@ def test_serving_loop_batches_concurrent_requests():
   ts = [threading.Thread(target=call, args=(i,)) for i in range(2)]
   [t.start() for t in ts]
   [t.join(60) for t in ts]
-  loop.stop()
   assert [o["choices"][0]["tokens"] for o in out] == want
   assert out[0]["usage"]["prompt_tokens"] == 4 and loop.served == 2
+  # one request with two prompts: one choice each, same tokens
+  both = loop.complete({"prompt_tokens": prompts, "max_tokens": 6})
+  assert [c["tokens"] for c in both["choices"]] == want and [c["index"] for c in both["choices"]] == [0, 1]
+  # chat: the messages go through the chat template with the generation prompt
+  from maxtext_b200.input_pipeline import chat as chat_lib
+  msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+  reply = loop.chat({"messages": msgs, "max_tokens": 4})
+  text = chat_lib.render(msgs, chat_lib.load_template(cfg), add_generation_prompt=True)
+  direct = loop.complete({"prompt": text, "max_tokens": 4})
+  assert reply["object"] == "chat.completion" and reply["choices"][0]["message"]["role"] == "assistant"
+  assert reply["choices"][0]["message"]["content"] == direct["choices"][0]["text"] and reply["usage"]["prompt_tokens"] == direct["usage"]["prompt_tokens"]
+  with pytest.raises(ValueError):
+    loop.chat({"messages": []})
+  loop.stop()
   app = create_app(loop)
-  assert {r.path for r in app.routes} >= {"/v1/health", "/v1/completions"}
+  assert {r.path for r in app.routes} >= {"/v1/health", "/v1/completions", "/v1/chat/completions"}
 
 
 @pytest.mark.parametrize("model", ["llama3-8b", "deepseek2-16b"])
