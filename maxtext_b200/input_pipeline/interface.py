@@ -17,6 +17,11 @@ def _create(config, data_rank: int = 0, data_world: int = 1, split: str = "train
   if t == "synthetic":
     from .synthetic import SyntheticDataIterator
     return SyntheticDataIterator(config, data_rank, data_world)
+  if t == "olmo_grain" and str(getattr(config, "olmo_index_path", "") or ""):
+    # windows of flat token files in a seeded global shuffle (input_pipeline/olmo_data.py); without an index the type reads
+    # files like the other file pipelines
+    from .olmo_data import OlmoDataIterator
+    return OlmoDataIterator(config, data_rank, data_world, split)
   if t in ("hf", "grain", "tfds", "c4_mlperf", "olmo_grain"):
     from .file_pipeline import create_file_iterator
     it = create_file_iterator(config, data_rank, data_world, split)

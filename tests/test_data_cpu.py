@@ -339,3 +339,56 @@ def test_streaming_huggingface_dataset_backend(tmp_path):
   a = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", sh))]
   b2 = [b["inputs"].clone() for b in create_data_iterator(tiny_config("llama3-8b", sh))]
   assert all(torch.equal(x, y) for x, y in zip(a, b2)) and not all(torch.equal(x, y) for x, y in zip(a, plain))
+
+
+def test_olmo_mix_index_sampler_filter_and_resume(tmp_path):
+  """Flat token files -> windows, one seeded permutation per epoch split over the data ranks, repetitive windows masked, the
+  reader position is the batch count."""
+  import numpy as np
+  import torch
+  from helpers import tiny_config
+  from maxtext_b200.input_pipeline import olmo_data as O
+  from maxtext_b200.input_pipeline.interface import create_data_iterator
+  S = 32
+  rng = np.random.default_rng(0)
+  a = rng.integers(5, 200, size=S * 5 + 7).astype(np.uint32)           # 5 windows, 7 tokens dropped
+  b = rng.integers(5, 200, size=S * 4).astype(np.uint16)               # raw file, 4 windows
+  b[S * 2: S * 3] = np.tile(np.array([9, 8], dtype=np.uint16), S // 2)  # window 2 of b: period 2 repeated 16 times
+  b[S * 3: S * 4] = 7                                                   # window 3 of b: one token 32 times
+  np.save(tmp_path / "a.npy", a)
+  b.tofile(tmp_path / "b.bin")
+  # files of different element types need separate calls for raw data: index them together through explicit entries
+  ia = O.build_index([str(tmp_path / "a.npy")], S)
+  ib = O.build_index([str(tmp_path / "b.bin")], S, "uint16")
+  idx = O.MixIndex(S, ia.files + [O.FileEntry(**{**ib.files[0].__dict__, "instance_offset": ia.total_instances})])
+  assert idx.total_instances == 9 and [f.n_instances for f in idx.files] == [5, 4] and idx.files[0].data_offset > 0
+  f, start = idx.locate(6)
+  assert f.path.endswith("b.bin") and start == S
+  idx.save(str(tmp_path / "index.json"))
+  again = O.load_index(str(tmp_path / "index.json"), str(tmp_path), "/elsewhere")
+  assert again.files[0].path == "/elsewhere/a.npy" and again.fingerprint() == idx.fingerprint()
+  # repetition filter
+  assert O.longest_repetition(np.tile([1, 2, 3], 10)) == 10 and O.longest_repetition(np.arange(50)) == 1
+  assert not O.is_clean_instance(np.full(40, 7)) and O.is_clean_instance(np.tile([9, 8], 16)) and not O.is_clean_instance(np.tile([9, 8], 32))
+  # sampler: each epoch is a permutation split over the ranks, epochs differ
+  s0, s1 = O.OlmoSampler(9, 3, 0, 2), O.OlmoSampler(9, 3, 1, 2)
+  ep0 = [s0[i] for i in range(4)] + [s1[i] for i in range(4)]
+  assert len(set(ep0)) == 8 and [s0[i] for i in range(4)] != [s0[4 + i] for i in range(4)]
+  assert [O.OlmoSampler(9, 3, 0, 2)[i] for i in range(8)] == [s0[i] for i in range(8)]
+  # iterator through the dispatcher
+  cfg = tiny_config("llama3-8b", ["dataset_type=olmo_grain", f"olmo_index_path={tmp_path / 'index.json'}", f"max_target_length={S}",
+                                  "per_device_batch_size=3", "enable_data_shuffling=false"])
+  it = create_data_iterator(cfg)
+  batches = [next(it) for _ in range(3)]
+  flat = torch.cat([x["inputs"] for x in batches])
+  assert flat.shape == (9, S) and torch.equal(flat[0], torch.from_numpy(a[:S].astype(np.int32)))
+  assert torch.equal(batches[0]["targets"][0, :-1], batches[0]["inputs"][0, 1:]) and int(batches[0]["targets_segmentation"][0, -1]) == 0
+  seg = torch.cat([x["targets_segmentation"] for x in batches])
+  assert int(seg[8].sum()) == 0 and int(seg[7].sum()) == S - 1 and int(seg[0].sum()) == S - 1      # only the 32-fold repetition is masked
+  st = it.state()
+  nxt = next(it)
+  it2 = create_data_iterator(cfg)
+  it2.load_state(st)
+  assert torch.equal(next(it2)["inputs"], nxt["inputs"])
+  O.main(["--out", str(tmp_path / "cli.json"), "--sequence-length", str(S), str(tmp_path / "a.npy")])
+  assert O.load_index(str(tmp_path / "cli.json")).total_instances == 5
