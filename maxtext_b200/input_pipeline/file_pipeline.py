@@ -207,7 +207,10 @@ class FileDataIterator:
         except StopIteration:
           return
         yield pos, [packing._emit([ids[:S1]], S1)]
-    mode = self.c.grain_packing_type
+    # the MLPerf C4 recipe concatenates the tokenised documents and cuts rows of the target length, whatever packing type is
+    # configured for the other pipelines (src/maxtext/input_pipeline/tfds_data_processing_c4_mlperf.py `reduce_concat_tokens`
+    # + `split_tokens_to_targets_length`)
+    mode = "concat_then_split" if self.c.dataset_type == "c4_mlperf" else self.c.grain_packing_type
     while True:
       pos, window = self._pos(), []
       for ids in ts:
