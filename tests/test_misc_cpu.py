@@ -305,3 +305,23 @@ def test_convergence_recipe_resolves_samples_and_tokens_into_steps():
   # the same specification on another machine size keeps the token budget
   r2 = convergence_recipe(RECIPES["llama3_8b_8192_fsdp8"], C4_MLPERF, spec, gpus=4, global_batch=32)
   assert r2.tuning["steps"] == 1000 and r2.tuning["per_device_batch_size"] == 8.0
+
+
+def test_results_database_keeps_runs_and_ignores_throttled_ones(tmp_path):
+  from maxtext_b200.benchmarks.results_db import ResultsDB, main
+  db = ResultsDB(str(tmp_path / "runs.sqlite"))
+  line = {"metric": "tokens/sec", "value": 15436.0, "unit": "tokens/s", "n_gpus": 1, "ms_per_step": 1061.4, "dtype": "bf16",
+          "config": {"model": "llama3-8b", "parallelism": "fsdp1"}, "clocks": {"sm_mhz": 1470, "reasons": ["sw_power_cap"]},
+          "e2e": {"value": 15428.0}}
+  a = db.add(line)
+  b = db.add({**line, "value": 17000.0, "clocks": {"sm_mhz": 900, "reasons": ["hw_thermal_slowdown"]}})
+  c = db.add({**line, "value": 118000.0, "n_gpus": 8, "config": {"model": "llama3-8b", "parallelism": "fsdp8"}})
+  assert (a, b, c) == (1, 2, 3) and len(db.query(model="llama3-8b")) == 3 and len(db.query(gpus=8)) == 1
+  assert db.best(model="llama3-8b", gpus=1)["id"] == a                      # the faster run was throttled
+  assert db.best(model="llama3-8b", gpus=1, ignore_throttled=False)["id"] == b
+  assert db.record(c)["config"]["parallelism"] == "fsdp8" and db.best(model="other") is None
+  import pytest
+  with pytest.raises(ValueError):
+    db.add({"value": 1})
+  db.close()
+  assert main(["best", str(tmp_path / "runs.sqlite"), "--gpus", "8"]) == 0
