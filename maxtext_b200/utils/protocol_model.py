@@ -116,6 +116,6 @@ def epoch_flag_model(ranks: int, rounds: int, wait_before_overwrite: bool = True
     return step
 
   def invariant(st):
-    return "a rank read a peer buffer that did not hold this round's data" if st[4] else None
+    return "a rank read a peer buffer that did not hold the data of the current exchange" if st[4] else None
 
   return init, [role(r) for r in range(R)], invariant, (lambda st: all(p[0] >= rounds for p in st[0]))
