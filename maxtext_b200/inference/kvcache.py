@@ -159,6 +159,7 @@ class MlaLayerCache(LayerKVCache):
 
   def __init__(self, slots, max_len, kv_lora_rank, rope_dim, dtype, device):
     self.slots, self.max_len, self.quant, self.dtype = slots, max_len, None, dtype
+    self.seq_group, self.seq_rank, self.seq_size, self.global_len = None, 0, 1, max_len        # latent caches are not split along the sequence
     self.latent = torch.zeros(slots, max_len, kv_lora_rank, dtype=dtype, device=device)
     self.k_rope = torch.zeros(slots, max_len, rope_dim, dtype=dtype, device=device)
     self.slot_ids = self.lengths = None
