@@ -1,98 +1,42 @@
-"""Stand-alone drivers: checkpointer loop, data-loader loop, parameter-only checkpoint, FLOPs report."""
-import os
+"""Small operator tools: multi-host launcher command lines, weight comparison."""
+import io
+import subprocess
+import sys
 
 import torch
 
-from helpers import BASE_YML, TINY, make_engine, tiny_config
-from maxtext_b200.utils import generate_param_only_checkpoint, get_flops, standalone_checkpointer, standalone_dataloader
+
+def test_multihost_runner_builds_one_command_per_host_and_stops_on_failure(tmp_path, capsys):
+  from maxtext_b200.orchestration import multihost_runner as M
+  cmds = M.host_commands(["n0", "n1"], 8, ["python", "-m", "maxtext.train", "cfg.yml", "run_name=a b"], "/repo", port=1234, env={"NCCL_DEBUG": "WARN"})
+  assert len(cmds) == 2 and cmds[0][0] == "ssh" and cmds[1][-2] == "n1"
+  r1 = cmds[1][-1]
+  assert "NNODES=2" in r1 and "NODE_RANK=1" in r1 and "JAX_COORDINATOR_ADDRESS=n0" in r1 and "JAX_COORDINATOR_PORT=1234" in r1
+  assert "GPUS_PER_NODE=8" in r1 and "NCCL_DEBUG=WARN" in r1 and "gpu_multi_process_run.sh" in r1 and "'run_name=a b'" in r1
+  assert M.main(["--hosts", "a,b,c", "--dry-run", "--", "echo", "hi"]) == 0
+  assert capsys.readouterr().out.count("ssh ") == 3
+  # run(): local stand-ins for ssh; host "bad" fails, the job's exit code is its code and output lines carry the host name
+  def fake(argv, **kw):
+    host = argv[-2]
+    code = "import sys,time; print('up'); sys.stdout.flush(); " + ("sys.exit(3)" if host == "bad" else "time.sleep(30)")
+    return subprocess.Popen([sys.executable, "-c", code], **kw)
+  sink = io.StringIO()
+  rc = M.run(["good", "bad"], 1, ["true"], "/repo", runner=fake, sink=sink)
+  assert rc == 3 and "[good] up" in sink.getvalue() and "[bad] exited with 3" in sink.getvalue()
 
 
-def test_standalone_checkpointer_roundtrip(tmp_path):
-  cfg = tiny_config(extra=["steps=5", "checkpoint_period=2", "enable_checkpointing=true", "async_checkpointing=false",
-                           f"base_output_directory={tmp_path}", "run_name=sc"])
-  out = standalone_checkpointer.checkpoint_loop(cfg)
-  assert out["saves"] == 3 and out["restored_step"] == 5 and out["save_gb_per_s"] > 0 and out["roundtrip_exact"]
-  assert sorted(int(n) for n in os.listdir(cfg.checkpoint_dir) if n.isdigit()) == [0, 2, 4]
-
-
-def test_standalone_dataloader_counts_tokens():
-  cfg = tiny_config(extra=["steps=4"])
-  out = standalone_dataloader.data_load_loop(cfg)
-  assert out["batches"] == 4 and out["seq_len"] == cfg.max_target_length and out["tokens_per_second"] > 0
-
-
-def test_param_only_checkpoint_drops_optimizer_and_loads(tmp_path):
-  from maxtext_b200.checkpoint import manager as ckpt_lib
-  from maxtext_b200.train import train as train_lib
-  cfg = tiny_config(extra=["steps=2", "checkpoint_period=1", "enable_checkpointing=true", "async_checkpointing=false",
-                           f"base_output_directory={tmp_path}", "run_name=full"])
-  eng, _ = train_lib.train_loop(cfg)
-  full_step = os.path.join(cfg.checkpoint_dir, "1")
-  cfg2 = tiny_config(extra=[f"load_full_state_path={full_step}", f"base_output_directory={tmp_path}", "run_name=po",
-                            "enable_checkpointing=true"])
-  items = generate_param_only_checkpoint.generate(cfg2)
-  names = os.listdir(items)
-  assert any(n.startswith("params") for n in names) and not any(n.startswith("opt_state.0.mu") or n.startswith("opt_state.0.nu") for n in names)
-  fresh = make_engine(tiny_config())
-  ckpt_lib.load_params_only(os.path.dirname(items), fresh)
-  assert torch.equal(fresh.store.master, eng.store.master)
-
-
-def test_get_flops_llama3_8b(capsys):
-  out = get_flops.main(["t", BASE_YML, "model_name=llama3-8b", "per_device_batch_size=2", "max_target_length=8192"])
-  # 6 * params(non-embedding) * tokens + attention: the number behind the bench's TFLOP/s/device figure
-  assert 800 < out["total_tflops_per_device_per_step"] < 900
-  assert out["tokens_per_device_per_step"] == 2 * 8192
-
-
-def test_tokenizer_trainer_writes_a_loadable_sentencepiece_model(tmp_path):
-  """The vocabulary trainer samples a jsonl corpus, trains a small unigram model and the data pipeline can load it."""
-  import json
-  import pytest
-  pytest.importorskip("sentencepiece")
-  from maxtext_b200.input_pipeline.tokenizer import build_tokenizer
-  from maxtext_b200.trainers.tokenizer import train_tokenizer as tt
-  words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta", "eta", "theta", "iota", "kappa", "lambda", "omega"]
-  for j in range(2):
-    with open(tmp_path / f"c{j}.jsonl", "w") as fh:
-      for i in range(400):
-        fh.write(json.dumps({"text": " ".join(words[(i * 7 + k * 3 + j) % len(words)] for k in range(12))}) + "\n")
-  assert len(list(tt.example_texts(str(tmp_path / "*.jsonl")))) == 800
-  tt.main([f"--train_files={tmp_path}/*.jsonl", "--file_type=jsonl", "--vocab_size=64", "--max_corpus_chars=20000",
-           f"--assets_path={tmp_path}/assets", "--vocab_model_name=tok.model"])
-  model = tmp_path / "assets" / "tok.model"
-  assert model.is_file()
-  cfg = tiny_config(extra=["tokenizer_type=sentencepiece", f"tokenizer_path={model}"])
-  tok = build_tokenizer(cfg)
-  ids = tok.encode("alpha beta omega", add_bos=False, add_eos=True)
-  assert ids[-1] == 1 and "alpha" in tok.decode(ids)
-
-
-def test_layerwise_quantization_matches_whole_model_quantization(tmp_path):
-  """Quantising layer by layer from the checkpoint arrays gives the file the serving engine writes when it quantises the
-  loaded model at once, and an engine that loads it generates with the de-quantised weights."""
-  from safetensors.torch import load_file
-  from maxtext_b200.checkpoint import manager as ckpt_lib
-  from maxtext_b200.inference.maxengine import MaxEngine
-  from maxtext_b200.utils import layerwise_quantization as LQ
-  cfg = tiny_config(extra=["steps=1", "checkpoint_period=1", "enable_checkpointing=true", "async_checkpointing=false",
-                           f"base_output_directory={tmp_path}", "run_name=lq"])
-  eng = make_engine(cfg)
-  eng.store.initialize(seed=3)
-  ckpt_lib.CheckpointManager(cfg, eng).save_params_only(0)
-  src = os.path.join(cfg.checkpoint_dir, "0")
-  qcfg = cfg.replace(load_parameters_path=src, save_quantized_params_path=str(tmp_path / "q"), quantization="int8")
-  info = LQ.layerwise_quantize(qcfg)
-  assert info["layers"] == cfg.num_decoder_layers and info["quantized_bytes"] < info["fp32_bytes"] / 3
-  assert info["peak_layer_bytes"] <= info["fp32_bytes"] // cfg.num_decoder_layers + 1
-  got = load_file(info["file"])
-  whole = MaxEngine(cfg.replace(load_parameters_path=src), device=torch.device("cpu"))
-  whole.load_params()
-  ref_file = whole.save_quantized_params(str(tmp_path / "ref"), 8)
-  want = load_file(ref_file)
-  assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
-  served = MaxEngine(cfg.replace(load_parameters_path=src, checkpoint_is_quantized=True), device=torch.device("cpu"))
-  os.replace(info["file"], os.path.join(src, "quantized_params.safetensors"))
-  served.load_params()
-  name = "layers_0/mlp/wo/kernel"
-  assert torch.allclose(served.model.store.full_master(served.model.store.params[name]), whole.model.store.full_master(whole.model.store.params[name]))
+def test_weight_inspector_reports_structure_and_value_differences(tmp_path):
+  from safetensors.torch import save_file
+  from maxtext_b200.utils import weight_inspector as W
+  a = {"layers.0.w": torch.ones(4, 4), "layers.1.w": torch.arange(6.0).view(2, 3), "only_a": torch.zeros(2)}
+  b = {"layers.0.w": torch.ones(4, 4) + 1e-7, "layers.1.w": torch.arange(6.0).view(2, 3).clone(), "only_b": torch.zeros(2)}
+  b["layers.1.w"][1, 2] = 9.0
+  save_file(a, str(tmp_path / "a.safetensors"))
+  torch.save(b, str(tmp_path / "b.pt"))
+  rep = W.compare(W.load_weights(str(tmp_path / "a.safetensors")), W.load_weights(str(tmp_path / "b.pt")))
+  assert rep["only_lhs"] == ["only_a"] and rep["only_rhs"] == ["only_b"] and rep["equal"] == 1 and not rep["match"]
+  d = rep["different"][0]
+  assert d["key"] == "layers.1.w" and d["max_abs"] == 4.0 and d["at"] == 5 and abs(d["fraction"] - 1 / 6) < 1e-6
+  assert W.compare(a, b, pattern=r"layers\\.0")["match"]
+  assert W.compare({"x": torch.zeros(2, 3)}, {"x": torch.zeros(3, 2)})["shape_mismatch"][0]["lhs"] == [2, 3]
+  assert W.main(["--lhs", str(tmp_path / "a.safetensors"), "--rhs", str(tmp_path / "a.safetensors")]) == 0
