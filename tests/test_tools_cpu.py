@@ -40,3 +40,26 @@ def test_weight_inspector_reports_structure_and_value_differences(tmp_path):
   assert W.compare(a, b, pattern=r"layers\\.0")["match"]
   assert W.compare({"x": torch.zeros(2, 3)}, {"x": torch.zeros(3, 2)})["shape_mismatch"][0]["lhs"] == [2, 3]
   assert W.main(["--lhs", str(tmp_path / "a.safetensors"), "--rhs", str(tmp_path / "a.safetensors")]) == 0
+
+
+def test_distillation_data_generation_filters_long_prompts_and_repeats_generations(tmp_path):
+  import json
+  from maxtext_b200.trainers.post_train.distillation import generate_distillation_data as G
+  rows = [{"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "old answer"}]},
+          {"messages": [{"role": "user", "content": "x" * 500}]},
+          {"messages": [{"role": "assistant", "content": "orphan"}]},
+          {"prompt": "plain"}]
+  calls = []
+
+  def teacher(prompts, max_new):
+    calls.append(list(prompts))
+    return [f"answer{len(calls)} to {p[-12:]!r}" for p in prompts]
+  out = list(G.generate(rows, teacher, len, 100, column="messages", num_generations=2, batch_size=8))
+  assert len(out) == 2 and len(calls) == 2 and G.generate.skipped == 3          # the long one, the orphan, and the row without `messages`
+  assert out[0]["messages"][-1] == {"role": "assistant", "content": out[0]["completion"]} and len(out[0]["messages"]) == 2
+  assert out[0]["prompt"].endswith("assistant: ") and out[0]["generation"] == 0 and out[1]["generation"] == 1
+  plain = list(G.generate(rows, teacher, len, 100, column="prompt"))
+  assert len(plain) == 1 and plain[0]["prompt"] == "plain" and "messages" not in plain[0]
+  f = tmp_path / "p.jsonl"
+  f.write_text("\n".join(json.dumps(r) for r in rows))
+  assert G.read_rows(str(f)) == rows
