@@ -63,3 +63,41 @@ def test_distillation_data_generation_filters_long_prompts_and_repeats_generatio
   f = tmp_path / "p.jsonl"
   f.write_text("\n".join(json.dumps(r) for r in rows))
   assert G.read_rows(str(f)) == rows
+
+
+def test_mxfp4_and_fp8_block_checkpoints_dequantize(tmp_path):
+  import json
+  from safetensors.torch import load_file, save_file
+  from maxtext_b200.checkpoint_conversion import dequantize as D
+  # every code decodes to its table value, low nibble first, scaled by 2^(s - 127)
+  blocks = torch.tensor([[[0x21, 0xF7] + [0] * 14]], dtype=torch.uint8)              # codes 1, 2, 7, 15
+  out = D.dequantize_mxfp4(blocks, torch.tensor([[128]], dtype=torch.uint8), torch.float32)
+  assert out.shape == (1, 32) and out[0, :4].tolist() == [1.0, 2.0, 12.0, -12.0] and float(out[0, 4:].abs().sum()) == 0.0
+  torch.manual_seed(0)
+  w = torch.randn(3, 4, 64) * 0.3
+  b, s = D.quantize_mxfp4(w)
+  assert b.shape == (3, 4, 2, 16) and s.shape == (3, 4, 2)
+  back = D.dequantize_mxfp4(b, s, torch.float32)
+  scale = torch.exp2(s.float() - 127).repeat_interleave(32, -1)
+  assert float(((back - w).abs() / scale).max()) <= 1.0 + 1e-6                        # within half the widest gap (2) of the grid
+  assert torch.equal(D.dequantize_mxfp4(*D.quantize_mxfp4(back), torch.float32), back)  # grid values are fixed points
+  # fp8 block scaling: ragged 200 x 300 weight with 2 x 3 tile scales
+  wf = torch.randn(200, 300)
+  sc = torch.rand(2, 3) + 0.5
+  q = (wf / sc.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]).to(torch.float8_e4m3fn)
+  deq = D.dequantize_fp8_blocks(q, sc, torch.float32)
+  assert float((deq - wf).abs().max()) < 0.13 * float(wf.abs().max())
+  # a directory with both kinds, the scale of one weight in another shard
+  src, dst = tmp_path / "in", tmp_path / "out"
+  src.mkdir()
+  save_file({"experts.gate_up_proj_blocks": b, "experts.gate_up_proj_scales": s, "a.weight": q, "norm.weight": torch.ones(4)}, str(src / "m-1.safetensors"))
+  save_file({"a.weight_scale_inv": sc}, str(src / "m-2.safetensors"))
+  (src / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": {}}))
+  (src / "config.json").write_text("{}")
+  rep = D.convert_directory(str(src), str(dst), torch.float32)
+  assert rep == {"files": 2, "rewritten": 2}
+  got = load_file(str(dst / "m-1.safetensors"))
+  assert set(got) == {"experts.gate_up_proj", "a.weight", "norm.weight"} and torch.equal(got["experts.gate_up_proj"], back)
+  assert torch.allclose(got["a.weight"], deq) and (dst / "config.json").exists()
+  wm = json.loads((dst / "model.safetensors.index.json").read_text())["weight_map"]
+  assert wm["experts.gate_up_proj"] == "m-1.safetensors" and "a.weight_scale_inv" not in wm
