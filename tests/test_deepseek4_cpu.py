@@ -211,3 +211,21 @@ def test_sqrt_softplus_router_weights_are_positive_and_normalised():
   assert torch.allclose(wts.sum(-1), torch.full((32,), float(cfg.routed_scaling_factor)), atol=1e-5)
   want = torch.sqrt(torch.nn.functional.softplus(logits.float())) + moe.gate_bias.data.float()
   assert torch.equal(idx.sort(-1).values, want.topk(int(cfg.num_experts_per_tok), -1).indices.sort(-1).values)
+
+
+def test_flops_accounting_counts_each_layer_kind():
+  from maxtext_b200.utils import flops
+  base = V4 + ["max_target_length=1024", "per_device_batch_size=1", "sliding_window_size=128", "indexer_topk=16", "mhc_expansion_rate=1"]
+  def att(ratios):
+    cfg = tiny_config("deepseek4-tiny", [e for e in base if not e.startswith(("compress_ratios", "base_num_decoder_layers", "first_num_hash"))] +
+                      [f"compress_ratios={ratios}", f"base_num_decoder_layers={len(ratios)}", "first_num_hash_layers=1"])
+    return cfg, flops.training_tflops_per_device(cfg)
+  cfg, (t0, w0, a0) = att([0, 0, 0])
+  B, S, W, H, dh = 1, 1024, 128, cfg.num_query_heads, cfg.head_dim
+  window = 4 * B * (S * W - 0.5 * W * W) * H * dh
+  assert abs(a0 - 3 * 3 * window / 1e12) < 1e-12 and abs(t0 - (w0 + a0)) < 1e-12
+  _, (_, w1, a1) = att([0, 128, 128])
+  assert abs((a1 - a0) - 3 * 2 * (2 * B * S * (S / 128) * H * dh) / 1e12) < 1e-12          # two heavy layers add S / 128 entries each
+  assert abs((w1 - w0) - 3 * 2 * (4 * B * S * cfg.emb_dim * dh) / 1e12) < 1e-12            # and their kv / gate poolers
+  _, (_, w2, a2) = att([0, 4, 4])
+  assert a2 > a0 and w2 > w1                                                                 # sparse layers: indexer + wider poolers
