@@ -55,38 +55,63 @@ def training_tflops_per_device(c, batch_per_device: float | None = None) -> tupl
   bs = B * S
   d, L = c.emb_dim, c.num_decoder_layers
   n_act = len(c.mlp_activations)
-  if c.attention_type == "mla":
+  from ..models import families
+  if c.decoder_block == "deepseek4":
+    ffn_total = L * (2 * bs * d * c.num_experts + _ffn(bs, d, c.moe_mlp_dim, n_act) * c.num_experts_per_tok
+                     + (_ffn(bs, d, c.moe_mlp_dim * c.shared_experts, n_act) if c.shared_experts > 0 else 0))
+    weight, attention = _deepseek4(c, B, S, ffn_total, 2 * bs * d * c.vocab_size)
+  else:
+    # walk the layer plans: every block contributes its own projections, feed-forward kind and attention pattern, so families with
+    # mixed layers (local / global, chunked, dense / routed, gated-delta) are counted layer by layer
+    weight, attention = 2 * bs * d * c.vocab_size, 0.0
+    for plan in families.layer_plans(c):
+      for bp in plan.blocks:
+        w_, a_ = _block(c, bp, B, S, n_act)
+        weight += w_
+        attention += a_
+  g = c.gradient_accumulation_steps
+  return 3 * (weight + attention) * g / 1e12, 3 * weight * g / 1e12, 3 * attention * g / 1e12
+
+
+def _block(c, bp, B, S, n_act):
+  """(weight FLOPs, attention FLOPs) of one block, forward."""
+  bs, d = B * S, c.emb_dim
+  if bp.attention == "mla":
     qk = c.qk_nope_head_dim + c.qk_rope_head_dim
     if c.q_lora_rank > 0:
       q = 2 * bs * (d * c.q_lora_rank + c.q_lora_rank * c.num_query_heads * qk)
     else:
       q = 2 * bs * d * c.num_query_heads * qk
     kv = 2 * bs * (d * (c.kv_lora_rank + c.qk_rope_head_dim) + c.kv_lora_rank * c.num_query_heads * (c.qk_nope_head_dim + c.v_head_dim))
-    qkv = q + kv
+    proj_w = q + kv + 2 * bs * d * c.num_query_heads * c.v_head_dim
     attn = 2 * bs * S * c.num_query_heads * (qk + c.v_head_dim) / 2
-    proj = 2 * bs * d * c.num_query_heads * c.v_head_dim
+  elif bp.attention == "gdn":
+    # gated delta network (src/maxtext/utils/maxtext_utils.py:772-820): projections, short convolution, 8 FLOPs per state element and token
+    kd, vd = c.gdn_num_key_heads * c.gdn_key_head_dim, c.gdn_num_value_heads * c.gdn_value_head_dim
+    proj_w = 2 * bs * d * (2 * kd + 2 * vd + 2 * c.gdn_num_value_heads) + 2 * bs * d * vd + 2 * bs * c.gdn_conv_kernel_dim * (2 * kd + vd)
+    attn = bs * c.gdn_num_value_heads * c.gdn_key_head_dim * c.gdn_value_head_dim * 8
   else:
-    qkv = 2 * bs * d * (c.num_query_heads + 2 * c.num_kv_heads) * c.head_dim
-    attn = 4 * bs * S * c.num_query_heads * c.head_dim / 2
-    proj = 2 * bs * d * c.num_query_heads * c.head_dim
-  if c.num_experts > 1:
-    gate = 2 * bs * d * c.num_experts
-    moe = gate + _ffn(bs, d, c.moe_mlp_dim, n_act) * c.num_experts_per_tok
-    if c.shared_experts > 0:
-      moe += _ffn(bs, d, c.moe_mlp_dim * c.shared_experts, n_act)
-    nd = c.first_num_dense_layers if c.decoder_block == "deepseek" else 0
-    ffn_total = nd * _ffn(bs, d, c.mlp_dim, n_act) + (L - nd) * moe
+    dh = int(bp.head_dim or c.head_dim)
+    hkv = int(bp.kv_heads or c.num_kv_heads)
+    n_kv_proj = 1 if bp.share_kv else 2
+    proj_w = 2 * bs * d * (c.num_query_heads + n_kv_proj * hkv) * dh + 2 * bs * d * c.num_query_heads * dh
+    if bp.window and bp.window > 0:
+      w = min(int(bp.window), S)
+      attn = 4 * B * (S * w - 0.5 * w * w) * c.num_query_heads * dh              # causal band of width w
+    elif bp.chunk and 0 < bp.chunk < S:
+      n, rem = divmod(S, int(bp.chunk))
+      attn = 4 * B * (n * bp.chunk ** 2 + rem ** 2) * c.num_query_heads * dh / 2   # causal triangles of the chunks
+    else:
+      attn = 4 * bs * S * c.num_query_heads * dh / 2
+  if bp.mlp in ("moe", "moe_shared", "gemma4_moe"):
+    ffn = 2 * bs * d * c.num_experts + _ffn(bs, d, c.moe_mlp_dim, n_act) * c.num_experts_per_tok
+    if bp.mlp == "moe_shared" and c.shared_experts > 0:
+      ffn += _ffn(bs, d, c.moe_mlp_dim * c.shared_experts, n_act)
+    if bp.mlp == "gemma4_moe":
+      ffn += _ffn(bs, d, c.mlp_dim, n_act)                                         # the dense MLP next to the routed experts
   else:
-    ffn_total = L * _ffn(bs, d, c.mlp_dim, n_act)
-  if c.decoder_block == "deepseek4":
-    weight, attention = _deepseek4(c, B, S, ffn_total, 2 * bs * d * c.vocab_size)
-    g = c.gradient_accumulation_steps
-    return 3 * (weight + attention) * g / 1e12, 3 * weight * g / 1e12, 3 * attention * g / 1e12
-  blocks = 2 if c.decoder_block == "gemma2" else 1
-  weight = (ffn_total + L * (qkv + proj)) * blocks + 2 * bs * d * c.vocab_size
-  attention = L * attn * blocks
-  g = c.gradient_accumulation_steps
-  return 3 * (weight + attention) * g / 1e12, 3 * weight * g / 1e12, 3 * attention * g / 1e12
+    ffn = _ffn(bs, d, int(bp.mlp_hidden or c.mlp_dim), n_act)
+  return proj_w + ffn, attn
 
 
 def tokens_per_device(c, batch_per_device: float | None = None) -> float:
