@@ -1,0 +1,8 @@
+"""Alias of `maxtext_b200.checkpoint_conversion.to_maxtext` under the module path the reference uses."""
+from maxtext_b200.checkpoint_conversion.to_maxtext import *  # noqa: F401,F403
+from maxtext_b200.checkpoint_conversion.to_maxtext import main  # noqa: F401
+
+if __name__ == "__main__":
+  import sys
+  _rc = main()
+  sys.exit(_rc if isinstance(_rc, int) else 0)

@@ -101,3 +101,13 @@ def test_mxfp4_and_fp8_block_checkpoints_dequantize(tmp_path):
   assert torch.allclose(got["a.weight"], deq) and (dst / "config.json").exists()
   wm = json.loads((dst / "model.safetensors.index.json").read_text())["weight_map"]
   assert wm["experts.gate_up_proj"] == "m-1.safetensors" and "a.weight_scale_inv" not in wm
+
+
+def test_reference_module_paths_resolve_to_this_repository():
+  import importlib
+  for name in ("maxtext.train", "maxtext.train_compile", "maxtext.inference.decode", "maxtext.inference.maxengine.maxengine_server",
+               "maxtext.inference.inference_microbenchmark", "maxtext.inference.mlperf.offline_mode", "maxtext.checkpoint_conversion.to_maxtext",
+               "maxtext.checkpoint_conversion.to_huggingface", "maxtext.utils.standalone_checkpointer", "maxtext.utils.get_flops",
+               "maxtext.utils.layerwise_quantization", "maxtext.eval.runner.run", "maxtext.trainers.post_train.sft.train_sft",
+               "maxtext.trainers.post_train.rl.train_rl", "maxtext.trainers.tokenizer.train_tokenizer"):
+    assert callable(getattr(importlib.import_module(name), "main")), name
