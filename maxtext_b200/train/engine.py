@@ -286,7 +286,10 @@ class TrainEngine:
         store.acquire_full_grad(u)
     if sp_on:
       dx = sp.all_gather_seq(dx, ctx.tp_group)
-    self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm)
+    if mm is not None and not bool(getattr(c, "freeze_vision_encoder_params", True)):
+      self._towers_backward(batch, tokens, positions, dx, accumulate_rs)
+    else:
+      self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm)
     for r_tokens, r_pos, d_emb in mtp_embed_grads:          # embeddings of the tokens further ahead, used by the MTP modules
       self._run_embed(r_tokens, r_pos, grad=True, dx=d_emb)
     self._finish_unit_grads(0, accumulate_rs)
@@ -362,8 +365,6 @@ class TrainEngine:
     gradient, and let the tokens of each image attend to each other in both directions."""
     if batch.get("images") is None or self.model.vision is None:
       return None
-    if not bool(getattr(self.config, "freeze_vision_encoder_params", True)):
-      raise NotImplementedError("training the vision tower (freeze_vision_encoder_params=false) is not implemented")
     from ..multimodal.utils import bidirectional_block_mask
     units = [u for k, u in self.store.units.items() if k == "vision" or k.startswith("vision#")]
     for u in units:
@@ -382,8 +383,6 @@ class TrainEngine:
     """Batches with `audio` ([B, mel, frames] or a list of clips) + `audio_mask` [B, S]: run the frozen audio tower once."""
     if batch.get("audio") is None or self.model.audio is None:
       return None
-    if not bool(getattr(self.config, "freeze_vision_encoder_params", True)):
-      raise NotImplementedError("training the audio tower (freeze_vision_encoder_params=false) is not implemented")
     units = [u for k, u in self.store.units.items() if k == "audio" or k.startswith("audio#")]
     for u in units:
       if u.group_size > 1 and not u.resident:
@@ -393,6 +392,31 @@ class TrainEngine:
     for u in units:
       self.store.release_full(u)
     return am
+
+  def _towers_backward(self, batch, tokens, positions, dx, accumulate_rs):
+    """`freeze_vision_encoder_params=false`: the towers ran without gradient in the forward pass; here they run again under
+    autograd, the soft tokens enter the embedding, and d(embedding output) flows back into the tower parameters together with
+    the embedding table's own gradient. Features that reach the decoder by another route (Qwen3-VL deepstack) are not
+    differentiated: their mergers receive no gradient."""
+    model, store = self.model, self.store
+    units = [u for k, u in store.units.items() if k.split("#")[0] in ("vision", "audio")]
+    for u in units:
+      if u.group_size > 1 and not u.resident:
+        store.gather_unit(u, async_op=False)
+      store.acquire_full_grad(u)
+    with torch.enable_grad():
+      mm_g = []
+      if batch.get("images") is not None and model.vision is not None:
+        mm_g.append(model.encode_images(batch["images"].to(self.device), batch["image_mask"].to(self.device)))
+      if batch.get("audio") is not None and model.audio is not None:
+        mm_g.append(model.encode_audio(batch["audio"], batch["audio_mask"].to(self.device)))
+    self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm_g[0] if len(mm_g) == 1 else mm_g)
+    for p in list(model.vision_params) + list(model.audio_params):
+      p.collect_leaf_grad()
+    for u in units:
+      if u.group_size > 1:
+        store.reduce_scatter_unit(u, async_op=True, accumulate=accumulate_rs)
+      store.release_full(u)
 
   def _run_embed(self, tokens, positions, grad: bool, dx=None, mm=None):
     model = self.model

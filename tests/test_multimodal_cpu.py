@@ -153,3 +153,48 @@ def test_llama4_processor_tiles_and_tokens():
   assert seq.count(pl.TILE_X_SEPARATOR_TOKEN) == 2 and seq.count(pl.TILE_Y_SEPARATOR_TOKEN) == 2 and seq[-6] == pl.IMAGE_TOKEN
   ids, mask, pix = pl.prepare([5, pl.IMAGE_TOKEN, 6], [rng.integers(0, 255, (32, 64, 3), dtype=np.uint8)], tile=32, patch=4, max_tiles=4)
   assert pix.shape[0] == 3 and int(mask.sum()) == 3 * pl.tokens_per_tile(32, 4) and ids[0] == 5 and ids[-1] == 6
+
+
+def test_unfrozen_tower_trains_and_its_gradient_matches_a_finite_difference():
+  """freeze_vision_encoder_params=false: the vision parameters move, and the analytic directional derivative along a random
+  direction in the tower's parameters equals the finite difference of the loss."""
+  cfg = tiny_config("gemma3-4b", MM + ["image_size_for_vit=64", "max_target_length=288", "per_device_batch_size=1", "freeze_vision_encoder_params=false",
+                                      "gradient_clipping_threshold=0"])
+  eng = make_engine(cfg)
+  store = eng.store
+  assert not any(p.pdef.frozen for p in eng.model.vision_params)
+  b = batch_of(cfg)
+  B, S = b["inputs"].shape
+  mask = torch.zeros(B, S, dtype=torch.bool)
+  mask[:, 4:260] = True
+  b["images"], b["image_mask"] = torch.randn(B, 1, 3, 64, 64, generator=torch.Generator().manual_seed(0)), mask
+  eng.fwd_bwd(dict(b))
+  store.finish_resident_grads()
+  acc = eng._accum
+  eng._accum = None
+  g = store.grad_shard.clone() / float(acc["weights"])
+  sel = torch.zeros_like(g, dtype=torch.bool)                  # the tower's part of the flat parameter vector
+  for k, u in store.units.items():
+    if k.split("#")[0] == "vision":
+      sel[u.shard_offset: u.shard_offset + u.numel] = True
+  assert float(g[sel].abs().sum()) > 0
+  v = torch.randn(g.shape, generator=torch.Generator().manual_seed(1)) * sel
+  v = v / v.norm()
+
+  def loss():
+    m = eng.eval_step(dict(b))
+    return float(m["evaluation/total_loss"]) / float(m["evaluation/total_weights"])
+  w0, eps = store.master.clone(), 1e-2
+  vals = []
+  for sign in (1.0, -1.0):
+    store.master.copy_(w0 + sign * eps * v)
+    store.sync_compute_from_master()
+    vals.append(loss())
+  store.master.copy_(w0)
+  store.sync_compute_from_master()
+  fd, an = (vals[0] - vals[1]) / (2 * eps), float((g * v).sum())
+  assert abs(fd - an) <= 0.05 * max(abs(fd), abs(an)) + 1e-4, (fd, an)
+  before = {p.name: store.full_master(p).clone() for p in eng.model.vision_params}
+  losses = [float(eng.train_step(dict(b))["learning/loss"]) for _ in range(3)]
+  assert losses[-1] < losses[0]
+  assert any(not torch.equal(before[p.name], store.full_master(p)) for p in eng.model.vision_params)
