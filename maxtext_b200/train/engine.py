@@ -254,6 +254,8 @@ class TrainEngine:
       # and the ranks' gradients are summed, so it is seeded with weight / (layers x data shards)
       aux_scale = self._global_weight(total_w) / self.n_moe_layers / self._data_shards()
     self._gather(len(model.layers) - 1)  # unit index of layer L-2 is L-1
+    train_towers = mm is not None and not bool(getattr(c, "freeze_vision_encoder_params", True))
+    deep_grads: dict = {}
     for i in reversed(range(len(model.layers))):
       ui = i + 1
       layer = model.layers[i]
@@ -264,6 +266,13 @@ class TrainEngine:
       x_in, saved = ckpts.pop()
       x_in = x_in.detach().requires_grad_(True)
       ctx.saved, ctx.recompute, ctx.layer_index, ctx.aux_losses = saved, True, i, []
+      deep_leaf = None
+      if train_towers and ctx.deepstack is not None and layer.index < len(ctx.deepstack[1]):
+        # a trainable tower also feeds this layer directly (deepstack): differentiate with respect to that feature as well
+        deep_leaf = ctx.deepstack[1][layer.index].detach().requires_grad_(True)
+        feats = list(ctx.deepstack[1])
+        feats[layer.index] = deep_leaf
+        ctx.deepstack = (ctx.deepstack[0], feats)
       with torch.enable_grad():
         y = layer(x_in, ctx)
         outs, grads = [y], [dx]
@@ -273,6 +282,8 @@ class TrainEngine:
             grads.append(aux_scale.to(a.dtype))
       torch.autograd.backward(outs, grads)
       dx = x_in.grad
+      if deep_leaf is not None and deep_leaf.grad is not None:
+        deep_grads[layer.index] = deep_leaf.grad
       del y, outs, grads, x_in, saved
       for p in layer.params:
         p.collect_leaf_grad()
@@ -287,7 +298,7 @@ class TrainEngine:
     if sp_on:
       dx = sp.all_gather_seq(dx, ctx.tp_group)
     if mm is not None and not bool(getattr(c, "freeze_vision_encoder_params", True)):
-      self._towers_backward(batch, tokens, positions, dx, accumulate_rs)
+      self._towers_backward(batch, tokens, positions, dx, accumulate_rs, deep_grads)
     else:
       self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm)
     for r_tokens, r_pos, d_emb in mtp_embed_grads:          # embeddings of the tokens further ahead, used by the MTP modules
@@ -393,11 +404,11 @@ class TrainEngine:
       self.store.release_full(u)
     return am
 
-  def _towers_backward(self, batch, tokens, positions, dx, accumulate_rs):
+  def _towers_backward(self, batch, tokens, positions, dx, accumulate_rs, deep_grads=None):
     """`freeze_vision_encoder_params=false`: the towers ran without gradient in the forward pass; here they run again under
     autograd, the soft tokens enter the embedding, and d(embedding output) flows back into the tower parameters together with
-    the embedding table's own gradient. Features that reach the decoder by another route (Qwen3-VL deepstack) are not
-    differentiated: their mergers receive no gradient."""
+    the embedding table's own gradient. Features that reach the decoder by another route (Qwen3-VL deepstack, added after the
+    first layers) bring the gradients collected while those layers were replayed (`deep_grads`: feature index -> gradient)."""
     model, store = self.model, self.store
     units = [u for k, u in store.units.items() if k.split("#")[0] in ("vision", "audio")]
     for u in units:
@@ -410,8 +421,15 @@ class TrainEngine:
         mm_g.append(model.encode_images(batch["images"].to(self.device), batch["image_mask"].to(self.device)))
       if batch.get("audio") is not None and model.audio is not None:
         mm_g.append(model.encode_audio(batch["audio"], batch["audio_mask"].to(self.device)))
-    self._run_embed(tokens, positions, grad=True, dx=dx, mm=mm_g[0] if len(mm_g) == 1 else mm_g)
-    for p in list(model.vision_params) + list(model.audio_params):
+      x = model.embed(tokens, positions, mm_g[0] if len(mm_g) == 1 else mm_g)
+      outs, grads = [x], [dx]
+      deep = getattr(model, "_deepstack", None)
+      for i, g in (deep_grads or {}).items():
+        if deep is not None and i < len(deep[1]) and deep[1][i].requires_grad:
+          outs.append(deep[1][i])
+          grads.append(g.to(deep[1][i].dtype).reshape(deep[1][i].shape))
+    torch.autograd.backward(outs, grads)
+    for p in list(model.embed_params) + list(model.vision_params) + list(model.audio_params):
       p.collect_leaf_grad()
     for u in units:
       if u.group_size > 1:

@@ -158,3 +158,46 @@ def test_multi_axis_rotary_positions_and_angles_match_huggingface():
     b = model.forward(tokens, positions3=p3[None])
     c = model.forward(tokens, positions3=torch.arange(11)[None, :, None].expand(-1, -1, 3))
   assert torch.allclose(a, c, atol=1e-4) and not torch.allclose(a, b, atol=1e-4)
+
+
+def test_unfrozen_qwen_tower_gradient_includes_the_deepstack_route():
+  """The tower feeds the decoder twice (soft tokens at the embedding, deepstack features after the first layers); the analytic
+  directional derivative over the tower's parameters matches the finite difference only if both routes are differentiated."""
+  from helpers import batch_of, make_engine
+  cfg = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=64", "freeze_vision_encoder_params=false", "gradient_clipping_threshold=0",
+                                          "per_device_batch_size=1", "max_target_length=32"])
+  eng = make_engine(cfg)
+  store = eng.store
+  b = batch_of(cfg)
+  B, S = b["inputs"].shape
+  mask = torch.zeros(B, S, dtype=torch.bool)
+  mask[:, 3:7] = True
+  b["images"], b["image_mask"] = torch.randn(B, 1, 3, 16, 16, generator=torch.Generator().manual_seed(0)), mask
+  eng.fwd_bwd(dict(b))
+  store.finish_resident_grads()
+  acc = eng._accum
+  eng._accum = None
+  g = store.grad_shard.clone() / float(acc["weights"])
+  sel = torch.zeros_like(g, dtype=torch.bool)
+  for k, u in store.units.items():
+    if k.split("#")[0] == "vision":
+      sel[u.shard_offset: u.shard_offset + u.numel] = True
+  # the deepstack mergers only act through the second route: they must have a gradient
+  deep_names = [p.name for p in eng.model.vision_params if "vision_encoder/merger_" in p.name]
+  assert deep_names and any(float(p.main_grad.abs().sum()) > 0 for p in eng.model.vision_params if p.name in deep_names)
+  v = torch.randn(g.shape, generator=torch.Generator().manual_seed(1)) * sel
+  v = v / v.norm()
+
+  def loss():
+    m = eng.eval_step(dict(b))
+    return float(m["evaluation/total_loss"]) / float(m["evaluation/total_weights"])
+  w0, eps = store.master.clone(), 1e-2
+  vals = []
+  for sign in (1.0, -1.0):
+    store.master.copy_(w0 + sign * eps * v)
+    store.sync_compute_from_master()
+    vals.append(loss())
+  store.master.copy_(w0)
+  store.sync_compute_from_master()
+  fd, an = (vals[0] - vals[1]) / (2 * eps), float((g * v).sum())
+  assert abs(fd - an) <= 0.05 * max(abs(fd), abs(an)) + 1e-4, (fd, an)
