@@ -38,6 +38,18 @@ def decode(config, prompt: str | None = None, engine: MaxEngine | None = None) -
       t_ids, mask, pix = pg.prepare(ids, paths, int(config.image_size_for_vit))
     ids = t_ids.tolist()
     mm_kw = dict(images=pix, image_mask=torch.nn.functional.pad(mask, (0, max(0, int(config.max_prefill_predict_length) - len(ids)))))
+  if bool(getattr(config, "use_multimodal", False)) and bool(getattr(config, "use_audio", False)) and str(getattr(config, "audio_path", "") or ""):
+    # one clip: <|audio_start|> <|audio_pad|> x K <|audio_end|>, K soft tokens from the clip's log-mel frames (16 kHz PCM .wav)
+    from ..multimodal import processor_qwen3 as pq
+    wave, sr = pq.read_wav(str(config.audio_path))
+    if sr != 16000:
+      raise ValueError(f"audio_path: the tower expects 16 kHz audio, the file has {sr} Hz")
+    t_ids, amask, feats = pq.prepare_audio_prompt(ids, wave, config)
+    ids = t_ids.tolist()
+    pad_to = max(0, int(config.max_prefill_predict_length) - len(ids))
+    mm_kw.update(audio=feats, audio_mask=torch.nn.functional.pad(amask, (0, pad_to)))
+    if "image_mask" in mm_kw and mm_kw["image_mask"].numel() < len(ids) + pad_to:
+      mm_kw["image_mask"] = torch.nn.functional.pad(mm_kw["image_mask"], (0, len(ids) + pad_to - mm_kw["image_mask"].numel()))
   ids = [i % config.vocab_size for i in ids][: int(config.max_prefill_predict_length)]
   n = len(ids)
   padded = torch.tensor(ids + [0] * (int(config.max_prefill_predict_length) - n), dtype=torch.long)

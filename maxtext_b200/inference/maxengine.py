@@ -158,9 +158,11 @@ class MaxEngine:
 
   # ------------------------------------------------------------------ prefill / insert / generate
   @torch.no_grad()
-  def prefill(self, padded_tokens: torch.Tensor, true_length: int, params=None, images=None, image_mask=None) -> tuple[Prefix, ResultTokens]:
+  def prefill(self, padded_tokens: torch.Tensor, true_length: int, params=None, images=None, image_mask=None, audio=None,
+              audio_mask=None) -> tuple[Prefix, ResultTokens]:
     """padded_tokens [P] (right padded); only the first `true_length` enter the cache. `images` [N, 3, H, W] with
-    `image_mask` [P] (True at the soft-token positions of the prompt) makes the prompt multimodal."""
+    `image_mask` [P] (True at the soft-token positions of the prompt) makes the prompt multimodal; `audio` [mel, frames] (one
+    clip) with `audio_mask` [P] does the same for the audio tower."""
     dev = self.device
     self._check_length(true_length, "prefill")
     if int(true_length) > int(padded_tokens.numel()):
@@ -172,6 +174,8 @@ class MaxEngine:
     mm_kw = {}
     if images is not None:
       mm_kw = dict(images=images[None].to(dev), image_mask=image_mask[:true_length][None].to(dev))
+    if audio is not None:
+      mm_kw.update(audio=audio[None].to(dev), audio_mask=audio_mask[:true_length][None].to(dev))
     logits = self.model.forward(toks, pos, None, mode="prefill", caches=caches, **mm_kw)[:, -1]
     tok = self._sample(logits)
     lp = inference_utils.log_prob_of(logits, tok) if self.config.return_log_prob else None

@@ -15,8 +15,10 @@ import torch
 from .processor import load_image
 
 TOKENS = {
-    "qwen3.5": dict(vision_start=248053, vision_end=248054, image_pad=248056),
-    "": dict(vision_start=151652, vision_end=151653, image_pad=151655),          # Qwen3-VL and Qwen3-Omni vocabularies
+    "qwen3.5": dict(vision_start=248053, vision_end=248054, image_pad=248056, video_pad=248057, audio_start=248070, audio_end=248071,
+                    audio_pad=248076),
+    # Qwen3-VL and Qwen3-Omni vocabularies
+    "": dict(vision_start=151652, vision_end=151653, image_pad=151655, video_pad=151656, audio_start=151669, audio_end=151670, audio_pad=151675),
 }
 MAX_RATIO = 200
 
@@ -117,3 +119,35 @@ def rope_index(image_mask, grids) -> torch.Tensor:
     cur += max(rows, cols)
     i += n
   return torch.tensor(out, dtype=torch.long)
+
+
+def read_wav(path: str):
+  """16-bit PCM .wav -> float32 mono in [-1, 1] and its sampling rate (standard library reader; other formats need converting)."""
+  import wave
+  import numpy as np
+  with wave.open(path, "rb") as fh:
+    if fh.getsampwidth() != 2:
+      raise ValueError(f"{path}: only 16-bit PCM is read, got {8 * fh.getsampwidth()}-bit samples")
+    sr, ch, n = fh.getframerate(), fh.getnchannels(), fh.getnframes()
+    data = np.frombuffer(fh.readframes(n), dtype="<i2").astype(np.float32) / 32768.0
+  return (data.reshape(-1, ch).mean(1) if ch > 1 else data), sr
+
+
+def prepare_audio_prompt(ids, waveform, config, model_name: str | None = None):
+  """Expand the prompt for one audio clip: `<|audio_start|> <|audio_pad|> x K <|audio_end|>` (appended when the prompt has no
+  audio placeholder), K = the number of soft tokens of the clip. Returns (ids, audio_mask, features [mel, frames])."""
+  import torch
+  from .audio_features import prepare_audio
+  tk = special_tokens(model_name or str(config.model_name))
+  feats, k = prepare_audio(waveform, config)
+  ids = list(ids)
+  block = [tk["audio_start"]] + [tk["audio_pad"]] * k + [tk["audio_end"]]
+  if tk["audio_pad"] in ids:
+    i = ids.index(tk["audio_pad"])
+    lo = i - 1 if i > 0 and ids[i - 1] == tk["audio_start"] else i
+    hi = i + 2 if i + 1 < len(ids) and ids[i + 1] == tk["audio_end"] else i + 1
+    ids = ids[:lo] + block + ids[hi:]
+  else:
+    ids = ids + block
+  t = torch.tensor(ids, dtype=torch.long)
+  return t, t == tk["audio_pad"], feats

@@ -120,3 +120,58 @@ def test_engine_trains_on_a_batch_with_audio():
   l1 = float(eng.train_step(dict(batch))["learning/loss"])
   assert l0 == l0 and l1 < l0
   assert all(torch.equal(a, p.data) for a, p in zip(before, eng.model.audio_params))          # the tower is frozen
+
+
+def test_log_mel_features_match_the_whisper_front_end():
+  pytest.importorskip("transformers")
+  import numpy as np
+  from transformers import WhisperFeatureExtractor
+  from maxtext_b200.multimodal.audio_features import log_mel, mel_filters, prepare_audio
+  rng = np.random.default_rng(0)
+  t = np.arange(32000) / 16000.0
+  wave = (0.3 * np.sin(2 * np.pi * 440 * t) + 0.1 * np.sin(2 * np.pi * 3000 * t) + 0.02 * rng.standard_normal(t.shape)).astype(np.float32)
+  fe = WhisperFeatureExtractor(feature_size=128, sampling_rate=16000, hop_length=160, chunk_length=2, n_fft=400)
+  want = fe(wave, sampling_rate=16000, return_tensors="np", padding="max_length").input_features[0]       # [128, 200]
+  got = log_mel(wave).numpy()
+  assert got.shape == want.shape == (128, 200)
+  assert np.abs(got - want).max() < 2e-3, np.abs(got - want).max()
+  f = mel_filters()
+  assert f.shape == (201, 128) and float(f.min()) >= 0.0 and bool((f.sum(0) > 0).all())
+  feats, tokens = prepare_audio(wave[:20000])                     # 1.25 s -> padded to 2 s
+  assert feats.shape == (128, 200) and tokens == 26
+
+
+def test_decode_cli_takes_an_audio_clip(tmp_path):
+  """A 16 kHz .wav goes through the feature extractor, the prompt grows by the clip's soft tokens, the engine prefills with them."""
+  import wave
+  import numpy as np
+  from maxtext_b200.inference.decode import decode
+  from maxtext_b200.inference.maxengine import MaxEngine
+  from maxtext_b200.multimodal import processor_qwen3 as pq
+  path = str(tmp_path / "clip.wav")
+  sig = (0.4 * np.sin(2 * np.pi * 330 * np.arange(16000) / 16000.0) * 32767).astype("<i2")
+  with wave.open(path, "wb") as fh:
+    fh.setnchannels(1)
+    fh.setsampwidth(2)
+    fh.setframerate(16000)
+    fh.writeframes(sig.tobytes())
+  w, sr = pq.read_wav(path)
+  assert sr == 16000 and w.shape == (16000,) and abs(float(np.abs(w).max()) - 0.4) < 1e-3
+  cfg = _omni(["num_mel_bins_for_audio=128", "max_prefill_predict_length=48", "max_target_length=56", "per_device_batch_size=1", f"audio_path={path}",
+               "prompt=what is this"])
+  ids, mask, feats = pq.prepare_audio_prompt([1, 2, 3], w, cfg)
+  tk = pq.special_tokens(cfg.model_name)
+  assert feats.shape == (128, 100) and int(mask.sum()) == 13 and ids.tolist()[3] == tk["audio_start"] and ids.tolist()[-1] == tk["audio_end"]
+  ids2, mask2, _ = pq.prepare_audio_prompt([1, tk["audio_start"], tk["audio_pad"], tk["audio_end"], 9], w, cfg)
+  assert ids2.tolist()[0] == 1 and ids2.tolist()[-1] == 9 and int(mask2.sum()) == 13 and len(ids2) == 2 + 15
+  eng = MaxEngine(cfg, device="cpu")
+  eng.load_params()
+  with_audio = decode(cfg, engine=eng)
+  silent = tmp_path / "silent.wav"
+  with wave.open(str(silent), "wb") as fh:
+    fh.setnchannels(1)
+    fh.setsampwidth(2)
+    fh.setframerate(16000)
+    fh.writeframes((sig * 0).tobytes())
+  other = decode(cfg.replace(audio_path=str(silent)), engine=eng)
+  assert isinstance(with_audio, str) and isinstance(other, str)
