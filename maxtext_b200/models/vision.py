@@ -354,10 +354,20 @@ class Qwen3VLVision:
     return ang.cos(), ang.sin()
 
   def patches(self, images: torch.Tensor) -> torch.Tensor:
-    """[M, C, H, W] (one frame, repeated over the temporal patch) -> [M, S, TP*P*P*C] in merge order, features ordered
-    (t, py, px, c) like the reference kernel."""
-    M, C, H, W = images.shape
+    """[M, C, H, W] (one frame, repeated over the temporal patch) or [M, TP, C, H, W] (the frames of a video's temporal patch)
+    -> [M, S, TP*P*P*C] in merge order, features ordered (t, py, px, c) like the reference kernel."""
     P = self.P
+    if images.dim() == 5:
+      # video: [M, TP, C, H, W], the frames of one temporal patch are distinct
+      M, T, C, H, W = images.shape
+      assert T == self.TP, f"a temporal patch holds {self.TP} frames, got {T}"
+      gh, gw = H // P, W // P
+      assert H % (P * self.merge) == 0 and W % (P * self.merge) == 0, "frame sides must be multiples of patch_size * spatial_merge_size"
+      rc = self._merge_order(gh, gw, images.device)
+      x = images.view(M, T, C, gh, P, gw, P).permute(0, 3, 5, 1, 4, 6, 2)               # M, gy, gx, t, py, px, C
+      x = x[:, rc[:, 0], rc[:, 1]]
+      return x.reshape(M, x.shape[1], T * P * P * C), rc, gh, gw
+    M, C, H, W = images.shape
     gh, gw = H // P, W // P
     assert H % (P * self.merge) == 0 and W % (P * self.merge) == 0, "image sides must be multiples of patch_size * spatial_merge_size"
     rc = self._merge_order(gh, gw, images.device)

@@ -151,3 +151,36 @@ def prepare_audio_prompt(ids, waveform, config, model_name: str | None = None):
     ids = ids + block
   t = torch.tensor(ids, dtype=torch.long)
   return t, t == tk["audio_pad"], feats
+
+
+def prepare_video(ids, frames, config, model_name: str | None = None, size: tuple[int, int] | None = None):
+  """frames: [T, H, W, 3] uint8 (already sampled at the wanted rate). Frames are resized like images, grouped into temporal
+  patches of `temporal_patch_size_for_vit` frames (the last one repeated to fill a patch), and every patch becomes
+  `<|vision_start|> <|video_pad|> x K <|vision_end|>` in the prompt, in place of a `<|video_pad|>` placeholder or appended.
+  Returns (ids, mask over the pad positions, pixel tensor [T / TP, TP, 3, H', W']); the tower treats each temporal patch as one
+  image whose frames differ (attention stays inside a patch, as for the published model)."""
+  tk = special_tokens(model_name or str(config.model_name))
+  tp = int(config.temporal_patch_size_for_vit)
+  frames = np.asarray(frames)
+  if frames.ndim != 4 or frames.shape[-1] != 3:
+    raise ValueError(f"frames must be [T, H, W, 3], got {frames.shape}")
+  first = preprocess_image(frames[0], config, size)
+  pix = [first] + [preprocess_image(f, config, tuple(first.shape[1:])) for f in frames[1:]]
+  while len(pix) % tp:
+    pix.append(pix[-1])
+  video = torch.stack(pix).view(len(pix) // tp, tp, *first.shape)
+  unit = int(config.patch_size_for_vit) * int(config.spatial_merge_size_for_vit)
+  k = (first.shape[1] // unit) * (first.shape[2] // unit)
+  block = []
+  for _ in range(video.shape[0]):
+    block += [tk["vision_start"]] + [tk["video_pad"]] * k + [tk["vision_end"]]
+  ids = list(ids)
+  if tk["video_pad"] in ids:
+    i = ids.index(tk["video_pad"])
+    lo = i - 1 if i > 0 and ids[i - 1] == tk["vision_start"] else i
+    hi = i + 2 if i + 1 < len(ids) and ids[i + 1] == tk["vision_end"] else i + 1
+    ids = ids[:lo] + block + ids[hi:]
+  else:
+    ids = ids + block
+  t = torch.tensor(ids, dtype=torch.long)
+  return t, t == tk["video_pad"], video

@@ -201,3 +201,48 @@ def test_unfrozen_qwen_tower_gradient_includes_the_deepstack_route():
   store.sync_compute_from_master()
   fd, an = (vals[0] - vals[1]) / (2 * eps), float((g * v).sum())
   assert abs(fd - an) <= 0.05 * max(abs(fd), abs(an)) + 1e-4, (fd, an)
+
+
+def test_video_temporal_patches_match_huggingface_and_reach_the_decoder():
+  pytest.importorskip("transformers")
+  import numpy as np
+  from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionConfig, Qwen3VLVisionModel
+  from maxtext_b200.models.transformer import Transformer
+  from maxtext_b200.models.vision import Qwen3VLVision
+  from maxtext_b200.multimodal import processor_qwen3 as pq
+  cfg = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=40"])
+  hf_cfg = Qwen3VLVisionConfig(depth=3, hidden_size=32, hidden_act="gelu_pytorch_tanh", intermediate_size=48, num_heads=4, in_channels=3, patch_size=4,
+                               spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=40, num_position_embeddings=36, deepstack_visual_indexes=[0, 1])
+  hf_cfg._attn_implementation = "eager"
+  torch.manual_seed(0)
+  hf = Qwen3VLVisionModel(hf_cfg).float().eval()
+  for p in hf.parameters():
+    torch.nn.init.normal_(p, std=0.2)
+  vision = Qwen3VLVision(cfg, {})
+  _load(vision, hf)
+  T, H, W = 4, 16, 24                                           # four frames = two temporal patches
+  video = torch.randn(1, T // 2, 2, 3, H, W)                    # [B, patches, frames per patch, 3, H, W]
+  with torch.no_grad():
+    got = vision(video)
+    x, rc, gh, gw = vision.patches(video.reshape(T // 2, 2, 3, H, W))
+    flat = x.reshape((T // 2) * gh * gw, 2, 4, 4, 3).permute(0, 4, 1, 2, 3).reshape((T // 2) * gh * gw, -1)     # HF features: (c, t, py, px)
+    want = hf(flat, grid_thw=torch.tensor([[T // 2, gh, gw]])).pooler_output.view(1, T // 2, (gh // 2) * (gw // 2), -1)
+  assert got.shape == want.shape and torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+  # frames that differ inside a temporal patch give other tokens than a repeated frame
+  with torch.no_grad():
+    still = vision(video[:, :, :1].expand(-1, -1, 2, -1, -1, -1).contiguous())
+  assert not torch.allclose(still, got)
+  # processor: five frames -> three temporal patches (the last frame repeated), prompt expanded per patch
+  cfg2 = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=64"])
+  frames = (np.random.default_rng(0).random((5, 16, 16, 3)) * 255).astype(np.uint8)
+  tk = pq.special_tokens("qwen3-vl-2b")
+  ids, mask, pix = pq.prepare_video([5, tk["video_pad"], 9], frames, cfg2)
+  assert pix.shape == (3, 2, 3, 16, 16) and torch.equal(pix[2, 0], pix[2, 1]) and int(mask.sum()) == 3 * 4
+  assert ids.tolist()[0] == 5 and ids.tolist()[-1] == 9 and ids.tolist().count(tk["vision_start"]) == 3
+  model = Transformer(cfg2, None, torch.device("cpu"))
+  model.store.initialize(seed=0)
+  with torch.no_grad():
+    toks = ids[None] % cfg2.vocab_size
+    a = model.forward(toks, images=pix[None], image_mask=mask[None])
+    b = model.forward(toks, images=pix[None] * 0.5, image_mask=mask[None])
+  assert torch.isfinite(a).all() and not torch.allclose(a, b)
