@@ -222,5 +222,23 @@ def main(argv=None):
   return sup.run(lambda attempt, world: train_loop(config, attempt=attempt))
 
 
+def cli(argv=None):
+  """Entry point of `python -m ...train`: run, then close the process group and leave without interpreter teardown. With a live
+  process group, helper threads of the collective backend have ended otherwise correct multi-rank runs with std::terminate
+  (exit code -6) while the interpreter was shutting down; everything the run writes is flushed and closed before this point."""
+  main(argv)
+  sys.stdout.flush()
+  sys.stderr.flush()
+  import torch.distributed as dist
+  if dist.is_available() and dist.is_initialized():
+    try:
+      dist.barrier()
+      dist.destroy_process_group()
+    except Exception as e:  # pylint: disable=broad-except
+      max_logging.log(f"destroy_process_group: {e!r}")
+    sys.stdout.flush()
+    os._exit(0)
+
+
 if __name__ == "__main__":
-  main()
+  cli()
