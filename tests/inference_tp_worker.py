@@ -29,7 +29,10 @@ def main():
     with open(out_path, "w") as fh:
       json.dump({"tokens": toks, "logits": prefix.logits[0, :8].tolist()}, fh)
   if world > 1:
+    torch.distributed.barrier()
     torch.distributed.destroy_process_group()
+  sys.stdout.flush()
+  os._exit(0)                 # the result is on disk; skip interpreter teardown (see multirank_worker.py)
 
 
 if __name__ == "__main__":
