@@ -95,9 +95,43 @@ def _llama4_vision_name(path: str) -> tuple[str, str] | None:
   return pre + sub[mod] + (".bias" if leaf == "bias" else ".weight"), ("linear" if leaf == "kernel" else "vec")
 
 
+def _qwen_vision_name(path: str) -> tuple[str, str] | None:
+  """Qwen3-VL vision tower (HF: model.visual.*). The fused qkv of the HF blocks is cut into our query / key / value (kinds
+  qkv0..2 name the third), the 3-D patch convolution becomes a matrix over (t, py, px, c) features (kind patch3d)."""
+  import re
+  v = "model.visual."
+  top = {"vision_encoder/patch_embed/proj/kernel": (v + "patch_embed.proj.weight", "patch3d"),
+         "vision_encoder/patch_embed/proj/bias": (v + "patch_embed.proj.bias", "vec"),
+         "vision_encoder/pos_embed_interpolate/pos_embed": (v + "pos_embed.weight", "vec")}
+  if path in top:
+    return top[path]
+  m = re.match(r"(vision_projector/merger|vision_encoder/merger_(\d+))/(ln_q|mlp_0|mlp_2)/(scale|bias|kernel)$", path)
+  if m:
+    mod = "merger" if m.group(2) is None else f"deepstack_merger_list.{m.group(2)}"
+    sub = {"ln_q": "norm", "mlp_0": "linear_fc1", "mlp_2": "linear_fc2"}[m.group(3)]
+    return v + f"{mod}.{sub}." + ("bias" if m.group(4) == "bias" else "weight"), ("linear" if m.group(4) == "kernel" else "vec")
+  m = re.match(r"vision_encoder/blocks_(\d+)/(.+)/(scale|bias|kernel)$", path)
+  if not m:
+    return None
+  pre, mod, leaf = v + f"blocks.{m.group(1)}.", m.group(2), m.group(3)
+  suffix = "bias" if leaf == "bias" else "weight"
+  if mod in ("ln1", "ln2"):
+    return pre + {"ln1": "norm1", "ln2": "norm2"}[mod] + "." + suffix, "vec"
+  if mod in ("attn/attn/query", "attn/attn/key", "attn/attn/value"):
+    j = ("query", "key", "value").index(mod.rsplit("/", 1)[1])
+    return pre + "attn.qkv." + suffix, f"qkv{j}"
+  sub = {"attn/attn/out": "attn.proj", "mlp": "mlp.linear_fc1", "mlp_out": "mlp.linear_fc2"}.get(mod)
+  if sub is None:
+    return None
+  return pre + sub + "." + suffix, ("linear" if leaf == "kernel" else "vec")
+
+
 def _vision_name(path: str) -> tuple[str, str] | None:
   """Gemma-3 vision tower and projector (HF: SigLIP under model.vision_tower, model.multi_modal_projector)."""
   import re
+  if path.startswith(("vision_encoder/patch_embed/", "vision_encoder/pos_embed_interpolate/", "vision_encoder/blocks_", "vision_encoder/merger_",
+                      "vision_projector/merger/")):
+    return _qwen_vision_name(path)
   if path.startswith(("vision_encoder/Llama4VisionModel_0/", "vision_encoder/Llama4MultiModalProjector_0/")):
     return _llama4_vision_name(path)
   vt = "model.vision_tower.vision_model."
@@ -129,7 +163,7 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
   """(hf key, kind) for one of our parameters. Kinds: linear, vec, norm, embed, q, k, qbias, kbias, and
   experts:<part> for stacked expert tensors (the key is then the HF layer prefix)."""
   path, L = _locate(pdef, cfg)
-  if path.startswith("vision_encoder/"):
+  if path.startswith(("vision_encoder/", "vision_projector/")):
     return _vision_name(path)
   pre = f"model.layers.{L}." if L is not None else ""
   blk = cfg.decoder_block
@@ -401,6 +435,11 @@ def to_maxtext(hf_state: dict, store, cfg) -> list[str]:
         missing.append(name)
         continue
     w = hf_state[key].float()
+    if kind.startswith("qkv"):
+      third = w.shape[0] // 3                # HF fuses query | key | value along the output dimension
+      w = w[int(kind[3]) * third:(int(kind[3]) + 1) * third]
+    elif kind == "patch3d":
+      w = w.permute(0, 2, 3, 4, 1).reshape(w.shape[0], -1)          # conv [out, C, T, P, P] -> features (t, py, px, c)
     if kind == "q":
       if inter:
         w = _interleave(w, cfg.num_query_heads, cfg.head_dim)
@@ -436,6 +475,15 @@ def to_hf(store, cfg) -> dict:
       continue
     key, kind = m
     w = store.full_master(p).float().clone()
+    if kind.startswith("qkv"):
+      j, third = int(kind[3]), w.shape[0]
+      full = out.setdefault(key, torch.zeros((3 * third,) + tuple(w.shape[1:])))
+      full[j * third:(j + 1) * third] = w
+      continue
+    if kind == "patch3d":
+      P, T = int(cfg.patch_size_for_vit), int(cfg.temporal_patch_size_for_vit)
+      out[key] = w.view(w.shape[0], T, P, P, -1).permute(0, 4, 1, 2, 3).contiguous()
+      continue
     if kind.startswith("experts:"):
       _store_experts(out, key, kind.split(":")[1], w, cfg)
       continue

@@ -246,3 +246,36 @@ def test_video_temporal_patches_match_huggingface_and_reach_the_decoder():
     a = model.forward(toks, images=pix[None], image_mask=mask[None])
     b = model.forward(toks, images=pix[None] * 0.5, image_mask=mask[None])
   assert torch.isfinite(a).all() and not torch.allclose(a, b)
+
+
+def test_checkpoint_converter_maps_the_vision_tower_both_ways():
+  """HuggingFace `model.visual.*` tensors -> the tower's parameters (fused qkv cut in three, 3-D patch convolution flattened) and
+  back; the converted tower reproduces the HuggingFace tower's output."""
+  pytest.importorskip("transformers")
+  from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionConfig, Qwen3VLVisionModel
+  from maxtext_b200.checkpoint_conversion import hf as conv
+  from maxtext_b200.models.transformer import Transformer
+  cfg = tiny_config("qwen3-vl-2b", VIT + ["out_hidden_size_for_vit=64"])
+  hf_cfg = Qwen3VLVisionConfig(depth=3, hidden_size=32, hidden_act="gelu_pytorch_tanh", intermediate_size=48, num_heads=4, in_channels=3, patch_size=4,
+                               spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=36, deepstack_visual_indexes=[0, 1])
+  hf_cfg._attn_implementation = "eager"
+  torch.manual_seed(0)
+  hf = Qwen3VLVisionModel(hf_cfg).float().eval()
+  for p in hf.parameters():
+    torch.nn.init.normal_(p, std=0.2)
+  state = {"model.visual." + k: v.detach() for k, v in hf.state_dict().items()}
+  model = Transformer(cfg, None, torch.device("cpu"))
+  model.store.initialize(seed=0)
+  missing = conv.to_maxtext(state, model.store, cfg)
+  vis = {p.name for p in model.vision_params}
+  assert not (vis & set(missing)), sorted(vis & set(missing))[:5]            # every tower tensor found its source (the text side has none here)
+  images = torch.randn(1, 1, 3, 16, 24)
+  with torch.no_grad():
+    got = model.vision(images)
+    x, rc, gh, gw = model.vision.patches(images.reshape(1, 3, 16, 24))
+    flat = x.reshape(gh * gw, 2, 4, 4, 3).permute(0, 4, 1, 2, 3).reshape(gh * gw, -1)
+    want = hf(flat, grid_thw=torch.tensor([[1, gh, gw]])).pooler_output.view(got.shape)
+  assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+  back = conv.to_hf(model.store, cfg)
+  for k, v in state.items():
+    assert k in back and torch.allclose(back[k].reshape(v.shape), v.float(), atol=1e-6), k
