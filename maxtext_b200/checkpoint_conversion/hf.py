@@ -167,7 +167,7 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
     return _vision_name(path)
   pre = f"model.layers.{L}." if L is not None else ""
   blk = cfg.decoder_block
-  sandwich = blk in ("gemma2", "gemma3")
+  sandwich = blk in ("gemma2", "gemma3", "gemma4")
   table = {
       "token_embedder/embedding": ("model.embed_tokens.weight", "embed"),
       "decoder/decoder_norm/scale": ("model.norm.weight", "norm"),
@@ -225,6 +225,17 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
       "mlp/shared_expert_gate/kernel": (pre + "mlp.shared_expert_gate.weight", "linear"),
       "GptOssMlp/gate/kernel": (pre + "mlp.router.weight", "linear"),
       "GptOssMlp/gate/bias": (pre + "mlp.router.bias", "vec"),
+      # gemma4: learned layer scalar; MoE layers keep a dense MLP (stored as the block's shared experts) next to the routed experts
+      "layer_scalar": (pre + "layer_scalar", "vec"),
+      "mlp/moe_block/shared_experts/wi_0/kernel": (pre + "mlp.gate_proj.weight", "linear"),
+      "mlp/moe_block/shared_experts/wi_1/kernel": (pre + "mlp.up_proj.weight", "linear"),
+      "mlp/moe_block/shared_experts/wo/kernel": (pre + "mlp.down_proj.weight", "linear"),
+      "mlp/moe_block/MoeBlock_0/gate/kernel": (pre + "router.proj.weight", "linear"),
+      "mlp/moe_block/MoeBlock_0/per_expert_scale": (pre + "router.per_expert_scale", "vec"),
+      "mlp/pre_forward_scale_2": (pre + "router.scale", "vec"),
+      "mlp/pre_feedforward_layernorm_2/scale": (pre + "pre_feedforward_layernorm_2.weight", "norm"),
+      "mlp/post_feedforward_layernorm_1/scale": (pre + "post_feedforward_layernorm_1.weight", "norm"),
+      "mlp/post_feedforward_layernorm_2/scale": (pre + "post_feedforward_layernorm_2.weight", "norm"),
       "Llama4MoEBlock_0/MoeBlock_0/gate/kernel": (pre + "feed_forward.router.weight", "linear"),
       "Llama4MoEBlock_0/shared_experts/wi_0/kernel": (pre + "feed_forward.shared_expert.gate_proj.weight", "linear"),
       "Llama4MoEBlock_0/shared_experts/wi_1/kernel": (pre + "feed_forward.shared_expert.up_proj.weight", "linear"),
@@ -245,7 +256,7 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
 
 
 def _expert_style(cfg) -> str:
-  return {"mixtral": "mixtral", "gpt_oss": "gpt_oss", "llama4": "llama4"}.get(cfg.decoder_block, "split")
+  return {"mixtral": "mixtral", "gpt_oss": "gpt_oss", "llama4": "llama4", "gemma4": "gemma4"}.get(cfg.decoder_block, "split")
 
 
 def _load_experts(hf_state: dict, pre: str, part: str, cfg) -> torch.Tensor | None:
@@ -278,6 +289,16 @@ def _load_experts(hf_state: dict, pre: str, part: str, cfg) -> torch.Tensor | No
       return None
     half = gu.shape[2] // 2
     return (gu.float()[:, :, :half] if part == "gate" else gu.float()[:, :, half:]).transpose(1, 2).contiguous()
+  if style == "gemma4":
+    # experts sit directly under the layer: gate_up_proj [E, 2*out, in] (gate | up halves), down_proj [E, out, in]
+    if part == "down":
+      d = hf_state.get(pre + "experts.down_proj")
+      return None if d is None else d.float()
+    gu = hf_state.get(pre + "experts.gate_up_proj")
+    if gu is None:
+      return None
+    half = gu.shape[1] // 2
+    return gu.float()[:, :half] if part == "gate" else gu.float()[:, half:]
   if style == "mixtral":
     per = pre + "block_sparse_moe.experts.{e}." + {"gate": "w1", "up": "w3", "down": "w2"}[part] + ".weight"
   else:
@@ -298,6 +319,14 @@ def _load_experts(hf_state: dict, pre: str, part: str, cfg) -> torch.Tensor | No
 def _store_experts(out: dict, pre: str, part: str, w: torch.Tensor, cfg):
   """Inverse of `_load_experts`, writing the layout hub checkpoints of the family use."""
   style = _expert_style(cfg)
+  if style == "gemma4":
+    if part == "down":
+      out[pre + "experts.down_proj"] = w.contiguous()
+    else:
+      E_, half, d_in = w.shape
+      gu = out.setdefault(pre + "experts.gate_up_proj", torch.zeros(E_, 2 * half, d_in))
+      (gu[:, :half] if part == "gate" else gu[:, half:]).copy_(w)
+    return
   if style in ("gpt_oss", "llama4"):
     base = pre + ("mlp.experts." if style == "gpt_oss" else "feed_forward.experts.")
     if part == "down":
@@ -330,12 +359,12 @@ def _norm_offset(cfg) -> float:
 
 def _embed_scale(cfg) -> float:
   # Gemma: HF multiplies the looked-up embedding by sqrt(hidden) at run time; here the factor lives in the table
-  return math.sqrt(cfg.emb_dim) if cfg.decoder_block in ("gemma", "gemma2", "gemma3") else 1.0
+  return math.sqrt(cfg.emb_dim) if cfg.decoder_block in ("gemma", "gemma2", "gemma3", "gemma4") else 1.0
 
 
 def _q_scale(cfg) -> float:
   """Factor folded into the stored query projection: 1/sqrt(head_dim) unless the family scales at run time."""
-  if cfg.use_qk_norm or cfg.attention_type == "mla" or cfg.decoder_block in ("gemma3", "qwen3", "qwen3_moe", "qwen3_custom_moe", "olmo3",
+  if cfg.use_qk_norm or cfg.attention_type == "mla" or cfg.decoder_block in ("gemma3", "gemma4", "qwen3", "qwen3_moe", "qwen3_custom_moe", "olmo3",
                                                                               "llama4", "gpt_oss", "qwen3_next", "qwen3_5"):
     return 1.0
   return 1.0 / math.sqrt(cfg.head_dim)

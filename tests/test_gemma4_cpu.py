@@ -152,3 +152,28 @@ def test_vision_tower_matches_huggingface():
     out = tower(images[None])
   assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
   assert out.shape == (1, 2, 6, cfg.emb_dim) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_checkpoint_converter_covers_the_text_model(moe):
+  """`to_maxtext` fills every decoder parameter from the HuggingFace state dict exactly as the hand-written loader of this file
+  does, and `to_hf` gives the HuggingFace tensors back."""
+  pytest.importorskip("transformers")
+  from maxtext_b200.checkpoint_conversion import hf as conv
+  hf = _hf(moe)
+  _, model_a = _ours(moe)
+  _, model_b = _ours(moe)
+  _load(model_a, hf, moe)
+  missing = conv.to_maxtext(hf.state_dict(), model_b.store, model_b.config)
+  assert not missing, missing[:8]
+  for name, p in model_a.store.params.items():
+    a, b = model_a.store.full_master(p), model_b.store.full_master(model_b.store.params[name])
+    assert torch.allclose(a, b, atol=1e-6), name
+  back = conv.to_hf(model_b.store, model_b.config)
+  sd = hf.state_dict()
+  for k, v in sd.items():
+    if k in back:
+      assert torch.allclose(back[k].reshape(v.shape), v.float(), atol=1e-5), k
+  assert {"model.embed_tokens.weight", "model.layers.0.layer_scalar", "model.layers.0.self_attn.q_proj.weight"} <= set(back)
+  if moe:
+    assert "model.layers.0.experts.gate_up_proj" in back and "model.layers.0.router.scale" in back
