@@ -39,8 +39,9 @@ def test_greedy_decode_matches_full_forward(model):
   assert seq == want
 
 
-def test_chunked_prefill_equals_prefill():
-  eng, cfg = _engine()
+@pytest.mark.parametrize("model", ["llama3-8b", "deepseek4-tiny"])
+def test_chunked_prefill_equals_prefill(model):
+  eng, cfg = _engine(model)
   prompt = torch.randint(1, cfg.vocab_size, (13,))
   a, _ = eng.prefill(prompt, 13)
   b, _ = eng.prefill_chunked(prompt, chunk=4)
