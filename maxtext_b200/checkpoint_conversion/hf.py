@@ -95,6 +95,30 @@ def _llama4_vision_name(path: str) -> tuple[str, str] | None:
   return pre + sub[mod] + (".bias" if leaf == "bias" else ".weight"), ("linear" if leaf == "kernel" else "vec")
 
 
+def _qwen_audio_name(path: str) -> tuple[str, str] | None:
+  """Qwen3-Omni audio tower (HF: thinker.audio_tower.*): convolutions, encoder layers with biased projections, output head."""
+  import re
+  a = "thinker.audio_tower."
+  m = re.match(r"audio_encoder/(conv2d[123]|conv_out)/(kernel|bias)$", path)
+  if m:
+    return a + m.group(1) + (".weight" if m.group(2) == "kernel" else ".bias"), ("linear" if m.group(1) == "conv_out" else "vec")
+  m = re.match(r"audio_encoder/ln_post/(scale|bias)$", path)
+  if m:
+    return a + "ln_post." + ("weight" if m.group(1) == "scale" else "bias"), "vec"
+  m = re.match(r"audio_projector/(proj[12])/(kernel|bias)$", path)
+  if m:
+    return a + m.group(1) + (".weight" if m.group(2) == "kernel" else ".bias"), ("linear" if m.group(2) == "kernel" else "vec")
+  m = re.match(r"audio_encoder/layers_(\d+)/(.+)/(scale|bias|kernel)$", path)
+  if not m:
+    return None
+  pre, mod, leaf = a + f"layers.{m.group(1)}.", m.group(2), m.group(3)
+  sub = {"self_attn_layer_norm": "self_attn_layer_norm", "final_layer_norm": "final_layer_norm", "self_attn/query": "self_attn.q_proj",
+         "self_attn/key": "self_attn.k_proj", "self_attn/value": "self_attn.v_proj", "self_attn/out": "self_attn.out_proj", "fc1": "fc1", "fc2": "fc2"}.get(mod)
+  if sub is None:
+    return None
+  return pre + sub + (".bias" if leaf == "bias" else ".weight"), ("linear" if leaf == "kernel" else "vec")
+
+
 def _qwen_vision_name(path: str) -> tuple[str, str] | None:
   """Qwen3-VL vision tower (HF: model.visual.*). The fused qkv of the HF blocks is cut into our query / key / value (kinds
   qkv0..2 name the third), the 3-D patch convolution becomes a matrix over (t, py, px, c) features (kind patch3d)."""
@@ -165,6 +189,8 @@ def _hf_name(pdef, cfg) -> tuple[str, str] | None:
   path, L = _locate(pdef, cfg)
   if path.startswith(("vision_encoder/", "vision_projector/")):
     return _vision_name(path)
+  if path.startswith(("audio_encoder/", "audio_projector/")):
+    return _qwen_audio_name(path)
   pre = f"model.layers.{L}." if L is not None else ""
   blk = cfg.decoder_block
   sandwich = blk in ("gemma2", "gemma3", "gemma4")

@@ -175,3 +175,34 @@ def test_decode_cli_takes_an_audio_clip(tmp_path):
     fh.writeframes((sig * 0).tobytes())
   other = decode(cfg.replace(audio_path=str(silent)), engine=eng)
   assert isinstance(with_audio, str) and isinstance(other, str)
+
+
+def test_checkpoint_converter_maps_the_audio_tower_both_ways():
+  pytest.importorskip("transformers")
+  from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeAudioEncoderConfig
+  from transformers.models.qwen3_omni_moe.modeling_qwen3_omni_moe import Qwen3OmniMoeAudioEncoder
+  from maxtext_b200.checkpoint_conversion import hf as conv
+  from maxtext_b200.models.transformer import Transformer
+  cfg = _omni(["n_window_for_audio=50", "n_window_infer_for_audio=200"])
+  hf_cfg = Qwen3OmniMoeAudioEncoderConfig(num_mel_bins=16, encoder_layers=1, encoder_attention_heads=2, encoder_ffn_dim=48, d_model=32,
+                                          activation_function="gelu", scale_embedding=False, max_source_positions=64, n_window=50,
+                                          output_dim=cfg.emb_dim, n_window_infer=200, conv_chunksize=4, downsample_hidden_size=8)
+  hf_cfg._attn_implementation = "eager"
+  torch.manual_seed(0)
+  hf = Qwen3OmniMoeAudioEncoder(hf_cfg).float().eval()
+  with torch.no_grad():
+    for p in hf.parameters():
+      p.copy_(torch.randn_like(p) * 0.2)
+  state = {"thinker.audio_tower." + k: v.detach() for k, v in hf.state_dict().items() if "positional_embedding" not in k}
+  model = Transformer(cfg, None, torch.device("cpu"))
+  model.store.initialize(seed=0)
+  missing = set(conv.to_maxtext(state, model.store, cfg))
+  assert not ({p.name for p in model.audio_params} & missing), sorted({p.name for p in model.audio_params} & missing)[:5]
+  feats = torch.randn(16, 100)
+  with torch.no_grad():
+    got = model.audio(feats)
+    want = hf(feats, feature_lens=torch.tensor([100])).last_hidden_state          # one window: no mask needed on the HF side
+  assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), float((got - want).abs().max())
+  back = conv.to_hf(model.store, cfg)
+  for k, v in state.items():
+    assert k in back and torch.allclose(back[k].reshape(v.shape), v.float(), atol=1e-6), k
