@@ -38,7 +38,10 @@ def run(config, engine: MaxEngine | None = None) -> dict:
         continue
       toks = torch.randint(1, config.vocab_size, (n,))
       dt = _time(lambda: eng.prefill(toks, n), iters, cuda)
-      out["prefill"][n] = {"ms": dt * 1e3, "tokens_per_s": n / dt}
+      from ..utils import flops
+      n_par = sum(p.pdef.numel for p in eng.model.all_params())
+      tf = flops.prefill_tflops_per_device(config, n_par, n)[0]
+      out["prefill"][n] = {"ms": dt * 1e3, "tokens_per_s": n / dt, "tflops": tf, "tflops_per_s": tf / dt}
   if "generate" in stages:
     slots = max(1, int(config.per_device_batch_size))
     state = eng.init_decode_state(slots)

@@ -117,3 +117,11 @@ def _block(c, bp, B, S, n_act):
 def tokens_per_device(c, batch_per_device: float | None = None) -> float:
   B = float(batch_per_device if batch_per_device is not None else c.per_device_batch_size)
   return B * c.max_target_length * c.gradient_accumulation_steps
+
+
+def prefill_tflops_per_device(c, num_parameters: int, prefill_length: int, num_devices: int = 1) -> tuple[float, float, float]:
+  """(total, weight, causal attention) TFLOPs of one prefill pass (src/maxtext/utils/maxtext_utils.py:1396-1420): two FLOPs per
+  parameter and token, plus the causal half of the attention products."""
+  weight = 2.0 * num_parameters * prefill_length / num_devices / 1e12
+  attention = 4.0 * c.num_query_heads * c.num_decoder_layers * c.head_dim * prefill_length ** 2 / num_devices / 1e12 / 2
+  return weight + attention, weight, attention
