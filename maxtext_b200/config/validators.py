@@ -284,6 +284,13 @@ def check_misc(t):
     for flag, off in (("use_ring_of_experts", False),):            # random routing works on one rank here, the ring needs peers
       if _g(t, flag, off) != off:
         _fail(f"When EP rank is 1, {flag} must be {off} (was {t.get(flag)}).")
+  if _g(t, "use_batch_split_schedule", False):
+    pp = max(1, int(_g(t, "ici_pipeline_parallelism", 1) or 1)) * max(1, int(_g(t, "dcn_pipeline_parallelism", 1) or 1))
+    if pp > 1:
+      _fail("`use_batch_split_schedule=True` is not implemented under pipeline parallelism (the pipeline already runs micro-batches).")
+    split = int(_g(t, "batch_split_factor", 1) or 1)
+    if split < 1:
+      _fail(f"`batch_split_factor` must be >= 1, got {split}.")
   dpo = t.get("dpo") if isinstance(t.get("dpo"), dict) else None
   if _g(t, "use_dpo", False) and dpo and dpo.get("max_prompt_length") is not None:
     if int(dpo["max_prompt_length"]) >= int(t["max_target_length"]):

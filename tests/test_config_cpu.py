@@ -158,6 +158,7 @@ REJECTED = [
     (["load_full_state_path=/tmp/none", "enable_checkpointing=false"], "enable_checkpointing=True to load"),
     (["enable_multi_tier_checkpointing=true", "local_checkpoint_directory=/tmp/x", "local_checkpoint_period=2"], "Exactly one of"),
     (["elastic_backup_kind=tape"], "elastic_backup_kind"),
+    (["use_batch_split_schedule=true", "batch_split_factor=0"], "batch_split_factor"),
     (["context_parallel_strategy=spiral"], "context_parallel_strategy"),
     (["sharding_tolerance=1.5"], "sharding_tolerance"),
     (["indexer_cutoff_threshold=device"], "indexer_cutoff_threshold"),
