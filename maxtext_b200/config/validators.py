@@ -288,7 +288,7 @@ def check_misc(t):
     pp = max(1, int(_g(t, "ici_pipeline_parallelism", 1) or 1)) * max(1, int(_g(t, "dcn_pipeline_parallelism", 1) or 1))
     if pp > 1:
       _fail("`use_batch_split_schedule=True` is not implemented under pipeline parallelism (the pipeline already runs micro-batches).")
-    split = int(_g(t, "batch_split_factor", 1) or 1)
+    split = int(_g(t, "batch_split_factor", 1))
     if split < 1:
       _fail(f"`batch_split_factor` must be >= 1, got {split}.")
   dpo = t.get("dpo") if isinstance(t.get("dpo"), dict) else None
